@@ -1,0 +1,211 @@
+// Embedding gather, residual add + RMS norm, SiLU-multiply, and the fused
+// per-head norm + rotary encoding + cache write.  Every kernel is a template
+// over the element type (float: the true 32-bit path; bfloat16: serving) and
+// does its arithmetic in float32.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------------
+// out[t, :] = float(table[ids[t], :])      (reference src/layers/ops/embedding.py:28-44)
+// The residual stream is float32 in both paths.  An id outside the table gives NaN rows.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                                 float* __restrict__ out, int H, int V) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  float* dst = out + (size_t)t * H;
+  if (id < 0 || id >= V) {
+    for (int h = threadIdx.x; h < H; h += blockDim.x) dst[h] = __int_as_float(0x7fc00000);
+    return;
+  }
+  const T* src = table + (size_t)id * H;
+  for (int h = threadIdx.x; h < H; h += blockDim.x) dst[h] = to_f32(src[h]);
+}
+
+extern "C" int qe_embedding(const int* ids, const void* table, float* out, int T, int H, int V,
+                            int dtype, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (dtype == QE_DTYPE_F32)
+    embedding_kernel<float><<<T, 256, 0, stream>>>(ids, (const float*)table, out, H, V);
+  else if (dtype == QE_DTYPE_BF16)
+    embedding_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, H, V);
+  else QE_REFUSE("embedding: unknown dtype %d", dtype);
+  QE_CHECK_LAUNCH("embedding");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// x = resid[row] (+ delta[row]);  out = x * rsqrt(mean(x^2) + eps) * w
+// (reference src/layers/ops/layernorm.py:50-88).  Without `rows` the sum is written back
+// to the float32 stream; with `rows` (the rows whose logits are wanted) row n of the output
+// comes from row rows[n] and the stream is left alone.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                   const int* __restrict__ rows, const float* __restrict__ w,
+                                   float eps, T* __restrict__ out, int H) {
+  __shared__ float scratch[33];
+  const int n = blockIdx.x;
+  const int src_row = rows ? rows[n] : n;
+  float* r = resid + (size_t)src_row * H;
+  const T* d = delta ? delta + (size_t)src_row * H : nullptr;
+  T* o = out + (size_t)n * H;
+  float ss = 0.f;
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    float x = r[h];
+    if (d) x += to_f32(d[h]);
+    if (d && !rows) r[h] = x;
+    ss += x * x;
+  }
+  ss = block_sum(ss, scratch);
+  const float rstd = rsqrtf(ss / (float)H + eps);
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    float x = r[h];
+    if (d && rows) x += to_f32(d[h]);
+    o[h] = from_f32<T>(x * rstd * w[h]);
+  }
+}
+
+extern "C" int qe_add_rmsnorm(float* resid, const void* delta, const int* rows, const float* w,
+                              float eps, void* out, int n_rows, int H, int dtype, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
+  if (dtype == QE_DTYPE_F32)
+    add_rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(resid, (const float*)delta, rows, w, eps, (float*)out, H);
+  else if (dtype == QE_DTYPE_BF16)
+    add_rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(resid, (const __nv_bfloat16*)delta, rows, w, eps, (__nv_bfloat16*)out, H);
+  else QE_REFUSE("add_rmsnorm: unknown dtype %d", dtype);
+  QE_CHECK_LAUNCH("add_rmsnorm");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i],  silu(g) = g / (1 + exp(-g))
+// (reference src/layers/fused_ops/silumul.py:50-53), all in float32, rounded once.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I, size_t total) {
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = e / I;
+    const int i = (int)(e - t * I);
+    const float g = to_f32(gate_up[t * 2 * I + i]);
+    const float u = to_f32(gate_up[t * 2 * I + I + i]);
+    out[e] = from_f32<T>(g / (1.f + expf(-g)) * u);
+  }
+}
+
+extern "C" int qe_silu_mul(const void* gate_up, void* out, int T, int I, int dtype, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const size_t total = (size_t)T * I;
+  const int threads = 256;
+  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  if (dtype == QE_DTYPE_F32)
+    silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, I, total);
+  else if (dtype == QE_DTYPE_BF16)
+    silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, I, total);
+  else QE_REFUSE("silu_mul: unknown dtype %d", dtype);
+  QE_CHECK_LAUNCH("silu_mul");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// One warp per (token, head).  For q and k heads: optional RMS norm over the head
+// (src/layers/ops/layernorm.py:127-134), then optional half-split rotation by
+// angle = position * inv_freq[j] computed in float32 (src/layers/ops/rope.py:37-121), written
+// back in place; k is also written to the token's slot of the cache, v is copied there.
+// Cache layout of one layer: [page][K or V][kv head][offset in page][D].
+// ---------------------------------------------------------------------------------------
+#define QKR_MAX_D 512
+template <typename T>
+__global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ q, T* __restrict__ k, const T* __restrict__ v,
+                                             long q_stride, long k_stride, long v_stride,
+                                             const int* __restrict__ positions,
+                                             const float* __restrict__ qw, const float* __restrict__ kw, float eps,
+                                             const float* __restrict__ inv_freq, int rotary_dim,
+                                             T* __restrict__ pages, const int* __restrict__ slot_mapping,
+                                             int T_tokens, int Hq, int Hkv, int D, int page_size, int write_kv) {
+  extern __shared__ float smem[];
+  const int warps_per_block = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads_total = Hq + 2 * Hkv;
+  const long item = (long)blockIdx.x * warps_per_block + warp;
+  if (item >= (long)T_tokens * heads_total) return;
+  const int t = (int)(item / heads_total);
+  const int head = (int)(item % heads_total);
+  float* buf = smem + (size_t)warp * D;
+
+  if (head >= Hq + Hkv) {           // a value head: copy into the cache
+    if (!write_kv) return;
+    const int h = head - Hq - Hkv;
+    const int slot = slot_mapping[t];
+    const int page = slot / page_size, off = slot % page_size;
+    const T* src = v + (size_t)t * v_stride + (size_t)h * D;
+    T* dst = pages + ((((size_t)page * 2 + 1) * Hkv + h) * page_size + off) * D;
+    for (int d = lane; d < D; d += 32) dst[d] = src[d];
+    return;
+  }
+  const bool is_q = head < Hq;
+  const int h = is_q ? head : head - Hq;
+  T* x = is_q ? q + (size_t)t * q_stride + (size_t)h * D : k + (size_t)t * k_stride + (size_t)h * D;
+  const float* w = is_q ? qw : kw;
+  float ss = 0.f;
+  for (int d = lane; d < D; d += 32) {
+    const float val = to_f32(x[d]);
+    buf[d] = val;
+    ss += val * val;
+  }
+  if (w) {
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)D + eps);
+    for (int d = lane; d < D; d += 32) buf[d] = buf[d] * rstd * w[d];
+  }
+  __syncwarp();
+  T* cache_dst = nullptr;
+  if (!is_q && write_kv) {
+    const int slot = slot_mapping[t];
+    const int page = slot / page_size, off = slot % page_size;
+    cache_dst = pages + ((((size_t)page * 2 + 0) * Hkv + h) * page_size + off) * D;
+  }
+  const int half = rotary_dim >> 1;
+  const float pos = (float)positions[t];
+  for (int d = lane; d < D; d += 32) {
+    float o = buf[d];
+    if (inv_freq && d < rotary_dim) {
+      const int j = d < half ? d : d - half;
+      const float ang = pos * inv_freq[j];
+      float s, c;
+      sincosf(ang, &s, &c);
+      o = d < half ? c * buf[d] - s * buf[d + half] : s * buf[d - half] + c * buf[d];
+    }
+    const T r = from_f32<T>(o);
+    x[d] = r;
+    if (cache_dst) cache_dst[d] = r;
+  }
+}
+
+extern "C" int qe_qk_norm_rope_kv_write(void* q, void* k, const void* v, long q_stride, long k_stride, long v_stride,
+                                        const int* positions, const float* qw, const float* kw, float eps,
+                                        const float* inv_freq, int rotary_dim, void* pages,
+                                        const int* slot_mapping, int T, int Hq, int Hkv, int D, int page_size,
+                                        int write_kv, int dtype, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (D > QKR_MAX_D) QE_REFUSE("qk_norm_rope_kv_write: head_dim %d is above %d", D, QKR_MAX_D);
+  if (inv_freq && (rotary_dim % 2 || rotary_dim > D || rotary_dim <= 0))
+    QE_REFUSE("qk_norm_rope_kv_write: rotary_dim %d does not fit head_dim %d", rotary_dim, D);
+  if (write_kv && (!pages || !slot_mapping)) QE_REFUSE("qk_norm_rope_kv_write: cache write without cache");
+  const int warps = 4;
+  const long items = (long)T * (Hq + 2 * Hkv);
+  const int blocks = (int)((items + warps - 1) / warps);
+  const size_t smem = (size_t)warps * D * sizeof(float);
+  if (dtype == QE_DTYPE_F32)
+    qk_norm_rope_kv_write_kernel<float><<<blocks, warps * 32, smem, stream>>>(
+        (float*)q, (float*)k, (const float*)v, q_stride, k_stride, v_stride, positions, qw, kw, eps, inv_freq,
+        rotary_dim, (float*)pages, slot_mapping, T, Hq, Hkv, D, page_size, write_kv);
+  else if (dtype == QE_DTYPE_BF16)
+    qk_norm_rope_kv_write_kernel<__nv_bfloat16><<<blocks, warps * 32, smem, stream>>>(
+        (__nv_bfloat16*)q, (__nv_bfloat16*)k, (const __nv_bfloat16*)v, q_stride, k_stride, v_stride, positions, qw, kw,
+        eps, inv_freq, rotary_dim, (__nv_bfloat16*)pages, slot_mapping, T, Hq, Hkv, D, page_size, write_kv);
+  else QE_REFUSE("qk_norm_rope_kv_write: unknown dtype %d", dtype);
+  QE_CHECK_LAUNCH("qk_norm_rope_kv_write");
+  return 0;
+}

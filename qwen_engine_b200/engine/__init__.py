@@ -1,0 +1,3 @@
+from .runner import ModelRunner, StepEntry
+
+__all__ = ["ModelRunner", "StepEntry"]

@@ -1,0 +1,184 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+A step takes any mixture of prompt portions and single decoded tokens, cut
+anywhere.  It runs only the tokens it is given, as one flat batch, against
+what earlier steps left in the cache, and returns float32 logits at the places
+asked for.  The reference runs either whole prompts or single tokens, never
+both, builds its index tensors with per-token device writes and computes
+logits for every row (src/engine/executor.py:56-103, 105-208;
+src/models/qwen3/model.py:420-422); here all of a step's index data is packed
+on the host and copied once.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import torch
+
+from .. import ops
+from ..cache.manager import CacheManager, RequestCache
+from ..cache.page_pool import OutOfPages
+from ..models.decoder import DecoderModel
+from ..parts.base import Arena, GroupStepView, StepContext
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens and the places among them
+    (0-based within ``tokens``) whose logits are wanted."""
+
+    cache: RequestCache
+    tokens: Sequence[int]
+    want: Sequence[int] = field(default_factory=tuple)
+
+
+class _Pack:
+    """Named int32 arrays laid out in one buffer, each starting on a 16-byte boundary."""
+
+    def __init__(self):
+        self.parts: list[tuple[str, int, int]] = []
+        self.data: list[int] = []
+
+    def add(self, name: str, values: Sequence[int]) -> None:
+        pad = (-len(self.data)) % 4
+        self.data.extend([0] * pad)
+        self.parts.append((name, len(self.data), len(values)))
+        self.data.extend(values)
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, cache: CacheManager, device, dtype: torch.dtype,
+                 max_positions: Optional[int] = None):
+        self.model = model
+        self.cache = cache
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.arena = Arena(self.device)
+        self.max_positions = max_positions if max_positions is not None else model.layout.max_positions
+        self._on_gpu = self.device.type == "cuda"
+        self._host: list[Optional[torch.Tensor]] = [None, None]
+        self._host_free: list[Optional[torch.cuda.Event]] = [None, None]
+        self._dev_meta: Optional[torch.Tensor] = None
+        self._flip = 0
+        self.num_steps = 0
+        self.num_tokens_run = 0
+
+    # ---- metadata transfer ----------------------------------------------------------------
+    def _upload(self, pack: _Pack) -> dict[str, torch.Tensor]:
+        n = len(pack.data)
+        src = torch.tensor(pack.data, dtype=torch.int32)
+        if not self._on_gpu:
+            dev = src.to(self.device)
+        else:
+            i = self._flip
+            self._flip ^= 1
+            if self._host[i] is None or self._host[i].numel() < n:
+                self._host[i] = torch.empty(max(4096, 2 * n), dtype=torch.int32, pin_memory=True)
+                self._host_free[i] = None
+            if self._host_free[i] is not None:
+                self._host_free[i].synchronize()      # the copy that last read this buffer is done
+            self._host[i][:n].copy_(src)
+            if self._dev_meta is None or self._dev_meta.numel() < n:
+                self._dev_meta = torch.empty(max(4096, 2 * n), dtype=torch.int32, device=self.device)
+            dev = self._dev_meta[:n]
+            dev.copy_(self._host[i][:n], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            self._host_free[i] = ev
+        return {name: dev[off:off + cnt] for name, off, cnt in pack.parts}
+
+    # ---- the step -------------------------------------------------------------------------
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run one batch.  Returns float32 logits [wanted places, vocab] in the order
+        of the entries and of each entry's ``want`` (None if nothing is wanted).
+        The tensor lives in the step's scratch memory: it is valid until the next step."""
+        entries = [e for e in entries if len(e.tokens) > 0]
+        if not entries:
+            return None
+        cache = self.cache
+        vocab = self.model.layout.vocab_size
+        appended: list[RequestCache] = []
+        try:
+            for e in entries:
+                for t in e.tokens:
+                    if not (0 <= int(t) < vocab):
+                        raise ValueError(f"token id {t} of request {e.cache.req_id!r} is outside the vocabulary (0..{vocab - 1})")
+                end = e.cache.num_tokens + len(e.tokens)
+                if self.max_positions is not None and end > self.max_positions:
+                    raise ValueError(f"request {e.cache.req_id!r} would reach {end} tokens, beyond "
+                                     f"max_position_embeddings = {self.max_positions}")
+                for w in e.want:
+                    if not (0 <= int(w) < len(e.tokens)):
+                        raise ValueError(f"wanted place {w} is outside the {len(e.tokens)} tokens of request {e.cache.req_id!r}")
+                cache.append(e.cache, e.tokens)
+                appended.append(e.cache)
+        except (OutOfPages, ValueError):
+            for rc in appended:
+                cache.abort_pending(rc)
+            raise
+
+        token_ids: list[int] = []
+        positions: list[int] = []
+        cu_q = [0]
+        ctx_lens: list[int] = []
+        slot_ids: list[int] = []
+        logit_rows: list[int] = []
+        q_lens: list[int] = []
+        for e in entries:
+            rc = e.cache
+            n, c = len(e.tokens), rc.num_tokens
+            base = cu_q[-1]
+            token_ids.extend(int(t) for t in e.tokens)
+            positions.extend(range(c, c + n))
+            cu_q.append(base + n)
+            ctx_lens.append(c)
+            slot_ids.append(rc.state_slot)
+            q_lens.append(n)
+            logit_rows.extend(base + int(w) for w in e.want)
+        T, R, N = cu_q[-1], len(entries), len(logit_rows)
+
+        pack = _Pack()
+        pack.add("token_ids", token_ids)
+        pack.add("positions", positions)
+        pack.add("cu_q", cu_q)
+        pack.add("ctx_lens", ctx_lens)
+        pack.add("slot_ids", slot_ids)
+        pack.add("logit_rows", logit_rows)
+        max_blocks: dict[int, int] = {}
+        for g in cache.paged_groups:
+            mb = max(len(e.cache.tables[g.index]) for e in entries)
+            max_blocks[g.index] = mb
+            flat: list[int] = []
+            slots: list[int] = []
+            for e in entries:
+                table = e.cache.tables[g.index]
+                flat.extend(table)
+                flat.extend([-1] * (mb - len(table)))
+                slots.extend(cache.slot_mapping(e.cache, g.index))
+            pack.add(f"bt{g.index}", flat)
+            pack.add(f"sm{g.index}", slots)
+        plan = ops.plan_attention(q_lens, ctx_lens, cache.page_size)
+        for name, values in plan.items():
+            pack.add("plan_" + name, values)
+        dev = self._upload(pack)
+
+        cache.run_page_copies()
+        cache.zero_fresh_state([e.cache for e in entries])
+
+        groups = {g.index: GroupStepView(dev[f"bt{g.index}"].view(R, max_blocks[g.index]),
+                                         dev[f"sm{g.index}"], max_blocks[g.index])
+                  for g in cache.paged_groups}
+        self.arena.reset()
+        ctx = StepContext(
+            num_tokens=T, num_reqs=R, dtype=self.dtype, device=self.device, page_size=cache.page_size,
+            token_ids=dev["token_ids"], positions=dev["positions"], cu_q=dev["cu_q"],
+            ctx_lens=dev["ctx_lens"], slot_ids=dev["slot_ids"], logit_rows=dev["logit_rows"],
+            num_logit_rows=N, groups=groups, q_lens_host=q_lens, ctx_lens_host=ctx_lens,
+            arena=self.arena, attn_plan={k: dev["plan_" + k] for k in plan})
+        logits = self.model.forward(ctx, cache)
+        for e in entries:
+            cache.commit(e.cache)
+        self.num_steps += 1
+        self.num_tokens_run += T
+        return logits

@@ -1,0 +1,253 @@
+"""The engine's operations: thin Python fronts of the hand-written CUDA kernels.
+
+Every function works on CUDA tensors, writes into an output the caller
+provides, and launches on torch's current stream.  There is no CPU path and no
+library fallback: without the compiled extension, or with a tensor that is not
+on a CUDA device, a call raises.  The plain PyTorch restatement of each
+operation lives with the tests (tests/ref_ops.py).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from ..csrc import build as _build
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+_lib = None
+
+ATTN_TILE_Q = 16        # queries per work item of the generic attention kernel
+
+
+class ExtensionMissing(RuntimeError):
+    """The CUDA extension could not be built or loaded."""
+
+
+class KernelRefused(ValueError):
+    """A kernel refused its arguments (a size it does not take, a wrong dtype)."""
+
+
+def lib():
+    """The loaded extension; builds it at the first call."""
+    global _lib
+    if _lib is None:
+        try:
+            path = _build.library_path()
+            handle = ctypes.CDLL(path)
+        except Exception as e:                       # noqa: BLE001 - re-raised with context
+            raise ExtensionMissing(
+                f"qwen_engine_b200 needs its CUDA extension and could not get it: {e}") from e
+        handle.qe_last_error.restype = ctypes.c_char_p
+        _lib = handle
+    return _lib
+
+
+def extension_path() -> str:
+    return _build.library_path()
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    if t is None:
+        return ctypes.c_void_p(0)
+    if not t.is_cuda:
+        raise ExtensionMissing("qwen_engine_b200 ops run on CUDA tensors only (there is no CPU path); "
+                               f"got a tensor on {t.device}")
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(rc: int, name: str) -> None:
+    if rc != 0:
+        msg = lib().qe_last_error().decode("utf-8", "replace")
+        if rc == 1:
+            raise KernelRefused(msg or f"{name} refused its arguments")
+        raise RuntimeError(msg or f"{name} failed with code {rc}")
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelRefused(f"dtype {t.dtype} is not supported (float32 or bfloat16)") from None
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelRefused(msg)
+
+
+def _i32(t: torch.Tensor, name: str) -> None:
+    _need(t.dtype == torch.int32 and t.is_contiguous(), f"{name} must be a contiguous int32 tensor")
+
+
+# --------------------------------------------------------------------------------------
+
+def prepare_matrix(w: torch.Tensor) -> torch.Tensor:
+    """A [out, in] matrix as the product kernels want it (row-major, contiguous)."""
+    return w.contiguous()
+
+
+def embedding(token_ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = float32(table[token_ids[t]]); out is the float32 residual stream [T, H]."""
+    _i32(token_ids, "token_ids")
+    T, (V, H) = token_ids.numel(), table.shape
+    _need(out.dtype == torch.float32 and out.shape == (T, H) and out.is_contiguous(), "embedding: out must be float32 [T, H]")
+    _need(table.is_contiguous(), "embedding: table must be contiguous")
+    _check(lib().qe_embedding(_ptr(token_ids), _ptr(table), _ptr(out), T, H, V, _dt(table), _stream()), "embedding")
+
+
+def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out: torch.Tensor) -> None:
+    """resid += delta (if given), in place in float32; out = rmsnorm(resid) * weight."""
+    T, H = resid.shape
+    _need(resid.dtype == torch.float32 and resid.is_contiguous(), "add_rmsnorm: resid must be contiguous float32")
+    _need(weight.dtype == torch.float32 and weight.shape == (H,), "add_rmsnorm: weight must be float32 [H]")
+    _need(out.shape == (T, H) and out.is_contiguous(), "add_rmsnorm: out must be contiguous [T, H]")
+    if delta is not None:
+        _need(delta.shape == (T, H) and delta.dtype == out.dtype and delta.is_contiguous(),
+              "add_rmsnorm: delta must match out")
+    _check(lib().qe_add_rmsnorm(_ptr(resid), _ptr(delta), _ptr(None), _ptr(weight), ctypes.c_float(eps),
+                                _ptr(out), T, H, _dt(out), _stream()), "add_rmsnorm")
+
+
+def add_rmsnorm_rows(resid: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor,
+                     weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """out[n] = rmsnorm(resid[rows[n]] + delta[rows[n]]) * weight; resid is not changed."""
+    _i32(rows, "rows")
+    N, H = out.shape
+    _need(rows.numel() >= N, "add_rmsnorm_rows: fewer rows than outputs")
+    _need(resid.dtype == torch.float32 and resid.is_contiguous() and resid.shape[1] == H,
+          "add_rmsnorm_rows: resid must be contiguous float32 [T, H]")
+    _need(weight.dtype == torch.float32 and weight.shape == (H,), "add_rmsnorm_rows: weight must be float32 [H]")
+    _need(out.is_contiguous(), "add_rmsnorm_rows: out must be contiguous")
+    if delta is not None:
+        _need(delta.shape == resid.shape and delta.dtype == out.dtype and delta.is_contiguous(),
+              "add_rmsnorm_rows: delta must match")
+    _check(lib().qe_add_rmsnorm(_ptr(resid), _ptr(delta), _ptr(rows), _ptr(weight), ctypes.c_float(eps),
+                                _ptr(out), N, H, _dt(out), _stream()), "add_rmsnorm_rows")
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, N] = x[M, K] · w[N, K]^T, float32 accumulation; out in x's dtype or float32."""
+    M, K = x.shape
+    N = w.shape[0]
+    _need(w.shape == (N, K) and w.dtype == x.dtype, f"linear: w {tuple(w.shape)} {w.dtype} does not fit x {tuple(x.shape)} {x.dtype}")
+    _need(out.shape == (M, N) and out.dtype in (x.dtype, torch.float32), "linear: out must be [M, N] in x's dtype or float32")
+    _need(x.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "linear: operands must be contiguous")
+    out_f32 = int(out.dtype == torch.float32)
+    _check(lib().qe_linear_generic(_ptr(x), _ptr(w), _ptr(out), M, N, K, _dt(x), out_f32, _stream()), "linear")
+
+
+def qk_norm_rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, q_norm_w: Optional[torch.Tensor],
+                          k_norm_w: Optional[torch.Tensor], eps: float, inv_freq: Optional[torch.Tensor],
+                          rotary_dim: int, kv_pages: Optional[torch.Tensor], slot_mapping: Optional[torch.Tensor],
+                          num_heads: int, num_kv_heads: int, head_dim: int, write_kv: bool = True) -> None:
+    """On the stacked projection output qkv [T, (Hq + 2 Hkv) D], in place: per-head RMS norm of q and
+    k (if weights are given), half-split rotation by positions (if inv_freq is given); then k and v
+    are written to the slots of ``slot_mapping`` in ``kv_pages`` [pages, 2, Hkv, page, D]."""
+    T = qkv.shape[0]
+    Hq, Hkv, D = num_heads, num_kv_heads, head_dim
+    _need(qkv.shape == (T, (Hq + 2 * Hkv) * D) and qkv.is_contiguous(), "qk_norm_rope_kv_write: qkv must be [T, (Hq+2Hkv)D]")
+    _i32(positions, "positions")
+    stride = qkv.shape[1]
+    q = qkv
+    k = qkv[:, Hq * D:]
+    v = qkv[:, (Hq + Hkv) * D:]
+    page_size = 1
+    if write_kv:
+        _need(kv_pages is not None and slot_mapping is not None, "qk_norm_rope_kv_write: cache write without a cache")
+        _need(kv_pages.dtype == qkv.dtype and kv_pages.is_contiguous() and kv_pages.dim() == 5
+              and kv_pages.shape[1] == 2 and kv_pages.shape[2] == Hkv and kv_pages.shape[4] == D,
+              "qk_norm_rope_kv_write: kv_pages must be [pages, 2, Hkv, page, D] in qkv's dtype")
+        _i32(slot_mapping, "slot_mapping")
+        page_size = kv_pages.shape[3]
+    for wt in (q_norm_w, k_norm_w):
+        if wt is not None:
+            _need(wt.dtype == torch.float32 and wt.shape == (D,), "qk_norm_rope_kv_write: norm weights must be float32 [D]")
+    if inv_freq is not None:
+        _need(inv_freq.dtype == torch.float32 and inv_freq.numel() == rotary_dim // 2,
+              "qk_norm_rope_kv_write: inv_freq must be float32 [rotary_dim / 2]")
+    _check(lib().qe_qk_norm_rope_kv_write(
+        ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(k.data_ptr()), ctypes.c_void_p(v.data_ptr()),
+        ctypes.c_long(stride), ctypes.c_long(stride), ctypes.c_long(stride), _ptr(positions),
+        _ptr(q_norm_w), _ptr(k_norm_w), ctypes.c_float(eps), _ptr(inv_freq), int(rotary_dim),
+        _ptr(kv_pages if write_kv else None), _ptr(slot_mapping if write_kv else None),
+        T, Hq, Hkv, D, page_size, int(bool(write_kv)), _dt(qkv), _stream()), "qk_norm_rope_kv_write")
+
+
+def rope_neox(q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
+              rotary_dim: int) -> None:
+    """Half-split rotation of q [T, Hq, D] and k [T, Hkv, D] in place (rows may be strided)."""
+    T, Hq, D = q.shape
+    Hkv = k.shape[1]
+    _need(q.stride(2) == 1 and q.stride(1) == D and k.stride(2) == 1 and k.stride(1) == D,
+          "rope_neox: heads of a token must be contiguous")
+    _i32(positions, "positions")
+    _check(lib().qe_qk_norm_rope_kv_write(
+        ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(k.data_ptr()), ctypes.c_void_p(0),
+        ctypes.c_long(q.stride(0)), ctypes.c_long(k.stride(0)), ctypes.c_long(0), _ptr(positions),
+        _ptr(None), _ptr(None), ctypes.c_float(0.0), _ptr(inv_freq), int(rotary_dim),
+        _ptr(None), _ptr(None), T, Hq, Hkv, D, 1, 0, _dt(q), _stream()), "rope_neox")
+
+
+def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int) -> dict[str, list[int]]:
+    """Work lists of the attention kernels for one step's batch, as named int32 lists that the
+    step function copies to the device with the rest of the step's metadata."""
+    tiles: list[int] = []
+    for r, n in enumerate(q_lens):
+        for q0 in range(0, n, ATTN_TILE_Q):
+            tiles += [r, q0]
+    return {"tiles": tiles}
+
+
+def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: torch.Tensor, ctx,
+                    out: torch.Tensor, scale: float, window: int, num_heads: int, num_kv_heads: int,
+                    head_dim: int) -> None:
+    """Attention of the step's queries (the q part of qkv [T, (Hq+2Hkv) D]) over the keys and values
+    of their requests in ``kv_pages``; out [T, Hq D].  ``ctx`` is the StepContext (cu_q, ctx_lens
+    and the plan that ``plan_attention`` made)."""
+    Hq, Hkv, D = num_heads, num_kv_heads, head_dim
+    T = qkv.shape[0]
+    _need(out.shape == (T, Hq * D) and out.is_contiguous() and out.dtype == qkv.dtype, "paged_attention: out must be [T, Hq D]")
+    _need(kv_pages.dtype == qkv.dtype and kv_pages.dim() == 5 and kv_pages.is_contiguous(),
+          "paged_attention: kv_pages must be [pages, 2, Hkv, page, D] in q's dtype")
+    _i32(block_tables, "block_tables")
+    tiles = ctx.attn_plan["tiles"]
+    n_tiles = tiles.numel() // 2
+    _check(lib().qe_paged_attention_generic(
+        _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(block_tables), int(block_tables.shape[1]),
+        _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), _ptr(tiles), n_tiles, _ptr(out), ctypes.c_float(scale), int(window),
+        Hq, Hkv, D, int(kv_pages.shape[3]), _dt(qkv), _stream()), "paged_attention")
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    T, I2 = gate_up.shape
+    _need(I2 % 2 == 0 and out.shape == (T, I2 // 2) and out.dtype == gate_up.dtype
+          and out.is_contiguous() and gate_up.is_contiguous(), "silu_mul: out must be [T, I] for gate_up [T, 2I]")
+    _check(lib().qe_silu_mul(_ptr(gate_up), _ptr(out), T, I2 // 2, _dt(out), _stream()), "silu_mul")
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """out[n] = index of the largest logit of row n (the lowest index on a tie)."""
+    N, V = logits.shape
+    _need(logits.dtype == torch.float32 and logits.is_contiguous(), "argmax: logits must be contiguous float32")
+    _i32(out, "out")
+    _check(lib().qe_argmax(_ptr(logits), _ptr(out), N, V, _stream()), "argmax")
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, uniform: torch.Tensor,
+           out: torch.Tensor) -> None:
+    """Row n: temperature 0 -> argmax; else inverse-CDF sampling of softmax(top-k logits / temperature)
+    with the uniform number uniform[n] in [0, 1)."""
+    N, V = logits.shape
+    _need(logits.dtype == torch.float32 and logits.is_contiguous(), "sample: logits must be contiguous float32")
+    _need(temperature.dtype == torch.float32 and uniform.dtype == torch.float32, "sample: temperature and uniform must be float32")
+    _i32(top_k, "top_k")
+    _i32(out, "out")
+    _check(lib().qe_sample(_ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(uniform), _ptr(out), N, V, _stream()), "sample")

@@ -1,0 +1,39 @@
+"""SwiGLU feed-forward: down(silu(gate(x)) * up(x)), no biases
+(reference src/models/qwen3/model.py:227-237; silu(g) = g / (1 + exp(-g)) in
+float32, src/layers/fused_ops/silumul.py:50-53).  gate and up are one product
+over the stacked weights."""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..weights.spec import MATRIX, WeightSpec
+from .base import FeedForward, StepContext, register
+
+
+@register("feed_forward", "swiglu")
+class SwiGLU(FeedForward):
+    def __init__(self, hidden_size: int, intermediate_size: int):
+        self.hidden_size = hidden_size
+        self.intermediate_size = intermediate_size
+        self.w_gate_up = self.w_down = None
+
+    def weight_specs(self, prefix: str) -> list[WeightSpec]:
+        I, H = self.intermediate_size, self.hidden_size
+        return [WeightSpec(prefix + "gate_proj.weight", (I, H), MATRIX),
+                WeightSpec(prefix + "up_proj.weight", (I, H), MATRIX),
+                WeightSpec(prefix + "down_proj.weight", (H, I), MATRIX)]
+
+    def load(self, prefix, source, dtype, device) -> None:
+        stacked = torch.cat([source.get(prefix + "gate_proj.weight"),
+                             source.get(prefix + "up_proj.weight")], dim=0)
+        self.w_gate_up = ops.prepare_matrix(stacked.to(dtype).to(device))
+        self.w_down = ops.prepare_matrix(source.get(prefix + "down_proj.weight").to(dtype).to(device))
+
+    def forward(self, ctx: StepContext, x, out) -> None:
+        T, I = ctx.num_tokens, self.intermediate_size
+        gate_up = ctx.arena.alloc((T, 2 * I), ctx.dtype)
+        ops.linear(x, self.w_gate_up, gate_up)
+        act = ctx.arena.alloc((T, I), ctx.dtype)
+        ops.silu_mul(gate_up, act)
+        ops.linear(act, self.w_down, out)
