@@ -1,0 +1,270 @@
+"""Each CUDA kernel alone against its plain PyTorch restatement (tests/ref_ops.py), in float32
+and bfloat16, at sizes other than the engine's models: widths and vocabularies that are no
+power of two, head sizes in steps of 16, odd numbers of heads and groups."""
+import math
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+import ref_ops
+from qwen_engine_b200 import ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def _close(got, want, dtype, scale=None, tol32=2e-5, tol16=1.6e-2):
+    got, want = got.float().cpu(), want.float().cpu()
+    s = max(1.0, float(want.abs().max())) if scale is None else scale
+    tol = tol32 if dtype == torch.float32 else tol16
+    err = float((got - want).abs().max())
+    assert torch.isfinite(got).all()
+    assert err <= tol * s, f"max |diff| {err:.3e} > {tol} * {s:.3f}"
+
+
+def _randn(shape, dtype, seed, std=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * std).to(dtype)
+
+
+def test_extension_loads():
+    assert ops.lib().qe_abi_version() == 1
+
+
+def test_cpu_tensor_is_refused():
+    with pytest.raises(ops.ExtensionMissing):
+        ops.silu_mul(torch.zeros(2, 4), torch.zeros(2, 2))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,H,V", [(1, 64, 300), (37, 200, 1001), (5, 1000, 50)])
+def test_embedding(dtype, T, H, V):
+    table = _randn((V, H), dtype, 1)
+    ids = torch.randint(0, V, (T,), generator=torch.Generator().manual_seed(2), dtype=torch.int32)
+    want = torch.empty(T, H)
+    ref_ops.embedding(ids, table, want)
+    got = torch.empty(T, H, device=DEV)
+    ops.embedding(ids.to(DEV), table.to(DEV), got)
+    assert torch.equal(got.cpu(), want)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,H", [(1, 48), (33, 200), (7, 1000), (3, 4100)])
+@pytest.mark.parametrize("with_delta", [False, True])
+def test_add_rmsnorm(dtype, T, H, with_delta):
+    resid = _randn((T, H), torch.float32, 3, 2.0)
+    delta = _randn((T, H), dtype, 4) if with_delta else None
+    w = 1 + 0.3 * _randn((H,), torch.float32, 5)
+    eps = 1e-5
+    r_ref, out_ref = resid.clone(), torch.empty(T, H, dtype=dtype)
+    ref_ops.add_rmsnorm(r_ref, delta, w, eps, out_ref)
+    r_gpu, out_gpu = resid.to(DEV), torch.empty(T, H, dtype=dtype, device=DEV)
+    ops.add_rmsnorm(r_gpu, delta.to(DEV) if with_delta else None, w.to(DEV), eps, out_gpu)
+    _close(r_gpu, r_ref, torch.float32, tol32=1e-6)
+    _close(out_gpu, out_ref, dtype)
+    # the rows variant: chosen rows, stream untouched
+    rows = torch.tensor([T - 1, 0, T // 2], dtype=torch.int32)
+    out_ref2 = torch.empty(3, H, dtype=dtype)
+    ref_ops.add_rmsnorm_rows(resid, delta, rows, w, eps, out_ref2)
+    r_gpu2, out_gpu2 = resid.to(DEV), torch.empty(3, H, dtype=dtype, device=DEV)
+    ops.add_rmsnorm_rows(r_gpu2, delta.to(DEV) if with_delta else None, rows.to(DEV), w.to(DEV), eps, out_gpu2)
+    assert torch.equal(r_gpu2.cpu(), resid)
+    _close(out_gpu2, out_ref2, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 17, 5), (3, 389, 80), (70, 130, 224), (129, 64, 1000), (16, 1030, 72)])
+@pytest.mark.parametrize("out_f32", [False, True])
+def test_linear(dtype, M, N, K, out_f32):
+    x = _randn((M, K), dtype, 6)
+    w = _randn((N, K), dtype, 7, 0.1)
+    odt = torch.float32 if out_f32 else dtype
+    want = torch.empty(M, N, dtype=odt)
+    ref_ops.linear(x, w, want)
+    got = torch.empty(M, N, dtype=odt, device=DEV)
+    ops.linear(x.to(DEV), w.to(DEV), got)
+    _close(got, want, odt, tol16=8e-3)
+
+
+def test_linear_row_does_not_depend_on_batch():
+    """A row's product is the same bits whatever else is in the batch (32-bit path)."""
+    x = _randn((67, 200), torch.float32, 8).to(DEV)
+    w = _randn((150, 200), torch.float32, 9).to(DEV)
+    full = torch.empty(67, 150, device=DEV)
+    ops.linear(x, w, full)
+    for r in (0, 13, 66):
+        one = torch.empty(1, 150, device=DEV)
+        ops.linear(x[r:r + 1].contiguous(), w, one)
+        assert torch.equal(one[0], full[r])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,I", [(1, 10), (9, 224), (33, 1001)])
+def test_silu_mul(dtype, T, I):
+    gu = _randn((T, 2 * I), dtype, 10, 3.0)
+    want = torch.empty(T, I, dtype=dtype)
+    ref_ops.silu_mul(gu, want)
+    got = torch.empty(T, I, dtype=dtype, device=DEV)
+    ops.silu_mul(gu.to(DEV), got)
+    _close(got, want, dtype, tol32=1e-6, tol16=8e-3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("Hq,Hkv,D,P,rot", [(4, 2, 16, 4, 16), (6, 3, 48, 8, 48), (5, 1, 128, 16, 128),
+                                            (2, 2, 80, 2, 32), (3, 1, 256, 16, 256)])
+@pytest.mark.parametrize("norm", [True, False])
+def test_qk_norm_rope_kv_write(dtype, Hq, Hkv, D, P, rot, norm):
+    T, pages = 11, 9
+    qkv = _randn((T, (Hq + 2 * Hkv) * D), dtype, 11)
+    positions = torch.tensor([0, 1, 2, 3, 500, 501, 7, 40000, 9, 10, 11], dtype=torch.int32)
+    qw = (1 + 0.2 * _randn((D,), torch.float32, 12)) if norm else None
+    kw = (1 + 0.2 * _randn((D,), torch.float32, 13)) if norm else None
+    inv_freq = 1.0 / (1e6 ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))
+    slots = torch.randperm(pages * P, generator=torch.Generator().manual_seed(14))[:T].to(torch.int32)
+    cache_ref = torch.zeros(pages, 2, Hkv, P, D, dtype=dtype)
+    qkv_ref = qkv.clone()
+    ref_ops.qk_norm_rope_kv_write(qkv_ref, positions, qw, kw, 1e-6, inv_freq, rot, cache_ref, slots, Hq, Hkv, D)
+    cache_gpu = torch.zeros(pages, 2, Hkv, P, D, dtype=dtype, device=DEV)
+    qkv_gpu = qkv.to(DEV)
+    ops.qk_norm_rope_kv_write(qkv_gpu, positions.to(DEV), qw.to(DEV) if norm else None, kw.to(DEV) if norm else None,
+                              1e-6, inv_freq.to(DEV), rot, cache_gpu, slots.to(DEV), Hq, Hkv, D)
+    _close(qkv_gpu, qkv_ref, dtype, tol32=3e-5)
+    _close(cache_gpu, cache_ref, dtype, tol32=3e-5)
+    # untouched slots stay zero
+    mask = torch.ones(pages * P, dtype=torch.bool)
+    mask[slots.long()] = False
+    flat = cache_gpu.cpu().permute(0, 3, 1, 2, 4).reshape(pages * P, -1)
+    assert float(flat[mask].abs().max()) == 0.0
+
+
+def _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, seed, spike=None):
+    """Build a paged cache with scattered pages for requests with ctx_lens[r] cached tokens and
+    q_lens[r] new ones; returns everything both implementations need."""
+    g = torch.Generator().manual_seed(seed)
+    R = len(q_lens)
+    totals = [c + n for c, n in zip(ctx_lens, q_lens)]
+    blocks = [-(-t // P) for t in totals]
+    n_pages = sum(blocks) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    mb = max(blocks)
+    table = torch.full((R, mb), -1, dtype=torch.int32)
+    it = iter(perm)
+    for r in range(R):
+        for b in range(blocks[r]):
+            table[r, b] = next(it)
+    cache = (torch.randn(n_pages, 2, Hkv, P, D, generator=g)).to(dtype)
+    T = sum(q_lens)
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, generator=g).to(dtype)
+    if spike is not None:
+        # make one far key decide the output: scale the query and that key so its score stands out
+        r, key_pos, head = spike
+        kvh = head // (Hq // Hkv)
+        page, off = int(table[r, key_pos // P]), key_pos % P
+        direction = torch.randn(D, generator=g)
+        direction = direction / direction.norm()
+        cache[page, 0, kvh, off, :] = (direction * 6.0).to(dtype)
+        row = sum(q_lens[:r]) + q_lens[r] - 1
+        qkv[row, head * D:(head + 1) * D] = (direction * 6.0 * math.sqrt(D)).to(dtype)
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
+    return dict(qkv=qkv, cache=cache, table=table, cu_q=torch.tensor(cu, dtype=torch.int32),
+                ctx=torch.tensor(ctx_lens, dtype=torch.int32), T=T)
+
+
+def _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, fn, dev):
+    scale = 1.0 / math.sqrt(D)
+    plan = ops.plan_attention(list(q_lens), list(ctx_lens), P)
+    ctx = SimpleNamespace(cu_q=case["cu_q"].to(dev), ctx_lens=case["ctx"].to(dev),
+                          attn_plan={k: torch.tensor(v, dtype=torch.int32, device=dev) for k, v in plan.items()},
+                          q_lens_host=list(q_lens), ctx_lens_host=list(ctx_lens))
+    out = torch.zeros(case["T"], Hq * D, dtype=dtype, device=dev)
+    fn(case["qkv"].to(dev), case["cache"].to(dev), case["table"].to(dev), ctx, out, scale, window, Hq, Hkv, D)
+    return out
+
+
+ATTN_SHAPES = [(4, 2, 16, 4), (6, 2, 48, 8), (4, 1, 32, 8), (8, 4, 128, 16), (3, 3, 80, 2), (2, 1, 256, 16)]
+ATTN_BATCHES = [
+    ([13], [0]),                          # a whole short prompt
+    ([1], [77]),                          # one decoded token
+    ([1, 1, 1], [5, 130, 33]),            # a decode batch
+    ([7, 1, 2, 1], [9, 40, 0, 63]),       # portions beside decoded tokens
+    ([40], [25]),                         # a portion with earlier context, several query tiles
+    ([2, 33], [64, 31]),                  # starts at a page's edge; crosses key tiles
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("Hq,Hkv,D,P", ATTN_SHAPES)
+@pytest.mark.parametrize("q_lens,ctx_lens", ATTN_BATCHES)
+def test_paged_attention(dtype, Hq, Hkv, D, P, q_lens, ctx_lens):
+    case = _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, seed=21)
+    want = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, ref_ops.paged_attention, "cpu")
+    got = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, ops.paged_attention, DEV)
+    _close(got, want, dtype, tol32=2e-5, tol16=1.6e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [1, 5, 32, 33])
+def test_paged_attention_window(dtype, window):
+    Hq, Hkv, D, P = 4, 2, 32, 8
+    q_lens, ctx_lens = [9, 1, 40], [30, 70, 3]
+    case = _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, seed=22)
+    want = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ref_ops.paged_attention, "cpu")
+    got = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ops.paged_attention, DEV)
+    _close(got, want, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("key_pos", [0, 15, 16, 255, 256, 700])
+def test_paged_attention_far_key_stands_out(dtype, key_pos):
+    """One key among hundreds carries almost all the weight: the output must be its value.
+    A kernel that misses a page, a tile or a split would return something else."""
+    Hq, Hkv, D, P = 4, 2, 64, 16
+    q_lens, ctx_lens = [1, 3], [900, 760]
+    for r, head in ((0, 1), (1, 2)):
+        case = _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, seed=23, spike=(r, key_pos, head))
+        got = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, ops.paged_attention, DEV)
+        want = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, ref_ops.paged_attention, "cpu")
+        _close(got, want, dtype)
+        row = sum(q_lens[:r]) + q_lens[r] - 1
+        page, off = int(case["table"][r, key_pos // P]), key_pos % P
+        value = case["cache"][page, 1, head // (Hq // Hkv), off, :].float()
+        out = got[row, head * D:(head + 1) * D].float().cpu()
+        assert float((out - value).abs().max()) < 0.05, "the far key's value did not come through"
+
+
+@pytest.mark.parametrize("V", [5, 389, 151936])
+def test_argmax(V):
+    logits = _randn((6, V), torch.float32, 30)
+    logits[1, V - 1] = 50.0
+    logits[2, 0] = 50.0
+    logits[3, V // 2] = 9.0
+    logits[3, V // 3] = 9.0          # a tie: the lower index wins
+    logits[3].clamp_(max=9.0)
+    want = torch.empty(6, dtype=torch.int32)
+    ref_ops.argmax(logits, want)
+    got = torch.empty(6, dtype=torch.int32, device=DEV)
+    ops.argmax(logits.to(DEV), got)
+    assert got.cpu().tolist() == want.tolist()
+    assert got[3].item() == min(V // 2, V // 3)
+
+
+@pytest.mark.parametrize("V", [7, 389, 50021])
+def test_sample(V):
+    N = 16
+    logits = _randn((N, V), torch.float32, 31, 2.0)
+    temps = torch.tensor([0.0, 0.8, 1.0, 1.5] * 4)
+    top_k = torch.tensor([0, 0, 5, 1, 3, 0, V, V + 5, 2, 50, 0, 0, 7, 7, 1, 0], dtype=torch.int32)
+    u = torch.rand(N, generator=torch.Generator().manual_seed(32))
+    u[5] = 0.0
+    u[6] = 0.99999994
+    want = torch.empty(N, dtype=torch.int32)
+    ref_ops.sample(logits, temps, top_k, u, want)
+    got = torch.empty(N, dtype=torch.int32, device=DEV)
+    ops.sample(logits.to(DEV), temps.to(DEV), top_k.to(DEV), u.to(DEV), got)
+    assert got.cpu().tolist() == want.tolist()
+    # top_k = 1 is argmax whatever the temperature
+    assert got[3].item() == int(torch.argmax(logits[3]))
