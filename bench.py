@@ -1,0 +1,293 @@
+"""Benchmark of the engine on one B200: decode tokens a second at a fixed batch and context,
+prefill tokens a second at 2,048 tokens, for Qwen3-0.6B-shaped random weights.
+
+    python bench.py --gpus 1 --steps K --warmup W        # prints ONE JSON line
+
+A step is one decode step of the whole batch.  ``value`` is timed on the device over the step
+function (tokens already on the host side of the step function, no sampling read-back);
+``e2e`` is the same through the Python entry point (LLMEngine.step: host tokens in, sampled
+tokens out, every step).  ``prefill`` is one 2,048-token prompt to its last logits;
+``roofline`` is the decode step's bytes (every weight once, the cache of the live requests)
+over its time; ``points`` holds batch 1 and 64.  The step's inputs (1.2 GB of weights plus the
+cache) are larger than L2, so successive steps do not find them there.
+
+``--impl reference`` would run kzw3933/Qwen-Engine itself from baseline/_ref; see
+``reference_arm``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import random
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks() -> tuple[dict, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                raw = json.load(f)
+            flat = {}
+
+            def walk(d):
+                for k, v in d.items():
+                    if isinstance(v, dict):
+                        walk(v)
+                    elif isinstance(v, (int, float)):
+                        flat.setdefault(k, float(v))
+            walk(raw)
+            peaks = dict(FALLBACK_PEAKS)
+            for k in FALLBACK_PEAKS:
+                if k in flat:
+                    peaks[k] = flat[k]
+            return peaks, "measured"
+        except Exception:       # noqa: BLE001
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi in the background during the timed regions (read-only)."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows: list[list[str]] = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+
+        def pump():
+            for line in self.proc.stdout:
+                self.rows.append([c.strip() for c in line.split(",")])
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def mark(self) -> int:
+        return len(self.rows)
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, spans: list[tuple[int, int]]) -> dict:
+        rows = [r for a, b in spans for r in self.rows[a:b]] or self.rows
+        sm = sorted(int(r[0]) for r in rows if r and r[0].isdigit())
+        mx = [int(r[1]) for r in rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i].lower() == "active" for r in rows)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(rows)}
+
+
+def reference_arm(args) -> int:
+    """The reference arm: kzw3933/Qwen-Engine from baseline/_ref through its own public API."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    why = None
+    if not os.path.isdir(ref) or not os.listdir(ref):
+        why = ("not installed: the reference's pyproject.toml declares no packages (its sources are loose "
+               "folders under src/ reached by sys.path edits), so an offline pip install into baseline/_ref "
+               "yields no importable package")
+    else:
+        why = "baseline/_ref holds no importable engine package"
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--preset", default="qwen3-0.6b")
+    ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=1024)
+    ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    ap.add_argument("--dtype", default="bfloat16")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    from qwen_engine_b200 import ops
+    from qwen_engine_b200.config import EngineConfig, parse_dtype, preset_config_dict, preset_init
+    from qwen_engine_b200.engine.llm import LLMEngine
+    from qwen_engine_b200.engine.loading import load_model
+    from qwen_engine_b200.engine.runner import StepEntry
+    from qwen_engine_b200.registry import config_from_dict
+    from qwen_engine_b200.sampling import SamplingParams
+
+    peaks, peaks_src = load_peaks()
+    dtype = parse_dtype(args.dtype)
+    raw = preset_config_dict(args.preset)
+    layers_of_config = raw["num_hidden_layers"]
+    if args.layers:
+        raw["num_hidden_layers"] = args.layers
+    cfg = config_from_dict(raw)
+    init = preset_init(args.preset)
+    page = init["block_size"]
+    big_batch = args.batch if args.no_points else max(args.batch, 64)
+    extra = args.warmup + args.steps + 8
+    per_req = -(-(args.context + 3 * extra) // page) + 1
+    pages = big_batch * per_req + -(-args.prefill_tokens // page) + 8
+    t_load = time.time()
+    loaded = load_model(None, dtype, "cuda:0", page, pages, big_batch + 2, enable_prefix_cache=False, config=cfg,
+                        random_seed=init["seed"], random_std=init["std"], random_norm_std=init["norm_std"])
+    print(f"[bench] model ready in {time.time() - t_load:.1f}s", file=sys.stderr, flush=True)
+    runner, cache, model = loaded.runner, loaded.cache, loaded.model
+    rng = random.Random(0)
+    V = cfg.vocab_size
+
+    def tokens(n):
+        return [rng.randrange(V) for _ in range(n)]
+
+    def timed(fn, n_iter):
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n_iter):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / n_iter
+
+    clocks = ClockSampler()
+    clocks.start()
+    spans = []
+
+    # ---- prefill: one prompt of 2,048 tokens to its last logits ----------------------------------
+    P = args.prefill_tokens
+    prompt = tokens(P)
+
+    def prefill_once():
+        rc = cache.open("prefill")
+        runner.step([StepEntry(rc, prompt, [P - 1])])
+        cache.close(rc)
+    for _ in range(args.warmup):
+        prefill_once()
+    m0 = clocks.mark()
+    prefill_ms = timed(prefill_once, 5)
+    spans.append((m0, clocks.mark()))
+    c = cfg
+    gemm_params = c.num_hidden_layers * (c.hidden_size * (c.q_width + 2 * c.kv_width) + c.q_width * c.hidden_size
+                                         + 3 * c.hidden_size * c.intermediate_size)
+    prefill_flops = 2.0 * P * gemm_params + c.num_hidden_layers * 4.0 * c.num_attention_heads * c.head_dim * P * P / 2 \
+        + 2.0 * c.vocab_size * c.hidden_size
+    prefill = {"value": round(P / (prefill_ms / 1e3), 1), "tokens": P, "ms": round(prefill_ms, 3),
+               "frac": round(prefill_flops / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)}
+
+    # ---- decode at batch 64, 8, 1 over real, scattered pages ----------------------------------------
+    reqs = [cache.open(f"d{i}") for i in range(big_batch)]
+    per_step = max(1, 4096 // args.context)
+    for i in range(0, big_batch, per_step):
+        runner.step([StepEntry(rc, tokens(args.context), []) for rc in reqs[i:i + per_step]])
+    torch.cuda.synchronize()
+    weight_bytes = model.weight_bytes()
+    kv_bytes_per_token = sum(g.tensor[:, 0].numel() // g.tensor.shape[4] * g.tensor.element_size()
+                             for g in cache.paged_groups)      # all layers, K and V, one token
+
+    def decode_rate(batch, steps, warmup, record=None):
+        live = reqs[:batch]
+
+        def one():
+            runner.step([StepEntry(rc, [rng.randrange(V)], [0]) for rc in live])
+        for _ in range(warmup):
+            one()
+        l0, m = ops.launch_count, clocks.mark()
+        ms = timed(one, steps)
+        if record is not None:
+            record["launches"] = ops.launch_count - l0
+            spans.append((m, clocks.mark()))
+        return batch * 1e3 / ms, ms
+
+    points = {}
+    if not args.no_points and big_batch >= 64:
+        points["decode_b64"] = round(decode_rate(64, max(5, args.steps // 2), 3)[0], 1)
+    rec = {}
+    value, ms_per_step = decode_rate(args.batch, args.steps, args.warmup, rec)
+    ctx_now = reqs[0].num_tokens
+    step_bytes = weight_bytes + args.batch * ctx_now * kv_bytes_per_token
+    achieved = step_bytes / (ms_per_step / 1e3) / 1e9
+    if not args.no_points:
+        points["decode_b1"] = round(decode_rate(1, args.steps, 3)[0], 1)
+    for rc in reqs:
+        cache.close(rc)
+
+    # ---- end to end through the Python entry point ----------------------------------------------------
+    ec = EngineConfig(dtype=dtype, device="cuda:0", block_size=page, num_blocks=pages, max_model_len=args.context + 4 * extra,
+                      max_num_seqs=args.batch, max_num_batched_tokens=4096, enable_prefix_cache=False)
+    eng = LLMEngine(loaded, ec)
+    sp = SamplingParams(max_new_tokens=args.warmup + args.steps + 2, ignore_eos=True)
+    for _ in range(args.batch):
+        eng.add_request(tokens(args.context), sp)
+    while eng.stats.decode_tokens < args.batch * args.warmup:     # prompts, then W decode steps
+        eng.step()
+    torch.cuda.synchronize()
+    m0 = clocks.mark()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        eng.step()                                                  # host tokens in, sampled tokens out
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    spans.append((m0, clocks.mark()))
+    e2e = {"value": round(args.batch * args.steps / e2e_s, 1), "unit": "tokens/s",
+           "h2d_bytes_per_step": runner.last_h2d_bytes, "d2h_bytes_per_step": 4 * args.batch}
+    while eng.has_work():
+        eng.step()
+    clocks.stop()
+
+    line = {
+        "metric": "decode tok/s (Qwen3-0.6B, batch 8, context 1024)", "value": round(value, 1), "unit": "tokens/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if dtype == torch.bfloat16 else "fp32",
+        "data": "synthetic: uniform random token ids, random weights N(0, 0.02) seed 2", "impl": "ours",
+        "config": {"model": args.preset, "layers": cfg.num_hidden_layers, "layers_of_config": layers_of_config,
+                   "hidden": c.hidden_size, "heads": c.num_attention_heads, "kv_heads": c.num_key_value_heads,
+                   "head_dim": c.head_dim, "intermediate": c.intermediate_size, "vocab": c.vocab_size,
+                   "global_batch": args.batch, "seq_len": args.context, "context_at_timing": ctx_now,
+                   "page_size": page, "prefill_tokens": P, "l2": "inputs larger than L2", "parallelism": "single GPU",
+                   "peaks": peaks_src},
+        "e2e": e2e, "gpu_launches": rec.get("launches", 0),
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clocks.summary(spans),
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

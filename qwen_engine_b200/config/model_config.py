@@ -128,7 +128,7 @@ class Qwen3Config(ModelConfig):
             num_hidden_layers=raw.get("num_hidden_layers", defaults.num_hidden_layers),
             hidden_size=hidden,
             num_attention_heads=heads,
-            num_key_value_heads=raw.get("num_key_value_heads", heads),
+            num_key_value_heads=raw.get("num_key_value_heads", defaults.num_key_value_heads),
             head_dim=head_dim,
             intermediate_size=raw.get("intermediate_size", defaults.intermediate_size),
             vocab_size=raw.get("vocab_size", defaults.vocab_size),

@@ -1,0 +1,352 @@
+// Flash attention over the paged cache in bfloat16 with tensor cores (mma.sync.m16n8k16), for
+// prompt portions and for decoded tokens alike.
+//
+// One CTA serves one kv head and a tile of 64 "rows": a row is (query token, query head of the kv
+// head's group), so the keys and values of a kv head are read once for all its query heads (the
+// reference reads them once per query head, src/layers/fused_ops/attn.py:181-182, 405-406).  Keys come
+// in tiles of 64 through a two-stage cp.async pipeline, gathered page by page from the block table.
+// Scores, running max, running sum and the output accumulator are float32; P is rounded to
+// bfloat16 before P·V (attn.py:263); the mask is key <= position (and > position - window)
+// (attn.py:195, 239).  Tiles above the causal frontier are never visited.
+//
+// A work item may cover only a range of keys (a split of a long context for a decoded token:
+// flash decoding, attn.py:374-594 with split_size 256); then it writes its unnormalised
+// accumulator with max and sum in float32 to scratch memory and a merge kernel combines the parts.
+//
+// Work items (int32 x 8): req, q0 (first token of the tile within the request's new tokens),
+// kv_lo, kv_hi (key range; kv_hi is further capped by causality), part (-1: write the output;
+// else index of the partial), n_splits, split (when n_splits > 0 the key range is computed here
+// from the request's length on the device: the keys from the window's start on, cut into
+// n_splits equal runs of whole key tiles, of which this item takes run `split`; so the work
+// list of a decode step does not change as contexts grow), 1 unused.
+// Merge items (int32 x 4): req, q0, first part, number of parts.
+#include "common.cuh"
+#include <math.h>
+
+#define FA_BM 64
+#define FA_BN 64
+#define FA_WARPS 4
+#define FA_THREADS (FA_WARPS * 32)
+#define FA_ITEM_INTS 8
+
+__device__ __forceinline__ void fa_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" :: "r"(a), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" :: "n"(N)); }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// D: head size, a multiple of 16 up to 256.  Rows of the shared-memory tiles are padded by 16 bytes
+// so that the 8 row addresses of an ldmatrix fall into different banks for every D.
+template <int D>
+__global__ void __launch_bounds__(FA_THREADS)
+flash_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride,
+                       const __nv_bfloat16* __restrict__ pages, const int* __restrict__ block_tables,
+                       int max_blocks, const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
+                       const int* __restrict__ items, __nv_bfloat16* __restrict__ out,
+                       float* __restrict__ part_acc, float* __restrict__ part_ml, int part_rows,
+                       float scale_log2, int window, int Hq, int Hkv, int page_size) {
+  constexpr int LD = D + 8;                         // padded row, in elements
+  constexpr int KS = D / 16;                        // k-steps over the head size
+  constexpr int CH = D / 8;                         // 16-byte chunks in a row
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* sq = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [64][LD]
+  __nv_bfloat16* sk = sq + FA_BM * LD;                                     // [2][64][LD]
+  __nv_bfloat16* sv = sk + 2 * FA_BN * LD;                                 // [2][64][LD]
+
+  const int* it = items + (size_t)blockIdx.x * FA_ITEM_INTS;
+  const int req = it[0], q0 = it[1], part = it[4], n_splits = it[5], split = it[6];
+  int kv_lo = it[2], kv_hi_item = it[3];
+  const int hkv = blockIdx.y;
+  const int G = Hq / Hkv;
+  const int tpt = FA_BM / G;                        // tokens in a tile
+  const int row0 = cu_q[req];
+  const int q_len = cu_q[req + 1] - row0;
+  const int ctx = ctx_lens[req];
+  const int ntok = min(tpt, q_len - q0);
+  const int nrows = ntok * G;
+  const int* table = block_tables + (size_t)req * max_blocks;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, c = lane & 3;
+
+  const int first_pos = ctx + q0;
+  if (n_splits > 0) {
+    const int total = ctx + q_len;
+    const int lo = window > 0 ? max(0, ctx - window + 1) / FA_BN * FA_BN : 0;
+    const int per = ((total - lo + n_splits - 1) / n_splits + FA_BN - 1) / FA_BN * FA_BN;
+    kv_lo = lo + split * per;
+    kv_hi_item = min(total, kv_lo + per);
+  }
+  const int kv_end = min(kv_hi_item, first_pos + ntok);                    // causal frontier of the tile
+  int kv_begin = kv_lo;
+  if (window > 0) kv_begin = max(kv_begin, first_pos - window + 1);
+  kv_begin = max(kv_begin, 0);
+  const int kt_first = (kv_begin / FA_BN) * FA_BN;
+  const int n_tiles = kv_end > kt_first ? (kv_end - kt_first + FA_BN - 1) / FA_BN : 0;
+
+  // ---- stage the query rows --------------------------------------------------------------
+  for (int e = threadIdx.x; e < FA_BM * CH; e += FA_THREADS) {
+    const int r = e / CH, ch = e - r * CH;
+    __nv_bfloat16* dst = sq + r * LD + ch * 8;
+    if (r < nrows) {
+      const int ti = r / G, hg = r - ti * G;
+      cp_async16(dst, q + (size_t)(row0 + q0 + ti) * q_stride + (size_t)(hkv * G + hg) * D + ch * 8);
+    } else {
+      *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    }
+  }
+  auto load_tile = [&](int stage, int kt) {
+    __nv_bfloat16* dk = sk + stage * FA_BN * LD;
+    __nv_bfloat16* dv = sv + stage * FA_BN * LD;
+    for (int e = threadIdx.x; e < FA_BN * CH; e += FA_THREADS) {
+      const int j = e / CH, ch = e - j * CH;
+      const int kj = kt + j;
+      if (kj >= kv_begin && kj < kv_end) {
+        const int page = table[kj / page_size];
+        const size_t base = ((((size_t)page * 2) * Hkv + hkv) * page_size + (kj % page_size)) * D + ch * 8;
+        cp_async16(dk + j * LD + ch * 8, pages + base);
+        cp_async16(dv + j * LD + ch * 8, pages + base + (size_t)Hkv * page_size * D);
+      } else {
+        *reinterpret_cast<uint4*>(dk + j * LD + ch * 8) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(dv + j * LD + ch * 8) = make_uint4(0, 0, 0, 0);
+      }
+    }
+  };
+  if (n_tiles > 0) load_tile(0, kt_first);
+  cp_async_commit();
+
+  // rows of this thread: r_lo = 16 warp + g and r_lo + 8
+  const int r_lo = warp * 16 + g, r_hi = r_lo + 8;
+  const int pos_lo = r_lo < nrows ? first_pos + r_lo / G : -1;             // -1: the row is padding
+  const int pos_hi = r_hi < nrows ? first_pos + r_hi / G : -1;
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+
+  const bool warp_active = warp * 16 < nrows;       // warps without rows only help loading
+
+  for (int t = 0; t < n_tiles; ++t) {
+    const int kt = kt_first + t * FA_BN;
+    if (t + 1 < n_tiles) load_tile((t + 1) & 1, kt + FA_BN);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    if (warp_active) {
+      const __nv_bfloat16* tk = sk + (t & 1) * FA_BN * LD;
+      const __nv_bfloat16* tv = sv + (t & 1) * FA_BN * LD;
+      // ---- S = Q K^T -------------------------------------------------------------------
+      float s[FA_BN / 8][4];
+#pragma unroll
+      for (int i = 0; i < FA_BN / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        uint32_t a[4];
+        // A fragment of Q: matrices (rows 0-7, k 0-7), (rows 8-15, k 0-7), (rows 0-7, k 8-15), (rows 8-15, k 8-15)
+        ldsm_x4(a, sq + (warp * 16 + (lane & 15)) * LD + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+        for (int np = 0; np < FA_BN / 16; ++np) {
+          uint32_t b[4];
+          // B fragments of two key tiles: (keys 0-7, k 0-7), (keys 0-7, k 8-15), (keys 8-15, k 0-7), (keys 8-15, k 8-15)
+          ldsm_x4(b, tk + (np * 16 + (lane >> 4) * 8 + (lane & 7)) * LD + ks * 16 + ((lane >> 3) & 1) * 8);
+          fa_mma(s[2 * np], a, b[0], b[1]);
+          fa_mma(s[2 * np + 1], a, b[2], b[3]);
+        }
+      }
+      // ---- mask, online softmax ------------------------------------------------------------
+      float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < FA_BN / 8; ++i) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int key = kt + i * 8 + 2 * c + e;
+          const bool in_range = key >= kv_begin && key < kv_end;
+          const bool ok_lo = in_range && key <= pos_lo && (window <= 0 || key > pos_lo - window);
+          const bool ok_hi = in_range && key <= pos_hi && (window <= 0 || key > pos_hi - window);
+          s[i][e] = ok_lo ? s[i][e] * scale_log2 : -INFINITY;
+          s[i][2 + e] = ok_hi ? s[i][2 + e] * scale_log2 : -INFINITY;
+          mx_lo = fmaxf(mx_lo, s[i][e]);
+          mx_hi = fmaxf(mx_hi, s[i][2 + e]);
+        }
+      }
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+      const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+      const float base_lo = mn_lo == -INFINITY ? 0.f : mn_lo;      // a row with nothing allowed so far
+      const float base_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+      const float al_lo = exp2f(m_lo - base_lo), al_hi = exp2f(m_hi - base_hi);
+      m_lo = mn_lo; m_hi = mn_hi;
+      float sum_lo = 0.f, sum_hi = 0.f;
+#pragma unroll
+      for (int i = 0; i < FA_BN / 8; ++i) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          s[i][e] = exp2f(s[i][e] - base_lo);
+          s[i][2 + e] = exp2f(s[i][2 + e] - base_hi);
+          sum_lo += s[i][e];
+          sum_hi += s[i][2 + e];
+        }
+      }
+      sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 1);
+      sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 2);
+      sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 1);
+      sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 2);
+      l_lo = l_lo * al_lo + sum_lo;
+      l_hi = l_hi * al_hi + sum_hi;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) { o[i][0] *= al_lo; o[i][1] *= al_lo; o[i][2] *= al_hi; o[i][3] *= al_hi; }
+      // ---- O += P V ------------------------------------------------------------------------
+#pragma unroll
+      for (int kk = 0; kk < FA_BN / 16; ++kk) {
+        uint32_t a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int dp = 0; dp < D / 16; ++dp) {
+          uint32_t b[4];
+          // transposed loads of V: (keys 0-7, d 0-7), (keys 8-15, d 0-7), (keys 0-7, d 8-15), (keys 8-15, d 8-15)
+          ldsm_x4_t(b, tv + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LD + dp * 16 + (lane >> 4) * 8);
+          fa_mma(o[2 * dp], a, b[0], b[1]);
+          fa_mma(o[2 * dp + 1], a, b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();                                // the stage is free for the load after next
+  }
+  cp_async_wait<0>();
+
+  if (!warp_active) return;
+  // ---- write: the output, or this part's accumulator with max and sum ------------------------
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int r = half ? r_hi : r_lo;
+    if (r >= nrows) continue;
+    const int ti = r / G, hg = r - ti * G;
+    const float l = half ? l_hi : l_lo, m = half ? m_hi : m_lo;
+    if (part < 0) {
+      const float inv = 1.f / l;
+      __nv_bfloat16* dst = out + (size_t)(row0 + q0 + ti) * ((size_t)Hq * D) + (size_t)(hkv * G + hg) * D;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) {
+        const float v0 = o[i][2 * half] * inv, v1 = o[i][2 * half + 1] * inv;
+        *reinterpret_cast<uint32_t*>(dst + i * 8 + 2 * c) = pack_bf16(v0, v1);
+      }
+    } else {
+      const size_t slot = ((size_t)part * Hkv + hkv) * part_rows + r;
+      float* dst = part_acc + slot * D;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) {
+        *reinterpret_cast<float2*>(dst + i * 8 + 2 * c) = make_float2(o[i][2 * half], o[i][2 * half + 1]);
+      }
+      if (c == 0) { part_ml[2 * slot] = m; part_ml[2 * slot + 1] = l; }
+    }
+  }
+}
+
+// out = sum_s 2^(m_s - m) acc_s / sum_s 2^(m_s - m) l_s  (reference attn.py:520-594), float32.
+template <int D>
+__global__ void flash_merge_kernel(const int* __restrict__ merge_items, const int* __restrict__ cu_q,
+                                   const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                   int part_rows, __nv_bfloat16* __restrict__ out, int Hq, int Hkv) {
+  const int* it = merge_items + 4 * blockIdx.x;
+  const int req = it[0], q0 = it[1], first = it[2], n = it[3];
+  const int hkv = blockIdx.y;
+  const int G = Hq / Hkv;
+  const int row0 = cu_q[req];
+  const int q_len = cu_q[req + 1] - row0;
+  const int nrows = min(FA_BM / G, q_len - q0) * G;
+  for (int r = threadIdx.y; r < nrows; r += blockDim.y) {
+    float m = -INFINITY;
+    for (int s = 0; s < n; ++s) m = fmaxf(m, part_ml[2 * ((((size_t)first + s) * Hkv + hkv) * part_rows + r)]);
+    float l = 0.f;
+    for (int s = 0; s < n; ++s) {
+      const size_t slot = (((size_t)first + s) * Hkv + hkv) * part_rows + r;
+      l += exp2f(part_ml[2 * slot] - m) * part_ml[2 * slot + 1];
+    }
+    const int ti = r / G, hg = r - ti * G;
+    __nv_bfloat16* dst = out + (size_t)(row0 + q0 + ti) * ((size_t)Hq * D) + (size_t)(hkv * G + hg) * D;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+      float acc = 0.f;
+      for (int s = 0; s < n; ++s) {
+        const size_t slot = (((size_t)first + s) * Hkv + hkv) * part_rows + r;
+        acc += exp2f(part_ml[2 * slot] - m) * part_acc[slot * D + d];
+      }
+      dst[d] = __float2bfloat16_rn(acc / l);
+    }
+  }
+}
+
+template <int D>
+static int launch_flash(const void* q, long q_stride, const void* pages, const int* block_tables, int max_blocks,
+                        const int* cu_q, const int* ctx_lens, const int* items, int n_items,
+                        const int* merge_items, int n_merge, void* out, float* part_acc, float* part_ml,
+                        int part_rows, float scale, int window, int Hq, int Hkv, int page_size, cudaStream_t stream) {
+  constexpr int LD = D + 8;
+  const size_t smem = (size_t)(FA_BM + 4 * FA_BN) * LD * sizeof(__nv_bfloat16);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(flash_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) QE_REFUSE("flash_attention: shared memory %zu: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  const float scale_log2 = scale * 1.4426950408889634f;
+  dim3 grid(n_items, Hkv);
+  flash_attention_kernel<D><<<grid, FA_THREADS, smem, stream>>>(
+      (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pages, block_tables, max_blocks, cu_q, ctx_lens, items,
+      (__nv_bfloat16*)out, part_acc, part_ml, part_rows, scale_log2, window, Hq, Hkv, page_size);
+  QE_CHECK_LAUNCH("flash_attention");
+  if (n_merge > 0) {
+    dim3 mgrid(n_merge, Hkv), mblock(32, 4);
+    flash_merge_kernel<D><<<mgrid, mblock, 0, stream>>>(merge_items, cu_q, part_acc, part_ml, part_rows,
+                                                       (__nv_bfloat16*)out, Hq, Hkv);
+    QE_CHECK_LAUNCH("flash_merge");
+  }
+  return 0;
+}
+
+extern "C" int qe_flash_attention_supported(int Hq, int Hkv, int D) {
+  return (D % 16 == 0 && D >= 16 && D <= 256 && Hkv >= 1 && Hq % Hkv == 0 && Hq / Hkv <= FA_BM && Hkv <= 65535) ? 1 : 0;
+}
+
+extern "C" int qe_flash_attention(const void* q, long q_stride, const void* pages, const int* block_tables,
+                                  int max_blocks, const int* cu_q, const int* ctx_lens, const int* items,
+                                  int n_items, const int* merge_items, int n_merge, void* out, float* part_acc,
+                                  float* part_ml, int part_rows, float scale, int window, int Hq, int Hkv, int D,
+                                  int page_size, cudaStream_t stream) {
+  if (n_items <= 0) return 0;
+  if (!qe_flash_attention_supported(Hq, Hkv, D))
+    QE_REFUSE("flash_attention: heads %d/%d with head_dim %d are not supported", Hq, Hkv, D);
+  if (((uintptr_t)q | (uintptr_t)pages) & 15 || (q_stride % 8)) QE_REFUSE("flash_attention: operands must be 16-byte aligned");
+#define FA_CASE(DD) case DD: return launch_flash<DD>(q, q_stride, pages, block_tables, max_blocks, cu_q, ctx_lens, items, \
+      n_items, merge_items, n_merge, out, part_acc, part_ml, part_rows, scale, window, Hq, Hkv, page_size, stream);
+  switch (D) {
+    FA_CASE(16) FA_CASE(32) FA_CASE(48) FA_CASE(64) FA_CASE(80) FA_CASE(96) FA_CASE(112) FA_CASE(128)
+    FA_CASE(144) FA_CASE(160) FA_CASE(176) FA_CASE(192) FA_CASE(208) FA_CASE(224) FA_CASE(240) FA_CASE(256)
+  }
+#undef FA_CASE
+  QE_REFUSE("flash_attention: head_dim %d is not supported", D);
+}

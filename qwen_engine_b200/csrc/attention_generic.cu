@@ -133,16 +133,20 @@ extern "C" int qe_paged_attention_generic(const void* q, long q_stride, const vo
   if (Hq > 65535) QE_REFUSE("paged_attention: too many heads (%d)", Hq);
   const size_t smem = ((size_t)AG_BM * D + (size_t)AG_BN * (D + 1) + (size_t)AG_BN * D) * sizeof(float);
   dim3 grid(n_tiles, Hq);
-  cudaError_t e;
+  // the largest head size sets the limit once (not per launch: launches may be under stream capture)
+  static bool configured = false;
+  if (!configured) {
+    const int max_smem = (int)(((size_t)AG_BM * AG_MAX_D + (size_t)AG_BN * (AG_MAX_D + 1) + (size_t)AG_BN * AG_MAX_D) * sizeof(float));
+    cudaError_t e = cudaFuncSetAttribute(attention_generic_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_generic_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (e != cudaSuccess) QE_REFUSE("paged_attention: shared memory %d: %s", max_smem, cudaGetErrorString(e));
+    configured = true;
+  }
   if (dtype == QE_DTYPE_F32) {
-    e = cudaFuncSetAttribute(attention_generic_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) QE_REFUSE("paged_attention: shared memory %zu: %s", smem, cudaGetErrorString(e));
     attention_generic_kernel<float><<<grid, AG_WARPS * 32, smem, stream>>>(
         (const float*)q, q_stride, (const float*)pages, block_tables, max_blocks, cu_q, ctx_lens, tiles,
         (float*)out, scale, window, Hq, Hkv, D, page_size);
   } else if (dtype == QE_DTYPE_BF16) {
-    e = cudaFuncSetAttribute(attention_generic_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) QE_REFUSE("paged_attention: shared memory %zu: %s", smem, cudaGetErrorString(e));
     attention_generic_kernel<__nv_bfloat16><<<grid, AG_WARPS * 32, smem, stream>>>(
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pages, block_tables, max_blocks, cu_q, ctx_lens,
         tiles, (__nv_bfloat16*)out, scale, window, Hq, Hkv, D, page_size);

@@ -34,7 +34,8 @@ def require_cuda(device) -> torch.device:
 def load_model(model_dir: Optional[str], dtype: torch.dtype, device, page_size: int, num_pages: int,
                num_state_slots: int, enable_prefix_cache: bool = True, config: Optional[ModelConfig] = None,
                random_seed: Optional[int] = None, random_std: float = 0.02, random_norm_std: float = 0.1,
-               poison_cache: bool = False, check_device: bool = True) -> LoadedModel:
+               poison_cache: bool = False, check_device: bool = True,
+               use_cuda_graphs: bool = True) -> LoadedModel:
     """Read ``config.json``, pick the model class by its ``architectures`` entry, load
     ``model.safetensors`` by tensor name (or draw seeded random weights when ``model_dir``
     is None and a configuration is given), and set up the cache and the step function."""
@@ -55,5 +56,5 @@ def load_model(model_dir: Optional[str], dtype: torch.dtype, device, page_size: 
     model.load_weights(source, dtype, device, where)
     cache = CacheManager(model.cache_specs(), page_size, num_pages, num_state_slots, dtype, device,
                          enable_prefix_cache=enable_prefix_cache, poison=poison_cache)
-    runner = ModelRunner(model, cache, device, dtype)
+    runner = ModelRunner(model, cache, device, dtype, use_cuda_graphs=use_cuda_graphs)
     return LoadedModel(config, model, cache, runner)

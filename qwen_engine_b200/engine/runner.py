@@ -48,8 +48,10 @@ class _Pack:
 
 
 class ModelRunner:
+    GRAPH_BLOCK_BUCKET = 64       # block tables of replayed steps are padded to multiples of this
+
     def __init__(self, model: DecoderModel, cache: CacheManager, device, dtype: torch.dtype,
-                 max_positions: Optional[int] = None):
+                 max_positions: Optional[int] = None, use_cuda_graphs: bool = True):
         self.model = model
         self.cache = cache
         self.device = torch.device(device)
@@ -61,12 +63,18 @@ class ModelRunner:
         self._host_free: list[Optional[torch.cuda.Event]] = [None, None]
         self._dev_meta: Optional[torch.Tensor] = None
         self._flip = 0
+        self.use_cuda_graphs = bool(use_cuda_graphs) and self._on_gpu
+        # decode steps by shape: None after the first (eager) run, then (graph, logits, launches)
+        self._graphs: dict[tuple, Optional[tuple]] = {}
+        self.num_graph_replays = 0
         self.num_steps = 0
+        self.last_h2d_bytes = 0
         self.num_tokens_run = 0
 
     # ---- metadata transfer ----------------------------------------------------------------
     def _upload(self, pack: _Pack) -> dict[str, torch.Tensor]:
         n = len(pack.data)
+        self.last_h2d_bytes = 4 * n
         src = torch.tensor(pack.data, dtype=torch.int32)
         if not self._on_gpu:
             dev = src.to(self.device)
@@ -80,13 +88,51 @@ class ModelRunner:
                 self._host_free[i].synchronize()      # the copy that last read this buffer is done
             self._host[i][:n].copy_(src)
             if self._dev_meta is None or self._dev_meta.numel() < n:
-                self._dev_meta = torch.empty(max(4096, 2 * n), dtype=torch.int32, device=self.device)
+                self._dev_meta = torch.empty(max(1 << 18, 2 * n), dtype=torch.int32, device=self.device)
+                self._graphs.clear()                  # captured steps point into the old buffer
             dev = self._dev_meta[:n]
             dev.copy_(self._host[i][:n], non_blocking=True)
             ev = torch.cuda.Event()
             ev.record()
             self._host_free[i] = ev
         return {name: dev[off:off + cnt] for name, off, cnt in pack.parts}
+
+    def _forward(self, ctx: StepContext, graph_key) -> Optional[torch.Tensor]:
+        if graph_key is None:
+            return self.model.forward(ctx, self.cache)
+        if graph_key not in self._graphs:
+            self._graphs[graph_key] = None                # first time: run eagerly (also sizes the arena)
+            return self.model.forward(ctx, self.cache)
+        entry = self._graphs[graph_key]
+        if entry is None:
+            if len(self._graphs) > 512:                   # many shapes: drop the oldest captures
+                for k in list(self._graphs)[:256]:
+                    del self._graphs[k]
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launch_count
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(ctx, self.cache)
+            entry = (graph, logits, ops.launch_count - before, self.arena.buffer)
+            self._graphs[graph_key] = entry
+        graph, logits, launches, arena_buffer = entry
+        if arena_buffer is not self.arena.buffer:         # the arena grew since: capture again
+            self._graphs[graph_key] = None
+            return self._forward(ctx, graph_key)
+        graph.replay()
+        ops.launch_count += launches
+        self.num_graph_replays += 1
+        return logits
+
+    @staticmethod
+    def _device_plan(plan: dict, dev: dict, geometries) -> dict:
+        """The plan's lists as device tensors, plus what the host keeps: which geometry has which
+        index, and the small ``*_info`` lists as Python ints."""
+        out = {k: dev["plan_" + k] for k in plan}
+        out["geometry_index"] = {g: i for i, g in enumerate(geometries)}
+        for k, v in plan.items():
+            if k.endswith("_info"):
+                out[k + "_host"] = list(v)
+        return out
 
     # ---- the step -------------------------------------------------------------------------
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
@@ -138,6 +184,19 @@ class ModelRunner:
             logit_rows.extend(base + int(w) for w in e.want)
         T, R, N = cu_q[-1], len(entries), len(logit_rows)
 
+        # A step of single decoded tokens has a shape that recurs: it is captured in a CUDA graph
+        # the second time the shape is seen and replayed from then on.  Everything the kernels
+        # read that changes from step to step lives in the metadata buffer.
+        graph_key = None
+        uniform_splits = None
+        if self.use_cuda_graphs and all(n == 1 for n in q_lens):
+            B = self.GRAPH_BLOCK_BUCKET
+            buckets = tuple(-(-max(len(e.cache.tables[g.index]) for e in entries) // B) * B
+                            for g in cache.paged_groups)
+            graph_key = (R, N, buckets)
+            uniform_splits = ops.decode_splits(R, max(buckets, default=B) * cache.page_size,
+                                               self.model.attention_geometries, self.dtype)
+
         pack = _Pack()
         pack.add("token_ids", token_ids)
         pack.add("positions", positions)
@@ -146,8 +205,10 @@ class ModelRunner:
         pack.add("slot_ids", slot_ids)
         pack.add("logit_rows", logit_rows)
         max_blocks: dict[int, int] = {}
-        for g in cache.paged_groups:
+        for gi, g in enumerate(cache.paged_groups):
             mb = max(len(e.cache.tables[g.index]) for e in entries)
+            if graph_key is not None:
+                mb = graph_key[2][gi]
             max_blocks[g.index] = mb
             flat: list[int] = []
             slots: list[int] = []
@@ -158,7 +219,9 @@ class ModelRunner:
                 slots.extend(cache.slot_mapping(e.cache, g.index))
             pack.add(f"bt{g.index}", flat)
             pack.add(f"sm{g.index}", slots)
-        plan = ops.plan_attention(q_lens, ctx_lens, cache.page_size)
+        geometries = self.model.attention_geometries
+        plan = ops.plan_attention(q_lens, ctx_lens, cache.page_size, geometries, self.dtype,
+                                  uniform_splits=uniform_splits)
         for name, values in plan.items():
             pack.add("plan_" + name, values)
         dev = self._upload(pack)
@@ -175,8 +238,8 @@ class ModelRunner:
             token_ids=dev["token_ids"], positions=dev["positions"], cu_q=dev["cu_q"],
             ctx_lens=dev["ctx_lens"], slot_ids=dev["slot_ids"], logit_rows=dev["logit_rows"],
             num_logit_rows=N, groups=groups, q_lens_host=q_lens, ctx_lens_host=ctx_lens,
-            arena=self.arena, attn_plan={k: dev["plan_" + k] for k in plan})
-        logits = self.model.forward(ctx, cache)
+            arena=self.arena, attn_plan=self._device_plan(plan, dev, geometries))
+        logits = self._forward(ctx, graph_key)
         for e in entries:
             cache.commit(e.cache)
         self.num_steps += 1

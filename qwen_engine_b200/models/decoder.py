@@ -83,6 +83,12 @@ class DecoderModel:
             if specs[slot] is not None and n != 1:
                 raise ValueError(f"cache slot {slot} must be written by exactly one plan entry, not {n}")
         self._cache_specs = specs
+        geos = []
+        for b in self.blocks:
+            geo = b.mixer.attention_geometry()
+            if geo is not None and geo not in geos:
+                geos.append(geo)
+        self.attention_geometries = tuple(geos)
 
     # ---- what the cache manager and the loader ask --------------------------------------
     def cache_specs(self) -> list[Optional[CacheSpec]]:

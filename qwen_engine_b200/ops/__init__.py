@@ -19,6 +19,11 @@ _DT = {torch.float32: 0, torch.bfloat16: 1}
 _lib = None
 
 ATTN_TILE_Q = 16        # queries per work item of the generic attention kernel
+SMALL_M_MAX = 64        # rows up to which the weight-streaming product is used
+FLASH_ROWS = 64         # rows (query token x query head of a group) per work item of the flash kernel
+FLASH_BN = 64           # keys per tile of the flash kernel
+FLASH_SPLIT = 256       # keys per part when a decoded token's context is split (reference attn.py:605)
+FLASH_TARGET_CTAS = 296  # two CTAs per SM: below this, long contexts are split to fill the GPU
 
 
 class ExtensionMissing(RuntimeError):
@@ -61,7 +66,12 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+launch_count = 0        # kernels launched through this module since import (read by the benchmark)
+
+
 def _check(rc: int, name: str) -> None:
+    global launch_count
+    launch_count += 1
     if rc != 0:
         msg = lib().qe_last_error().decode("utf-8", "replace")
         if rc == 1:
@@ -140,6 +150,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     _need(out.shape == (M, N) and out.dtype in (x.dtype, torch.float32), "linear: out must be [M, N] in x's dtype or float32")
     _need(x.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "linear: operands must be contiguous")
     out_f32 = int(out.dtype == torch.float32)
+    if x.dtype == torch.bfloat16 and M <= SMALL_M_MAX and K % 8 == 0:
+        # a few rows: stream every weight once through the tensor cores
+        _check(lib().qe_linear_small_m(_ptr(x), _ptr(w), _ptr(out), M, N, K, out_f32, _stream()), "linear")
+        return
     _check(lib().qe_linear_generic(_ptr(x), _ptr(w), _ptr(out), M, N, K, _dt(x), out_f32, _stream()), "linear")
 
 
@@ -195,29 +209,103 @@ def rope_neox(q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor, inv_fre
         _ptr(None), _ptr(None), T, Hq, Hkv, D, 1, 0, _dt(q), _stream()), "rope_neox")
 
 
-def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int) -> dict[str, list[int]]:
+def flash_supported(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
+    """Whether the tensor-core attention kernel takes this geometry (else the generic kernel runs)."""
+    return (dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256
+            and num_kv_heads >= 1 and num_heads % num_kv_heads == 0 and num_heads // num_kv_heads <= FLASH_ROWS)
+
+
+def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
+                   geometries=(), dtype: torch.dtype = torch.float32,
+                   uniform_splits: Optional[dict] = None) -> dict[str, list[int]]:
     """Work lists of the attention kernels for one step's batch, as named int32 lists that the
-    step function copies to the device with the rest of the step's metadata."""
+    step function copies to the device with the rest of the step's metadata.
+
+    ``geometries``: the (heads, kv heads, head size, window) of the model's attention layers.
+    ``tiles`` serves the generic kernel; for each geometry the flash kernel takes, ``fa<i>_items``
+    and ``fa<i>_merge`` hold its work and merge items and ``fa<i>_info`` = [parts, rows per part].
+    ``uniform_splits`` (geometry -> number of parts) fixes the number of parts of every request,
+    so that the lists depend on the batch's shape only (for steps replayed from a CUDA graph)."""
     tiles: list[int] = []
     for r, n in enumerate(q_lens):
         for q0 in range(0, n, ATTN_TILE_Q):
             tiles += [r, q0]
-    return {"tiles": tiles}
+    plan = {"tiles": tiles}
+    for gi, geo in enumerate(geometries):
+        Hq, Hkv, D, window = geo
+        if not flash_supported(dtype, Hq, Hkv, D):
+            continue
+        G = Hq // Hkv
+        tpt = FLASH_ROWS // G
+        base = sum(-(-n // tpt) for n in q_lens) * Hkv
+        items: list[int] = []
+        merge: list[int] = []
+        n_parts, part_rows = 0, 1
+        for r, (n, c) in enumerate(zip(q_lens, ctx_lens)):
+            total = c + n
+            if uniform_splits is not None:
+                splits = uniform_splits[geo]
+            else:
+                lo = (max(0, c - window + 1) // FLASH_BN) * FLASH_BN if window else 0
+                splits = 1
+                if n <= tpt and base < FLASH_TARGET_CTAS and total - lo > FLASH_SPLIT:
+                    splits = min(-(-(total - lo) // FLASH_SPLIT), -(-FLASH_TARGET_CTAS // base))
+            if splits > 1:
+                for sp in range(splits):
+                    items += [r, 0, 0, 0, n_parts + sp, splits, sp, 0]
+                merge += [r, 0, n_parts, splits]
+                n_parts += splits
+                part_rows = max(part_rows, n * G)
+            else:
+                for q0 in range(0, n, tpt):
+                    items += [r, q0, 0, total, -1, 0, 0, 0]
+        plan[f"fa{gi}_items"] = items
+        plan[f"fa{gi}_merge"] = merge
+        plan[f"fa{gi}_info"] = [n_parts, part_rows]
+    return plan
+
+
+def decode_splits(num_reqs: int, max_tokens: int, geometries, dtype: torch.dtype) -> dict:
+    """The fixed number of parts per request for a decode step of ``num_reqs`` requests whose block
+    tables hold up to ``max_tokens`` tokens: enough parts to fill the GPU, none shorter than a split."""
+    out = {}
+    for geo in geometries:
+        Hq, Hkv, D, window = geo
+        span = min(max_tokens, window) if window else max_tokens
+        want = -(-FLASH_TARGET_CTAS // max(1, num_reqs * Hkv))
+        out[geo] = max(1, min(want, -(-span // FLASH_SPLIT)))
+    return out
 
 
 def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: torch.Tensor, ctx,
                     out: torch.Tensor, scale: float, window: int, num_heads: int, num_kv_heads: int,
                     head_dim: int) -> None:
     """Attention of the step's queries (the q part of qkv [T, (Hq+2Hkv) D]) over the keys and values
-    of their requests in ``kv_pages``; out [T, Hq D].  ``ctx`` is the StepContext (cu_q, ctx_lens
-    and the plan that ``plan_attention`` made)."""
+    of their requests in ``kv_pages``; out [T, Hq D].  ``ctx`` is the StepContext (cu_q, ctx_lens,
+    the plan that ``plan_attention`` made, and the arena for the parts of split contexts)."""
     Hq, Hkv, D = num_heads, num_kv_heads, head_dim
     T = qkv.shape[0]
     _need(out.shape == (T, Hq * D) and out.is_contiguous() and out.dtype == qkv.dtype, "paged_attention: out must be [T, Hq D]")
     _need(kv_pages.dtype == qkv.dtype and kv_pages.dim() == 5 and kv_pages.is_contiguous(),
           "paged_attention: kv_pages must be [pages, 2, Hkv, page, D] in q's dtype")
     _i32(block_tables, "block_tables")
-    tiles = ctx.attn_plan["tiles"]
+    plan = ctx.attn_plan
+    key = plan.get("geometry_index", {}).get((Hq, Hkv, D, window))
+    if key is not None and f"fa{key}_items" in plan:
+        items, merge = plan[f"fa{key}_items"], plan[f"fa{key}_merge"]
+        n_parts, part_rows = plan[f"fa{key}_info_host"]
+        n_items, n_merge = items.numel() // 8, merge.numel() // 4
+        part_acc = part_ml = None
+        if n_parts:
+            part_acc = ctx.arena.alloc((n_parts * Hkv * part_rows, D), torch.float32)
+            part_ml = ctx.arena.alloc((n_parts * Hkv * part_rows, 2), torch.float32)
+        _check(lib().qe_flash_attention(
+            _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(block_tables), int(block_tables.shape[1]),
+            _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), _ptr(items), n_items, _ptr(merge), n_merge, _ptr(out),
+            _ptr(part_acc), _ptr(part_ml), int(part_rows), ctypes.c_float(scale), int(window), Hq, Hkv, D,
+            int(kv_pages.shape[3]), _stream()), "flash_attention")
+        return
+    tiles = plan["tiles"]
     n_tiles = tiles.numel() // 2
     _check(lib().qe_paged_attention_generic(
         _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(block_tables), int(block_tables.shape[1]),

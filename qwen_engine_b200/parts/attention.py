@@ -43,6 +43,9 @@ class GQAAttention(Mixer):
     def cache_spec(self):
         return PagedKVSpec(self.num_kv_heads, self.head_dim, self.window)
 
+    def attention_geometry(self):
+        return (self.num_heads, self.num_kv_heads, self.head_dim, self.window or 0)
+
     def weight_specs(self, prefix: str) -> list[WeightSpec]:
         specs = [
             WeightSpec(prefix + "q_proj.weight", (self.q_width, self.hidden_size), MATRIX),

@@ -169,6 +169,11 @@ class Mixer(Part):
     def cache_spec(self) -> Optional[CacheSpec]:
         return None
 
+    def attention_geometry(self) -> Optional[tuple[int, int, int, int]]:
+        """(heads, kv heads, head size, window or 0) if the mixer calls ``ops.paged_attention``:
+        the step function plans the attention kernels' work once per step for every geometry."""
+        return None
+
     def forward(self, ctx: StepContext, x: torch.Tensor, cache: Optional[torch.Tensor],
                 group: Optional[int], out: torch.Tensor, write_cache: bool = True) -> None:
         raise NotImplementedError

@@ -155,3 +155,33 @@ def mixed_steps(reqs, seed):
     return steps
 
 
+
+
+# ---- generation helpers ------------------------------------------------------------------------
+def make_engine(folder, name, dtype, device="cuda:0", **engine_kwargs):
+    """An LLMEngine over a model folder; on the CPU the caller has put the plain operations in
+    the place of the kernels."""
+    from qwen_engine_b200.config import EngineConfig
+    from qwen_engine_b200.engine.llm import LLMEngine
+    from qwen_engine_b200.engine.loading import load_model
+    kw = dict(dtype=dtype, device=device, block_size=TINY[name]["page"], max_model_len=128, max_num_seqs=4,
+              max_num_batched_tokens=64)
+    kw.update(engine_kwargs)
+    ec = EngineConfig(**kw)
+    loaded = load_model(folder, ec.dtype, ec.device, ec.block_size, ec.resolved_num_blocks(), ec.max_num_seqs,
+                        ec.enable_prefix_cache, check_device=(device != "cpu"))
+    return LLMEngine(loaded, ec)
+
+
+def plain_sampled_generate(folder, prompt, steps, temperature, top_k, seed, request_index):
+    """Generation by the plain implementation with the engine's sampling rule and the same
+    uniform numbers: recompute the whole sequence at every step."""
+    import ref_ops
+    from qwen_engine_b200.sampling import uniform_for
+    tokens, out = list(prompt), []
+    for i in range(steps):
+        row = plain_logits(folder, tokens)[-1]
+        nxt = ref_ops.sample_row(row, temperature, top_k, uniform_for(seed, request_index, i))
+        out.append(nxt)
+        tokens.append(nxt)
+    return out

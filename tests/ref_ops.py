@@ -87,7 +87,7 @@ def rope_neox(q, k, positions, inv_freq, rotary_dim):
     k.copy_(_rotate(k.to(torch.float32), positions, inv_freq, rotary_dim).to(k.dtype))
 
 
-def plan_attention(q_lens, ctx_lens, page_size):
+def plan_attention(q_lens, ctx_lens, page_size, geometries=(), dtype=None, uniform_splits=None):
     tiles = []
     for r, n in enumerate(q_lens):
         for q0 in range(0, n, ATTN_TILE_Q):

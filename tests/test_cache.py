@@ -1,0 +1,237 @@
+"""The cache manager on the host: no page lost, held twice or freed twice under random orders
+of requests; sharing of full pages, the private copy of a fully shared prompt's last page,
+reuse of freed pages, windows that give pages back early, state slots."""
+import random
+
+import pytest
+import torch
+
+from qwen_engine_b200.cache import (CacheManager, FixedStateSpec, OutOfPages, OutOfSlots, PagedKVSpec,
+                                    PagePool, StateSlotPool, hash_block)
+
+F32 = torch.float32
+
+
+def _manager(num_pages=16, page=4, slots=4, specs=None, prefix=True):
+    specs = specs or [PagedKVSpec(2, 8)] * 3
+    return CacheManager(specs, page, num_pages, slots, F32, "cpu", enable_prefix_cache=prefix)
+
+
+def _feed(cm, rc, tokens):
+    cm.append(rc, tokens)
+    cm.commit(rc)
+
+
+def test_pool_hands_out_page_zero_first_and_reuses_freed_pages():
+    pool = PagePool(4, 4)
+    a, b = pool.allocate(), pool.allocate()
+    assert (a, b) == (0, 1)
+    pool.release(a)
+    assert pool.allocate() == 0                      # a freed page is used again
+    pool.check_invariants({0: 1, 1: 1})
+
+
+def test_pool_refuses_double_free_and_bad_ids():
+    pool = PagePool(2, 4)
+    p = pool.allocate()
+    pool.release(p)
+    with pytest.raises(RuntimeError):
+        pool.release(p)
+    with pytest.raises(ValueError):
+        pool.release(7)
+    with pytest.raises(RuntimeError):
+        pool.retain(1)                               # never handed out
+    pool.allocate(), pool.allocate()
+    with pytest.raises(OutOfPages):
+        pool.allocate()
+
+
+def test_hash_chain_depends_on_parent_and_tokens():
+    h1 = hash_block(0, [1, 2, 3, 4])
+    assert h1 == hash_block(0, [1, 2, 3, 4])
+    assert h1 != hash_block(0, [1, 2, 3, 5])
+    assert hash_block(h1, [9, 9, 9, 9]) != hash_block(0, [9, 9, 9, 9])
+
+
+def test_groups_by_need_have_pages_of_their_own():
+    specs = [PagedKVSpec(2, 8), PagedKVSpec(2, 8, window=6), PagedKVSpec(2, 8), FixedStateSpec((3, 5)), None,
+             PagedKVSpec(1, 16)]
+    cm = CacheManager(specs, 4, 10, 3, F32, "cpu")
+    assert [g.cache_slots for g in cm.groups] == [[0, 2], [1], [3], [5]]
+    assert cm.groups[0].tensor.shape == (2, 10, 2, 2, 4, 8)
+    assert cm.groups[2].tensor.shape == (1, 3, 3, 5)
+    assert cm.layer_view(2).shape == (10, 2, 2, 4, 8) and cm.layer_view(4) is None
+    assert not cm.prefix_cache                        # a window and a state rule sharing out
+    rc = cm.open("a")
+    _feed(cm, rc, list(range(9)))
+    assert len(rc.tables[0]) == 3 and len(rc.tables[1]) == 3 and len(rc.tables[3]) == 3
+    cm.check_invariants()
+
+
+def test_window_gives_pages_back_while_the_request_runs():
+    cm = CacheManager([PagedKVSpec(1, 8, window=6)], 4, 8, 2, F32, "cpu")
+    rc = cm.open("a")
+    _feed(cm, rc, list(range(5)))                     # next query at 5 needs keys >= 0
+    assert rc.tables[0] == [0, 1]
+    _feed(cm, rc, list(range(5)))                     # next query at 10 needs keys >= 5: page 0 (keys 0-3) goes
+    assert rc.tables[0][0] == -1 and rc.tables[0][1:] == [1, 2]
+    assert cm.groups[0].pool.num_free == 6
+    for _ in range(30):                               # long decoding in constant space
+        _feed(cm, rc, [1])
+        assert sum(p >= 0 for p in rc.tables[0]) <= 3
+        cm.check_invariants()
+    cm.close(rc)
+    assert cm.pages_in_use() == 0
+
+
+def test_full_pages_are_shared_and_the_last_token_is_left_to_compute():
+    cm = _manager()
+    a = cm.open("a", known_tokens=list(range(10)))
+    assert a.num_tokens == 0
+    _feed(cm, a, list(range(10)))                     # pages 0,1 full (tokens 0-7), page 2 partial
+    b = cm.open("b", known_tokens=list(range(8)) + [77, 78])
+    assert b.num_tokens == 8 and b.tables[0] == a.tables[0][:2]
+    pool = cm.groups[0].pool
+    assert pool.refcounts[a.tables[0][0]] == 2
+    _feed(cm, b, [77, 78])
+    assert b.tables[0][2] != a.tables[0][2]
+    cm.check_invariants()
+    # a prompt that is found whole: its last page is copied, one token is left to run
+    c = cm.open("c", known_tokens=list(range(8)))
+    assert c.num_tokens == 7 and c.tables[0][0] == a.tables[0][0] and c.tables[0][1] not in a.tables[0]
+    assert cm.take_page_copies() == [(0, a.tables[0][1], c.tables[0][1])]
+    _feed(cm, c, [7])
+    cm.check_invariants()
+    for rc in (a, b, c):
+        cm.close(rc)
+    assert cm.pages_in_use() == 0
+    cm.check_invariants()
+
+
+def test_a_page_is_sharable_only_once_it_is_full_and_written():
+    cm = _manager()
+    a = cm.open("a", known_tokens=list(range(8)))
+    cm.append(a, list(range(8)))                      # appended, step not yet run
+    b = cm.open("b", known_tokens=list(range(8)))
+    assert b.num_tokens == 0                          # nothing to share yet
+    cm.commit(a)
+    cm.close(b)
+    c = cm.open("c", known_tokens=list(range(8)) + [1])
+    assert c.num_tokens == 8
+
+
+def test_freed_pages_stay_findable_until_they_are_reused():
+    cm = _manager(num_pages=4)
+    a = cm.open("a")
+    _feed(cm, a, list(range(8)))
+    cm.close(a)
+    assert cm.pages_in_use() == 0
+    b = cm.open("b", known_tokens=list(range(8)) + [5])
+    assert b.num_tokens == 8                          # found although its owner is gone
+    cm.close(b)
+    c = cm.open("c")
+    _feed(cm, c, [9] * 16)                            # takes all four pages: the hashes are dropped
+    cm.close(c)
+    d = cm.open("d", known_tokens=list(range(8)) + [5])
+    assert d.num_tokens == 0
+    cm.check_invariants()
+
+
+def test_max_shared_tokens_limits_the_match():
+    cm = _manager()
+    a = cm.open("a")
+    _feed(cm, a, list(range(12)))
+    b = cm.open("b", known_tokens=list(range(12)), max_shared_tokens=5)
+    assert b.num_tokens == 4
+
+
+def test_append_is_all_or_nothing():
+    cm = _manager(num_pages=3)
+    a = cm.open("a")
+    _feed(cm, a, list(range(6)))
+    b = cm.open("b")
+    with pytest.raises(OutOfPages):
+        cm.append(b, list(range(9)))
+    assert b.tables[0] == [] and cm.groups[0].pool.num_free == 1
+    cm.check_invariants()
+    assert cm.can_append(b, 4) and not cm.can_append(b, 5)
+    assert not cm.can_append(b, 4, reserved={0: 1})
+
+
+def test_state_slots():
+    pool = StateSlotPool(2)
+    a, b = pool.allocate(), pool.allocate()
+    assert {a, b} == {0, 1}
+    with pytest.raises(OutOfSlots):
+        pool.allocate()
+    pool.release(a)
+    with pytest.raises(RuntimeError):
+        pool.release(a)
+    assert pool.allocate() == a
+    cm = CacheManager([FixedStateSpec((4,)), PagedKVSpec(1, 8)], 4, 8, 2, F32, "cpu")
+    r1, r2 = cm.open(1), cm.open(2)
+    with pytest.raises(OutOfSlots):
+        cm.open(3)
+    cm.groups[0].tensor.fill_(5.0)
+    cm.zero_fresh_state([r1])
+    assert float(cm.groups[0].tensor[0, r1.state_slot].abs().sum()) == 0
+    assert float(cm.groups[0].tensor[0, r2.state_slot].sum()) == 20.0
+    cm.close(r1)
+    r3 = cm.open(3)
+    assert r3.state_slot == r1.state_slot and r3.fresh_state
+
+
+def test_closing_twice_is_refused():
+    cm = _manager()
+    a = cm.open("a")
+    cm.close(a)
+    with pytest.raises(RuntimeError):
+        cm.close(a)
+    with pytest.raises(RuntimeError):
+        cm.append(a, [1])
+
+
+@pytest.mark.parametrize("seed", range(6))
+@pytest.mark.parametrize("prefix", [True, False])
+def test_random_orders_keep_every_page_accounted_for(seed, prefix):
+    rng = random.Random(seed)
+    specs = [PagedKVSpec(2, 8)] * 2 if prefix else [PagedKVSpec(2, 8), PagedKVSpec(2, 8, window=7)]
+    cm = CacheManager(specs, 4, 24, 5, F32, "cpu", enable_prefix_cache=prefix)
+    prompts = [[rng.randrange(3) for _ in range(rng.randrange(1, 30))] for _ in range(6)]  # few symbols: prefixes collide
+    live, next_id = {}, 0
+    for _ in range(400):
+        op = rng.random()
+        if op < 0.25 and len(live) < 5:
+            toks = list(rng.choice(prompts))
+            try:
+                rc = cm.open(next_id, known_tokens=toks)
+            except OutOfPages:
+                continue
+            live[next_id] = (rc, toks)
+            next_id += 1
+        elif op < 0.8 and live:
+            rid = rng.choice(list(live))
+            rc, toks = live[rid]
+            rest = toks[rc.num_tokens:]
+            new = rest[:rng.randrange(1, 9)] if rest else [rng.randrange(3)]
+            try:
+                cm.append(rc, new)
+            except OutOfPages:
+                victim = rng.choice(list(live))
+                cm.close(live.pop(victim)[0])
+            else:
+                if rng.random() < 0.1:
+                    cm.abort_pending(rc)
+                else:
+                    cm.commit(rc)
+                    if not rest:
+                        toks.extend(new)
+        elif live:
+            rid = rng.choice(list(live))
+            cm.close(live.pop(rid)[0])
+        cm.check_invariants()
+        cm.take_page_copies()
+    for rc, _ in live.values():
+        cm.close(rc)
+    cm.check_invariants()
+    assert cm.pages_in_use() == 0 and cm.slots.num_free == 5

@@ -1,0 +1,140 @@
+"""Generation through the Python entry point on the GPU against the plain implementation:
+greedy and sampled workloads of the two tiny configurations, long decoding, the first tokens of
+a sequence, preemption, and the command line."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import helpers
+import plain_qwen3
+from helpers import assert_close_logits, make_engine, plain_logits, plain_sampled_generate, random_tokens
+from qwen_engine_b200.sampling import SamplingParams
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _plain_greedy(folder, prompt, steps):
+    cfg, w = plain_qwen3.read_model_folder(folder)
+    return plain_qwen3.greedy_generate(cfg, w, prompt, steps)
+
+
+def _margin_ok(folder, prompt, out, min_margin):
+    """Whether every greedy choice of the plain implementation was clear by min_margin (else a
+    bfloat16 run may rightly pick the runner-up)."""
+    toks = list(prompt)
+    for t in out:
+        top2 = torch.topk(plain_logits(folder, toks)[-1], 2).values
+        if float(top2[0] - top2[1]) < min_margin:
+            return False
+        toks.append(t)
+    return True
+
+
+@pytest.mark.parametrize("name", ["tiny-a", "tiny-b", "tiny-c"])
+def test_greedy_generation_float32(model_folders, name):
+    from qwen_engine_b200 import LLM
+    folder = model_folders[name]
+    V = helpers.vocab_of(name)
+    prompts = [random_tokens(V, n, 70 + n) for n in (5, 9, 13)]
+    llm = LLM(folder, dtype="float32", block_size=helpers.TINY[name]["page"], max_model_len=64)
+    outs = llm.generate(prompts, SamplingParams(max_new_tokens=8))
+    for o, p in zip(outs, prompts):
+        assert o.prompt_token_ids == p and o.finish_reason == "length"
+        assert o.output_token_ids == _plain_greedy(folder, p, 8)
+
+
+@pytest.mark.parametrize("name", ["tiny-a", "tiny-b"])
+def test_greedy_generation_bfloat16(model_folders, name):
+    """In bfloat16 the tokens are compared where the plain choice is clear; prompts whose plain
+    run has a near tie are skipped, not excused."""
+    from qwen_engine_b200 import LLM
+    folder = model_folders[name]
+    V = helpers.vocab_of(name)
+    llm = LLM(folder, dtype="bfloat16", block_size=helpers.TINY[name]["page"], max_model_len=64)
+    checked = 0
+    for seed in range(12):
+        p = random_tokens(V, 6 + seed, 300 + seed)
+        want = _plain_greedy(folder, p, 8)
+        if not _margin_ok(folder, p, want, 2 * helpers.TOL[torch.bfloat16] * max(1.0, float(plain_logits(folder, p).abs().max()))):
+            continue
+        got = llm.generate([p], SamplingParams(max_new_tokens=8))[0].output_token_ids
+        assert got == want
+        checked += 1
+    assert checked >= 2
+
+
+def test_sampled_workload_of_tiny_b(model_folders):
+    name = "tiny-b"
+    folder = model_folders[name]
+    V = helpers.vocab_of(name)
+    common = random_tokens(V, 16, 80)
+    prompts = [random_tokens(V, 3, 81), common + random_tokens(V, 1, 82), common + random_tokens(V, 8, 83),
+               random_tokens(V, 31, 84)]
+    eng = make_engine(folder, name, torch.float32, prefill_chunk_size=7, max_num_batched_tokens=16, seed=5,
+                      max_num_seqs=2)   # the third request is admitted once the second has filled its pages
+    sp = SamplingParams(max_new_tokens=6, temperature=0.8, top_k=20, seed=5)
+    ids = [eng.add_request(p, sp) for p in prompts]
+    outs = {o.request_id: o for o in eng.serving()}
+    for i, p in zip(ids, prompts):
+        assert outs[i].output_token_ids == plain_sampled_generate(folder, p, 6, 0.8, 20, 5, i)
+    assert eng.stats.prefix_hit_tokens >= 16
+
+
+def test_preemption_on_the_gpu(model_folders):
+    name = "tiny-a"
+    folder = model_folders[name]
+    V = helpers.vocab_of(name)
+    prompts = [random_tokens(V, 10, 90 + i) for i in range(3)]
+    eng = make_engine(folder, name, torch.float32, num_blocks=12, max_model_len=32, enable_prefix_cache=False)
+    ids = eng.submit(prompts, max_new_tokens=14)
+    outs = {o.request_id: o for o in eng.serving()}
+    assert eng.stats.preemptions >= 1
+    for i, p in zip(ids, prompts):
+        assert outs[i].output_token_ids == _plain_greedy(folder, p, 14)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_long_decoding(model_folders, dtype):
+    """400 tokens decoded one by one after a short prompt (teacher-forced, so that both dtypes
+    walk the same path); logits compared every 25 steps and at the end."""
+    name = "tiny-b"
+    folder = model_folders[name]
+    V = helpers.vocab_of(name)
+    toks = random_tokens(V, 420, 123)
+    rep = helpers.make_replayer(folder, name, dtype, 448)
+    steps = [{"entries": [{"id": "r", "tokens": toks[:20], "want": [19]}]}]
+    for i in range(20, 420):
+        steps.append({"entries": [{"id": "r", "tokens": [toks[i]], "want": [0] if (i % 25 == 0 or i == 419) else []}]})
+    got = helpers.run_steps(rep, steps)
+    helpers.check_requests(got, folder, {"r": toks}, dtype, "long decode")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", ["tiny-a", "tiny-b", "tiny-c"])
+def test_first_tokens_of_a_sequence(model_folders, name, dtype):
+    """Positions 0, 1, 2: a single token as a whole request, then one by one."""
+    folder = model_folders[name]
+    V = helpers.vocab_of(name)
+    toks = random_tokens(V, 3, 77)
+    rep = helpers.make_replayer(folder, name, dtype, 128)
+    got = helpers.run_steps(rep, [{"entries": [{"id": "r", "tokens": [t], "want": [0]}]} for t in toks])
+    helpers.check_requests(got, folder, {"r": toks}, dtype, "first tokens")
+    got = helpers.run_steps(rep, [{"entries": [{"id": "s", "tokens": toks[:1], "want": [0]}], "end": ["s"]}])
+    assert_close_logits(got["s"][0][None], plain_logits(folder, toks[:1]), dtype, "one token")
+
+
+def test_command_line(model_folders):
+    name = "tiny-a"
+    folder = model_folders[name]
+    prompt = random_tokens(helpers.vocab_of(name), 7, 5)
+    proc = subprocess.run(
+        [sys.executable, os.path.join(ROOT, "main.py"), "--model-name-or-path", folder, "--dtype", "float32",
+         "--prompt-ids", ",".join(map(str, prompt)), "--max-new-tokens", "5", "--block-size", "4", "--stats"],
+        capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    want = " ".join(str(t) for t in _plain_greedy(folder, prompt, 5))
+    assert want in proc.stdout

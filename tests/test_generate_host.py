@@ -1,0 +1,83 @@
+"""Generation through the engine on the CPU (plain operations in the place of the kernels): the
+scheduler, the step function, the cache and the sampler's host side against the plain
+implementation.  The same workloads run on the GPU in tests/test_generate_gpu.py."""
+import pytest
+import torch
+
+import helpers
+import plain_qwen3
+from helpers import make_engine, plain_sampled_generate, random_tokens
+from qwen_engine_b200.sampling import SamplingParams, uniform_for
+
+F32 = torch.float32
+
+
+def _plain_greedy(folder, prompt, steps):
+    cfg, w = plain_qwen3.read_model_folder(folder)
+    return plain_qwen3.greedy_generate(cfg, w, prompt, steps)
+
+
+def test_greedy_workload_of_tiny_a(model_folders, cpu_ops):
+    """Three prompts of 5, 9 and 13 tokens, 8 greedy steps each."""
+    folder = model_folders["tiny-a"]
+    V = helpers.vocab_of("tiny-a")
+    prompts = [random_tokens(V, n, 70 + n) for n in (5, 9, 13)]
+    eng = make_engine(folder, "tiny-a", F32, device="cpu")
+    ids = eng.submit(prompts, max_new_tokens=8)
+    outs = {o.request_id: o for o in eng.serving()}
+    for i, p in zip(ids, prompts):
+        assert outs[i].output_token_ids == _plain_greedy(folder, p, 8)
+        assert outs[i].finish_reason == "length"
+    assert eng.cache.pages_in_use() == 0
+
+
+def test_sampled_workload_of_tiny_b(model_folders, cpu_ops):
+    """Four prompts of 3, 17, 24 and 31 tokens, two sharing 16 tokens; portions of 7 mixed with
+    decoded tokens; 6 steps at temperature 0.8 with a fixed seed."""
+    name = "tiny-b"
+    folder = model_folders[name]
+    V = helpers.vocab_of(name)
+    common = random_tokens(V, 16, 80)
+    prompts = [random_tokens(V, 3, 81), common + random_tokens(V, 1, 82), common + random_tokens(V, 8, 83),
+               random_tokens(V, 31, 84)]
+    eng = make_engine(folder, name, F32, device="cpu", prefill_chunk_size=7, max_num_batched_tokens=16, seed=5,
+                      max_num_seqs=2)   # the third request is admitted once the second has filled its pages
+    sp = SamplingParams(max_new_tokens=6, temperature=0.8, top_k=20, seed=5)
+    ids = [eng.add_request(p, sp) for p in prompts]
+    outs = {o.request_id: o for o in eng.serving()}
+    for i, p in zip(ids, prompts):
+        assert outs[i].output_token_ids == plain_sampled_generate(folder, p, 6, 0.8, 20, 5, i)
+    assert eng.stats.prefix_hit_tokens >= 16
+    assert eng.stats.prefill_tokens + eng.stats.prefix_hit_tokens >= sum(len(p) for p in prompts)
+
+
+def test_preemption_does_not_change_the_tokens(model_folders, cpu_ops):
+    name = "tiny-a"
+    folder = model_folders[name]
+    V = helpers.vocab_of(name)
+    prompts = [random_tokens(V, 10, 90 + i) for i in range(3)]
+    # 3 requests of up to 10 + 14 tokens need 18 pages of 4; with 12 someone has to wait
+    eng = make_engine(folder, name, F32, device="cpu", num_blocks=12, max_model_len=32, enable_prefix_cache=False)
+    ids = eng.submit(prompts, max_new_tokens=14)
+    outs = {o.request_id: o for o in eng.serving()}
+    assert eng.stats.preemptions >= 1
+    for i, p in zip(ids, prompts):
+        assert outs[i].output_token_ids == _plain_greedy(folder, p, 14)
+    assert eng.cache.pages_in_use() == 0
+
+
+def test_uniform_numbers_are_a_function_of_seed_request_and_position():
+    assert uniform_for(1, 2, 3) == uniform_for(1, 2, 3)
+    vals = {uniform_for(s, r, p) for s in range(3) for r in range(3) for p in range(3)}
+    assert len(vals) == 27 and all(0.0 <= v < 1.0 for v in vals)
+    assert torch.tensor(uniform_for(9, 9, 9), dtype=torch.float32).item() == uniform_for(9, 9, 9)
+
+
+def test_bad_requests_are_refused(model_folders, cpu_ops):
+    eng = make_engine(model_folders["tiny-a"], "tiny-a", F32, device="cpu")
+    with pytest.raises(ValueError, match="vocabulary"):
+        eng.add_request([1, 2, 999999])
+    with pytest.raises(ValueError, match="tokenizer"):
+        eng.add_request("some text")
+    with pytest.raises(ValueError):
+        eng.add_request(list(range(1, 200)))

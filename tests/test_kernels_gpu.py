@@ -75,7 +75,9 @@ def test_add_rmsnorm(dtype, T, H, with_delta):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("M,N,K", [(1, 17, 5), (3, 389, 80), (70, 130, 224), (129, 64, 1000), (16, 1030, 72)])
+@pytest.mark.parametrize("M,N,K", [(1, 17, 5), (3, 389, 80), (70, 130, 224), (129, 64, 1000), (16, 1030, 72),
+                                   (8, 4096, 1024), (64, 1000, 3072), (33, 389, 224), (1, 20011, 64), (17, 24, 2048),
+                                   (9, 130, 8), (40, 16, 1032)])
 @pytest.mark.parametrize("out_f32", [False, True])
 def test_linear(dtype, M, N, K, out_f32):
     x = _randn((M, K), dtype, 6)
@@ -174,14 +176,22 @@ def _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, seed, spike=
                 ctx=torch.tensor(ctx_lens, dtype=torch.int32), T=T)
 
 
-def _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, fn, dev):
+def _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, fn, dev, flash=True):
+    """Run one implementation.  On the GPU ``flash`` lets the step's plan carry the tensor-core
+    kernel's work items (used when the kernel takes the geometry); without it the generic kernel runs."""
+    from qwen_engine_b200.engine.runner import ModelRunner
+    from qwen_engine_b200.parts.base import Arena
     scale = 1.0 / math.sqrt(D)
-    plan = ops.plan_attention(list(q_lens), list(ctx_lens), P)
-    ctx = SimpleNamespace(cu_q=case["cu_q"].to(dev), ctx_lens=case["ctx"].to(dev),
-                          attn_plan={k: torch.tensor(v, dtype=torch.int32, device=dev) for k, v in plan.items()},
-                          q_lens_host=list(q_lens), ctx_lens_host=list(ctx_lens))
+    geos = ((Hq, Hkv, D, window),) if (flash and dev != "cpu") else ()
+    plan = ops.plan_attention(list(q_lens), list(ctx_lens), P, geos, dtype)
+    devplan = ModelRunner._device_plan(
+        plan, {"plan_" + k: torch.tensor(v, dtype=torch.int32, device=dev) for k, v in plan.items()}, geos)
+    ctx = SimpleNamespace(cu_q=case["cu_q"].to(dev), ctx_lens=case["ctx"].to(dev), attn_plan=devplan,
+                          q_lens_host=list(q_lens), ctx_lens_host=list(ctx_lens), arena=Arena(dev))
     out = torch.zeros(case["T"], Hq * D, dtype=dtype, device=dev)
     fn(case["qkv"].to(dev), case["cache"].to(dev), case["table"].to(dev), ctx, out, scale, window, Hq, Hkv, D)
+    if dev != "cpu":
+        torch.cuda.synchronize()
     return out
 
 
@@ -199,11 +209,30 @@ ATTN_BATCHES = [
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("Hq,Hkv,D,P", ATTN_SHAPES)
 @pytest.mark.parametrize("q_lens,ctx_lens", ATTN_BATCHES)
-def test_paged_attention(dtype, Hq, Hkv, D, P, q_lens, ctx_lens):
+@pytest.mark.parametrize("flash", [False, True])
+def test_paged_attention(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, flash):
+    """flash=False: the generic kernel (the 32-bit path's, and the fallback); flash=True: the
+    tensor-core kernel where it takes the geometry (bfloat16), with split contexts merged."""
+    if flash and not ops.flash_supported(dtype, Hq, Hkv, D):
+        pytest.skip("the generic kernel serves this case")
     case = _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, seed=21)
     want = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, ref_ops.paged_attention, "cpu")
-    got = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, ops.paged_attention, DEV)
+    got = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, ops.paged_attention, DEV, flash=flash)
     _close(got, want, dtype, tol32=2e-5, tol16=1.6e-2)
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,P", [(16, 8, 128, 16), (4, 1, 32, 8), (6, 2, 48, 4), (8, 1, 64, 16)])
+@pytest.mark.parametrize("q_lens,ctx_lens", [([1], [1024]), ([1, 1], [257, 2000]), ([3, 1], [700, 511]),
+                                             ([1] * 8, [1024] * 8), ([70, 1], [300, 900])])
+def test_flash_attention_split_contexts(Hq, Hkv, D, P, q_lens, ctx_lens):
+    """Long contexts of decoded tokens are cut into parts that are merged afterwards."""
+    dtype = torch.bfloat16
+    plan = ops.plan_attention(list(q_lens), list(ctx_lens), P, ((Hq, Hkv, D, 0),), dtype)
+    assert plan["fa0_info"][0] > 1, "the case must split"
+    case = _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, seed=24)
+    want = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, ref_ops.paged_attention, "cpu")
+    got = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, ops.paged_attention, DEV)
+    _close(got, want, dtype)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
