@@ -131,6 +131,8 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--dtype", default="bfloat16")
+    ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
+                    help="bracket that timed region with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -172,7 +174,14 @@ def main() -> int:
     def tokens(n):
         return [rng.randrange(V) for _ in range(n)]
 
-    def timed(fn, n_iter):
+    def timed(fn, n_iter, what=None):
+        if what is not None and what == args.profile:
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()
+            try:
+                return timed(fn, n_iter)
+            finally:
+                torch.cuda.profiler.stop()
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
@@ -197,7 +206,7 @@ def main() -> int:
     for _ in range(args.warmup):
         prefill_once()
     m0 = clocks.mark()
-    prefill_ms = timed(prefill_once, 5)
+    prefill_ms = timed(prefill_once, 5 if args.profile is None else 1, "prefill")
     spans.append((m0, clocks.mark()))
     c = cfg
     gemm_params = c.num_hidden_layers * (c.hidden_size * (c.q_width + 2 * c.kv_width) + c.q_width * c.hidden_size
@@ -217,7 +226,7 @@ def main() -> int:
     kv_bytes_per_token = sum(g.tensor[:, 0].numel() // g.tensor.shape[4] * g.tensor.element_size()
                              for g in cache.paged_groups)      # all layers, K and V, one token
 
-    def decode_rate(batch, steps, warmup, record=None):
+    def decode_rate(batch, steps, warmup, record=None, what=None):
         live = reqs[:batch]
 
         def one():
@@ -225,7 +234,7 @@ def main() -> int:
         for _ in range(warmup):
             one()
         l0, m = ops.launch_count, clocks.mark()
-        ms = timed(one, steps)
+        ms = timed(one, steps, what)
         if record is not None:
             record["launches"] = ops.launch_count - l0
             spans.append((m, clocks.mark()))
@@ -235,7 +244,7 @@ def main() -> int:
     if not args.no_points and big_batch >= 64:
         points["decode_b64"] = round(decode_rate(64, max(5, args.steps // 2), 3)[0], 1)
     rec = {}
-    value, ms_per_step = decode_rate(args.batch, args.steps, args.warmup, rec)
+    value, ms_per_step = decode_rate(args.batch, args.steps, args.warmup, rec, "decode")
     ctx_now = reqs[0].num_tokens
     step_bytes = weight_bytes + args.batch * ctx_now * kv_bytes_per_token
     achieved = step_bytes / (ms_per_step / 1e3) / 1e9

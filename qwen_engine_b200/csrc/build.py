@@ -115,7 +115,7 @@ def _compile(bdir: str, lib: str, verbose: bool) -> None:
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as pool:
         objs = list(pool.map(one, srcs))
     tmp = lib + f".tmp{os.getpid()}"
-    r = subprocess.run([nvcc, *ARCH_FLAGS, "-shared", "-o", tmp, *objs, "-lcuda"], capture_output=True, text=True)
+    r = subprocess.run([nvcc, *ARCH_FLAGS, "-shared", "-o", tmp, *objs], capture_output=True, text=True)
     if r.returncode != 0:
         raise BuildError(f"linking {lib} failed:\n{r.stdout}\n{r.stderr}")
     os.replace(tmp, lib)

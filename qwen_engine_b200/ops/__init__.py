@@ -20,6 +20,7 @@ _lib = None
 
 ATTN_TILE_Q = 16        # queries per work item of the generic attention kernel
 SMALL_M_MAX = 64        # rows up to which the weight-streaming product is used
+TCGEN05_ENABLED = True  # the tcgen05 product for more rows (False: the generic kernel serves them)
 FLASH_ROWS = 64         # rows (query token x query head of a group) per work item of the flash kernel
 FLASH_BN = 64           # keys per tile of the flash kernel
 FLASH_SPLIT = 256       # keys per part when a decoded token's context is split (reference attn.py:605)
@@ -154,7 +155,18 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         # a few rows: stream every weight once through the tensor cores
         _check(lib().qe_linear_small_m(_ptr(x), _ptr(w), _ptr(out), M, N, K, out_f32, _stream()), "linear")
         return
+    if x.dtype == torch.bfloat16 and M > SMALL_M_MAX and K % 8 == 0 and TCGEN05_ENABLED:
+        # many rows: TMA-fed tcgen05 tensor cores with the accumulator in tensor memory
+        _check(lib().qe_linear_tcgen05(_ptr(x), _ptr(w), _ptr(out), M, N, K, out_f32, _stream()), "linear")
+        return
     _check(lib().qe_linear_generic(_ptr(x), _ptr(w), _ptr(out), M, N, K, _dt(x), out_f32, _stream()), "linear")
+
+
+def tcgen05_status() -> int:
+    """0 if no bounded wait of the tcgen05 product kernel ever ran out; else the code of the first
+    that did (1: a shared-memory slot never came free, 2: TMA bytes never landed, 3: the
+    accumulator never completed).  Synchronises the device."""
+    return int(lib().qe_gemm_tc_status())
 
 
 def qk_norm_rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, q_norm_w: Optional[torch.Tensor],

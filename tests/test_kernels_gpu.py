@@ -90,6 +90,23 @@ def test_linear(dtype, M, N, K, out_f32):
     _close(got, want, odt, tol16=8e-3)
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 128, 256), (65, 128, 64), (300, 200, 136), (2048, 4096, 1024),
+                                   (130, 1000, 3072), (257, 389 * 8, 80), (1000, 24, 2048), (128, 6144, 1024)])
+@pytest.mark.parametrize("out_f32", [False, True])
+def test_linear_tcgen05(M, N, K, out_f32):
+    """More than 64 rows in bfloat16: the TMA + tcgen05 kernel, with edges in M, N and K."""
+    x = _randn((M, K), torch.bfloat16, 16)
+    w = _randn((N, K), torch.bfloat16, 17, 0.1)
+    odt = torch.float32 if out_f32 else torch.bfloat16
+    want = torch.empty(M, N, dtype=odt)
+    ref_ops.linear(x, w, want)
+    got = torch.empty(M, N, dtype=odt, device=DEV)
+    ops.linear(x.to(DEV), w.to(DEV), got)
+    torch.cuda.synchronize()
+    assert ops.tcgen05_status() == 0, "a bounded wait of the tcgen05 kernel ran out"
+    _close(got, want, odt, tol16=8e-3)
+
+
 def test_linear_row_does_not_depend_on_batch():
     """A row's product is the same bits whatever else is in the batch (32-bit path)."""
     x = _randn((67, 200), torch.float32, 8).to(DEV)
