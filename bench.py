@@ -105,17 +105,131 @@ class ClockSampler:
 
 
 def reference_arm(args) -> int:
-    """The reference arm: kzw3933/Qwen-Engine from baseline/_ref through its own public API."""
+    """The reference arm: the unmodified kzw3933/Qwen-Engine as installed into baseline/_ref
+    (pip install --no-deps --target), through its own classes and stock code path in
+    ``mode="triton"``: Qwen3Config defaults (Qwen3-0.6B) -> Qwen3ForCausalLM with its own random
+    initialisation -> KVCachePool -> ModelExecutor.run_prefill / run_decode_step -> its argmax
+    sampler, i.e. the body of its LLMEngine.serving loop (src/engine/llm_engine.py:101-145) with
+    the step count under the benchmark's control.  Token ids stand in for its tokenizer, which needs
+    the network.  Nothing of this repository's engine is imported."""
     ref = os.path.join(ROOT, "baseline", "_ref")
-    why = None
-    if not os.path.isdir(ref) or not os.listdir(ref):
-        why = ("not installed: the reference's pyproject.toml declares no packages (its sources are loose "
-               "folders under src/ reached by sys.path edits), so an offline pip install into baseline/_ref "
-               "yields no importable package")
-    else:
-        why = "baseline/_ref holds no importable engine package"
-    print(json.dumps({"impl": "reference", "unavailable": why}))
-    return 0
+    if not os.path.isdir(os.path.join(ref, "engine")) or not os.path.isdir(os.path.join(ref, "models")):
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "baseline/_ref does not hold the reference's engine and models packages (not installed)"}))
+        return 0
+    if args.gpus != 1:
+        print(json.dumps({"impl": "reference", "unavailable": "the reference is single-GPU"}))
+        return 0
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device")
+        sys.path.insert(0, ref)
+        from engine import KVCachePool                       # the reference's own packages
+        from engine.executor import ModelExecutor
+        from engine.sequence import Sequence
+        from models import Qwen3Config, Qwen3ForCausalLM
+        args.warmup = max(args.warmup, 3)
+        rng = random.Random(0)
+        cfg = Qwen3Config()
+        dev = torch.device("cuda:0")
+        torch.manual_seed(2)
+        t0 = time.time()
+        model = Qwen3ForCausalLM(**cfg.to_model_kwargs(), dtype=torch.bfloat16).to(dev).eval()
+        print(f"[bench reference] model ready in {time.time() - t0:.1f}s", file=sys.stderr, flush=True)
+        V, block = cfg.vocab_size, 16
+        extra = args.warmup + args.steps + 4
+        big = args.batch if args.no_points else max(args.batch, 64)
+        blocks = big * (-(-(args.context + 3 * extra) // block) + 1) + args.prefill_tokens // block + 8
+        pool = KVCachePool(num_layers=cfg.num_hidden_layers, num_blocks=blocks, block_size=block,
+                           num_kv_heads=cfg.num_key_value_heads, head_dim=cfg.head_dim, dtype=torch.bfloat16, device=dev)
+        ex = ModelExecutor(model, pool, dev, mode="triton")
+        sid = [0]
+
+        def new_seq(n):
+            sid[0] += 1
+            return Sequence(sid[0], "", [rng.randrange(V) for _ in range(n)])
+
+        def decode_step(seqs):
+            logits = ex.run_decode_step(seqs)                 # llm_engine.py:132-143
+            toks = ex.sample_next_tokens(logits)
+            for s, t in zip(seqs, toks):
+                s.output_token_ids.append(t)
+                s.num_computed_tokens += 1
+                s.num_kv_tokens += 1
+            ex.register_shared_blocks(seqs)
+
+        clocks = ClockSampler()
+        clocks.start()
+        spans = []
+        with torch.no_grad():
+            # prefill of one 2,048-token prompt (its executor computes logits for every row)
+            def prefill_once():
+                s = new_seq(args.prefill_tokens)
+                logits, ctx = ex.run_prefill([s])
+                ex.sample_next_tokens(ex.gather_prefill_last_logits(logits, ctx.cu_seqlens))
+                ex.release_sequence(s)
+            for _ in range(2):
+                prefill_once()
+            torch.cuda.synchronize()
+            m0 = clocks.mark()
+            t0 = time.perf_counter()
+            for _ in range(3):
+                prefill_once()
+            torch.cuda.synchronize()
+            prefill_ms = (time.perf_counter() - t0) / 3 * 1e3
+            spans.append((m0, clocks.mark()))
+
+            def decode_rate(batch, steps, warmup):
+                seqs = [new_seq(args.context) for _ in range(batch)]
+                for i in range(0, batch, 8):
+                    group = seqs[i:i + 8]
+                    logits, ctx = ex.run_prefill(group)
+                    toks = ex.sample_next_tokens(ex.gather_prefill_last_logits(logits, ctx.cu_seqlens))
+                    for s, t in zip(group, toks):                # llm_engine.py:115-119
+                        s.output_token_ids.append(t)
+                        s.num_computed_tokens = s.num_kv_tokens = s.prompt_len
+                for _ in range(warmup):
+                    decode_step(seqs)
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                m = clocks.mark()
+                t0 = time.perf_counter()
+                a.record()
+                for _ in range(steps):
+                    decode_step(seqs)
+                b.record()
+                torch.cuda.synchronize()
+                wall = time.perf_counter() - t0
+                spans.append((m, clocks.mark()))
+                for s in seqs:
+                    ex.release_sequence(s)
+                return batch * steps / (a.elapsed_time(b) / 1e3), a.elapsed_time(b) / steps, batch * steps / wall
+            value, ms_per_step, e2e_value = decode_rate(args.batch, args.steps, args.warmup)
+            points = {}
+            if not args.no_points:
+                points["decode_b1"] = round(decode_rate(1, args.steps, 3)[0], 1)
+                points["decode_b64"] = round(decode_rate(64, max(3, args.steps // 4), 2)[0], 1)
+        clocks.stop()
+        print(json.dumps({
+            "metric": "decode tok/s (Qwen3-0.6B, batch 8, context 1024)", "value": round(value, 1), "unit": "tokens/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "impl": "reference",
+            "data": "synthetic: uniform random token ids, the reference's own random initialisation",
+            "config": {"model": "qwen3-0.6b", "layers": cfg.num_hidden_layers, "hidden": cfg.hidden_size,
+                       "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+                       "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "global_batch": args.batch,
+                       "seq_len": args.context, "page_size": block, "prefill_tokens": args.prefill_tokens,
+                       "mode": "triton", "parallelism": "single GPU"},
+            "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s"},
+            "prefill": {"value": round(args.prefill_tokens / (prefill_ms / 1e3), 1), "tokens": args.prefill_tokens,
+                        "ms": round(prefill_ms, 3)},
+            "points": points, "clocks": clocks.summary(spans)}))
+        return 0
+    except Exception as e:          # noqa: BLE001 - the arm reports instead of failing the round
+        msg = f"{type(e).__name__}: {e}".replace("\n", " ")[:300]
+        print(json.dumps({"impl": "reference", "unavailable": f"the reference did not run here: {msg}"}))
+        return 0
 
 
 def main() -> int:
