@@ -350,3 +350,53 @@ extern "C" int qe_flash_attention(const void* q, long q_stride, const void* page
 #undef FA_CASE
   QE_REFUSE("flash_attention: head_dim %d is not supported", D);
 }
+
+// ---------------------------------------------------------------------------------------------------
+// The same attention for callers that must not allocate (see no_alloc.h): the parts of split
+// contexts go to a fixed array of this library instead of to memory the caller provides.
+// ---------------------------------------------------------------------------------------------------
+#include "no_alloc.h"
+
+// Device memory of the library itself: present on every GPU that loads it, until the process ends.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[QE_NOALLOC_SCRATCH_BYTES];
+
+#define QE_NOALLOC_MAX_DEVICES 64
+// In host code the name g_noalloc_scratch is only a handle for the runtime, not an address a kernel
+// can use; the device address is asked for once per device and kept here.
+static float* g_noalloc_scratch_addr[QE_NOALLOC_MAX_DEVICES] = {nullptr};
+
+extern "C" int qe_flash_attention_noalloc(const void* q, long q_stride, const void* pages, const int* block_tables,
+                                          int max_blocks, const int* cu_q, const int* ctx_lens, const int* items,
+                                          int n_items, const int* merge_items, int n_merge, void* out, int n_parts,
+                                          int part_rows, float scale, int window, int Hq, int Hkv, int D,
+                                          int page_size, cudaStream_t stream) {
+  if (n_items <= 0) return 0;
+  if (n_parts < 0 || part_rows < 1) QE_REFUSE("flash_attention_noalloc: bad part counts (%d parts of %d rows)", n_parts, part_rows);
+  if (!qe_flash_attention_supported(Hq, Hkv, D))
+    QE_REFUSE("flash_attention_noalloc: heads %d/%d with head_dim %d are not supported", Hq, Hkv, D);
+  // accumulators [slots][D] first, then (max, sum) pairs [slots][2], all float32
+  const size_t slots = (size_t)n_parts * Hkv * part_rows;
+  const size_t acc_bytes = (slots * D * sizeof(float) + 255) / 256 * 256;
+  const size_t need = acc_bytes + slots * 2 * sizeof(float);
+  if (need > QE_NOALLOC_SCRATCH_BYTES)
+    QE_REFUSE("flash_attention_noalloc: %d parts x %d kv heads x %d rows of head size %d need %zu bytes of scratch; "
+              "the library's fixed array holds %u", n_parts, Hkv, part_rows, D, need, QE_NOALLOC_SCRATCH_BYTES);
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) { qe_set_error("flash_attention_noalloc: cudaGetDevice: %s", cudaGetErrorString(e)); return 2; }
+  if (dev < 0 || dev >= QE_NOALLOC_MAX_DEVICES) QE_REFUSE("flash_attention_noalloc: device %d is outside 0..%d", dev, QE_NOALLOC_MAX_DEVICES - 1);
+  if (g_noalloc_scratch_addr[dev] == nullptr) {
+    // set-up, once per device, with that device current: the device address of the array
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      qe_set_error("flash_attention_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+      return 2;
+    }
+    g_noalloc_scratch_addr[dev] = static_cast<float*>(p);
+  }
+  float* part_acc = g_noalloc_scratch_addr[dev];
+  float* part_ml = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(part_acc) + acc_bytes);
+  return qe_flash_attention(q, q_stride, pages, block_tables, max_blocks, cu_q, ctx_lens, items, n_items, merge_items,
+                            n_merge, out, part_acc, part_ml, part_rows, scale, window, Hq, Hkv, D, page_size, stream);
+}
