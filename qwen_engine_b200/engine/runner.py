@@ -63,7 +63,7 @@ class ModelRunner:
         self._host_free: list[Optional[torch.cuda.Event]] = [None, None]
         self._dev_meta: Optional[torch.Tensor] = None
         self._flip = 0
-        self.use_cuda_graphs = bool(use_cuda_graphs) and self._on_gpu
+        self.use_cuda_graphs = bool(use_cuda_graphs) and self._on_gpu and getattr(model, "capturable", True)
         # decode steps by shape: None after the first (eager) run, then (graph, logits, launches)
         self._graphs: dict[tuple, Optional[tuple]] = {}
         self.num_graph_replays = 0

@@ -166,6 +166,10 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # False for a mixer whose forward reads device data on the host or allocates: steps of a model
+    # that holds such a mixer are never captured in a CUDA graph.
+    capturable = True
+
     def cache_spec(self) -> Optional[CacheSpec]:
         return None
 

@@ -1,0 +1,408 @@
+"""The parts a layer is put together from, each alone against the plain implementation; and that
+parts defined outside the package (a mixer with state of its own, another position encoding), a
+layer plan that names a layer twice and lets a layer read another layer's cache, and a whole toy
+architecture can be registered, built and stepped without a change to the package's files."""
+import math
+from dataclasses import dataclass
+from typing import ClassVar
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from qwen_engine_b200 import ops
+from qwen_engine_b200.cache import CacheManager, FixedStateSpec
+from qwen_engine_b200.config import ModelConfig
+from qwen_engine_b200.engine.runner import ModelRunner, StepEntry
+from qwen_engine_b200.models.decoder import DecoderModel, LayerSpec, ModelLayout, PlanEntry
+from qwen_engine_b200.parts import (Mixer, PartSpec, PositionEncoding, register, MIXERS, POSITION_ENCODINGS)
+from qwen_engine_b200.registry import ARCHITECTURES, build_model, config_from_dict, register_architecture
+from qwen_engine_b200.weights import NORM, MATRIX, RandomSource, WeightSpec
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+TOL = {torch.float32: 2e-5, torch.bfloat16: 2e-2}
+
+
+def _close(got, want, dtype, what=""):
+    got, want = got.float().cpu(), want.float().cpu()
+    scale = max(1.0, float(want.abs().max()))
+    err = float((got - want).abs().max())
+    assert torch.isfinite(got).all(), what
+    assert err <= TOL[dtype] * scale, f"{what}: max |diff| {err:.3e} > {TOL[dtype]} * {scale:.3f}"
+
+
+class DictSource:
+    def __init__(self, tensors):
+        self.t = tensors
+
+    def names(self):
+        return self.t.keys()
+
+    def shape(self, n):
+        return tuple(self.t[n].shape)
+
+    def get(self, n):
+        return self.t[n]
+
+
+def _weights(specs, seed, std=0.1, dtype=torch.bfloat16):
+    src = RandomSource(specs, seed, std, 0.2, dtype)
+    return {n: src.get(n) for n in src.names()}
+
+
+def _single_layer_model(block: PartSpec, hidden, vocab=50):
+    """A model of one layer around a part, to run the part through the real step function."""
+    layout = ModelLayout(vocab_size=vocab, hidden_size=hidden, layers=(LayerSpec(block, "L."),),
+                         plan=(PlanEntry(0, 0, True),), final_norm=PartSpec("rmsnorm", dict(width=hidden, eps=1e-6)),
+                         tie_head=True)
+    return DecoderModel(layout)
+
+
+# ---- norm -------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rmsnorm_part(dtype):
+    H, T = 72, 9
+    norm = PartSpec("rmsnorm", dict(width=H, eps=3e-6)).build("norm")
+    w = _weights(norm.weight_specs("n."), 1)
+    norm.load("n.", DictSource(w), dtype, DEV)
+    assert norm.weight.dtype == torch.float32
+    g = torch.Generator().manual_seed(2)
+    resid = torch.randn(T, H, generator=g)
+    delta = torch.randn(T, H, generator=g).to(dtype)
+    r = resid.to(DEV)
+    out = torch.empty(T, H, dtype=dtype, device=DEV)
+    norm.add_norm(None, r, delta.to(DEV), out)
+    summed = resid + delta.float()
+    _close(r, summed, torch.float32, "stream after add")
+    _close(out, plain.rmsnorm(summed, w["n.weight"].float(), 3e-6), dtype, "normed")
+    rows = torch.tensor([8, 0], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(2, H, dtype=dtype, device=DEV)
+    norm.add_norm_rows(None, r, None, rows, out2)
+    _close(out2, plain.rmsnorm(summed[[8, 0]], w["n.weight"].float(), 3e-6), dtype, "rows")
+
+
+# ---- position encoding ------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("D,theta", [(16, 1e4), (48, 5e4), (128, 1e6)])
+def test_rope_part(dtype, D, theta):
+    from types import SimpleNamespace
+    rope = PartSpec("rope_neox", dict(head_dim=D, theta=theta)).build("position_encoding")
+    rope.load("", DictSource({}), dtype, DEV)
+    T, Hq, Hkv = 7, 3, 2
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn(T, Hq, D, generator=g).to(dtype)
+    k = torch.randn(T, Hkv, D, generator=g).to(dtype)
+    pos = torch.tensor([0, 1, 5, 77, 1000, 4095, 12], dtype=torch.int32)
+    qd, kd = q.to(DEV), k.to(DEV)
+    rope.rotate(SimpleNamespace(positions=pos.to(DEV)), qd, kd)
+    cos, sin = plain.rope_angles(pos, D, theta)
+    _close(qd, plain.rope_rotate(q.float(), cos, sin), dtype, "q")
+    _close(kd, plain.rope_rotate(k.float(), cos, sin), dtype, "k")
+
+
+# ---- mixer, feed-forward and block, through a one-layer model and the real cache ----------------------------
+def _run_whole_and_cut(model, tensors, dtype, tokens, page=4):
+    model.load_weights(DictSource(tensors), dtype, DEV)
+    cm = CacheManager(model.cache_specs(), page, 64, 4, dtype, DEV)
+    runner = ModelRunner(model, cm, DEV, dtype)
+    rc = cm.open("whole")
+    whole = runner.step([StepEntry(rc, tokens, list(range(len(tokens))))]).float().cpu().clone()
+    cm.close(rc)
+    rc = cm.open("cut")
+    rows, p = [], 0
+    for n in [3, 2, 5, 1, 1, 2] + [1] * 40:
+        if p >= len(tokens):
+            break
+        n = min(n, len(tokens) - p)
+        rows.append(runner.step([StepEntry(rc, tokens[p:p + n], list(range(n)))]).float().cpu().clone())
+        p += n
+    cm.close(rc)
+    return whole, torch.cat(rows)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_mlp_and_block_parts(dtype):
+    """One pre-norm block of attention and SwiGLU with odd sizes, against the plain layer."""
+    H, Hq, Hkv, D, I, V = 72, 6, 2, 48, 152, 50
+    rope = PartSpec("rope_neox", dict(head_dim=D, theta=5e4))
+    block = PartSpec("pre_norm", dict(
+        hidden_size=H, norm=PartSpec("rmsnorm", dict(width=H, eps=1e-5)),
+        mixer=PartSpec("gqa_attention", dict(hidden_size=H, num_heads=Hq, num_kv_heads=Hkv, head_dim=D,
+                                             scale=1 / math.sqrt(D), qk_norm_eps=1e-5, position_encoding=rope)),
+        feed_forward=PartSpec("swiglu", dict(hidden_size=H, intermediate_size=I))))
+    model = _single_layer_model(block, H, V)
+    tensors = _weights(model.weight_manifest(), 4)
+    tokens = [(5 * i + 3) % V for i in range(23)]
+    whole, cut = _run_whole_and_cut(model, tensors, dtype, tokens)
+    # the plain layer, with the same tensors under the plain implementation's names
+    w = {n.replace("L.", "model.layers.0."): t.float() for n, t in tensors.items()}
+    n = dict(layers=1, hidden=H, heads=Hq, kv_heads=Hkv, head_dim=D, inter=I, vocab=V, theta=5e4, eps=1e-5,
+             tied=True, scale=1 / math.sqrt(D))
+    ids = torch.tensor(tokens)
+    x = plain.embedding(ids, w["model.embed_tokens.weight"])
+    x = plain.decoder_layer(x, torch.arange(len(tokens)), w, 0, n)
+    want = plain.linear(plain.rmsnorm(x, w["model.norm.weight"], 1e-6), w["model.embed_tokens.weight"])
+    _close(whole, want, dtype, "whole")
+    _close(cut, want, dtype, "cut into portions")
+    # the parts alone: attention and feed-forward outputs of the first branch
+    blk = model.blocks[0]
+    assert blk.mixer.cache_spec().num_kv_heads == Hkv and blk.mixer.attention_geometry() == (Hq, Hkv, D, 0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu_part_alone(dtype):
+    from types import SimpleNamespace
+    from qwen_engine_b200.parts import Arena
+    H, I, T = 40, 56, 13
+    ffn = PartSpec("swiglu", dict(hidden_size=H, intermediate_size=I)).build("feed_forward")
+    w = _weights(ffn.weight_specs("m."), 5)
+    ffn.load("m.", DictSource(w), dtype, DEV)
+    x = torch.randn(T, H, generator=torch.Generator().manual_seed(6)).to(dtype)
+    out = torch.empty(T, H, dtype=dtype, device=DEV)
+    ffn.forward(SimpleNamespace(num_tokens=T, dtype=dtype, arena=Arena(DEV)), x.to(DEV), out)
+    _close(out, plain.mlp_part(x.float(), {k: v.float() for k, v in w.items()}, "m."), dtype, "swiglu")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_part_alone(dtype):
+    """The attention mixer alone (the feed-forward's output projection is zero), cut into steps."""
+    H, Hq, Hkv, D, V = 48, 4, 1, 32, 30
+    block = PartSpec("pre_norm", dict(
+        hidden_size=H, norm=PartSpec("rmsnorm", dict(width=H, eps=1e-6)),
+        mixer=PartSpec("gqa_attention", dict(hidden_size=H, num_heads=Hq, num_kv_heads=Hkv, head_dim=D,
+                                             scale=1 / math.sqrt(D), qk_norm_eps=1e-6,
+                                             position_encoding=PartSpec("rope_neox", dict(head_dim=D, theta=1e6)))),
+        feed_forward=PartSpec("swiglu", dict(hidden_size=H, intermediate_size=16))))
+    model = _single_layer_model(block, H, V)
+    tensors = _weights(model.weight_manifest(), 8)
+    tensors["L.mlp.down_proj.weight"] = torch.zeros_like(tensors["L.mlp.down_proj.weight"])
+    tokens = [(11 * i + 1) % V for i in range(17)]
+    whole, cut = _run_whole_and_cut(model, tensors, dtype, tokens, page=8)
+    w = {n.replace("L.", "model.layers.0."): t.float() for n, t in tensors.items()}
+    n = dict(heads=Hq, kv_heads=Hkv, head_dim=D, theta=1e6, eps=1e-6, scale=1 / math.sqrt(D))
+    x = plain.embedding(torch.tensor(tokens), w["model.embed_tokens.weight"])
+    h = plain.rmsnorm(x, w["model.layers.0.input_layernorm.weight"], 1e-6)
+    x = x + plain.attention_part(h, torch.arange(len(tokens)), w, "model.layers.0.self_attn.", n)
+    want = plain.linear(plain.rmsnorm(x, w["model.norm.weight"], 1e-6), w["model.embed_tokens.weight"])
+    _close(whole, want, dtype, "attention whole")
+    _close(cut, want, dtype, "attention cut")
+
+
+# ---- parts defined here, outside the package ----------------------------------------------------------------
+class DecayMixer(Mixer):
+    """A toy mixer with state of fixed size: s <- a * s + x_t for each token of a request in order,
+    y_t = s * w.  The state of a request lives in its slot between steps."""
+
+    capturable = False      # it reads step data on the host: its steps are not for CUDA graphs
+
+    def __init__(self, hidden_size: int, decay: float):
+        self.hidden_size, self.decay = hidden_size, decay
+        self.w = None
+
+    def cache_spec(self):
+        return FixedStateSpec((self.hidden_size,), torch.float32)
+
+    def weight_specs(self, prefix):
+        return [WeightSpec(prefix + "gain", (self.hidden_size,), NORM)]
+
+    def load(self, prefix, source, dtype, device):
+        self.w = source.get(prefix + "gain").float().to(device)
+
+    def forward(self, ctx, x, cache, group, out, write_cache=True):
+        # cache: [state slots, hidden] float32 of this layer; plain torch operations are fine in a test
+        slots = ctx.slot_ids.tolist()
+        cu = ctx.cu_q.tolist()
+        for r, slot in enumerate(slots):
+            s = cache[slot]
+            for t in range(cu[r], cu[r + 1]):
+                s = self.decay * s + x[t].float()
+                out[t] = (s * self.w).to(out.dtype)
+            cache[slot] = s
+
+
+class ShiftedRope(PositionEncoding):
+    """Another position encoding: interleaved pairs (2j, 2j+1) instead of half-split ones."""
+
+    def __init__(self, head_dim: int, theta: float):
+        self.head_dim, self.theta = head_dim, theta
+
+    def rotate(self, ctx, q, k):
+        D = self.head_dim
+        inv = 1.0 / (self.theta ** (torch.arange(0, D, 2, dtype=torch.float32, device=q.device) / D))
+        ang = ctx.positions.float()[:, None] * inv[None, :]
+        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        for x in (q, k):
+            xf = x.float().clone()
+            a, b = xf[..., 0::2], xf[..., 1::2]
+            x[..., 0::2] = (c * a - s * b).to(x.dtype)
+            x[..., 1::2] = (s * a + c * b).to(x.dtype)
+
+
+@dataclass
+class ToyConfig(ModelConfig):
+    architecture: ClassVar[str] = "ToyForCausalLM"
+    hidden_size: int = 40
+    vocab_size: int = 61
+    num_heads: int = 4
+    num_kv_heads: int = 2
+    head_dim: int = 16
+    intermediate_size: int = 56
+    decay: float = 0.7
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(**{k: v for k, v in raw.items() if k != "architectures"})
+
+    def validate(self):
+        pass
+
+
+def toy_layout(cfg: ToyConfig) -> ModelLayout:
+    H = cfg.hidden_size
+    norm = PartSpec("rmsnorm", dict(width=H, eps=1e-5))
+    ffn = PartSpec("swiglu", dict(hidden_size=H, intermediate_size=cfg.intermediate_size))
+    attn = lambda pos: PartSpec("gqa_attention", dict(
+        hidden_size=H, num_heads=cfg.num_heads, num_kv_heads=cfg.num_kv_heads, head_dim=cfg.head_dim,
+        scale=cfg.head_dim ** -0.5, qk_norm_eps=1e-5, position_encoding=pos))
+    rope = PartSpec("rope_neox", dict(head_dim=cfg.head_dim, theta=1e4))
+    other = PartSpec("test_interleaved_rope", dict(head_dim=cfg.head_dim, theta=1e4))
+    block = lambda mixer: PartSpec("pre_norm", dict(hidden_size=H, mixer=mixer, feed_forward=ffn, norm=norm))
+    layers = (LayerSpec(block(attn(rope)), "layers.0."),
+              LayerSpec(block(PartSpec("test_decay", dict(hidden_size=H, decay=cfg.decay))), "layers.1."),
+              LayerSpec(block(attn(other)), "layers.2."))
+    # layer 0 runs twice (a cache slot for each run); layer 2 runs once with a cache of its own and
+    # once more reading what layer 0's first run wrote (same cache description, so the same group)
+    plan = (PlanEntry(0, 0, True), PlanEntry(1, 1, True), PlanEntry(0, 2, True), PlanEntry(2, 3, True),
+            PlanEntry(2, 0, False))
+    return ModelLayout(vocab_size=cfg.vocab_size, hidden_size=H, layers=layers, plan=plan, final_norm=norm,
+                       embed_name="embed.weight", final_norm_prefix="norm.", head_name="head.weight", tie_head=False)
+
+
+def _toy_plain(cfg: ToyConfig, w, tokens):
+    """The toy model on whole sequences, from the plain implementation's functions."""
+    T, H, D = len(tokens), cfg.hidden_size, cfg.head_dim
+    pos = torch.arange(T)
+    x = plain.embedding(torch.tensor(tokens), w["embed.weight"])
+
+    def qkv(h, p):
+        q = plain.rmsnorm(plain.linear(h, w[p + "q_proj.weight"]).view(T, cfg.num_heads, D), w[p + "q_norm.weight"], 1e-5)
+        k = plain.rmsnorm(plain.linear(h, w[p + "k_proj.weight"]).view(T, cfg.num_kv_heads, D), w[p + "k_norm.weight"], 1e-5)
+        v = plain.linear(h, w[p + "v_proj.weight"]).view(T, cfg.num_kv_heads, D)
+        return q, k, v
+
+    def interleaved(t):
+        inv = 1.0 / (1e4 ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+        ang = pos.float()[:, None] * inv[None, :]
+        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        a, b = t[..., 0::2], t[..., 1::2]
+        out = torch.empty_like(t)
+        out[..., 0::2], out[..., 1::2] = c * a - s * b, s * a + c * b
+        return out
+
+    def attn_block(x, i, kind, kv=None):
+        p = f"layers.{i}."
+        h = plain.rmsnorm(x, w[p + "input_layernorm.weight"], 1e-5)
+        q, k, v = qkv(h, p + "self_attn.")
+        if kind == "neox":
+            cos, sin = plain.rope_angles(pos, D, 1e4)
+            q, k = plain.rope_rotate(q, cos, sin), plain.rope_rotate(k, cos, sin)
+        else:
+            q, k = interleaved(q), interleaved(k)
+        keep = (k, v)
+        if kv is not None:
+            k, v = kv
+        o = plain.causal_attention(q, k, v, D ** -0.5).reshape(T, -1)
+        x = x + plain.linear(o, w[p + "self_attn.o_proj.weight"])
+        h = plain.rmsnorm(x, w[p + "post_attention_layernorm.weight"], 1e-5)
+        return x + plain.mlp_part(h, w, p + "mlp."), keep
+
+    x, kv0 = attn_block(x, 0, "neox")
+    p = "layers.1."
+    h = plain.rmsnorm(x, w[p + "input_layernorm.weight"], 1e-5)
+    s, ys = torch.zeros(H), []
+    for t in range(T):
+        s = cfg.decay * s + h[t]
+        ys.append(s * w[p + "self_attn.gain"])
+    x = x + torch.stack(ys)
+    x = x + plain.mlp_part(plain.rmsnorm(x, w[p + "post_attention_layernorm.weight"], 1e-5), w, p + "mlp.")
+    x, _ = attn_block(x, 0, "neox")
+    x, _ = attn_block(x, 2, "interleaved")
+    x, _ = attn_block(x, 2, "interleaved", kv=kv0)
+    return plain.linear(plain.rmsnorm(x, w["norm.weight"], 1e-5), w["head.weight"])
+
+
+@pytest.fixture
+def toy_registered():
+    register("mixer", "test_decay")(DecayMixer)
+    register("position_encoding", "test_interleaved_rope")(ShiftedRope)
+    register_architecture("ToyForCausalLM", ToyConfig, toy_layout)
+    yield
+    del MIXERS["test_decay"], POSITION_ENCODINGS["test_interleaved_rope"], ARCHITECTURES["ToyForCausalLM"]
+
+
+def test_toy_architecture_with_its_own_parts(toy_registered):
+    """Registered from outside: built by the registry, loaded by the loader's checks, given cache
+    groups of its own (pages for attention, state slots for the toy mixer) and stepped by the
+    engine's step function, whole and in portions mixed with another request."""
+    dtype = torch.float32
+    cfg = config_from_dict({"architectures": ["ToyForCausalLM"], "hidden_size": 40, "decay": 0.6})
+    assert isinstance(cfg, ToyConfig)
+    model = build_model(cfg)
+    tensors = _weights(model.weight_manifest(), 9, dtype=torch.float32)
+    model.load_weights(DictSource(tensors), dtype, DEV)
+    specs = model.cache_specs()
+    assert len(specs) == 4 and isinstance(specs[1], FixedStateSpec)
+    cm = CacheManager(specs, 4, 48, 3, dtype, DEV)
+    assert [g.cache_slots for g in cm.groups] == [[0, 2, 3], [1]] and not cm.prefix_cache
+    runner = ModelRunner(model, cm, DEV, dtype)
+    w = {n: t.float() for n, t in tensors.items()}
+    a = [(3 * i + 1) % cfg.vocab_size for i in range(19)]
+    b = [(7 * i + 2) % cfg.vocab_size for i in range(11)]
+    want_a, want_b = _toy_plain(cfg, w, a), _toy_plain(cfg, w, b)
+    rc = cm.open("whole")
+    got = runner.step([StepEntry(rc, a, list(range(len(a))))]).float().cpu().clone()
+    cm.close(rc)
+    _close(got, want_a, dtype, "toy whole")
+    ra, rb = cm.open("a"), cm.open("b")
+    pa = pb = 0
+    rows_a, rows_b = [], []
+    for na, nb in [(4, 2), (1, 3), (6, 1), (1, 1), (2, 4), (5, 0)]:
+        na, nb = min(na, len(a) - pa), min(nb, len(b) - pb)
+        entries = []
+        if na:
+            entries.append(StepEntry(ra, a[pa:pa + na], list(range(na))))
+        if nb:
+            entries.append(StepEntry(rb, b[pb:pb + nb], list(range(nb))))
+        out = runner.step(entries).float().cpu().clone()
+        rows_a.append(out[:na])
+        rows_b.append(out[na:na + nb])
+        pa, pb = pa + na, pb + nb
+    assert pa == len(a) and pb == len(b)
+    _close(torch.cat(rows_a), want_a, dtype, "toy a in portions")
+    _close(torch.cat(rows_b), want_b, dtype, "toy b in portions")
+    # the slot of an ended request is zeroed for the next one
+    cm.close(ra)
+    rc = cm.open("again")
+    assert rc.state_slot == ra.state_slot
+    got = runner.step([StepEntry(rc, a, list(range(len(a))))]).float().cpu().clone()
+    _close(got, want_a, dtype, "toy reuse of a state slot")
+    cm.check_invariants()
+
+
+def test_plan_is_checked():
+    H = 32
+    norm = PartSpec("rmsnorm", dict(width=H, eps=1e-5))
+    ffn = PartSpec("swiglu", dict(hidden_size=H, intermediate_size=48))
+    attn = PartSpec("gqa_attention", dict(hidden_size=H, num_heads=2, num_kv_heads=1, head_dim=16, scale=0.25))
+    block = PartSpec("pre_norm", dict(hidden_size=H, mixer=attn, feed_forward=ffn, norm=norm))
+    base = dict(vocab_size=10, hidden_size=H, layers=(LayerSpec(block, "l0."),), final_norm=norm)
+    with pytest.raises(ValueError, match="exactly one"):
+        DecoderModel(ModelLayout(plan=(PlanEntry(0, 0, True), PlanEntry(0, 0, True)), **base))
+    with pytest.raises(ValueError, match="exactly one"):
+        DecoderModel(ModelLayout(plan=(PlanEntry(0, 0, False),), **base))
+    with pytest.raises(ValueError, match="names layer"):
+        DecoderModel(ModelLayout(plan=(PlanEntry(3, 0, True),), **base))
+    with pytest.raises(ValueError, match="unknown mixer"):
+        PartSpec("no_such_mixer").build("mixer")
