@@ -56,8 +56,129 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// One warp's share of a key tile: rows [row_base, row_base + 16) of the query tile against NB blocks
+// of 16 keys starting at block kb0 of the tile.  Updates the rows' running max, sum and output.
+template <int D, int NB>
+__device__ __forceinline__ void fa_tile(const __nv_bfloat16* sq, const __nv_bfloat16* tk, const __nv_bfloat16* tv,
+                                        int row_base, int kb0, int kt, int kv_begin, int kv_end, int pos_lo, int pos_hi,
+                                        int window, float scale_log2, int lane, float& m_lo, float& m_hi, float& l_lo,
+                                        float& l_hi, float (&o)[D / 8][4]) {
+  constexpr int LD = D + 8, KS = D / 16;
+  const int c = lane & 3;
+  // ---- S = Q K^T ---------------------------------------------------------------------------
+  float s[2 * NB][4];
+#pragma unroll
+  for (int i = 0; i < 2 * NB; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) {
+    uint32_t a[4];
+    // A fragment of Q: matrices (rows 0-7, k 0-7), (rows 8-15, k 0-7), (rows 0-7, k 8-15), (rows 8-15, k 8-15)
+    ldsm_x4(a, sq + (row_base + (lane & 15)) * LD + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+      uint32_t b[4];
+      // B fragments of two groups of 8 keys: (keys 0-7, k 0-7), (keys 0-7, k 8-15), (keys 8-15, k 0-7), (keys 8-15, k 8-15)
+      ldsm_x4(b, tk + ((kb0 + nb) * 16 + (lane >> 4) * 8 + (lane & 7)) * LD + ks * 16 + ((lane >> 3) & 1) * 8);
+      fa_mma(s[2 * nb], a, b[0], b[1]);
+      fa_mma(s[2 * nb + 1], a, b[2], b[3]);
+    }
+  }
+  // ---- mask, online softmax --------------------------------------------------------------------
+  float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < 2 * NB; ++i) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int key = kt + kb0 * 16 + i * 8 + 2 * c + e;
+      const bool in_range = key >= kv_begin && key < kv_end;
+      const bool ok_lo = in_range && key <= pos_lo && (window <= 0 || key > pos_lo - window);
+      const bool ok_hi = in_range && key <= pos_hi && (window <= 0 || key > pos_hi - window);
+      s[i][e] = ok_lo ? s[i][e] * scale_log2 : -INFINITY;
+      s[i][2 + e] = ok_hi ? s[i][2 + e] * scale_log2 : -INFINITY;
+      mx_lo = fmaxf(mx_lo, s[i][e]);
+      mx_hi = fmaxf(mx_hi, s[i][2 + e]);
+    }
+  }
+  mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+  mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+  mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+  mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+  const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+  const float base_lo = mn_lo == -INFINITY ? 0.f : mn_lo;      // a row with nothing allowed so far
+  const float base_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+  const float al_lo = exp2f(m_lo - base_lo), al_hi = exp2f(m_hi - base_hi);
+  m_lo = mn_lo; m_hi = mn_hi;
+  float sum_lo = 0.f, sum_hi = 0.f;
+#pragma unroll
+  for (int i = 0; i < 2 * NB; ++i) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      s[i][e] = exp2f(s[i][e] - base_lo);
+      s[i][2 + e] = exp2f(s[i][2 + e] - base_hi);
+      sum_lo += s[i][e];
+      sum_hi += s[i][2 + e];
+    }
+  }
+  sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 1);
+  sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 2);
+  sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 1);
+  sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 2);
+  l_lo = l_lo * al_lo + sum_lo;
+  l_hi = l_hi * al_hi + sum_hi;
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) { o[i][0] *= al_lo; o[i][1] *= al_lo; o[i][2] *= al_hi; o[i][3] *= al_hi; }
+  // ---- O += P V --------------------------------------------------------------------------------
+#pragma unroll
+  for (int kk = 0; kk < NB; ++kk) {
+    uint32_t a[4];
+    a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+    a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+    a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+    a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+    for (int dp = 0; dp < D / 16; ++dp) {
+      uint32_t b[4];
+      // transposed loads of V: (keys 0-7, d 0-7), (keys 8-15, d 0-7), (keys 0-7, d 8-15), (keys 8-15, d 8-15)
+      ldsm_x4_t(b, tv + ((kb0 + kk) * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LD + dp * 16 + (lane >> 4) * 8);
+      fa_mma(o[2 * dp], a, b[0], b[1]);
+      fa_mma(o[2 * dp + 1], a, b[2], b[3]);
+    }
+  }
+}
+
+// Combine the parts of one (request, kv head): out = sum_s 2^(m_s - m) acc_s / sum_s 2^(m_s - m) l_s
+// (reference attn.py:520-594), in float32, in the order of the parts.  Run by a whole CTA.
+template <int D>
+__device__ __forceinline__ void fa_merge_parts(const float* part_acc, const float* part_ml, int part_rows, int first,
+                                               int n, int hkv, int Hkv, int nrows, int G, int Hq,
+                                               __nv_bfloat16* out_row0 /* row of the tile's first token */) {
+  for (int e = threadIdx.x; e < nrows * D; e += blockDim.x) {
+    const int r = e / D, d = e - r * D;
+    float m = -INFINITY;
+    for (int sp = 0; sp < n; ++sp) m = fmaxf(m, __ldcg(part_ml + 2 * ((((size_t)first + sp) * Hkv + hkv) * part_rows + r)));
+    float l = 0.f, acc = 0.f;
+    for (int sp = 0; sp < n; ++sp) {
+      const size_t slot = (((size_t)first + sp) * Hkv + hkv) * part_rows + r;
+      const float wgt = exp2f(__ldcg(part_ml + 2 * slot) - m);
+      l += wgt * __ldcg(part_ml + 2 * slot + 1);
+      acc += wgt * __ldcg(part_acc + slot * D + d);
+    }
+    const int ti = r / G, hg = r - ti * G;
+    out_row0[(size_t)ti * ((size_t)Hq * D) + (size_t)(hkv * G + hg) * D + d] = __float2bfloat16_rn(acc / l);
+  }
+}
+
 // D: head size, a multiple of 16 up to 256.  Rows of the shared-memory tiles are padded by 16 bytes
 // so that the 8 row addresses of an ldmatrix fall into different banks for every D.
+//
+// Two ways of sharing a key tile between the 4 warps.  A tile of many rows (a prompt portion): each
+// warp owns 16 rows and visits all 64 keys.  A tile of at most 16 rows (decoded tokens: the query
+// heads of one group): every warp takes the same rows and 16 of the 64 keys, with a running max, sum
+// and output of its own; the four are combined in shared memory at the end.
+//
+// `counters` (may be null): one int per (first part, kv head), zero before the launch.  The CTA that
+// finishes a request's last part combines the parts itself and sets the counter back to zero, so no
+// merge kernel is needed; with a null pointer the parts are left for flash_merge_kernel.
 template <int D>
 __global__ void __launch_bounds__(FA_THREADS)
 flash_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride,
@@ -65,15 +186,17 @@ flash_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride,
                        int max_blocks, const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
                        const int* __restrict__ items, __nv_bfloat16* __restrict__ out,
                        float* __restrict__ part_acc, float* __restrict__ part_ml, int part_rows,
-                       float scale_log2, int window, int Hq, int Hkv, int page_size) {
+                       int* __restrict__ counters, float scale_log2, int window, int Hq, int Hkv, int page_size) {
   constexpr int LD = D + 8;                         // padded row, in elements
-  constexpr int KS = D / 16;                        // k-steps over the head size
   constexpr int CH = D / 8;                         // 16-byte chunks in a row
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* sq = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [64][LD]
   __nv_bfloat16* sk = sq + FA_BM * LD;                                     // [2][64][LD]
   __nv_bfloat16* sv = sk + 2 * FA_BN * LD;                                 // [2][64][LD]
+  __shared__ int s_last;
 
+  // the work lists, lengths and block tables come from the host's copy, not from a kernel
+  pdl_launch_dependents();
   const int* it = items + (size_t)blockIdx.x * FA_ITEM_INTS;
   const int req = it[0], q0 = it[1], part = it[4], n_splits = it[5], split = it[6];
   int kv_lo = it[2], kv_hi_item = it[3];
@@ -104,6 +227,7 @@ flash_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride,
   const int kt_first = (kv_begin / FA_BN) * FA_BN;
   const int n_tiles = kv_end > kt_first ? (kv_end - kt_first + FA_BN - 1) / FA_BN : 0;
 
+  pdl_wait();            // q and the newest keys and values are the previous kernel's output
   // ---- stage the query rows --------------------------------------------------------------
   for (int e = threadIdx.x; e < FA_BM * CH; e += FA_THREADS) {
     const int r = e / CH, ch = e - r * CH;
@@ -135,8 +259,10 @@ flash_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride,
   if (n_tiles > 0) load_tile(0, kt_first);
   cp_async_commit();
 
-  // rows of this thread: r_lo = 16 warp + g and r_lo + 8
-  const int r_lo = warp * 16 + g, r_hi = r_lo + 8;
+  const bool keysplit = nrows <= 16;                // few rows: the warps share the keys, not the rows
+  const int row_base = keysplit ? 0 : warp * 16;
+  // rows of this thread: r_lo = row_base + g and r_lo + 8
+  const int r_lo = row_base + g, r_hi = r_lo + 8;
   const int pos_lo = r_lo < nrows ? first_pos + r_lo / G : -1;             // -1: the row is padding
   const int pos_hi = r_hi < nrows ? first_pos + r_hi / G : -1;
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
@@ -144,7 +270,7 @@ flash_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride,
 #pragma unroll
   for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
 
-  const bool warp_active = warp * 16 < nrows;       // warps without rows only help loading
+  const bool warp_active = keysplit || warp * 16 < nrows;       // warps without rows only help loading
 
   for (int t = 0; t < n_tiles; ++t) {
     const int kt = kt_first + t * FA_BN;
@@ -155,114 +281,96 @@ flash_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride,
     if (warp_active) {
       const __nv_bfloat16* tk = sk + (t & 1) * FA_BN * LD;
       const __nv_bfloat16* tv = sv + (t & 1) * FA_BN * LD;
-      // ---- S = Q K^T -------------------------------------------------------------------
-      float s[FA_BN / 8][4];
-#pragma unroll
-      for (int i = 0; i < FA_BN / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
-#pragma unroll
-      for (int ks = 0; ks < KS; ++ks) {
-        uint32_t a[4];
-        // A fragment of Q: matrices (rows 0-7, k 0-7), (rows 8-15, k 0-7), (rows 0-7, k 8-15), (rows 8-15, k 8-15)
-        ldsm_x4(a, sq + (warp * 16 + (lane & 15)) * LD + ks * 16 + (lane >> 4) * 8);
-#pragma unroll
-        for (int np = 0; np < FA_BN / 16; ++np) {
-          uint32_t b[4];
-          // B fragments of two key tiles: (keys 0-7, k 0-7), (keys 0-7, k 8-15), (keys 8-15, k 0-7), (keys 8-15, k 8-15)
-          ldsm_x4(b, tk + (np * 16 + (lane >> 4) * 8 + (lane & 7)) * LD + ks * 16 + ((lane >> 3) & 1) * 8);
-          fa_mma(s[2 * np], a, b[0], b[1]);
-          fa_mma(s[2 * np + 1], a, b[2], b[3]);
-        }
-      }
-      // ---- mask, online softmax ------------------------------------------------------------
-      float mx_lo = -INFINITY, mx_hi = -INFINITY;
-#pragma unroll
-      for (int i = 0; i < FA_BN / 8; ++i) {
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int key = kt + i * 8 + 2 * c + e;
-          const bool in_range = key >= kv_begin && key < kv_end;
-          const bool ok_lo = in_range && key <= pos_lo && (window <= 0 || key > pos_lo - window);
-          const bool ok_hi = in_range && key <= pos_hi && (window <= 0 || key > pos_hi - window);
-          s[i][e] = ok_lo ? s[i][e] * scale_log2 : -INFINITY;
-          s[i][2 + e] = ok_hi ? s[i][2 + e] * scale_log2 : -INFINITY;
-          mx_lo = fmaxf(mx_lo, s[i][e]);
-          mx_hi = fmaxf(mx_hi, s[i][2 + e]);
-        }
-      }
-      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
-      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
-      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
-      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-      const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
-      const float base_lo = mn_lo == -INFINITY ? 0.f : mn_lo;      // a row with nothing allowed so far
-      const float base_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
-      const float al_lo = exp2f(m_lo - base_lo), al_hi = exp2f(m_hi - base_hi);
-      m_lo = mn_lo; m_hi = mn_hi;
-      float sum_lo = 0.f, sum_hi = 0.f;
-#pragma unroll
-      for (int i = 0; i < FA_BN / 8; ++i) {
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          s[i][e] = exp2f(s[i][e] - base_lo);
-          s[i][2 + e] = exp2f(s[i][2 + e] - base_hi);
-          sum_lo += s[i][e];
-          sum_hi += s[i][2 + e];
-        }
-      }
-      sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 1);
-      sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 2);
-      sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 1);
-      sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, 2);
-      l_lo = l_lo * al_lo + sum_lo;
-      l_hi = l_hi * al_hi + sum_hi;
-#pragma unroll
-      for (int i = 0; i < D / 8; ++i) { o[i][0] *= al_lo; o[i][1] *= al_lo; o[i][2] *= al_hi; o[i][3] *= al_hi; }
-      // ---- O += P V ------------------------------------------------------------------------
-#pragma unroll
-      for (int kk = 0; kk < FA_BN / 16; ++kk) {
-        uint32_t a[4];
-        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
-#pragma unroll
-        for (int dp = 0; dp < D / 16; ++dp) {
-          uint32_t b[4];
-          // transposed loads of V: (keys 0-7, d 0-7), (keys 8-15, d 0-7), (keys 0-7, d 8-15), (keys 8-15, d 8-15)
-          ldsm_x4_t(b, tv + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LD + dp * 16 + (lane >> 4) * 8);
-          fa_mma(o[2 * dp], a, b[0], b[1]);
-          fa_mma(o[2 * dp + 1], a, b[2], b[3]);
-        }
-      }
+      if (keysplit)
+        fa_tile<D, 1>(sq, tk, tv, 0, warp, kt, kv_begin, kv_end, pos_lo, pos_hi, window, scale_log2, lane,
+                      m_lo, m_hi, l_lo, l_hi, o);
+      else
+        fa_tile<D, FA_BN / 16>(sq, tk, tv, row_base, 0, kt, kv_begin, kv_end, pos_lo, pos_hi, window, scale_log2,
+                               lane, m_lo, m_hi, l_lo, l_hi, o);
     }
     __syncthreads();                                // the stage is free for the load after next
   }
   cp_async_wait<0>();
 
-  if (!warp_active) return;
-  // ---- write: the output, or this part's accumulator with max and sum ------------------------
+  __nv_bfloat16* out_row0 = out + (size_t)(row0 + q0) * ((size_t)Hq * D);
+  if (keysplit) {
+    // ---- combine the four warps' shares of the keys in shared memory (the tiles are done) ------
+    __syncthreads();
+    float* xo = reinterpret_cast<float*>(sk);                  // [4 warps][16 rows][D]
+    float* xml = xo + FA_WARPS * 16 * D;                        // [4 warps][16 rows][2]
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int r = half ? r_hi : r_lo;
-    if (r >= nrows) continue;
-    const int ti = r / G, hg = r - ti * G;
-    const float l = half ? l_hi : l_lo, m = half ? m_hi : m_lo;
-    if (part < 0) {
-      const float inv = 1.f / l;
-      __nv_bfloat16* dst = out + (size_t)(row0 + q0 + ti) * ((size_t)Hq * D) + (size_t)(hkv * G + hg) * D;
+    for (int i = 0; i < D / 8; ++i) {
+      *reinterpret_cast<float2*>(xo + ((size_t)warp * 16 + g) * D + i * 8 + 2 * c) = make_float2(o[i][0], o[i][1]);
+      *reinterpret_cast<float2*>(xo + ((size_t)warp * 16 + g + 8) * D + i * 8 + 2 * c) = make_float2(o[i][2], o[i][3]);
+    }
+    if (c == 0) {
+      xml[(warp * 16 + g) * 2] = m_lo; xml[(warp * 16 + g) * 2 + 1] = l_lo;
+      xml[(warp * 16 + g + 8) * 2] = m_hi; xml[(warp * 16 + g + 8) * 2 + 1] = l_hi;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < nrows * D; e += FA_THREADS) {
+      const int r = e / D, d = e - r * D;
+      float m = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < D / 8; ++i) {
-        const float v0 = o[i][2 * half] * inv, v1 = o[i][2 * half + 1] * inv;
-        *reinterpret_cast<uint32_t*>(dst + i * 8 + 2 * c) = pack_bf16(v0, v1);
+      for (int w = 0; w < FA_WARPS; ++w) m = fmaxf(m, xml[(w * 16 + r) * 2]);
+      const float base = m == -INFINITY ? 0.f : m;
+      float l = 0.f, acc = 0.f;
+#pragma unroll
+      for (int w = 0; w < FA_WARPS; ++w) {
+        const float wgt = exp2f(xml[(w * 16 + r) * 2] - base);
+        l += wgt * xml[(w * 16 + r) * 2 + 1];
+        acc += wgt * xo[((size_t)w * 16 + r) * D + d];
       }
-    } else {
-      const size_t slot = ((size_t)part * Hkv + hkv) * part_rows + r;
-      float* dst = part_acc + slot * D;
-#pragma unroll
-      for (int i = 0; i < D / 8; ++i) {
-        *reinterpret_cast<float2*>(dst + i * 8 + 2 * c) = make_float2(o[i][2 * half], o[i][2 * half + 1]);
+      if (part < 0) {
+        const int ti = r / G, hg = r - ti * G;
+        out_row0[(size_t)ti * ((size_t)Hq * D) + (size_t)(hkv * G + hg) * D + d] = __float2bfloat16_rn(acc / l);
+      } else {
+        const size_t slot = ((size_t)part * Hkv + hkv) * part_rows + r;
+        part_acc[slot * D + d] = acc;
+        if (d == 0) { part_ml[2 * slot] = m; part_ml[2 * slot + 1] = l; }
       }
-      if (c == 0) { part_ml[2 * slot] = m; part_ml[2 * slot + 1] = l; }
+    }
+  } else if (warp_active) {
+    // ---- write: the output, or this part's accumulator with max and sum ------------------------
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = half ? r_hi : r_lo;
+      if (r >= nrows) continue;
+      const int ti = r / G, hg = r - ti * G;
+      const float l = half ? l_hi : l_lo, m = half ? m_hi : m_lo;
+      if (part < 0) {
+        const float inv = 1.f / l;
+        __nv_bfloat16* dst = out_row0 + (size_t)ti * ((size_t)Hq * D) + (size_t)(hkv * G + hg) * D;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+          const float v0 = o[i][2 * half] * inv, v1 = o[i][2 * half + 1] * inv;
+          *reinterpret_cast<uint32_t*>(dst + i * 8 + 2 * c) = pack_bf16(v0, v1);
+        }
+      } else {
+        const size_t slot = ((size_t)part * Hkv + hkv) * part_rows + r;
+        float* dst = part_acc + slot * D;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+          *reinterpret_cast<float2*>(dst + i * 8 + 2 * c) = make_float2(o[i][2 * half], o[i][2 * half + 1]);
+        }
+        if (c == 0) { part_ml[2 * slot] = m; part_ml[2 * slot + 1] = l; }
+      }
+    }
+  }
+  // ---- the CTA that finishes a request's last part combines the parts ---------------------------------
+  if (part >= 0 && counters != nullptr && n_splits > 0) {
+    const int first = part - split;
+    __threadfence();                                // this CTA's part is visible before it is counted
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int done = atomicAdd(&counters[first * Hkv + hkv], 1);
+      s_last = (done == n_splits - 1);
+      if (s_last) counters[first * Hkv + hkv] = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    if (s_last) {
+      __threadfence();
+      fa_merge_parts<D>(part_acc, part_ml, part_rows, first, n_splits, hkv, Hkv, nrows, G, Hq, out_row0);
     }
   }
 }
@@ -272,6 +380,8 @@ template <int D>
 __global__ void flash_merge_kernel(const int* __restrict__ merge_items, const int* __restrict__ cu_q,
                                    const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                    int part_rows, __nv_bfloat16* __restrict__ out, int Hq, int Hkv) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int* it = merge_items + 4 * blockIdx.x;
   const int req = it[0], q0 = it[1], first = it[2], n = it[3];
   const int hkv = blockIdx.y;
@@ -304,7 +414,8 @@ template <int D>
 static int launch_flash(const void* q, long q_stride, const void* pages, const int* block_tables, int max_blocks,
                         const int* cu_q, const int* ctx_lens, const int* items, int n_items,
                         const int* merge_items, int n_merge, void* out, float* part_acc, float* part_ml,
-                        int part_rows, float scale, int window, int Hq, int Hkv, int page_size, cudaStream_t stream) {
+                        int part_rows, int* counters, float scale, int window, int Hq, int Hkv, int page_size,
+                        cudaStream_t stream) {
   constexpr int LD = D + 8;
   const size_t smem = (size_t)(FA_BM + 4 * FA_BN) * LD * sizeof(__nv_bfloat16);
   static bool configured = false;
@@ -315,14 +426,14 @@ static int launch_flash(const void* q, long q_stride, const void* pages, const i
   }
   const float scale_log2 = scale * 1.4426950408889634f;
   dim3 grid(n_items, Hkv);
-  flash_attention_kernel<D><<<grid, FA_THREADS, smem, stream>>>(
+  qe_launch(flash_attention_kernel<D>, grid, dim3(FA_THREADS), smem, stream,
       (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pages, block_tables, max_blocks, cu_q, ctx_lens, items,
-      (__nv_bfloat16*)out, part_acc, part_ml, part_rows, scale_log2, window, Hq, Hkv, page_size);
+      (__nv_bfloat16*)out, part_acc, part_ml, part_rows, counters, scale_log2, window, Hq, Hkv, page_size);
   QE_CHECK_LAUNCH("flash_attention");
-  if (n_merge > 0) {
+  if (n_merge > 0 && counters == nullptr) {
     dim3 mgrid(n_merge, Hkv), mblock(32, 4);
-    flash_merge_kernel<D><<<mgrid, mblock, 0, stream>>>(merge_items, cu_q, part_acc, part_ml, part_rows,
-                                                       (__nv_bfloat16*)out, Hq, Hkv);
+    qe_launch(flash_merge_kernel<D>, mgrid, mblock, 0, stream, merge_items, cu_q, (const float*)part_acc,
+              (const float*)part_ml, part_rows, (__nv_bfloat16*)out, Hq, Hkv);
     QE_CHECK_LAUNCH("flash_merge");
   }
   return 0;
@@ -332,17 +443,37 @@ extern "C" int qe_flash_attention_supported(int Hq, int Hkv, int D) {
   return (D % 16 == 0 && D >= 16 && D <= 256 && Hkv >= 1 && Hq % Hkv == 0 && Hq / Hkv <= FA_BM && Hkv <= 65535) ? 1 : 0;
 }
 
+// The entry point with a counter array (see the kernel): parts are combined by the CTA that finishes
+// last, without a merge kernel.  counters: n_parts * Hkv ints, zero before the first use.
+extern "C" int qe_flash_attention_fused_merge(const void* q, long q_stride, const void* pages, const int* block_tables,
+                                              int max_blocks, const int* cu_q, const int* ctx_lens, const int* items,
+                                              int n_items, const int* merge_items, int n_merge, void* out,
+                                              float* part_acc, float* part_ml, int part_rows, int* counters,
+                                              float scale, int window, int Hq, int Hkv, int D, int page_size,
+                                              cudaStream_t stream);
+
 extern "C" int qe_flash_attention(const void* q, long q_stride, const void* pages, const int* block_tables,
                                   int max_blocks, const int* cu_q, const int* ctx_lens, const int* items,
                                   int n_items, const int* merge_items, int n_merge, void* out, float* part_acc,
                                   float* part_ml, int part_rows, float scale, int window, int Hq, int Hkv, int D,
                                   int page_size, cudaStream_t stream) {
+  return qe_flash_attention_fused_merge(q, q_stride, pages, block_tables, max_blocks, cu_q, ctx_lens, items, n_items,
+                                        merge_items, n_merge, out, part_acc, part_ml, part_rows, nullptr, scale,
+                                        window, Hq, Hkv, D, page_size, stream);
+}
+
+extern "C" int qe_flash_attention_fused_merge(const void* q, long q_stride, const void* pages, const int* block_tables,
+                                              int max_blocks, const int* cu_q, const int* ctx_lens, const int* items,
+                                              int n_items, const int* merge_items, int n_merge, void* out,
+                                              float* part_acc, float* part_ml, int part_rows, int* counters,
+                                              float scale, int window, int Hq, int Hkv, int D, int page_size,
+                                              cudaStream_t stream) {
   if (n_items <= 0) return 0;
   if (!qe_flash_attention_supported(Hq, Hkv, D))
     QE_REFUSE("flash_attention: heads %d/%d with head_dim %d are not supported", Hq, Hkv, D);
   if (((uintptr_t)q | (uintptr_t)pages) & 15 || (q_stride % 8)) QE_REFUSE("flash_attention: operands must be 16-byte aligned");
 #define FA_CASE(DD) case DD: return launch_flash<DD>(q, q_stride, pages, block_tables, max_blocks, cu_q, ctx_lens, items, \
-      n_items, merge_items, n_merge, out, part_acc, part_ml, part_rows, scale, window, Hq, Hkv, page_size, stream);
+      n_items, merge_items, n_merge, out, part_acc, part_ml, part_rows, counters, scale, window, Hq, Hkv, page_size, stream);
   switch (D) {
     FA_CASE(16) FA_CASE(32) FA_CASE(48) FA_CASE(64) FA_CASE(80) FA_CASE(96) FA_CASE(112) FA_CASE(128)
     FA_CASE(144) FA_CASE(160) FA_CASE(176) FA_CASE(192) FA_CASE(208) FA_CASE(224) FA_CASE(240) FA_CASE(256)

@@ -27,6 +27,8 @@ attention_generic_kernel(const T* __restrict__ q, long q_stride, const T* __rest
                          const int* __restrict__ tiles, T* __restrict__ out, float scale, int window,
                          int Hq, int Hkv, int D, int page_size) {
   extern __shared__ float smem[];
+  pdl_launch_dependents();
+  pdl_wait();
   const int Dp = D + 1;
   float* qs = smem;                           // [AG_BM][D]
   float* ks = qs + AG_BM * D;                 // [AG_BN][D + 1]
@@ -143,11 +145,11 @@ extern "C" int qe_paged_attention_generic(const void* q, long q_stride, const vo
     configured = true;
   }
   if (dtype == QE_DTYPE_F32) {
-    attention_generic_kernel<float><<<grid, AG_WARPS * 32, smem, stream>>>(
+    qe_launch(attention_generic_kernel<float>, grid, dim3(AG_WARPS * 32), smem, stream,
         (const float*)q, q_stride, (const float*)pages, block_tables, max_blocks, cu_q, ctx_lens, tiles,
         (float*)out, scale, window, Hq, Hkv, D, page_size);
   } else if (dtype == QE_DTYPE_BF16) {
-    attention_generic_kernel<__nv_bfloat16><<<grid, AG_WARPS * 32, smem, stream>>>(
+    qe_launch(attention_generic_kernel<__nv_bfloat16>, grid, dim3(AG_WARPS * 32), smem, stream,
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pages, block_tables, max_blocks, cu_q, ctx_lens,
         tiles, (__nv_bfloat16*)out, scale, window, Hq, Hkv, D, page_size);
   } else QE_REFUSE("paged_attention: unknown dtype %d", dtype);

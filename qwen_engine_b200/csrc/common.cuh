@@ -50,3 +50,33 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   __syncthreads();
   return scratch[32];
 }
+
+// ---- programmatic dependent launch --------------------------------------------------------------------
+// Kernels of a step form a chain on one stream.  Launched with the attribute below, a kernel may
+// start while its predecessor is still running; it must call pdl_wait() before it touches anything
+// the predecessor reads or writes, and may do independent work first (a matrix product starts to
+// fetch its weights, which no kernel of the step writes).  pdl_launch_dependents() lets the next
+// kernel of the chain start early in turn.  Every kernel of this library calls pdl_wait() in all of
+// its threads, so a kernel never completes before its predecessor has, and waiting on the
+// predecessor alone is enough.  qe_set_pdl(0) turns the attribute off (plain stream order).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+extern "C" void qe_set_pdl(int enabled);
+int qe_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t qe_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = qe_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

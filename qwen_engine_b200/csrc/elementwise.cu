@@ -12,7 +12,9 @@ template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ out, int H, int V) {
   const int t = blockIdx.x;
-  const int id = ids[t];
+  const int id = ids[t];                           // written by the host's copy, not by a kernel
+  pdl_launch_dependents();
+  pdl_wait();
   float* dst = out + (size_t)t * H;
   if (id < 0 || id >= V) {
     for (int h = threadIdx.x; h < H; h += blockDim.x) dst[h] = __int_as_float(0x7fc00000);
@@ -26,9 +28,9 @@ extern "C" int qe_embedding(const int* ids, const void* table, float* out, int T
                             int dtype, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (dtype == QE_DTYPE_F32)
-    embedding_kernel<float><<<T, 256, 0, stream>>>(ids, (const float*)table, out, H, V);
+    qe_launch(embedding_kernel<float>, dim3(T), dim3(256), 0, stream, ids, (const float*)table, out, H, V);
   else if (dtype == QE_DTYPE_BF16)
-    embedding_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, H, V);
+    qe_launch(embedding_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, ids, (const __nv_bfloat16*)table, out, H, V);
   else QE_REFUSE("embedding: unknown dtype %d", dtype);
   QE_CHECK_LAUNCH("embedding");
   return 0;
@@ -45,6 +47,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
                                    const int* __restrict__ rows, const float* __restrict__ w,
                                    float eps, T* __restrict__ out, int H) {
   __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
   const int n = blockIdx.x;
   const int src_row = rows ? rows[n] : n;
   float* r = resid + (size_t)src_row * H;
@@ -71,9 +75,9 @@ extern "C" int qe_add_rmsnorm(float* resid, const void* delta, const int* rows, 
   if (n_rows <= 0) return 0;
   const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
   if (dtype == QE_DTYPE_F32)
-    add_rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(resid, (const float*)delta, rows, w, eps, (float*)out, H);
+    qe_launch(add_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, resid, (const float*)delta, rows, w, eps, (float*)out, H);
   else if (dtype == QE_DTYPE_BF16)
-    add_rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(resid, (const __nv_bfloat16*)delta, rows, w, eps, (__nv_bfloat16*)out, H);
+    qe_launch(add_rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, resid, (const __nv_bfloat16*)delta, rows, w, eps, (__nv_bfloat16*)out, H);
   else QE_REFUSE("add_rmsnorm: unknown dtype %d", dtype);
   QE_CHECK_LAUNCH("add_rmsnorm");
   return 0;
@@ -85,6 +89,8 @@ extern "C" int qe_add_rmsnorm(float* resid, const void* delta, const int* rows, 
 // ---------------------------------------------------------------------------------------
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
   for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
     const size_t t = e / I;
     const int i = (int)(e - t * I);
@@ -100,9 +106,9 @@ extern "C" int qe_silu_mul(const void* gate_up, void* out, int T, int I, int dty
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   if (dtype == QE_DTYPE_F32)
-    silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, I, total);
+    qe_launch(silu_mul_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)gate_up, (float*)out, I, total);
   else if (dtype == QE_DTYPE_BF16)
-    silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, I, total);
+    qe_launch(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, I, total);
   else QE_REFUSE("silu_mul: unknown dtype %d", dtype);
   QE_CHECK_LAUNCH("silu_mul");
   return 0;
@@ -125,6 +131,8 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ q, T* __restrict__ 
                                              T* __restrict__ pages, const int* __restrict__ slot_mapping,
                                              int T_tokens, int Hq, int Hkv, int D, int page_size, int write_kv) {
   extern __shared__ float smem[];
+  pdl_launch_dependents();
+  pdl_wait();
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads_total = Hq + 2 * Hkv;
@@ -198,11 +206,11 @@ extern "C" int qe_qk_norm_rope_kv_write(void* q, void* k, const void* v, long q_
   const int blocks = (int)((items + warps - 1) / warps);
   const size_t smem = (size_t)warps * D * sizeof(float);
   if (dtype == QE_DTYPE_F32)
-    qk_norm_rope_kv_write_kernel<float><<<blocks, warps * 32, smem, stream>>>(
+    qe_launch(qk_norm_rope_kv_write_kernel<float>, dim3(blocks), dim3(warps * 32), smem, stream,
         (float*)q, (float*)k, (const float*)v, q_stride, k_stride, v_stride, positions, qw, kw, eps, inv_freq,
         rotary_dim, (float*)pages, slot_mapping, T, Hq, Hkv, D, page_size, write_kv);
   else if (dtype == QE_DTYPE_BF16)
-    qk_norm_rope_kv_write_kernel<__nv_bfloat16><<<blocks, warps * 32, smem, stream>>>(
+    qe_launch(qk_norm_rope_kv_write_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), smem, stream,
         (__nv_bfloat16*)q, (__nv_bfloat16*)k, (const __nv_bfloat16*)v, q_stride, k_stride, v_stride, positions, qw, kw,
         eps, inv_freq, rotary_dim, (__nv_bfloat16*)pages, slot_mapping, T, Hq, Hkv, D, page_size, write_kv);
   else QE_REFUSE("qk_norm_rope_kv_write: unknown dtype %d", dtype);

@@ -15,3 +15,7 @@ void qe_set_error(const char* fmt, ...) {
 extern "C" const char* qe_last_error() { return g_error; }
 
 extern "C" int qe_abi_version() { return 1; }
+
+static int g_pdl_enabled = 1;
+extern "C" void qe_set_pdl(int enabled) { g_pdl_enabled = enabled ? 1 : 0; }
+int qe_pdl_enabled() { return g_pdl_enabled; }

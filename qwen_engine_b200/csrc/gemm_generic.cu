@@ -17,6 +17,8 @@ gemm_generic_kernel(const TIn* __restrict__ x, const TIn* __restrict__ w, TOut* 
                     int M, int N, int K) {
   __shared__ float xs[GG_BK][GG_BM + 4];
   __shared__ float ws[GG_BK][GG_BN + 4];
+  pdl_launch_dependents();
+  pdl_wait();
   const int m0 = blockIdx.y * GG_BM, n0 = blockIdx.x * GG_BN;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;   // 16 x 16 threads, 4 x 4 outputs each
   float acc[4][4];
@@ -70,13 +72,13 @@ extern "C" int qe_linear_generic(const void* x, const void* w, void* out, int M,
   dim3 grid((N + GG_BN - 1) / GG_BN, (M + GG_BM - 1) / GG_BM);
   if (grid.y > 65535) QE_REFUSE("linear: M %d is too large for the generic kernel", M);
   if (dtype == QE_DTYPE_F32) {
-    gemm_generic_kernel<float, float><<<grid, 256, 0, stream>>>((const float*)x, (const float*)w, (float*)out, M, N, K);
+    qe_launch(gemm_generic_kernel<float, float>, grid, dim3(256), 0, stream, (const float*)x, (const float*)w, (float*)out, M, N, K);
   } else if (dtype == QE_DTYPE_BF16) {
     if (out_f32)
-      gemm_generic_kernel<__nv_bfloat16, float><<<grid, 256, 0, stream>>>(
+      qe_launch(gemm_generic_kernel<__nv_bfloat16, float>, grid, dim3(256), 0, stream,
           (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (float*)out, M, N, K);
     else
-      gemm_generic_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, stream>>>(
+      qe_launch(gemm_generic_kernel<__nv_bfloat16, __nv_bfloat16>, grid, dim3(256), 0, stream,
           (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, N, K);
   } else QE_REFUSE("linear: unknown dtype %d", dtype);
   QE_CHECK_LAUNCH("linear_generic");

@@ -28,7 +28,18 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {   // read once: do
   return v;
 }
 
-template <int MT, typename TOut>
+// silu(g) * u for a pair of bfloat16 values, in float32, rounded once (the reference's silumul,
+// src/layers/fused_ops/silumul.py:50-53, without its intermediate rounding of silu)
+__device__ __forceinline__ uint32_t silu_mul_pair(uint32_t g, uint32_t u) {
+  const float2 gf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&g));
+  const float2 uf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u));
+  __nv_bfloat162 r = __floats2bfloat162_rn(gf.x / (1.f + expf(-gf.x)) * uf.x, gf.y / (1.f + expf(-gf.y)) * uf.y);
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+
+// SILU: the token operand is not x[M, K] but gate_up[M, 2K]: x[m, k] = silu(gate_up[m, k]) * gate_up[m, K + k]
+// is formed while loading (the feed-forward's activation fused into its output projection).
+template <int MT, typename TOut, bool SILU>
 __global__ void __launch_bounds__(512)
 gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                     TOut* __restrict__ out, int M, int N, int K, int k_per_warp) {
@@ -40,6 +51,7 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
   const __nv_bfloat16* w0 = w + (size_t)r0 * K;
   const __nv_bfloat16* w1 = w + (size_t)r1 * K;
   const int kbeg = warp * k_per_warp, kend = min(K, kbeg + k_per_warp);
+  const int x_ld = SILU ? 2 * K : K;
 
   float acc[MT][4];
 #pragma unroll
@@ -48,25 +60,52 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
     for (int i = 0; i < 4; ++i) acc[t][i] = 0.f;
 
   const uint4 zero = make_uint4(0, 0, 0, 0);
-#pragma unroll 2
-  for (int k0 = kbeg; k0 < kend; k0 += 64) {
+  // a chunk: 64 k of the 16 rows = four 16-byte loads per lane (K and k_per_warp are multiples of 8)
+  struct Chunk { uint4 a0, b0, a1, b1; };
+  auto load_chunk = [&](int k0) {
+    Chunk ch;
     const int ka = k0 + 8 * c, kb = k0 + 32 + 8 * c;
-    const bool ina = ka < kend, inb = kb < kend;      // K and k_per_warp are multiples of 8
-    const uint4 wa0 = ina ? ld_stream16(w0 + ka) : zero;
-    const uint4 wb0 = ina ? ld_stream16(w1 + ka) : zero;
-    const uint4 wa1 = inb ? ld_stream16(w0 + kb) : zero;
-    const uint4 wb1 = inb ? ld_stream16(w1 + kb) : zero;
+    ch.a0 = ka < kend ? ld_stream16(w0 + ka) : zero;
+    ch.b0 = ka < kend ? ld_stream16(w1 + ka) : zero;
+    ch.a1 = kb < kend ? ld_stream16(w0 + kb) : zero;
+    ch.b1 = kb < kend ? ld_stream16(w1 + kb) : zero;
+    return ch;
+  };
+  auto load_x = [&](int m, int k) {
+    if (m >= M || k >= kend) return zero;
+    const __nv_bfloat16* p = x + (size_t)m * x_ld + k;
+    uint4 v = __ldg(reinterpret_cast<const uint4*>(p));
+    if (SILU) {
+      const uint4 u = __ldg(reinterpret_cast<const uint4*>(p + K));
+      v.x = silu_mul_pair(v.x, u.x); v.y = silu_mul_pair(v.y, u.y);
+      v.z = silu_mul_pair(v.z, u.z); v.w = silu_mul_pair(v.w, u.w);
+    }
+    return v;
+  };
+  auto compute = [&](const Chunk& ch, int k0) {
+    const int ka = k0 + 8 * c, kb = k0 + 32 + 8 * c;
 #pragma unroll
     for (int t = 0; t < MT; ++t) {
-      const int m = t * 8 + g;
-      const __nv_bfloat16* xr = x + (size_t)m * K;
-      const uint4 xa = (m < M && ina) ? __ldg(reinterpret_cast<const uint4*>(xr + ka)) : zero;
-      const uint4 xb = (m < M && inb) ? __ldg(reinterpret_cast<const uint4*>(xr + kb)) : zero;
-      mma_bf16_16816(acc[t], wa0.x, wb0.x, wa0.y, wb0.y, xa.x, xa.y);
-      mma_bf16_16816(acc[t], wa0.z, wb0.z, wa0.w, wb0.w, xa.z, xa.w);
-      mma_bf16_16816(acc[t], wa1.x, wb1.x, wa1.y, wb1.y, xb.x, xb.y);
-      mma_bf16_16816(acc[t], wa1.z, wb1.z, wa1.w, wb1.w, xb.z, xb.w);
+      const uint4 xa = load_x(t * 8 + g, ka);
+      const uint4 xb = load_x(t * 8 + g, kb);
+      mma_bf16_16816(acc[t], ch.a0.x, ch.b0.x, ch.a0.y, ch.b0.y, xa.x, xa.y);
+      mma_bf16_16816(acc[t], ch.a0.z, ch.b0.z, ch.a0.w, ch.b0.w, xa.z, xa.w);
+      mma_bf16_16816(acc[t], ch.a1.x, ch.b1.x, ch.a1.y, ch.b1.y, xb.x, xb.y);
+      mma_bf16_16816(acc[t], ch.a1.z, ch.b1.z, ch.a1.w, ch.b1.w, xb.z, xb.w);
     }
+  };
+  // The weights are nobody's output: their first two chunks are on their way before this kernel
+  // waits for the one before it, whose output x is.
+  Chunk c0 = load_chunk(kbeg), c1 = load_chunk(kbeg + 64);
+  pdl_launch_dependents();
+  pdl_wait();
+  for (int k0 = kbeg; k0 < kend; k0 += 128) {
+    const Chunk n0c = load_chunk(k0 + 128);
+    compute(c0, k0);
+    const Chunk n1c = load_chunk(k0 + 192);
+    compute(c1, k0 + 64);
+    c0 = n0c;
+    c1 = n1c;
   }
   // acc[t][0..1]: weight row g, tokens 8t + 2c + {0,1};  acc[t][2..3]: weight row g + 8
   constexpr int MW = 8 * MT;
@@ -89,7 +128,7 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
   }
 }
 
-template <int MT>
+template <int MT, bool SILU>
 static int launch_small_m(const void* x, const void* w, void* out, int M, int N, int K, int out_f32,
                           cudaStream_t stream) {
   // warps split K in slices that are multiples of 64; more warps when there are few CTAs
@@ -101,30 +140,43 @@ static int launch_small_m(const void* x, const void* w, void* out, int M, int N,
   static bool configured = false;             // once, not per launch: launches may be under stream capture
   if (!configured) {
     const int max_smem = 16 * 16 * 8 * MT * (int)sizeof(float);
-    cudaFuncSetAttribute(gemm_small_m_kernel<MT, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-    cudaFuncSetAttribute(gemm_small_m_kernel<MT, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    cudaFuncSetAttribute(gemm_small_m_kernel<MT, float, SILU>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    cudaFuncSetAttribute(gemm_small_m_kernel<MT, __nv_bfloat16, SILU>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
     configured = true;
   }
   if (out_f32) {
-    gemm_small_m_kernel<MT, float><<<ctas, warps * 32, smem, stream>>>(
-        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (float*)out, M, N, K, k_per_warp);
+    qe_launch(gemm_small_m_kernel<MT, float, SILU>, dim3(ctas), dim3(warps * 32), smem, stream,
+              (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (float*)out, M, N, K, k_per_warp);
   } else {
-    gemm_small_m_kernel<MT, __nv_bfloat16><<<ctas, warps * 32, smem, stream>>>(
-        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, N, K, k_per_warp);
+    qe_launch(gemm_small_m_kernel<MT, __nv_bfloat16, SILU>, dim3(ctas), dim3(warps * 32), smem, stream,
+              (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, N, K, k_per_warp);
   }
   QE_CHECK_LAUNCH("linear_small_m");
   return 0;
 }
 
-// Returns 0 when run, 1 when refused (qe_last_error says why), 2 on a launch error.
-extern "C" int qe_linear_small_m(const void* x, const void* w, void* out, int M, int N, int K,
-                                 int out_f32, cudaStream_t stream) {
+template <bool SILU>
+static int dispatch_small_m(const void* x, const void* w, void* out, int M, int N, int K, int out_f32,
+                            cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 64) QE_REFUSE("linear_small_m: M = %d is above 64", M);
   if (K <= 0 || K % 8) QE_REFUSE("linear_small_m: K = %d is not a positive multiple of 8", K);
   if (((uintptr_t)x | (uintptr_t)w) & 15) QE_REFUSE("linear_small_m: operands must be 16-byte aligned");
-  if (M <= 8) return launch_small_m<1>(x, w, out, M, N, K, out_f32, stream);
-  if (M <= 16) return launch_small_m<2>(x, w, out, M, N, K, out_f32, stream);
-  if (M <= 32) return launch_small_m<4>(x, w, out, M, N, K, out_f32, stream);
-  return launch_small_m<8>(x, w, out, M, N, K, out_f32, stream);
+  if (M <= 8) return launch_small_m<1, SILU>(x, w, out, M, N, K, out_f32, stream);
+  if (M <= 16) return launch_small_m<2, SILU>(x, w, out, M, N, K, out_f32, stream);
+  if (M <= 32) return launch_small_m<4, SILU>(x, w, out, M, N, K, out_f32, stream);
+  return launch_small_m<8, SILU>(x, w, out, M, N, K, out_f32, stream);
+}
+
+// Returns 0 when run, 1 when refused (qe_last_error says why), 2 on a launch error.
+extern "C" int qe_linear_small_m(const void* x, const void* w, void* out, int M, int N, int K,
+                                 int out_f32, cudaStream_t stream) {
+  return dispatch_small_m<false>(x, w, out, M, N, K, out_f32, stream);
+}
+
+// out[M, N] = (silu(gate_up[:, :K]) * gate_up[:, K:]) · w[N, K]^T: the activation of the feed-forward
+// formed while its output projection loads it.
+extern "C" int qe_linear_small_m_silu(const void* gate_up, const void* w, void* out, int M, int N, int K,
+                                      int out_f32, cudaStream_t stream) {
+  return dispatch_small_m<true>(gate_up, w, out, M, N, K, out_f32, stream);
 }

@@ -115,6 +115,8 @@ __global__ void __launch_bounds__(TC_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     TOut* __restrict__ out, int M, int N, int K) {
   extern __shared__ unsigned char smem_raw[];
+  pdl_launch_dependents();
+  pdl_wait();
   TcSmem& sm = *reinterpret_cast<TcSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * TC_BN;
@@ -312,9 +314,9 @@ extern "C" int qe_linear_tcgen05(const void* x, const void* w, void* out, int M,
     configured = true;
   }
   if (out_f32)
-    gemm_tcgen05_kernel<float><<<grid, TC_THREADS, smem, stream>>>(map_x, map_w, (float*)out, M, N, K);
+    qe_launch(gemm_tcgen05_kernel<float>, grid, dim3(TC_THREADS), smem, stream, map_x, map_w, (float*)out, M, N, K);
   else
-    gemm_tcgen05_kernel<__nv_bfloat16><<<grid, TC_THREADS, smem, stream>>>(map_x, map_w, (__nv_bfloat16*)out, M, N, K);
+    qe_launch(gemm_tcgen05_kernel<__nv_bfloat16>, grid, dim3(TC_THREADS), smem, stream, map_x, map_w, (__nv_bfloat16*)out, M, N, K);
   QE_CHECK_LAUNCH("linear_tcgen05");
   return 0;
 }

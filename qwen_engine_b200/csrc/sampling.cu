@@ -53,6 +53,8 @@ __global__ void __launch_bounds__(SM_THREADS)
 argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
   __shared__ float sv[33];
   __shared__ int si[33];
+  pdl_launch_dependents();
+  pdl_wait();
   float bv; int bi;
   block_argmax(logits + (size_t)blockIdx.x * V, V, bv, bi, sv, si);
   if (threadIdx.x == 0) out[blockIdx.x] = bi;
@@ -61,7 +63,7 @@ argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
 extern "C" int qe_argmax(const float* logits, int* out, int N, int V, cudaStream_t stream) {
   if (N <= 0) return 0;
   if (V <= 0) QE_REFUSE("argmax: empty vocabulary");
-  argmax_kernel<<<N, SM_THREADS, 0, stream>>>(logits, out, V);
+  qe_launch(argmax_kernel, dim3(N), dim3(SM_THREADS), 0, stream, logits, out, V);
   QE_CHECK_LAUNCH("argmax");
   return 0;
 }
@@ -79,6 +81,8 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
   __shared__ double s_part[SM_THREADS];
   __shared__ int s_result;
   __shared__ double s_total;
+  pdl_launch_dependents();
+  pdl_wait();
   const int n = blockIdx.x;
   const float* row = logits + (size_t)n * V;
   float mx; int arg;
@@ -148,7 +152,7 @@ extern "C" int qe_sample(const float* logits, const float* temperature, const in
                          const float* uniform, int* out, int N, int V, cudaStream_t stream) {
   if (N <= 0) return 0;
   if (V <= 0) QE_REFUSE("sample: empty vocabulary");
-  sample_kernel<<<N, SM_THREADS, 0, stream>>>(logits, temperature, top_k, uniform, out, V);
+  qe_launch(sample_kernel, dim3(N), dim3(SM_THREADS), 0, stream, logits, temperature, top_k, uniform, out, V);
   QE_CHECK_LAUNCH("sample");
   return 0;
 }

@@ -24,7 +24,7 @@ TCGEN05_ENABLED = True  # the tcgen05 product for more rows (False: the generic 
 FLASH_ROWS = 64         # rows (query token x query head of a group) per work item of the flash kernel
 FLASH_BN = 64           # keys per tile of the flash kernel
 FLASH_SPLIT = 256       # keys per part when a decoded token's context is split (reference attn.py:605)
-FLASH_TARGET_CTAS = 296  # two CTAs per SM: below this, long contexts are split to fill the GPU
+FLASH_TARGET_CTAS = 296  # two CTAs per SM: long contexts are split into as many parts as fit in one wave
 
 
 class ExtensionMissing(RuntimeError):
@@ -162,6 +162,31 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     _check(lib().qe_linear_generic(_ptr(x), _ptr(w), _ptr(out), M, N, K, _dt(x), out_f32, _stream()), "linear")
 
 
+def linear_silu_mul(gate_up: torch.Tensor, w: torch.Tensor, out: torch.Tensor, scratch) -> None:
+    """out[M, N] = (silu(gate_up[:, :I]) * gate_up[:, I:]) · w[N, I]^T.  For a few rows in bfloat16 the
+    activation is formed while the product loads it; otherwise ``silu_mul`` runs first into a buffer
+    that ``scratch(shape, dtype)`` provides."""
+    M, I2 = gate_up.shape
+    I = I2 // 2
+    N = w.shape[0]
+    _need(I2 % 2 == 0 and w.shape == (N, I) and w.dtype == gate_up.dtype, "linear_silu_mul: w must be [N, I] for gate_up [M, 2I]")
+    _need(out.shape == (M, N) and out.dtype in (gate_up.dtype, torch.float32), "linear_silu_mul: out must be [M, N]")
+    _need(gate_up.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "linear_silu_mul: operands must be contiguous")
+    if gate_up.dtype == torch.bfloat16 and M <= SMALL_M_MAX and I % 8 == 0:
+        _check(lib().qe_linear_small_m_silu(_ptr(gate_up), _ptr(w), _ptr(out), M, N, I,
+                                            int(out.dtype == torch.float32), _stream()), "linear_silu_mul")
+        return
+    act = scratch((M, I), gate_up.dtype)
+    silu_mul(gate_up, act)
+    linear(act, w, out)
+
+
+def set_pdl(enabled: bool) -> None:
+    """Programmatic dependent launch of the kernels (on by default): a kernel may start, and a
+    product may begin to fetch its weights, while the kernel before it is still running."""
+    lib().qe_set_pdl(int(bool(enabled)))
+
+
 def tcgen05_status() -> int:
     """0 if no bounded wait of the tcgen05 product kernel ever ran out; else the code of the first
     that did (1: a shared-memory slot never came free, 2: TMA bytes never landed, 3: the
@@ -261,7 +286,7 @@ def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
                 lo = (max(0, c - window + 1) // FLASH_BN) * FLASH_BN if window else 0
                 splits = 1
                 if n <= tpt and base < FLASH_TARGET_CTAS and total - lo > FLASH_SPLIT:
-                    splits = min(-(-(total - lo) // FLASH_SPLIT), -(-FLASH_TARGET_CTAS // base))
+                    splits = min(-(-(total - lo) // FLASH_SPLIT), max(1, FLASH_TARGET_CTAS // base))
             if splits > 1:
                 for sp in range(splits):
                     items += [r, 0, 0, 0, n_parts + sp, splits, sp, 0]
@@ -284,9 +309,25 @@ def decode_splits(num_reqs: int, max_tokens: int, geometries, dtype: torch.dtype
     for geo in geometries:
         Hq, Hkv, D, window = geo
         span = min(max_tokens, window) if window else max_tokens
-        want = -(-FLASH_TARGET_CTAS // max(1, num_reqs * Hkv))
+        want = max(1, FLASH_TARGET_CTAS // max(1, num_reqs * Hkv))      # all parts run in one wave
         out[geo] = max(1, min(want, -(-span // FLASH_SPLIT)))
     return out
+
+
+_MERGE_COUNTERS = 1 << 16
+_merge_counter_tensors: dict = {}
+
+
+def _merge_counters(device) -> torch.Tensor:
+    """Zeroed ints, one per (part, kv head), that the flash kernel uses to find the CTA that finishes a
+    split context last (it merges the parts and sets its counter back to zero).  One tensor per device
+    for the life of the process, so that its address is the same in every captured step."""
+    key = torch.device(device).index
+    t = _merge_counter_tensors.get(key)
+    if t is None:
+        t = torch.zeros(_MERGE_COUNTERS, dtype=torch.int32, device=device)
+        _merge_counter_tensors[key] = t
+    return t
 
 
 def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: torch.Tensor, ctx,
@@ -311,11 +352,12 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
         if n_parts:
             part_acc = ctx.arena.alloc((n_parts * Hkv * part_rows, D), torch.float32)
             part_ml = ctx.arena.alloc((n_parts * Hkv * part_rows, 2), torch.float32)
-        _check(lib().qe_flash_attention(
+        counters = _merge_counters(qkv.device) if 0 < n_parts * Hkv <= _MERGE_COUNTERS else None
+        _check(lib().qe_flash_attention_fused_merge(
             _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(block_tables), int(block_tables.shape[1]),
             _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), _ptr(items), n_items, _ptr(merge), n_merge, _ptr(out),
-            _ptr(part_acc), _ptr(part_ml), int(part_rows), ctypes.c_float(scale), int(window), Hq, Hkv, D,
-            int(kv_pages.shape[3]), _stream()), "flash_attention")
+            _ptr(part_acc), _ptr(part_ml), int(part_rows), _ptr(counters), ctypes.c_float(scale), int(window),
+            Hq, Hkv, D, int(kv_pages.shape[3]), _stream()), "flash_attention")
         return
     tiles = plan["tiles"]
     n_tiles = tiles.numel() // 2

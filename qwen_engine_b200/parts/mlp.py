@@ -34,6 +34,4 @@ class SwiGLU(FeedForward):
         T, I = ctx.num_tokens, self.intermediate_size
         gate_up = ctx.arena.alloc((T, 2 * I), ctx.dtype)
         ops.linear(x, self.w_gate_up, gate_up)
-        act = ctx.arena.alloc((T, I), ctx.dtype)
-        ops.silu_mul(gate_up, act)
-        ops.linear(act, self.w_down, out)
+        ops.linear_silu_mul(gate_up, self.w_down, out, ctx.arena.alloc)

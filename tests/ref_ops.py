@@ -139,6 +139,12 @@ def silu_mul(gate_up, out):
     out.copy_((g / (1.0 + torch.exp(-g)) * u).to(out.dtype))
 
 
+def linear_silu_mul(gate_up, w, out, scratch):
+    act = scratch((gate_up.shape[0], gate_up.shape[1] // 2), gate_up.dtype)
+    silu_mul(gate_up, act)
+    linear(act, w, out)
+
+
 def argmax(logits, out):
     out.copy_(torch.argmax(logits, dim=-1).to(torch.int32))
 
@@ -170,7 +176,7 @@ def sample(logits, temperature, top_k, uniform, out):
 
 
 _NAMES = ["prepare_matrix", "embedding", "add_rmsnorm", "add_rmsnorm_rows", "linear",
-          "qk_norm_rope_kv_write", "rope_neox", "plan_attention", "paged_attention", "silu_mul",
+          "qk_norm_rope_kv_write", "rope_neox", "plan_attention", "paged_attention", "silu_mul", "linear_silu_mul",
           "argmax", "sample"]
 
 

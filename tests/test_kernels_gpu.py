@@ -131,6 +131,20 @@ def test_silu_mul(dtype, T, I):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,I", [(1, 40, 56), (8, 1024, 3072), (33, 80, 224), (64, 72, 152), (70, 100, 64), (5, 30, 10)])
+def test_linear_silu_mul(dtype, M, N, I):
+    """The feed-forward's activation fused into its output projection (few rows, bfloat16), and the
+    two-kernel route for everything else."""
+    gu = _randn((M, 2 * I), dtype, 40, 2.0)
+    w = _randn((N, I), dtype, 41, 0.1)
+    want = torch.empty(M, N, dtype=dtype)
+    ref_ops.linear_silu_mul(gu, w, want, lambda shape, dt: torch.empty(shape, dtype=dt))
+    got = torch.empty(M, N, dtype=dtype, device=DEV)
+    ops.linear_silu_mul(gu.to(DEV), w.to(DEV), got, lambda shape, dt: torch.empty(shape, dtype=dt, device=DEV))
+    _close(got, want, dtype, tol16=1.2e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("Hq,Hkv,D,P,rot", [(4, 2, 16, 4, 16), (6, 3, 48, 8, 48), (5, 1, 128, 16, 128),
                                             (2, 2, 80, 2, 32), (3, 1, 256, 16, 256)])
 @pytest.mark.parametrize("norm", [True, False])
