@@ -13,12 +13,13 @@
 // flash decoding, attn.py:374-594 with split_size 256); then it writes its unnormalised
 // accumulator with max and sum in float32 to scratch memory and a merge kernel combines the parts.
 //
-// Work items (int32 x 8): req, q0 (first token of the tile within the request's new tokens),
+// Work items (int32 x 12): req, q0 (first token of the tile within the request's new tokens),
 // kv_lo, kv_hi (key range; kv_hi is further capped by causality), part (-1: write the output;
 // else index of the partial), n_splits, split (when n_splits > 0 the key range is computed here
-// from the request's length on the device: the keys from the window's start on, cut into
-// n_splits equal runs of whole key tiles, of which this item takes run `split`; so the work
-// list of a decode step does not change as contexts grow), 1 unused.
+// from the request's length: the keys from the window's start on, cut into n_splits equal runs
+// of whole key tiles, of which this item takes run `split`), then the request's first row in the
+// flat batch, its number of new tokens and its tokens already in the cache (copies of cu_q and
+// ctx_lens, so that a CTA needs one load to know its work), 2 unused.
 // Merge items (int32 x 4): req, q0, first part, number of parts.
 #include "common.cuh"
 #include <math.h>
@@ -27,7 +28,7 @@
 #define FA_BN 64
 #define FA_WARPS 4
 #define FA_THREADS (FA_WARPS * 32)
-#define FA_ITEM_INTS 8
+#define FA_ITEM_INTS 12
 
 __device__ __forceinline__ void fa_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -152,7 +153,7 @@ template <int D>
 __device__ __forceinline__ void fa_merge_parts(const float* part_acc, const float* part_ml, int part_rows, int first,
                                                int n, int hkv, int Hkv, int nrows, int G, int Hq,
                                                __nv_bfloat16* out_row0 /* row of the tile's first token */) {
-  for (int e = threadIdx.x; e < nrows * D; e += blockDim.x) {
+  for (int e = threadIdx.x; e < nrows * D; e += FA_THREADS) {       // the computing threads only
     const int r = e / D, d = e - r * D;
     float m = -INFINITY;
     for (int sp = 0; sp < n; ++sp) m = fmaxf(m, __ldcg(part_ml + 2 * ((((size_t)first + sp) * Hkv + hkv) * part_rows + r)));
@@ -179,8 +180,56 @@ __device__ __forceinline__ void fa_merge_parts(const float* part_acc, const floa
 // `counters` (may be null): one int per (first part, kv head), zero before the launch.  The CTA that
 // finishes a request's last part combines the parts itself and sets the counter back to zero, so no
 // merge kernel is needed; with a null pointer the parts are left for flash_merge_kernel.
-template <int D>
-__global__ void __launch_bounds__(FA_THREADS)
+// ---- mbarrier helpers of the tile pipeline; every wait is bounded ------------------------------------
+#define FA_WAIT_LIMIT (1u << 22)
+__device__ int g_fa_status = 0;          // 0 = fine; else code of the first wait that ran out
+
+__device__ __forceinline__ uint32_t fa_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void fa_bar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" :: "r"(fa_smem(bar)), "r"(count));
+}
+__device__ __forceinline__ void fa_bar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" :: "r"(fa_smem(bar)) : "memory");
+}
+// arrives (without adding to the expected count) once this thread's earlier cp.async have landed
+__device__ __forceinline__ void fa_bar_arrive_on_copies(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" :: "r"(fa_smem(bar)) : "memory");
+}
+__device__ __forceinline__ bool fa_bar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
+  for (uint32_t i = 0; i < FA_WAIT_LIMIT; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(ok) : "r"(fa_smem(bar)), "r"(parity) : "memory");
+    if (ok) return true;
+    if ((i & 63) == 63 && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicCAS(&g_fa_status, 0, code);
+  return false;
+}
+__device__ __forceinline__ void fa_consumer_sync() { asm volatile("bar.sync 1, %0;\n" :: "n"(FA_THREADS) : "memory"); }
+
+// STAGES: depth of the key-tile pipeline; QROWS: rows of the query tile that are staged (64, or 16 in
+// launches whose items all have at most 16 rows: decode steps, which then afford a third stage).
+//
+// 8 warps: warps 0-3 compute, warps 4-7 only fetch.  The fetching warps run ahead of the computing
+// ones by up to STAGES tiles: they gather a tile's keys and values page by page with cp.async into a
+// free slot and arrive on the slot's `full` barrier when their copies have landed; a computing warp
+// waits for `full`, works on the tile, and arrives on the slot's `empty` barrier, which the fetching
+// warps wait for before they reuse the slot.  So no address arithmetic and no CTA-wide barrier sits
+// between two tiles of the computing warps.
+//
+// Two ways of sharing a key tile between the 4 computing warps.  A tile of many rows (a prompt
+// portion): each warp owns 16 rows and visits all 64 keys.  A tile of at most 16 rows (decoded
+// tokens: the query heads of one group): every warp takes the same rows and 16 of the 64 keys, with
+// a running max, sum and output of its own; the four are combined in shared memory at the end.
+//
+// `counters` (may be null): one int per (first part, kv head), zero before the launch.  The CTA that
+// finishes a request's last part combines the parts itself and sets the counter back to zero, so no
+// merge kernel is needed; with a null pointer the parts are left for flash_merge_kernel.
+template <int D, int STAGES, int QROWS>
+__global__ void __launch_bounds__(2 * FA_THREADS, (D <= 128 ? 2 : 1))
 flash_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride,
                        const __nv_bfloat16* __restrict__ pages, const int* __restrict__ block_tables,
                        int max_blocks, const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
@@ -190,12 +239,13 @@ flash_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride,
   constexpr int LD = D + 8;                         // padded row, in elements
   constexpr int CH = D / 8;                         // 16-byte chunks in a row
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* sq = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [64][LD]
-  __nv_bfloat16* sk = sq + FA_BM * LD;                                     // [2][64][LD]
-  __nv_bfloat16* sv = sk + 2 * FA_BN * LD;                                 // [2][64][LD]
-  __shared__ int s_last;
+  __nv_bfloat16* sq = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [QROWS][LD]
+  __nv_bfloat16* sk = sq + QROWS * LD;                                     // [STAGES][64][LD]
+  __nv_bfloat16* sv = sk + STAGES * FA_BN * LD;                            // [STAGES][64][LD]
+  __shared__ uint64_t bar_full[STAGES], bar_empty[STAGES];
+  __shared__ int s_last, s_abort;
 
-  // the work lists, lengths and block tables come from the host's copy, not from a kernel
+  // the work lists come from the host's copy, not from a kernel
   pdl_launch_dependents();
   const int* it = items + (size_t)blockIdx.x * FA_ITEM_INTS;
   const int req = it[0], q0 = it[1], part = it[4], n_splits = it[5], split = it[6];
@@ -203,12 +253,9 @@ flash_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride,
   const int hkv = blockIdx.y;
   const int G = Hq / Hkv;
   const int tpt = FA_BM / G;                        // tokens in a tile
-  const int row0 = cu_q[req];
-  const int q_len = cu_q[req + 1] - row0;
-  const int ctx = ctx_lens[req];
+  const int row0 = it[7], q_len = it[8], ctx = it[9];
   const int ntok = min(tpt, q_len - q0);
   const int nrows = ntok * G;
-  const int* table = block_tables + (size_t)req * max_blocks;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
 
@@ -227,39 +274,73 @@ flash_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride,
   const int kt_first = (kv_begin / FA_BN) * FA_BN;
   const int n_tiles = kv_end > kt_first ? (kv_end - kt_first + FA_BN - 1) / FA_BN : 0;
 
-  pdl_wait();            // q and the newest keys and values are the previous kernel's output
-  // ---- stage the query rows --------------------------------------------------------------
-  for (int e = threadIdx.x; e < FA_BM * CH; e += FA_THREADS) {
-    const int r = e / CH, ch = e - r * CH;
-    __nv_bfloat16* dst = sq + r * LD + ch * 8;
-    if (r < nrows) {
-      const int ti = r / G, hg = r - ti * G;
-      cp_async16(dst, q + (size_t)(row0 + q0 + ti) * q_stride + (size_t)(hkv * G + hg) * D + ch * 8);
-    } else {
-      *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+  if (threadIdx.x == 0) {
+    for (int st = 0; st < STAGES; ++st) {
+      fa_bar_init(&bar_full[st], 2 * FA_THREADS);   // each fetching thread: once for its copies, once for its stores
+      fa_bar_init(&bar_empty[st], FA_WARPS);        // one arrival per computing warp
     }
+    s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  auto load_tile = [&](int stage, int kt) {
-    __nv_bfloat16* dk = sk + stage * FA_BN * LD;
-    __nv_bfloat16* dv = sv + stage * FA_BN * LD;
-    for (int e = threadIdx.x; e < FA_BN * CH; e += FA_THREADS) {
-      const int j = e / CH, ch = e - j * CH;
-      const int kj = kt + j;
-      if (kj >= kv_begin && kj < kv_end) {
-        const int page = table[kj / page_size];
-        const size_t base = ((((size_t)page * 2) * Hkv + hkv) * page_size + (kj % page_size)) * D + ch * 8;
-        cp_async16(dk + j * LD + ch * 8, pages + base);
-        cp_async16(dv + j * LD + ch * 8, pages + base + (size_t)Hkv * page_size * D);
-      } else {
-        *reinterpret_cast<uint4*>(dk + j * LD + ch * 8) = make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4*>(dv + j * LD + ch * 8) = make_uint4(0, 0, 0, 0);
+  __syncthreads();
+  pdl_wait();            // q and the newest keys and values are the previous kernel's output
+  if (QROWS < FA_BM && nrows > QROWS) return;       // the launcher promised small tiles (never taken)
+  volatile int* abort_flag = &s_abort;
+
+  if (warp >= FA_WARPS) {
+    // ================= fetching warps ==================================================================
+    const int ptid = threadIdx.x - FA_THREADS;
+    const int* table = block_tables + (size_t)req * max_blocks;
+    // address arithmetic of the gather, hoisted: a page's stride, this head's offset in a page, K -> V
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
+    const size_t page_stride = (size_t)2 * Hkv * page_size * D;
+    const size_t v_off = (size_t)Hkv * page_size * D;
+    const __nv_bfloat16* head_base = pages + (size_t)hkv * page_size * D;
+    if (n_tiles > 0) {                              // the query rows travel with the first tile
+      for (int e = ptid; e < QROWS * CH; e += FA_THREADS) {
+        const int r = e / CH, ch = e - r * CH;
+        __nv_bfloat16* dst = sq + r * LD + ch * 8;
+        if (r < nrows) {
+          const int ti = r / G, hg = r - ti * G;
+          cp_async16(dst, q + (size_t)(row0 + q0 + ti) * q_stride + (size_t)(hkv * G + hg) * D + ch * 8);
+        } else {
+          *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
       }
     }
-  };
-  if (n_tiles > 0) load_tile(0, kt_first);
-  cp_async_commit();
+    for (int t = 0; t < n_tiles; ++t) {
+      const int stage = t % STAGES;
+      if (t >= STAGES && !fa_bar_wait(&bar_empty[stage], ((t / STAGES) - 1) & 1, abort_flag, 1)) break;
+      const int kt = kt_first + t * FA_BN;
+      __nv_bfloat16* dk = sk + stage * FA_BN * LD;
+      __nv_bfloat16* dv = sv + stage * FA_BN * LD;
+#pragma unroll 4
+      for (int e = ptid; e < FA_BN * CH; e += FA_THREADS) {
+        const int j = e / CH, ch = e - j * CH;
+        const int kj = kt + j;
+        const int so = j * LD + ch * 8;
+        if (kj >= kv_begin && kj < kv_end) {
+          int blk, off;
+          if (page_shift >= 0) { blk = kj >> page_shift; off = kj & (page_size - 1); }
+          else { blk = kj / page_size; off = kj - blk * page_size; }
+          const __nv_bfloat16* src = head_base + (size_t)table[blk] * page_stride + off * D + ch * 8;
+          cp_async16(dk + so, src);
+          cp_async16(dv + so, src + v_off);
+        } else {
+          *reinterpret_cast<uint4*>(dk + so) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(dv + so) = make_uint4(0, 0, 0, 0);
+        }
+      }
+      fa_bar_arrive_on_copies(&bar_full[stage]);    // when this thread's copies have landed
+      fa_bar_arrive(&bar_full[stage]);              // and its zero stores are released
+    }
+    cp_async_commit();
+    cp_async_wait<0>();                             // nothing of this thread's is in flight when it leaves
+    return;
+  }
 
-  const bool keysplit = nrows <= 16;                // few rows: the warps share the keys, not the rows
+  // ================= computing warps =====================================================================
+  const bool keysplit = nrows <= 16 || QROWS < FA_BM;   // few rows: the warps share the keys, not the rows
   const int row_base = keysplit ? 0 : warp * 16;
   // rows of this thread: r_lo = row_base + g and r_lo + 8
   const int r_lo = row_base + g, r_hi = r_lo + 8;
@@ -270,17 +351,16 @@ flash_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride,
 #pragma unroll
   for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
 
-  const bool warp_active = keysplit || warp * 16 < nrows;       // warps without rows only help loading
-
+  const bool warp_active = keysplit || warp * 16 < nrows;       // a warp without rows only hands slots back
+  bool ok = true;
   for (int t = 0; t < n_tiles; ++t) {
-    const int kt = kt_first + t * FA_BN;
-    if (t + 1 < n_tiles) load_tile((t + 1) & 1, kt + FA_BN);
-    cp_async_commit();
-    cp_async_wait<1>();
-    __syncthreads();
+    const int stage = t % STAGES;
+    ok = __all_sync(0xffffffffu, fa_bar_wait(&bar_full[stage], (t / STAGES) & 1, abort_flag, 2));
+    if (!ok) break;
     if (warp_active) {
-      const __nv_bfloat16* tk = sk + (t & 1) * FA_BN * LD;
-      const __nv_bfloat16* tv = sv + (t & 1) * FA_BN * LD;
+      const int kt = kt_first + t * FA_BN;
+      const __nv_bfloat16* tk = sk + stage * FA_BN * LD;
+      const __nv_bfloat16* tv = sv + stage * FA_BN * LD;
       if (keysplit)
         fa_tile<D, 1>(sq, tk, tv, 0, warp, kt, kv_begin, kv_end, pos_lo, pos_hi, window, scale_log2, lane,
                       m_lo, m_hi, l_lo, l_hi, o);
@@ -288,14 +368,15 @@ flash_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride,
         fa_tile<D, FA_BN / 16>(sq, tk, tv, row_base, 0, kt, kv_begin, kv_end, pos_lo, pos_hi, window, scale_log2,
                                lane, m_lo, m_hi, l_lo, l_hi, o);
     }
-    __syncthreads();                                // the stage is free for the load after next
+    __syncwarp();
+    if (lane == 0) fa_bar_arrive(&bar_empty[stage]);      // this warp is done with the slot
   }
-  cp_async_wait<0>();
+  if (!ok) return;                                  // a wait ran out: the status flag says so; nothing is written
 
   __nv_bfloat16* out_row0 = out + (size_t)(row0 + q0) * ((size_t)Hq * D);
   if (keysplit) {
     // ---- combine the four warps' shares of the keys in shared memory (the tiles are done) ------
-    __syncthreads();
+    fa_consumer_sync();
     float* xo = reinterpret_cast<float*>(sk);                  // [4 warps][16 rows][D]
     float* xml = xo + FA_WARPS * 16 * D;                        // [4 warps][16 rows][2]
 #pragma unroll
@@ -307,7 +388,7 @@ flash_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride,
       xml[(warp * 16 + g) * 2] = m_lo; xml[(warp * 16 + g) * 2 + 1] = l_lo;
       xml[(warp * 16 + g + 8) * 2] = m_hi; xml[(warp * 16 + g + 8) * 2 + 1] = l_hi;
     }
-    __syncthreads();
+    fa_consumer_sync();
     for (int e = threadIdx.x; e < nrows * D; e += FA_THREADS) {
       const int r = e / D, d = e - r * D;
       float m = -INFINITY;
@@ -361,13 +442,13 @@ flash_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride,
   if (part >= 0 && counters != nullptr && n_splits > 0) {
     const int first = part - split;
     __threadfence();                                // this CTA's part is visible before it is counted
-    __syncthreads();
+    fa_consumer_sync();
     if (threadIdx.x == 0) {
       const int done = atomicAdd(&counters[first * Hkv + hkv], 1);
       s_last = (done == n_splits - 1);
       if (s_last) counters[first * Hkv + hkv] = 0;  // ready for the next launch
     }
-    __syncthreads();
+    fa_consumer_sync();
     if (s_last) {
       __threadfence();
       fa_merge_parts<D>(part_acc, part_ml, part_rows, first, n_splits, hkv, Hkv, nrows, G, Hq, out_row0);
@@ -410,23 +491,23 @@ __global__ void flash_merge_kernel(const int* __restrict__ merge_items, const in
   }
 }
 
-template <int D>
+template <int D, int STAGES, int QROWS>
 static int launch_flash(const void* q, long q_stride, const void* pages, const int* block_tables, int max_blocks,
                         const int* cu_q, const int* ctx_lens, const int* items, int n_items,
                         const int* merge_items, int n_merge, void* out, float* part_acc, float* part_ml,
                         int part_rows, int* counters, float scale, int window, int Hq, int Hkv, int page_size,
                         cudaStream_t stream) {
   constexpr int LD = D + 8;
-  const size_t smem = (size_t)(FA_BM + 4 * FA_BN) * LD * sizeof(__nv_bfloat16);
+  const size_t smem = (size_t)(QROWS + 2 * STAGES * FA_BN) * LD * sizeof(__nv_bfloat16);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(flash_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(flash_attention_kernel<D, STAGES, QROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) QE_REFUSE("flash_attention: shared memory %zu: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
   const float scale_log2 = scale * 1.4426950408889634f;
   dim3 grid(n_items, Hkv);
-  qe_launch(flash_attention_kernel<D>, grid, dim3(FA_THREADS), smem, stream,
+  qe_launch(flash_attention_kernel<D, STAGES, QROWS>, grid, dim3(2 * FA_THREADS), smem, stream,
       (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pages, block_tables, max_blocks, cu_q, ctx_lens, items,
       (__nv_bfloat16*)out, part_acc, part_ml, part_rows, counters, scale_log2, window, Hq, Hkv, page_size);
   QE_CHECK_LAUNCH("flash_attention");
@@ -439,6 +520,14 @@ static int launch_flash(const void* q, long q_stride, const void* pages, const i
   return 0;
 }
 
+// 0 if no bounded wait of the attention kernel's tile pipeline ever ran out (1: a slot never came
+// free, 2: a tile never landed).  Synchronises the device.
+extern "C" int qe_flash_attention_status() {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_fa_status, sizeof(int));
+  return v;
+}
+
 extern "C" int qe_flash_attention_supported(int Hq, int Hkv, int D) {
   return (D % 16 == 0 && D >= 16 && D <= 256 && Hkv >= 1 && Hq % Hkv == 0 && Hq / Hkv <= FA_BM && Hkv <= 65535) ? 1 : 0;
 }
@@ -449,8 +538,8 @@ extern "C" int qe_flash_attention_fused_merge(const void* q, long q_stride, cons
                                               int max_blocks, const int* cu_q, const int* ctx_lens, const int* items,
                                               int n_items, const int* merge_items, int n_merge, void* out,
                                               float* part_acc, float* part_ml, int part_rows, int* counters,
-                                              float scale, int window, int Hq, int Hkv, int D, int page_size,
-                                              cudaStream_t stream);
+                                              int small_tiles, float scale, int window, int Hq, int Hkv, int D,
+                                              int page_size, cudaStream_t stream);
 
 extern "C" int qe_flash_attention(const void* q, long q_stride, const void* pages, const int* block_tables,
                                   int max_blocks, const int* cu_q, const int* ctx_lens, const int* items,
@@ -458,7 +547,7 @@ extern "C" int qe_flash_attention(const void* q, long q_stride, const void* page
                                   float* part_ml, int part_rows, float scale, int window, int Hq, int Hkv, int D,
                                   int page_size, cudaStream_t stream) {
   return qe_flash_attention_fused_merge(q, q_stride, pages, block_tables, max_blocks, cu_q, ctx_lens, items, n_items,
-                                        merge_items, n_merge, out, part_acc, part_ml, part_rows, nullptr, scale,
+                                        merge_items, n_merge, out, part_acc, part_ml, part_rows, nullptr, 0, scale,
                                         window, Hq, Hkv, D, page_size, stream);
 }
 
@@ -466,19 +555,23 @@ extern "C" int qe_flash_attention_fused_merge(const void* q, long q_stride, cons
                                               int max_blocks, const int* cu_q, const int* ctx_lens, const int* items,
                                               int n_items, const int* merge_items, int n_merge, void* out,
                                               float* part_acc, float* part_ml, int part_rows, int* counters,
-                                              float scale, int window, int Hq, int Hkv, int D, int page_size,
-                                              cudaStream_t stream) {
+                                              int small_tiles, float scale, int window, int Hq, int Hkv, int D,
+                                              int page_size, cudaStream_t stream) {
+  // small_tiles: every item has at most 16 rows (a decode step): 16 query rows are staged and the key
+  // tiles run through a deeper pipeline
   if (n_items <= 0) return 0;
   if (!qe_flash_attention_supported(Hq, Hkv, D))
     QE_REFUSE("flash_attention: heads %d/%d with head_dim %d are not supported", Hq, Hkv, D);
   if (((uintptr_t)q | (uintptr_t)pages) & 15 || (q_stride % 8)) QE_REFUSE("flash_attention: operands must be 16-byte aligned");
-#define FA_CASE(DD) case DD: return launch_flash<DD>(q, q_stride, pages, block_tables, max_blocks, cu_q, ctx_lens, items, \
-      n_items, merge_items, n_merge, out, part_acc, part_ml, part_rows, counters, scale, window, Hq, Hkv, page_size, stream);
+#define FA_ARGS q, q_stride, pages, block_tables, max_blocks, cu_q, ctx_lens, items, n_items, merge_items, n_merge, out, \
+      part_acc, part_ml, part_rows, counters, scale, window, Hq, Hkv, page_size, stream
+#define FA_CASE(DD) case DD: return small_tiles ? launch_flash<DD, 3, 16>(FA_ARGS) : launch_flash<DD, 2, FA_BM>(FA_ARGS);
   switch (D) {
     FA_CASE(16) FA_CASE(32) FA_CASE(48) FA_CASE(64) FA_CASE(80) FA_CASE(96) FA_CASE(112) FA_CASE(128)
     FA_CASE(144) FA_CASE(160) FA_CASE(176) FA_CASE(192) FA_CASE(208) FA_CASE(224) FA_CASE(240) FA_CASE(256)
   }
 #undef FA_CASE
+#undef FA_ARGS
   QE_REFUSE("flash_attention: head_dim %d is not supported", D);
 }
 

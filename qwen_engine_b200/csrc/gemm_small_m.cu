@@ -29,11 +29,14 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {   // read once: do
 }
 
 // silu(g) * u for a pair of bfloat16 values, in float32, rounded once (the reference's silumul,
-// src/layers/fused_ops/silumul.py:50-53, without its intermediate rounding of silu)
+// src/layers/fused_ops/silumul.py:50-53, without its intermediate rounding of silu).  The result has
+// 8 bits of mantissa, so the fast exponential and division (errors of a few float32 ulps) are used:
+// every CTA forms the whole activation again, and the exact routines would cost more than the product.
+__device__ __forceinline__ float silu_fast(float g) { return __fdividef(g, 1.f + __expf(-g)); }
 __device__ __forceinline__ uint32_t silu_mul_pair(uint32_t g, uint32_t u) {
   const float2 gf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&g));
   const float2 uf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u));
-  __nv_bfloat162 r = __floats2bfloat162_rn(gf.x / (1.f + expf(-gf.x)) * uf.x, gf.y / (1.f + expf(-gf.y)) * uf.y);
+  __nv_bfloat162 r = __floats2bfloat162_rn(silu_fast(gf.x) * uf.x, silu_fast(gf.y) * uf.y);
   return *reinterpret_cast<uint32_t*>(&r);
 }
 

@@ -23,6 +23,7 @@ SMALL_M_MAX = 64        # rows up to which the weight-streaming product is used
 TCGEN05_ENABLED = True  # the tcgen05 product for more rows (False: the generic kernel serves them)
 FLASH_ROWS = 64         # rows (query token x query head of a group) per work item of the flash kernel
 FLASH_BN = 64           # keys per tile of the flash kernel
+FLASH_ITEM_INTS = 12    # int32 per work item of the flash kernel
 FLASH_SPLIT = 256       # keys per part when a decoded token's context is split (reference attn.py:605)
 FLASH_TARGET_CTAS = 296  # two CTAs per SM: long contexts are split into as many parts as fit in one wave
 
@@ -260,7 +261,8 @@ def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
 
     ``geometries``: the (heads, kv heads, head size, window) of the model's attention layers.
     ``tiles`` serves the generic kernel; for each geometry the flash kernel takes, ``fa<i>_items``
-    and ``fa<i>_merge`` hold its work and merge items and ``fa<i>_info`` = [parts, rows per part].
+    and ``fa<i>_merge`` hold its work and merge items and ``fa<i>_info`` = [parts, rows per part,
+    whether every item has at most 16 rows].
     ``uniform_splits`` (geometry -> number of parts) fixes the number of parts of every request,
     so that the lists depend on the batch's shape only (for steps replayed from a CUDA graph)."""
     tiles: list[int] = []
@@ -277,7 +279,7 @@ def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
         base = sum(-(-n // tpt) for n in q_lens) * Hkv
         items: list[int] = []
         merge: list[int] = []
-        n_parts, part_rows = 0, 1
+        n_parts, part_rows, row0, max_rows = 0, 1, 0, 0
         for r, (n, c) in enumerate(zip(q_lens, ctx_lens)):
             total = c + n
             if uniform_splits is not None:
@@ -289,16 +291,18 @@ def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
                     splits = min(-(-(total - lo) // FLASH_SPLIT), max(1, FLASH_TARGET_CTAS // base))
             if splits > 1:
                 for sp in range(splits):
-                    items += [r, 0, 0, 0, n_parts + sp, splits, sp, 0]
+                    items += [r, 0, 0, 0, n_parts + sp, splits, sp, row0, n, c, 0, 0]
                 merge += [r, 0, n_parts, splits]
                 n_parts += splits
                 part_rows = max(part_rows, n * G)
             else:
                 for q0 in range(0, n, tpt):
-                    items += [r, q0, 0, total, -1, 0, 0, 0]
+                    items += [r, q0, 0, total, -1, 0, 0, row0, n, c, 0, 0]
+            row0 += n
+            max_rows = max(max_rows, min(n, tpt) * G)
         plan[f"fa{gi}_items"] = items
         plan[f"fa{gi}_merge"] = merge
-        plan[f"fa{gi}_info"] = [n_parts, part_rows]
+        plan[f"fa{gi}_info"] = [n_parts, part_rows, int(max_rows <= 16)]
     return plan
 
 
@@ -346,8 +350,8 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
     key = plan.get("geometry_index", {}).get((Hq, Hkv, D, window))
     if key is not None and f"fa{key}_items" in plan:
         items, merge = plan[f"fa{key}_items"], plan[f"fa{key}_merge"]
-        n_parts, part_rows = plan[f"fa{key}_info_host"]
-        n_items, n_merge = items.numel() // 8, merge.numel() // 4
+        n_parts, part_rows, small_tiles = plan[f"fa{key}_info_host"]
+        n_items, n_merge = items.numel() // FLASH_ITEM_INTS, merge.numel() // 4
         part_acc = part_ml = None
         if n_parts:
             part_acc = ctx.arena.alloc((n_parts * Hkv * part_rows, D), torch.float32)
@@ -356,7 +360,7 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
         _check(lib().qe_flash_attention_fused_merge(
             _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(block_tables), int(block_tables.shape[1]),
             _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), _ptr(items), n_items, _ptr(merge), n_merge, _ptr(out),
-            _ptr(part_acc), _ptr(part_ml), int(part_rows), _ptr(counters), ctypes.c_float(scale), int(window),
+            _ptr(part_acc), _ptr(part_ml), int(part_rows), _ptr(counters), int(small_tiles), ctypes.c_float(scale), int(window),
             Hq, Hkv, D, int(kv_pages.shape[3]), _stream()), "flash_attention")
         return
     tiles = plan["tiles"]

@@ -46,7 +46,7 @@ def _plan(Hq, Hkv, D, P, q_lens, ctx_lens):
     plan = ops.plan_attention(list(q_lens), list(ctx_lens), P, ((Hq, Hkv, D, 0),), torch.bfloat16)
     items = torch.tensor(plan["fa0_items"], dtype=torch.int32, device=DEV)
     merge = torch.tensor(plan["fa0_merge"], dtype=torch.int32, device=DEV)
-    n_parts, part_rows = plan["fa0_info"]
+    n_parts, part_rows = plan["fa0_info"][:2]
     return items, merge, n_parts, part_rows
 
 
@@ -61,7 +61,7 @@ def _run(entry, case, plan, Hq, Hkv, D, P, with_scratch):
     lib = ops.lib()
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     common = [_p(case["qkv"]), ctypes.c_long(case["qkv"].stride(0)), _p(case["cache"]), _p(case["table"]),
-              int(case["table"].shape[1]), _p(case["cu_q"]), _p(case["ctx"]), _p(items), items.numel() // 8,
+              int(case["table"].shape[1]), _p(case["cu_q"]), _p(case["ctx"]), _p(items), items.numel() // ops.FLASH_ITEM_INTS,
               _p(merge), merge.numel() // 4, _p(out)]
     tail = [ctypes.c_float(1.0 / math.sqrt(D)), 0, Hq, Hkv, D, P, stream]
     if with_scratch:
