@@ -59,11 +59,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 // One warp's share of a key tile: rows [row_base, row_base + 16) of the query tile against NB blocks
 // of 16 keys starting at block kb0 of the tile.  Updates the rows' running max, sum and output.
+// `all_allowed`: every key of the tile is allowed for every row of the warp (a tile below the causal
+// diagonal, inside the key range and the window): the mask is skipped (uniform over the warp).
 template <int D, int NB>
 __device__ __forceinline__ void fa_tile(const __nv_bfloat16* sq, const __nv_bfloat16* tk, const __nv_bfloat16* tv,
                                         int row_base, int kb0, int kt, int kv_begin, int kv_end, int pos_lo, int pos_hi,
                                         int window, float scale_log2, int lane, float& m_lo, float& m_hi, float& l_lo,
-                                        float& l_hi, float (&o)[D / 8][4]) {
+                                        float& l_hi, float (&o)[D / 8][4], bool all_allowed) {
   constexpr int LD = D + 8, KS = D / 16;
   const int c = lane & 3;
   // ---- S = Q K^T ---------------------------------------------------------------------------
@@ -86,6 +88,18 @@ __device__ __forceinline__ void fa_tile(const __nv_bfloat16* sq, const __nv_bflo
   }
   // ---- mask, online softmax --------------------------------------------------------------------
   float mx_lo = -INFINITY, mx_hi = -INFINITY;
+  if (all_allowed) {
+#pragma unroll
+    for (int i = 0; i < 2 * NB; ++i) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        s[i][e] *= scale_log2;
+        s[i][2 + e] *= scale_log2;
+        mx_lo = fmaxf(mx_lo, s[i][e]);
+        mx_hi = fmaxf(mx_hi, s[i][2 + e]);
+      }
+    }
+  } else
 #pragma unroll
   for (int i = 0; i < 2 * NB; ++i) {
 #pragma unroll
@@ -361,12 +375,17 @@ flash_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride,
       const int kt = kt_first + t * FA_BN;
       const __nv_bfloat16* tk = sk + stage * FA_BN * LD;
       const __nv_bfloat16* tv = sv + stage * FA_BN * LD;
+      // whether the whole tile is allowed for all 16 rows of this warp (then no mask is needed)
+      const int row_first = row_base, row_last = min(row_base + 15, nrows - 1);
+      const int pos_first = first_pos + row_first / G, pos_last = first_pos + row_last / G;
+      const bool all_allowed = row_base + 16 <= nrows && kt >= kv_begin && kt + FA_BN <= kv_end &&
+                               kt + FA_BN - 1 <= pos_first && (window <= 0 || kt > pos_last - window);
       if (keysplit)
         fa_tile<D, 1>(sq, tk, tv, 0, warp, kt, kv_begin, kv_end, pos_lo, pos_hi, window, scale_log2, lane,
-                      m_lo, m_hi, l_lo, l_hi, o);
+                      m_lo, m_hi, l_lo, l_hi, o, false);
       else
         fa_tile<D, FA_BN / 16>(sq, tk, tv, row_base, 0, kt, kv_begin, kv_end, pos_lo, pos_hi, window, scale_log2,
-                               lane, m_lo, m_hi, l_lo, l_hi, o);
+                               lane, m_lo, m_hi, l_lo, l_hi, o, all_allowed);
     }
     __syncwarp();
     if (lane == 0) fa_bar_arrive(&bar_empty[stage]);      // this warp is done with the slot

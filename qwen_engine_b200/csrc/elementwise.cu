@@ -70,10 +70,81 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const T* __restric
   }
 }
 
+// The same for bfloat16 with H % 8 == 0: 8 elements per thread and step (16- and 32-byte accesses).
+__device__ __forceinline__ void bf16x8_to_f32(const uint4& v, float (&f)[8]) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 t = __bfloat1622float2(p[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+__device__ __forceinline__ uint4 f32_to_bf16x8(const float (&f)[8]) {
+  uint4 v;
+  __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return v;
+}
+
+__global__ void add_rmsnorm_bf16x8_kernel(float* __restrict__ resid, const __nv_bfloat16* __restrict__ delta,
+                                          const int* __restrict__ rows, const float* __restrict__ w,
+                                          float eps, __nv_bfloat16* __restrict__ out, int H) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int n = blockIdx.x;
+  const int src_row = rows ? rows[n] : n;
+  float* r = resid + (size_t)src_row * H;
+  const __nv_bfloat16* d = delta ? delta + (size_t)src_row * H : nullptr;
+  __nv_bfloat16* o = out + (size_t)n * H;
+  float ss = 0.f;
+  for (int h = threadIdx.x * 8; h < H; h += blockDim.x * 8) {
+    float x[8];
+    *reinterpret_cast<float4*>(x) = *reinterpret_cast<const float4*>(r + h);
+    *reinterpret_cast<float4*>(x + 4) = *reinterpret_cast<const float4*>(r + h + 4);
+    if (d) {
+      float dv[8];
+      bf16x8_to_f32(*reinterpret_cast<const uint4*>(d + h), dv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] += dv[i];
+      if (!rows) {
+        *reinterpret_cast<float4*>(r + h) = *reinterpret_cast<const float4*>(x);
+        *reinterpret_cast<float4*>(r + h + 4) = *reinterpret_cast<const float4*>(x + 4);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+  }
+  ss = block_sum(ss, scratch);
+  const float rstd = rsqrtf(ss / (float)H + eps);
+  for (int h = threadIdx.x * 8; h < H; h += blockDim.x * 8) {
+    float x[8], wv[8];
+    *reinterpret_cast<float4*>(x) = *reinterpret_cast<const float4*>(r + h);
+    *reinterpret_cast<float4*>(x + 4) = *reinterpret_cast<const float4*>(r + h + 4);
+    if (d && rows) {
+      float dv[8];
+      bf16x8_to_f32(*reinterpret_cast<const uint4*>(d + h), dv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] += dv[i];
+    }
+    *reinterpret_cast<float4*>(wv) = *reinterpret_cast<const float4*>(w + h);
+    *reinterpret_cast<float4*>(wv + 4) = *reinterpret_cast<const float4*>(w + h + 4);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[i] = x[i] * rstd * wv[i];
+    *reinterpret_cast<uint4*>(o + h) = f32_to_bf16x8(x);
+  }
+}
+
 extern "C" int qe_add_rmsnorm(float* resid, const void* delta, const int* rows, const float* w,
                               float eps, void* out, int n_rows, int H, int dtype, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
+  if (dtype == QE_DTYPE_BF16 && H % 8 == 0 &&
+      (((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)out) & 15) == 0) {
+    const int vthreads = H >= 2048 ? 256 : 128;
+    qe_launch(add_rmsnorm_bf16x8_kernel, dim3(n_rows), dim3(vthreads), 0, stream, resid, (const __nv_bfloat16*)delta,
+              rows, w, eps, (__nv_bfloat16*)out, H);
+    QE_CHECK_LAUNCH("add_rmsnorm");
+    return 0;
+  }
   if (dtype == QE_DTYPE_F32)
     qe_launch(add_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, resid, (const float*)delta, rows, w, eps, (float*)out, H);
   else if (dtype == QE_DTYPE_BF16)
@@ -100,9 +171,34 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
   }
 }
 
+__global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
+                                       int I, size_t total8) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int I8 = I / 8;
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total8; e += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = e / I8;
+    const int i = (int)(e - t * I8) * 8;
+    float g[8], u[8];
+    bf16x8_to_f32(*reinterpret_cast<const uint4*>(gate_up + t * 2 * I + i), g);
+    bf16x8_to_f32(*reinterpret_cast<const uint4*>(gate_up + t * 2 * I + I + i), u);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) g[k] = g[k] / (1.f + expf(-g[k])) * u[k];
+    *reinterpret_cast<uint4*>(out + t * I + i) = f32_to_bf16x8(g);
+  }
+}
+
 extern "C" int qe_silu_mul(const void* gate_up, void* out, int T, int I, int dtype, cudaStream_t stream) {
   if (T <= 0) return 0;
   const size_t total = (size_t)T * I;
+  if (dtype == QE_DTYPE_BF16 && I % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
+    const size_t total8 = total / 8;
+    const int vblocks = (int)((total8 + 255) / 256 < 148 * 8 ? (total8 + 255) / 256 : 148 * 8);
+    qe_launch(silu_mul_bf16x8_kernel, dim3(vblocks), dim3(256), 0, stream, (const __nv_bfloat16*)gate_up,
+              (__nv_bfloat16*)out, I, total8);
+    QE_CHECK_LAUNCH("silu_mul");
+    return 0;
+  }
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   if (dtype == QE_DTYPE_F32)
@@ -191,6 +287,75 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ q, T* __restrict__ 
   }
 }
 
+// The common case in bfloat16, head size 128 with all of it rotated (or none): a lane holds 4
+// consecutive elements, its rotation partner (d +- 64) is held by lane +- 16, no shared memory.
+__global__ void qk_norm_rope_kv_write_d128_kernel(__nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ k,
+                                                  const __nv_bfloat16* __restrict__ v, long q_stride, long k_stride,
+                                                  long v_stride, const int* __restrict__ positions,
+                                                  const float* __restrict__ qw, const float* __restrict__ kw, float eps,
+                                                  const float* __restrict__ inv_freq,
+                                                  __nv_bfloat16* __restrict__ pages, const int* __restrict__ slot_mapping,
+                                                  int T_tokens, int Hq, int Hkv, int page_size, int write_kv) {
+  constexpr int D = 128;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads_total = Hq + 2 * Hkv;
+  const long item = (long)blockIdx.x * (blockDim.x >> 5) + warp;
+  if (item >= (long)T_tokens * heads_total) return;
+  const int t = (int)(item / heads_total);
+  const int head = (int)(item % heads_total);
+  if (head >= Hq + Hkv) {           // a value head: copy into the cache
+    if (!write_kv) return;
+    const int h = head - Hq - Hkv;
+    const int slot = slot_mapping[t];
+    const int page = slot / page_size, off = slot % page_size;
+    const uint2 val = *reinterpret_cast<const uint2*>(v + (size_t)t * v_stride + (size_t)h * D + 4 * lane);
+    *reinterpret_cast<uint2*>(pages + ((((size_t)page * 2 + 1) * Hkv + h) * page_size + off) * D + 4 * lane) = val;
+    return;
+  }
+  const bool is_q = head < Hq;
+  const int h = is_q ? head : head - Hq;
+  __nv_bfloat16* x = (is_q ? q + (size_t)t * q_stride : k + (size_t)t * k_stride) + (size_t)h * D + 4 * lane;
+  const float* w = is_q ? qw : kw;
+  const uint2 raw = *reinterpret_cast<const uint2*>(x);
+  float f[4];
+  {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+  }
+  if (w) {
+    const float ss = warp_sum(f[0] * f[0] + f[1] * f[1] + f[2] * f[2] + f[3] * f[3]);
+    const float rstd = rsqrtf(ss / (float)D + eps);
+    const float4 wv = *reinterpret_cast<const float4*>(w + 4 * lane);
+    f[0] = f[0] * rstd * wv.x; f[1] = f[1] * rstd * wv.y; f[2] = f[2] * rstd * wv.z; f[3] = f[3] * rstd * wv.w;
+  }
+  if (inv_freq) {
+    const float pos = (float)positions[t];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float partner = __shfl_xor_sync(0xffffffffu, f[i], 16);
+      const float ang = pos * inv_freq[(4 * lane + i) & 63];
+      float sn, cs;
+      sincosf(ang, &sn, &cs);
+      f[i] = lane < 16 ? cs * f[i] - sn * partner : sn * partner + cs * f[i];
+    }
+  }
+  uint2 res;
+  {
+    __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+    res.x = *reinterpret_cast<uint32_t*>(&a);
+    res.y = *reinterpret_cast<uint32_t*>(&b);
+  }
+  *reinterpret_cast<uint2*>(x) = res;
+  if (!is_q && write_kv) {
+    const int slot = slot_mapping[t];
+    const int page = slot / page_size, off = slot % page_size;
+    *reinterpret_cast<uint2*>(pages + ((((size_t)page * 2 + 0) * Hkv + h) * page_size + off) * D + 4 * lane) = res;
+  }
+}
+
 extern "C" int qe_qk_norm_rope_kv_write(void* q, void* k, const void* v, long q_stride, long k_stride, long v_stride,
                                         const int* positions, const float* qw, const float* kw, float eps,
                                         const float* inv_freq, int rotary_dim, void* pages,
@@ -201,6 +366,17 @@ extern "C" int qe_qk_norm_rope_kv_write(void* q, void* k, const void* v, long q_
   if (inv_freq && (rotary_dim % 2 || rotary_dim > D || rotary_dim <= 0))
     QE_REFUSE("qk_norm_rope_kv_write: rotary_dim %d does not fit head_dim %d", rotary_dim, D);
   if (write_kv && (!pages || !slot_mapping)) QE_REFUSE("qk_norm_rope_kv_write: cache write without cache");
+  if (dtype == QE_DTYPE_BF16 && D == 128 && (!inv_freq || rotary_dim == D) &&
+      ((q_stride | k_stride | v_stride) % 4) == 0 &&
+      (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)pages) & 7) == 0) {
+    const long n_items = (long)T * (Hq + 2 * Hkv);
+    const int vwarps = 8;
+    qe_launch(qk_norm_rope_kv_write_d128_kernel, dim3((unsigned)((n_items + vwarps - 1) / vwarps)), dim3(vwarps * 32), 0,
+              stream, (__nv_bfloat16*)q, (__nv_bfloat16*)k, (const __nv_bfloat16*)v, q_stride, k_stride, v_stride,
+              positions, qw, kw, eps, inv_freq, (__nv_bfloat16*)pages, slot_mapping, T, Hq, Hkv, page_size, write_kv);
+    QE_CHECK_LAUNCH("qk_norm_rope_kv_write");
+    return 0;
+  }
   const int warps = 4;
   const long items = (long)T * (Hq + 2 * Hkv);
   const int blocks = (int)((items + warps - 1) / warps);

@@ -280,6 +280,7 @@ def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
         items: list[int] = []
         merge: list[int] = []
         n_parts, part_rows, row0, max_rows = 0, 1, 0, 0
+        whole: list[tuple[int, list[int]]] = []        # (keys the tile visits, its work item)
         for r, (n, c) in enumerate(zip(q_lens, ctx_lens)):
             total = c + n
             if uniform_splits is not None:
@@ -297,9 +298,12 @@ def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
                 part_rows = max(part_rows, n * G)
             else:
                 for q0 in range(0, n, tpt):
-                    items += [r, q0, 0, total, -1, 0, 0, row0, n, c, 0, 0]
+                    whole.append((c + min(n, q0 + tpt), [r, q0, 0, total, -1, 0, 0, row0, n, c, 0, 0]))
             row0 += n
             max_rows = max(max_rows, min(n, tpt) * G)
+        # tiles that visit many keys start first, so that the last wave of CTAs is made of short ones
+        whole.sort(key=lambda kv: -kv[0])
+        items = [x for _, item in whole for x in item] + items
         plan[f"fa{gi}_items"] = items
         plan[f"fa{gi}_merge"] = merge
         plan[f"fa{gi}_info"] = [n_parts, part_rows, int(max_rows <= 16)]
