@@ -256,7 +256,7 @@ flash_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride,
   __nv_bfloat16* sq = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [QROWS][LD]
   __nv_bfloat16* sk = sq + QROWS * LD;                                     // [STAGES][64][LD]
   __nv_bfloat16* sv = sk + STAGES * FA_BN * LD;                            // [STAGES][64][LD]
-  __shared__ uint64_t bar_full[STAGES], bar_empty[STAGES];
+  __shared__ uint64_t bar_full[STAGES], bar_empty[STAGES], bar_q;
   __shared__ int s_last, s_abort;
 
   // the work lists come from the host's copy, not from a kernel
@@ -293,13 +293,16 @@ flash_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride,
       fa_bar_init(&bar_full[st], 2 * FA_THREADS);   // each fetching thread: once for its copies, once for its stores
       fa_bar_init(&bar_empty[st], FA_WARPS);        // one arrival per computing warp
     }
+    fa_bar_init(&bar_q, 2 * FA_THREADS);
     s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   __syncthreads();
-  pdl_wait();            // q and the newest keys and values are the previous kernel's output
   if (QROWS < FA_BM && nrows > QROWS) return;       // the launcher promised small tiles (never taken)
   volatile int* abort_flag = &s_abort;
+  // The previous kernel of the step wrote q and the keys and values of the new tokens (positions
+  // from ctx on).  Key tiles that end before ctx hold only what earlier steps wrote: the fetching
+  // warps start on them at once and wait for the previous kernel only before they touch the rest.
 
   if (warp >= FA_WARPS) {
     // ================= fetching warps ==================================================================
@@ -310,22 +313,32 @@ flash_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride,
     const size_t page_stride = (size_t)2 * Hkv * page_size * D;
     const size_t v_off = (size_t)Hkv * page_size * D;
     const __nv_bfloat16* head_base = pages + (size_t)hkv * page_size * D;
-    if (n_tiles > 0) {                              // the query rows travel with the first tile
-      for (int e = ptid; e < QROWS * CH; e += FA_THREADS) {
-        const int r = e / CH, ch = e - r * CH;
-        __nv_bfloat16* dst = sq + r * LD + ch * 8;
-        if (r < nrows) {
-          const int ti = r / G, hg = r - ti * G;
-          cp_async16(dst, q + (size_t)(row0 + q0 + ti) * q_stride + (size_t)(hkv * G + hg) * D + ch * 8);
-        } else {
-          *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    bool waited = false;
+    auto wait_and_fetch_q = [&]() {
+      pdl_wait();
+      waited = true;
+      if (n_tiles > 0) {
+        for (int e = ptid; e < QROWS * CH; e += FA_THREADS) {
+          const int r = e / CH, ch = e - r * CH;
+          __nv_bfloat16* dst = sq + r * LD + ch * 8;
+          if (r < nrows) {
+            const int ti = r / G, hg = r - ti * G;
+            cp_async16(dst, q + (size_t)(row0 + q0 + ti) * q_stride + (size_t)(hkv * G + hg) * D + ch * 8);
+          } else {
+            *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+          }
         }
+        fa_bar_arrive_on_copies(&bar_q);
+        fa_bar_arrive(&bar_q);
       }
-    }
+    };
     for (int t = 0; t < n_tiles; ++t) {
       const int stage = t % STAGES;
-      if (t >= STAGES && !fa_bar_wait(&bar_empty[stage], ((t / STAGES) - 1) & 1, abort_flag, 1)) break;
       const int kt = kt_first + t * FA_BN;
+      // the query rows are fetched as soon as the head of the pipeline is on its way, or before the
+      // first tile that may hold a new token's keys
+      if (!waited && (t >= STAGES - 1 || kt + FA_BN > ctx)) wait_and_fetch_q();
+      if (t >= STAGES && !fa_bar_wait(&bar_empty[stage], ((t / STAGES) - 1) & 1, abort_flag, 1)) break;
       __nv_bfloat16* dk = sk + stage * FA_BN * LD;
       __nv_bfloat16* dv = sv + stage * FA_BN * LD;
 #pragma unroll 4
@@ -348,6 +361,7 @@ flash_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride,
       fa_bar_arrive_on_copies(&bar_full[stage]);    // when this thread's copies have landed
       fa_bar_arrive(&bar_full[stage]);              // and its zero stores are released
     }
+    if (!waited) wait_and_fetch_q();
     cp_async_commit();
     cp_async_wait<0>();                             // nothing of this thread's is in flight when it leaves
     return;
@@ -366,8 +380,9 @@ flash_attention_kernel(const __nv_bfloat16* __restrict__ q, long q_stride,
   for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
 
   const bool warp_active = keysplit || warp * 16 < nrows;       // a warp without rows only hands slots back
-  bool ok = true;
-  for (int t = 0; t < n_tiles; ++t) {
+  pdl_wait();
+  bool ok = n_tiles == 0 || __all_sync(0xffffffffu, fa_bar_wait(&bar_q, 0, abort_flag, 3));
+  for (int t = 0; ok && t < n_tiles; ++t) {
     const int stage = t % STAGES;
     ok = __all_sync(0xffffffffu, fa_bar_wait(&bar_full[stage], (t / STAGES) & 1, abort_flag, 2));
     if (!ok) break;
