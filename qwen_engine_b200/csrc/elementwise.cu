@@ -10,7 +10,8 @@
 // ---------------------------------------------------------------------------------------
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                                 float* __restrict__ out, int H, int V) {
+                                 float* __restrict__ out, int H, int V, float* __restrict__ ssq_out, int ssq_ld) {
+  __shared__ float scratch[33];
   const int t = blockIdx.x;
   const int id = ids[t];                           // written by the host's copy, not by a kernel
   pdl_launch_dependents();
@@ -21,16 +22,21 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
     return;
   }
   const T* src = table + (size_t)id * H;
-  for (int h = threadIdx.x; h < H; h += blockDim.x) dst[h] = to_f32(src[h]);
+  float ss = 0.f;
+  for (int h = threadIdx.x; h < H; h += blockDim.x) { const float v = to_f32(src[h]); dst[h] = v; ss += v * v; }
+  if (ssq_out) {                                   // the row's sum of squares, for a norm fused downstream
+    ss = block_sum(ss, scratch);
+    if (threadIdx.x == 0) ssq_out[(size_t)t * ssq_ld] = ss;
+  }
 }
 
 extern "C" int qe_embedding(const int* ids, const void* table, float* out, int T, int H, int V,
-                            int dtype, cudaStream_t stream) {
+                            int dtype, float* ssq_out, int ssq_ld, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (dtype == QE_DTYPE_F32)
-    qe_launch(embedding_kernel<float>, dim3(T), dim3(256), 0, stream, ids, (const float*)table, out, H, V);
+    qe_launch(embedding_kernel<float>, dim3(T), dim3(256), 0, stream, ids, (const float*)table, out, H, V, ssq_out, ssq_ld);
   else if (dtype == QE_DTYPE_BF16)
-    qe_launch(embedding_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, ids, (const __nv_bfloat16*)table, out, H, V);
+    qe_launch(embedding_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, ids, (const __nv_bfloat16*)table, out, H, V, ssq_out, ssq_ld);
   else QE_REFUSE("embedding: unknown dtype %d", dtype);
   QE_CHECK_LAUNCH("embedding");
   return 0;

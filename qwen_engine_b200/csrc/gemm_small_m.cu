@@ -40,13 +40,38 @@ __device__ __forceinline__ uint32_t silu_mul_pair(uint32_t g, uint32_t u) {
   return *reinterpret_cast<uint32_t*>(&r);
 }
 
-// SILU: the token operand is not x[M, K] but gate_up[M, 2K]: x[m, k] = silu(gate_up[m, k]) * gate_up[m, K + k]
-// is formed while loading (the feed-forward's activation fused into its output projection).
-template <int MT, typename TOut, bool SILU>
+// What the token operand is made of (formed while loading, so that no kernel and no buffer stands
+// between the producer of the data and the product):
+//   PLAIN  x[M, K] as it is;
+//   SILU   x[m, k] = silu(gate_up[m, k]) * gate_up[m, K + k] from gate_up[M, 2K] (the feed-forward's
+//          activation fused into its output projection);
+//   NORM   x[m, k] = resid[m, k] * rstd[m] * norm_w[k] with rstd[m] = rsqrt(sum_k resid[m, k]^2 / K + eps):
+//          the RMS norm of the float32 residual stream fused into the projection that follows it.  The
+//          row's sum of squares comes in n_ssq partial sums that the kernel that last wrote the stream
+//          left behind (see RESID), so no pass over the row is needed here.
+// And what happens to the result:
+//   RESID  the product is a branch's output: it is added into the float32 residual stream in place
+//          (each element belongs to one thread), and the CTA leaves the sum of squares of its 16
+//          columns of every row in ssq_out[m, blockIdx.x] for the norm that follows.
+enum { X_PLAIN = 0, X_SILU = 1, X_NORM = 2 };
+
+struct FuseArgs {
+  const float* resid;               // NORM: [M, K] float32
+  const float* ssq;                 // NORM: [M, ssq_ld] partial sums of squares of the rows
+  const float* norm_w;              // NORM: [K]
+  float* ssq_out;                   // RESID: [M, ssq_ld]
+  int n_ssq, ssq_ld;
+  float eps;
+};
+
+template <int MT, typename TOut, int XMODE, bool RESID>
 __global__ void __launch_bounds__(512)
 gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
-                    TOut* __restrict__ out, int M, int N, int K, int k_per_warp) {
+                    TOut* __restrict__ out, int M, int N, int K, int k_per_warp, FuseArgs na) {
+  constexpr bool SILU = XMODE == X_SILU;
+  constexpr bool NORM = XMODE == X_NORM;
   extern __shared__ float red[];                    // [warps][16][8 MT]
+  __shared__ float s_rstd[8 * MT];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const int g = lane >> 2, c = lane & 3;
   const int n0 = blockIdx.x * 16;
@@ -76,6 +101,20 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
   };
   auto load_x = [&](int m, int k) {
     if (m >= M || k >= kend) return zero;
+    if (NORM) {
+      const size_t o = (size_t)m * K + k;
+      float f[8], wv[8];
+      *reinterpret_cast<float4*>(f) = __ldcg(reinterpret_cast<const float4*>(na.resid + o));
+      *reinterpret_cast<float4*>(f + 4) = __ldcg(reinterpret_cast<const float4*>(na.resid + o + 4));
+      *reinterpret_cast<float4*>(wv) = __ldg(reinterpret_cast<const float4*>(na.norm_w + k));
+      *reinterpret_cast<float4*>(wv + 4) = __ldg(reinterpret_cast<const float4*>(na.norm_w + k + 4));
+      const float rs = s_rstd[m];
+      uint4 v;
+      __nv_bfloat162* vp = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) vp[i] = __floats2bfloat162_rn(f[2 * i] * rs * wv[2 * i], f[2 * i + 1] * rs * wv[2 * i + 1]);
+      return v;
+    }
     const __nv_bfloat16* p = x + (size_t)m * x_ld + k;
     uint4 v = __ldg(reinterpret_cast<const uint4*>(p));
     if (SILU) {
@@ -102,6 +141,23 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
   Chunk c0 = load_chunk(kbeg), c1 = load_chunk(kbeg + 64);
   pdl_launch_dependents();
   pdl_wait();
+  float resid_old = 0.f;                            // RESID: this thread's element of the stream, fetched early
+  if (RESID) {
+    const int m = threadIdx.x >> 4, n = n0 + (threadIdx.x & 15);
+    if (threadIdx.x < 16 * 8 * MT && m < M && n < N) resid_old = __ldcg(reinterpret_cast<const float*>(out) + (size_t)m * N + n);
+  }
+  if (NORM) {
+    // the row norms from the partial sums of squares: a warp per row, all loads at once, summed in a
+    // fixed order (lane l adds parts l, l + 32, ...; then the lanes are added in a tree)
+    for (int m = warp; m < M; m += nwarps) {
+      const float* p = na.ssq + (size_t)m * na.ssq_ld;
+      float ss = 0.f;
+      for (int i = lane; i < na.n_ssq; i += 32) ss += __ldcg(p + i);
+      ss = warp_sum(ss);
+      if (lane == 0) s_rstd[m] = rsqrtf(ss / (float)K + na.eps);
+    }
+    __syncthreads();
+  }
   for (int k0 = kbeg; k0 < kend; k0 += 128) {
     const Chunk n0c = load_chunk(k0 + 128);
     compute(c0, k0);
@@ -124,16 +180,34 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
   for (int e = threadIdx.x; e < 16 * MW; e += blockDim.x) {
     const int m = e >> 4, i = e & 15;               // consecutive threads: consecutive weight rows
     const int n = n0 + i;
-    if (m >= M || n >= N) continue;
-    float s = 0.f;
-    for (int wi = 0; wi < nwarps; ++wi) s += red[((size_t)wi * 16 + i) * MW + m];
-    out[(size_t)m * N + n] = from_f32<TOut>(s);
+    if (!RESID) {
+      if (m >= M || n >= N) continue;
+      float s = 0.f;
+      for (int wi = 0; wi < nwarps; ++wi) s += red[((size_t)wi * 16 + i) * MW + m];
+      out[(size_t)m * N + n] = from_f32<TOut>(s);
+    } else {
+      // whole warps run this loop (16 MW is a multiple of 32); lanes outside the matrix add zero
+      float v = 0.f;
+      if (m < M && n < N) {
+        float s = 0.f;
+        for (int wi = 0; wi < nwarps; ++wi) s += red[((size_t)wi * 16 + i) * MW + m];
+        float* dst = reinterpret_cast<float*>(out) + (size_t)m * N + n;
+        v = (e == threadIdx.x ? resid_old : *dst) + s;
+        *dst = v;
+      }
+      float sq = v * v;                              // over the 16 columns of the row: lanes i = 0..15
+      sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+      if (i == 0 && m < M) na.ssq_out[(size_t)m * na.ssq_ld + blockIdx.x] = sq;
+    }
   }
 }
 
-template <int MT, bool SILU>
+template <int MT, int XMODE, bool RESID>
 static int launch_small_m(const void* x, const void* w, void* out, int M, int N, int K, int out_f32,
-                          cudaStream_t stream) {
+                          cudaStream_t stream, FuseArgs na) {
   // warps split K in slices that are multiples of 64; more warps when there are few CTAs
   const int ctas = (N + 15) / 16;
   int warps = ctas >= 2048 ? 4 : (ctas >= 256 ? 8 : 16);
@@ -143,43 +217,68 @@ static int launch_small_m(const void* x, const void* w, void* out, int M, int N,
   static bool configured = false;             // once, not per launch: launches may be under stream capture
   if (!configured) {
     const int max_smem = 16 * 16 * 8 * MT * (int)sizeof(float);
-    cudaFuncSetAttribute(gemm_small_m_kernel<MT, float, SILU>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-    cudaFuncSetAttribute(gemm_small_m_kernel<MT, __nv_bfloat16, SILU>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    cudaFuncSetAttribute(gemm_small_m_kernel<MT, float, XMODE, RESID>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (!RESID)
+      cudaFuncSetAttribute(gemm_small_m_kernel<MT, __nv_bfloat16, XMODE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
     configured = true;
   }
-  if (out_f32) {
-    qe_launch(gemm_small_m_kernel<MT, float, SILU>, dim3(ctas), dim3(warps * 32), smem, stream,
-              (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (float*)out, M, N, K, k_per_warp);
+  if (out_f32 || RESID) {
+    qe_launch(gemm_small_m_kernel<MT, float, XMODE, RESID>, dim3(ctas), dim3(warps * 32), smem, stream,
+              (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (float*)out, M, N, K, k_per_warp, na);
   } else {
-    qe_launch(gemm_small_m_kernel<MT, __nv_bfloat16, SILU>, dim3(ctas), dim3(warps * 32), smem, stream,
-              (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, N, K, k_per_warp);
+    qe_launch(gemm_small_m_kernel<MT, __nv_bfloat16, XMODE, false>, dim3(ctas), dim3(warps * 32), smem, stream,
+              (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, N, K, k_per_warp, na);
   }
   QE_CHECK_LAUNCH("linear_small_m");
   return 0;
 }
 
-template <bool SILU>
+template <int XMODE, bool RESID>
 static int dispatch_small_m(const void* x, const void* w, void* out, int M, int N, int K, int out_f32,
-                            cudaStream_t stream) {
+                            cudaStream_t stream, FuseArgs na = FuseArgs{}) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 64) QE_REFUSE("linear_small_m: M = %d is above 64", M);
   if (K <= 0 || K % 8) QE_REFUSE("linear_small_m: K = %d is not a positive multiple of 8", K);
   if (((uintptr_t)x | (uintptr_t)w) & 15) QE_REFUSE("linear_small_m: operands must be 16-byte aligned");
-  if (M <= 8) return launch_small_m<1, SILU>(x, w, out, M, N, K, out_f32, stream);
-  if (M <= 16) return launch_small_m<2, SILU>(x, w, out, M, N, K, out_f32, stream);
-  if (M <= 32) return launch_small_m<4, SILU>(x, w, out, M, N, K, out_f32, stream);
-  return launch_small_m<8, SILU>(x, w, out, M, N, K, out_f32, stream);
+  if (M <= 8) return launch_small_m<1, XMODE, RESID>(x, w, out, M, N, K, out_f32, stream, na);
+  if (M <= 16) return launch_small_m<2, XMODE, RESID>(x, w, out, M, N, K, out_f32, stream, na);
+  if (M <= 32) return launch_small_m<4, XMODE, RESID>(x, w, out, M, N, K, out_f32, stream, na);
+  return launch_small_m<8, XMODE, RESID>(x, w, out, M, N, K, out_f32, stream, na);
 }
 
 // Returns 0 when run, 1 when refused (qe_last_error says why), 2 on a launch error.
 extern "C" int qe_linear_small_m(const void* x, const void* w, void* out, int M, int N, int K,
                                  int out_f32, cudaStream_t stream) {
-  return dispatch_small_m<false>(x, w, out, M, N, K, out_f32, stream);
+  return dispatch_small_m<X_PLAIN, false>(x, w, out, M, N, K, out_f32, stream);
 }
 
 // out[M, N] = (silu(gate_up[:, :K]) * gate_up[:, K:]) · w[N, K]^T: the activation of the feed-forward
 // formed while its output projection loads it.
 extern "C" int qe_linear_small_m_silu(const void* gate_up, const void* w, void* out, int M, int N, int K,
                                       int out_f32, cudaStream_t stream) {
-  return dispatch_small_m<true>(gate_up, w, out, M, N, K, out_f32, stream);
+  return dispatch_small_m<X_SILU, false>(gate_up, w, out, M, N, K, out_f32, stream);
+}
+
+// resid[M, N] += x · w^T (silu: x formed from gate_up as above), float32 in place, and
+// ssq_out[m, j] = sum of squares of resid[m, 16 j .. 16 j + 15] for j < ceil(N / 16).
+extern "C" int qe_linear_small_m_resid(const void* x, const void* w, float* resid, float* ssq_out, int ssq_ld,
+                                       int M, int N, int K, int silu, cudaStream_t stream) {
+  if (!ssq_out || ssq_ld < (N + 15) / 16) QE_REFUSE("linear_small_m_resid: ssq_out must hold %d columns", (N + 15) / 16);
+  FuseArgs na{};
+  na.ssq_out = ssq_out;
+  na.ssq_ld = ssq_ld;
+  return silu ? dispatch_small_m<X_SILU, true>(x, w, resid, M, N, K, 1, stream, na)
+              : dispatch_small_m<X_PLAIN, true>(x, w, resid, M, N, K, 1, stream, na);
+}
+
+// out[M, N] = rmsnorm(resid; norm_w, eps) · w[N, K]^T with the rows' sums of squares given as n_ssq
+// partial sums per row in ssq[M, ssq_ld].
+extern "C" int qe_linear_small_m_norm(const float* resid, const float* ssq, int n_ssq, int ssq_ld, const float* norm_w,
+                                      float eps, const void* w, void* out, int M, int N, int K, int out_f32,
+                                      cudaStream_t stream) {
+  if (((uintptr_t)resid | (uintptr_t)norm_w) & 15) QE_REFUSE("linear_small_m_norm: operands must be 16-byte aligned");
+  if (!ssq || n_ssq < 1 || n_ssq > ssq_ld) QE_REFUSE("linear_small_m_norm: bad partial sums (%d of %d)", n_ssq, ssq_ld);
+  FuseArgs na{};
+  na.resid = resid; na.ssq = ssq; na.norm_w = norm_w; na.n_ssq = n_ssq; na.ssq_ld = ssq_ld; na.eps = eps;
+  return dispatch_small_m<X_NORM, false>(w, w, out, M, N, K, out_f32, stream, na);
 }

@@ -147,22 +147,26 @@ class DecoderModel:
         [num_logit_rows, vocab] (None when no logits are wanted)."""
         lo = self.layout
         T, H = ctx.num_tokens, lo.hidden_size
-        resid = ctx.arena.alloc((T, H), torch.float32)
-        delta = ctx.arena.alloc((T, H), ctx.dtype)
-        ops.embedding(ctx.token_ids, self.embed, resid)
-        has_delta = False
+        # a few rows in bfloat16: kernels that write the stream leave its rows' sums of squares behind,
+        # ceil(H / 16) partial sums a row, for the norms fused into the products that follow
+        ssq = None
+        if ctx.dtype == torch.bfloat16 and T <= ops.SMALL_M_MAX:
+            ssq = ctx.arena.alloc((T, -(-(-(-H // 16)) // 4) * 4), torch.float32)
+        stream = ops.ResidualStream(ctx.arena.alloc((T, H), torch.float32), ctx.arena.alloc((T, H), ctx.dtype), ssq)
+        ops.embedding(ctx.token_ids, self.embed, stream.resid, ssq)
+        stream.n_ssq = 1 if ssq is not None else 0
         for entry in lo.plan:
             view, group = None, None
             if entry.cache_slot is not None:
                 view = cache.layer_view(entry.cache_slot)
                 group = cache.group_of_slot[entry.cache_slot][0]
-            has_delta = self.blocks[entry.layer].forward(ctx, resid, delta, has_delta, view, group,
-                                                         entry.write_cache)
+            self.blocks[entry.layer].forward(ctx, stream, view, group, entry.write_cache)
         if ctx.num_logit_rows == 0:
             return None
         N = ctx.num_logit_rows
         normed = ctx.arena.alloc((N, H), ctx.dtype)
-        self.final_norm.add_norm_rows(ctx, resid, delta if has_delta else None, ctx.logit_rows, normed)
+        self.final_norm.add_norm_rows(ctx, stream.resid, stream.delta if stream.has_delta else None,
+                                      ctx.logit_rows, normed)
         logits = ctx.arena.alloc((N, lo.vocab_size), torch.float32)
         ops.linear(normed, self.head, logits)
         return logits

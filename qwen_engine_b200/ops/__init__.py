@@ -104,13 +104,19 @@ def prepare_matrix(w: torch.Tensor) -> torch.Tensor:
     return w.contiguous()
 
 
-def embedding(token_ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t] = float32(table[token_ids[t]]); out is the float32 residual stream [T, H]."""
+def embedding(token_ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
+              ssq: Optional[torch.Tensor] = None) -> None:
+    """out[t] = float32(table[token_ids[t]]); out is the float32 residual stream [T, H].  With ``ssq``
+    [T, P] float32, ssq[t, 0] gets the row's sum of squares (one partial sum per row)."""
     _i32(token_ids, "token_ids")
     T, (V, H) = token_ids.numel(), table.shape
     _need(out.dtype == torch.float32 and out.shape == (T, H) and out.is_contiguous(), "embedding: out must be float32 [T, H]")
     _need(table.is_contiguous(), "embedding: table must be contiguous")
-    _check(lib().qe_embedding(_ptr(token_ids), _ptr(table), _ptr(out), T, H, V, _dt(table), _stream()), "embedding")
+    if ssq is not None:
+        _need(ssq.dtype == torch.float32 and ssq.dim() == 2 and ssq.shape[0] == T and ssq.is_contiguous(),
+              "embedding: ssq must be float32 [T, P]")
+    _check(lib().qe_embedding(_ptr(token_ids), _ptr(table), _ptr(out), T, H, V, _dt(table), _ptr(ssq),
+                              int(ssq.shape[1]) if ssq is not None else 0, _stream()), "embedding")
 
 
 def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
@@ -144,8 +150,111 @@ def add_rmsnorm_rows(resid: torch.Tensor, delta: Optional[torch.Tensor], rows: t
                                 _ptr(out), N, H, _dt(out), _stream()), "add_rmsnorm_rows")
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    """out[M, N] = x[M, K] · w[N, K]^T, float32 accumulation; out in x's dtype or float32."""
+class ResidualStream:
+    """The float32 residual stream of a step, with the output of the last branch still to be added.
+
+    ``resid`` [T, H] float32 is the stream.  A branch (mixer or feed-forward) either adds its output
+    into it at once (``ResidualSink``), or leaves it in ``delta`` [T, H] (compute dtype) with
+    ``has_delta`` set, to be added by the next norm.  ``ssq`` [T, P] float32 holds ``n_ssq`` partial
+    sums of squares of every row of ``resid`` when the kernel that last wrote the stream left them
+    (``n_ssq`` = 0: unknown); a norm fused into the next product starts from them."""
+
+    def __init__(self, resid: torch.Tensor, delta: torch.Tensor, ssq: Optional[torch.Tensor] = None):
+        self.resid, self.delta, self.ssq = resid, delta, ssq
+        self.has_delta = False
+        self.n_ssq = 0
+
+
+class ResidualSink:
+    """Given to ``linear`` / ``linear_silu_mul`` as ``out``: the product is a branch's output and is to be
+    added to the residual stream.  For a few rows in bfloat16 the add happens in the product's epilogue
+    (which also leaves the rows' sums of squares for the next norm); otherwise the product goes to
+    ``stream.delta`` and the next norm adds it."""
+
+    def __init__(self, stream: ResidualStream):
+        self.stream = stream
+
+    def as_delta(self) -> torch.Tensor:
+        st = self.stream
+        st.has_delta, st.n_ssq = True, 0
+        return st.delta
+
+
+class NormedInput:
+    """``rmsnorm(stream.resid + stream.delta) * weight`` that is not computed yet.
+
+    ``linear`` takes it in the place of a tensor: for a few rows in bfloat16, when the stream is up to
+    date and its sums of squares are known, the norm runs inside the product kernel (no kernel and no
+    buffer between them); otherwise, and for any other consumer, ``materialize`` runs the add-and-norm
+    kernel once and returns the tensor."""
+
+    def __init__(self, stream: ResidualStream, weight: torch.Tensor, eps: float, alloc, dtype: torch.dtype):
+        self.stream, self.weight, self.eps, self.alloc, self.dtype = stream, weight, float(eps), alloc, dtype
+        self._tensor: Optional[torch.Tensor] = None
+
+    @property
+    def shape(self):
+        return self.stream.resid.shape
+
+    def materialize(self) -> torch.Tensor:
+        if self._tensor is None:
+            st = self.stream
+            out = self.alloc(tuple(st.resid.shape), self.dtype)
+            add_rmsnorm(st.resid, st.delta if st.has_delta else None, self.weight, self.eps, out)
+            if st.has_delta:
+                st.has_delta, st.n_ssq = False, 0
+            self._tensor = out
+        return self._tensor
+
+
+FUSED_NORM_MAX_M = 16   # rows up to which a norm is fused into the product that follows
+
+
+def _linear_normed(x: NormedInput, w: torch.Tensor, out: torch.Tensor) -> bool:
+    """The fused route of ``linear`` for a NormedInput; False if it does not apply."""
+    st = x.stream
+    M, K = st.resid.shape
+    N = w.shape[0]
+    if not (x._tensor is None and not st.has_delta and st.n_ssq > 0 and st.ssq is not None
+            and w.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and M <= FUSED_NORM_MAX_M
+            and K % 8 == 0 and st.resid.is_cuda and isinstance(out, torch.Tensor)):
+        return False
+    _need(w.shape == (N, K) and out.shape == (M, N) and out.dtype in (torch.bfloat16, torch.float32)
+          and w.is_contiguous() and out.is_contiguous(), "linear: operands do not fit the normed input")
+    _check(lib().qe_linear_small_m_norm(_ptr(st.resid), _ptr(st.ssq), int(st.n_ssq), int(st.ssq.shape[1]),
+                                        _ptr(x.weight), ctypes.c_float(x.eps), _ptr(w), _ptr(out), M, N, K,
+                                        int(out.dtype == torch.float32), _stream()), "linear")
+    return True
+
+
+def _linear_into_stream(x: torch.Tensor, w: torch.Tensor, sink: ResidualSink, silu: bool) -> bool:
+    """The fused route for a ResidualSink: resid += product, sums of squares left behind."""
+    st = sink.stream
+    M = x.shape[0]
+    K = x.shape[1] // 2 if silu else x.shape[1]
+    N = w.shape[0]
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M <= SMALL_M_MAX and K % 8 == 0
+            and not st.has_delta and st.ssq is not None and st.ssq.shape[1] >= -(-N // 16)
+            and st.resid.shape == (M, N)):
+        return False
+    _need(w.shape == (N, K) and x.is_contiguous() and w.is_contiguous(), "linear: operands do not fit")
+    _check(lib().qe_linear_small_m_resid(_ptr(x), _ptr(w), _ptr(st.resid), _ptr(st.ssq), int(st.ssq.shape[1]),
+                                         M, N, K, int(silu), _stream()), "linear")
+    st.n_ssq = -(-N // 16)
+    return True
+
+
+def linear(x, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, N] = x[M, K] · w[N, K]^T, float32 accumulation; out in x's dtype or float32.
+    ``x`` may be a NormedInput (see there)."""
+    if isinstance(x, NormedInput):
+        if _linear_normed(x, w, out):
+            return
+        x = x.materialize()
+    if isinstance(out, ResidualSink):
+        if _linear_into_stream(x, w, out, silu=False):
+            return
+        out = out.as_delta()
     M, K = x.shape
     N = w.shape[0]
     _need(w.shape == (N, K) and w.dtype == x.dtype, f"linear: w {tuple(w.shape)} {w.dtype} does not fit x {tuple(x.shape)} {x.dtype}")
@@ -167,6 +276,10 @@ def linear_silu_mul(gate_up: torch.Tensor, w: torch.Tensor, out: torch.Tensor, s
     """out[M, N] = (silu(gate_up[:, :I]) * gate_up[:, I:]) · w[N, I]^T.  For a few rows in bfloat16 the
     activation is formed while the product loads it; otherwise ``silu_mul`` runs first into a buffer
     that ``scratch(shape, dtype)`` provides."""
+    if isinstance(out, ResidualSink):
+        if _linear_into_stream(gate_up, w, out, silu=True):
+            return
+        out = out.as_delta()
     M, I2 = gate_up.shape
     I = I2 // 2
     N = w.shape[0]

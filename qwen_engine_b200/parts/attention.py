@@ -23,6 +23,8 @@ from .rope import NeoxRope
 
 @register("mixer", "gqa_attention")
 class GQAAttention(Mixer):
+    takes_lazy_input = True       # x goes to one product only
+    writes_through_linear = True  # out is the out of the last product
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  scale: float, qk_norm_eps: Optional[float] = None,
                  position_encoding: Optional[PartSpec] = None, window: Optional[int] = None):

@@ -150,6 +150,12 @@ class Part:
 class Norm(Part):
     width: int
 
+    def normed(self, ctx: "StepContext", stream, lazy: bool = False):
+        """The normed rows of ``stream`` (an ``ops.ResidualStream``) after its pending branch output
+        is added.  With ``lazy`` the result may be an ``ops.NormedInput`` that ``ops.linear`` fuses
+        into the product; a consumer that needs a tensor calls its ``materialize()``."""
+        raise NotImplementedError
+
     def add_norm(self, ctx: StepContext, resid: torch.Tensor, delta: Optional[torch.Tensor],
                  out: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
@@ -169,6 +175,12 @@ class Mixer(Part):
     # False for a mixer whose forward reads device data on the host or allocates: steps of a model
     # that holds such a mixer are never captured in a CUDA graph.
     capturable = True
+    # True if forward passes its input x only to ops.linear (which also takes an ops.NormedInput);
+    # a mixer that looks at x itself keeps False and always gets a tensor.
+    takes_lazy_input = False
+    # True if forward writes ``out`` only as the ``out`` of ops.linear / ops.linear_silu_mul (which
+    # also take an ops.ResidualSink and then add into the residual stream at once).
+    writes_through_linear = False
 
     def cache_spec(self) -> Optional[CacheSpec]:
         return None
@@ -184,6 +196,9 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    takes_lazy_input = False      # as for Mixer
+    writes_through_linear = False
+
     def forward(self, ctx: StepContext, x: torch.Tensor, out: torch.Tensor) -> None:
         raise NotImplementedError
 
@@ -191,14 +206,11 @@ class FeedForward(Part):
 class Block(Part):
     mixer: Mixer
 
-    def forward(self, ctx: StepContext, resid: torch.Tensor, delta: torch.Tensor, has_delta: bool,
-                cache: Optional[torch.Tensor], group: Optional[int], write_cache: bool) -> bool:
-        """Run the layer on the residual stream ``resid`` (float32, in place).
-
-        ``delta`` is a buffer for a branch's output that is not yet added to the
-        stream; ``has_delta`` says whether it holds one on entry.  Returns
-        whether it holds one on exit, so that the add can be fused into the
-        next norm."""
+    def forward(self, ctx: StepContext, stream, cache: Optional[torch.Tensor], group: Optional[int],
+                write_cache: bool) -> None:
+        """Run the layer on the residual stream (an ``ops.ResidualStream``: the float32 stream, and
+        the last branch's output that is not yet added to it, so that the add is fused into the next
+        norm).  Branches write their output to ``stream.delta`` and set ``stream.has_delta``."""
         raise NotImplementedError
 
 

@@ -3,6 +3,7 @@
 next norm as a pending delta so that one kernel adds and norms."""
 from __future__ import annotations
 
+from .. import ops
 from .base import Block, PartSpec, StepContext, register
 
 
@@ -28,12 +29,25 @@ class PreNormBlock(Block):
         for part, p in self._parts():
             part.load(prefix + p, source, dtype, device)
 
-    def forward(self, ctx: StepContext, resid, delta, has_delta, cache, group, write_cache) -> bool:
+    def forward(self, ctx: StepContext, stream, cache, group, write_cache) -> None:
         mark = ctx.arena.mark()
-        h = ctx.arena.alloc((ctx.num_tokens, self.hidden_size), ctx.dtype)
-        self.norm1.add_norm(ctx, resid, delta if has_delta else None, h)
-        self.mixer.forward(ctx, h, cache, group, delta, write_cache)
-        self.norm2.add_norm(ctx, resid, delta, h)
-        self.ffn.forward(ctx, h, delta)
+        h = self.norm1.normed(ctx, stream, lazy=self.mixer.takes_lazy_input)
+        out = self._branch_out(stream, self.mixer)
+        self.mixer.forward(ctx, h, cache, group, out, write_cache)
+        self._branch_done(stream, out)
+        h = self.norm2.normed(ctx, stream, lazy=self.ffn.takes_lazy_input)
+        out = self._branch_out(stream, self.ffn)
+        self.ffn.forward(ctx, h, out)
+        self._branch_done(stream, out)
         ctx.arena.release(mark)
-        return True
+
+    @staticmethod
+    def _branch_out(stream, part):
+        """Where a branch writes: a sink that adds into the stream for parts whose last operation is
+        an ``ops`` product (they declare it), else the stream's delta buffer."""
+        return ops.ResidualSink(stream) if part.writes_through_linear else stream.delta
+
+    @staticmethod
+    def _branch_done(stream, out) -> None:
+        if not isinstance(out, ops.ResidualSink):      # the output waits in delta for the next norm
+            stream.has_delta, stream.n_ssq = True, 0

@@ -13,6 +13,8 @@ from .base import FeedForward, StepContext, register
 
 @register("feed_forward", "swiglu")
 class SwiGLU(FeedForward):
+    takes_lazy_input = True       # x goes to one product only
+    writes_through_linear = True  # out is the out of the last product
     def __init__(self, hidden_size: int, intermediate_size: int):
         self.hidden_size = hidden_size
         self.intermediate_size = intermediate_size

@@ -32,6 +32,10 @@ class RMSNorm(Norm):
         # scale vectors are float32 on the device whatever the compute dtype
         self.weight = source.get(prefix + self.weight_name).to(torch.float32).to(device).contiguous()
 
+    def normed(self, ctx: StepContext, stream, lazy: bool = False):
+        x = ops.NormedInput(stream, self.weight, self.eps, ctx.arena.alloc, ctx.dtype)
+        return x if lazy else x.materialize()
+
     def add_norm(self, ctx: StepContext, resid, delta, out):
         ops.add_rmsnorm(resid, delta, self.weight, self.eps, out)
         return out

@@ -21,7 +21,7 @@ def prepare_matrix(w):
     return w.contiguous()
 
 
-def embedding(token_ids, table, out):
+def embedding(token_ids, table, out, ssq=None):
     out.copy_(table[token_ids.long()].to(torch.float32))
 
 
@@ -46,6 +46,11 @@ def add_rmsnorm_rows(resid, delta, rows, weight, eps, out):
 
 
 def linear(x, w, out):
+    from qwen_engine_b200.ops import NormedInput, ResidualSink
+    if isinstance(x, NormedInput):
+        x = x.materialize()
+    if isinstance(out, ResidualSink):
+        out = out.as_delta()
     out.copy_((x.to(torch.float32) @ w.to(torch.float32).t()).to(out.dtype))
 
 
@@ -140,6 +145,9 @@ def silu_mul(gate_up, out):
 
 
 def linear_silu_mul(gate_up, w, out, scratch):
+    from qwen_engine_b200.ops import ResidualSink
+    if isinstance(out, ResidualSink):
+        out = out.as_delta()
     act = scratch((gate_up.shape[0], gate_up.shape[1] // 2), gate_up.dtype)
     silu_mul(gate_up, act)
     linear(act, w, out)

@@ -107,6 +107,45 @@ def test_linear_tcgen05(M, N, K, out_f32):
     _close(got, want, odt, tol16=8e-3)
 
 
+@pytest.mark.parametrize("M,H,N", [(1, 64, 40), (8, 1024, 4096), (16, 80, 389), (5, 1032, 72), (17, 128, 64)])
+def test_branch_into_stream_then_fused_norm(M, H, N):
+    """A branch's product added into the float32 stream by the product's own epilogue (which leaves
+    the rows' sums of squares), then the next norm fused into the next product (few rows, bfloat16);
+    more rows fall back to the delta buffer and the separate norm kernel.  Same numbers either way."""
+    dt = torch.bfloat16
+    K1 = 136
+    resid = _randn((M, H), torch.float32, 50, 2.0)
+    x1 = _randn((M, K1), dt, 51)
+    w1 = _randn((H, K1), dt, 54, 0.1)
+    gu = _randn((M, 2 * K1), dt, 55)
+    nw = 1 + 0.3 * _randn((H,), torch.float32, 52)
+    w2 = _randn((N, H), dt, 53, 0.1)
+
+    # plain reference: resid += x1 w1^T (rounded as the delta buffer would hold it is NOT applied: the
+    # fused route adds the float32 product), then += silu-mul branch, then norm and product
+    want_resid = resid + x1.float() @ w1.float().t()
+    g, u = gu[:, :K1].float(), gu[:, K1:].float()
+    want_resid = want_resid + (g / (1 + torch.exp(-g)) * u).to(dt).float() @ w1.float().t()
+    normed = want_resid * torch.rsqrt((want_resid ** 2).mean(-1, keepdim=True) + 1e-5) * nw
+    want = normed.to(dt).float() @ w2.float().t()
+
+    alloc = lambda shape, d: torch.empty(shape, dtype=d, device=DEV)
+    ssq = torch.full((M, -(-(-(-H // 16)) // 4) * 4), float("nan"), device=DEV)
+    st = ops.ResidualStream(resid.to(DEV), torch.empty(M, H, dtype=dt, device=DEV), ssq)
+    ops.linear(x1.to(DEV), w1.to(DEV), ops.ResidualSink(st))
+    ops.linear_silu_mul(gu.to(DEV), w1.to(DEV), ops.ResidualSink(st), alloc)
+    fused = M <= ops.SMALL_M_MAX
+    assert (st.n_ssq == -(-H // 16) and not st.has_delta) if fused else st.has_delta
+    out = torch.empty(M, N, dtype=dt, device=DEV)
+    ops.linear(ops.NormedInput(st, nw.to(DEV), 1e-5, alloc, dt), w2.to(DEV), out)
+    assert not st.has_delta
+    _close(st.resid, want_resid, torch.float32, tol32=2e-2)          # bfloat16 operands, float32 sums
+    _close(out, want, dt, tol16=2e-2)
+    if fused:
+        got_ssq = st.ssq[:, :st.n_ssq].sum(-1).cpu()
+        assert torch.allclose(got_ssq, (st.resid.cpu() ** 2).sum(-1), rtol=1e-4)
+
+
 def test_linear_row_does_not_depend_on_batch():
     """A row's product is the same bits whatever else is in the batch (32-bit path)."""
     x = _randn((67, 200), torch.float32, 8).to(DEV)
