@@ -406,3 +406,111 @@ def test_plan_is_checked():
         DecoderModel(ModelLayout(plan=(PlanEntry(3, 0, True),), **base))
     with pytest.raises(ValueError, match="unknown mixer"):
         PartSpec("no_such_mixer").build("mixer")
+
+
+# ---- a windowed attention layer through the engine: pages behind the window go back while it runs -----------
+@dataclass
+class WindowToyConfig(ModelConfig):
+    architecture: ClassVar[str] = "WindowToyForCausalLM"
+    hidden_size: int = 48
+    vocab_size: int = 53
+    window: int = 11
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(**{k: v for k, v in raw.items() if k != "architectures"})
+
+    def validate(self):
+        pass
+
+
+def window_toy_layout(cfg: WindowToyConfig) -> ModelLayout:
+    H, D = cfg.hidden_size, 16
+    norm = PartSpec("rmsnorm", dict(width=H, eps=1e-5))
+    ffn = PartSpec("swiglu", dict(hidden_size=H, intermediate_size=64))
+    rope = PartSpec("rope_neox", dict(head_dim=D, theta=1e4))
+    attn = lambda window: PartSpec("gqa_attention", dict(hidden_size=H, num_heads=4, num_kv_heads=2, head_dim=D, scale=D ** -0.5,
+                                                         qk_norm_eps=1e-5, position_encoding=rope, window=window))
+    block = lambda w: PartSpec("pre_norm", dict(hidden_size=H, mixer=attn(w), feed_forward=ffn, norm=norm))
+    # one layer that sees every earlier token, one that sees a window of them: two cache groups
+    return ModelLayout(vocab_size=cfg.vocab_size, hidden_size=H,
+                       layers=(LayerSpec(block(None), "layers.0."), LayerSpec(block(cfg.window), "layers.1.")),
+                       plan=(PlanEntry(0, 0, True), PlanEntry(1, 1, True)), final_norm=norm,
+                       embed_name="embed.weight", final_norm_prefix="norm.", tie_head=True)
+
+
+def _window_toy_plain(cfg, w, tokens):
+    T, D = len(tokens), 16
+    pos = torch.arange(T)
+    x = plain.embedding(torch.tensor(tokens), w["embed.weight"])
+    for i, window in ((0, None), (1, cfg.window)):
+        p = f"layers.{i}."
+        h = plain.rmsnorm(x, w[p + "input_layernorm.weight"], 1e-5)
+        q = plain.rmsnorm(plain.linear(h, w[p + "self_attn.q_proj.weight"]).view(T, 4, D), w[p + "self_attn.q_norm.weight"], 1e-5)
+        k = plain.rmsnorm(plain.linear(h, w[p + "self_attn.k_proj.weight"]).view(T, 2, D), w[p + "self_attn.k_norm.weight"], 1e-5)
+        v = plain.linear(h, w[p + "self_attn.v_proj.weight"]).view(T, 2, D)
+        cos, sin = plain.rope_angles(pos, D, 1e4)
+        o = plain.causal_attention(plain.rope_rotate(q, cos, sin), plain.rope_rotate(k, cos, sin), v, D ** -0.5, window)
+        x = x + plain.linear(o.reshape(T, -1), w[p + "self_attn.o_proj.weight"])
+        x = x + plain.mlp_part(plain.rmsnorm(x, w[p + "post_attention_layernorm.weight"], 1e-5), w, p + "mlp.")
+    return plain.linear(plain.rmsnorm(x, w["norm.weight"], 1e-5), w["embed.weight"])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_windowed_layer_gives_pages_back_and_still_agrees(dtype):
+    """A layer with a window of 11 keys beside a layer that keeps all keys: the windowed group's pages
+    are handed back while the request runs (its page count stays bounded over 150 tokens), entries of
+    its block table become -1, and the logits still equal the plain implementation's, through
+    portions and single tokens.  The window's edge falls inside pages (page size 4)."""
+    register_architecture("WindowToyForCausalLM", WindowToyConfig, window_toy_layout)
+    try:
+        cfg = config_from_dict({"architectures": ["WindowToyForCausalLM"], "window": 11})
+        model = build_model(cfg)
+        tensors = _weights(model.weight_manifest(), 21)
+        model.load_weights(DictSource(tensors), dtype, DEV)
+        cm = CacheManager(model.cache_specs(), 4, 48, 2, dtype, DEV, poison=True)
+        assert [g.spec.window for g in cm.groups] == [None, 11] and not cm.prefix_cache
+        runner = ModelRunner(model, cm, DEV, dtype)
+        tokens = [(13 * i + 5) % cfg.vocab_size for i in range(150)]
+        want = _window_toy_plain(cfg, {n: t.float() for n, t in tensors.items()}, tokens)
+        rc = cm.open("r")
+        rows, p = [], 0
+        for n in [9, 3, 14, 2, 1, 1, 30, 1, 1, 1, 5] + [1] * 90:
+            n = min(n, len(tokens) - p)
+            if n == 0:
+                break
+            rows.append(runner.step([StepEntry(rc, tokens[p:p + n], list(range(n)))]).float().cpu().clone())
+            p += n
+            held = sum(pg >= 0 for pg in rc.tables[1])
+            assert held <= -(-(11 + n) // 4) + 1, "the windowed group holds more pages than its window needs"
+            cm.check_invariants()
+        assert p == len(tokens) and rc.tables[1][0] == -1 and all(pg >= 0 for pg in rc.tables[0])
+        _close(torch.cat(rows), want, dtype, "windowed layer")
+        cm.close(rc)
+        assert cm.pages_in_use() == 0
+    finally:
+        del ARCHITECTURES["WindowToyForCausalLM"]
+
+
+# ---- the real layer sizes of the benchmark model, few layers, against the plain implementation -----------------
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_real_layer_sizes_of_qwen3_0_6b(dtype, tmp_path):
+    """Two layers with the widths of Qwen3-0.6B (hidden 1024, 16/8 heads of 128, intermediate 3072) and a
+    cut vocabulary: the tensor-core kernels at the sizes they are tuned for, inside the model, through
+    a whole prompt, portions and decoded tokens."""
+    import helpers
+    from qwen_engine_b200.weights import write_model_folder
+    raw = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=1024, num_attention_heads=16,
+               num_key_value_heads=8, head_dim=128, intermediate_size=3072, vocab_size=2048, rope_theta=1e6,
+               rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=4096)
+    folder = write_model_folder(config_from_dict(raw), str(tmp_path / "m"), seed=2, std=0.02, norm_std=0.1)
+    from qwen_engine_b200.engine.loading import load_model
+    from qwen_engine_b200.engine.trace import TraceReplayer
+    loaded = load_model(folder, dtype, DEV, 16, 64, 4)
+    rep = TraceReplayer(folder, dtype, 1024, page_size=16, loaded=loaded)
+    toks = helpers.random_tokens(2048, 200, 31)
+    steps = [{"entries": [{"id": "a", "tokens": toks[:130], "want": [0, 64, 129]}]},
+             {"entries": [{"id": "a", "tokens": toks[130:170], "want": list(range(40))}]}]
+    steps += [{"entries": [{"id": "a", "tokens": [t], "want": [0]}]} for t in toks[170:]]
+    got = helpers.run_steps(rep, steps)
+    helpers.check_requests(got, folder, {"a": toks}, dtype, "real layer sizes")
