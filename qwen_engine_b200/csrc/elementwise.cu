@@ -3,6 +3,7 @@
 // over the element type (float: the true 32-bit path; bfloat16: serving) and
 // does its arithmetic in float32.
 #include "common.cuh"
+#include "rope_d128.cuh"
 
 // ---------------------------------------------------------------------------------------
 // out[t, :] = float(table[ids[t], :])      (reference src/layers/ops/embedding.py:28-44)
@@ -293,73 +294,10 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ q, T* __restrict__ 
   }
 }
 
-// The common case in bfloat16, head size 128 with all of it rotated (or none): a lane holds 4
-// consecutive elements, its rotation partner (d +- 64) is held by lane +- 16, no shared memory.
-__global__ void qk_norm_rope_kv_write_d128_kernel(__nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ k,
-                                                  const __nv_bfloat16* __restrict__ v, long q_stride, long k_stride,
-                                                  long v_stride, const int* __restrict__ positions,
-                                                  const float* __restrict__ qw, const float* __restrict__ kw, float eps,
-                                                  const float* __restrict__ inv_freq,
-                                                  __nv_bfloat16* __restrict__ pages, const int* __restrict__ slot_mapping,
-                                                  int T_tokens, int Hq, int Hkv, int page_size, int write_kv) {
-  constexpr int D = 128;
+__global__ void qk_norm_rope_kv_write_d128_kernel(RopeD128Args args) {
   pdl_launch_dependents();
   pdl_wait();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int heads_total = Hq + 2 * Hkv;
-  const long item = (long)blockIdx.x * (blockDim.x >> 5) + warp;
-  if (item >= (long)T_tokens * heads_total) return;
-  const int t = (int)(item / heads_total);
-  const int head = (int)(item % heads_total);
-  if (head >= Hq + Hkv) {           // a value head: copy into the cache
-    if (!write_kv) return;
-    const int h = head - Hq - Hkv;
-    const int slot = slot_mapping[t];
-    const int page = slot / page_size, off = slot % page_size;
-    const uint2 val = *reinterpret_cast<const uint2*>(v + (size_t)t * v_stride + (size_t)h * D + 4 * lane);
-    *reinterpret_cast<uint2*>(pages + ((((size_t)page * 2 + 1) * Hkv + h) * page_size + off) * D + 4 * lane) = val;
-    return;
-  }
-  const bool is_q = head < Hq;
-  const int h = is_q ? head : head - Hq;
-  __nv_bfloat16* x = (is_q ? q + (size_t)t * q_stride : k + (size_t)t * k_stride) + (size_t)h * D + 4 * lane;
-  const float* w = is_q ? qw : kw;
-  const uint2 raw = *reinterpret_cast<const uint2*>(x);
-  float f[4];
-  {
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
-  }
-  if (w) {
-    const float ss = warp_sum(f[0] * f[0] + f[1] * f[1] + f[2] * f[2] + f[3] * f[3]);
-    const float rstd = rsqrtf(ss / (float)D + eps);
-    const float4 wv = *reinterpret_cast<const float4*>(w + 4 * lane);
-    f[0] = f[0] * rstd * wv.x; f[1] = f[1] * rstd * wv.y; f[2] = f[2] * rstd * wv.z; f[3] = f[3] * rstd * wv.w;
-  }
-  if (inv_freq) {
-    const float pos = (float)positions[t];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float partner = __shfl_xor_sync(0xffffffffu, f[i], 16);
-      const float ang = pos * inv_freq[(4 * lane + i) & 63];
-      float sn, cs;
-      sincosf(ang, &sn, &cs);
-      f[i] = lane < 16 ? cs * f[i] - sn * partner : sn * partner + cs * f[i];
-    }
-  }
-  uint2 res;
-  {
-    __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
-    res.x = *reinterpret_cast<uint32_t*>(&a);
-    res.y = *reinterpret_cast<uint32_t*>(&b);
-  }
-  *reinterpret_cast<uint2*>(x) = res;
-  if (!is_q && write_kv) {
-    const int slot = slot_mapping[t];
-    const int page = slot / page_size, off = slot % page_size;
-    *reinterpret_cast<uint2*>(pages + ((((size_t)page * 2 + 0) * Hkv + h) * page_size + off) * D + 4 * lane) = res;
-  }
+  rope_d128_item(args, (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5));
 }
 
 extern "C" int qe_qk_norm_rope_kv_write(void* q, void* k, const void* v, long q_stride, long k_stride, long v_stride,
@@ -377,9 +315,10 @@ extern "C" int qe_qk_norm_rope_kv_write(void* q, void* k, const void* v, long q_
       (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)pages) & 7) == 0) {
     const long n_items = (long)T * (Hq + 2 * Hkv);
     const int vwarps = 8;
+    RopeD128Args ra{(__nv_bfloat16*)q, (__nv_bfloat16*)k, (const __nv_bfloat16*)v, q_stride, k_stride, v_stride, positions,
+                    qw, kw, eps, inv_freq, (__nv_bfloat16*)pages, slot_mapping, T, Hq, Hkv, page_size, write_kv};
     qe_launch(qk_norm_rope_kv_write_d128_kernel, dim3((unsigned)((n_items + vwarps - 1) / vwarps)), dim3(vwarps * 32), 0,
-              stream, (__nv_bfloat16*)q, (__nv_bfloat16*)k, (const __nv_bfloat16*)v, q_stride, k_stride, v_stride,
-              positions, qw, kw, eps, inv_freq, (__nv_bfloat16*)pages, slot_mapping, T, Hq, Hkv, page_size, write_kv);
+              stream, ra);
     QE_CHECK_LAUNCH("qk_norm_rope_kv_write");
     return 0;
   }

@@ -1,0 +1,219 @@
+// Device functions of the product for a few rows (see gemm_small_m.cu): shared by the stand-alone
+// kernel and by the persistent kernel that runs a decode step's operations as a program.
+#pragma once
+#include "common.cuh"
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {   // read once: do not keep in L1
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+// silu(g) * u for a pair of bfloat16 values, in float32, rounded once (the reference's silumul,
+// src/layers/fused_ops/silumul.py:50-53, without its intermediate rounding of silu).  The result has
+// 8 bits of mantissa, so the fast exponential and division (errors of a few float32 ulps) are used:
+// every CTA forms the whole activation again, and the exact routines would cost more than the product.
+__device__ __forceinline__ float silu_fast(float g) { return __fdividef(g, 1.f + __expf(-g)); }
+__device__ __forceinline__ uint32_t silu_mul_pair(uint32_t g, uint32_t u) {
+  const float2 gf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&g));
+  const float2 uf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u));
+  __nv_bfloat162 r = __floats2bfloat162_rn(silu_fast(gf.x) * uf.x, silu_fast(gf.y) * uf.y);
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+
+// What the token operand is made of (formed while loading, so that no kernel and no buffer stands
+// between the producer of the data and the product):
+//   PLAIN  x[M, K] as it is;
+//   SILU   x[m, k] = silu(gate_up[m, k]) * gate_up[m, K + k] from gate_up[M, 2K] (the feed-forward's
+//          activation fused into its output projection);
+//   NORM   x[m, k] = resid[m, k] * rstd[m] * norm_w[k] with rstd[m] = rsqrt(sum_k resid[m, k]^2 / K + eps):
+//          the RMS norm of the float32 residual stream fused into the projection that follows it.  The
+//          row's sum of squares comes in n_ssq partial sums that the kernel that last wrote the stream
+//          left behind (see RESID), so no pass over the row is needed here.
+// And what happens to the result:
+//   RESID  the product is a branch's output: it is added into the float32 residual stream in place
+//          (each element belongs to one thread), and the CTA leaves the sum of squares of its 16
+//          columns of every row in ssq_out[m, blockIdx.x] for the norm that follows.
+enum { X_PLAIN = 0, X_SILU = 1, X_NORM = 2 };
+
+struct FuseArgs {
+  const float* resid;               // NORM: [M, K] float32
+  const float* ssq;                 // NORM: [M, ssq_ld] partial sums of squares of the rows
+  const float* norm_w;              // NORM: [K]
+  float* ssq_out;                   // RESID: [M, ssq_ld]
+  int n_ssq, ssq_ld;
+  float eps;
+};
+
+// a chunk of weights: 64 k of 16 rows = four 16-byte loads per lane
+struct GsmChunk { uint4 a0, b0, a1, b1; };
+
+// The first two chunks of the weights of CTA `vb` (16 rows from 16 vb on), for the calling warp's
+// slice of K.  They depend on nothing a kernel writes, so a caller issues them before it waits for
+// whatever produces the token operand (the previous kernel, or a grid barrier).
+__device__ __forceinline__ void gsm_prefetch(const __nv_bfloat16* __restrict__ w, int N, int K, int k_per_warp, int vb,
+                                             GsmChunk& c0, GsmChunk& c1) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, c = lane & 3;
+  const int n0 = vb * 16;
+  const __nv_bfloat16* w0 = w + (size_t)min(n0 + g, N - 1) * K;
+  const __nv_bfloat16* w1 = w + (size_t)min(n0 + g + 8, N - 1) * K;
+  const int kbeg = warp * k_per_warp, kend = min(K, kbeg + k_per_warp);
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  auto load_chunk = [&](int k0, GsmChunk& ch) {
+    const int ka = k0 + 8 * c, kb = k0 + 32 + 8 * c;
+    ch.a0 = ka < kend ? ld_stream16(w0 + ka) : zero;
+    ch.b0 = ka < kend ? ld_stream16(w1 + ka) : zero;
+    ch.a1 = kb < kend ? ld_stream16(w0 + kb) : zero;
+    ch.b1 = kb < kend ? ld_stream16(w1 + kb) : zero;
+  };
+  load_chunk(kbeg, c0);
+  load_chunk(kbeg + 64, c1);
+}
+
+// The work of CTA `vb` of the product, by all threads of the calling CTA (blockDim.x / 32 warps split
+// K in slices of k_per_warp).  `red`: shared memory for (warps x 16 x 8 MT) floats; `s_rstd`: 8 MT
+// floats; c0, c1: what gsm_prefetch fetched for this vb.  Loads of everything a kernel may have
+// written bypass L1 (ld.global.cg), so the function may also run in a kernel that outlives the
+// producer of its operands.
+template <int MT, typename TOut, int XMODE, bool RESID>
+__device__ __forceinline__ void gsm_cta(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                        TOut* __restrict__ out, int M, int N, int K, int k_per_warp, const FuseArgs& na,
+                                        int vb, float* red, float* s_rstd, GsmChunk c0, GsmChunk c1) {
+  constexpr bool SILU = XMODE == X_SILU;
+  constexpr bool NORM = XMODE == X_NORM;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int g = lane >> 2, c = lane & 3;
+  const int n0 = vb * 16;
+  const int r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1);     // clamped; discarded at the store
+  const __nv_bfloat16* w0 = w + (size_t)r0 * K;
+  const __nv_bfloat16* w1 = w + (size_t)r1 * K;
+  const int kbeg = warp * k_per_warp, kend = min(K, kbeg + k_per_warp);
+  const int x_ld = SILU ? 2 * K : K;
+
+  float acc[MT][4];
+#pragma unroll
+  for (int t = 0; t < MT; ++t)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[t][i] = 0.f;
+
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  auto load_chunk = [&](int k0) {
+    GsmChunk ch;
+    const int ka = k0 + 8 * c, kb = k0 + 32 + 8 * c;
+    ch.a0 = ka < kend ? ld_stream16(w0 + ka) : zero;
+    ch.b0 = ka < kend ? ld_stream16(w1 + ka) : zero;
+    ch.a1 = kb < kend ? ld_stream16(w0 + kb) : zero;
+    ch.b1 = kb < kend ? ld_stream16(w1 + kb) : zero;
+    return ch;
+  };
+  auto load_x = [&](int m, int k) {
+    if (m >= M || k >= kend) return zero;
+    if (NORM) {
+      const size_t o = (size_t)m * K + k;
+      float f[8], wv[8];
+      *reinterpret_cast<float4*>(f) = __ldcg(reinterpret_cast<const float4*>(na.resid + o));
+      *reinterpret_cast<float4*>(f + 4) = __ldcg(reinterpret_cast<const float4*>(na.resid + o + 4));
+      *reinterpret_cast<float4*>(wv) = __ldg(reinterpret_cast<const float4*>(na.norm_w + k));
+      *reinterpret_cast<float4*>(wv + 4) = __ldg(reinterpret_cast<const float4*>(na.norm_w + k + 4));
+      const float rs = s_rstd[m];
+      uint4 v;
+      __nv_bfloat162* vp = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) vp[i] = __floats2bfloat162_rn(f[2 * i] * rs * wv[2 * i], f[2 * i + 1] * rs * wv[2 * i + 1]);
+      return v;
+    }
+    const __nv_bfloat16* p = x + (size_t)m * x_ld + k;
+    uint4 v = __ldcg(reinterpret_cast<const uint4*>(p));
+    if (SILU) {
+      const uint4 u = __ldcg(reinterpret_cast<const uint4*>(p + K));
+      v.x = silu_mul_pair(v.x, u.x); v.y = silu_mul_pair(v.y, u.y);
+      v.z = silu_mul_pair(v.z, u.z); v.w = silu_mul_pair(v.w, u.w);
+    }
+    return v;
+  };
+  auto compute = [&](const GsmChunk& ch, int k0) {
+    const int ka = k0 + 8 * c, kb = k0 + 32 + 8 * c;
+#pragma unroll
+    for (int t = 0; t < MT; ++t) {
+      const uint4 xa = load_x(t * 8 + g, ka);
+      const uint4 xb = load_x(t * 8 + g, kb);
+      mma_bf16_16816(acc[t], ch.a0.x, ch.b0.x, ch.a0.y, ch.b0.y, xa.x, xa.y);
+      mma_bf16_16816(acc[t], ch.a0.z, ch.b0.z, ch.a0.w, ch.b0.w, xa.z, xa.w);
+      mma_bf16_16816(acc[t], ch.a1.x, ch.b1.x, ch.a1.y, ch.b1.y, xb.x, xb.y);
+      mma_bf16_16816(acc[t], ch.a1.z, ch.b1.z, ch.a1.w, ch.b1.w, xb.z, xb.w);
+    }
+  };
+  float resid_old = 0.f;                            // RESID: this thread's element of the stream, fetched early
+  if (RESID) {
+    const int m = threadIdx.x >> 4, n = n0 + (threadIdx.x & 15);
+    if (threadIdx.x < 16 * 8 * MT && m < M && n < N) resid_old = __ldcg(reinterpret_cast<const float*>(out) + (size_t)m * N + n);
+  }
+  if (NORM) {
+    // the row norms from the partial sums of squares: a warp per row, all loads at once, summed in a
+    // fixed order (lane l adds parts l, l + 32, ...; then the lanes are added in a tree)
+    for (int m = warp; m < M; m += nwarps) {
+      const float* p = na.ssq + (size_t)m * na.ssq_ld;
+      float ss = 0.f;
+      for (int i = lane; i < na.n_ssq; i += 32) ss += __ldcg(p + i);
+      ss = warp_sum(ss);
+      if (lane == 0) s_rstd[m] = rsqrtf(ss / (float)K + na.eps);
+    }
+    __syncthreads();
+  }
+  for (int k0 = kbeg; k0 < kend; k0 += 128) {
+    const GsmChunk n0c = load_chunk(k0 + 128);
+    compute(c0, k0);
+    const GsmChunk n1c = load_chunk(k0 + 192);
+    compute(c1, k0 + 64);
+    c0 = n0c;
+    c1 = n1c;
+  }
+  // acc[t][0..1]: weight row g, tokens 8t + 2c + {0,1};  acc[t][2..3]: weight row g + 8
+  constexpr int MW = 8 * MT;
+  float* mine = red + (size_t)warp * 16 * MW;
+#pragma unroll
+  for (int t = 0; t < MT; ++t) {
+    mine[g * MW + t * 8 + 2 * c] = acc[t][0];
+    mine[g * MW + t * 8 + 2 * c + 1] = acc[t][1];
+    mine[(g + 8) * MW + t * 8 + 2 * c] = acc[t][2];
+    mine[(g + 8) * MW + t * 8 + 2 * c + 1] = acc[t][3];
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < 16 * MW; e += blockDim.x) {
+    const int m = e >> 4, i = e & 15;               // consecutive threads: consecutive weight rows
+    const int n = n0 + i;
+    if (!RESID) {
+      if (m >= M || n >= N) continue;
+      float s = 0.f;
+      for (int wi = 0; wi < nwarps; ++wi) s += red[((size_t)wi * 16 + i) * MW + m];
+      out[(size_t)m * N + n] = from_f32<TOut>(s);
+    } else {
+      // whole warps run this loop (16 MW is a multiple of 32); lanes outside the matrix add zero
+      float v = 0.f;
+      if (m < M && n < N) {
+        float s = 0.f;
+        for (int wi = 0; wi < nwarps; ++wi) s += red[((size_t)wi * 16 + i) * MW + m];
+        float* dst = reinterpret_cast<float*>(out) + (size_t)m * N + n;
+        v = (e == threadIdx.x ? resid_old : __ldcg(dst)) + s;
+        *dst = v;
+      }
+      float sq = v * v;                              // over the 16 columns of the row: lanes i = 0..15
+      sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+      if (i == 0 && m < M) na.ssq_out[(size_t)m * na.ssq_ld + vb] = sq;
+    }
+  }
+}
+

@@ -1,0 +1,80 @@
+// The fused per-head norm + rotary encoding + cache write for head size 128 in bfloat16 as a device
+// function (see elementwise.cu): shared by the stand-alone kernel and the decode program kernel.
+#pragma once
+#include "common.cuh"
+
+// The common case in bfloat16, head size 128 with all of it rotated (or none): a lane holds 4
+// consecutive elements, its rotation partner (d +- 64) is held by lane +- 16, no shared memory.
+struct RopeD128Args {
+  __nv_bfloat16* q; __nv_bfloat16* k; const __nv_bfloat16* v;
+  long q_stride, k_stride, v_stride;
+  const int* positions; const float* qw; const float* kw; float eps; const float* inv_freq;
+  __nv_bfloat16* pages; const int* slot_mapping;
+  int T_tokens, Hq, Hkv, page_size, write_kv;
+};
+
+// One (token, head) by the calling warp; `item` = token * (Hq + 2 Hkv) + head.  Loads of q, k, v
+// bypass L1 (they are another kernel's or an earlier phase's output).
+__device__ __forceinline__ void rope_d128_item(const RopeD128Args& A, long item) {
+  constexpr int D = 128;
+  __nv_bfloat16* q = A.q; __nv_bfloat16* k = A.k; const __nv_bfloat16* v = A.v;
+  const long q_stride = A.q_stride, k_stride = A.k_stride, v_stride = A.v_stride;
+  const int* positions = A.positions; const float* qw = A.qw; const float* kw = A.kw; const float eps = A.eps;
+  const float* inv_freq = A.inv_freq; __nv_bfloat16* pages = A.pages; const int* slot_mapping = A.slot_mapping;
+  const int T_tokens = A.T_tokens, Hq = A.Hq, Hkv = A.Hkv, page_size = A.page_size, write_kv = A.write_kv;
+  const int lane = threadIdx.x & 31;
+  const int heads_total = Hq + 2 * Hkv;
+  if (item >= (long)T_tokens * heads_total) return;
+  const int t = (int)(item / heads_total);
+  const int head = (int)(item % heads_total);
+  if (head >= Hq + Hkv) {           // a value head: copy into the cache
+    if (!write_kv) return;
+    const int h = head - Hq - Hkv;
+    const int slot = slot_mapping[t];
+    const int page = slot / page_size, off = slot % page_size;
+    const uint2 val = __ldcg(reinterpret_cast<const uint2*>(v + (size_t)t * v_stride + (size_t)h * D + 4 * lane));
+    *reinterpret_cast<uint2*>(pages + ((((size_t)page * 2 + 1) * Hkv + h) * page_size + off) * D + 4 * lane) = val;
+    return;
+  }
+  const bool is_q = head < Hq;
+  const int h = is_q ? head : head - Hq;
+  __nv_bfloat16* x = (is_q ? q + (size_t)t * q_stride : k + (size_t)t * k_stride) + (size_t)h * D + 4 * lane;
+  const float* w = is_q ? qw : kw;
+  const uint2 raw = __ldcg(reinterpret_cast<const uint2*>(x));
+  float f[4];
+  {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+  }
+  if (w) {
+    const float ss = warp_sum(f[0] * f[0] + f[1] * f[1] + f[2] * f[2] + f[3] * f[3]);
+    const float rstd = rsqrtf(ss / (float)D + eps);
+    const float4 wv = *reinterpret_cast<const float4*>(w + 4 * lane);
+    f[0] = f[0] * rstd * wv.x; f[1] = f[1] * rstd * wv.y; f[2] = f[2] * rstd * wv.z; f[3] = f[3] * rstd * wv.w;
+  }
+  if (inv_freq) {
+    const float pos = (float)positions[t];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float partner = __shfl_xor_sync(0xffffffffu, f[i], 16);
+      const float ang = pos * inv_freq[(4 * lane + i) & 63];
+      float sn, cs;
+      sincosf(ang, &sn, &cs);
+      f[i] = lane < 16 ? cs * f[i] - sn * partner : sn * partner + cs * f[i];
+    }
+  }
+  uint2 res;
+  {
+    __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+    res.x = *reinterpret_cast<uint32_t*>(&a);
+    res.y = *reinterpret_cast<uint32_t*>(&b);
+  }
+  *reinterpret_cast<uint2*>(x) = res;
+  if (!is_q && write_kv) {
+    const int slot = slot_mapping[t];
+    const int page = slot / page_size, off = slot % page_size;
+    *reinterpret_cast<uint2*>(pages + ((((size_t)page * 2 + 0) * Hkv + h) * page_size + off) * D + 4 * lane) = res;
+  }
+}
+
