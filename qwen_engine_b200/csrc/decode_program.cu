@@ -47,20 +47,31 @@ __device__ __forceinline__ bool grid_barrier(unsigned* counter, unsigned target,
     unsigned spins = 0;
     for (;;) {
       unsigned v;
-      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];\n" : "=r"(v) : "l"(counter) : "memory");
+      asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];\n" : "=r"(v) : "l"(counter) : "memory");
       if (v >= target) break;
       if (++spins > PROG_BARRIER_LIMIT) { ok = 0; atomicCAS(&g_program_status, 0, 1); break; }
     }
-    __threadfence();
+    __threadfence();                               // what the other CTAs wrote before they were counted is visible
     *s_ok = ok;
   }
   __syncthreads();
   return *s_ok != 0;
 }
 
+// Asks L2 for the weights of work item `vb` of a product (16 rows of K bfloat16 each), one 128-byte
+// line per thread and step.  No register holds anything: after the barrier the loads hit L2.
+__device__ __forceinline__ void prefetch_weights_l2(const __nv_bfloat16* w, int N, int K, int vb) {
+  const int lines_per_row = (K * 2 + 127) / 128;
+  const int rows = min(16, N - vb * 16);
+  for (int e = threadIdx.x; e < rows * lines_per_row; e += PROG_THREADS) {
+    const int r = e / lines_per_row, l = e - r * lines_per_row;
+    const char* p = reinterpret_cast<const char*>(w + (size_t)(vb * 16 + r) * K) + (size_t)l * 128;
+    asm volatile("prefetch.global.L2 [%0];\n" :: "l"(p));
+  }
+}
+
 template <int MT>
-__device__ __forceinline__ void run_gemm(const QeOp& op, float* red, float* s_rstd, GsmChunk c0, GsmChunk c1,
-                                         bool prefetched) {
+__device__ __forceinline__ void run_gemm(const QeOp& op, float* red, float* s_rstd) {
   const int M = op.i[0], N = op.i[1], K = op.i[2], kpw = op.i[3], xmode = op.i[4], resid = op.i[5], out_f32 = op.i[6];
   const __nv_bfloat16* x = (const __nv_bfloat16*)op.p[0];
   const __nv_bfloat16* w = (const __nv_bfloat16*)op.p[1];
@@ -74,7 +85,8 @@ __device__ __forceinline__ void run_gemm(const QeOp& op, float* red, float* s_rs
   na.ssq_ld = op.i[8];
   na.eps = op.f[0];
   for (int vb = blockIdx.x; vb < op.n_vblocks; vb += gridDim.x) {
-    if (!(prefetched && vb == (int)blockIdx.x)) gsm_prefetch(w, N, K, kpw, vb, c0, c1);
+    GsmChunk c0, c1;
+    gsm_prefetch(w, N, K, kpw, vb, c0, c1);
     if (xmode == X_NORM) {
       if (out_f32) gsm_cta<MT, float, X_NORM, false>(x, w, (float*)out, M, N, K, kpw, na, vb, red, s_rstd, c0, c1);
       else gsm_cta<MT, __nv_bfloat16, X_NORM, false>(x, w, (__nv_bfloat16*)out, M, N, K, kpw, na, vb, red, s_rstd, c0, c1);
@@ -93,27 +105,24 @@ __device__ __forceinline__ void run_gemm(const QeOp& op, float* red, float* s_rs
 __global__ void __launch_bounds__(PROG_THREADS, 2)
 decode_program_kernel(const QeOp* __restrict__ ops, int n_ops, unsigned* barrier) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __shared__ QeOp s_op;
+  __shared__ QeOp s_ops[2];                        // this operation and the next (fetched while this one runs)
   __shared__ float s_rstd[16];
   __shared__ int s_ok;
   float* red = reinterpret_cast<float*>(smem_raw);
+  constexpr int OP_INTS = (int)(sizeof(QeOp) / sizeof(int));
+  if (threadIdx.x < OP_INTS) reinterpret_cast<int*>(&s_ops[0])[threadIdx.x] = __ldg(reinterpret_cast<const int*>(ops) + threadIdx.x);
   for (int oi = 0; oi < n_ops; ++oi) {
-    __syncthreads();
-    for (int e = threadIdx.x; e < (int)(sizeof(QeOp) / sizeof(int)); e += PROG_THREADS)
-      reinterpret_cast<int*>(&s_op)[e] = __ldg(reinterpret_cast<const int*>(ops + oi) + e);
-    __syncthreads();
-    const QeOp& op = s_op;
-    // weights of this CTA's first item of a product: on their way before the barrier
-    GsmChunk c0, c1;
-    bool prefetched = false;
-    if (op.type == OP_GEMM && (int)blockIdx.x < op.n_vblocks) {
-      gsm_prefetch((const __nv_bfloat16*)op.p[1], op.i[1], op.i[2], op.i[3], blockIdx.x, c0, c1);
-      prefetched = true;
-    }
+    __syncthreads();                               // s_ops[oi & 1] is complete; s_ops[(oi + 1) & 1] is free
+    if (oi + 1 < n_ops && threadIdx.x < OP_INTS)
+      reinterpret_cast<int*>(&s_ops[(oi + 1) & 1])[threadIdx.x] = __ldg(reinterpret_cast<const int*>(ops + oi + 1) + threadIdx.x);
+    const QeOp& op = s_ops[oi & 1];
+    // weights of this CTA's first item of a product: on their way to L2 before the barrier
+    if (op.type == OP_GEMM && (int)blockIdx.x < op.n_vblocks)
+      prefetch_weights_l2((const __nv_bfloat16*)op.p[1], op.i[1], op.i[2], blockIdx.x);
     if (oi > 0 && !grid_barrier(barrier, (unsigned)oi * gridDim.x, &s_ok)) return;
     if (op.type == OP_GEMM) {
-      if (op.i[0] <= 8) run_gemm<1>(op, red, s_rstd, c0, c1, prefetched);
-      else run_gemm<2>(op, red, s_rstd, c0, c1, prefetched);
+      if (op.i[0] <= 8) run_gemm<1>(op, red, s_rstd);
+      else run_gemm<2>(op, red, s_rstd);
     } else if (op.type == OP_ROPE) {
       RopeD128Args ra{(__nv_bfloat16*)const_cast<void*>(op.p[0]), (__nv_bfloat16*)const_cast<void*>(op.p[1]),
                       (const __nv_bfloat16*)op.p[2], (long)op.l[0], (long)op.l[1], (long)op.l[2], (const int*)op.p[3],

@@ -66,6 +66,12 @@ class ModelRunner:
         self.use_cuda_graphs = bool(use_cuda_graphs) and self._on_gpu and getattr(model, "capturable", True)
         # decode steps by shape: None after the first (eager) run, then (graph, logits, launches)
         self._graphs: dict[tuple, Optional[tuple]] = {}
+        # the recorded operations of such steps (ops.DecodeProgram segments), made on the eager run
+        self._programs: dict[tuple, list] = {}
+        # Off by default: measured on a B200 the program kernel is slower than the graph of launches
+        # (3.0 ms against 1.3 ms a step at batch 8): its grid barrier over 296 CTAs costs 2.5 us, as
+        # much as a dependent launch, and its products run at 8 warps a CTA.  Kept as a tested option.
+        self.use_decode_program = False
         self.num_graph_replays = 0
         self.num_steps = 0
         self.last_h2d_bytes = 0
@@ -90,6 +96,7 @@ class ModelRunner:
             if self._dev_meta is None or self._dev_meta.numel() < n:
                 self._dev_meta = torch.empty(max(1 << 18, 2 * n), dtype=torch.int32, device=self.device)
                 self._graphs.clear()                  # captured steps point into the old buffer
+                self._programs.clear()
             dev = self._dev_meta[:n]
             dev.copy_(self._host[i][:n], non_blocking=True)
             ev = torch.cuda.Event()
@@ -100,23 +107,50 @@ class ModelRunner:
     def _forward(self, ctx: StepContext, graph_key) -> Optional[torch.Tensor]:
         if graph_key is None:
             return self.model.forward(ctx, self.cache)
+        # steps of a few rows in bfloat16: the operations are recorded as a program that one
+        # persistent kernel runs (ops.DecodeProgram); what cannot be recorded is launched as usual
+        program = (self.use_decode_program and self.dtype == torch.bfloat16
+                   and ctx.num_tokens <= ops.PROGRAM_MAX_M)
         if graph_key not in self._graphs:
-            self._graphs[graph_key] = None                # first time: run eagerly (also sizes the arena)
-            return self.model.forward(ctx, self.cache)
+            # first time: run eagerly (also sizes the arena, and uploads the program's descriptors)
+            if program:
+                ops.program_begin(self.device)
+            try:
+                logits = self.model.forward(ctx, self.cache)
+                segments = ops.program_end() if program else None
+            except BaseException:
+                ops.program_abort()
+                raise
+            if not self.arena._overflow:                  # else the buffers move at the next reset: try again
+                self._graphs[graph_key] = None
+                if program:
+                    self._programs[graph_key] = segments
+            return logits
         entry = self._graphs[graph_key]
         if entry is None:
             if len(self._graphs) > 512:                   # many shapes: drop the oldest captures
                 for k in list(self._graphs)[:256]:
                     del self._graphs[k]
+                    self._programs.pop(k, None)
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count
-            with torch.cuda.graph(graph):
-                logits = self.model.forward(ctx, self.cache)
+            segments = self._programs.get(graph_key) if program else None
+            try:
+                with torch.cuda.graph(graph):
+                    if segments is not None:
+                        ops.program_begin(self.device, segments)
+                    logits = self.model.forward(ctx, self.cache)
+                    if segments is not None:
+                        ops.program_end()
+            except BaseException:
+                ops.program_abort()
+                raise
             entry = (graph, logits, ops.launch_count - before, self.arena.buffer)
             self._graphs[graph_key] = entry
         graph, logits, launches, arena_buffer = entry
-        if arena_buffer is not self.arena.buffer:         # the arena grew since: capture again
-            self._graphs[graph_key] = None
+        if arena_buffer is not self.arena.buffer:         # the arena grew since: record and capture again
+            del self._graphs[graph_key]
+            self._programs.pop(graph_key, None)
             return self._forward(ctx, graph_key)
         graph.replay()
         ops.launch_count += launches

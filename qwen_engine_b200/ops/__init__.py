@@ -9,6 +9,7 @@ operation lives with the tests (tests/ref_ops.py).
 from __future__ import annotations
 
 import ctypes
+import struct
 from typing import Optional
 
 import torch
@@ -65,7 +66,122 @@ def _ptr(t: Optional[torch.Tensor]):
 
 
 def _stream():
+    """The current stream, for a launch.  Operations recorded for the decode program (see
+    ``DecodeProgram``) are launched first, so that the order of the step is kept."""
+    if _program is not None and _program.pending:
+        _program.flush()
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+# ---- a decode step's operations as a program run by one persistent kernel -------------------------------
+_OP_FORMAT = "<ii14i2f4q10Q8x"          # type, work items, 14 ints, 2 floats, 4 int64, 10 pointers: 192 bytes
+_OP_GEMM, _OP_ROPE, _OP_ATTN = 1, 2, 3
+PROGRAM_MAX_M = 16                        # rows up to which a step's operations are recorded
+PROGRAM_WARPS = 8                         # warps of a CTA of the program kernel
+_program: Optional["DecodeProgram"] = None
+_program_barriers: dict = {}
+
+
+class ProgramMismatch(RuntimeError):
+    """A step recorded again differs from its first recording (its buffers moved)."""
+
+
+class DecodeProgram:
+    """Recorder of a decode step's operations (``program_begin`` .. ``program_end``).
+
+    While one is active, the products over a few rows, the fused rotary kernel and the decode
+    attention are not launched but written down as descriptors; ``flush`` (called before any other
+    launch and at the end) runs what is pending with ONE launch of a persistent cooperative kernel
+    that walks the list with grid barriers between operations (csrc/decode_program.cu).  The first
+    recording of a step's shape uploads the descriptors; later recordings (under CUDA graph
+    capture) must produce the same bytes and reuse the uploaded copy."""
+
+    def __init__(self, device, segments: Optional[list] = None):
+        self.device = torch.device(device)
+        self.pending: list[bytes] = []
+        self.reuse = segments is not None
+        self.segments: list = segments if segments is not None else []
+        self.index = 0
+        self._flushing = False
+
+    def add(self, op_type: int, n_items: int, ints=(), floats=(), longs=(), ptrs=()) -> None:
+        ints = list(ints) + [0] * (14 - len(ints))
+        floats = list(floats) + [0.0] * (2 - len(floats))
+        longs = list(longs) + [0] * (4 - len(longs))
+        ptrs = [0 if t is None else (t if isinstance(t, int) else t.data_ptr()) for t in ptrs]
+        ptrs += [0] * (10 - len(ptrs))
+        self.pending.append(struct.pack(_OP_FORMAT, op_type, int(n_items), *[int(v) for v in ints],
+                                        *[float(v) for v in floats], *[int(v) for v in longs], *ptrs))
+
+    def flush(self) -> None:
+        if not self.pending or self._flushing:
+            return
+        self._flushing = True
+        try:
+            blob, n = b"".join(self.pending), len(self.pending)
+            self.pending = []
+            if self.reuse:
+                if self.index >= len(self.segments) or self.segments[self.index][0] != blob:
+                    raise ProgramMismatch("the step's operations differ from their first recording")
+                dev = self.segments[self.index][1]
+            else:
+                dev = torch.frombuffer(bytearray(blob), dtype=torch.uint8).to(self.device)
+                self.segments.append((blob, dev, n))
+            self.index += 1
+            key = self.device.index
+            if key not in _program_barriers:
+                _program_barriers[key] = torch.zeros(4, dtype=torch.int32, device=self.device)
+            stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+            _check(lib().qe_run_decode_program(_ptr(dev), n, _ptr(_program_barriers[key]), stream), "decode_program")
+        finally:
+            self._flushing = False
+
+
+def program_begin(device, segments: Optional[list] = None) -> DecodeProgram:
+    global _program
+    assert lib().qe_program_op_bytes() == struct.calcsize(_OP_FORMAT)
+    _program = DecodeProgram(device, segments)
+    return _program
+
+
+def program_flush() -> None:
+    if _program is not None:
+        _program.flush()
+
+
+def program_end() -> list:
+    """Run what is pending, stop recording; returns the uploaded segments for later reuse."""
+    global _program
+    prog, _program = _program, None
+    if prog is None:
+        return []
+    prog.flush()
+    return prog.segments
+
+
+def program_abort() -> None:
+    global _program
+    _program = None
+
+
+def decode_program_status() -> int:
+    """0 if no grid barrier or tile wait of the program kernel ever ran out.  Synchronises the device."""
+    return int(lib().qe_decode_program_status())
+
+
+def _program_kpw(K: int) -> int:
+    return -(-(-(-K // PROGRAM_WARPS)) // 64) * 64
+
+
+def _record_gemm(x, w, out, M, N, K, xmode, resid, out_f32, norm=None, ssq_out=None, ssq_ld=0) -> bool:
+    if _program is None or M > PROGRAM_MAX_M:
+        return False
+    n_resid, n_ssq, n_w, eps, n_ssq_n, n_ld = None, None, None, 0.0, 0, ssq_ld
+    if norm is not None:
+        n_resid, n_ssq, n_w, eps, n_ssq_n, n_ld = norm
+    _program.add(_OP_GEMM, -(-N // 16), ints=[M, N, K, _program_kpw(K), xmode, int(resid), int(out_f32), n_ssq_n, n_ld],
+                 floats=[eps], ptrs=[x, w, out, n_resid, n_ssq, n_w, ssq_out])
+    return True
 
 
 launch_count = 0        # kernels launched through this module since import (read by the benchmark)
@@ -221,6 +337,9 @@ def _linear_normed(x: NormedInput, w: torch.Tensor, out: torch.Tensor) -> bool:
         return False
     _need(w.shape == (N, K) and out.shape == (M, N) and out.dtype in (torch.bfloat16, torch.float32)
           and w.is_contiguous() and out.is_contiguous(), "linear: operands do not fit the normed input")
+    if _record_gemm(w, w, out, M, N, K, 2, False, out.dtype == torch.float32,
+                    norm=(st.resid, st.ssq, x.weight, x.eps, int(st.n_ssq), int(st.ssq.shape[1]))):
+        return True
     _check(lib().qe_linear_small_m_norm(_ptr(st.resid), _ptr(st.ssq), int(st.n_ssq), int(st.ssq.shape[1]),
                                         _ptr(x.weight), ctypes.c_float(x.eps), _ptr(w), _ptr(out), M, N, K,
                                         int(out.dtype == torch.float32), _stream()), "linear")
@@ -238,8 +357,9 @@ def _linear_into_stream(x: torch.Tensor, w: torch.Tensor, sink: ResidualSink, si
             and st.resid.shape == (M, N)):
         return False
     _need(w.shape == (N, K) and x.is_contiguous() and w.is_contiguous(), "linear: operands do not fit")
-    _check(lib().qe_linear_small_m_resid(_ptr(x), _ptr(w), _ptr(st.resid), _ptr(st.ssq), int(st.ssq.shape[1]),
-                                         M, N, K, int(silu), _stream()), "linear")
+    if not _record_gemm(x, w, st.resid, M, N, K, 1 if silu else 0, True, True, ssq_out=st.ssq, ssq_ld=int(st.ssq.shape[1])):
+        _check(lib().qe_linear_small_m_resid(_ptr(x), _ptr(w), _ptr(st.resid), _ptr(st.ssq), int(st.ssq.shape[1]),
+                                             M, N, K, int(silu), _stream()), "linear")
     st.n_ssq = -(-N // 16)
     return True
 
@@ -263,6 +383,8 @@ def linear(x, w: torch.Tensor, out: torch.Tensor) -> None:
     out_f32 = int(out.dtype == torch.float32)
     if x.dtype == torch.bfloat16 and M <= SMALL_M_MAX and K % 8 == 0:
         # a few rows: stream every weight once through the tensor cores
+        if _record_gemm(x, w, out, M, N, K, 0, False, out_f32):
+            return
         _check(lib().qe_linear_small_m(_ptr(x), _ptr(w), _ptr(out), M, N, K, out_f32, _stream()), "linear")
         return
     if x.dtype == torch.bfloat16 and M > SMALL_M_MAX and K % 8 == 0 and TCGEN05_ENABLED:
@@ -287,6 +409,8 @@ def linear_silu_mul(gate_up: torch.Tensor, w: torch.Tensor, out: torch.Tensor, s
     _need(out.shape == (M, N) and out.dtype in (gate_up.dtype, torch.float32), "linear_silu_mul: out must be [M, N]")
     _need(gate_up.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "linear_silu_mul: operands must be contiguous")
     if gate_up.dtype == torch.bfloat16 and M <= SMALL_M_MAX and I % 8 == 0:
+        if _record_gemm(gate_up, w, out, M, N, I, 1, False, out.dtype == torch.float32):
+            return
         _check(lib().qe_linear_small_m_silu(_ptr(gate_up), _ptr(w), _ptr(out), M, N, I,
                                             int(out.dtype == torch.float32), _stream()), "linear_silu_mul")
         return
@@ -337,6 +461,13 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, q_norm_w: 
     if inv_freq is not None:
         _need(inv_freq.dtype == torch.float32 and inv_freq.numel() == rotary_dim // 2,
               "qk_norm_rope_kv_write: inv_freq must be float32 [rotary_dim / 2]")
+    if (_program is not None and T <= PROGRAM_MAX_M and qkv.dtype == torch.bfloat16 and D == 128
+            and (inv_freq is None or rotary_dim == D) and stride % 4 == 0):
+        _program.add(_OP_ROPE, -(-T * (Hq + 2 * Hkv) // PROGRAM_WARPS), ints=[T, Hq, Hkv, page_size, int(bool(write_kv))],
+                     floats=[eps], longs=[stride, stride, stride],
+                     ptrs=[q.data_ptr(), k.data_ptr(), v.data_ptr(), positions, q_norm_w, k_norm_w, inv_freq,
+                           kv_pages if write_kv else None, slot_mapping if write_kv else None])
+        return
     _check(lib().qe_qk_norm_rope_kv_write(
         ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(k.data_ptr()), ctypes.c_void_p(v.data_ptr()),
         ctypes.c_long(stride), ctypes.c_long(stride), ctypes.c_long(stride), _ptr(positions),
@@ -474,6 +605,13 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
             part_acc = ctx.arena.alloc((n_parts * Hkv * part_rows, D), torch.float32)
             part_ml = ctx.arena.alloc((n_parts * Hkv * part_rows, 2), torch.float32)
         counters = _merge_counters(qkv.device) if 0 < n_parts * Hkv <= _MERGE_COUNTERS else None
+        if (_program is not None and T <= PROGRAM_MAX_M and D == 128 and small_tiles and n_items > 0
+                and (n_parts == 0 or counters is not None) and qkv.stride(0) % 8 == 0):
+            _program.add(_OP_ATTN, n_items * Hkv,
+                         ints=[n_items, Hkv, Hq, int(kv_pages.shape[3]), int(block_tables.shape[1]), int(part_rows), int(window)],
+                         floats=[scale * 1.4426950408889634], longs=[qkv.stride(0)],
+                         ptrs=[qkv, kv_pages, block_tables, items, out, part_acc, part_ml, counters])
+            return
         _check(lib().qe_flash_attention_fused_merge(
             _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(block_tables), int(block_tables.shape[1]),
             _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), _ptr(items), n_items, _ptr(merge), n_merge, _ptr(out),
