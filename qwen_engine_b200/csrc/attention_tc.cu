@@ -1,0 +1,450 @@
+// Flash attention over the paged cache on the fifth-generation tensor cores, for prompt portions:
+// head size 128 in bfloat16.  (What it computes is the reference's prefill attention,
+// src/layers/fused_ops/attn.py:130-290: scores and softmax statistics in float32, P rounded to
+// bfloat16 before P·V, the mask key <= position and > position - window.  The reference's Triton
+// kernel leaves the instructions to the compiler; here S = Q·K^T and O += P·V are tcgen05.mma with
+// the accumulators, and P itself, in tensor memory.)
+//
+// One CTA serves one kv head and a tile of 256 "rows" (a row is a query token x a query head of the kv
+// head's group, so the keys and values are read once for the whole group), as two halves of 128 rows,
+// one per softmax group.  Ten warps:
+//   warps 0-3, 4-7  the two softmax groups: one thread per row (= tensor-memory lane).  Per key step
+//                   a thread reads its row of S from tensor memory, masks, takes the running max,
+//                   exponentiates, writes P (bfloat16) back over S, and rescales O when the max grew;
+//   warp 8          fetches Q once and the key and value tiles of every step (128 keys) with TMA, page
+//                   by page from the block table, through a two-stage ring;
+//   warp 9          owns tensor memory and issues all MMAs from one thread.
+// While one group works on its softmax, the tensor core runs the other group's products.
+// Tensor memory (512 columns): S of group 0 | S of group 1 | O of group 0 | O of group 1; P lies over
+// the first 64 columns of its S.
+//
+// The running max is allowed to lag: O and the running sum are rescaled only when the max grew by more
+// than 2^8 since the last rescale, which leaves the quotient O / sum unchanged but for rounding.
+//
+// A work item may cover only a range of keys (a part of a long context); then the CTA writes its
+// unnormalised accumulator with max and sum in float32 to scratch memory, and the CTA that finishes a
+// tile's last part combines the parts (same protocol as the mma.sync kernel, attention_flash.cuh).
+//
+// Keys of a tile that lie in no page (block table entry -1, or past the table) are read as zeros; keys
+// of a held page past the request's length are read as they are and masked, so pages must hold finite
+// values (the cache starts as zeros and only kernels write to it).
+//
+// Every wait on an mbarrier is bounded: a wait that runs out records a code in a device flag, raises a
+// CTA-wide abort that the other roles see in their own waits, and the CTA skips its stores, frees its
+// tensor memory and returns; the host reads the flag with qe_flash_attention_tc_status().
+#include "tcgen05.cuh"
+#include <math.h>
+
+#define AT_ROWS 128             // rows of a softmax group
+#define AT_BN 128               // keys per step
+#define AT_D 128                // head size
+#define AT_THREADS 320
+#define AT_SOFTMAX_THREADS 256
+#define AT_ITEM_INTS 12
+#define AT_TMEM_COLS 512
+#define AT_RESCALE_STEP 8.0f    // log2 of the growth of the max that forces a rescale
+
+static __device__ int g_at_status = 0;          // 0 = fine; else code of the first wait that ran out
+
+struct __align__(1024) AtSmem {
+  __nv_bfloat16 q[2][2][AT_ROWS * 64];          // [group][half of D][row][64]: 128-byte swizzled rows
+  __nv_bfloat16 k[2][2][AT_BN * 64];            // [stage][half of D][key][64]
+  __nv_bfloat16 v[2][2][AT_BN * 64];
+  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_ready[2], p_ready[2], o_ready[2];
+  uint32_t tmem_base;
+  int abort_flag, last;
+};
+
+struct AtArgs {
+  const int* block_tables; int max_blocks; int num_pages;
+  const int* items; __nv_bfloat16* out;
+  float* part_acc; float* part_ml; int part_rows; int* counters;
+  float scale_log2; int window, Hq, Hkv, page_shift;
+};
+
+__device__ __forceinline__ uint32_t at_pack(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void at_softmax_sync() { asm volatile("bar.sync 1, %0;\n" :: "n"(AT_SOFTMAX_THREADS) : "memory"); }
+
+__global__ void __launch_bounds__(AT_THREADS, 1)
+flash_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, AtArgs A) {
+  extern __shared__ unsigned char smem_raw[];
+  pdl_launch_dependents();
+  AtSmem& sm = *reinterpret_cast<AtSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int Hq = A.Hq, Hkv = A.Hkv, window = A.window;
+  const int item_idx = blockIdx.x / Hkv, hkv = blockIdx.x - item_idx * Hkv;
+  volatile int* abort_flag = &sm.abort_flag;
+
+  // the work lists come from the host's copy, not from a kernel
+  const int* it = A.items + (size_t)item_idx * AT_ITEM_INTS;
+  const int req = it[0], q0 = it[1], part = it[4], n_parts_of_tile = it[5], split = it[6];
+  const int row0 = it[7], q_len = it[8], ctx = it[9];
+  const int G = Hq / Hkv;
+  const int tpw = AT_ROWS / G;                      // tokens of one softmax group
+  const int ntok = min(2 * tpw, q_len - q0);
+  const int nrows = ntok * G;
+  const bool two = nrows > AT_ROWS;                 // the second group has rows
+  const int first_pos = ctx + q0;
+  const int kv_end = min(it[3], first_pos + ntok);  // causal frontier of the tile
+  int kv_begin = max(it[2], 0);
+  if (window > 0) kv_begin = max(kv_begin, first_pos - window + 1);
+  const int kt_first = kv_begin / AT_BN * AT_BN;
+  const int n_steps = kv_end > kt_first ? (kv_end - kt_first + AT_BN - 1) / AT_BN : 0;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&sm.q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&sm.k_full[s], 1); mbar_init(&sm.k_empty[s], 1);
+      mbar_init(&sm.v_full[s], 1); mbar_init(&sm.v_empty[s], 1);
+      mbar_init(&sm.s_ready[s], 1); mbar_init(&sm.p_ready[s], AT_ROWS); mbar_init(&sm.o_ready[s], 1);
+    }
+    sm.abort_flag = 0;
+    sm.last = 0;
+    mbar_init_fence();
+  }
+  if (warp == 9) tc_alloc(&sm.tmem_base, AT_TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+  pdl_wait();                                       // q, the new keys and values: the previous kernels' outputs
+
+  if (warp == 8) {
+    // ================= producer ==========================================================================
+    if (n_steps > 0) {
+      const int page_shift = A.page_shift, page_size = 1 << page_shift;
+      const int box_rows = min(page_size, AT_BN);
+      const int nb = AT_BN / box_rows;              // boxes per half tile
+      const int* table = A.block_tables + (size_t)req * A.max_blocks;
+      if (lane == 0) {
+        mbar_expect_tx(&sm.q_full, (two ? 2 : 1) * AT_ROWS * AT_D * (uint32_t)sizeof(__nv_bfloat16));
+        for (int w = 0; w < (two ? 2 : 1); ++w)
+          for (int half = 0; half < 2; ++half)
+            tma_load_3d(sm.q[w][half], &map_q, &sm.q_full, half * 64, hkv * G, row0 + q0 + w * tpw);
+      }
+      int issued = 0;
+      for (int j = 0; j < n_steps; ++j) {
+        const int st = j & 1;
+        bool ok = true;
+        if (j >= 2) {
+          const uint32_t par = ((j >> 1) - 1) & 1;
+          ok = mbar_wait(&sm.k_empty[st], par, abort_flag, 1, &g_at_status) &&
+               mbar_wait(&sm.v_empty[st], par, abort_flag, 2, &g_at_status);
+        }
+        if (!__all_sync(0xffffffffu, ok)) break;
+        if (lane == 0) {
+          mbar_expect_tx(&sm.k_full[st], AT_BN * AT_D * (uint32_t)sizeof(__nv_bfloat16));
+          mbar_expect_tx(&sm.v_full[st], AT_BN * AT_D * (uint32_t)sizeof(__nv_bfloat16));
+        }
+        __syncwarp();
+        const int kt = kt_first + j * AT_BN;
+        for (int idx = lane; idx < 4 * nb; idx += 32) {
+          const int kind = idx / (2 * nb), rem = idx - kind * 2 * nb;
+          const int box = rem >> 1, half = rem & 1;
+          const int key0 = kt + box * box_rows;
+          const int blk = key0 >> page_shift, y = key0 & (page_size - 1);
+          int page = blk < A.max_blocks ? table[blk] : -1;
+          if (page < 0) page = A.num_pages;         // outside the tensor: the box is filled with zeros
+          __nv_bfloat16* dst = (kind ? sm.v[st][half] : sm.k[st][half]) + (size_t)box * box_rows * 64;
+          tma_load_5d(dst, &map_kv, kind ? &sm.v_full[st] : &sm.k_full[st], half * 64, y, hkv, kind, page);
+        }
+        ++issued;
+      }
+      if (*abort_flag && lane == 0) {
+        // giving up: let the copies that are still in flight land before the CTA leaves (bounded)
+        for (uint32_t spin = 0; spin < TC_WAIT_LIMIT; ++spin) if (mbar_try_wait(&sm.q_full, 0)) break;
+        for (int i = max(0, issued - 2); i < issued; ++i) {
+          for (uint32_t spin = 0; spin < TC_WAIT_LIMIT; ++spin) if (mbar_try_wait(&sm.k_full[i & 1], (i >> 1) & 1)) break;
+          for (uint32_t spin = 0; spin < TC_WAIT_LIMIT; ++spin) if (mbar_try_wait(&sm.v_full[i & 1], (i >> 1) & 1)) break;
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ================= MMA issuer: one thread ===========================================================
+    if (lane == 0 && n_steps > 0) {
+      constexpr uint32_t idesc_qk = make_idesc(AT_ROWS, AT_BN);
+      constexpr uint32_t idesc_pv = make_idesc(AT_ROWS, AT_D, true);
+      const int groups = two ? 2 : 1;
+      auto issue_qk = [&](int w, int st) {          // S_w = Q_w · K^T: 8 instructions of k = 16 over the head size
+#pragma unroll
+        for (int ks = 0; ks < AT_D / 16; ++ks) {
+          const uint64_t da = make_smem_desc(smem_u32(sm.q[w][ks >> 2])) + 2 * (ks & 3);
+          const uint64_t db = make_smem_desc(smem_u32(sm.k[st][ks >> 2])) + 2 * (ks & 3);
+          tc_mma_bf16(tmem + w * AT_BN, da, db, idesc_qk, ks != 0);
+        }
+      };
+      auto issue_pv = [&](int w, int st, bool acc) {  // O_w (+)= P_w · V: 8 instructions of k = 16 over the keys
+        const uint64_t dv = make_smem_desc_mn(smem_u32(sm.v[st][0]), AT_BN * 128, 1024);
+#pragma unroll
+        for (int ks = 0; ks < AT_BN / 16; ++ks)
+          tc_mma_bf16_ts(tmem + 2 * AT_BN + w * AT_D, tmem + w * AT_BN + ks * 8, dv + ks * (2048 >> 4), idesc_pv,
+                         acc || ks != 0);
+      };
+      bool ok = mbar_wait(&sm.q_full, 0, abort_flag, 3, &g_at_status) &&
+                mbar_wait(&sm.k_full[0], 0, abort_flag, 4, &g_at_status);
+      if (ok) {
+        tc_fence_after();
+        for (int w = 0; w < groups; ++w) { issue_qk(w, 0); tc_commit(&sm.s_ready[w]); }
+        tc_commit(&sm.k_empty[0]);
+      }
+      for (int j = 0; ok && j < n_steps; ++j) {
+        const int st = j & 1, nst = st ^ 1;
+        const bool more = j + 1 < n_steps;
+        ok = mbar_wait(&sm.v_full[st], (j >> 1) & 1, abort_flag, 5, &g_at_status);
+        for (int w = 0; ok && w < groups; ++w) {
+          ok = mbar_wait(&sm.p_ready[w], j & 1, abort_flag, 6, &g_at_status);
+          if (!ok) break;
+          tc_fence_after();
+          issue_pv(w, st, j > 0);
+          if (more) {
+            if (w == 0) {
+              ok = mbar_wait(&sm.k_full[nst], ((j + 1) >> 1) & 1, abort_flag, 7, &g_at_status);
+              if (!ok) break;
+              tc_fence_after();
+            }
+            issue_qk(w, nst);
+            tc_commit(&sm.s_ready[w]);
+          } else {
+            tc_commit(&sm.o_ready[w]);
+          }
+        }
+        if (!ok) break;
+        tc_commit(&sm.v_empty[st]);
+        if (more) tc_commit(&sm.k_empty[nst]);
+      }
+    }
+  } else {
+    // ================= softmax groups ====================================================================
+    const int w = warp >> 2, quarter = warp & 3;
+    const int r = w * AT_ROWS + quarter * 32 + lane;        // row of the tile
+    const bool active = w == 0 || two;
+    const bool valid = r < nrows;
+    const int ti = r / G, hg = r - ti * G;
+    const int pos = valid ? first_pos + ti : -1;
+    const int hi = valid ? min(kv_end, pos + 1) : 0;          // keys [lo, hi) are allowed for this row
+    const int lo = window > 0 ? max(kv_begin, pos - window + 1) : kv_begin;
+    const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
+    const uint32_t s_col = w * AT_BN, o_col = 2 * AT_BN + w * AT_D;
+    const float scale_log2 = A.scale_log2;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    if (active) {
+      for (int j = 0; j < n_steps; ++j) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&sm.s_ready[w], j & 1, abort_flag, 8, &g_at_status));
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t s[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tc_ld_32x32b_x32(lane_base + s_col + c * 32, s[c]);
+        tc_wait_ld();
+        const int kt = kt_first + j * AT_BN;
+        float mx = -INFINITY;
+        if (kt >= lo && kt + AT_BN <= hi) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[c][i]));
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int key = kt + c * 32 + i;
+              const float v = (key >= lo && key < hi) ? __uint_as_float(s[c][i]) : -INFINITY;
+              s[c][i] = __float_as_uint(v);
+              mx = fmaxf(mx, v);
+            }
+        }
+        mx *= scale_log2;                               // the scale is positive
+        // the reference max moves only when the row's max has grown by more than the step
+        const bool grow = mx > m_run + AT_RESCALE_STEP;
+        const float alpha = grow ? exp2f(m_run - mx) : 1.f;
+        if (grow) m_run = mx;
+        const float base = m_run == -INFINITY ? 0.f : m_run;   // a row with nothing allowed so far
+        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[32];
+            tc_ld_32x32b_x32(lane_base + o_col + c * 32, o);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tc_st_32x32b_x32(lane_base + o_col + c * 32, o);
+          }
+        }
+        float sum = 0.f;
+        uint32_t pk[2][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = exp2f(fmaf(__uint_as_float(s[c][i]), scale_log2, -base));
+            const float p1 = exp2f(fmaf(__uint_as_float(s[c][i + 1]), scale_log2, -base));
+            sum += p0 + p1;
+            pk[c >> 1][(c & 1) * 16 + (i >> 1)] = at_pack(p0, p1);
+          }
+        l_run = l_run * alpha + sum;
+        tc_st_32x32b_x32(lane_base + s_col, pk[0]);
+        tc_st_32x32b_x32(lane_base + s_col + 32, pk[1]);
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(&sm.p_ready[w]);
+      }
+      // ---- the tile's output, or this part's accumulator with max and sum ----------------------------
+      if (ok && n_steps > 0) ok = __all_sync(0xffffffffu, mbar_wait(&sm.o_ready[w], 0, abort_flag, 9, &g_at_status));
+      if (ok) {
+        tc_fence_after();
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        __nv_bfloat16* dst = A.out + (size_t)(row0 + q0 + ti) * ((size_t)Hq * AT_D) + (size_t)(hkv * G + hg) * AT_D;
+        const size_t slot = part >= 0 ? ((size_t)part * Hkv + hkv) * A.part_rows + r : 0;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+          if (n_steps > 0) {
+            tc_ld_32x32b_x32(lane_base + o_col + c * 32, o);
+            tc_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = 0u;
+          }
+          if (!valid) continue;
+          if (part < 0) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 v4;
+              v4.x = at_pack(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+              v4.y = at_pack(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+              v4.z = at_pack(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+              v4.w = at_pack(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + c * 32 + i) = v4;
+            }
+          } else {
+            float* pa = A.part_acc + slot * AT_D + c * 32;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              *reinterpret_cast<uint4*>(pa + i) = make_uint4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+          }
+        }
+        if (valid && part >= 0) { A.part_ml[2 * slot] = m_run; A.part_ml[2 * slot + 1] = l_run; }
+      }
+    }
+    // ---- the CTA that finishes a tile's last part combines the parts ---------------------------------
+    if (part >= 0 && A.counters != nullptr && n_parts_of_tile > 0) {
+      const int first = part - split;
+      if (!ok) sm.abort_flag = 1;
+      __threadfence();                              // this CTA's part is visible before it is counted
+      at_softmax_sync();
+      if (threadIdx.x == 0 && !sm.abort_flag) {
+        const int done = atomicAdd(&A.counters[first * Hkv + hkv], 1);
+        sm.last = (done == n_parts_of_tile - 1);
+        if (sm.last) A.counters[first * Hkv + hkv] = 0;      // ready for the next launch
+      }
+      at_softmax_sync();
+      if (sm.last) {
+        __threadfence();
+        __nv_bfloat16* out_row0 = A.out + (size_t)(row0 + q0) * ((size_t)Hq * AT_D);
+        // out = sum_s 2^(m_s - m) acc_s / sum_s 2^(m_s - m) l_s, in float32, in the order of the parts
+        // (reference attn.py:520-594)
+        for (int e = threadIdx.x; e < nrows * (AT_D / 4); e += AT_SOFTMAX_THREADS) {
+          const int rr = e / (AT_D / 4), d4 = e - rr * (AT_D / 4);
+          float m = -INFINITY;
+          for (int sp = 0; sp < n_parts_of_tile; ++sp)
+            m = fmaxf(m, __ldcg(A.part_ml + 2 * ((((size_t)first + sp) * Hkv + hkv) * A.part_rows + rr)));
+          const float mb = m == -INFINITY ? 0.f : m;
+          float l = 0.f;
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int sp = 0; sp < n_parts_of_tile; ++sp) {
+            const size_t sl = (((size_t)first + sp) * Hkv + hkv) * A.part_rows + rr;
+            const float wgt = exp2f(__ldcg(A.part_ml + 2 * sl) - mb);
+            l += wgt * __ldcg(A.part_ml + 2 * sl + 1);
+            const float4 a4 = __ldcg(reinterpret_cast<const float4*>(A.part_acc + sl * AT_D) + d4);
+            acc.x += wgt * a4.x; acc.y += wgt * a4.y; acc.z += wgt * a4.z; acc.w += wgt * a4.w;
+          }
+          const float inv = l > 0.f ? 1.f / l : 0.f;
+          const int t2 = rr / G, h2 = rr - t2 * G;
+          uint2 v2;
+          v2.x = at_pack(acc.x * inv, acc.y * inv);
+          v2.y = at_pack(acc.z * inv, acc.w * inv);
+          *reinterpret_cast<uint2*>(out_row0 + (size_t)t2 * ((size_t)Hq * AT_D) + (size_t)(hkv * G + h2) * AT_D + 4 * d4) = v2;
+        }
+      }
+    }
+  }
+  // everyone meets here; the allocating warp frees the tensor memory
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tc_fence_after();
+    tc_dealloc(tmem, AT_TMEM_COLS);
+  }
+}
+
+extern "C" int qe_flash_attention_tc_status() {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_at_status, sizeof(int));
+  return v;
+}
+extern "C" void qe_flash_attention_tc_clear_status() {
+  int v = 0;
+  cudaMemcpyToSymbol(g_at_status, &v, sizeof(int));
+}
+
+// Whether the kernel takes this geometry: head size 128; a group size (query heads per kv head) that
+// divides 128; pages of a power of two of at least 8 tokens.
+extern "C" int qe_flash_attention_tc_supported(int Hq, int Hkv, int D, int page_size) {
+  if (D != AT_D || Hkv < 1 || Hq % Hkv) return 0;
+  const int G = Hq / Hkv;
+  if (G > AT_ROWS || (G & (G - 1))) return 0;
+  if (page_size < 8 || (page_size & (page_size - 1))) return 0;
+  return 1;
+}
+
+// q: the step's queries [T, Hq, 128] with q_stride elements between tokens; pages [num_pages, 2, Hkv,
+// page_size, 128]; items: 12 ints each (see attention_flash.cuh; a tile here is 256 / G tokens, and
+// n_splits is the number of parts of the tile when part >= 0); counters: one int per (first part, kv
+// head), zero before the first launch, needed when any item has part >= 0.
+extern "C" int qe_flash_attention_tc(const void* q, long q_stride, int T, const void* pages, int num_pages,
+                                     const int* block_tables, int max_blocks, const int* items, int n_items,
+                                     void* out, float* part_acc, float* part_ml, int part_rows, int* counters,
+                                     float scale, int window, int Hq, int Hkv, int D, int page_size,
+                                     cudaStream_t stream) {
+  if (n_items <= 0) return 0;
+  if (!qe_flash_attention_tc_supported(Hq, Hkv, D, page_size))
+    QE_REFUSE("flash_attention_tc: heads %d/%d, head_dim %d, page size %d are not supported", Hq, Hkv, D, page_size);
+  if ((((uintptr_t)q | (uintptr_t)pages | (uintptr_t)out) & 15) || (q_stride % 8))
+    QE_REFUSE("flash_attention_tc: operands must be 16-byte aligned");
+  if (scale <= 0.f) QE_REFUSE("flash_attention_tc: the scale must be positive");
+  if ((long)n_items * Hkv > 0x7fffffffL) QE_REFUSE("flash_attention_tc: too many work items");
+  const int G = Hq / Hkv;
+  CUtensorMap map_q, map_kv;
+  {
+    const uint64_t dims[3] = {(uint64_t)AT_D, (uint64_t)Hq, (uint64_t)T};
+    const uint64_t strides[2] = {(uint64_t)AT_D * 2, (uint64_t)q_stride * 2};
+    const uint32_t box[3] = {64, (uint32_t)G, (uint32_t)(AT_ROWS / G)};
+    if (!qe_tensor_map_bf16(q, 3, dims, strides, box, &map_q)) return 1;
+  }
+  {
+    const uint64_t P = (uint64_t)page_size;
+    const uint64_t dims[5] = {(uint64_t)AT_D, P, (uint64_t)Hkv, 2, (uint64_t)num_pages};
+    const uint64_t strides[4] = {(uint64_t)AT_D * 2, P * AT_D * 2, (uint64_t)Hkv * P * AT_D * 2, 2ull * Hkv * P * AT_D * 2};
+    const uint32_t box[5] = {64, (uint32_t)(page_size < AT_BN ? page_size : AT_BN), 1, 1, 1};
+    if (!qe_tensor_map_bf16(pages, 5, dims, strides, box, &map_kv)) return 1;
+  }
+  int page_shift = 0;
+  while ((1 << page_shift) < page_size) ++page_shift;
+  AtArgs args{block_tables, max_blocks, num_pages, items, (__nv_bfloat16*)out, part_acc, part_ml, part_rows, counters,
+              scale * 1.4426950408889634f, window, Hq, Hkv, page_shift};
+  const size_t smem = sizeof(AtSmem) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(flash_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) QE_REFUSE("flash_attention_tc: shared memory %zu: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  qe_launch(flash_attention_tc_kernel, dim3((unsigned)(n_items * Hkv)), dim3(AT_THREADS), smem, stream, map_q, map_kv, args);
+  QE_CHECK_LAUNCH("flash_attention_tc");
+  return 0;
+}

@@ -126,7 +126,7 @@ decode_program_kernel(const QeOp* __restrict__ ops, int n_ops, unsigned* barrier
     } else if (op.type == OP_ROPE) {
       RopeD128Args ra{(__nv_bfloat16*)const_cast<void*>(op.p[0]), (__nv_bfloat16*)const_cast<void*>(op.p[1]),
                       (const __nv_bfloat16*)op.p[2], (long)op.l[0], (long)op.l[1], (long)op.l[2], (const int*)op.p[3],
-                      (const float*)op.p[4], (const float*)op.p[5], op.f[0], (const float*)op.p[6],
+                      (const float*)op.p[4], (const float*)op.p[5], op.f[0], (const float*)op.p[6], nullptr,
                       (__nv_bfloat16*)const_cast<void*>(op.p[7]), (const int*)op.p[8],
                       op.i[0], op.i[1], op.i[2], op.i[3], op.i[4]};
       for (int vb = blockIdx.x; vb < op.n_vblocks; vb += gridDim.x)

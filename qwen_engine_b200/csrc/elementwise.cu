@@ -300,9 +300,33 @@ __global__ void qk_norm_rope_kv_write_d128_kernel(RopeD128Args args) {
   rope_d128_item(args, (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5));
 }
 
+// cos_sin[t, j] = (cos, sin)(positions[t] * inv_freq[j]) in float32: the angles of a step, computed
+// once and shared by every layer and head (the reference keeps such a table for every position of
+// the model in every layer, src/models/qwen3/model.py:75-84).
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                  float2* __restrict__ cos_sin, int T, int half) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= T * half) return;
+  const int t = e / half, j = e - t * half;
+  float s, c;
+  sincosf((float)positions[t] * inv_freq[j], &s, &c);
+  cos_sin[e] = make_float2(c, s);
+}
+
+extern "C" int qe_rope_table(const int* positions, const float* inv_freq, void* cos_sin, int T, int half,
+                             cudaStream_t stream) {
+  if (T <= 0 || half <= 0) return 0;
+  const int n = T * half;
+  qe_launch(rope_table_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, positions, inv_freq, (float2*)cos_sin, T, half);
+  QE_CHECK_LAUNCH("rope_table");
+  return 0;
+}
+
 extern "C" int qe_qk_norm_rope_kv_write(void* q, void* k, const void* v, long q_stride, long k_stride, long v_stride,
                                         const int* positions, const float* qw, const float* kw, float eps,
-                                        const float* inv_freq, int rotary_dim, void* pages,
+                                        const float* inv_freq, const void* cos_sin, int rotary_dim, void* pages,
                                         const int* slot_mapping, int T, int Hq, int Hkv, int D, int page_size,
                                         int write_kv, int dtype, cudaStream_t stream) {
   if (T <= 0) return 0;
@@ -316,7 +340,7 @@ extern "C" int qe_qk_norm_rope_kv_write(void* q, void* k, const void* v, long q_
     const long n_items = (long)T * (Hq + 2 * Hkv);
     const int vwarps = 8;
     RopeD128Args ra{(__nv_bfloat16*)q, (__nv_bfloat16*)k, (const __nv_bfloat16*)v, q_stride, k_stride, v_stride, positions,
-                    qw, kw, eps, inv_freq, (__nv_bfloat16*)pages, slot_mapping, T, Hq, Hkv, page_size, write_kv};
+                    qw, kw, eps, inv_freq, (const float2*)cos_sin, (__nv_bfloat16*)pages, slot_mapping, T, Hq, Hkv, page_size, write_kv};
     qe_launch(qk_norm_rope_kv_write_d128_kernel, dim3((unsigned)((n_items + vwarps - 1) / vwarps)), dim3(vwarps * 32), 0,
               stream, ra);
     QE_CHECK_LAUNCH("qk_norm_rope_kv_write");

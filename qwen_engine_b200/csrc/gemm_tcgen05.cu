@@ -17,10 +17,7 @@
 //
 // Edges: TMA fills what lies outside M, N or K with zeros, and the epilogue stores only rows < M and
 // columns < N.  Needs K % 8 == 0 and 16-byte aligned bases (TMA strides); the launcher refuses the rest.
-#include "common.cuh"
-#include <cuda.h>
-#include <mutex>
-#include <unordered_map>
+#include "tcgen05.cuh"
 
 #define TC_BM 128
 #define TC_BN 128
@@ -28,77 +25,8 @@
 #define TC_STAGES 3
 #define TC_THREADS 192
 #define TC_TMEM_COLS 128
-#define TC_WAIT_LIMIT (1u << 22)     // polls of a barrier before giving up (each poll may itself block for a while)
 
 __device__ int g_tc_status = 0;      // 0 = fine; else code of the first wait that ran out
-
-// ---- PTX wrappers ----------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" :: "r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" :: "r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}\n"
-      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-  return ok != 0;
-}
-// Bounded wait: false if the barrier did not flip within the limit or the CTA is aborting.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
-  for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 63) == 63 && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  atomicCAS(&g_tc_status, 0, code);
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-      :: "r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" :: "r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
-      :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
-
-// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle (rows of 64 bfloat16 = 128
-// bytes, groups of 8 rows = 1024 bytes): start address, leading offset 1, stride offset 1024 bytes
-// (both in 16-byte units), descriptor version 1, layout type 2 (128-byte swizzle).
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr) {
-  return (uint64_t)((addr >> 4) & 0x3fff) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-// Instruction descriptor: D float32, A and B bfloat16, both K-major, N / 8 at bit 17, M / 16 at bit 24.
-__host__ __device__ constexpr uint32_t make_idesc(int M, int N) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
-}
 
 struct __align__(1024) TcSmem {
   __nv_bfloat16 a[TC_STAGES][TC_BM * TC_BK];       // 16 KB each
@@ -127,12 +55,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
     mbar_init(&sm.acc_full, 1);
     sm.abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    mbar_init_fence();
   }
   if (warp == 1) {        // tensor memory: one warp allocates (and later frees) 128 columns
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
-                 :: "r"(smem_u32(&sm.tmem_base)), "r"(TC_TMEM_COLS) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    tc_alloc(&sm.tmem_base, TC_TMEM_COLS);
   }
   tc_fence_before();
   __syncthreads();
@@ -146,7 +72,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       for (int kb = 0; kb < num_kb; ++kb) {
         const int s = kb % TC_STAGES;
         const uint32_t round = kb / TC_STAGES;
-        if (round > 0 && !mbar_wait(&sm.empty[s], (round - 1) & 1, abort_flag, 1)) break;
+        if (round > 0 && !mbar_wait(&sm.empty[s], (round - 1) & 1, abort_flag, 1, &g_tc_status)) break;
         mbar_expect_tx(&sm.full[s], (TC_BM + TC_BN) * TC_BK * sizeof(__nv_bfloat16));
         tma_load_2d(sm.a[s], &map_x, &sm.full[s], kb * TC_BK, m0);
         tma_load_2d(sm.b[s], &map_w, &sm.full[s], kb * TC_BK, n0);
@@ -168,7 +94,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       bool ok = true;
       for (int kb = 0; kb < num_kb && ok; ++kb) {
         const int s = kb % TC_STAGES;
-        ok = mbar_wait(&sm.full[s], (kb / TC_STAGES) & 1, abort_flag, 2);
+        ok = mbar_wait(&sm.full[s], (kb / TC_STAGES) & 1, abort_flag, 2, &g_tc_status);
         if (!ok) break;
         tc_fence_after();
         const uint64_t da = make_smem_desc(smem_u32(sm.a[s]));
@@ -185,7 +111,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   } else {
     // ---- epilogue: warps 2..5 read lanes 32 (warp % 4) .. +31, one output row per thread ------
     const int quarter = warp & 3;
-    const bool ok = __all_sync(0xffffffffu, mbar_wait(&sm.acc_full, 0, abort_flag, 3));   // warp-uniform
+    const bool ok = __all_sync(0xffffffffu, mbar_wait(&sm.acc_full, 0, abort_flag, 3, &g_tc_status));   // warp-uniform
     tc_fence_after();
     const int row = m0 + quarter * 32 + lane;
     if (ok) {
@@ -229,62 +155,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" :: "r"(tmem), "r"(TC_TMEM_COLS) : "memory");
+    tc_dealloc(tmem, TC_TMEM_COLS);
   }
 }
 
-// ---- host side: tensor maps (cached by what they describe) and the launcher ---------------------------
-namespace {
-struct MapKey {
-  const void* ptr; int rows, cols, box_rows;
-  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
-};
-struct MapKeyHash {
-  size_t operator()(const MapKey& k) const {
-    return std::hash<const void*>()(k.ptr) ^ (std::hash<long long>()(((long long)k.rows << 32) ^ k.cols) * 31) ^ k.box_rows;
-  }
-};
-std::mutex g_map_mutex;
-std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
-
+// ---- host side ---------------------------------------------------------------------------------------------
 // [rows, cols] bfloat16 row-major; box = box_rows x 64 columns; 128-byte swizzle; zero fill outside.
-bool get_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out) {
-  std::lock_guard<std::mutex> lock(g_map_mutex);
-  MapKey key{ptr, rows, cols, box_rows};
-  auto it = g_maps.find(key);
-  if (it != g_maps.end()) { *out = it->second; return true; }
-  if (g_maps.size() > 4096) g_maps.clear();
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)cols * sizeof(__nv_bfloat16)};
-  cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
-  cuuint32_t elem[2] = {1, 1};
-  CUtensorMap m;
-  // the driver entry point is looked up at run time, so the library does not link against libcuda
-  typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-  static EncodeFn encode = nullptr;
-  if (!encode) {
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn) {
-      qe_set_error("linear_tcgen05: the driver does not offer cuTensorMapEncodeTiled");
-      return false;
-    }
-    encode = (EncodeFn)fn;
-  }
-  CUresult r = encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box,
-                                      elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    qe_set_error("linear_tcgen05: cuTensorMapEncodeTiled failed with code %d", (int)r);
-    return false;
-  }
-  g_maps[key] = m;
-  *out = m;
-  return true;
+static bool get_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out) {
+  const uint64_t dims[2] = {(uint64_t)cols, (uint64_t)rows};
+  const uint64_t strides[1] = {(uint64_t)cols * sizeof(__nv_bfloat16)};
+  const uint32_t box[2] = {TC_BK, (uint32_t)box_rows};
+  return qe_tensor_map_bf16(ptr, 2, dims, strides, box, out);
 }
-}  // namespace
 
 extern "C" int qe_gemm_tc_status() {
   int v = 0;

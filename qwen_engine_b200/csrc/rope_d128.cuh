@@ -9,6 +9,7 @@ struct RopeD128Args {
   __nv_bfloat16* q; __nv_bfloat16* k; const __nv_bfloat16* v;
   long q_stride, k_stride, v_stride;
   const int* positions; const float* qw; const float* kw; float eps; const float* inv_freq;
+  const float2* cos_sin;            // optional [T, 64] (cos, sin) of position * inv_freq, made once per step
   __nv_bfloat16* pages; const int* slot_mapping;
   int T_tokens, Hq, Hkv, page_size, write_kv;
 };
@@ -58,9 +59,13 @@ __device__ __forceinline__ void rope_d128_item(const RopeD128Args& A, long item)
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const float partner = __shfl_xor_sync(0xffffffffu, f[i], 16);
-      const float ang = pos * inv_freq[(4 * lane + i) & 63];
       float sn, cs;
-      sincosf(ang, &sn, &cs);
+      if (A.cos_sin) {
+        const float2 t2 = __ldg(A.cos_sin + (size_t)t * 64 + ((4 * lane + i) & 63));
+        cs = t2.x; sn = t2.y;
+      } else {
+        sincosf(pos * inv_freq[(4 * lane + i) & 63], &sn, &cs);
+      }
       f[i] = lane < 16 ? cs * f[i] - sn * partner : sn * partner + cs * f[i];
     }
   }

@@ -27,6 +27,11 @@ FLASH_BN = 64           # keys per tile of the flash kernel
 FLASH_ITEM_INTS = 12    # int32 per work item of the flash kernel
 FLASH_SPLIT = 256       # keys per part when a decoded token's context is split (reference attn.py:605)
 FLASH_TARGET_CTAS = 296  # two CTAs per SM: long contexts are split into as many parts as fit in one wave
+TC_ROWS = 256           # rows per work item of the tcgen05 attention kernel (two halves of 128)
+TC_BN = 128             # keys per step of the tcgen05 attention kernel
+TC_MIN_ROWS = 65        # rows of a request's portion from which the tcgen05 kernel serves it
+TC_TARGET_CTAS = 148    # one CTA per SM: tiles with many key steps are cut into parts so that no CTA runs much longer than its share
+TC_MIN_PART_STEPS = 4   # key steps below which a tile is not cut
 
 
 class ExtensionMissing(RuntimeError):
@@ -425,6 +430,11 @@ def set_pdl(enabled: bool) -> None:
     lib().qe_set_pdl(int(bool(enabled)))
 
 
+def tc_attention_status() -> int:
+    """0, or the code of the first wait inside the tcgen05 attention kernel that ran out."""
+    return int(lib().qe_flash_attention_tc_status())
+
+
 def tcgen05_status() -> int:
     """0 if no bounded wait of the tcgen05 product kernel ever ran out; else the code of the first
     that did (1: a shared-memory slot never came free, 2: TMA bytes never landed, 3: the
@@ -432,10 +442,22 @@ def tcgen05_status() -> int:
     return int(lib().qe_gemm_tc_status())
 
 
+ROPE_TABLE_MIN_T = 64   # tokens from which a step's rotation angles are computed once (below: in the kernel)
+
+
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, j] = (cos, sin)(positions[t] * inv_freq[j]) in float32; out [T, len(inv_freq), 2]."""
+    _i32(positions, "positions")
+    T, half = positions.numel(), inv_freq.numel()
+    _need(out.dtype == torch.float32 and out.shape == (T, half, 2) and out.is_contiguous(), "rope_table: out must be float32 [T, half, 2]")
+    _check(lib().qe_rope_table(_ptr(positions), _ptr(inv_freq), _ptr(out), T, half, _stream()), "rope_table")
+
+
 def qk_norm_rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, q_norm_w: Optional[torch.Tensor],
                           k_norm_w: Optional[torch.Tensor], eps: float, inv_freq: Optional[torch.Tensor],
                           rotary_dim: int, kv_pages: Optional[torch.Tensor], slot_mapping: Optional[torch.Tensor],
-                          num_heads: int, num_kv_heads: int, head_dim: int, write_kv: bool = True) -> None:
+                          num_heads: int, num_kv_heads: int, head_dim: int, write_kv: bool = True,
+                          cos_sin: Optional[torch.Tensor] = None) -> None:
     """On the stacked projection output qkv [T, (Hq + 2 Hkv) D], in place: per-head RMS norm of q and
     k (if weights are given), half-split rotation by positions (if inv_freq is given); then k and v
     are written to the slots of ``slot_mapping`` in ``kv_pages`` [pages, 2, Hkv, page, D]."""
@@ -471,7 +493,8 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, q_norm_w: 
     _check(lib().qe_qk_norm_rope_kv_write(
         ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(k.data_ptr()), ctypes.c_void_p(v.data_ptr()),
         ctypes.c_long(stride), ctypes.c_long(stride), ctypes.c_long(stride), _ptr(positions),
-        _ptr(q_norm_w), _ptr(k_norm_w), ctypes.c_float(eps), _ptr(inv_freq), int(rotary_dim),
+        _ptr(q_norm_w), _ptr(k_norm_w), ctypes.c_float(eps), _ptr(inv_freq),
+        _ptr(cos_sin if (cos_sin is not None and D == 128 and rotary_dim == D) else None), int(rotary_dim),
         _ptr(kv_pages if write_kv else None), _ptr(slot_mapping if write_kv else None),
         T, Hq, Hkv, D, page_size, int(bool(write_kv)), _dt(qkv), _stream()), "qk_norm_rope_kv_write")
 
@@ -487,7 +510,7 @@ def rope_neox(q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor, inv_fre
     _check(lib().qe_qk_norm_rope_kv_write(
         ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(k.data_ptr()), ctypes.c_void_p(0),
         ctypes.c_long(q.stride(0)), ctypes.c_long(k.stride(0)), ctypes.c_long(0), _ptr(positions),
-        _ptr(None), _ptr(None), ctypes.c_float(0.0), _ptr(inv_freq), int(rotary_dim),
+        _ptr(None), _ptr(None), ctypes.c_float(0.0), _ptr(inv_freq), _ptr(None), int(rotary_dim),
         _ptr(None), _ptr(None), T, Hq, Hkv, D, 1, 0, _dt(q), _stream()), "rope_neox")
 
 
@@ -495,6 +518,39 @@ def flash_supported(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_
     """Whether the tensor-core attention kernel takes this geometry (else the generic kernel runs)."""
     return (dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 256
             and num_kv_heads >= 1 and num_heads % num_kv_heads == 0 and num_heads // num_kv_heads <= FLASH_ROWS)
+
+
+def tc_attention_supported(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int) -> bool:
+    """Whether the tcgen05 attention kernel takes this geometry (prompt portions; else the mma.sync kernel)."""
+    if dtype != torch.bfloat16 or head_dim != 128 or num_kv_heads < 1 or num_heads % num_kv_heads:
+        return False
+    G = num_heads // num_kv_heads
+    return G <= 128 and G & (G - 1) == 0 and page_size >= 8 and page_size & (page_size - 1) == 0
+
+
+def _plan_tc_tiles(tiles: list, Hkv: int) -> tuple[list[int], int]:
+    """Work items of the tcgen05 kernel from its tiles (key steps, first key, last key, item fields):
+    tiles whose key steps exceed a CTA's share of all steps are cut into parts of whole steps; all
+    items sorted by their steps, longest first.  Returns the items and the number of parts."""
+    total = sum(t[0] for t in tiles) * Hkv
+    cap = max(TC_MIN_PART_STEPS, -(-total // TC_TARGET_CTAS))
+    out: list[tuple[int, list[int]]] = []
+    n_parts = 0
+    for steps, lo, hi, (r, q0, row0, n, c) in tiles:
+        parts = -(-steps // cap) if steps > cap else 1
+        if parts == 1:
+            out.append((steps, [r, q0, lo, hi, -1, 0, 0, row0, n, c, 0, 0]))
+            continue
+        per = -(-steps // parts)
+        lo_al = lo // TC_BN * TC_BN
+        parts = -(-steps // per)
+        for sp in range(parts):
+            k0 = lo if sp == 0 else lo_al + sp * per * TC_BN
+            k1 = min(hi, lo_al + (sp + 1) * per * TC_BN)
+            out.append((min(per, steps - sp * per), [r, q0, k0, k1, n_parts + sp, parts, sp, row0, n, c, 0, 0]))
+        n_parts += parts
+    out.sort(key=lambda kv: -kv[0])
+    return [x for _, item in out for x in item], n_parts
 
 
 def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
@@ -506,7 +562,8 @@ def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
     ``geometries``: the (heads, kv heads, head size, window) of the model's attention layers.
     ``tiles`` serves the generic kernel; for each geometry the flash kernel takes, ``fa<i>_items``
     and ``fa<i>_merge`` hold its work and merge items and ``fa<i>_info`` = [parts, rows per part,
-    whether every item has at most 16 rows].
+    whether every item has at most 16 rows]; requests that bring many rows go to the tcgen05 kernel
+    instead where it takes the geometry: ``tc<i>_items`` and ``tc<i>_info`` = [parts, rows per part].
     ``uniform_splits`` (geometry -> number of parts) fixes the number of parts of every request,
     so that the lists depend on the batch's shape only (for steps replayed from a CUDA graph)."""
     tiles: list[int] = []
@@ -520,13 +577,24 @@ def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
             continue
         G = Hq // Hkv
         tpt = FLASH_ROWS // G
-        base = sum(-(-n // tpt) for n in q_lens) * Hkv
+        use_tc = uniform_splits is None and tc_attention_supported(dtype, Hq, Hkv, D, page_size)
+        on_tc = [use_tc and n * G >= TC_MIN_ROWS for n in q_lens]
+        tc_tiles: list = []
+        base = sum(-(-n // tpt) for n, tc in zip(q_lens, on_tc) if not tc) * Hkv
         items: list[int] = []
         merge: list[int] = []
         n_parts, part_rows, row0, max_rows = 0, 1, 0, 0
         whole: list[tuple[int, list[int]]] = []        # (keys the tile visits, its work item)
         for r, (n, c) in enumerate(zip(q_lens, ctx_lens)):
             total = c + n
+            if on_tc[r]:
+                tc_tpt = TC_ROWS // G
+                for q0 in range(0, n, tc_tpt):
+                    lo = max(0, c + q0 - window + 1) if window else 0
+                    hi = c + min(n, q0 + tc_tpt)
+                    tc_tiles.append((-(-(hi - lo // TC_BN * TC_BN) // TC_BN), lo, hi, (r, q0, row0, n, c)))
+                row0 += n
+                continue
             if uniform_splits is not None:
                 splits = uniform_splits[geo]
             else:
@@ -551,6 +619,10 @@ def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
         plan[f"fa{gi}_items"] = items
         plan[f"fa{gi}_merge"] = merge
         plan[f"fa{gi}_info"] = [n_parts, part_rows, int(max_rows <= 16)]
+        if tc_tiles:
+            tc_items, tc_parts = _plan_tc_tiles(tc_tiles, Hkv)
+            plan[f"tc{gi}_items"] = tc_items
+            plan[f"tc{gi}_info"] = [tc_parts, TC_ROWS]
     return plan
 
 
@@ -570,11 +642,11 @@ _MERGE_COUNTERS = 1 << 16
 _merge_counter_tensors: dict = {}
 
 
-def _merge_counters(device) -> torch.Tensor:
-    """Zeroed ints, one per (part, kv head), that the flash kernel uses to find the CTA that finishes a
+def _merge_counters(device, kernel: str = "fa") -> torch.Tensor:
+    """Zeroed ints, one per (part, kv head), that an attention kernel uses to find the CTA that finishes a
     split context last (it merges the parts and sets its counter back to zero).  One tensor per device
-    for the life of the process, so that its address is the same in every captured step."""
-    key = torch.device(device).index
+    and kernel for the life of the process, so that its address is the same in every captured step."""
+    key = (torch.device(device).index, kernel)
     t = _merge_counter_tensors.get(key)
     if t is None:
         t = torch.zeros(_MERGE_COUNTERS, dtype=torch.int32, device=device)
@@ -596,6 +668,20 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
     _i32(block_tables, "block_tables")
     plan = ctx.attn_plan
     key = plan.get("geometry_index", {}).get((Hq, Hkv, D, window))
+    if key is not None and f"tc{key}_items" in plan:
+        tc_items = plan[f"tc{key}_items"]
+        tc_parts, tc_rows = plan[f"tc{key}_info_host"]
+        part_acc = part_ml = counters = None
+        if tc_parts:
+            _need(tc_parts * Hkv <= _MERGE_COUNTERS, "paged_attention: too many parts")
+            part_acc = ctx.arena.alloc((tc_parts * Hkv * tc_rows, D), torch.float32)
+            part_ml = ctx.arena.alloc((tc_parts * Hkv * tc_rows, 2), torch.float32)
+            counters = _merge_counters(qkv.device, "tc")
+        _check(lib().qe_flash_attention_tc(
+            _ptr(qkv), ctypes.c_long(qkv.stride(0)), T, _ptr(kv_pages), int(kv_pages.shape[0]), _ptr(block_tables),
+            int(block_tables.shape[1]), _ptr(tc_items), tc_items.numel() // FLASH_ITEM_INTS, _ptr(out),
+            _ptr(part_acc), _ptr(part_ml), int(tc_rows), _ptr(counters), ctypes.c_float(scale), int(window),
+            Hq, Hkv, D, int(kv_pages.shape[3]), _stream()), "flash_attention_tc")
     if key is not None and f"fa{key}_items" in plan:
         items, merge = plan[f"fa{key}_items"], plan[f"fa{key}_merge"]
         n_parts, part_rows, small_tiles = plan[f"fa{key}_info_host"]

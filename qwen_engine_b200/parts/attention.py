@@ -96,7 +96,8 @@ class GQAAttention(Mixer):
                 qkv, ctx.positions, self.q_norm_w, self.k_norm_w, self.qk_norm_eps or 0.0,
                 self.pos.inv_freq if fused_rope else None,
                 self.pos.rotary_dim if fused_rope else 0,
-                cache, view.slot_mapping, H, Hkv, D, write_kv=write_cache)
+                cache, view.slot_mapping, H, Hkv, D, write_kv=write_cache,
+                cos_sin=self.pos.step_table(ctx) if fused_rope else None)
         attn = ctx.arena.alloc((T, self.q_width), ctx.dtype)
         ops.paged_attention(qkv, cache, view.block_tables, ctx, attn, self.scale,
                             self.window or 0, H, Hkv, D)

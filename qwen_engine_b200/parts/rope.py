@@ -32,5 +32,20 @@ class NeoxRope(PositionEncoding):
     def load(self, prefix, source, dtype, device) -> None:
         self.inv_freq = self._inv_freq_cpu.to(device).contiguous()
 
+    def step_table(self, ctx: StepContext):
+        """The cosines and sines of this step's angles [T, rotary_dim / 2, 2], computed once per step
+        and shared by every layer with the same frequencies; None for small steps (the kernel then
+        computes them itself) and where the fused kernel takes no table."""
+        if (ctx.num_tokens < ops.ROPE_TABLE_MIN_T or ctx.dtype != torch.bfloat16 or self.head_dim != 128
+                or self.rotary_dim != self.head_dim):
+            return None
+        key = ("rope_table", self.theta, self.rotary_dim)
+        table = ctx.extras.get(key)
+        if table is None:
+            table = ctx.arena.alloc((ctx.num_tokens, self.rotary_dim // 2, 2), torch.float32)
+            ops.rope_table(ctx.positions, self.inv_freq, table)
+            ctx.extras[key] = table
+        return table
+
     def rotate(self, ctx: StepContext, q, k) -> None:
         ops.rope_neox(q, k, ctx.positions, self.inv_freq, self.rotary_dim)

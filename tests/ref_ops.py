@@ -63,8 +63,13 @@ def _rotate(x, positions, inv_freq, rotary_dim):
     return torch.cat([c * x1 - s * x2, s * x1 + c * x2, x[..., rotary_dim:]], dim=-1)
 
 
+def rope_table(positions, inv_freq, out):
+    ang = positions.to(torch.float32)[:, None] * inv_freq[None, :]
+    out[..., 0], out[..., 1] = torch.cos(ang), torch.sin(ang)
+
+
 def qk_norm_rope_kv_write(qkv, positions, q_norm_w, k_norm_w, eps, inv_freq, rotary_dim, kv_pages,
-                          slot_mapping, num_heads, num_kv_heads, head_dim, write_kv=True):
+                          slot_mapping, num_heads, num_kv_heads, head_dim, write_kv=True, cos_sin=None):
     T = qkv.shape[0]
     Hq, Hkv, D = num_heads, num_kv_heads, head_dim
     q = qkv[:, :Hq * D].reshape(T, Hq, D).to(torch.float32)
@@ -184,7 +189,7 @@ def sample(logits, temperature, top_k, uniform, out):
 
 
 _NAMES = ["prepare_matrix", "embedding", "add_rmsnorm", "add_rmsnorm_rows", "linear",
-          "qk_norm_rope_kv_write", "rope_neox", "plan_attention", "paged_attention", "silu_mul", "linear_silu_mul",
+          "qk_norm_rope_kv_write", "rope_neox", "rope_table", "plan_attention", "paged_attention", "silu_mul", "linear_silu_mul",
           "argmax", "sample"]
 
 

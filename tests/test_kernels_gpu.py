@@ -305,6 +305,71 @@ def test_flash_attention_split_contexts(Hq, Hkv, D, P, q_lens, ctx_lens):
     _close(got, want, dtype)
 
 
+TC_SHAPES = [(16, 8, 128, 16), (4, 4, 128, 8), (8, 1, 128, 32), (4, 2, 128, 128), (2, 1, 128, 256)]
+TC_BATCHES = [
+    ([300], [0]),                         # a whole prompt: several tiles, the diagonal inside a step
+    ([200, 1, 70], [100, 50, 0]),         # portions with and without context beside a decoded token
+    ([129, 640], [1000, 77]),             # a long context before a portion; one row more than a half tile
+    ([33, 70], [95, 64]),                 # few rows: the second softmax group stays idle for some tiles
+]
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,P", TC_SHAPES)
+@pytest.mark.parametrize("q_lens,ctx_lens", TC_BATCHES)
+def test_tc_attention(Hq, Hkv, D, P, q_lens, ctx_lens):
+    """Prompt portions on the tcgen05 kernel (the plan sends requests with many rows there and the
+    rest to the mma.sync kernel), against the plain reference."""
+    dtype = torch.bfloat16
+    plan = ops.plan_attention(list(q_lens), list(ctx_lens), P, ((Hq, Hkv, D, 0),), dtype)
+    assert plan.get("tc0_items"), "the case must reach the tcgen05 kernel"
+    case = _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, seed=31)
+    want = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, ref_ops.paged_attention, "cpu")
+    got = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, ops.paged_attention, DEV)
+    assert ops.tc_attention_status() == 0
+    _close(got, want, dtype)
+
+
+@pytest.mark.parametrize("q_lens,ctx_lens", [([2048], [0]), ([1024, 600], [3000, 0])])
+def test_tc_attention_parts(q_lens, ctx_lens):
+    """Tiles with many key steps are cut into parts that the last CTA merges."""
+    Hq, Hkv, D, P = 4, 2, 128, 16
+    dtype = torch.bfloat16
+    plan = ops.plan_attention(list(q_lens), list(ctx_lens), P, ((Hq, Hkv, D, 0),), dtype)
+    assert plan["tc0_info"][0] > 1, "the case must cut tiles into parts"
+    case = _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, seed=32)
+    want = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, ref_ops.paged_attention, "cpu")
+    for _ in range(2):                     # twice: the counters are back at zero after a launch
+        got = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, ops.paged_attention, DEV)
+        assert ops.tc_attention_status() == 0
+        _close(got, want, dtype)
+
+
+@pytest.mark.parametrize("window", [1, 100, 128, 129, 300])
+def test_tc_attention_window(window):
+    Hq, Hkv, D, P = 4, 2, 128, 16
+    dtype = torch.bfloat16
+    q_lens, ctx_lens = [260, 1, 150], [30, 70, 400]
+    case = _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, seed=33)
+    want = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ref_ops.paged_attention, "cpu")
+    got = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ops.paged_attention, DEV)
+    assert ops.tc_attention_status() == 0
+    _close(got, want, dtype)
+
+
+@pytest.mark.parametrize("key_pos", [0, 15, 16, 127, 128, 255, 256, 700, 1100])
+def test_tc_attention_far_key_stands_out(key_pos):
+    """One key among a thousand carries almost all the weight of the last query: the output must
+    be its value.  A kernel that misses a page, a step or a part would return something else."""
+    Hq, Hkv, D, P = 4, 2, 128, 16
+    dtype = torch.bfloat16
+    q_lens, ctx_lens = [400, 300], [800, 0]
+    case = _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, seed=34, spike=(0, key_pos, 3))
+    got = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, ops.paged_attention, DEV)
+    want = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, ref_ops.paged_attention, "cpu")
+    assert ops.tc_attention_status() == 0
+    _close(got, want, dtype)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("window", [1, 5, 32, 33])
 def test_paged_attention_window(dtype, window):
