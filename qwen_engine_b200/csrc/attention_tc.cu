@@ -43,6 +43,7 @@
 #define AT_ITEM_INTS 12
 #define AT_TMEM_COLS 512
 #define AT_RESCALE_STEP 8.0f    // log2 of the growth of the max that forces a rescale
+#define AT_MAX_PARTS 8          // parts of one tile at most
 
 static __device__ int g_at_status = 0;          // 0 = fine; else code of the first wait that ran out
 
@@ -65,6 +66,36 @@ struct AtArgs {
 __device__ __forceinline__ uint32_t at_pack(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
+}
+// 2^x by the special-function unit alone (no range fix-up: denormal results are flushed to zero)
+__device__ __forceinline__ float at_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float at_max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// two float32 operations in one instruction (packed pairs in 64-bit registers)
+__device__ __forceinline__ float2 at_fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}\n"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 at_add2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "add.rn.f32x2 rd, ra, rb;\n\t"
+      "mov.b64 {%0, %1}, rd;\n\t}\n"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
 }
 __device__ __forceinline__ void at_softmax_sync() { asm volatile("bar.sync 1, %0;\n" :: "n"(AT_SOFTMAX_THREADS) : "memory"); }
 
@@ -243,10 +274,14 @@ flash_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         const int kt = kt_first + j * AT_BN;
         float mx = -INFINITY;
         if (kt >= lo && kt + AT_BN <= hi) {
+          float mc[4];                                  // four chains of three-input maxima
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
+          for (int c = 0; c < 4; ++c) {
+            mc[c] = fmaxf(__uint_as_float(s[c][0]), __uint_as_float(s[c][1]));
 #pragma unroll
-            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[c][i]));
+            for (int i = 2; i < 32; i += 2) mc[c] = at_max3(mc[c], __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
+          }
+          mx = fmaxf(fmaxf(mc[0], mc[1]), fmaxf(mc[2], mc[3]));
         } else {
 #pragma unroll
           for (int c = 0; c < 4; ++c)
@@ -275,18 +310,22 @@ flash_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
             tc_st_32x32b_x32(lane_base + o_col + c * 32, o);
           }
         }
-        float sum = 0.f;
         uint32_t pk[2][32];
+        float2 sums[4];
+        const float2 sc2 = make_float2(scale_log2, scale_log2), nb2 = make_float2(-base, -base);
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 4; ++c) {
+          sums[c] = make_float2(0.f, 0.f);
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            const float p0 = exp2f(fmaf(__uint_as_float(s[c][i]), scale_log2, -base));
-            const float p1 = exp2f(fmaf(__uint_as_float(s[c][i + 1]), scale_log2, -base));
-            sum += p0 + p1;
-            pk[c >> 1][(c & 1) * 16 + (i >> 1)] = at_pack(p0, p1);
+            const float2 x = at_fma2(make_float2(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])), sc2, nb2);
+            const float2 p = make_float2(at_ex2(x.x), at_ex2(x.y));
+            sums[c] = at_add2(sums[c], p);
+            pk[c >> 1][(c & 1) * 16 + (i >> 1)] = at_pack(p.x, p.y);
           }
-        l_run = l_run * alpha + sum;
+        }
+        const float2 s01 = at_add2(sums[0], sums[1]), s23 = at_add2(sums[2], sums[3]);
+        l_run = l_run * alpha + ((s01.x + s01.y) + (s23.x + s23.y));
         tc_st_32x32b_x32(lane_base + s_col, pk[0]);
         tc_st_32x32b_x32(lane_base + s_col + 32, pk[1]);
         tc_wait_st();
@@ -347,28 +386,66 @@ flash_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         __threadfence();
         __nv_bfloat16* out_row0 = A.out + (size_t)(row0 + q0) * ((size_t)Hq * AT_D);
         // out = sum_s 2^(m_s - m) acc_s / sum_s 2^(m_s - m) l_s, in float32, in the order of the parts
-        // (reference attn.py:520-594)
-        for (int e = threadIdx.x; e < nrows * (AT_D / 4); e += AT_SOFTMAX_THREADS) {
-          const int rr = e / (AT_D / 4), d4 = e - rr * (AT_D / 4);
+        // (reference attn.py:520-594).  A warp takes the rows warp, warp + 8, ...: lane i first works
+        // out the parts' weights of the warp's i-th row, then the warp adds up 16 rows at a time,
+        // one 16-byte piece of a row per lane, with all the loads of a part in flight together.
+        const int mwarp = threadIdx.x >> 5;
+        float f[AT_MAX_PARTS];
+        {
+          const int rr = mwarp + 8 * lane;
+          float mm[AT_MAX_PARTS], ll[AT_MAX_PARTS];
+#pragma unroll
+          for (int sp = 0; sp < AT_MAX_PARTS; ++sp) {
+            mm[sp] = -INFINITY; ll[sp] = 0.f;
+            if (sp < n_parts_of_tile && rr < nrows) {
+              const size_t sl = (((size_t)first + sp) * Hkv + hkv) * A.part_rows + rr;
+              mm[sp] = __ldcg(A.part_ml + 2 * sl);
+              ll[sp] = __ldcg(A.part_ml + 2 * sl + 1);
+            }
+          }
           float m = -INFINITY;
-          for (int sp = 0; sp < n_parts_of_tile; ++sp)
-            m = fmaxf(m, __ldcg(A.part_ml + 2 * ((((size_t)first + sp) * Hkv + hkv) * A.part_rows + rr)));
+#pragma unroll
+          for (int sp = 0; sp < AT_MAX_PARTS; ++sp) m = fmaxf(m, mm[sp]);
           const float mb = m == -INFINITY ? 0.f : m;
           float l = 0.f;
-          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-          for (int sp = 0; sp < n_parts_of_tile; ++sp) {
-            const size_t sl = (((size_t)first + sp) * Hkv + hkv) * A.part_rows + rr;
-            const float wgt = exp2f(__ldcg(A.part_ml + 2 * sl) - mb);
-            l += wgt * __ldcg(A.part_ml + 2 * sl + 1);
-            const float4 a4 = __ldcg(reinterpret_cast<const float4*>(A.part_acc + sl * AT_D) + d4);
-            acc.x += wgt * a4.x; acc.y += wgt * a4.y; acc.z += wgt * a4.z; acc.w += wgt * a4.w;
-          }
+#pragma unroll
+          for (int sp = 0; sp < AT_MAX_PARTS; ++sp) { f[sp] = exp2f(mm[sp] - mb); l += f[sp] * ll[sp]; }
           const float inv = l > 0.f ? 1.f / l : 0.f;
-          const int t2 = rr / G, h2 = rr - t2 * G;
-          uint2 v2;
-          v2.x = at_pack(acc.x * inv, acc.y * inv);
-          v2.y = at_pack(acc.z * inv, acc.w * inv);
-          *reinterpret_cast<uint2*>(out_row0 + (size_t)t2 * ((size_t)Hq * AT_D) + (size_t)(hkv * G + h2) * AT_D + 4 * d4) = v2;
+#pragma unroll
+          for (int sp = 0; sp < AT_MAX_PARTS; ++sp) f[sp] *= inv;
+        }
+#pragma unroll 1
+        for (int b0 = 0; b0 < 32; b0 += 16) {
+          float4 acc[16];
+#pragma unroll
+          for (int u = 0; u < 16; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int sp = 0; sp < AT_MAX_PARTS; ++sp) {
+            if (sp >= n_parts_of_tile) break;
+            float4 a4[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+              const int rr = mwarp + 8 * (b0 + u);
+              const size_t sl = (((size_t)first + sp) * Hkv + hkv) * A.part_rows + rr;
+              a4[u] = rr < nrows ? __ldcg(reinterpret_cast<const float4*>(A.part_acc + sl * AT_D) + lane)
+                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+              const float wgt = __shfl_sync(0xffffffffu, f[sp], b0 + u);
+              acc[u].x += wgt * a4[u].x; acc[u].y += wgt * a4[u].y; acc[u].z += wgt * a4[u].z; acc[u].w += wgt * a4[u].w;
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 16; ++u) {
+            const int rr = mwarp + 8 * (b0 + u);
+            if (rr >= nrows) continue;
+            const int t2 = rr / G, h2 = rr - t2 * G;
+            uint2 v2;
+            v2.x = at_pack(acc[u].x, acc[u].y);
+            v2.y = at_pack(acc[u].z, acc[u].w);
+            *reinterpret_cast<uint2*>(out_row0 + (size_t)t2 * ((size_t)Hq * AT_D) + (size_t)(hkv * G + h2) * AT_D + 4 * lane) = v2;
+          }
         }
       }
     }
@@ -412,6 +489,7 @@ extern "C" int qe_flash_attention_tc(const void* q, long q_stride, int T, const 
                                      float scale, int window, int Hq, int Hkv, int D, int page_size,
                                      cudaStream_t stream) {
   if (n_items <= 0) return 0;
+  if (part_acc && part_rows != 2 * AT_ROWS) QE_REFUSE("flash_attention_tc: parts have %d rows, not %d", part_rows, 2 * AT_ROWS);
   if (!qe_flash_attention_tc_supported(Hq, Hkv, D, page_size))
     QE_REFUSE("flash_attention_tc: heads %d/%d, head_dim %d, page size %d are not supported", Hq, Hkv, D, page_size);
   if ((((uintptr_t)q | (uintptr_t)pages | (uintptr_t)out) & 15) || (q_stride % 8))

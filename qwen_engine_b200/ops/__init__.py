@@ -30,8 +30,9 @@ FLASH_TARGET_CTAS = 296  # two CTAs per SM: long contexts are split into as many
 TC_ROWS = 256           # rows per work item of the tcgen05 attention kernel (two halves of 128)
 TC_BN = 128             # keys per step of the tcgen05 attention kernel
 TC_MIN_ROWS = 65        # rows of a request's portion from which the tcgen05 kernel serves it
-TC_TARGET_CTAS = 148    # one CTA per SM: tiles with many key steps are cut into parts so that no CTA runs much longer than its share
-TC_MIN_PART_STEPS = 4   # key steps below which a tile is not cut
+TC_TARGET_CTAS = 148    # one CTA per SM
+TC_MIN_PART_STEPS = 8   # key steps of a part at least, when tiles are cut to fill idle SMs
+TC_MAX_PARTS = 8        # parts of one tile at most
 
 
 class ExtensionMissing(RuntimeError):
@@ -529,15 +530,17 @@ def tc_attention_supported(dtype: torch.dtype, num_heads: int, num_kv_heads: int
 
 
 def _plan_tc_tiles(tiles: list, Hkv: int) -> tuple[list[int], int]:
-    """Work items of the tcgen05 kernel from its tiles (key steps, first key, last key, item fields):
-    tiles whose key steps exceed a CTA's share of all steps are cut into parts of whole steps; all
-    items sorted by their steps, longest first.  Returns the items and the number of parts."""
-    total = sum(t[0] for t in tiles) * Hkv
-    cap = max(TC_MIN_PART_STEPS, -(-total // TC_TARGET_CTAS))
+    """Work items of the tcgen05 kernel from its tiles (key steps, first key, last key, item fields),
+    sorted by their steps, longest first.  When the tiles are too few to give every SM a CTA (a short
+    portion behind a long context), tiles are cut into parts of whole steps, as many as SMs are idle
+    but none shorter than TC_MIN_PART_STEPS: a part costs a CTA's start and end and the merge, about as
+    much as a few steps.  Returns the items and the number of parts."""
+    n_ctas = len(tiles) * Hkv
+    most = min(TC_MAX_PARTS, TC_TARGET_CTAS // n_ctas) if n_ctas else 1
     out: list[tuple[int, list[int]]] = []
     n_parts = 0
     for steps, lo, hi, (r, q0, row0, n, c) in tiles:
-        parts = -(-steps // cap) if steps > cap else 1
+        parts = max(1, min(most, steps // TC_MIN_PART_STEPS))
         if parts == 1:
             out.append((steps, [r, q0, lo, hi, -1, 0, 0, row0, n, c, 0, 0]))
             continue

@@ -329,7 +329,7 @@ def test_tc_attention(Hq, Hkv, D, P, q_lens, ctx_lens):
     _close(got, want, dtype)
 
 
-@pytest.mark.parametrize("q_lens,ctx_lens", [([2048], [0]), ([1024, 600], [3000, 0])])
+@pytest.mark.parametrize("q_lens,ctx_lens", [([2048], [0]), ([1024, 600], [3000, 0]), ([130], [5000])])
 def test_tc_attention_parts(q_lens, ctx_lens):
     """Tiles with many key steps are cut into parts that the last CTA merges."""
     Hq, Hkv, D, P = 4, 2, 128, 16
