@@ -4,12 +4,14 @@
 // tensor memory, read back with tcgen05.ld and rounded once.  (Contract of the reference's linear,
 // src/layers/ops/linear.py:101-122; its Triton kernel leaves the instruction choice to the compiler.)
 //
-// One CTA per 128 x 128 output tile, 6 warps: warp 0 feeds TMA, warp 1 owns tensor memory and issues
-// the MMAs, warps 2-5 are the epilogue (one quarter of the 128 accumulator lanes each).  A ring of
-// STAGES shared-memory slots is handed back and forth through mbarriers: `full` (TMA bytes landed),
-// `empty` (the MMAs that read the slot retired, signalled by tcgen05.commit), `acc_full` (all MMAs
-// of the tile retired).  Two CTAs fit on an SM, so one tile's epilogue overlaps another's main loop.
-// No cluster, no multicast: every CTA fetches its own tiles.
+// A persistent kernel: one CTA per SM walks over the 128 x BN output tiles (BN = 256, or 128 when that
+// gives too few tiles), 6 warps: warp 0 feeds TMA, warp 1 owns tensor memory and issues the MMAs,
+// warps 2-5 are the epilogue (one quarter of the 128 accumulator lanes each).  A ring of STAGES
+// shared-memory slots (all the shared memory an SM has: what is in flight bounds the rate at which an
+// SM can pull operands from L2) is handed back and forth through mbarriers: `full` (TMA bytes landed),
+// `empty` (the MMAs that read the slot retired, signalled by tcgen05.commit).  Two accumulators in
+// tensor memory take turns (`acc_full`, `acc_empty`), so the epilogue of one tile runs under the main
+// loop of the next.  No cluster, no multicast: every CTA fetches its own tiles.
 //
 // Every wait on an mbarrier is bounded.  A wait that runs out records a code in a device flag, raises
 // a CTA-wide abort that the other roles see in their own waits, and the CTA skips its stores, frees
@@ -20,107 +22,126 @@
 #include "tcgen05.cuh"
 
 #define TC_BM 128
-#define TC_BN 128
 #define TC_BK 64
-#define TC_STAGES 3
 #define TC_THREADS 192
-#define TC_TMEM_COLS 128
 
 __device__ int g_tc_status = 0;      // 0 = fine; else code of the first wait that ran out
 
+template <int BN, int STAGES>
 struct __align__(1024) TcSmem {
-  __nv_bfloat16 a[TC_STAGES][TC_BM * TC_BK];       // 16 KB each
-  __nv_bfloat16 b[TC_STAGES][TC_BN * TC_BK];       // 16 KB each
-  uint64_t full[TC_STAGES];
-  uint64_t empty[TC_STAGES];
-  uint64_t acc_full;
+  __nv_bfloat16 a[STAGES][TC_BM * TC_BK];       // 16 KB each
+  __nv_bfloat16 b[STAGES][BN * TC_BK];          // 16 or 32 KB each
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t acc_full[2], acc_empty[2];
   uint32_t tmem_base;
   int abort_flag;
 };
 
-template <typename TOut>
-__global__ void __launch_bounds__(TC_THREADS)
+template <typename TOut, int BN, int STAGES>
+__global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     TOut* __restrict__ out, int M, int N, int K) {
   extern __shared__ unsigned char smem_raw[];
+  using Smem = TcSmem<BN, STAGES>;
+  constexpr uint32_t TMEM_COLS = 2 * BN;
   pdl_launch_dependents();
   pdl_wait();
-  TcSmem& sm = *reinterpret_cast<TcSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * TC_BN;
   const int num_kb = (K + TC_BK - 1) / TC_BK;
+  const int n_blocks = (N + BN - 1) / BN;
+  const int n_tiles = n_blocks * ((M + TC_BM - 1) / TC_BM);
   volatile int* abort_flag = &sm.abort_flag;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
-    mbar_init(&sm.acc_full, 1);
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&sm.acc_full[s], 1); mbar_init(&sm.acc_empty[s], 4); }
     sm.abort_flag = 0;
     mbar_init_fence();
   }
-  if (warp == 1) {        // tensor memory: one warp allocates (and later frees) 128 columns
-    tc_alloc(&sm.tmem_base, TC_TMEM_COLS);
-  }
+  if (warp == 1) tc_alloc(&sm.tmem_base, TMEM_COLS);     // one warp allocates (and later frees) both accumulators
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
 
   if (warp == 0) {
-    // ---- producer: TMA loads of the k-blocks into the ring ----------------------------------
+    // ---- producer: TMA loads of the k-blocks of this CTA's tiles into the ring -------------------
     if (lane == 0) {
-      int issued = 0;
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % TC_STAGES;
-        const uint32_t round = kb / TC_STAGES;
-        if (round > 0 && !mbar_wait(&sm.empty[s], (round - 1) & 1, abort_flag, 1, &g_tc_status)) break;
-        mbar_expect_tx(&sm.full[s], (TC_BM + TC_BN) * TC_BK * sizeof(__nv_bfloat16));
-        tma_load_2d(sm.a[s], &map_x, &sm.full[s], kb * TC_BK, m0);
-        tma_load_2d(sm.b[s], &map_w, &sm.full[s], kb * TC_BK, n0);
-        ++issued;
+      uint32_t kc = 0;                                    // k-blocks issued so far, over all tiles
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+        const int m0 = (tile / n_blocks) * TC_BM, n0 = (tile % n_blocks) * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++kc) {
+          const uint32_t s = kc % STAGES, round = kc / STAGES;
+          if (round > 0 && !mbar_wait(&sm.empty[s], (round - 1) & 1, abort_flag, 1, &g_tc_status)) { ok = false; break; }
+          mbar_expect_tx(&sm.full[s], (TC_BM + BN) * TC_BK * sizeof(__nv_bfloat16));
+          tma_load_2d(sm.a[s], &map_x, &sm.full[s], kb * TC_BK, m0);
+          tma_load_2d(sm.b[s], &map_w, &sm.full[s], kb * TC_BK, n0);
+        }
       }
       if (*abort_flag) {
         // giving up: let the copies that are still in flight land before the CTA leaves (bounded)
-        for (int i = max(0, issued - TC_STAGES); i < issued; ++i) {
-          const int s = i % TC_STAGES;
+        for (uint32_t i = kc > (uint32_t)STAGES ? kc - STAGES : 0; i < kc; ++i) {
+          const uint32_t s = i % STAGES;
           for (uint32_t spin = 0; spin < TC_WAIT_LIMIT; ++spin)
-            if (mbar_try_wait(&sm.full[s], (i / TC_STAGES) & 1)) break;
+            if (mbar_try_wait(&sm.full[s], (i / STAGES) & 1)) break;
         }
       }
     }
   } else if (warp == 1) {
     // ---- MMA issuer: one thread, 4 instructions of K = 16 per k-block -------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(TC_BM, TC_BN);
+      constexpr uint32_t idesc = make_idesc(TC_BM, BN);
+      uint32_t kc = 0;
       bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % TC_STAGES;
-        ok = mbar_wait(&sm.full[s], (kb / TC_STAGES) & 1, abort_flag, 2, &g_tc_status);
-        if (!ok) break;
+      int it = 0;
+      for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++it) {
+        const int buf = it & 1;
+        // the epilogue has read this accumulator's previous tile out of tensor memory
+        if (it >= 2 && !mbar_wait(&sm.acc_empty[buf], ((it >> 1) - 1) & 1, abort_flag, 4, &g_tc_status)) { ok = false; break; }
         tc_fence_after();
-        const uint64_t da = make_smem_desc(smem_u32(sm.a[s]));
-        const uint64_t db = make_smem_desc(smem_u32(sm.b[s]));
+        const uint32_t acc = tmem + buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++kc) {
+          const uint32_t s = kc % STAGES;
+          if (!mbar_wait(&sm.full[s], (kc / STAGES) & 1, abort_flag, 2, &g_tc_status)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t da = make_smem_desc(smem_u32(sm.a[s]));
+          const uint64_t db = make_smem_desc(smem_u32(sm.b[s]));
 #pragma unroll
-        for (int k = 0; k < TC_BK / 16; ++k) {
-          // 16 bfloat16 = 32 bytes further along K inside the swizzled row: +2 in 16-byte units
-          tc_mma_bf16(tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+          for (int k = 0; k < TC_BK / 16; ++k) {
+            // 16 bfloat16 = 32 bytes further along K inside the swizzled row: +2 in 16-byte units
+            tc_mma_bf16(acc, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+          }
+          tc_commit(&sm.empty[s]);          // arrives when the MMAs that read this slot have retired
         }
-        tc_commit(&sm.empty[s]);          // arrives when the MMAs that read this slot have retired
+        if (ok) tc_commit(&sm.acc_full[buf]);
       }
-      if (ok) tc_commit(&sm.acc_full);
     }
   } else {
     // ---- epilogue: warps 2..5 read lanes 32 (warp % 4) .. +31, one output row per thread ------
     const int quarter = warp & 3;
-    const bool ok = __all_sync(0xffffffffu, mbar_wait(&sm.acc_full, 0, abort_flag, 3, &g_tc_status));   // warp-uniform
-    tc_fence_after();
-    const int row = m0 + quarter * 32 + lane;
-    if (ok) {
+    int it = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
+      const int buf = it & 1;
+      const int m0 = (tile / n_blocks) * TC_BM, n0 = (tile % n_blocks) * BN;
+      const bool ok = __all_sync(0xffffffffu, mbar_wait(&sm.acc_full[buf], (it >> 1) & 1, abort_flag, 3, &g_tc_status));
+      if (!ok) break;                                     // warp-uniform
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
 #pragma unroll 1
-      for (int c0 = 0; c0 < TC_BN; c0 += 32) {
+      for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
-        tc_ld_32x32b_x32(tmem + ((uint32_t)(quarter * 32) << 16) + c0, r);
+        tc_ld_32x32b_x32(tmem + ((uint32_t)(quarter * 32) << 16) + buf * BN + c0, r);
         tc_wait_ld();
-        if (row < M) {
+        if (c0 + 32 == BN) {
+          // the accumulator is in registers: the MMA warp may start the tile after the next in it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sm.acc_empty[buf]);
+        }
+        if (row < M && n0 + c0 < N) {
           TOut* dst = out + (size_t)row * N + n0 + c0;
           if (n0 + c0 + 32 <= N && (N % 8) == 0) {
             if constexpr (sizeof(TOut) == 2) {
@@ -155,7 +176,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tc_dealloc(tmem, TC_TMEM_COLS);
+    tc_dealloc(tmem, TMEM_COLS);
   }
 }
 
@@ -178,27 +199,48 @@ extern "C" void qe_gemm_tc_clear_status() {
   cudaMemcpyToSymbol(g_tc_status, &v, sizeof(int));
 }
 
+template <int BN, int STAGES>
+static int launch_tc(const void* x, const void* w, void* out, int M, int N, int K, int out_f32, int sms, cudaStream_t stream) {
+  CUtensorMap map_x, map_w;
+  if (!get_map(x, M, K, TC_BM, &map_x) || !get_map(w, N, K, BN, &map_w)) return 1;
+  const size_t smem = sizeof(TcSmem<BN, STAGES>) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<__nv_bfloat16, BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tcgen05_kernel<float, BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) QE_REFUSE("linear_tcgen05: shared memory %zu: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  const long tiles = (long)((N + BN - 1) / BN) * ((M + TC_BM - 1) / TC_BM);
+  const dim3 grid((unsigned)(tiles < sms ? tiles : sms));
+  if (out_f32)
+    qe_launch(gemm_tcgen05_kernel<float, BN, STAGES>, grid, dim3(TC_THREADS), smem, stream, map_x, map_w, (float*)out, M, N, K);
+  else
+    qe_launch(gemm_tcgen05_kernel<__nv_bfloat16, BN, STAGES>, grid, dim3(TC_THREADS), smem, stream, map_x, map_w, (__nv_bfloat16*)out, M, N, K);
+  QE_CHECK_LAUNCH("linear_tcgen05");
+  return 0;
+}
+
+static int sm_count() {
+  static int sms[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (sms[dev] == 0) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+    sms[dev] = v;
+  }
+  return sms[dev];
+}
+
 extern "C" int qe_linear_tcgen05(const void* x, const void* w, void* out, int M, int N, int K, int out_f32,
                                  cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8) QE_REFUSE("linear_tcgen05: K = %d is not a positive multiple of 8", K);
   if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) QE_REFUSE("linear_tcgen05: operands must be 16-byte aligned");
-  dim3 grid((N + TC_BN - 1) / TC_BN, (M + TC_BM - 1) / TC_BM);
-  if (grid.y > 65535) QE_REFUSE("linear_tcgen05: M = %d is too large", M);
-  CUtensorMap map_x, map_w;
-  if (!get_map(x, M, K, TC_BM, &map_x) || !get_map(w, N, K, TC_BN, &map_w)) return 1;
-  const size_t smem = sizeof(TcSmem) + 1024;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tcgen05_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) QE_REFUSE("linear_tcgen05: shared memory %zu: %s", smem, cudaGetErrorString(e));
-    configured = true;
-  }
-  if (out_f32)
-    qe_launch(gemm_tcgen05_kernel<float>, grid, dim3(TC_THREADS), smem, stream, map_x, map_w, (float*)out, M, N, K);
-  else
-    qe_launch(gemm_tcgen05_kernel<__nv_bfloat16>, grid, dim3(TC_THREADS), smem, stream, map_x, map_w, (__nv_bfloat16*)out, M, N, K);
-  QE_CHECK_LAUNCH("linear_tcgen05");
-  return 0;
+  const int sms = sm_count();
+  // wide tiles reuse the fetched rows of x twice as often; narrow ones when wide ones would leave SMs idle
+  const long wide_tiles = (long)((N + 255) / 256) * ((M + TC_BM - 1) / TC_BM);
+  if (wide_tiles >= sms) return launch_tc<256, 4>(x, w, out, M, N, K, out_f32, sms, stream);
+  return launch_tc<128, 6>(x, w, out, M, N, K, out_f32, sms, stream);
 }
