@@ -215,18 +215,21 @@ class CacheManager:
             raise
         for g, p in taken:
             rc.tables[g.index].append(p)
-        rc.pending_tokens = [int(t) for t in new_tokens]
+        rc.pending_tokens = list(map(int, new_tokens))
         self.peak_pages_used = max(self.peak_pages_used, self.pages_in_use())
 
     def slot_mapping(self, rc: RequestCache, group: int) -> list[int]:
         """Flat slot (page * page_size + offset) of each pending token in a group."""
         P = self.page_size
         table = rc.tables[group]
-        out = []
-        for pos in range(rc.num_tokens, rc.num_tokens + len(rc.pending_tokens)):
-            page = table[pos // P]
+        out: list[int] = []
+        pos, end = rc.num_tokens, rc.num_tokens + len(rc.pending_tokens)
+        while pos < end:                             # a page's run of slots at a time
+            page, off = table[pos // P], pos % P
             assert page >= 0
-            out.append(page * P + pos % P)
+            n = min(P - off, end - pos)
+            out.extend(range(page * P + off, page * P + off + n))
+            pos += n
         return out
 
     def commit(self, rc: RequestCache) -> None:

@@ -140,12 +140,91 @@ __global__ void add_rmsnorm_bf16x8_kernel(float* __restrict__ resid, const __nv_
   }
 }
 
+// The same with one warp per row, for widths that are multiples of 256 up to 2048: a lane keeps its
+// NC pieces of 8 elements in registers between the sum of squares and the scaling, all its loads are
+// in flight together, and no block-wide barrier is needed.
+template <int NC>
+__global__ void add_rmsnorm_bf16_warp_kernel(float* __restrict__ resid, const __nv_bfloat16* __restrict__ delta,
+                                             const int* __restrict__ rows, const float* __restrict__ w,
+                                             float eps, __nv_bfloat16* __restrict__ out, int n_rows) {
+  constexpr int H = NC * 256;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (n >= n_rows) return;
+  const int src_row = rows ? rows[n] : n;
+  float* r = resid + (size_t)src_row * H;
+  const __nv_bfloat16* d = delta ? delta + (size_t)src_row * H : nullptr;
+  float x[NC][8];
+  uint4 dv[NC];
+#pragma unroll
+  for (int c = 0; c < NC; ++c) {
+    const int h = (c * 32 + lane) * 8;
+    *reinterpret_cast<float4*>(x[c]) = __ldcg(reinterpret_cast<const float4*>(r + h));
+    *reinterpret_cast<float4*>(x[c] + 4) = __ldcg(reinterpret_cast<const float4*>(r + h + 4));
+    if (d) dv[c] = __ldcg(reinterpret_cast<const uint4*>(d + h));
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < NC; ++c) {
+    const int h = (c * 32 + lane) * 8;
+    if (d) {
+      float f[8];
+      bf16x8_to_f32(dv[c], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[c][i] += f[i];
+      if (!rows) {
+        *reinterpret_cast<float4*>(r + h) = *reinterpret_cast<const float4*>(x[c]);
+        *reinterpret_cast<float4*>(r + h + 4) = *reinterpret_cast<const float4*>(x[c] + 4);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += x[c][i] * x[c][i];
+  }
+  ss = warp_sum(ss);
+  const float rstd = rsqrtf(ss / (float)H + eps);
+  __nv_bfloat16* o = out + (size_t)n * H;
+#pragma unroll
+  for (int c = 0; c < NC; ++c) {
+    const int h = (c * 32 + lane) * 8;
+    float wv[8];
+    *reinterpret_cast<float4*>(wv) = *reinterpret_cast<const float4*>(w + h);
+    *reinterpret_cast<float4*>(wv + 4) = *reinterpret_cast<const float4*>(w + h + 4);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[c][i] = x[c][i] * rstd * wv[i];
+    *reinterpret_cast<uint4*>(o + h) = f32_to_bf16x8(x[c]);
+  }
+}
+
+template <int NC>
+static void launch_add_rmsnorm_warp(float* resid, const void* delta, const int* rows, const float* w, float eps, void* out,
+                                    int n_rows, cudaStream_t stream) {
+  const int warps = 4;
+  qe_launch(add_rmsnorm_bf16_warp_kernel<NC>, dim3((n_rows + warps - 1) / warps), dim3(warps * 32), 0, stream, resid,
+            (const __nv_bfloat16*)delta, rows, w, eps, (__nv_bfloat16*)out, n_rows);
+}
+
 extern "C" int qe_add_rmsnorm(float* resid, const void* delta, const int* rows, const float* w,
                               float eps, void* out, int n_rows, int H, int dtype, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
   if (dtype == QE_DTYPE_BF16 && H % 8 == 0 &&
       (((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)out) & 15) == 0) {
+    if (H % 256 == 0 && H <= 2048) {
+      switch (H / 256) {
+        case 1: launch_add_rmsnorm_warp<1>(resid, delta, rows, w, eps, out, n_rows, stream); break;
+        case 2: launch_add_rmsnorm_warp<2>(resid, delta, rows, w, eps, out, n_rows, stream); break;
+        case 3: launch_add_rmsnorm_warp<3>(resid, delta, rows, w, eps, out, n_rows, stream); break;
+        case 4: launch_add_rmsnorm_warp<4>(resid, delta, rows, w, eps, out, n_rows, stream); break;
+        case 5: launch_add_rmsnorm_warp<5>(resid, delta, rows, w, eps, out, n_rows, stream); break;
+        case 6: launch_add_rmsnorm_warp<6>(resid, delta, rows, w, eps, out, n_rows, stream); break;
+        case 7: launch_add_rmsnorm_warp<7>(resid, delta, rows, w, eps, out, n_rows, stream); break;
+        default: launch_add_rmsnorm_warp<8>(resid, delta, rows, w, eps, out, n_rows, stream); break;
+      }
+      QE_CHECK_LAUNCH("add_rmsnorm");
+      return 0;
+    }
     const int vthreads = H >= 2048 ? 256 : 128;
     qe_launch(add_rmsnorm_bf16x8_kernel, dim3(n_rows), dim3(vthreads), 0, stream, resid, (const __nv_bfloat16*)delta,
               rows, w, eps, (__nv_bfloat16*)out, H);
@@ -182,16 +261,32 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up
                                        int I, size_t total8) {
   pdl_launch_dependents();
   pdl_wait();
+  // two 16-byte pieces per thread and turn, all four loads in flight before the arithmetic; the
+  // exponential and the quotient by the fast hardware forms (the result is rounded to bfloat16)
   const int I8 = I / 8;
-  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total8; e += (size_t)gridDim.x * blockDim.x) {
-    const size_t t = e / I8;
-    const int i = (int)(e - t * I8) * 8;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t e0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e0 < total8; e0 += 2 * stride) {
+    const size_t e1 = e0 + stride;
+    const bool two = e1 < total8;
+    const size_t t0 = e0 / I8, t1 = two ? e1 / I8 : t0;
+    const int i0 = (int)(e0 - t0 * I8) * 8, i1 = two ? (int)(e1 - t1 * I8) * 8 : i0;
+    const uint4 rg0 = __ldcg(reinterpret_cast<const uint4*>(gate_up + t0 * 2 * I + i0));
+    const uint4 ru0 = __ldcg(reinterpret_cast<const uint4*>(gate_up + t0 * 2 * I + I + i0));
+    const uint4 rg1 = __ldcg(reinterpret_cast<const uint4*>(gate_up + t1 * 2 * I + i1));
+    const uint4 ru1 = __ldcg(reinterpret_cast<const uint4*>(gate_up + t1 * 2 * I + I + i1));
     float g[8], u[8];
-    bf16x8_to_f32(*reinterpret_cast<const uint4*>(gate_up + t * 2 * I + i), g);
-    bf16x8_to_f32(*reinterpret_cast<const uint4*>(gate_up + t * 2 * I + I + i), u);
+    bf16x8_to_f32(rg0, g);
+    bf16x8_to_f32(ru0, u);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) g[k] = g[k] / (1.f + expf(-g[k])) * u[k];
-    *reinterpret_cast<uint4*>(out + t * I + i) = f32_to_bf16x8(g);
+    for (int k = 0; k < 8; ++k) g[k] = __fdividef(g[k], 1.f + __expf(-g[k])) * u[k];
+    *reinterpret_cast<uint4*>(out + t0 * I + i0) = f32_to_bf16x8(g);
+    if (two) {
+      bf16x8_to_f32(rg1, g);
+      bf16x8_to_f32(ru1, u);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) g[k] = __fdividef(g[k], 1.f + __expf(-g[k])) * u[k];
+      *reinterpret_cast<uint4*>(out + t1 * I + i1) = f32_to_bf16x8(g);
+    }
   }
 }
 
@@ -294,10 +389,17 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ q, T* __restrict__ 
   }
 }
 
+// U consecutive (token, head) per warp, their loads in flight together (large steps: U = 4)
+template <int U>
 __global__ void qk_norm_rope_kv_write_d128_kernel(RopeD128Args args) {
   pdl_launch_dependents();
   pdl_wait();
-  rope_d128_item(args, (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5));
+  const long item0 = ((long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * U;
+  uint2 raw[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) raw[u] = rope_d128_load(args, item0 + u);
+#pragma unroll
+  for (int u = 0; u < U; ++u) rope_d128_finish(args, item0 + u, raw[u]);
 }
 
 // cos_sin[t, j] = (cos, sin)(positions[t] * inv_freq[j]) in float32: the angles of a step, computed
@@ -341,8 +443,12 @@ extern "C" int qe_qk_norm_rope_kv_write(void* q, void* k, const void* v, long q_
     const int vwarps = 8;
     RopeD128Args ra{(__nv_bfloat16*)q, (__nv_bfloat16*)k, (const __nv_bfloat16*)v, q_stride, k_stride, v_stride, positions,
                     qw, kw, eps, inv_freq, (const float2*)cos_sin, (__nv_bfloat16*)pages, slot_mapping, T, Hq, Hkv, page_size, write_kv};
-    qe_launch(qk_norm_rope_kv_write_d128_kernel, dim3((unsigned)((n_items + vwarps - 1) / vwarps)), dim3(vwarps * 32), 0,
-              stream, ra);
+    if (n_items >= 4096)
+      qe_launch(qk_norm_rope_kv_write_d128_kernel<4>, dim3((unsigned)((n_items + 4 * vwarps - 1) / (4 * vwarps))),
+                dim3(vwarps * 32), 0, stream, ra);
+    else
+      qe_launch(qk_norm_rope_kv_write_d128_kernel<1>, dim3((unsigned)((n_items + vwarps - 1) / vwarps)), dim3(vwarps * 32), 0,
+                stream, ra);
     QE_CHECK_LAUNCH("qk_norm_rope_kv_write");
     return 0;
   }

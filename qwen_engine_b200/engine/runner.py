@@ -181,9 +181,9 @@ class ModelRunner:
         appended: list[RequestCache] = []
         try:
             for e in entries:
-                for t in e.tokens:
-                    if not (0 <= int(t) < vocab):
-                        raise ValueError(f"token id {t} of request {e.cache.req_id!r} is outside the vocabulary (0..{vocab - 1})")
+                if not (0 <= min(e.tokens) and max(e.tokens) < vocab):
+                    bad = next(t for t in e.tokens if not (0 <= int(t) < vocab))
+                    raise ValueError(f"token id {bad} of request {e.cache.req_id!r} is outside the vocabulary (0..{vocab - 1})")
                 end = e.cache.num_tokens + len(e.tokens)
                 if self.max_positions is not None and end > self.max_positions:
                     raise ValueError(f"request {e.cache.req_id!r} would reach {end} tokens, beyond "
@@ -209,7 +209,7 @@ class ModelRunner:
             rc = e.cache
             n, c = len(e.tokens), rc.num_tokens
             base = cu_q[-1]
-            token_ids.extend(int(t) for t in e.tokens)
+            token_ids.extend(map(int, e.tokens))
             positions.extend(range(c, c + n))
             cu_q.append(base + n)
             ctx_lens.append(c)

@@ -76,7 +76,15 @@ def _stream():
     ``DecodeProgram``) are launched first, so that the order of the step is kept."""
     if _program is not None and _program.pending:
         _program.flush()
+    if _raw_stream is not None:
+        return ctypes.c_void_p(_raw_stream(_current_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+# torch's own fast paths to the current device and its current stream's handle (the public
+# torch.cuda.current_stream() builds a Stream object per call, which costs more than a launch)
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_current_device = getattr(torch._C, "_cuda_getDevice", None) or torch.cuda.current_device
 
 
 # ---- a decode step's operations as a program run by one persistent kernel -------------------------------

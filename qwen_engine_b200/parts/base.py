@@ -41,7 +41,9 @@ class Arena:
     intermediates are reused by the next layer.  Equal sequences of
     allocations give equal addresses, which CUDA graphs rely on.  When the
     buffer is too small the allocation falls back to a fresh tensor and the
-    buffer grows at the next ``reset()``.
+    buffer grows at the next ``reset()``.  Steps repeat the same allocations, so
+    the views into the buffer are kept by (offset, shape, dtype) and handed out
+    again: making a view costs more host time than a launch.
     """
 
     ALIGN = 256
@@ -54,9 +56,11 @@ class Arena:
         self.high_water = 0
         self._overflow: list[torch.Tensor] = []
         self._overflow_bytes = 0
+        self._views: dict = {}
 
     def reset(self) -> None:
         if self._overflow:
+            self._views = {}
             self.capacity = int((self.high_water + self._overflow_bytes) * 1.25) + self.ALIGN
             self._overflow = []
             self._overflow_bytes = 0
@@ -71,11 +75,19 @@ class Arena:
         self.offset = mark
 
     def alloc(self, shape, dtype: torch.dtype) -> torch.Tensor:
+        shape = tuple(shape)
+        hit = self._views.get((self.offset, shape, dtype))
+        if hit is not None:
+            view, end = hit
+            self.offset = end
+            if end > self.high_water:
+                self.high_water = end
+            return view
         shape = tuple(int(s) for s in shape)
         numel = 1
         for s in shape:
             numel *= s
-        nbytes = numel * torch.empty((), dtype=dtype).element_size()
+        nbytes = numel * dtype.itemsize
         padded = -(-max(nbytes, 1) // self.ALIGN) * self.ALIGN
         if self.offset + padded > self.capacity:
             t = torch.empty(shape, dtype=dtype, device=self.device)
@@ -83,6 +95,8 @@ class Arena:
             self._overflow_bytes += padded
             return t
         view = self.buffer[self.offset:self.offset + nbytes].view(dtype).view(shape)
+        if len(self._views) < 4096:
+            self._views[(self.offset, shape, dtype)] = (view, self.offset + padded)
         self.offset += padded
         self.high_water = max(self.high_water, self.offset)
         return view
