@@ -394,12 +394,20 @@ template <int U>
 __global__ void qk_norm_rope_kv_write_d128_kernel(RopeD128Args args) {
   pdl_launch_dependents();
   pdl_wait();
-  const long item0 = ((long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * U;
+  // the launcher keeps tokens x heads below 2^31
+  const int heads_total = args.Hq + 2 * args.Hkv;
+  const int item0 = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * U;
+  const int t0 = item0 / heads_total, head0 = item0 - t0 * heads_total;
   uint2 raw[U];
+  int t[U], head[U];
 #pragma unroll
-  for (int u = 0; u < U; ++u) raw[u] = rope_d128_load(args, item0 + u);
+  for (int u = 0; u < U; ++u) {
+    head[u] = head0 + u; t[u] = t0;
+    while (head[u] >= heads_total) { head[u] -= heads_total; ++t[u]; }
+    raw[u] = rope_d128_load(args, t[u], head[u]);
+  }
 #pragma unroll
-  for (int u = 0; u < U; ++u) rope_d128_finish(args, item0 + u, raw[u]);
+  for (int u = 0; u < U; ++u) rope_d128_finish(args, t[u], head[u], raw[u]);
 }
 
 // cos_sin[t, j] = (cos, sin)(positions[t] * inv_freq[j]) in float32: the angles of a step, computed
@@ -440,6 +448,7 @@ extern "C" int qe_qk_norm_rope_kv_write(void* q, void* k, const void* v, long q_
       ((q_stride | k_stride | v_stride) % 4) == 0 &&
       (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)pages) & 7) == 0) {
     const long n_items = (long)T * (Hq + 2 * Hkv);
+    if (n_items > 0x7fffff00L) QE_REFUSE("qk_norm_rope_kv_write: %d tokens x %d heads are too many for one launch", T, Hq + 2 * Hkv);
     const int vwarps = 8;
     RopeD128Args ra{(__nv_bfloat16*)q, (__nv_bfloat16*)k, (const __nv_bfloat16*)v, q_stride, k_stride, v_stride, positions,
                     qw, kw, eps, inv_freq, (const float2*)cos_sin, (__nv_bfloat16*)pages, slot_mapping, T, Hq, Hkv, page_size, write_kv};

@@ -14,17 +14,14 @@ struct RopeD128Args {
   int T_tokens, Hq, Hkv, page_size, write_kv;
 };
 
-// One (token, head) by the calling warp; `item` = token * (Hq + 2 Hkv) + head.  In two halves, so that
+// One (token, head) by the calling warp.  In two halves, so that
 // a warp can have the loads of several items in flight before it works on the first: the load of the
 // lane's 4 elements, and the rest.  Loads of q, k, v bypass L1 (they are another kernel's or an
 // earlier phase's output).
-__device__ __forceinline__ uint2 rope_d128_load(const RopeD128Args& A, long item) {
+__device__ __forceinline__ uint2 rope_d128_load(const RopeD128Args& A, int t, int head) {
   constexpr int D = 128;
   const int lane = threadIdx.x & 31;
-  const int heads_total = A.Hq + 2 * A.Hkv;
-  if (item >= (long)A.T_tokens * heads_total) return make_uint2(0u, 0u);
-  const int t = (int)(item / heads_total);
-  const int head = (int)(item % heads_total);
+  if (t >= A.T_tokens) return make_uint2(0u, 0u);
   const __nv_bfloat16* src;
   if (head < A.Hq) src = A.q + (size_t)t * A.q_stride + (size_t)head * D;
   else if (head < A.Hq + A.Hkv) src = A.k + (size_t)t * A.k_stride + (size_t)(head - A.Hq) * D;
@@ -35,23 +32,20 @@ __device__ __forceinline__ uint2 rope_d128_load(const RopeD128Args& A, long item
   return __ldcg(reinterpret_cast<const uint2*>(src + 4 * lane));
 }
 
-__device__ __forceinline__ void rope_d128_finish(const RopeD128Args& A, long item, const uint2 raw) {
+__device__ __forceinline__ void rope_d128_finish(const RopeD128Args& A, int t, int head, const uint2 raw) {
   constexpr int D = 128;
   __nv_bfloat16* q = A.q; __nv_bfloat16* k = A.k;
   const long q_stride = A.q_stride, k_stride = A.k_stride;
   const int* positions = A.positions; const float* qw = A.qw; const float* kw = A.kw; const float eps = A.eps;
   const float* inv_freq = A.inv_freq; __nv_bfloat16* pages = A.pages; const int* slot_mapping = A.slot_mapping;
-  const int T_tokens = A.T_tokens, Hq = A.Hq, Hkv = A.Hkv, page_size = A.page_size, write_kv = A.write_kv;
+  const int Hq = A.Hq, Hkv = A.Hkv, page_size = A.page_size, write_kv = A.write_kv;
   const int lane = threadIdx.x & 31;
-  const int heads_total = Hq + 2 * Hkv;
-  if (item >= (long)T_tokens * heads_total) return;
-  const int t = (int)(item / heads_total);
-  const int head = (int)(item % heads_total);
+  if (t >= A.T_tokens) return;
   if (head >= Hq + Hkv) {           // a value head: copy into the cache
     if (!write_kv) return;
     const int h = head - Hq - Hkv;
     const int slot = slot_mapping[t];
-    const int page = slot / page_size, off = slot % page_size;
+    const int page = slot / page_size, off = slot - page * page_size;
     *reinterpret_cast<uint2*>(pages + ((((size_t)page * 2 + 1) * Hkv + h) * page_size + off) * D + 4 * lane) = raw;
     return;
   }
@@ -95,12 +89,16 @@ __device__ __forceinline__ void rope_d128_finish(const RopeD128Args& A, long ite
   *reinterpret_cast<uint2*>(x) = res;
   if (!is_q && write_kv) {
     const int slot = slot_mapping[t];
-    const int page = slot / page_size, off = slot % page_size;
+    const int page = slot / page_size, off = slot - page * page_size;
     *reinterpret_cast<uint2*>(pages + ((((size_t)page * 2 + 0) * Hkv + h) * page_size + off) * D + 4 * lane) = res;
   }
 }
 
 
+// `item` = token * (Hq + 2 Hkv) + head
 __device__ __forceinline__ void rope_d128_item(const RopeD128Args& A, long item) {
-  rope_d128_finish(A, item, rope_d128_load(A, item));
+  const int heads_total = A.Hq + 2 * A.Hkv;
+  if (item >= (long)A.T_tokens * heads_total) return;
+  const int t = (int)(item / heads_total), head = (int)(item - (long)t * heads_total);
+  rope_d128_finish(A, t, head, rope_d128_load(A, t, head));
 }
