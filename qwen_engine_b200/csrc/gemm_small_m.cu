@@ -23,6 +23,17 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
   // waits for the one before it, whose output the token operand is.
   GsmChunk c0, c1;
   gsm_prefetch(w, N, K, k_per_warp, blockIdx.x, c0, c1);
+  {
+    // and L2 is asked for the rest of this CTA's 16 rows (one contiguous block), in pieces of 8 KB
+    const int rows = min(16, N - (int)blockIdx.x * 16);
+    const unsigned bytes = (unsigned)rows * (unsigned)K * 2u;
+    const unsigned off = threadIdx.x * 8192u;
+    if (off < bytes) {
+      const unsigned size = min(8192u, bytes - off);
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n"
+                   :: "l"(reinterpret_cast<const unsigned char*>(w + (size_t)blockIdx.x * 16 * K) + off), "r"(size) : "memory");
+    }
+  }
   pdl_launch_dependents();
   pdl_wait();
   gsm_cta<MT, TOut, XMODE, RESID>(x, w, out, M, N, K, k_per_warp, na, blockIdx.x, red, s_rstd, c0, c1);
