@@ -21,6 +21,8 @@ _lib = None
 
 ATTN_TILE_Q = 16        # queries per work item of the generic attention kernel
 SMALL_M_MAX = 64        # rows up to which the weight-streaming product is used
+SWAP_MIN_M = 17         # rows from which, up to SMALL_M_MAX, wide products go to the swapped tcgen05 kernel
+SWAP_MIN_N = 3072       # weight rows from which it has enough CTAs (one per 128) to pull the weights fast enough
 TCGEN05_ENABLED = True  # the tcgen05 product for more rows (False: the generic kernel serves them)
 FLASH_ROWS = 64         # rows (query token x query head of a group) per work item of the flash kernel
 FLASH_BN = 64           # keys per tile of the flash kernel
@@ -395,6 +397,11 @@ def linear(x, w: torch.Tensor, out: torch.Tensor) -> None:
     _need(out.shape == (M, N) and out.dtype in (x.dtype, torch.float32), "linear: out must be [M, N] in x's dtype or float32")
     _need(x.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "linear: operands must be contiguous")
     out_f32 = int(out.dtype == torch.float32)
+    if (x.dtype == torch.bfloat16 and SWAP_MIN_M <= M <= SMALL_M_MAX and N >= SWAP_MIN_N and K % 8 == 0
+            and TCGEN05_ENABLED and _program is None):
+        # some tens of rows and many weight rows: the weights on the 128-row side of tcgen05.mma
+        _check(lib().qe_linear_tcgen05_swap(_ptr(x), _ptr(w), _ptr(out), M, N, K, out_f32, _stream()), "linear")
+        return
     if x.dtype == torch.bfloat16 and M <= SMALL_M_MAX and K % 8 == 0:
         # a few rows: stream every weight once through the tensor cores
         if _record_gemm(x, w, out, M, N, K, 0, False, out_f32):
@@ -445,10 +452,11 @@ def tc_attention_status() -> int:
 
 
 def tcgen05_status() -> int:
-    """0 if no bounded wait of the tcgen05 product kernel ever ran out; else the code of the first
+    """0 if no bounded wait of the tcgen05 product kernels ever ran out; else the code of the first
     that did (1: a shared-memory slot never came free, 2: TMA bytes never landed, 3: the
-    accumulator never completed).  Synchronises the device."""
-    return int(lib().qe_gemm_tc_status())
+    accumulator never completed, 4: an accumulator was never read out; 11-13: the same as 1-3 in the
+    kernel for some tens of rows).  Synchronises the device."""
+    return int(lib().qe_gemm_tc_status()) or int(lib().qe_gemm_tc_swap_status())
 
 
 ROPE_TABLE_MIN_T = 64   # tokens from which a step's rotation angles are computed once (below: in the kernel)

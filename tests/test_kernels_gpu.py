@@ -90,11 +90,32 @@ def test_linear(dtype, M, N, K, out_f32):
     _close(got, want, odt, tol16=8e-3)
 
 
+@pytest.mark.parametrize("M", [17, 31, 48, 64])
+@pytest.mark.parametrize("N,K", [(3072, 64), (3080, 1024), (6144, 1032), (4100, 200)])
+@pytest.mark.parametrize("out_f32", [False, True])
+def test_linear_tcgen05_swapped(M, N, K, out_f32):
+    """Some tens of rows against many weight rows in bfloat16: the kernel with the weights on the
+    128-row side of the instruction; edges in M (not a multiple of 16), N and K."""
+    assert ops.SWAP_MIN_M <= M <= ops.SMALL_M_MAX and N >= ops.SWAP_MIN_N
+    x = _randn((M, K), torch.bfloat16, 18)
+    w = _randn((N, K), torch.bfloat16, 19, 0.1)
+    odt = torch.float32 if out_f32 else torch.bfloat16
+    want = torch.empty(M, N, dtype=odt)
+    ref_ops.linear(x, w, want)
+    got = torch.full((M, N), float("nan"), dtype=odt, device=DEV)
+    ops.linear(x.to(DEV), w.to(DEV), got)
+    torch.cuda.synchronize()
+    assert ops.tcgen05_status() == 0
+    _close(got, want, torch.bfloat16, scale=float(want.float().abs().max()))
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 128, 256), (65, 128, 64), (300, 200, 136), (2048, 4096, 1024),
-                                   (130, 1000, 3072), (257, 389 * 8, 80), (1000, 24, 2048), (128, 6144, 1024)])
+                                   (130, 1000, 3072), (257, 389 * 8, 80), (1000, 24, 2048), (128, 6144, 1024),
+                                   (2304, 4360, 192), (1280, 2568, 320)])
 @pytest.mark.parametrize("out_f32", [False, True])
 def test_linear_tcgen05(M, N, K, out_f32):
-    """More than 64 rows in bfloat16: the TMA + tcgen05 kernel, with edges in M, N and K."""
+    """More than 64 rows in bfloat16: the TMA + tcgen05 kernel, with edges in M, N and K; wide and
+    narrow tiles; up to three tiles per CTA, so that both accumulators and the ring wrap around."""
     x = _randn((M, K), torch.bfloat16, 16)
     w = _randn((N, K), torch.bfloat16, 17, 0.1)
     odt = torch.float32 if out_f32 else torch.bfloat16
