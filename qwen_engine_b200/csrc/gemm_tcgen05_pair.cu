@@ -1,0 +1,226 @@
+// out[M, N] = x[M, K] · w[N, K]^T in bfloat16 for many rows, by pairs of CTAs (tcgen05 cta_group::2):
+// two CTAs on neighbouring SMs share one 256 x BN output tile.  Each brings its own 128 rows of x and
+// only its half of the BN rows of w; one thread of the leading CTA issues MMAs that read both CTAs'
+// shared memory and write both CTAs' tensor memory.  An SM so fetches a quarter less (BN = 128) or a
+// third less (BN = 256) from L2 per multiply-add than alone with a 128 x BN tile, and what an SM can
+// pull from L2 is what bounds these products.  (Contract of the reference's linear,
+// src/layers/ops/linear.py:101-122.)
+//
+// Persistent: a cluster of two CTAs per pair of SMs walks over the tiles.  Per CTA 6 warps: warp 0
+// feeds TMA (its loads count their bytes on the leading CTA's `full` barrier), warp 1 owns tensor
+// memory (and, in the leading CTA, issues the MMAs), warps 2-5 read this CTA's 128 rows of the
+// accumulator and store them.  `empty` and `acc_full` are signalled to both CTAs by tcgen05.commit
+// with a CTA mask; `acc_empty` lives in the leading CTA and collects the epilogue warps of both.  No
+// TMA multicast.  Every wait on an mbarrier is bounded, as in gemm_tcgen05.cu.
+//
+// Needs K % 8 == 0 and 16-byte aligned bases (TMA strides); the launcher refuses the rest.
+#include "tcgen05.cuh"
+
+#define PR_BM 128               // rows of x per CTA (256 per pair)
+#define PR_BK 64
+#define PR_THREADS 192
+
+static __device__ int g_tc_status = 0;      // 0 = fine; else code of the first wait that ran out
+
+template <int BN, int STAGES>
+struct __align__(1024) PrSmem {
+  __nv_bfloat16 a[STAGES][PR_BM * PR_BK];            // 16 KB each
+  __nv_bfloat16 b[STAGES][(BN / 2) * PR_BK];         // this CTA's half of the tile's rows of w
+  uint64_t full[STAGES];                             // used in the leading CTA
+  uint64_t empty[STAGES];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];                             // used in the leading CTA
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <typename TOut, int BN, int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PR_THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                         TOut* __restrict__ out, int M, int N, int K) {
+  extern __shared__ unsigned char smem_raw[];
+  using Smem = PrSmem<BN, STAGES>;
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+  constexpr uint32_t STAGE_BYTES = (PR_BM + BN / 2) * PR_BK * sizeof(__nv_bfloat16);
+  pdl_launch_dependents();
+  pdl_wait();
+  Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();          // 0: the leading CTA of the pair
+  const int num_kb = (K + PR_BK - 1) / PR_BK;
+  const int n_blocks = (N + BN - 1) / BN;
+  const int n_tiles = n_blocks * ((M + 2 * PR_BM - 1) / (2 * PR_BM));
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  volatile int* abort_flag = &sm.abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&sm.acc_full[s], 1); mbar_init(&sm.acc_empty[s], 8); }
+    sm.abort_flag = 0;
+    mbar_init_fence();
+  }
+  if (warp == 1) tc_alloc_pair(&sm.tmem_base, TMEM_COLS);   // the same warp in both CTAs
+  tc_fence_before();
+  cluster_sync_all();                                // barriers and tensor memory of both CTAs are ready
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+
+  if (warp == 0) {
+    // ---- producer: this CTA's rows of x and its half of the rows of w; bytes counted in the leading CTA
+    if (lane == 0) {
+      uint32_t kc = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < n_tiles; tile += n_pairs) {
+        const int m0 = (tile / n_blocks) * 2 * PR_BM + (int)rank * PR_BM;
+        const int n0 = (tile % n_blocks) * BN + (int)rank * (BN / 2);
+        for (int kb = 0; kb < num_kb; ++kb, ++kc) {
+          const uint32_t s = kc % STAGES, round = kc / STAGES;
+          if (round > 0 && !mbar_wait(&sm.empty[s], (round - 1) & 1, abort_flag, 21, &g_tc_status)) { ok = false; break; }
+          if (rank == 0) mbar_expect_tx(&sm.full[s], 2 * STAGE_BYTES);     // both CTAs' bytes
+          const uint32_t full_addr = smem_u32(&sm.full[s]) & TC_PEER_BIT_MASK;
+          tma_load_2d_pair(sm.a[s], &map_x, full_addr, kb * PR_BK, m0);
+          tma_load_2d_pair(sm.b[s], &map_w, full_addr, kb * PR_BK, n0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer: one thread of the leading CTA ----------------------------------------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc(2 * PR_BM, BN);
+      uint32_t kc = 0;
+      bool ok = true;
+      int it = 0;
+      for (int tile = pair; ok && tile < n_tiles; tile += n_pairs, ++it) {
+        const int buf = it & 1;
+        if (it >= 2 && !mbar_wait(&sm.acc_empty[buf], ((it >> 1) - 1) & 1, abort_flag, 24, &g_tc_status)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t acc = tmem + buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++kc) {
+          const uint32_t s = kc % STAGES;
+          if (!mbar_wait(&sm.full[s], (kc / STAGES) & 1, abort_flag, 22, &g_tc_status)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t da = make_smem_desc(smem_u32(sm.a[s]));
+          const uint64_t db = make_smem_desc(smem_u32(sm.b[s]));
+#pragma unroll
+          for (int k = 0; k < PR_BK / 16; ++k) tc_mma_bf16_pair(acc, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+          tc_commit_pair(&sm.empty[s], 3);             // both CTAs' producers may refill the slot
+        }
+        if (ok) tc_commit_pair(&sm.acc_full[buf], 3);
+      }
+    }
+  } else {
+    // ---- epilogue: this CTA's 128 rows of the accumulator ----------------------------------------
+    const int quarter = warp & 3;
+    int it = 0;
+    for (int tile = pair; tile < n_tiles; tile += n_pairs, ++it) {
+      const int buf = it & 1;
+      const int m0 = (tile / n_blocks) * 2 * PR_BM + (int)rank * PR_BM, n0 = (tile % n_blocks) * BN;
+      const bool ok = __all_sync(0xffffffffu, mbar_wait(&sm.acc_full[buf], (it >> 1) & 1, abort_flag, 23, &g_tc_status));
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tc_ld_32x32b_x32(tmem + ((uint32_t)(quarter * 32) << 16) + buf * BN + c0, r);
+        tc_wait_ld();
+        if (c0 + 32 == BN) {
+          // the accumulator is in registers: tell the leading CTA's MMA thread
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(smem_u32(&sm.acc_empty[buf]) & TC_PEER_BIT_MASK);
+        }
+        if (row < M && n0 + c0 < N) {
+          TOut* dst = out + (size_t)row * N + n0 + c0;
+          if (n0 + c0 + 32 <= N && (N % 8) == 0) {
+            if constexpr (sizeof(TOut) == 2) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 v;
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                v.x = *reinterpret_cast<uint32_t*>(&p0); v.y = *reinterpret_cast<uint32_t*>(&p1);
+                v.z = *reinterpret_cast<uint32_t*>(&p2); v.w = *reinterpret_cast<uint32_t*>(&p3);
+                *reinterpret_cast<uint4*>(dst + j) = v;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                                  __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (n0 + c0 + j < N) dst[j] = from_f32<TOut>(__uint_as_float(r[j]));
+          }
+        }
+      }
+    }
+  }
+  // both CTAs meet here: neither leaves while the other may still signal its barriers, read its
+  // shared memory or write its tensor memory; then the allocating warps free the tensor memory
+  tc_fence_before();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tc_dealloc_pair(tmem, TMEM_COLS);
+  }
+}
+
+template <int BN, int STAGES>
+static int launch_pair(const void* x, const void* w, void* out, int M, int N, int K, int out_f32, int sms, cudaStream_t stream) {
+  CUtensorMap map_x, map_w;
+  {
+    const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    const uint64_t strides[1] = {(uint64_t)K * 2};
+    const uint32_t box[2] = {PR_BK, PR_BM};
+    if (!qe_tensor_map_bf16(x, 2, dims, strides, box, &map_x)) return 1;
+  }
+  {
+    const uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
+    const uint64_t strides[1] = {(uint64_t)K * 2};
+    const uint32_t box[2] = {PR_BK, BN / 2};
+    if (!qe_tensor_map_bf16(w, 2, dims, strides, box, &map_w)) return 1;
+  }
+  const size_t smem = sizeof(PrSmem<BN, STAGES>) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<__nv_bfloat16, BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<float, BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) QE_REFUSE("linear_tcgen05_pair: shared memory %zu: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  const long tiles = (long)((N + BN - 1) / BN) * ((M + 2 * PR_BM - 1) / (2 * PR_BM));
+  const long pairs = tiles < sms / 2 ? tiles : sms / 2;
+  const dim3 grid((unsigned)(2 * pairs));
+  if (out_f32)
+    qe_launch(gemm_tcgen05_pair_kernel<float, BN, STAGES>, grid, dim3(PR_THREADS), smem, stream, map_x, map_w, (float*)out, M, N, K);
+  else
+    qe_launch(gemm_tcgen05_pair_kernel<__nv_bfloat16, BN, STAGES>, grid, dim3(PR_THREADS), smem, stream, map_x, map_w, (__nv_bfloat16*)out, M, N, K);
+  QE_CHECK_LAUNCH("linear_tcgen05_pair");
+  return 0;
+}
+
+extern "C" int qe_gemm_tc_pair_status() {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int));
+  return v;
+}
+
+// Returns 0 when run, 1 when refused (qe_last_error says why), 2 on a launch error.
+extern "C" int qe_linear_tcgen05_pair(const void* x, const void* w, void* out, int M, int N, int K, int out_f32,
+                                      cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8) QE_REFUSE("linear_tcgen05_pair: K = %d is not a positive multiple of 8", K);
+  if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) QE_REFUSE("linear_tcgen05_pair: operands must be 16-byte aligned");
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (sms < 2) QE_REFUSE("linear_tcgen05_pair: needs at least two SMs");
+  // wide tiles when they give every pair of SMs a tile; else narrow ones
+  const long wide_tiles = (long)((N + 255) / 256) * ((M + 2 * PR_BM - 1) / (2 * PR_BM));
+  if (wide_tiles >= sms / 2) return launch_pair<256, 6>(x, w, out, M, N, K, out_f32, sms, stream);
+  return launch_pair<128, 8>(x, w, out, M, N, K, out_f32, sms, stream);
+}

@@ -116,6 +116,53 @@ __device__ __forceinline__ void tc_dealloc(uint32_t tmem, uint32_t cols) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" :: "r"(tmem), "r"(cols) : "memory");
 }
 
+// ---- CTA pairs (cta_group::2): two CTAs of a cluster, on neighbouring SMs, work on one tile -------------------
+// A shared-memory address of the odd CTA of a pair differs from the same offset in the even CTA by
+// this bit; with it cleared, an address names the even ("leading") CTA's copy.
+#define TC_PEER_BIT_MASK 0xFEFFFFFFu
+
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+  return r;
+}
+// all threads of all CTAs of the cluster
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// arrive on a barrier that may lie in the other CTA of the cluster (bar_addr: a shared::cluster address)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" :: "r"(bar_addr) : "memory");
+}
+// TMA tile load into this CTA's shared memory whose bytes are counted on a barrier of either CTA of the pair
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_addr, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+      :: "r"(smem_u32(dst)), "l"(map), "r"(bar_addr), "r"(c0), "r"(c1) : "memory");
+}
+// both CTAs of the pair execute these with the same arguments
+__device__ __forceinline__ void tc_alloc_pair(uint32_t* result_in_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n"
+               :: "r"(smem_u32(result_in_smem)), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tc_dealloc_pair(uint32_t tmem, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" :: "r"(tmem), "r"(cols) : "memory");
+}
+// issued by one thread of the leading CTA: D[tmem of both] (+)= A[256 rows: 128 of each CTA] · B[N: N/2 of each CTA]
+__device__ __forceinline__ void tc_mma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+      :: "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives on the barrier at this offset in every CTA of `cta_mask` when the pair's earlier MMAs have retired
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
+               :: "r"(smem_u32(bar)), "h"(cta_mask) : "memory");
+}
+
 // Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle (rows of 64 bfloat16 = 128
 // bytes, groups of 8 rows = 1024 bytes): start address, leading offset 1, stride offset 1024 bytes
 // (both in 16-byte units), descriptor version 1, layout type 2 (128-byte swizzle).

@@ -23,6 +23,8 @@ ATTN_TILE_Q = 16        # queries per work item of the generic attention kernel
 SMALL_M_MAX = 64        # rows up to which the weight-streaming product is used
 SWAP_MIN_M = 17         # rows from which, up to SMALL_M_MAX, wide products go to the swapped tcgen05 kernel
 SWAP_MIN_N = 3072       # weight rows from which it has enough CTAs (one per 128) to pull the weights fast enough
+TCGEN05_PAIRS = True    # CTA pairs for large products
+PAIR_MIN_TILES = 74     # 256 x 256 tiles from which they are used (one per pair of SMs)
 TCGEN05_ENABLED = True  # the tcgen05 product for more rows (False: the generic kernel serves them)
 FLASH_ROWS = 64         # rows (query token x query head of a group) per work item of the flash kernel
 FLASH_BN = 64           # keys per tile of the flash kernel
@@ -408,11 +410,29 @@ def linear(x, w: torch.Tensor, out: torch.Tensor) -> None:
             return
         _check(lib().qe_linear_small_m(_ptr(x), _ptr(w), _ptr(out), M, N, K, out_f32, _stream()), "linear")
         return
+    if (x.dtype == torch.bfloat16 and TCGEN05_PAIRS and TCGEN05_ENABLED and K % 8 == 0
+            and -(-M // 256) * -(-N // 256) >= PAIR_MIN_TILES):
+        # enough 256 x 256 tiles for every pair of SMs: pairs of CTAs share a tile (tcgen05 cta_group::2)
+        linear_pairs(x, w, out)
+        return
     if x.dtype == torch.bfloat16 and M > SMALL_M_MAX and K % 8 == 0 and TCGEN05_ENABLED:
         # many rows: TMA-fed tcgen05 tensor cores with the accumulator in tensor memory
         _check(lib().qe_linear_tcgen05(_ptr(x), _ptr(w), _ptr(out), M, N, K, out_f32, _stream()), "linear")
         return
     _check(lib().qe_linear_generic(_ptr(x), _ptr(w), _ptr(out), M, N, K, _dt(x), out_f32, _stream()), "linear")
+
+
+def linear_pairs(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """``linear`` in bfloat16 by the kernel in which two CTAs share a 256-row tile; any number of rows
+    (few tiles: 256 x 128 tiles; ``linear`` itself comes here only for large products)."""
+    M, K = x.shape
+    N = w.shape[0]
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape == (N, K) and K % 8 == 0,
+          "linear_pairs: bfloat16 operands with K a multiple of 8")
+    _need(out.shape == (M, N) and out.dtype in (torch.bfloat16, torch.float32), "linear_pairs: out must be [M, N]")
+    _need(x.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "linear_pairs: operands must be contiguous")
+    _check(lib().qe_linear_tcgen05_pair(_ptr(x), _ptr(w), _ptr(out), M, N, K, int(out.dtype == torch.float32), _stream()),
+           "linear_pairs")
 
 
 def linear_silu_mul(gate_up: torch.Tensor, w: torch.Tensor, out: torch.Tensor, scratch) -> None:
@@ -456,7 +476,7 @@ def tcgen05_status() -> int:
     that did (1: a shared-memory slot never came free, 2: TMA bytes never landed, 3: the
     accumulator never completed, 4: an accumulator was never read out; 11-13: the same as 1-3 in the
     kernel for some tens of rows).  Synchronises the device."""
-    return int(lib().qe_gemm_tc_status()) or int(lib().qe_gemm_tc_swap_status())
+    return int(lib().qe_gemm_tc_status()) or int(lib().qe_gemm_tc_swap_status()) or int(lib().qe_gemm_tc_pair_status())
 
 
 ROPE_TABLE_MIN_T = 64   # tokens from which a step's rotation angles are computed once (below: in the kernel)

@@ -90,6 +90,24 @@ def test_linear(dtype, M, N, K, out_f32):
     _close(got, want, odt, tol16=8e-3)
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 128, 64), (130, 72, 8), (300, 200, 136), (512, 256, 640), (2048, 1024, 2048),
+                                   (1000, 24, 2048), (2048, 4096, 1024), (2304, 4360, 192), (5000, 3000, 72)])
+@pytest.mark.parametrize("out_f32", [False, True])
+def test_linear_tcgen05_pairs(M, N, K, out_f32):
+    """Pairs of CTAs on one 256-row tile (cta_group::2): 256 x 128 tiles where tiles are few,
+    256 x 256 where they are many; edges in M, N and K; several tiles per pair of SMs."""
+    x = _randn((M, K), torch.bfloat16, 26)
+    w = _randn((N, K), torch.bfloat16, 27, 0.1)
+    odt = torch.float32 if out_f32 else torch.bfloat16
+    want = torch.empty(M, N, dtype=odt)
+    ref_ops.linear(x, w, want)
+    got = torch.full((M, N), float("nan"), dtype=odt, device=DEV)
+    ops.linear_pairs(x.to(DEV), w.to(DEV), got)
+    torch.cuda.synchronize()
+    assert ops.tcgen05_status() == 0
+    _close(got, want, torch.bfloat16, scale=float(want.float().abs().max()))
+
+
 @pytest.mark.parametrize("M", [17, 31, 48, 64])
 @pytest.mark.parametrize("N,K", [(3072, 64), (3080, 1024), (6144, 1032), (4100, 200)])
 @pytest.mark.parametrize("out_f32", [False, True])
