@@ -46,7 +46,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   using Smem = TcSmem<BN, STAGES>;
   constexpr uint32_t TMEM_COLS = 2 * BN;
   pdl_launch_dependents();
-  pdl_wait();
   Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = (K + TC_BK - 1) / TC_BK;
@@ -54,7 +53,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   const int n_tiles = n_blocks * ((M + TC_BM - 1) / TC_BM);
   volatile int* abort_flag = &sm.abort_flag;
 
+  // Everything up to the first load of x needs nothing from the kernel before this one (the weights
+  // are nobody's output): it runs before the wait for that kernel.
   if (threadIdx.x == 0) {
+    tma_prefetch_map(&map_x);
+    tma_prefetch_map(&map_w);
     for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
     for (int s = 0; s < 2; ++s) { mbar_init(&sm.acc_full[s], 1); mbar_init(&sm.acc_empty[s], 4); }
     sm.abort_flag = 0;
@@ -69,17 +72,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   if (warp == 0) {
     // ---- producer: TMA loads of the k-blocks of this CTA's tiles into the ring -------------------
     if (lane == 0) {
-      uint32_t kc = 0;                                    // k-blocks issued so far, over all tiles
-      bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-        const int m0 = (tile / n_blocks) * TC_BM, n0 = (tile % n_blocks) * BN;
-        for (int kb = 0; kb < num_kb; ++kb, ++kc) {
-          const uint32_t s = kc % STAGES, round = kc / STAGES;
-          if (round > 0 && !mbar_wait(&sm.empty[s], (round - 1) & 1, abort_flag, 1, &g_tc_status)) { ok = false; break; }
-          mbar_expect_tx(&sm.full[s], (TC_BM + BN) * TC_BK * sizeof(__nv_bfloat16));
-          tma_load_2d(sm.a[s], &map_x, &sm.full[s], kb * TC_BK, m0);
-          tma_load_2d(sm.b[s], &map_w, &sm.full[s], kb * TC_BK, n0);
-        }
+      const int my_tiles = (int)blockIdx.x < n_tiles ? (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+      const uint32_t total = (uint32_t)my_tiles * (uint32_t)num_kb;      // k-blocks of all this CTA's tiles
+      const uint32_t ahead = total < (uint32_t)STAGES ? total : (uint32_t)STAGES;
+      auto coords = [&](uint32_t kc, int& m0, int& n0, int& kb) {
+        const int t = (int)(kc / (uint32_t)num_kb);
+        kb = (int)(kc - (uint32_t)t * (uint32_t)num_kb);
+        const int tile = (int)blockIdx.x + t * (int)gridDim.x;
+        m0 = (tile / n_blocks) * TC_BM; n0 = (tile % n_blocks) * BN;
+      };
+      int m0, n0, kb;
+      // the ring's first round: the weights' tiles at once, x's after the wait for the kernel before
+      for (uint32_t kc = 0; kc < ahead; ++kc) {
+        coords(kc, m0, n0, kb);
+        mbar_expect_tx(&sm.full[kc], (TC_BM + BN) * TC_BK * sizeof(__nv_bfloat16));
+        tma_load_2d(sm.b[kc], &map_w, &sm.full[kc], kb * TC_BK, n0);
+      }
+      pdl_wait();
+      for (uint32_t kc = 0; kc < ahead; ++kc) {
+        coords(kc, m0, n0, kb);
+        tma_load_2d(sm.a[kc], &map_x, &sm.full[kc], kb * TC_BK, m0);
+      }
+      uint32_t kc = ahead;
+      for (; kc < total; ++kc) {
+        const uint32_t s = kc % STAGES, round = kc / STAGES;
+        if (!mbar_wait(&sm.empty[s], (round - 1) & 1, abort_flag, 1, &g_tc_status)) break;
+        coords(kc, m0, n0, kb);
+        mbar_expect_tx(&sm.full[s], (TC_BM + BN) * TC_BK * sizeof(__nv_bfloat16));
+        tma_load_2d(sm.a[s], &map_x, &sm.full[s], kb * TC_BK, m0);
+        tma_load_2d(sm.b[s], &map_w, &sm.full[s], kb * TC_BK, n0);
       }
       if (*abort_flag) {
         // giving up: let the copies that are still in flight land before the CTA leaves (bounded)
@@ -171,7 +192,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       }
     }
   }
-  // everyone meets here; the allocating warp frees the tensor memory
+  // everyone meets here (no thread leaves before the kernel before this one has completed); the
+  // allocating warp frees the tensor memory
+  pdl_wait();
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {

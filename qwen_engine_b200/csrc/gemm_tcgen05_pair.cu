@@ -43,7 +43,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   constexpr uint32_t TMEM_COLS = 2 * BN;
   constexpr uint32_t STAGE_BYTES = (PR_BM + BN / 2) * PR_BK * sizeof(__nv_bfloat16);
   pdl_launch_dependents();
-  pdl_wait();
   Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_cta_rank();          // 0: the leading CTA of the pair
@@ -53,7 +52,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   volatile int* abort_flag = &sm.abort_flag;
 
+  // Everything up to the first load of x needs nothing from the kernel before this one (the weights
+  // are nobody's output): it runs before the wait for that kernel.
   if (threadIdx.x == 0) {
+    tma_prefetch_map(&map_x);
+    tma_prefetch_map(&map_w);
     for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
     for (int s = 0; s < 2; ++s) { mbar_init(&sm.acc_full[s], 1); mbar_init(&sm.acc_empty[s], 8); }
     sm.abort_flag = 0;
@@ -68,19 +71,36 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   if (warp == 0) {
     // ---- producer: this CTA's rows of x and its half of the rows of w; bytes counted in the leading CTA
     if (lane == 0) {
-      uint32_t kc = 0;
-      bool ok = true;
-      for (int tile = pair; ok && tile < n_tiles; tile += n_pairs) {
-        const int m0 = (tile / n_blocks) * 2 * PR_BM + (int)rank * PR_BM;
-        const int n0 = (tile % n_blocks) * BN + (int)rank * (BN / 2);
-        for (int kb = 0; kb < num_kb; ++kb, ++kc) {
-          const uint32_t s = kc % STAGES, round = kc / STAGES;
-          if (round > 0 && !mbar_wait(&sm.empty[s], (round - 1) & 1, abort_flag, 21, &g_tc_status)) { ok = false; break; }
-          if (rank == 0) mbar_expect_tx(&sm.full[s], 2 * STAGE_BYTES);     // both CTAs' bytes
-          const uint32_t full_addr = smem_u32(&sm.full[s]) & TC_PEER_BIT_MASK;
-          tma_load_2d_pair(sm.a[s], &map_x, full_addr, kb * PR_BK, m0);
-          tma_load_2d_pair(sm.b[s], &map_w, full_addr, kb * PR_BK, n0);
-        }
+      const int my_tiles = pair < n_tiles ? (n_tiles - pair + n_pairs - 1) / n_pairs : 0;
+      const uint32_t total = (uint32_t)my_tiles * (uint32_t)num_kb;      // k-blocks of all this pair's tiles
+      const uint32_t ahead = total < (uint32_t)STAGES ? total : (uint32_t)STAGES;
+      auto coords = [&](uint32_t kc, int& m0, int& n0, int& kb) {
+        const int t = (int)(kc / (uint32_t)num_kb);
+        kb = (int)(kc - (uint32_t)t * (uint32_t)num_kb);
+        const int tile = pair + t * n_pairs;
+        m0 = (tile / n_blocks) * 2 * PR_BM + (int)rank * PR_BM;
+        n0 = (tile % n_blocks) * BN + (int)rank * (BN / 2);
+      };
+      int m0, n0, kb;
+      // the ring's first round: the weights' tiles at once, x's after the wait for the kernel before
+      for (uint32_t kc = 0; kc < ahead; ++kc) {
+        coords(kc, m0, n0, kb);
+        if (rank == 0) mbar_expect_tx(&sm.full[kc], 2 * STAGE_BYTES);    // both CTAs' bytes
+        tma_load_2d_pair(sm.b[kc], &map_w, smem_u32(&sm.full[kc]) & TC_PEER_BIT_MASK, kb * PR_BK, n0);
+      }
+      pdl_wait();
+      for (uint32_t kc = 0; kc < ahead; ++kc) {
+        coords(kc, m0, n0, kb);
+        tma_load_2d_pair(sm.a[kc], &map_x, smem_u32(&sm.full[kc]) & TC_PEER_BIT_MASK, kb * PR_BK, m0);
+      }
+      for (uint32_t kc = ahead; kc < total; ++kc) {
+        const uint32_t s = kc % STAGES, round = kc / STAGES;
+        if (!mbar_wait(&sm.empty[s], (round - 1) & 1, abort_flag, 21, &g_tc_status)) break;
+        coords(kc, m0, n0, kb);
+        if (rank == 0) mbar_expect_tx(&sm.full[s], 2 * STAGE_BYTES);
+        const uint32_t full_addr = smem_u32(&sm.full[s]) & TC_PEER_BIT_MASK;
+        tma_load_2d_pair(sm.a[s], &map_x, full_addr, kb * PR_BK, m0);
+        tma_load_2d_pair(sm.b[s], &map_w, full_addr, kb * PR_BK, n0);
       }
     }
   } else if (warp == 1) {
@@ -162,6 +182,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   }
   // both CTAs meet here: neither leaves while the other may still signal its barriers, read its
   // shared memory or write its tensor memory; then the allocating warps free the tensor memory
+  pdl_wait();                                        // no thread leaves before the kernel before this one has completed
   tc_fence_before();
   cluster_sync_all();
   if (warp == 1) {
