@@ -20,7 +20,7 @@ from typing import Optional, Sequence
 
 import torch
 
-from .page_pool import OutOfPages, PagePool
+from .page_pool import OutOfPages, PagePool, hash_block
 from .spec import CacheSpec, FixedStateSpec, PagedKVSpec
 from .state_slots import StateSlotPool
 
@@ -43,6 +43,9 @@ class CacheGroup:
         return self.cache_slots.index(cache_slot)
 
 
+UNKNOWN_TOKEN = -1      # stands for a token that a step takes from the device: its id is not known on the host yet
+
+
 @dataclass
 class RequestCache:
     """What one live request holds."""
@@ -57,6 +60,7 @@ class RequestCache:
     shared_tokens: int = 0                                # length found in the prefix table at open()
     fresh_state: bool = True                              # its state rows must be zeroed before its first step
     closed: bool = False
+    first_unknown: Optional[int] = None                   # position of a committed token whose id is not known yet
 
 
 class CacheManager:
@@ -238,19 +242,15 @@ class CacheManager:
         window has passed."""
         P = self.page_size
         old_len = rc.num_tokens
+        if rc.first_unknown is None and UNKNOWN_TOKEN in rc.pending_tokens:
+            rc.first_unknown = old_len + rc.pending_tokens.index(UNKNOWN_TOKEN)
         rc.tokens.extend(rc.pending_tokens)
         rc.num_tokens += len(rc.pending_tokens)
         rc.pending_tokens = []
         rc.fresh_state = False
+        self._register_full_pages(rc)
         for g in self.paged_groups:
             table = rc.tables[g.index]
-            if self.prefix_cache:
-                chain = rc.hashes[g.index]
-                # register in order so that the chain of parents is complete
-                for b in range(len(chain), rc.num_tokens // P):
-                    parent = chain[-1] if chain else 0
-                    chain.append(g.pool.register_full_page(table[b], parent,
-                                                           rc.tokens[b * P:(b + 1) * P]))
             window = g.spec.window
             if window is not None:
                 # the next query sits at position num_tokens and needs keys
@@ -263,6 +263,38 @@ class CacheManager:
                         table[b] = -1
                     b += 1
         del old_len
+
+    def _register_full_pages(self, rc: RequestCache) -> None:
+        """Make the request's full pages findable by their tokens, in order (so that the chain of
+        parents is complete), up to the first token whose id is not known yet."""
+        if not self.prefix_cache:
+            return
+        P = self.page_size
+        known = rc.num_tokens if rc.first_unknown is None else min(rc.num_tokens, rc.first_unknown)
+        for g in self.paged_groups:
+            table, chain = rc.tables[g.index], rc.hashes[g.index]
+            for b in range(len(chain), known // P):
+                parent = chain[-1] if chain else 0
+                if table[b] >= 0:
+                    chain.append(g.pool.register_full_page(table[b], parent, rc.tokens[b * P:(b + 1) * P]))
+                else:               # a window gave the page back before its tokens were known
+                    chain.append(hash_block(parent, rc.tokens[b * P:(b + 1) * P]))
+
+    def resolve_token(self, rc: RequestCache, position: int, token: int) -> None:
+        """The id of a token that was run before it was known on the host (a step launched ahead
+        took it from the device) is known now."""
+        if rc.closed:
+            return
+        if not (0 <= position < rc.num_tokens) or rc.tokens[position] != UNKNOWN_TOKEN:
+            raise RuntimeError(f"request {rc.req_id!r} has no unknown token at position {position}")
+        rc.tokens[position] = int(token)
+        if rc.first_unknown == position:
+            rc.first_unknown = None
+            for p in range(position + 1, rc.num_tokens):
+                if rc.tokens[p] == UNKNOWN_TOKEN:
+                    rc.first_unknown = p
+                    break
+        self._register_full_pages(rc)
 
     def abort_pending(self, rc: RequestCache) -> None:
         """Forget an append whose step did not run; the pages stay with the request."""

@@ -40,6 +40,7 @@ class EngineConfig:
     prefill_chunk_size: Optional[int] = None  # largest prompt portion; None: the budget
     enable_prefix_cache: bool = True
     use_cuda_graphs: bool = True
+    run_ahead: bool = True                # launch the next decode step before the host has read this one's tokens
     seed: int = 0
 
     def __post_init__(self) -> None:

@@ -477,3 +477,22 @@ extern "C" int qe_qk_norm_rope_kv_write(void* q, void* k, const void* v, long q_
   QE_CHECK_LAUNCH("qk_norm_rope_kv_write");
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------
+// dst[rows[i]] = src[src_index[i]]: token ids that the step before this one sampled and that the host
+// has not read yet are put into this step's token list on the device (a step launched ahead).
+// ---------------------------------------------------------------------------------------
+__global__ void place_tokens_kernel(int* __restrict__ dst, const int* __restrict__ rows, const int* __restrict__ src,
+                                    const int* __restrict__ src_index, int n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[rows[i]] = src[src_index[i]];
+}
+
+extern "C" int qe_place_tokens(int* dst, const int* rows, const int* src, const int* src_index, int n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  qe_launch(place_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, dst, rows, src, src_index, n);
+  QE_CHECK_LAUNCH("place_tokens");
+  return 0;
+}

@@ -16,9 +16,11 @@ from ..config import EngineConfig, ModelConfig, parse_dtype
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler, uniform_for
 from .loading import LoadedModel, load_model
+from ..cache.manager import UNKNOWN_TOKEN
+from ..sampling.sampler import SampledTokens
 from .runner import StepEntry
-from .scheduler import Scheduler, SchedulerOutput
-from .sequence import Sequence
+from .scheduler import ScheduledSeq, Scheduler, SchedulerOutput
+from .sequence import Sequence, SequenceStatus
 
 
 @dataclass
@@ -46,12 +48,30 @@ class EngineStats:
     step_seconds: float = 0.0
 
 
+@dataclass
+class _Flight:
+    """A step that is launched and whose sampled tokens the host has not read yet."""
+
+    out: SchedulerOutput
+    wanting: list                       # the scheduled requests that get a token, in the order of the logits' rows
+    tokens: Optional[SampledTokens]     # None: the step samples nothing (prompt portions only)
+    decode_tokens: int = 0
+    prefill_tokens: int = 0
+
+
 class LLMEngine:
     """The engine: a loaded model, its cache, a scheduler and a sampler.
 
     ``submit`` queues requests, ``step`` runs one scheduled batch, ``serving``
     runs until every queued request has ended (the reference's loop,
-    llm_engine.py:101-152)."""
+    llm_engine.py:101-152).
+
+    With ``EngineConfig.run_ahead`` a decode step is launched before the host has read the tokens of
+    the step before it: its token ids stay on the device, the requests' outputs hold a place for them
+    (``UNKNOWN_TOKEN``), and ``step`` returns what the older of the two steps produced.  A request
+    that turns out to have ended (a stop token) while the step launched ahead carried it loses that
+    step's token; one that ends by a count is known beforehand and is not carried.  Only steady
+    decoding runs ahead: nothing waiting, every running request getting a token, pages at hand."""
 
     def __init__(self, loaded: LoadedModel, engine_config: EngineConfig, tokenizer=None):
         self.loaded = loaded
@@ -66,6 +86,7 @@ class LLMEngine:
             engine_config.prefill_chunk_size, engine_config.max_model_len,
             eos_token_id=getattr(loaded.config, "eos_token_id", None))
         self._next_seq_id = 0
+        self._flight: Optional[_Flight] = None
         self.stats = EngineStats()
 
     # ---- intake -------------------------------------------------------------------------
@@ -101,36 +122,91 @@ class LLMEngine:
         return ids
 
     # ---- one step ---------------------------------------------------------------------
-    def step(self) -> list[Sequence]:
-        """Schedule, run and sample one batch; returns the requests that ended in it."""
-        t0 = time.perf_counter()
-        out: SchedulerOutput = self.scheduler.schedule()
+    def _launch(self, out: SchedulerOutput, before: Optional[_Flight]) -> Optional[_Flight]:
+        """Run and sample the scheduled batch without waiting for the device.  ``before``: the step
+        whose tokens are still on the device; requests whose newest token is a place for one of them
+        take it from there."""
         if not out.scheduled:
-            if self.scheduler.has_work():
-                raise RuntimeError("the scheduler found nothing to run although requests are pending")
-            return []
+            return None
+        source = {sch.seq.seq_id: i for i, sch in enumerate(before.wanting)} if before is not None else {}
         entries = []
+        flight = _Flight(out, [s for s in out.scheduled if s.wants_logits], None)
         for sch in out.scheduled:
             toks = sch.seq.get_tokens(sch.start, sch.num_tokens)
-            entries.append(StepEntry(sch.seq.cache, toks, [sch.num_tokens - 1] if sch.wants_logits else []))
-        logits = self.runner.step(entries)
-        sampled: dict[int, int] = {}
-        wanting = [s for s in out.scheduled if s.wants_logits]
-        if wanting:
-            params = [s.seq.sampling for s in wanting]
-            uniforms = [uniform_for(p.seed if p.seed is not None else self.config.seed, s.seq.seq_id,
-                                    s.seq.output_len) for p, s in zip(params, wanting)]
-            tokens = self.sampler.sample(logits, params, uniforms)
-            sampled = {s.seq.seq_id: t for s, t in zip(wanting, tokens)}
-        for sch in out.scheduled:
+            src = None
+            if toks and toks[-1] == UNKNOWN_TOKEN:
+                if len(toks) != 1 or sch.seq.seq_id not in source:
+                    raise RuntimeError(f"request {sch.seq.seq_id}: a token that is not known yet can only be run alone")
+                src = source[sch.seq.seq_id]
+            entries.append(StepEntry(sch.seq.cache, toks, [sch.num_tokens - 1] if sch.wants_logits else [], src))
             if sch.num_tokens == 1 and sch.seq.output_len > 0:
-                self.stats.decode_tokens += 1
+                flight.decode_tokens += 1
             else:
-                self.stats.prefill_tokens += sch.num_tokens
-        ended = self.scheduler.update(out, sampled)
+                flight.prefill_tokens += sch.num_tokens
+        device_tokens = before.tokens.device if (before is not None and before.tokens is not None) else None
+        logits = self.runner.step(entries, device_tokens=device_tokens)
+        if flight.wanting:
+            params = [s.seq.sampling for s in flight.wanting]
+            uniforms = [uniform_for(p.seed if p.seed is not None else self.config.seed, s.seq.seq_id,
+                                    s.seq.output_len) for p, s in zip(params, flight.wanting)]
+            flight.tokens = self.sampler.sample_async(logits, params, uniforms)
+        return flight
+
+    def _can_run_ahead(self, cur: _Flight) -> bool:
+        """Steady decoding: nothing waits, every running request gets a token from the step in
+        flight, and those that go on find their pages without anyone being preempted."""
+        sch = self.scheduler
+        if not self.config.run_ahead or sch.waiting or not cur.wanting or len(cur.wanting) != len(sch.running):
+            return False
+        if any(not s.wants_logits for s in cur.out.scheduled):
+            return False
+        need: dict[int, int] = {}
+        go_on = 0
+        for s in cur.wanting:
+            if s.seq.status is not SequenceStatus.RUNNING or s.seq.cache is None:
+                return False
+            if sch.ends_by_length_after(s.seq, 1):
+                continue
+            go_on += 1
+            for g, n in self.cache.pages_needed(s.seq.cache, 1).items():
+                need[g] = need.get(g, 0) + n
+        if go_on == 0:
+            return False
+        return all(n <= self.cache.groups[g].pool.num_free for g, n in need.items())
+
+    def step(self) -> list[Sequence]:
+        """Schedule, run and sample one batch; returns the requests that ended in the step whose
+        tokens were read (with ``run_ahead``, the step before the one just launched)."""
+        t0 = time.perf_counter()
+        if self._flight is None:
+            out: SchedulerOutput = self.scheduler.schedule()
+            if not out.scheduled:
+                if self.scheduler.has_work():
+                    raise RuntimeError("the scheduler found nothing to run although requests are pending")
+                return []
+            self._flight = self._launch(out, None)
+        cur, self._flight = self._flight, None
+        placed: Optional[dict[int, int]] = None
+        if self._can_run_ahead(cur):
+            placed = {}
+            for sch in cur.wanting:
+                seq = sch.seq
+                seq.hold = self.scheduler.ends_by_length_after(seq, 1)
+                placed[seq.seq_id] = seq.output_len
+                seq.output_token_ids.append(UNKNOWN_TOKEN)
+            ahead = self.scheduler.schedule()
+            if ahead.preempted or ahead.admitted:
+                raise RuntimeError("a step launched ahead must not preempt or admit")
+            self._flight = self._launch(ahead, cur)
+        sampled: dict[int, int] = {}
+        if cur.tokens is not None:
+            sampled = {s.seq.seq_id: t for s, t in zip(cur.wanting, cur.tokens.read())}
+        self.stats.decode_tokens += cur.decode_tokens
+        self.stats.prefill_tokens += cur.prefill_tokens
+        ended = self.scheduler.update(cur.out, sampled, placed)
         st = self.stats
         st.steps += 1
-        st.generated_tokens += len(sampled)
+        st.generated_tokens += sum(1 for s in cur.wanting if s.seq.seq_id in sampled)
         st.prefix_hit_tokens = self.scheduler.prefix_hit_tokens
         st.preemptions = self.scheduler.num_preemptions
         st.peak_pages_used = self.cache.peak_pages_used
@@ -139,7 +215,7 @@ class LLMEngine:
         return ended
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self._flight is not None or self.scheduler.has_work()
 
     def _output_of(self, seq: Sequence) -> RequestOutput:
         text = None

@@ -17,7 +17,7 @@ from typing import Optional, Sequence
 import torch
 
 from .. import ops
-from ..cache.manager import CacheManager, RequestCache
+from ..cache.manager import UNKNOWN_TOKEN, CacheManager, RequestCache
 from ..cache.page_pool import OutOfPages
 from ..models.decoder import DecoderModel
 from ..parts.base import Arena, GroupStepView, StepContext
@@ -31,6 +31,7 @@ class StepEntry:
     cache: RequestCache
     tokens: Sequence[int]
     want: Sequence[int] = field(default_factory=tuple)
+    token_source: Optional[int] = None      # tokens == [UNKNOWN_TOKEN]: index into the step's ``device_tokens``
 
 
 class _Pack:
@@ -169,10 +170,13 @@ class ModelRunner:
         return out
 
     # ---- the step -------------------------------------------------------------------------
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run one batch.  Returns float32 logits [wanted places, vocab] in the order
         of the entries and of each entry's ``want`` (None if nothing is wanted).
-        The tensor lives in the step's scratch memory: it is valid until the next step."""
+        The tensor lives in the step's scratch memory: it is valid until the next step.
+
+        An entry whose one token is ``UNKNOWN_TOKEN`` takes it from ``device_tokens[entry.token_source]``
+        (int32 on the device: what the step before sampled, not yet read by the host)."""
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return None
@@ -181,7 +185,10 @@ class ModelRunner:
         appended: list[RequestCache] = []
         try:
             for e in entries:
-                if not (0 <= min(e.tokens) and max(e.tokens) < vocab):
+                if e.token_source is not None:
+                    if device_tokens is None or list(e.tokens) != [UNKNOWN_TOKEN] or not (0 <= e.token_source < device_tokens.numel()):
+                        raise ValueError(f"request {e.cache.req_id!r}: a token taken from the device must be the entry's only one")
+                elif not (0 <= min(e.tokens) and max(e.tokens) < vocab):
                     bad = next(t for t in e.tokens if not (0 <= int(t) < vocab))
                     raise ValueError(f"token id {bad} of request {e.cache.req_id!r} is outside the vocabulary (0..{vocab - 1})")
                 end = e.cache.num_tokens + len(e.tokens)
@@ -199,6 +206,8 @@ class ModelRunner:
             raise
 
         token_ids: list[int] = []
+        fix_rows: list[int] = []                   # rows of token_ids to be filled on the device, and from where
+        fix_src: list[int] = []
         positions: list[int] = []
         cu_q = [0]
         ctx_lens: list[int] = []
@@ -209,7 +218,12 @@ class ModelRunner:
             rc = e.cache
             n, c = len(e.tokens), rc.num_tokens
             base = cu_q[-1]
-            token_ids.extend(map(int, e.tokens))
+            if e.token_source is not None:
+                fix_rows.append(base)
+                fix_src.append(e.token_source)
+                token_ids.append(0)
+            else:
+                token_ids.extend(map(int, e.tokens))
             positions.extend(range(c, c + n))
             cu_q.append(base + n)
             ctx_lens.append(c)
@@ -258,7 +272,12 @@ class ModelRunner:
                                   uniform_splits=uniform_splits)
         for name, values in plan.items():
             pack.add("plan_" + name, values)
+        if fix_rows:        # last, so that the places of everything a captured step reads stay where they are
+            pack.add("fix_rows", fix_rows)
+            pack.add("fix_src", fix_src)
         dev = self._upload(pack)
+        if fix_rows:
+            ops.place_tokens(dev["token_ids"], dev["fix_rows"], device_tokens, dev["fix_src"])
 
         cache.run_page_copies()
         cache.zero_fresh_state([e.cache for e in entries])

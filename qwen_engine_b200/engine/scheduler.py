@@ -23,7 +23,7 @@ from collections import deque
 from dataclasses import dataclass, field
 from typing import Optional
 
-from ..cache.manager import CacheManager
+from ..cache.manager import UNKNOWN_TOKEN, CacheManager
 from ..cache.page_pool import OutOfPages
 from ..cache.state_slots import OutOfSlots
 from .sequence import Sequence, SequenceStatus
@@ -101,6 +101,8 @@ class Scheduler:
         for seq in order:
             if seq.status is not SequenceStatus.RUNNING:
                 continue                                  # preempted a moment ago
+            if seq.hold or seq.num_remaining_tokens <= 0:
+                continue                                  # nothing to run until its token is known
             if budget <= 0:
                 break
             n = min(seq.num_remaining_tokens, self.prefill_chunk_size, budget)
@@ -184,15 +186,36 @@ class Scheduler:
             return "length"
         return None
 
-    def update(self, out: SchedulerOutput, new_tokens: dict[int, int]) -> list[Sequence]:
+    def ends_by_length_after(self, seq: Sequence, more: int) -> bool:
+        """Whether the request ends by a count once it has ``more`` more output tokens, whatever they are."""
+        return (seq.output_len + more >= seq.sampling.max_new_tokens
+                or seq.total_len + more >= self.max_model_len)
+
+    def update(self, out: SchedulerOutput, new_tokens: dict[int, int],
+               placed: Optional[dict[int, int]] = None) -> list[Sequence]:
         """Take in the step's sampled tokens (seq_id -> token); returns the requests that ended.
-        Their pages and slots go back at once."""
+        Their pages and slots go back at once.
+
+        ``placed`` (seq_id -> index in its output tokens): requests whose token of this step already
+        has a place, holding ``UNKNOWN_TOKEN``, because a step was launched ahead with it; the token
+        goes there (and into the cache's record of the request) instead of being appended.  A
+        request that ended while a step launched ahead still carried it is passed over."""
         ended = []
         for sch in out.scheduled:
             seq = sch.seq
-            if not sch.wants_logits:
+            if not sch.wants_logits or seq.status is SequenceStatus.FINISHED:
                 continue
-            seq.output_token_ids.append(int(new_tokens[seq.seq_id]))
+            token = int(new_tokens[seq.seq_id])
+            if placed is not None and seq.seq_id in placed:
+                idx = placed[seq.seq_id]
+                if seq.output_token_ids[idx] != UNKNOWN_TOKEN or idx != seq.output_len - 1:
+                    raise RuntimeError(f"request {seq.seq_id}: no place is waiting for its token")
+                seq.output_token_ids[idx] = token
+                if seq.cache is not None and seq.cache.num_tokens > seq.prompt_len + idx:
+                    self.cache.resolve_token(seq.cache, seq.prompt_len + idx, token)
+            else:
+                seq.output_token_ids.append(token)
+            seq.hold = False
             reason = self.finish_reason_for(seq)
             if reason is not None:
                 seq.finish_reason = reason

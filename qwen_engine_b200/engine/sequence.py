@@ -32,6 +32,7 @@ class Sequence:
     admit_order: int = -1            # larger: admitted later (the first to be preempted)
     num_preemptions: int = 0
     shared_prefix_len: int = 0       # tokens found in the cache at the last admission
+    hold: bool = False               # not to be scheduled: its last token is on its way and it ends with it
 
     @property
     def prompt_len(self) -> int:

@@ -751,6 +751,15 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
         Hq, Hkv, D, int(kv_pages.shape[3]), _dt(qkv), _stream()), "paged_attention")
 
 
+def place_tokens(token_ids: torch.Tensor, rows: torch.Tensor, src: torch.Tensor, src_index: torch.Tensor) -> None:
+    """token_ids[rows[i]] = src[src_index[i]], all int32 on the device."""
+    for t, name in ((token_ids, "token_ids"), (rows, "rows"), (src, "src"), (src_index, "src_index")):
+        _i32(t, name)
+    _need(rows.numel() == src_index.numel(), "place_tokens: one source index per row")
+    _check(lib().qe_place_tokens(_ptr(token_ids), _ptr(rows), _ptr(src), _ptr(src_index), rows.numel(), _stream()),
+           "place_tokens")
+
+
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
     T, I2 = gate_up.shape

@@ -31,6 +31,27 @@ def uniform_for(seed: int, request_index: int, position: int) -> float:
     return (h >> 40) / float(1 << 24)
 
 
+class SampledTokens:
+    """The tokens of one sampling call: on the device at once (``device``, int32 [N]), on the host
+    when ``read()`` is called (their copy to pinned memory is queued right behind the sampling)."""
+
+    def __init__(self, device_tokens: torch.Tensor):
+        self.device = device_tokens
+        self._host = None
+        self._event = None
+        if device_tokens.is_cuda:
+            self._host = torch.empty(device_tokens.shape, dtype=device_tokens.dtype, pin_memory=True)
+            self._host.copy_(device_tokens, non_blocking=True)
+            self._event = torch.cuda.Event()
+            self._event.record()
+
+    def read(self) -> list[int]:
+        if self._host is None:
+            return self.device.tolist()
+        self._event.synchronize()
+        return self._host.tolist()
+
+
 class Sampler:
     def __init__(self, device):
         self.device = torch.device(device)
@@ -38,6 +59,11 @@ class Sampler:
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams],
                uniforms: Sequence[float]) -> list[int]:
         """One token per row of float32 logits [N, V]; returns host ints."""
+        return self.sample_async(logits, params, uniforms).read()
+
+    def sample_async(self, logits: torch.Tensor, params: Sequence[SamplingParams],
+                     uniforms: Sequence[float]) -> SampledTokens:
+        """The same without waiting for the device."""
         N = logits.shape[0]
         assert N == len(params) == len(uniforms)
         out = torch.empty(N, dtype=torch.int32, device=self.device)
@@ -50,4 +76,4 @@ class Sampler:
                 meta = meta.pin_memory().to(self.device, non_blocking=True)
                 topk = topk.pin_memory().to(self.device, non_blocking=True)
             ops.sample(logits, meta[0].contiguous(), topk, meta[1].contiguous(), out)
-        return out.tolist()
+        return SampledTokens(out)

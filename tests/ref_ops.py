@@ -63,6 +63,10 @@ def _rotate(x, positions, inv_freq, rotary_dim):
     return torch.cat([c * x1 - s * x2, s * x1 + c * x2, x[..., rotary_dim:]], dim=-1)
 
 
+def place_tokens(token_ids, rows, src, src_index):
+    token_ids[rows.long()] = src[src_index.long()]
+
+
 def rope_table(positions, inv_freq, out):
     ang = positions.to(torch.float32)[:, None] * inv_freq[None, :]
     out[..., 0], out[..., 1] = torch.cos(ang), torch.sin(ang)
@@ -189,7 +193,7 @@ def sample(logits, temperature, top_k, uniform, out):
 
 
 _NAMES = ["prepare_matrix", "embedding", "add_rmsnorm", "add_rmsnorm_rows", "linear",
-          "qk_norm_rope_kv_write", "rope_neox", "rope_table", "plan_attention", "paged_attention", "silu_mul", "linear_silu_mul",
+          "qk_norm_rope_kv_write", "rope_neox", "rope_table", "place_tokens", "plan_attention", "paged_attention", "silu_mul", "linear_silu_mul",
           "argmax", "sample"]
 
 

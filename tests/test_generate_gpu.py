@@ -98,6 +98,47 @@ def test_preemption_on_the_gpu(model_folders):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_steps_launched_ahead_change_nothing_on_the_gpu(model_folders, dtype):
+    """run_ahead (a decode step launched before the host has read the tokens of the step before it,
+    which it takes from the device) against the step-by-step engine: the same tokens and finish
+    reasons for requests that end by a count and by a stop token, replayed decode steps included."""
+    from qwen_engine_b200.sampling import SamplingParams as SP
+    name = "tiny-b"
+    folder = model_folders[name]
+    V = helpers.vocab_of(name)
+    prompts = [random_tokens(V, n, 130 + n) for n in (6, 19, 4, 33)]
+    lengths = [7, 30, 12, 24]
+    first = {}
+    results = {}
+    for ahead in (False, True):
+        eng = helpers.make_engine(folder, name, dtype, run_ahead=ahead, max_model_len=96)
+        for i, (p, n) in enumerate(zip(prompts, lengths)):
+            stops = (first[i][5],) if (ahead and i in (1, 3)) else ()
+            eng.add_request(p, SP(max_new_tokens=n, stop_token_ids=stops, ignore_eos=True,
+                                  temperature=0.7 if i == 2 else 0.0, top_k=8 if i == 2 else 0, seed=3))
+        launched_ahead = 0
+        done = []
+        while eng.has_work():
+            done.extend(eng.step())
+            launched_ahead += eng._flight is not None
+        assert (launched_ahead > 0) == ahead
+        assert eng.cache.pages_in_use() == 0
+        eng.cache.check_invariants()
+        results[ahead] = {s.seq_id: (list(s.output_token_ids), s.finish_reason) for s in done}
+        if not ahead:
+            first = {i: results[False][i][0] for i in range(len(prompts))}
+    for i, n in enumerate(lengths):
+        want, reason = results[False][i]
+        assert reason == "length" and len(want) == n
+        got, got_reason = results[True][i]
+        if i in (1, 3):
+            cut = want.index(want[5]) + 1
+            assert got == want[:cut] and got_reason == "stop"
+        else:
+            assert got == want and got_reason == "length"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_long_decoding(model_folders, dtype):
     """400 tokens decoded one by one after a short prompt (teacher-forced, so that both dtypes
     walk the same path); logits compared every 25 steps and at the end."""

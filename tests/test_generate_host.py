@@ -66,6 +66,50 @@ def test_preemption_does_not_change_the_tokens(model_folders, cpu_ops):
     assert eng.cache.pages_in_use() == 0
 
 
+@pytest.mark.parametrize("prefix_cache", [False, True])
+def test_steps_launched_ahead_change_nothing(model_folders, cpu_ops, prefix_cache):
+    """With run_ahead a decode step is launched before the host has read the step before it.  The
+    outputs, finish reasons and final page counts are those of the step-by-step engine: requests of
+    different lengths that end by a count (known beforehand, not carried along) and by a stop token
+    (found out one step late: the token of the step launched ahead is dropped); pages of 4 tokens fill
+    up and are registered for sharing while a token's id is still on the device."""
+    name = "tiny-a"
+    folder = model_folders[name]
+    V = helpers.vocab_of(name)
+    prompts = [random_tokens(V, n, 120 + n) for n in (6, 9, 4, 11)]
+    lengths = [5, 12, 9, 16]
+    results = {}
+    for ahead in (False, True):
+        eng = make_engine(folder, name, F32, device="cpu", run_ahead=ahead, enable_prefix_cache=prefix_cache,
+                          max_model_len=64)
+        # the stop token of each request: what the plain implementation produces at its 4th step
+        # (for the last request none: it ends by the count)
+        ids = []
+        for i, (p, n) in enumerate(zip(prompts, lengths)):
+            plain = _plain_greedy(folder, p, n)
+            stops = (plain[3],) if i in (1, 2) else ()
+            ids.append(eng.add_request(p, SamplingParams(max_new_tokens=n, stop_token_ids=stops, ignore_eos=True)))
+        launched_ahead = 0
+        done = []
+        while eng.has_work():
+            done.extend(eng.step())
+            launched_ahead += eng._flight is not None
+        eng.cache.check_invariants()
+        assert eng.cache.pages_in_use() == 0
+        assert (launched_ahead > 0) == ahead
+        results[ahead] = {s.seq_id: (list(s.output_token_ids), s.finish_reason) for s in done}
+        assert len(done) == len(prompts)
+    assert results[True] == results[False]
+    for i, (p, n) in enumerate(zip(prompts, lengths)):
+        toks, reason = results[True][i]
+        plain = _plain_greedy(folder, p, n)
+        if i in (1, 2):
+            cut = plain.index(plain[3]) + 1
+            assert toks == plain[:cut] and reason == "stop"
+        else:
+            assert toks == plain and reason == "length"
+
+
 def test_uniform_numbers_are_a_function_of_seed_request_and_position():
     assert uniform_for(1, 2, 3) == uniform_for(1, 2, 3)
     vals = {uniform_for(s, r, p) for s in range(3) for r in range(3) for p in range(3)}
