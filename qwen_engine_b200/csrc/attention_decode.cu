@@ -1,0 +1,341 @@
+// Attention of decoded tokens over the paged cache in bfloat16, head size 128, for a few query rows
+// per kv head (one token x the query heads of the group): the latency-bound case of the reference's
+// flash decoding (src/layers/fused_ops/attn.py:374-594).  With so few rows the tensor cores have
+// nothing to do; what matters is that a CTA's keys and values are all on their way at once and that
+// nothing stands between them and the arithmetic.  So: no matrix instructions, no tile pipeline.
+//
+// One CTA (256 threads) serves one work item (a request's rows, a range of its keys) and one kv head;
+// it walks its keys in chunks of 160.  Per chunk:
+//   keys    8 lanes share a key (16 elements each, two 16-byte loads into registers), 32 keys per
+//           pass, 5 passes; dot products with the rows' queries in float32, summed over the 8 lanes
+//           by shuffles; scores (scaled to base 2, masked) go to shared memory;
+//   values  the chunk's values are copied to shared memory with cp.async (one buffer ahead), issued
+//           together with the keys' loads;
+//   softmax a warp per row: running max and sum, P in shared memory (float32: P is not rounded to
+//           bfloat16 here, which is closer to the exact result than attn.py:263);
+//   P·V     a warp takes every 8th key, a lane 4 elements of the head; float32 accumulators, rescaled
+//           when the max moves; the 8 warps' sums meet in shared memory at the end.
+// The loads of chunk c + 1 are issued before the softmax of chunk c.
+//
+// Work items, parts and the merge by the CTA that finishes a request's last part are those of the
+// mma.sync kernel (attention_flash.cuh): same item layout, same scratch layout, same counters.
+#include "attention_flash.cuh"
+
+#define AD_THREADS 256
+#define AD_CH 160               // keys per chunk: 5 passes of 32
+#define AD_PASSES (AD_CH / 32)
+#define AD_D 128
+
+template <int R>
+struct AdSmem {
+  __nv_bfloat16 v[2][AD_CH * AD_D];     // 40 KB each
+  float sc[R][AD_CH];                   // scores, then P
+  float red[8][R][AD_D];                // the warps' accumulators at the end
+  float m_run[R], l_run[R], alpha[R];
+  int tab[2][AD_CH + 2];                // pages of a chunk's keys (one entry per page the chunk touches)
+  int last;
+};
+
+__device__ __forceinline__ float2 ad_bf2(uint32_t u) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u));
+}
+
+// R: rows (query token x head of the group) a CTA holds at most: 1, 2 or 4
+template <int R>
+__global__ void __launch_bounds__(AD_THREADS, 2)
+decode_attention_kernel(FaArgs A) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  AdSmem<R>& sm = *reinterpret_cast<AdSmem<R>*>(smem_raw);
+  constexpr int D = AD_D;
+  pdl_launch_dependents();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int hkv = blockIdx.y;
+  const int Hq = A.Hq, Hkv = A.Hkv, window = A.window, page_size = A.page_size;
+  const int G = Hq / Hkv;
+
+  // the work lists come from the host's copy, not from a kernel
+  const int* it = A.items + (size_t)blockIdx.x * FA_ITEM_INTS;
+  const int req = it[0], q0 = it[1], part = it[4], n_splits = it[5], split = it[6];
+  int kv_lo = it[2], kv_hi_item = it[3];
+  const int row0 = it[7], q_len = it[8], ctx = it[9];
+  const int ntok = min(FA_BM / G, q_len - q0);
+  const int nrows = min(ntok * G, R);               // the launcher promised nrows <= R
+  const int first_pos = ctx + q0;
+  if (n_splits > 0) {
+    const int total = ctx + q_len;
+    const int lo = window > 0 ? max(0, ctx - window + 1) / FA_BN * FA_BN : 0;
+    const int per = ((total - lo + n_splits - 1) / n_splits + FA_BN - 1) / FA_BN * FA_BN;
+    kv_lo = lo + split * per;
+    kv_hi_item = min(total, kv_lo + per);
+  }
+  const int kv_end = min(kv_hi_item, first_pos + ntok);
+  int kv_begin = max(kv_lo, 0);
+  if (window > 0) kv_begin = max(kv_begin, first_pos - window + 1);
+  const int n_chunks = kv_end > kv_begin ? (kv_end - kv_begin + AD_CH - 1) / AD_CH : 0;
+
+  const int* table = A.block_tables + (size_t)req * A.max_blocks;
+  const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
+  const size_t page_stride = (size_t)2 * Hkv * page_size * D;
+  const size_t v_off = (size_t)Hkv * page_size * D;
+  const __nv_bfloat16* head_base = A.pages + (size_t)hkv * page_size * D;
+
+  // pages of chunk c's keys into tab[c & 1]: entry e is the page of block (first block of the chunk) + e
+  auto load_table = [&](int c) {
+    const int k0 = kv_begin + c * AD_CH;
+    const int b0 = page_shift >= 0 ? k0 >> page_shift : k0 / page_size;
+    const int k1 = min(k0 + AD_CH, kv_end) - 1;
+    const int b1 = page_shift >= 0 ? k1 >> page_shift : k1 / page_size;
+    for (int e = tid; e <= b1 - b0; e += AD_THREADS) sm.tab[c & 1][e] = table[b0 + e];
+  };
+  // address of key j's row of this head in the cache (K; + v_off for V)
+  auto row_of = [&](int c, int j) -> const __nv_bfloat16* {
+    const int k0 = kv_begin + c * AD_CH;
+    int blk, off, b0;
+    if (page_shift >= 0) { blk = j >> page_shift; off = j & (page_size - 1); b0 = k0 >> page_shift; }
+    else { blk = j / page_size; off = j - blk * page_size; b0 = k0 / page_size; }
+    return head_base + (size_t)sm.tab[c & 1][blk - b0] * page_stride + (size_t)off * D;
+  };
+
+  // ---- per-thread roles --------------------------------------------------------------------------
+  const int gi = tid >> 3, sub = tid & 7;           // keys: 8 lanes per key, 16 elements each
+  uint4 kreg[AD_PASSES][2];
+  auto issue_keys = [&](int c) {
+    const int k0 = kv_begin + c * AD_CH;
+#pragma unroll
+    for (int p = 0; p < AD_PASSES; ++p) {
+      const int j = k0 + p * 32 + gi;
+      if (j < kv_end) {
+        const uint4* src = reinterpret_cast<const uint4*>(row_of(c, j) + sub * 16);
+        kreg[p][0] = __ldcg(src);
+        kreg[p][1] = __ldcg(src + 1);
+      } else {
+        kreg[p][0] = kreg[p][1] = make_uint4(0, 0, 0, 0);
+      }
+    }
+  };
+  auto issue_values = [&](int c) {
+    const int k0 = kv_begin + c * AD_CH;
+    __nv_bfloat16* dst = sm.v[c & 1];
+    const int ch = tid & (D / 8 - 1);                // this thread's 16-byte piece of a row; 16 rows per turn
+#pragma unroll
+    for (int kc = tid / (D / 8); kc < AD_CH; kc += AD_THREADS / (D / 8)) {
+      const int j = k0 + kc;
+      if (j < kv_end) cp_async16(dst + kc * D + ch * 8, row_of(c, j) + v_off + ch * 8);
+      else *reinterpret_cast<uint4*>(dst + kc * D + ch * 8) = make_uint4(0, 0, 0, 0);
+    }
+    cp_async_commit();
+  };
+
+  if (n_chunks > 0) load_table(0);
+  if (tid < R) { sm.m_run[tid] = -INFINITY; sm.l_run[tid] = 0.f; sm.alpha[tid] = 1.f; }
+  if (tid == 0) sm.last = 0;
+  pdl_wait();                                       // q and the new token's key and value: the previous kernels' outputs
+  __syncthreads();
+
+  // this thread's 16 elements of every row's query: in float32 for up to 2 rows (converted once),
+  // else as packed bfloat16 (converted at every use: registers are the tighter resource then)
+  constexpr bool QF32 = R <= 2;
+  float2 qf[QF32 ? R : 1][8];
+  uint32_t qreg[QF32 ? 1 : R][8];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    uint32_t w8[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+    if (r < nrows) {
+      const int ti = r / G, hg = r - ti * G;
+      const uint4* src = reinterpret_cast<const uint4*>(A.q + (size_t)(row0 + q0 + ti) * A.q_stride +
+                                                        (size_t)(hkv * G + hg) * D + sub * 16);
+      const uint4 a = __ldcg(src), b = __ldcg(src + 1);
+      w8[0] = a.x; w8[1] = a.y; w8[2] = a.z; w8[3] = a.w; w8[4] = b.x; w8[5] = b.y; w8[6] = b.z; w8[7] = b.w;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if constexpr (QF32) qf[r][i] = ad_bf2(w8[i]); else qreg[r][i] = w8[i];
+    }
+  }
+  if (n_chunks > 0) { issue_values(0); issue_keys(0); }
+
+  float o[R][4];                                    // P·V: this warp's keys, this lane's 4 elements
+#pragma unroll
+  for (int r = 0; r < R; ++r) { o[r][0] = o[r][1] = o[r][2] = o[r][3] = 0.f; }
+
+  for (int c = 0; c < n_chunks; ++c) {
+    const int k0 = kv_begin + c * AD_CH;
+    const int clen = min(AD_CH, kv_end - k0);
+    if (c + 1 < n_chunks) load_table(c + 1);        // needed after the next barrier
+    // ---- scores of the chunk ---------------------------------------------------------------------
+#pragma unroll
+    for (int p = 0; p < AD_PASSES; ++p) {
+      const uint32_t kw[8] = {kreg[p][0].x, kreg[p][0].y, kreg[p][0].z, kreg[p][0].w,
+                              kreg[p][1].x, kreg[p][1].y, kreg[p][1].z, kreg[p][1].w};
+      float dot[R];
+#pragma unroll
+      for (int r = 0; r < R; ++r) dot[r] = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float2 kf = ad_bf2(kw[i]);
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          float2 q2;
+          if constexpr (QF32) q2 = qf[r][i]; else q2 = ad_bf2(qreg[r][i]);
+          dot[r] = fmaf(q2.x, kf.x, dot[r]);
+          dot[r] = fmaf(q2.y, kf.y, dot[r]);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        dot[r] += __shfl_xor_sync(0xffffffffu, dot[r], 4);
+        dot[r] += __shfl_xor_sync(0xffffffffu, dot[r], 2);
+        dot[r] += __shfl_xor_sync(0xffffffffu, dot[r], 1);
+      }
+      if (sub == 0) {
+        const int kc = p * 32 + gi, j = k0 + kc;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const int pos = first_pos + r / G;
+          const bool ok = r < nrows && j < kv_end && j <= pos && (window <= 0 || j > pos - window);
+          sm.sc[r][kc] = ok ? dot[r] * A.scale_log2 : -INFINITY;
+        }
+      }
+    }
+    __syncthreads();                                // scores written; the next chunk's pages known
+    if (c + 1 < n_chunks) { issue_values(c + 1); issue_keys(c + 1); }
+    // ---- softmax: a warp per row --------------------------------------------------------------------
+    for (int r = warp; r < R; r += AD_THREADS / 32) {
+      float s[AD_PASSES];
+      float mx = -INFINITY;
+#pragma unroll
+      for (int p = 0; p < AD_PASSES; ++p) { s[p] = sm.sc[r][p * 32 + lane]; mx = fmaxf(mx, s[p]); }
+      mx = warp_max(mx);
+      const float m_old = sm.m_run[r];
+      const float m_new = fmaxf(m_old, mx);
+      const float base = m_new == -INFINITY ? 0.f : m_new;
+      float sum = 0.f;
+#pragma unroll
+      for (int p = 0; p < AD_PASSES; ++p) {
+        const float pv = exp2f(s[p] - base);
+        sm.sc[r][p * 32 + lane] = pv;
+        sum += pv;
+      }
+      sum = warp_sum(sum);
+      if (lane == 0) {
+        const float al = exp2f(m_old - base);       // 0 when nothing was allowed before
+        sm.alpha[r] = al;
+        sm.l_run[r] = sm.l_run[r] * al + sum;
+        sm.m_run[r] = m_new;
+      }
+    }
+    if (c + 1 < n_chunks) cp_async_wait<1>(); else cp_async_wait<0>();   // this chunk's values have landed
+    __syncthreads();                                // P, alpha and everybody's copies are visible
+    // ---- P·V ----------------------------------------------------------------------------------------------
+    {
+      float al[R];
+#pragma unroll
+      for (int r = 0; r < R; ++r) { al[r] = sm.alpha[r]; o[r][0] *= al[r]; o[r][1] *= al[r]; o[r][2] *= al[r]; o[r][3] *= al[r]; }
+      const __nv_bfloat16* vb = sm.v[c & 1];
+      for (int kc = warp; kc < clen; kc += AD_THREADS / 32) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(vb + kc * D + 4 * lane);
+        const float2 v01 = ad_bf2(raw.x), v23 = ad_bf2(raw.y);
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const float pv = sm.sc[r][kc];
+          o[r][0] = fmaf(pv, v01.x, o[r][0]); o[r][1] = fmaf(pv, v01.y, o[r][1]);
+          o[r][2] = fmaf(pv, v23.x, o[r][2]); o[r][3] = fmaf(pv, v23.y, o[r][3]);
+        }
+      }
+    }
+    __syncthreads();                                // the scores' and this value buffer's readers are done
+  }
+
+  // ---- the 8 warps' sums meet --------------------------------------------------------------------------
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+    *reinterpret_cast<float4*>(&sm.red[warp][r][4 * lane]) = make_float4(o[r][0], o[r][1], o[r][2], o[r][3]);
+  __syncthreads();
+  __nv_bfloat16* out_row0 = A.out + (size_t)(row0 + q0) * ((size_t)Hq * D);
+  for (int e = tid; e < nrows * D; e += AD_THREADS) {
+    const int r = e / D, d = e - r * D;
+    float acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < AD_THREADS / 32; ++w) acc += sm.red[w][r][d];
+    const float l = sm.l_run[r];
+    if (part < 0) {
+      const int ti = r / G, hg = r - ti * G;
+      out_row0[(size_t)ti * ((size_t)Hq * D) + (size_t)(hkv * G + hg) * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    } else {
+      const size_t slot = ((size_t)part * Hkv + hkv) * A.part_rows + r;
+      A.part_acc[slot * D + d] = acc;
+      if (d == 0) { A.part_ml[2 * slot] = sm.m_run[r]; A.part_ml[2 * slot + 1] = l; }
+    }
+  }
+  // ---- the CTA that finishes a request's last part combines the parts ---------------------------------
+  if (part >= 0 && A.counters != nullptr && n_splits > 0) {
+    const int first = part - split;
+    __threadfence();                                // this CTA's part is visible before it is counted
+    __syncthreads();
+    if (tid == 0) {
+      const int done = atomicAdd(&A.counters[first * Hkv + hkv], 1);
+      sm.last = (done == n_splits - 1);
+      if (sm.last) A.counters[first * Hkv + hkv] = 0;        // ready for the next launch
+    }
+    __syncthreads();
+    if (sm.last) {
+      __threadfence();
+      // out = sum_s 2^(m_s - m) acc_s / sum_s 2^(m_s - m) l_s, in float32, in the order of the parts
+      for (int e = tid; e < nrows * D; e += AD_THREADS) {
+        const int r = e / D, d = e - r * D;
+        float m = -INFINITY;
+        for (int sp = 0; sp < n_splits; ++sp)
+          m = fmaxf(m, __ldcg(A.part_ml + 2 * ((((size_t)first + sp) * Hkv + hkv) * A.part_rows + r)));
+        const float mb = m == -INFINITY ? 0.f : m;
+        float l = 0.f, acc = 0.f;
+        for (int sp = 0; sp < n_splits; ++sp) {
+          const size_t slot = (((size_t)first + sp) * Hkv + hkv) * A.part_rows + r;
+          const float wgt = exp2f(__ldcg(A.part_ml + 2 * slot) - mb);
+          l += wgt * __ldcg(A.part_ml + 2 * slot + 1);
+          acc += wgt * __ldcg(A.part_acc + slot * D + d);
+        }
+        const int ti = r / G, hg = r - ti * G;
+        out_row0[(size_t)ti * ((size_t)Hq * D) + (size_t)(hkv * G + hg) * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+      }
+    }
+  }
+}
+
+template <int R>
+static int launch_decode(const FaArgs& fa, int n_items, int Hkv, cudaStream_t stream) {
+  const size_t smem = sizeof(AdSmem<R>);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) QE_REFUSE("decode_attention: shared memory %zu: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  qe_launch(decode_attention_kernel<R>, dim3(n_items, Hkv), dim3(AD_THREADS), smem, stream, fa);
+  QE_CHECK_LAUNCH("decode_attention");
+  return 0;
+}
+
+// Whether the kernel takes this geometry with at most max_rows rows (token x head of the group) per item.
+extern "C" int qe_decode_attention_supported(int Hq, int Hkv, int D, int max_rows) {
+  return (D == AD_D && Hkv >= 1 && Hkv <= 65535 && Hq % Hkv == 0 && max_rows >= 1 && max_rows <= 4) ? 1 : 0;
+}
+
+// Same arguments as qe_flash_attention_fused_merge's (attention_flash.cu) where they share a name;
+// every item has at most max_rows rows; parts are combined by the CTA that finishes last (counters
+// as there).  Returns 0 when run, 1 when refused, 2 on a launch error.
+extern "C" int qe_decode_attention(const void* q, long q_stride, const void* pages, const int* block_tables,
+                                   int max_blocks, const int* items, int n_items, void* out, float* part_acc,
+                                   float* part_ml, int part_rows, int* counters, int max_rows, float scale, int window,
+                                   int Hq, int Hkv, int D, int page_size, cudaStream_t stream) {
+  if (n_items <= 0) return 0;
+  if (!qe_decode_attention_supported(Hq, Hkv, D, max_rows))
+    QE_REFUSE("decode_attention: heads %d/%d, head_dim %d, %d rows are not supported", Hq, Hkv, D, max_rows);
+  if ((((uintptr_t)q | (uintptr_t)pages) & 15) || (q_stride % 8)) QE_REFUSE("decode_attention: operands must be 16-byte aligned");
+  if (part_acc && counters == nullptr) QE_REFUSE("decode_attention: parts need the counters");
+  FaArgs fa{(const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pages, block_tables, max_blocks, items,
+            (__nv_bfloat16*)out, part_acc, part_ml, part_rows, counters, scale * 1.4426950408889634f, window, Hq, Hkv,
+            page_size};
+  if (max_rows <= 1) return launch_decode<1>(fa, n_items, Hkv, stream);
+  if (max_rows <= 2) return launch_decode<2>(fa, n_items, Hkv, stream);
+  return launch_decode<4>(fa, n_items, Hkv, stream);
+}

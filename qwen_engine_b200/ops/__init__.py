@@ -31,6 +31,10 @@ FLASH_BN = 64           # keys per tile of the flash kernel
 FLASH_ITEM_INTS = 12    # int32 per work item of the flash kernel
 FLASH_SPLIT = 256       # keys per part when a decoded token's context is split (reference attn.py:605)
 FLASH_TARGET_CTAS = 296  # two CTAs per SM: long contexts are split into as many parts as fit in one wave
+DECODE_ATTENTION = True         # decoded tokens (few rows per kv head, head size 128): the kernel made for them
+DECODE_ATTENTION_MAX_ROWS = 4   # rows (token x head of the group) per item up to which it is used
+DECODE_ATTENTION_MAX_KEYS = 512 # context up to which it serves contexts that are not split (longer: the pipelined kernel)
+DECODE_ATTENTION_MIN_CTAS = 128 # CTAs from which it is used: measured, it gains where the GPU is full and loses a little below
 TC_ROWS = 256           # rows per work item of the tcgen05 attention kernel (two halves of 128)
 TC_BN = 128             # keys per step of the tcgen05 attention kernel
 TC_MIN_ROWS = 65        # rows of a request's portion from which the tcgen05 kernel serves it
@@ -601,7 +605,7 @@ def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
     ``geometries``: the (heads, kv heads, head size, window) of the model's attention layers.
     ``tiles`` serves the generic kernel; for each geometry the flash kernel takes, ``fa<i>_items``
     and ``fa<i>_merge`` hold its work and merge items and ``fa<i>_info`` = [parts, rows per part,
-    whether every item has at most 16 rows]; requests that bring many rows go to the tcgen05 kernel
+    whether every item has at most 16 rows, the most rows of an item]; requests that bring many rows go to the tcgen05 kernel
     instead where it takes the geometry: ``tc<i>_items`` and ``tc<i>_info`` = [parts, rows per part].
     ``uniform_splits`` (geometry -> number of parts) fixes the number of parts of every request,
     so that the lists depend on the batch's shape only (for steps replayed from a CUDA graph)."""
@@ -657,7 +661,7 @@ def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
         items = [x for _, item in whole for x in item] + items
         plan[f"fa{gi}_items"] = items
         plan[f"fa{gi}_merge"] = merge
-        plan[f"fa{gi}_info"] = [n_parts, part_rows, int(max_rows <= 16)]
+        plan[f"fa{gi}_info"] = [n_parts, part_rows, int(max_rows <= 16), max_rows]
         if tc_tiles:
             tc_items, tc_parts = _plan_tc_tiles(tc_tiles, Hkv)
             plan[f"tc{gi}_items"] = tc_items
@@ -723,7 +727,7 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
             Hq, Hkv, D, int(kv_pages.shape[3]), _stream()), "flash_attention_tc")
     if key is not None and f"fa{key}_items" in plan:
         items, merge = plan[f"fa{key}_items"], plan[f"fa{key}_merge"]
-        n_parts, part_rows, small_tiles = plan[f"fa{key}_info_host"]
+        n_parts, part_rows, small_tiles, max_rows = plan[f"fa{key}_info_host"]
         n_items, n_merge = items.numel() // FLASH_ITEM_INTS, merge.numel() // 4
         part_acc = part_ml = None
         if n_parts:
@@ -736,6 +740,17 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
                          ints=[n_items, Hkv, Hq, int(kv_pages.shape[3]), int(block_tables.shape[1]), int(part_rows), int(window)],
                          floats=[scale * 1.4426950408889634], longs=[qkv.stride(0)],
                          ptrs=[qkv, kv_pages, block_tables, items, out, part_acc, part_ml, counters])
+            return
+        if (DECODE_ATTENTION and 1 <= max_rows <= DECODE_ATTENTION_MAX_ROWS and D == 128 and n_items > 0
+                and (n_parts == 0 or counters is not None) and qkv.stride(0) % 8 == 0
+                and n_items * Hkv >= DECODE_ATTENTION_MIN_CTAS
+                and (n_parts > 0 or max(getattr(ctx, "ctx_lens_host", None) or [0]) <= DECODE_ATTENTION_MAX_KEYS)):
+            # a few rows per kv head (decoded tokens): the kernel without matrix instructions
+            _check(lib().qe_decode_attention(
+                _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(block_tables), int(block_tables.shape[1]),
+                _ptr(items), n_items, _ptr(out), _ptr(part_acc), _ptr(part_ml), int(part_rows), _ptr(counters),
+                int(max_rows), ctypes.c_float(scale), int(window), Hq, Hkv, D, int(kv_pages.shape[3]), _stream()),
+                "decode_attention")
             return
         _check(lib().qe_flash_attention_fused_merge(
             _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(block_tables), int(block_tables.shape[1]),

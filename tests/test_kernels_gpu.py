@@ -344,6 +344,56 @@ def test_flash_attention_split_contexts(Hq, Hkv, D, P, q_lens, ctx_lens):
     _close(got, want, dtype)
 
 
+@pytest.mark.parametrize("Hq,Hkv,P", [(16, 8, 16), (4, 4, 8), (8, 2, 32), (4, 1, 16), (6, 3, 4), (2, 1, 256)])
+@pytest.mark.parametrize("q_lens,ctx_lens", [([1], [77]), ([1, 1, 1], [5, 130, 333]), ([1] * 8, [1024] * 8),
+                                             ([1, 1], [257, 2000]), ([1, 1, 1, 1], [0, 159, 160, 161]),
+                                             ([1], [5000])])
+@pytest.mark.parametrize("window", [0, 100])
+def test_decode_attention(Hq, Hkv, P, q_lens, ctx_lens, window):
+    """Decoded tokens, head size 128: the kernel without matrix instructions (few rows per kv head),
+    with chunks of 160 keys, split contexts merged by the last CTA, and a window; against the plain
+    reference, and against the mma.sync kernel that serves the same items when it is switched off."""
+    D, dtype = 128, torch.bfloat16
+    plan = ops.plan_attention(list(q_lens), list(ctx_lens), P, ((Hq, Hkv, D, window),), dtype)
+    assert 1 <= plan["fa0_info"][3] <= ops.DECODE_ATTENTION_MAX_ROWS
+    case = _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, seed=41)
+    want = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ref_ops.paged_attention, "cpu")
+    launches = ops.launch_count
+    saved = ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_KEYS
+    ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_KEYS = 1, 1 << 30     # whatever the size of the case
+    try:
+        got = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ops.paged_attention, DEV)
+        _close(got, want, dtype)
+        ops.DECODE_ATTENTION = False
+        other = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ops.paged_attention, DEV)
+    finally:
+        ops.DECODE_ATTENTION = True
+        ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_KEYS = saved
+    _close(other, want, dtype)
+    assert ops.launch_count == launches + 2
+
+
+@pytest.mark.parametrize("key_pos", [0, 15, 16, 159, 160, 161, 255, 256, 700, 899])
+def test_decode_attention_far_key_stands_out(key_pos):
+    """One key among hundreds carries almost all the weight: the output must be its value.  A kernel
+    that misses a page, a chunk or a part would return something else."""
+    Hq, Hkv, D, P = 4, 2, 128, 16
+    dtype = torch.bfloat16
+    q_lens, ctx_lens = [1, 1], [900, 760]
+    saved = ops.DECODE_ATTENTION_MIN_CTAS
+    ops.DECODE_ATTENTION_MIN_CTAS = 1
+    try:
+        for r, head in ((0, 1), (1, 2)):
+            if key_pos > ctx_lens[r]:
+                continue
+            case = _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, seed=42, spike=(r, key_pos, head))
+            got = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, ops.paged_attention, DEV)
+            want = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, ref_ops.paged_attention, "cpu")
+            _close(got, want, dtype)
+    finally:
+        ops.DECODE_ATTENTION_MIN_CTAS = saved
+
+
 TC_SHAPES = [(16, 8, 128, 16), (4, 4, 128, 8), (8, 1, 128, 32), (4, 2, 128, 128), (2, 1, 128, 256)]
 TC_BATCHES = [
     ([300], [0]),                         # a whole prompt: several tiles, the diagonal inside a step
