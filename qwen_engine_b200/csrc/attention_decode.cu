@@ -19,21 +19,39 @@
 //
 // Work items, parts and the merge by the CTA that finishes a request's last part are those of the
 // mma.sync kernel (attention_flash.cuh): same item layout, same scratch layout, same counters.
+//
+// FUSE: the kernel takes q, k and v as the QKV product left them and does what the rotary kernel
+// would have done in between (elementwise.cu, rope_d128.cuh: per-head RMS norm of q and k, rotation
+// of both by position x inverse frequency, the new keys and values into the cache), with the same
+// arithmetic and the same rounding of q and k to bfloat16: a launch less per layer in a decode step.
+// Every CTA norms and rotates its rows' queries; the CTA whose keys include a new token's position
+// norms and rotates that token's key, writes it and the value into the cache, and uses its own copy.
 #include "attention_flash.cuh"
+#include <stddef.h>
 
 #define AD_THREADS 256
 #define AD_CH 160               // keys per chunk: 5 passes of 32
 #define AD_PASSES (AD_CH / 32)
 #define AD_D 128
 
+struct AdFuse {
+  const __nv_bfloat16* k; const __nv_bfloat16* v;   // the step's keys and values [T, Hkv, 128], strides as q's
+  const float* qw; const float* kw; float eps;      // norm weights (null: no norm)
+  const float* inv_freq;                            // [64]
+  __nv_bfloat16* pages_out;                         // the cache, to be written (null: this layer reads another's)
+};
+
 template <int R>
 struct AdSmem {
-  __nv_bfloat16 v[2][AD_CH * AD_D];     // 40 KB each
+  // (members that are read or written 8 or 16 bytes at a time are aligned for it whatever R is)
+  alignas(16) __nv_bfloat16 v[2][AD_CH * AD_D];     // 40 KB each
   float sc[R][AD_CH];                   // scores, then P
-  float red[8][R][AD_D];                // the warps' accumulators at the end
+  alignas(16) float red[8][R][AD_D];    // the warps' accumulators at the end
   float m_run[R], l_run[R], alpha[R];
   int tab[2][AD_CH + 2];                // pages of a chunk's keys (one entry per page the chunk touches)
   int last;
+  alignas(16) float2 cs[R][64];         // FUSE: (cos, sin) of the rows' tokens' angles
+  alignas(16) __nv_bfloat16 knew[R][AD_D];   // FUSE: the new tokens' keys after norm and rotation
 };
 
 __device__ __forceinline__ float2 ad_bf2(uint32_t u) {
@@ -41,9 +59,36 @@ __device__ __forceinline__ float2 ad_bf2(uint32_t u) {
 }
 
 // R: rows (query token x head of the group) a CTA holds at most: 1, 2 or 4
-template <int R>
+// x: 16 consecutive elements (from 16 sub on) of a head's 128, held by 8 lanes; norm over the head,
+// rotation of the pairs (d, d + 64) by the angles in cs, the result rounded to bfloat16 as the
+// rotary kernel rounds it
+__device__ __forceinline__ void ad_norm_rotate(float (&x)[16], const float* w, float eps, const float2* cs, int sub) {
+  if (w) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) ss += x[i] * x[i];
+    ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+    const float rstd = rsqrtf(ss / (float)AD_D + eps);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) x[i] = x[i] * rstd * w[sub * 16 + i];
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float partner = __shfl_xor_sync(0xffffffffu, x[i], 4);      // element d +- 64
+    const float2 c = cs[(sub & 3) * 16 + i];
+    x[i] = sub < 4 ? c.x * x[i] - c.y * partner : c.y * partner + c.x * x[i];
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) x[i] = __bfloat162float(__float2bfloat16_rn(x[i]));
+}
+
+template <int R, bool FUSE>
 __global__ void __launch_bounds__(AD_THREADS, 2)
-decode_attention_kernel(FaArgs A) {
+decode_attention_kernel(FaArgs A, AdFuse F) {
+  static_assert(offsetof(AdSmem<R>, knew) % 16 == 0 && offsetof(AdSmem<R>, red) % 16 == 0 && offsetof(AdSmem<R>, cs) % 8 == 0,
+                "vector accesses to shared memory need their alignment");
   extern __shared__ __align__(16) unsigned char smem_raw[];
   AdSmem<R>& sm = *reinterpret_cast<AdSmem<R>*>(smem_raw);
   constexpr int D = AD_D;
@@ -72,6 +117,10 @@ decode_attention_kernel(FaArgs A) {
   int kv_begin = max(kv_lo, 0);
   if (window > 0) kv_begin = max(kv_begin, first_pos - window + 1);
   const int n_chunks = kv_end > kv_begin ? (kv_end - kv_begin + AD_CH - 1) / AD_CH : 0;
+  // FUSE: this CTA's keys include the new tokens' positions (they lie together at the end of the
+  // request, and parts are cut at multiples of 64 keys while a tile holds at most 64 / G tokens; a
+  // tile whose tokens straddle two parts is not launched with FUSE)
+  const bool own_new = FUSE && F.pages_out != nullptr && kv_begin <= first_pos && kv_end >= first_pos + ntok;
 
   const int* table = A.block_tables + (size_t)req * A.max_blocks;
   const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
@@ -120,7 +169,9 @@ decode_attention_kernel(FaArgs A) {
 #pragma unroll
     for (int kc = tid / (D / 8); kc < AD_CH; kc += AD_THREADS / (D / 8)) {
       const int j = k0 + kc;
-      if (j < kv_end) cp_async16(dst + kc * D + ch * 8, row_of(c, j) + v_off + ch * 8);
+      if (FUSE && own_new && j >= first_pos && j < kv_end)
+        cp_async16(dst + kc * D + ch * 8, F.v + (size_t)(row0 + q0 + (j - first_pos)) * A.q_stride + (size_t)hkv * D + ch * 8);
+      else if (j < kv_end) cp_async16(dst + kc * D + ch * 8, row_of(c, j) + v_off + ch * 8);
       else *reinterpret_cast<uint4*>(dst + kc * D + ch * 8) = make_uint4(0, 0, 0, 0);
     }
     cp_async_commit();
@@ -131,7 +182,51 @@ decode_attention_kernel(FaArgs A) {
   if (tid == 0) sm.last = 0;
   pdl_wait();                                       // q and the new token's key and value: the previous kernels' outputs
   __syncthreads();
+  // the first chunk's keys and values are on their way before anything else is done
+  if (n_chunks > 0) { issue_values(0); issue_keys(0); }
 
+  if constexpr (FUSE) {
+    // the angles of the tile's tokens, one (cos, sin) per thread
+    for (int e = tid; e < ntok * 64; e += AD_THREADS) {
+      const int t = e >> 6, jf = e & 63;
+      float sn, cs;
+      sincosf((float)(first_pos + t) * F.inv_freq[jf], &sn, &cs);
+      sm.cs[t][jf] = make_float2(cs, sn);
+    }
+    __syncthreads();
+    // the new tokens' keys and values: group t of 8 lanes takes token t (whole warps take part in the
+    // shuffles: a group without a token works on the last token and writes nothing)
+    if (own_new && warp * 4 < ntok) {
+      const bool mine = gi < ntok;
+      const int tk = mine ? gi : ntok - 1;
+      const size_t tok = (size_t)(row0 + q0 + tk) * A.q_stride + (size_t)hkv * D + sub * 16;
+      const uint4 ka = __ldcg(reinterpret_cast<const uint4*>(F.k + tok)), kb = __ldcg(reinterpret_cast<const uint4*>(F.k + tok) + 1);
+      const uint32_t kraw[8] = {ka.x, ka.y, ka.z, ka.w, kb.x, kb.y, kb.z, kb.w};
+      float x[16];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { const float2 f2 = ad_bf2(kraw[i]); x[2 * i] = f2.x; x[2 * i + 1] = f2.y; }
+      ad_norm_rotate(x, F.kw, F.eps, sm.cs[tk], sub);
+      if (mine) {
+        uint32_t kout[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) kout[i] = pack_bf16(x[2 * i], x[2 * i + 1]);
+        const uint4 o0 = make_uint4(kout[0], kout[1], kout[2], kout[3]), o1 = make_uint4(kout[4], kout[5], kout[6], kout[7]);
+        *reinterpret_cast<uint4*>(&sm.knew[tk][sub * 16]) = o0;
+        *(reinterpret_cast<uint4*>(&sm.knew[tk][sub * 16]) + 1) = o1;
+        // into the cache, for the steps to come: page of the position from the block table
+        const int pos = first_pos + tk;
+        const int blk = page_shift >= 0 ? pos >> page_shift : pos / page_size;
+        const int off = pos - blk * page_size;
+        __nv_bfloat16* row = F.pages_out + (size_t)table[blk] * page_stride + (size_t)hkv * page_size * D + (size_t)off * D + sub * 16;
+        *reinterpret_cast<uint4*>(row) = o0;
+        *(reinterpret_cast<uint4*>(row) + 1) = o1;
+        const uint4* vsrc = reinterpret_cast<const uint4*>(F.v + tok);
+        *reinterpret_cast<uint4*>(row + v_off) = __ldcg(vsrc);
+        *(reinterpret_cast<uint4*>(row + v_off) + 1) = __ldcg(vsrc + 1);
+      }
+    }
+    __syncthreads();
+  }
   // this thread's 16 elements of every row's query: in float32 for up to 2 rows (converted once),
   // else as packed bfloat16 (converted at every use: registers are the tighter resource then)
   constexpr bool QF32 = R <= 2;
@@ -146,13 +241,20 @@ decode_attention_kernel(FaArgs A) {
                                                         (size_t)(hkv * G + hg) * D + sub * 16);
       const uint4 a = __ldcg(src), b = __ldcg(src + 1);
       w8[0] = a.x; w8[1] = a.y; w8[2] = a.z; w8[3] = a.w; w8[4] = b.x; w8[5] = b.y; w8[6] = b.z; w8[7] = b.w;
+      if constexpr (FUSE) {
+        float x[16];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { const float2 f2 = ad_bf2(w8[i]); x[2 * i] = f2.x; x[2 * i + 1] = f2.y; }
+        ad_norm_rotate(x, F.qw, F.eps, sm.cs[ti], sub);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w8[i] = pack_bf16(x[2 * i], x[2 * i + 1]);
+      }
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       if constexpr (QF32) qf[r][i] = ad_bf2(w8[i]); else qreg[r][i] = w8[i];
     }
   }
-  if (n_chunks > 0) { issue_values(0); issue_keys(0); }
 
   float o[R][4];                                    // P·V: this warp's keys, this lane's 4 elements
 #pragma unroll
@@ -165,8 +267,17 @@ decode_attention_kernel(FaArgs A) {
     // ---- scores of the chunk ---------------------------------------------------------------------
 #pragma unroll
     for (int p = 0; p < AD_PASSES; ++p) {
-      const uint32_t kw[8] = {kreg[p][0].x, kreg[p][0].y, kreg[p][0].z, kreg[p][0].w,
-                              kreg[p][1].x, kreg[p][1].y, kreg[p][1].z, kreg[p][1].w};
+      uint32_t kw[8] = {kreg[p][0].x, kreg[p][0].y, kreg[p][0].z, kreg[p][0].w,
+                        kreg[p][1].x, kreg[p][1].y, kreg[p][1].z, kreg[p][1].w};
+      if constexpr (FUSE) {
+        // a new token's key: this CTA's own copy (its write to the cache may not be visible yet)
+        const int j = k0 + p * 32 + gi;
+        if (own_new && j >= first_pos && j < kv_end) {
+          const uint4* src = reinterpret_cast<const uint4*>(&sm.knew[j - first_pos][sub * 16]);
+          const uint4 a = src[0], b = src[1];
+          kw[0] = a.x; kw[1] = a.y; kw[2] = a.z; kw[3] = a.w; kw[4] = b.x; kw[5] = b.y; kw[6] = b.z; kw[7] = b.w;
+        }
+      }
       float dot[R];
 #pragma unroll
       for (int r = 0; r < R; ++r) dot[r] = 0.f;
@@ -301,16 +412,16 @@ decode_attention_kernel(FaArgs A) {
   }
 }
 
-template <int R>
-static int launch_decode(const FaArgs& fa, int n_items, int Hkv, cudaStream_t stream) {
+template <int R, bool FUSE>
+static int launch_decode(const FaArgs& fa, const AdFuse& fu, int n_items, int Hkv, cudaStream_t stream) {
   const size_t smem = sizeof(AdSmem<R>);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<R, FUSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) QE_REFUSE("decode_attention: shared memory %zu: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  qe_launch(decode_attention_kernel<R>, dim3(n_items, Hkv), dim3(AD_THREADS), smem, stream, fa);
+  qe_launch(decode_attention_kernel<R, FUSE>, dim3(n_items, Hkv), dim3(AD_THREADS), smem, stream, fa, fu);
   QE_CHECK_LAUNCH("decode_attention");
   return 0;
 }
@@ -335,7 +446,34 @@ extern "C" int qe_decode_attention(const void* q, long q_stride, const void* pag
   FaArgs fa{(const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pages, block_tables, max_blocks, items,
             (__nv_bfloat16*)out, part_acc, part_ml, part_rows, counters, scale * 1.4426950408889634f, window, Hq, Hkv,
             page_size};
-  if (max_rows <= 1) return launch_decode<1>(fa, n_items, Hkv, stream);
-  if (max_rows <= 2) return launch_decode<2>(fa, n_items, Hkv, stream);
-  return launch_decode<4>(fa, n_items, Hkv, stream);
+  const AdFuse none{};
+  if (max_rows <= 1) return launch_decode<1, false>(fa, none, n_items, Hkv, stream);
+  if (max_rows <= 2) return launch_decode<2, false>(fa, none, n_items, Hkv, stream);
+  return launch_decode<4, false>(fa, none, n_items, Hkv, stream);
+}
+
+// The same with the per-head norm, the rotation and the cache write of the step's q, k, v done here
+// (see FUSE above).  qkv: the QKV product's output [T, (Hq + 2 Hkv) 128] as it left the product; qw, kw:
+// norm weights [128] or null; inv_freq [64]; write_kv 0: a layer that reads another layer's cache (its
+// keys are there already; only the queries are normed and rotated).  Every item must hold one token.
+extern "C" int qe_decode_attention_fused(const void* qkv, long q_stride, void* pages, const int* block_tables,
+                                         int max_blocks, const int* items, int n_items, void* out, float* part_acc,
+                                         float* part_ml, int part_rows, int* counters, int max_rows, float scale,
+                                         int window, const float* qw, const float* kw, float eps, const float* inv_freq,
+                                         int write_kv, int Hq, int Hkv, int D, int page_size, cudaStream_t stream) {
+  if (n_items <= 0) return 0;
+  if (!qe_decode_attention_supported(Hq, Hkv, D, max_rows) || max_rows > Hq / Hkv)
+    QE_REFUSE("decode_attention_fused: heads %d/%d, head_dim %d, %d rows are not supported", Hq, Hkv, D, max_rows);
+  if ((((uintptr_t)qkv | (uintptr_t)pages | (uintptr_t)qw | (uintptr_t)kw) & 15) || (q_stride % 8))
+    QE_REFUSE("decode_attention_fused: operands must be 16-byte aligned");
+  if (part_acc && counters == nullptr) QE_REFUSE("decode_attention_fused: parts need the counters");
+  if (!inv_freq) QE_REFUSE("decode_attention_fused: needs the inverse frequencies");
+  const __nv_bfloat16* q = (const __nv_bfloat16*)qkv;
+  FaArgs fa{q, q_stride, (const __nv_bfloat16*)pages, block_tables, max_blocks, items,
+            (__nv_bfloat16*)out, part_acc, part_ml, part_rows, counters, scale * 1.4426950408889634f, window, Hq, Hkv,
+            page_size};
+  AdFuse fu{q + (size_t)Hq * D, q + (size_t)(Hq + Hkv) * D, qw, kw, eps, inv_freq, write_kv ? (__nv_bfloat16*)pages : nullptr};
+  if (max_rows <= 1) return launch_decode<1, true>(fa, fu, n_items, Hkv, stream);
+  if (max_rows <= 2) return launch_decode<2, true>(fa, fu, n_items, Hkv, stream);
+  return launch_decode<4, true>(fa, fu, n_items, Hkv, stream);
 }

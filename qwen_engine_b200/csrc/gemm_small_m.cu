@@ -23,8 +23,10 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
   // waits for the one before it, whose output the token operand is.
   GsmChunk c0, c1;
   gsm_prefetch(w, N, K, k_per_warp, blockIdx.x, c0, c1);
-  {
-    // and L2 is asked for the rest of this CTA's 16 rows (one contiguous block), in pieces of 8 KB
+  if (gridDim.x <= 1024) {
+    // (a grid that is resident all at once, waiting for the kernel before it: a layer's product, not
+    // the vocabulary's) and L2 is asked for the rest of this CTA's 16 rows (one contiguous block), in
+    // pieces of 8 KB
     const int rows = min(16, N - (int)blockIdx.x * 16);
     const unsigned bytes = (unsigned)rows * (unsigned)K * 2u;
     const unsigned off = threadIdx.x * 8192u;

@@ -32,6 +32,9 @@ FLASH_ITEM_INTS = 12    # int32 per work item of the flash kernel
 FLASH_SPLIT = 256       # keys per part when a decoded token's context is split (reference attn.py:605)
 FLASH_TARGET_CTAS = 296  # two CTAs per SM: long contexts are split into as many parts as fit in one wave
 DECODE_ATTENTION = True         # decoded tokens (few rows per kv head, head size 128): the kernel made for them
+# Off: measured on a B200 at batch 8, context 1024, the step is 4 % slower with it (the attention kernel,
+# which the step waits for, grows by more than the rotary kernel's launch costs).  Kept as a tested option.
+FUSE_ROTARY_IN_DECODE = False   # the decode attention kernel norms and rotates q, k and writes the cache itself
 DECODE_ATTENTION_MAX_ROWS = 4   # rows (token x head of the group) per item up to which it is used
 DECODE_ATTENTION_MAX_KEYS = 512 # context up to which it serves contexts that are not split (longer: the pipelined kernel)
 DECODE_ATTENTION_MIN_CTAS = 128 # CTAs from which it is used: measured, it gains where the GPU is full and loses a little below
@@ -697,12 +700,41 @@ def _merge_counters(device, kernel: str = "fa") -> torch.Tensor:
     return t
 
 
+def _decode_kernel_serves(plan, key, ctx, qkv: torch.Tensor, Hkv: int, D: int) -> bool:
+    """Whether the whole step's attention (geometry index ``key`` of the plan) goes to the kernel for
+    decoded tokens: few rows per item, head size 128, enough CTAs to fill the GPU, contexts split or short."""
+    if not DECODE_ATTENTION or key is None or f"fa{key}_items" not in plan or f"tc{key}_items" in plan or D != 128:
+        return False
+    n_parts, part_rows, small_tiles, max_rows = plan[f"fa{key}_info_host"]
+    n_items = plan[f"fa{key}_items"].numel() // FLASH_ITEM_INTS
+    return (1 <= max_rows <= DECODE_ATTENTION_MAX_ROWS and n_items > 0 and n_items * Hkv >= DECODE_ATTENTION_MIN_CTAS
+            and n_parts * Hkv <= _MERGE_COUNTERS and qkv.stride(0) % 8 == 0
+            and (n_parts > 0 or max(getattr(ctx, "ctx_lens_host", None) or [0]) <= DECODE_ATTENTION_MAX_KEYS))
+
+
+def attention_fuses_rotary(qkv: torch.Tensor, ctx, num_heads: int, num_kv_heads: int, head_dim: int, window: int,
+                           rotary_dim: int) -> bool:
+    """Whether ``paged_attention`` can take q, k, v as the QKV product left them and do the per-head norm,
+    the rotation and the cache write itself (``fused=``): a decode step served by the kernel for decoded
+    tokens, one token per request, the whole head rotated."""
+    if not FUSE_ROTARY_IN_DECODE or _program is not None or rotary_dim != head_dim or ctx.dtype != torch.bfloat16:
+        return False
+    if any(n != 1 for n in ctx.q_lens_host):
+        return False
+    plan = ctx.attn_plan
+    key = plan.get("geometry_index", {}).get((num_heads, num_kv_heads, head_dim, window))
+    return _decode_kernel_serves(plan, key, ctx, qkv, num_kv_heads, head_dim)
+
+
 def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: torch.Tensor, ctx,
                     out: torch.Tensor, scale: float, window: int, num_heads: int, num_kv_heads: int,
-                    head_dim: int) -> None:
+                    head_dim: int, fused: Optional[dict] = None) -> None:
     """Attention of the step's queries (the q part of qkv [T, (Hq+2Hkv) D]) over the keys and values
     of their requests in ``kv_pages``; out [T, Hq D].  ``ctx`` is the StepContext (cu_q, ctx_lens,
-    the plan that ``plan_attention`` made, and the arena for the parts of split contexts)."""
+    the plan that ``plan_attention`` made, and the arena for the parts of split contexts).
+
+    ``fused`` (only where ``attention_fuses_rotary`` said yes): q_norm_w, k_norm_w, eps, inv_freq,
+    write_kv of the per-head norm, rotation and cache write that this call then does itself."""
     Hq, Hkv, D = num_heads, num_kv_heads, head_dim
     T = qkv.shape[0]
     _need(out.shape == (T, Hq * D) and out.is_contiguous() and out.dtype == qkv.dtype, "paged_attention: out must be [T, Hq D]")
@@ -741,10 +773,17 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
                          floats=[scale * 1.4426950408889634], longs=[qkv.stride(0)],
                          ptrs=[qkv, kv_pages, block_tables, items, out, part_acc, part_ml, counters])
             return
-        if (DECODE_ATTENTION and 1 <= max_rows <= DECODE_ATTENTION_MAX_ROWS and D == 128 and n_items > 0
-                and (n_parts == 0 or counters is not None) and qkv.stride(0) % 8 == 0
-                and n_items * Hkv >= DECODE_ATTENTION_MIN_CTAS
-                and (n_parts > 0 or max(getattr(ctx, "ctx_lens_host", None) or [0]) <= DECODE_ATTENTION_MAX_KEYS)):
+        serves = _decode_kernel_serves(plan, key, ctx, qkv, Hkv, D)
+        _need(fused is None or serves, "paged_attention: this step cannot take the rotation into the attention kernel")
+        if fused is not None:
+            _check(lib().qe_decode_attention_fused(
+                _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(block_tables), int(block_tables.shape[1]),
+                _ptr(items), n_items, _ptr(out), _ptr(part_acc), _ptr(part_ml), int(part_rows), _ptr(counters),
+                int(max_rows), ctypes.c_float(scale), int(window), _ptr(fused["q_norm_w"]), _ptr(fused["k_norm_w"]),
+                ctypes.c_float(fused["eps"]), _ptr(fused["inv_freq"]), int(bool(fused["write_kv"])),
+                Hq, Hkv, D, int(kv_pages.shape[3]), _stream()), "decode_attention_fused")
+            return
+        if serves:
             # a few rows per kv head (decoded tokens): the kernel without matrix instructions
             _check(lib().qe_decode_attention(
                 _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(block_tables), int(block_tables.shape[1]),

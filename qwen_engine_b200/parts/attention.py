@@ -80,6 +80,14 @@ class GQAAttention(Mixer):
         qkv = ctx.arena.alloc((T, self.q_width + 2 * self.kv_width), ctx.dtype)
         ops.linear(x, self.w_qkv, qkv)
         fused_rope = isinstance(self.pos, NeoxRope)
+        attn = ctx.arena.alloc((T, self.q_width), ctx.dtype)
+        if fused_rope and ops.attention_fuses_rotary(qkv, ctx, H, Hkv, D, self.window or 0, self.pos.rotary_dim):
+            # a decode step: the attention kernel norms and rotates q and k and writes the cache itself
+            ops.paged_attention(qkv, cache, view.block_tables, ctx, attn, self.scale, self.window or 0, H, Hkv, D,
+                                fused=dict(q_norm_w=self.q_norm_w, k_norm_w=self.k_norm_w, eps=self.qk_norm_eps or 0.0,
+                                           inv_freq=self.pos.inv_freq, write_kv=write_cache))
+            ops.linear(attn, self.w_o, out)
+            return
         if self.pos is not None and not fused_rope:
             # another position encoding: norm first (the order of model.py:204-208),
             # then the part's own rotation, then the plain cache write
@@ -98,7 +106,6 @@ class GQAAttention(Mixer):
                 self.pos.rotary_dim if fused_rope else 0,
                 cache, view.slot_mapping, H, Hkv, D, write_kv=write_cache,
                 cos_sin=self.pos.step_table(ctx) if fused_rope else None)
-        attn = ctx.arena.alloc((T, self.q_width), ctx.dtype)
         ops.paged_attention(qkv, cache, view.block_tables, ctx, attn, self.scale,
                             self.window or 0, H, Hkv, D)
         ops.linear(attn, self.w_o, out)

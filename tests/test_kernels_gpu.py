@@ -373,6 +373,52 @@ def test_decode_attention(Hq, Hkv, P, q_lens, ctx_lens, window):
     assert ops.launch_count == launches + 2
 
 
+@pytest.mark.parametrize("Hq,Hkv,P", [(16, 8, 16), (4, 4, 8), (8, 2, 32), (4, 1, 16)])
+@pytest.mark.parametrize("ctx_lens", [[77], [5, 130, 333], [1024] * 8, [0, 159, 160, 161, 319, 320, 63, 64]])
+@pytest.mark.parametrize("norm", [True, False])
+@pytest.mark.parametrize("write_kv", [True, False])
+def test_decode_attention_with_rotary_fused(Hq, Hkv, P, ctx_lens, norm, write_kv):
+    """A decode step in which the attention kernel itself norms and rotates q and k and writes the
+    new keys and values into the cache: outputs and cache against the plain rotary step followed
+    by plain attention.  write_kv off: a layer that reads another layer's cache, which holds the
+    new token already."""
+    D, dtype, window = 128, torch.bfloat16, 0
+    q_lens = [1] * len(ctx_lens)
+    case = _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, seed=43)
+    g = torch.Generator().manual_seed(44)
+    qw = (1.0 + 0.2 * torch.randn(D, generator=g)) if norm else None
+    kw = (1.0 + 0.2 * torch.randn(D, generator=g)) if norm else None
+    inv_freq = (10000.0 ** (-torch.arange(0, D, 2, dtype=torch.float32) / D))
+    positions = torch.tensor(ctx_lens, dtype=torch.int32)
+    slots = torch.tensor([int(case["table"][r, c // P]) * P + c % P for r, c in enumerate(ctx_lens)], dtype=torch.int32)
+    # the plain way on the CPU: rotary step (writes the cache), then attention
+    qkv_ref, cache_ref = case["qkv"].clone(), case["cache"].clone()
+    ref_ops.qk_norm_rope_kv_write(qkv_ref, positions, qw, kw, 1e-6, inv_freq, D, cache_ref, slots, Hq, Hkv, D)
+    ref_case = dict(case, qkv=qkv_ref, cache=cache_ref)
+    want = _run_attention(ref_case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ref_ops.paged_attention, "cpu")
+    # the kernel: raw q, k, v; the cache without the new token (or, write_kv off, with it)
+    cache_gpu = (case["cache"] if write_kv else cache_ref).clone().to(DEV)
+    fused = dict(q_norm_w=qw.to(DEV) if norm else None, k_norm_w=kw.to(DEV) if norm else None, eps=1e-6,
+                 inv_freq=inv_freq.to(DEV), write_kv=write_kv)
+    saved = ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_KEYS
+    ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_KEYS = 1, 1 << 30
+    try:
+        gpu_case = dict(case, cache=cache_gpu)
+        got = _run_attention(gpu_case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window,
+                             lambda *a: ops.paged_attention(*a, fused=fused), DEV)
+    finally:
+        ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_KEYS = saved
+    _close(got, want, dtype)
+    # the cache: the new token's key and value where the rotary kernel would have put them, nothing else touched
+    assert torch.equal(cache_gpu.cpu()[:, 1], cache_ref[:, 1])
+    _close(cache_gpu.cpu()[:, 0], cache_ref[:, 0], dtype, tol16=8e-3)
+    changed = (cache_gpu.cpu() != case["cache"]).any(dim=-1)          # [pages, 2, Hkv, P]
+    if write_kv:
+        assert int(changed.sum()) <= 2 * Hkv * len(ctx_lens)
+    else:
+        assert torch.equal(cache_gpu.cpu(), cache_ref)
+
+
 @pytest.mark.parametrize("key_pos", [0, 15, 16, 159, 160, 161, 255, 256, 700, 899])
 def test_decode_attention_far_key_stands_out(key_pos):
     """One key among hundreds carries almost all the weight: the output must be its value.  A kernel
