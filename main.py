@@ -37,6 +37,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--max-num-batched-tokens", type=int, default=2048)
     ap.add_argument("--prefill-chunk", type=int, default=None, help="largest portion of a prompt in one step")
     ap.add_argument("--no-prefix-cache", action="store_true")
+    ap.add_argument("--no-run-ahead", action="store_true",
+                    help="do not launch a decode step before the host has read the tokens of the step before it")
     ap.add_argument("--temperature", type=float, default=0.0)
     ap.add_argument("--top-k", type=int, default=0)
     ap.add_argument("--sample-seed", type=int, default=0)
@@ -85,7 +87,7 @@ def main(argv=None) -> int:
     llm = LLM(model, dtype=parse_dtype(args.dtype), device=args.device, block_size=block_size,
               num_blocks=args.num_blocks, max_model_len=args.max_model_len, max_num_seqs=args.max_num_seqs,
               max_num_batched_tokens=args.max_num_batched_tokens, prefill_chunk_size=args.prefill_chunk,
-              enable_prefix_cache=not args.no_prefix_cache, seed=args.sample_seed)
+              enable_prefix_cache=not args.no_prefix_cache, run_ahead=not args.no_run_ahead, seed=args.sample_seed)
     sp = SamplingParams(max_new_tokens=args.max_new_tokens, temperature=args.temperature, top_k=args.top_k,
                         seed=args.sample_seed, ignore_eos=args.ignore_eos)
 
