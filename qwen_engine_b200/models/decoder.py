@@ -89,7 +89,7 @@ class DecoderModel:
             if geo is not None and geo not in geos:
                 geos.append(geo)
         self.attention_geometries = tuple(geos)
-        self.capturable = all(getattr(b.mixer, "capturable", True) for b in self.blocks)
+        self.capturable = all(getattr(b, "capturable", True) and getattr(b.mixer, "capturable", True) for b in self.blocks)
 
     # ---- what the cache manager and the loader ask --------------------------------------
     def cache_specs(self) -> list[Optional[CacheSpec]]:

@@ -210,7 +210,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
-    takes_lazy_input = False      # as for Mixer
+    capturable = True             # as for Mixer: False if forward reads step data on the host (routing by sizes)
+    takes_lazy_input = False
     writes_through_linear = False
 
     def forward(self, ctx: StepContext, x: torch.Tensor, out: torch.Tensor) -> None:
@@ -219,6 +220,7 @@ class FeedForward(Part):
 
 class Block(Part):
     mixer: Mixer
+    capturable = True             # False if any of its parts says so: steps of the model are then never graph-captured
 
     def forward(self, ctx: StepContext, stream, cache: Optional[torch.Tensor], group: Optional[int],
                 write_cache: bool) -> None:

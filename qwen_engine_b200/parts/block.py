@@ -22,6 +22,10 @@ class PreNormBlock(Block):
     def _parts(self):
         return zip((self.norm1, self.mixer, self.norm2, self.ffn), self.prefixes)
 
+    @property
+    def capturable(self) -> bool:
+        return all(getattr(part, "capturable", True) for part, _ in self._parts())
+
     def weight_specs(self, prefix: str):
         return [s for part, p in self._parts() for s in part.weight_specs(prefix + p)]
 

@@ -15,7 +15,8 @@ from qwen_engine_b200.cache import CacheManager, FixedStateSpec
 from qwen_engine_b200.config import ModelConfig
 from qwen_engine_b200.engine.runner import ModelRunner, StepEntry
 from qwen_engine_b200.models.decoder import DecoderModel, LayerSpec, ModelLayout, PlanEntry
-from qwen_engine_b200.parts import (Mixer, PartSpec, PositionEncoding, register, MIXERS, POSITION_ENCODINGS)
+from qwen_engine_b200.parts import (FeedForward, Mixer, PartSpec, PositionEncoding, register, FEED_FORWARDS, MIXERS,
+                                    POSITION_ENCODINGS)
 from qwen_engine_b200.registry import ARCHITECTURES, build_model, config_from_dict, register_architecture
 from qwen_engine_b200.weights import NORM, MATRIX, RandomSource, WeightSpec
 
@@ -222,6 +223,50 @@ class DecayMixer(Mixer):
             cache[slot] = s
 
 
+class RoutedFFN(FeedForward):
+    """A toy feed-forward with routing: router logits and their softmax in float32, every token goes
+    to the expert with the largest probability (a SwiGLU of its own) and its output is scaled by that
+    probability.  The experts' products run through the engine's kernels on the gathered rows."""
+
+    capturable = False      # the rows of an expert are counted on the host
+
+    def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int):
+        self.H, self.I, self.E = hidden_size, intermediate_size, num_experts
+        self.router = None
+        self.w_gu, self.w_d = [], []
+
+    def weight_specs(self, prefix):
+        specs = [WeightSpec(prefix + "router.weight", (self.E, self.H), NORM)]
+        for e in range(self.E):
+            specs += [WeightSpec(prefix + f"experts.{e}.gate_proj.weight", (self.I, self.H), MATRIX),
+                      WeightSpec(prefix + f"experts.{e}.up_proj.weight", (self.I, self.H), MATRIX),
+                      WeightSpec(prefix + f"experts.{e}.down_proj.weight", (self.H, self.I), MATRIX)]
+        return specs
+
+    def load(self, prefix, source, dtype, device):
+        self.router = source.get(prefix + "router.weight").float().to(device)
+        for e in range(self.E):
+            g, u = (source.get(prefix + f"experts.{e}.{n}_proj.weight") for n in ("gate", "up"))
+            self.w_gu.append(ops.prepare_matrix(torch.cat([g, u], dim=0).to(dtype).to(device)))
+            self.w_d.append(ops.prepare_matrix(source.get(prefix + f"experts.{e}.down_proj.weight").to(dtype).to(device)))
+
+    def forward(self, ctx, x, out):
+        probs = torch.softmax(x.float() @ self.router.t(), dim=-1)
+        top_p, top_e = probs.max(dim=-1)
+        for e in range(self.E):
+            rows = (top_e == e).nonzero().flatten()
+            if rows.numel() == 0:
+                continue
+            xe = x[rows].contiguous()
+            gu = torch.empty(rows.numel(), 2 * self.I, dtype=x.dtype, device=x.device)
+            ops.linear(xe, self.w_gu[e], gu)
+            act = torch.empty(rows.numel(), self.I, dtype=x.dtype, device=x.device)
+            ops.silu_mul(gu, act)
+            oe = torch.empty(rows.numel(), self.H, dtype=x.dtype, device=x.device)
+            ops.linear(act, self.w_d[e], oe)
+            out[rows] = (oe.float() * top_p[rows, None]).to(out.dtype)
+
+
 class ShiftedRope(PositionEncoding):
     """Another position encoding: interleaved pairs (2j, 2j+1) instead of half-split ones."""
 
@@ -250,6 +295,8 @@ class ToyConfig(ModelConfig):
     head_dim: int = 16
     intermediate_size: int = 56
     decay: float = 0.7
+    num_experts: int = 3
+    expert_size: int = 24
 
     @classmethod
     def from_dict(cls, raw):
@@ -268,9 +315,10 @@ def toy_layout(cfg: ToyConfig) -> ModelLayout:
         scale=cfg.head_dim ** -0.5, qk_norm_eps=1e-5, position_encoding=pos))
     rope = PartSpec("rope_neox", dict(head_dim=cfg.head_dim, theta=1e4))
     other = PartSpec("test_interleaved_rope", dict(head_dim=cfg.head_dim, theta=1e4))
-    block = lambda mixer: PartSpec("pre_norm", dict(hidden_size=H, mixer=mixer, feed_forward=ffn, norm=norm))
+    block = lambda mixer, ff=ffn: PartSpec("pre_norm", dict(hidden_size=H, mixer=mixer, feed_forward=ff, norm=norm))
+    routed = PartSpec("test_routed", dict(hidden_size=H, intermediate_size=cfg.expert_size, num_experts=cfg.num_experts))
     layers = (LayerSpec(block(attn(rope)), "layers.0."),
-              LayerSpec(block(PartSpec("test_decay", dict(hidden_size=H, decay=cfg.decay))), "layers.1."),
+              LayerSpec(block(PartSpec("test_decay", dict(hidden_size=H, decay=cfg.decay)), routed), "layers.1."),
               LayerSpec(block(attn(other)), "layers.2."))
     # layer 0 runs twice (a cache slot for each run); layer 2 runs once with a cache of its own and
     # once more reading what layer 0's first run wrote (same cache description, so the same group)
@@ -326,7 +374,12 @@ def _toy_plain(cfg: ToyConfig, w, tokens):
         s = cfg.decay * s + h[t]
         ys.append(s * w[p + "self_attn.gain"])
     x = x + torch.stack(ys)
-    x = x + plain.mlp_part(plain.rmsnorm(x, w[p + "post_attention_layernorm.weight"], 1e-5), w, p + "mlp.")
+    h = plain.rmsnorm(x, w[p + "post_attention_layernorm.weight"], 1e-5)
+    probs = torch.softmax(h @ w[p + "mlp.router.weight"].t(), dim=-1)
+    top_p, top_e = probs.max(dim=-1)
+    routed = torch.stack([top_p[t] * plain.mlp_part(h[t:t + 1], w, p + f"mlp.experts.{int(top_e[t])}.")[0] for t in range(T)])
+    assert len(set(top_e.tolist())) > 1, "the tokens must not all go to one expert"
+    x = x + routed
     x, _ = attn_block(x, 0, "neox")
     x, _ = attn_block(x, 2, "interleaved")
     x, _ = attn_block(x, 2, "interleaved", kv=kv0)
@@ -337,15 +390,18 @@ def _toy_plain(cfg: ToyConfig, w, tokens):
 def toy_registered():
     register("mixer", "test_decay")(DecayMixer)
     register("position_encoding", "test_interleaved_rope")(ShiftedRope)
+    register("feed_forward", "test_routed")(RoutedFFN)
     register_architecture("ToyForCausalLM", ToyConfig, toy_layout)
     yield
-    del MIXERS["test_decay"], POSITION_ENCODINGS["test_interleaved_rope"], ARCHITECTURES["ToyForCausalLM"]
+    del MIXERS["test_decay"], POSITION_ENCODINGS["test_interleaved_rope"], FEED_FORWARDS["test_routed"]
+    del ARCHITECTURES["ToyForCausalLM"]
 
 
 def test_toy_architecture_with_its_own_parts(toy_registered):
-    """Registered from outside: built by the registry, loaded by the loader's checks, given cache
-    groups of its own (pages for attention, state slots for the toy mixer) and stepped by the
-    engine's step function, whole and in portions mixed with another request."""
+    """Registered from outside (a mixer with state of its own, a feed-forward with routing, another
+    position encoding): built by the registry, loaded by the loader's checks, given cache groups of
+    its own (pages for attention, state slots for the toy mixer) and stepped by the engine's step
+    function, whole and in portions mixed with another request."""
     dtype = torch.float32
     cfg = config_from_dict({"architectures": ["ToyForCausalLM"], "hidden_size": 40, "decay": 0.6})
     assert isinstance(cfg, ToyConfig)
