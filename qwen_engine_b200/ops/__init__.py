@@ -348,7 +348,18 @@ class NormedInput:
         return self._tensor
 
 
-FUSED_NORM_MAX_M = 16   # rows up to which a norm is fused into the product that follows
+# What is fused into the products of a few rows was settled by measurement on a B200 (decode, batch 8,
+# context 1024, tokens/s with / without):
+#   the norm of the stream into the product that follows it   0.6B 6 480 / 6 920, 1.7B 4 340 / 4 580, 4B 1 570 / 1 970:
+#       off.  Every CTA (16 weight rows) reads all of x; in float32 with the norm's arithmetic that costs
+#       more than the norm kernel's launch.  Kept as a tested option.
+#   SiLU-mul into the product that consumes it               0.6B equal, 4B 1 960 / 2 080: on up to 4 096 columns
+#       of gate/up per half (every CTA reads both halves of gate_up).
+#   the branch's add into the stream in the product's epilogue   0.6B 6 870 / 6 820, 4B 2 070 / 1 740: on.
+FUSED_NORM_MAX_M = 0    # rows up to which a norm is fused into the product that follows (0: never)
+FUSED_SILU_MAX_M = 64   # rows up to which SiLU-mul is formed by the product that consumes it ...
+FUSED_SILU_MAX_K = 4096  # ... when the activation has at most this many columns
+RESID_SINK_MAX_M = 64   # rows up to which a branch's last product adds into the stream itself
 
 
 def _linear_normed(x: NormedInput, w: torch.Tensor, out: torch.Tensor) -> bool:
@@ -377,7 +388,7 @@ def _linear_into_stream(x: torch.Tensor, w: torch.Tensor, sink: ResidualSink, si
     M = x.shape[0]
     K = x.shape[1] // 2 if silu else x.shape[1]
     N = w.shape[0]
-    if not (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M <= SMALL_M_MAX and K % 8 == 0
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M <= min(SMALL_M_MAX, RESID_SINK_MAX_M) and K % 8 == 0
             and not st.has_delta and st.ssq is not None and st.ssq.shape[1] >= -(-N // 16)
             and st.resid.shape == (M, N)):
         return False
@@ -446,13 +457,18 @@ def linear_silu_mul(gate_up: torch.Tensor, w: torch.Tensor, out: torch.Tensor, s
     """out[M, N] = (silu(gate_up[:, :I]) * gate_up[:, I:]) · w[N, I]^T.  For a few rows in bfloat16 the
     activation is formed while the product loads it; otherwise ``silu_mul`` runs first into a buffer
     that ``scratch(shape, dtype)`` provides."""
+    M, I2 = gate_up.shape
+    I = I2 // 2
+    N = w.shape[0]
+    if M > FUSED_SILU_MAX_M or I > FUSED_SILU_MAX_K:
+        act = scratch((M, I), gate_up.dtype)
+        silu_mul(gate_up, act)
+        linear(act, w, out)
+        return
     if isinstance(out, ResidualSink):
         if _linear_into_stream(gate_up, w, out, silu=True):
             return
         out = out.as_delta()
-    M, I2 = gate_up.shape
-    I = I2 // 2
-    N = w.shape[0]
     _need(I2 % 2 == 0 and w.shape == (N, I) and w.dtype == gate_up.dtype, "linear_silu_mul: w must be [N, I] for gate_up [M, 2I]")
     _need(out.shape == (M, N) and out.dtype in (gate_up.dtype, torch.float32), "linear_silu_mul: out must be [M, N]")
     _need(gate_up.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "linear_silu_mul: operands must be contiguous")

@@ -147,10 +147,13 @@ def test_linear_tcgen05(M, N, K, out_f32):
 
 
 @pytest.mark.parametrize("M,H,N", [(1, 64, 40), (8, 1024, 4096), (16, 80, 389), (5, 1032, 72), (17, 128, 64)])
-def test_branch_into_stream_then_fused_norm(M, H, N):
+@pytest.mark.parametrize("norm_rows", [0, 16])
+def test_branch_into_stream_then_fused_norm(M, H, N, norm_rows, monkeypatch):
     """A branch's product added into the float32 stream by the product's own epilogue (which leaves
-    the rows' sums of squares), then the next norm fused into the next product (few rows, bfloat16);
-    more rows fall back to the delta buffer and the separate norm kernel.  Same numbers either way."""
+    the rows' sums of squares), then the next norm: by its own kernel (the engine's setting), or fused
+    into the next product from those sums (few rows, bfloat16; an option that is off in the engine);
+    more rows fall back to the delta buffer and the separate norm kernel.  Same numbers every way."""
+    monkeypatch.setattr(ops, "FUSED_NORM_MAX_M", norm_rows)
     dt = torch.bfloat16
     K1 = 136
     resid = _randn((M, H), torch.float32, 50, 2.0)
