@@ -35,7 +35,7 @@ DECODE_ATTENTION = True         # decoded tokens (few rows per kv head, head siz
 # Off: measured on a B200 at batch 8, context 1024, the step is 4 % slower with it (the attention kernel,
 # which the step waits for, grows by more than the rotary kernel's launch costs).  Kept as a tested option.
 FUSE_ROTARY_IN_DECODE = False   # the decode attention kernel norms and rotates q, k and writes the cache itself
-DECODE_ATTENTION_MAX_ROWS = 4   # rows (token x head of the group) per item up to which it is used
+DECODE_ATTENTION_MAX_ROWS = 2   # rows (token x head of the group) per item up to which it is used (measured: with 4 rows the mma.sync kernel is 11 % ahead; the kernel takes up to 4)
 DECODE_ATTENTION_MAX_KEYS = 512 # context up to which it serves contexts that are not split (longer: the pipelined kernel)
 DECODE_ATTENTION_MIN_CTAS = 128 # CTAs from which it is used: measured, it gains where the GPU is full and loses a little below
 TC_ROWS = 256           # rows per work item of the tcgen05 attention kernel (two halves of 128)

@@ -358,12 +358,13 @@ def test_decode_attention(Hq, Hkv, P, q_lens, ctx_lens, window):
     reference, and against the mma.sync kernel that serves the same items when it is switched off."""
     D, dtype = 128, torch.bfloat16
     plan = ops.plan_attention(list(q_lens), list(ctx_lens), P, ((Hq, Hkv, D, window),), dtype)
-    assert 1 <= plan["fa0_info"][3] <= ops.DECODE_ATTENTION_MAX_ROWS
+    assert 1 <= plan["fa0_info"][3] <= 4
     case = _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, seed=41)
     want = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ref_ops.paged_attention, "cpu")
     launches = ops.launch_count
-    saved = ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_KEYS
-    ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_KEYS = 1, 1 << 30     # whatever the size of the case
+    saved = ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_KEYS, ops.DECODE_ATTENTION_MAX_ROWS
+    # whatever the size of the case, and up to the 4 rows the kernel takes
+    ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_KEYS, ops.DECODE_ATTENTION_MAX_ROWS = 1, 1 << 30, 4
     try:
         got = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ops.paged_attention, DEV)
         _close(got, want, dtype)
@@ -371,7 +372,7 @@ def test_decode_attention(Hq, Hkv, P, q_lens, ctx_lens, window):
         other = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ops.paged_attention, DEV)
     finally:
         ops.DECODE_ATTENTION = True
-        ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_KEYS = saved
+        ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_KEYS, ops.DECODE_ATTENTION_MAX_ROWS = saved
     _close(other, want, dtype)
     assert ops.launch_count == launches + 2
 
@@ -403,14 +404,14 @@ def test_decode_attention_with_rotary_fused(Hq, Hkv, P, ctx_lens, norm, write_kv
     cache_gpu = (case["cache"] if write_kv else cache_ref).clone().to(DEV)
     fused = dict(q_norm_w=qw.to(DEV) if norm else None, k_norm_w=kw.to(DEV) if norm else None, eps=1e-6,
                  inv_freq=inv_freq.to(DEV), write_kv=write_kv)
-    saved = ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_KEYS
-    ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_KEYS = 1, 1 << 30
+    saved = ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_KEYS, ops.DECODE_ATTENTION_MAX_ROWS
+    ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_KEYS, ops.DECODE_ATTENTION_MAX_ROWS = 1, 1 << 30, 4
     try:
         gpu_case = dict(case, cache=cache_gpu)
         got = _run_attention(gpu_case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window,
                              lambda *a: ops.paged_attention(*a, fused=fused), DEV)
     finally:
-        ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_KEYS = saved
+        ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_KEYS, ops.DECODE_ATTENTION_MAX_ROWS = saved
     _close(got, want, dtype)
     # the cache: the new token's key and value where the rotary kernel would have put them, nothing else touched
     assert torch.equal(cache_gpu.cpu()[:, 1], cache_ref[:, 1])
