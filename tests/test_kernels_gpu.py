@@ -483,6 +483,19 @@ def test_tc_attention_parts(q_lens, ctx_lens):
         _close(got, want, dtype)
 
 
+@pytest.mark.parametrize("q_lens,ctx_lens", [([200], [30000]), ([1, 1], [30000, 17]), ([3], [40000])])
+def test_attention_long_context(q_lens, ctx_lens):
+    """Tens of thousands of keys (the model's limit is 40 960 positions): a portion on the tcgen05
+    kernel with its tiles cut into parts, and decoded tokens with split contexts."""
+    Hq, Hkv, D, P = 4, 2, 128, 16
+    dtype = torch.bfloat16
+    case = _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, seed=35)
+    want = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, ref_ops.paged_attention, "cpu")
+    got = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, ops.paged_attention, DEV)
+    assert ops.tc_attention_status() == 0
+    _close(got, want, dtype)
+
+
 @pytest.mark.parametrize("window", [1, 100, 128, 129, 300])
 def test_tc_attention_window(window):
     Hq, Hkv, D, P = 4, 2, 128, 16
