@@ -73,6 +73,7 @@ class ModelRunner:
         # (3.0 ms against 1.3 ms a step at batch 8): its grid barrier over 296 CTAs costs 2.5 us, as
         # much as a dependent launch, and its products run at 8 warps a CTA.  Kept as a tested option.
         self.use_decode_program = False
+        self.capture_all_steps = True         # steps that are not all decoded tokens are captured too when they recur
         self.num_graph_replays = 0
         self.num_steps = 0
         self.last_h2d_bytes = 0
@@ -234,16 +235,23 @@ class ModelRunner:
 
         # A step of single decoded tokens has a shape that recurs: it is captured in a CUDA graph
         # the second time the shape is seen and replayed from then on.  Everything the kernels
-        # read that changes from step to step lives in the metadata buffer.
+        # read that changes from step to step lives in the metadata buffer.  Other steps recur too (a
+        # long prompt in portions of the token budget, prompts of one length): they are captured by
+        # what decides their launches, see below.
         graph_key = None
         uniform_splits = None
+        buckets = None
+        B = self.GRAPH_BLOCK_BUCKET
         if self.use_cuda_graphs and all(n == 1 for n in q_lens):
-            B = self.GRAPH_BLOCK_BUCKET
             buckets = tuple(-(-max(len(e.cache.tables[g.index]) for e in entries) // B) * B
                             for g in cache.paged_groups)
             graph_key = (R, N, buckets)
             uniform_splits = ops.decode_splits(R, max(buckets, default=B) * cache.page_size,
                                                self.model.attention_geometries, self.dtype)
+        elif self.use_cuda_graphs and self.capture_all_steps:
+            # block tables padded to 64 x a power of two entries, so that few widths occur
+            buckets = tuple(B << max(0, (-(-max(len(e.cache.tables[g.index]) for e in entries) // B) - 1).bit_length())
+                            for g in cache.paged_groups)
 
         pack = _Pack()
         pack.add("token_ids", token_ids)
@@ -255,8 +263,8 @@ class ModelRunner:
         max_blocks: dict[int, int] = {}
         for gi, g in enumerate(cache.paged_groups):
             mb = max(len(e.cache.tables[g.index]) for e in entries)
-            if graph_key is not None:
-                mb = graph_key[2][gi]
+            if buckets is not None:
+                mb = buckets[gi]
             max_blocks[g.index] = mb
             flat: list[int] = []
             slots: list[int] = []
@@ -272,6 +280,13 @@ class ModelRunner:
                                   uniform_splits=uniform_splits)
         for name, values in plan.items():
             pack.add("plan_" + name, values)
+        if graph_key is None and buckets is not None:
+            # what decides the launches of a step that is not all decoded tokens: the rows of every request,
+            # the widths of the block tables, the lengths of the work lists and what the plan says about
+            # them, and the one decision that is taken from the context lengths
+            graph_key = ("step", N, tuple(q_lens), buckets,
+                         tuple((k, tuple(v) if k.endswith("_info") else len(v)) for k, v in plan.items()),
+                         max(ctx_lens) <= ops.DECODE_ATTENTION_MAX_KEYS)
         if fix_rows:        # last, so that the places of everything a captured step reads stay where they are
             pack.add("fix_rows", fix_rows)
             pack.add("fix_src", fix_src)
