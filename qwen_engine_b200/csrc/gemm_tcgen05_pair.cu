@@ -13,6 +13,13 @@
 // with a CTA mask; `acc_empty` lives in the leading CTA and collects the epilogue warps of both.  No
 // TMA multicast.  Every wait on an mbarrier is bounded, as in gemm_tcgen05.cu.
 //
+//
+// SWIGLU: w is the feed-forward's stacked gate and up weights [2 I, K].  A tile's 256 columns are 128
+// columns of gate and the same 128 columns of up (the leading CTA loads the gate rows, the other CTA
+// the up rows: only the TMA coordinate differs), and the epilogue writes silu(gate) * up, computed on
+// the float32 accumulators, as 128 columns of out [M, I]: the activation never exists as gate_up in
+// memory (reference: src/layers/fused_ops/silumul.py:50-53 applies it to the rounded products).
+//
 // Needs K % 8 == 0 and 16-byte aligned bases (TMA strides); the launcher refuses the rest.
 #include "tcgen05.cuh"
 
@@ -34,10 +41,12 @@ struct __align__(1024) PrSmem {
   int abort_flag;
 };
 
-template <typename TOut, int BN, int STAGES>
+// N: columns of the product (SWIGLU: 2 I); n_up: SWIGLU: the first row of up in w (= I), else 0
+template <typename TOut, int BN, int STAGES, bool SWIGLU>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PR_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                         TOut* __restrict__ out, int M, int N, int K) {
+                         TOut* __restrict__ out, int M, int N, int K, int n_up) {
+  static_assert(!SWIGLU || BN == 256, "the fused activation pairs 128 columns of gate with 128 of up");
   extern __shared__ unsigned char smem_raw[];
   using Smem = PrSmem<BN, STAGES>;
   constexpr uint32_t TMEM_COLS = 2 * BN;
@@ -47,7 +56,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_cta_rank();          // 0: the leading CTA of the pair
   const int num_kb = (K + PR_BK - 1) / PR_BK;
-  const int n_blocks = (N + BN - 1) / BN;
+  const int n_blocks = SWIGLU ? (n_up + BN / 2 - 1) / (BN / 2) : (N + BN - 1) / BN;
   const int n_tiles = n_blocks * ((M + 2 * PR_BM - 1) / (2 * PR_BM));
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   volatile int* abort_flag = &sm.abort_flag;
@@ -79,7 +88,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         kb = (int)(kc - (uint32_t)t * (uint32_t)num_kb);
         const int tile = pair + t * n_pairs;
         m0 = (tile / n_blocks) * 2 * PR_BM + (int)rank * PR_BM;
-        n0 = (tile % n_blocks) * BN + (int)rank * (BN / 2);
+        n0 = SWIGLU ? (tile % n_blocks) * (BN / 2) + (int)rank * n_up      // gate rows, or the same rows of up
+                    : (tile % n_blocks) * BN + (int)rank * (BN / 2);
       };
       int m0, n0, kb;
       // the ring's first round: the weights' tiles at once, x's after the wait for the kernel before
@@ -139,6 +149,46 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
       if (!ok) break;
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
+      if constexpr (SWIGLU) {
+        // columns c0.. of gate and of up -> 32 columns of the activation
+        const int I = n_up, i0 = (tile % n_blocks) * (BN / 2);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN / 2; c0 += 32) {
+          uint32_t g[32], u[32];
+          tc_ld_32x32b_x32(tmem + ((uint32_t)(quarter * 32) << 16) + buf * BN + c0, g);
+          tc_ld_32x32b_x32(tmem + ((uint32_t)(quarter * 32) << 16) + buf * BN + BN / 2 + c0, u);
+          tc_wait_ld();
+          if (c0 + 32 == BN / 2) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(smem_u32(&sm.acc_empty[buf]) & TC_PEER_BIT_MASK);
+          }
+          if (row < M && i0 + c0 < I) {
+            float a[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float gv = __uint_as_float(g[j]);
+              a[j] = __fdividef(gv, 1.f + __expf(-gv)) * __uint_as_float(u[j]);
+            }
+            TOut* dst = out + (size_t)row * I + i0 + c0;
+            if (i0 + c0 + 32 <= I && (I % 8) == 0 && sizeof(TOut) == 2) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 v;
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(a[j], a[j + 1]), p1 = __floats2bfloat162_rn(a[j + 2], a[j + 3]);
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(a[j + 4], a[j + 5]), p3 = __floats2bfloat162_rn(a[j + 6], a[j + 7]);
+                v.x = *reinterpret_cast<uint32_t*>(&p0); v.y = *reinterpret_cast<uint32_t*>(&p1);
+                v.z = *reinterpret_cast<uint32_t*>(&p2); v.w = *reinterpret_cast<uint32_t*>(&p3);
+                *reinterpret_cast<uint4*>(dst + j) = v;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (i0 + c0 + j < I) dst[j] = from_f32<TOut>(a[j]);
+            }
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
@@ -178,6 +228,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
           }
         }
       }
+      }   // plain epilogue
     }
   }
   // both CTAs meet here: neither leaves while the other may still signal its barriers, read its
@@ -191,8 +242,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   }
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool SWIGLU = false>
 static int launch_pair(const void* x, const void* w, void* out, int M, int N, int K, int out_f32, int sms, cudaStream_t stream) {
+  const int n_up = SWIGLU ? N / 2 : 0;
   CUtensorMap map_x, map_w;
   {
     const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
@@ -209,18 +261,19 @@ static int launch_pair(const void* x, const void* w, void* out, int M, int N, in
   const size_t smem = sizeof(PrSmem<BN, STAGES>) + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<__nv_bfloat16, BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<float, BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<__nv_bfloat16, BN, STAGES, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<float, BN, STAGES, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) QE_REFUSE("linear_tcgen05_pair: shared memory %zu: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  const long tiles = (long)((N + BN - 1) / BN) * ((M + 2 * PR_BM - 1) / (2 * PR_BM));
+  const long n_blocks = SWIGLU ? (n_up + BN / 2 - 1) / (BN / 2) : (N + BN - 1) / BN;
+  const long tiles = n_blocks * ((M + 2 * PR_BM - 1) / (2 * PR_BM));
   const long pairs = tiles < sms / 2 ? tiles : sms / 2;
   const dim3 grid((unsigned)(2 * pairs));
   if (out_f32)
-    qe_launch(gemm_tcgen05_pair_kernel<float, BN, STAGES>, grid, dim3(PR_THREADS), smem, stream, map_x, map_w, (float*)out, M, N, K);
+    qe_launch(gemm_tcgen05_pair_kernel<float, BN, STAGES, SWIGLU>, grid, dim3(PR_THREADS), smem, stream, map_x, map_w, (float*)out, M, N, K, n_up);
   else
-    qe_launch(gemm_tcgen05_pair_kernel<__nv_bfloat16, BN, STAGES>, grid, dim3(PR_THREADS), smem, stream, map_x, map_w, (__nv_bfloat16*)out, M, N, K);
+    qe_launch(gemm_tcgen05_pair_kernel<__nv_bfloat16, BN, STAGES, SWIGLU>, grid, dim3(PR_THREADS), smem, stream, map_x, map_w, (__nv_bfloat16*)out, M, N, K, n_up);
   QE_CHECK_LAUNCH("linear_tcgen05_pair");
   return 0;
 }
@@ -244,4 +297,17 @@ extern "C" int qe_linear_tcgen05_pair(const void* x, const void* w, void* out, i
   const long wide_tiles = (long)((N + 255) / 256) * ((M + 2 * PR_BM - 1) / (2 * PR_BM));
   if (wide_tiles >= sms / 2) return launch_pair<256, 6>(x, w, out, M, N, K, out_f32, sms, stream);
   return launch_pair<128, 8>(x, w, out, M, N, K, out_f32, sms, stream);
+}
+
+// out[M, I] = silu(x · w[:I]^T) * (x · w[I:]^T) for the stacked gate and up weights w [2 I, K] (see SWIGLU
+// above).  Returns 0 when run, 1 when refused, 2 on a launch error.
+extern "C" int qe_linear_swiglu_tcgen05_pair(const void* x, const void* w, void* out, int M, int I, int K, int out_f32,
+                                             cudaStream_t stream) {
+  if (M <= 0 || I <= 0) return 0;
+  if (K <= 0 || K % 8) QE_REFUSE("linear_swiglu: K = %d is not a positive multiple of 8", K);
+  if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) QE_REFUSE("linear_swiglu: operands must be 16-byte aligned");
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (sms < 2) QE_REFUSE("linear_swiglu: needs at least two SMs");
+  return launch_pair<256, 6, true>(x, w, out, M, 2 * I, K, out_f32, sms, stream);
 }

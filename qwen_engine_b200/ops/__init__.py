@@ -23,6 +23,7 @@ ATTN_TILE_Q = 16        # queries per work item of the generic attention kernel
 SMALL_M_MAX = 64        # rows up to which the weight-streaming product is used
 SWAP_MIN_M = 17         # rows from which, up to SMALL_M_MAX, wide products go to the swapped tcgen05 kernel
 SWAP_MIN_N = 3072       # weight rows from which it has enough CTAs (one per 128) to pull the weights fast enough
+SWIGLU_FUSED = True     # SiLU-mul in the epilogue of the gate/up product where the CTA-pair kernel serves it
 TCGEN05_PAIRS = True    # CTA pairs for large products
 PAIR_MIN_TILES = 74     # 256 x 256 tiles from which they are used (one per pair of SMs)
 TCGEN05_ENABLED = True  # the tcgen05 product for more rows (False: the generic kernel serves them)
@@ -451,6 +452,26 @@ def linear_pairs(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     _need(x.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "linear_pairs: operands must be contiguous")
     _check(lib().qe_linear_tcgen05_pair(_ptr(x), _ptr(w), _ptr(out), M, N, K, int(out.dtype == torch.float32), _stream()),
            "linear_pairs")
+
+
+def swiglu_fused_applies(M: int, I: int, K: int, dtype: torch.dtype) -> bool:
+    """Whether ``linear_swiglu`` serves this shape: bfloat16 and enough 256-row x 128-column tiles of
+    the activation for every pair of SMs (the kernel is the CTA-pair product)."""
+    return (TCGEN05_PAIRS and TCGEN05_ENABLED and SWIGLU_FUSED and dtype == torch.bfloat16 and K % 8 == 0
+            and -(-M // 256) * -(-I // 128) >= PAIR_MIN_TILES)
+
+
+def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, I] = silu(x · w[:I]^T) * (x · w[I:]^T) for the stacked weights w [2 I, K]: the feed-forward's
+    activation formed in the product's epilogue on its float32 sums (bfloat16, many rows)."""
+    M, K = x.shape
+    I = w_gate_up.shape[0] // 2
+    _need(x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and w_gate_up.shape == (2 * I, K) and K % 8 == 0,
+          "linear_swiglu: bfloat16 operands, w [2 I, K] with K a multiple of 8")
+    _need(out.shape == (M, I) and out.dtype in (torch.bfloat16, torch.float32), "linear_swiglu: out must be [M, I]")
+    _need(x.is_contiguous() and w_gate_up.is_contiguous() and out.is_contiguous(), "linear_swiglu: operands must be contiguous")
+    _check(lib().qe_linear_swiglu_tcgen05_pair(_ptr(x), _ptr(w_gate_up), _ptr(out), M, I, K,
+                                               int(out.dtype == torch.float32), _stream()), "linear_swiglu")
 
 
 def linear_silu_mul(gate_up: torch.Tensor, w: torch.Tensor, out: torch.Tensor, scratch) -> None:

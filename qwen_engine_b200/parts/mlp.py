@@ -34,6 +34,14 @@ class SwiGLU(FeedForward):
 
     def forward(self, ctx: StepContext, x, out) -> None:
         T, I = ctx.num_tokens, self.intermediate_size
+        if ops.swiglu_fused_applies(T, I, self.hidden_size, ctx.dtype):
+            # many rows: the activation comes out of the gate/up product's epilogue
+            if isinstance(x, ops.NormedInput):
+                x = x.materialize()
+            act = ctx.arena.alloc((T, I), ctx.dtype)
+            ops.linear_swiglu(x, self.w_gate_up, act)
+            ops.linear(act, self.w_down, out)
+            return
         gate_up = ctx.arena.alloc((T, 2 * I), ctx.dtype)
         ops.linear(x, self.w_gate_up, gate_up)
         ops.linear_silu_mul(gate_up, self.w_down, out, ctx.arena.alloc)

@@ -71,6 +71,10 @@ def attention_fuses_rotary(*args, **kwargs):
     return False
 
 
+def swiglu_fused_applies(*args, **kwargs):
+    return False
+
+
 def rope_table(positions, inv_freq, out):
     ang = positions.to(torch.float32)[:, None] * inv_freq[None, :]
     out[..., 0], out[..., 1] = torch.cos(ang), torch.sin(ang)
@@ -197,7 +201,7 @@ def sample(logits, temperature, top_k, uniform, out):
 
 
 _NAMES = ["prepare_matrix", "embedding", "add_rmsnorm", "add_rmsnorm_rows", "linear",
-          "qk_norm_rope_kv_write", "rope_neox", "rope_table", "place_tokens", "attention_fuses_rotary", "plan_attention", "paged_attention", "silu_mul", "linear_silu_mul",
+          "qk_norm_rope_kv_write", "rope_neox", "rope_table", "place_tokens", "swiglu_fused_applies", "attention_fuses_rotary", "plan_attention", "paged_attention", "silu_mul", "linear_silu_mul",
           "argmax", "sample"]
 
 

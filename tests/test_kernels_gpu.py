@@ -108,6 +108,25 @@ def test_linear_tcgen05_pairs(M, N, K, out_f32):
     _close(got, want, torch.bfloat16, scale=float(want.float().abs().max()))
 
 
+@pytest.mark.parametrize("M,I,K", [(256, 128, 64), (300, 200, 136), (2048, 3072, 1024), (1000, 1032, 72), (4100, 392, 200)])
+@pytest.mark.parametrize("out_f32", [False, True])
+def test_linear_swiglu_fused(M, I, K, out_f32):
+    """silu(x w_gate^T) * (x w_up^T) out of the epilogue of the CTA-pair product over the stacked
+    weights (the activation is formed on the float32 sums; the two-kernel route rounds gate and up
+    to bfloat16 first: both are compared with the plain float32 formula); edges in M, I and K."""
+    x = _randn((M, K), torch.bfloat16, 36)
+    w = _randn((2 * I, K), torch.bfloat16, 37, 0.1)
+    g = x.float() @ w[:I].float().t()
+    u = x.float() @ w[I:].float().t()
+    want = g / (1 + torch.exp(-g)) * u
+    odt = torch.float32 if out_f32 else torch.bfloat16
+    got = torch.full((M, I), float("nan"), dtype=odt, device=DEV)
+    ops.linear_swiglu(x.to(DEV), w.to(DEV), got)
+    torch.cuda.synchronize()
+    assert ops.tcgen05_status() == 0
+    _close(got, want, torch.bfloat16, scale=float(want.abs().max()), tol16=1e-2)
+
+
 @pytest.mark.parametrize("M", [17, 31, 48, 64])
 @pytest.mark.parametrize("N,K", [(3072, 64), (3080, 1024), (6144, 1032), (4100, 200)])
 @pytest.mark.parametrize("out_f32", [False, True])
