@@ -7,19 +7,16 @@ scheduler, the step function and the sampler on the device.
 from __future__ import annotations
 
 import time
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Callable, Optional, Sequence as Seq, Union
 
-import torch
-
+from ..cache.manager import UNKNOWN_TOKEN
 from ..config import EngineConfig, ModelConfig, parse_dtype
 from ..sampling.params import SamplingParams
-from ..sampling.sampler import Sampler, uniform_for
+from ..sampling.sampler import SampledTokens, Sampler, uniform_for
 from .loading import LoadedModel, load_model
-from ..cache.manager import UNKNOWN_TOKEN
-from ..sampling.sampler import SampledTokens
 from .runner import StepEntry
-from .scheduler import ScheduledSeq, Scheduler, SchedulerOutput
+from .scheduler import Scheduler, SchedulerOutput
 from .sequence import Sequence, SequenceStatus
 
 

@@ -12,7 +12,7 @@ final norm and the head run on the rows whose logits are wanted only.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Optional
 
 import torch

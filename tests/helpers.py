@@ -1,7 +1,6 @@
 """Shared by the tests: the tiny configurations, model folders, tolerances, traces."""
 from __future__ import annotations
 
-import os
 import random
 
 import torch
