@@ -45,8 +45,9 @@ __device__ __forceinline__ void rope_d128_finish(const RopeD128Args& A, int t, i
     if (!write_kv) return;
     const int h = head - Hq - Hkv;
     const int slot = slot_mapping[t];
-    const int page = slot / page_size, off = slot - page * page_size;
-    *reinterpret_cast<uint2*>(pages + ((((size_t)page * 2 + 1) * Hkv + h) * page_size + off) * D + 4 * lane) = raw;
+    // slot = page * page_size + off: the row of (page, V, h, off) is slot + (page * (2 Hkv - 1) + Hkv + h) * page_size
+    const int page = (page_size & (page_size - 1)) == 0 ? slot >> (__ffs(page_size) - 1) : slot / page_size;
+    *reinterpret_cast<uint2*>(pages + ((size_t)slot + ((size_t)page * (2 * Hkv - 1) + Hkv + h) * page_size) * D + 4 * lane) = raw;
     return;
   }
   const bool is_q = head < Hq;
@@ -66,18 +67,22 @@ __device__ __forceinline__ void rope_d128_finish(const RopeD128Args& A, int t, i
     f[0] = f[0] * rstd * wv.x; f[1] = f[1] * rstd * wv.y; f[2] = f[2] * rstd * wv.z; f[3] = f[3] * rstd * wv.w;
   }
   if (inv_freq) {
-    const float pos = (float)positions[t];
+    float cs[4], sn[4];
+    if (A.cos_sin) {
+      // the lane's four (cos, sin) pairs lie side by side in the step's table: two 16-byte loads
+      const float4* tp = reinterpret_cast<const float4*>(A.cos_sin + (size_t)t * 64 + ((4 * lane) & 63));
+      const float4 t01 = __ldg(tp), t23 = __ldg(tp + 1);
+      cs[0] = t01.x; sn[0] = t01.y; cs[1] = t01.z; sn[1] = t01.w;
+      cs[2] = t23.x; sn[2] = t23.y; cs[3] = t23.z; sn[3] = t23.w;
+    } else {
+      const float pos = (float)positions[t];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sincosf(pos * inv_freq[(4 * lane + i) & 63], &sn[i], &cs[i]);
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const float partner = __shfl_xor_sync(0xffffffffu, f[i], 16);
-      float sn, cs;
-      if (A.cos_sin) {
-        const float2 t2 = __ldg(A.cos_sin + (size_t)t * 64 + ((4 * lane + i) & 63));
-        cs = t2.x; sn = t2.y;
-      } else {
-        sincosf(pos * inv_freq[(4 * lane + i) & 63], &sn, &cs);
-      }
-      f[i] = lane < 16 ? cs * f[i] - sn * partner : sn * partner + cs * f[i];
+      f[i] = lane < 16 ? cs[i] * f[i] - sn[i] * partner : sn[i] * partner + cs[i] * f[i];
     }
   }
   uint2 res;
@@ -89,8 +94,8 @@ __device__ __forceinline__ void rope_d128_finish(const RopeD128Args& A, int t, i
   *reinterpret_cast<uint2*>(x) = res;
   if (!is_q && write_kv) {
     const int slot = slot_mapping[t];
-    const int page = slot / page_size, off = slot - page * page_size;
-    *reinterpret_cast<uint2*>(pages + ((((size_t)page * 2 + 0) * Hkv + h) * page_size + off) * D + 4 * lane) = res;
+    const int page = (page_size & (page_size - 1)) == 0 ? slot >> (__ffs(page_size) - 1) : slot / page_size;
+    *reinterpret_cast<uint2*>(pages + ((size_t)slot + ((size_t)page * (2 * Hkv - 1) + h) * page_size) * D + 4 * lane) = res;
   }
 }
 
