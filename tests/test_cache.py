@@ -120,6 +120,36 @@ def test_a_page_is_sharable_only_once_it_is_full_and_written():
     assert c.num_tokens == 8
 
 
+def test_a_page_with_a_token_not_yet_known_is_sharable_once_it_is_known():
+    """A step launched ahead runs a token whose id is still on the device: the request's record
+    holds UNKNOWN_TOKEN in its place, the page it completes is not offered for sharing, and later
+    pages wait too (their hashes chain through it), until resolve_token brings the id."""
+    from qwen_engine_b200.cache.manager import UNKNOWN_TOKEN
+    cm = _manager()
+    a = cm.open("a", known_tokens=[1, 2, 3])
+    _feed(cm, a, [1, 2, 3])
+    _feed(cm, a, [UNKNOWN_TOKEN])                     # completes the first page of 4
+    assert a.first_unknown == 3 and a.hashes[0] == []
+    _feed(cm, a, [UNKNOWN_TOKEN])                     # a second one before the first is known
+    cm.resolve_token(a, 3, 40)
+    assert a.first_unknown == 4 and len(a.hashes[0]) == 1 and a.tokens[:4] == [1, 2, 3, 40]
+    _feed(cm, a, [6, 7, 8])                           # fills the second page, whose first token is not known yet
+    assert len(a.hashes[0]) == 1
+    cm.resolve_token(a, 4, 50)
+    assert a.first_unknown is None and len(a.hashes[0]) == 2
+    with pytest.raises(RuntimeError):
+        cm.resolve_token(a, 4, 51)                    # nothing waits there any more
+    b = cm.open("b", known_tokens=[1, 2, 3, 40, 50, 6, 7, 8, 9])
+    assert b.num_tokens == 8                          # both pages found by their tokens
+    wrong = cm.open("c", known_tokens=[1, 2, 3, 41, 50, 6, 7, 8, 9])
+    assert wrong.num_tokens == 0
+    for rc in (a, b, wrong):
+        cm.close(rc)
+    cm.check_invariants()
+    # a request that ended before its token arrived is passed over
+    cm.resolve_token(a, 3, 1)
+
+
 def test_freed_pages_stay_findable_until_they_are_reused():
     cm = _manager(num_pages=4)
     a = cm.open("a")

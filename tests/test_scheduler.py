@@ -183,3 +183,47 @@ def test_prefix_hits_are_counted_and_preempted_work_comes_back_cheaply():
     out = s.schedule()
     assert [(x.start, x.num_tokens) for x in out.scheduled] == [(8, 3)]
     assert b.shared_prefix_len == 8 and s.prefix_hit_tokens == 8
+
+
+def test_tokens_with_a_place_kept_for_them_holds_and_late_stops():
+    """What the engine does when it launches a step ahead: the requests' outputs get a place
+    (UNKNOWN_TOKEN) for the token on its way, a request that ends by a count with that token is
+    held back from the next step, the step launched ahead is scheduled from the lengths alone,
+    update() puts the tokens into their places, and a request that ended by a stop token is
+    passed over when the step that still carried it reports."""
+    from qwen_engine_b200.cache.manager import UNKNOWN_TOKEN
+    cm, s = _setup(num_pages=32)
+    a = _seq(0, 3, max_new=2)                          # ends by the count after two tokens
+    b = _seq(1, 5, max_new=9, stop_token_ids=(9,), ignore_eos=True)
+    c = _seq(2, 4, max_new=9)
+    for x in (a, b, c):
+        s.add(x)
+    first = s.schedule()
+    assert [x.num_tokens for x in first.scheduled] == [3, 5, 4]
+    s.update(first, _fake_step(cm, first, lambda seq: 7))
+    cur = s.schedule()                                  # the step whose tokens are "on the device"
+    step_tokens = _fake_step(cm, cur, lambda seq: 9 if seq is b else 8)
+    # ahead: places for cur's tokens; a ends with its second token whatever it is
+    placed = {}
+    for sch in cur.scheduled:
+        sch.seq.hold = s.ends_by_length_after(sch.seq, 1)
+        placed[sch.seq.seq_id] = sch.seq.output_len
+        sch.seq.output_token_ids.append(UNKNOWN_TOKEN)
+    assert a.hold and not b.hold and not c.hold
+    ahead = s.schedule()
+    assert [x.seq.seq_id for x in ahead.scheduled] == [1, 2] and not ahead.preempted and not ahead.admitted
+    assert ahead.scheduled[0].seq.get_tokens(ahead.scheduled[0].start, 1) == [UNKNOWN_TOKEN]
+    ahead_tokens = _fake_step(cm, ahead, lambda seq: 5)
+    assert b.cache.first_unknown == b.prompt_len + 1
+    # cur's tokens arrive: into their places; a ends by the count, b by its stop token
+    ended = s.update(cur, step_tokens, placed)
+    assert {x.seq_id: x.finish_reason for x in ended} == {0: "length", 1: "stop"}
+    assert a.output_token_ids == [7, 8] and b.output_token_ids == [7, 9] and c.output_token_ids == [7, 8]
+    assert c.cache.first_unknown is None and c.cache.tokens[-1] == 8
+    # the step launched ahead reports: b is passed over, c goes on
+    ended = s.update(ahead, ahead_tokens)
+    assert ended == [] and b.output_token_ids == [7, 9] and c.output_token_ids == [7, 8, 5]
+    cm.check_invariants()
+    assert [x.seq_id for x in s.running] == [2]
+    with pytest.raises(RuntimeError):
+        s.update(cur, {2: 1}, {2: 0})                   # no place is waiting there
