@@ -21,6 +21,10 @@ _lib = None
 
 ATTN_TILE_Q = 16        # queries per work item of the generic attention kernel
 SMALL_M_MAX = 64        # rows up to which the weight-streaming product is used
+SPLITK = True           # products of some tens of rows by clusters of CTAs that share K (gemm_tcgen05_splitk.cu)
+SPLITK_MIN_M = 17       # rows from which, up to SPLITK_MAX_M, that kernel serves
+SPLITK_MAX_M = 64
+SPLITK_MAX_CTAS = 148   # clusters x CTAs at most: all on the GPU at once
 SWAP_MIN_M = 17         # rows from which, up to SMALL_M_MAX, wide products go to the swapped tcgen05 kernel
 SWAP_MIN_N = 3072       # weight rows from which it has enough CTAs (one per 128) to pull the weights fast enough
 SWIGLU_FUSED = True     # SiLU-mul in the epilogue of the gate/up product where the CTA-pair kernel serves it
@@ -383,12 +387,46 @@ def _linear_normed(x: NormedInput, w: torch.Tensor, out: torch.Tensor) -> bool:
     return True
 
 
+def splitk_splits(M: int, N: int, K: int, dtype: torch.dtype) -> int:
+    """How many CTAs share a tile of 128 weight rows, each with a share of K, in the product of some tens
+    of rows (``linear_splitk``): as many of 8, 4, 2 as keep all clusters on the GPU at once; 0 where that
+    kernel does not apply (few rows, enough weight rows for every SM, other types)."""
+    if not (TCGEN05_ENABLED and SPLITK and _program is None and dtype == torch.bfloat16
+            and SPLITK_MIN_M <= M <= SPLITK_MAX_M and K % 8 == 0 and N % 4 == 0):
+        return 0
+    tiles = -(-N // 128)
+    for s in (8, 4, 2):
+        if tiles * s <= SPLITK_MAX_CTAS and -(-K // 64) >= 2 * s:
+            return s
+    return 0
+
+
+def linear_splitk(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, splits: int, add: bool = False) -> None:
+    """``linear`` in bfloat16 for up to 64 rows by clusters of ``splits`` CTAs that share 128 weight rows
+    and meet through distributed shared memory; ``add``: out (float32) += the product."""
+    M, K = x.shape
+    N = w.shape[0]
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape == (N, K), "linear_splitk: bfloat16 operands, w [N, K]")
+    _need(out.shape == (M, N) and out.dtype in (torch.bfloat16, torch.float32) and (not add or out.dtype == torch.float32),
+          "linear_splitk: out must be [M, N], float32 to be added to")
+    _need(x.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "linear_splitk: operands must be contiguous")
+    mode = 2 if add else int(out.dtype == torch.float32)
+    _check(lib().qe_linear_tcgen05_splitk(_ptr(x), _ptr(w), _ptr(out), M, N, K, int(splits), mode, _stream()), "linear_splitk")
+
+
 def _linear_into_stream(x: torch.Tensor, w: torch.Tensor, sink: ResidualSink, silu: bool) -> bool:
     """The fused route for a ResidualSink: resid += product, sums of squares left behind."""
     st = sink.stream
     M = x.shape[0]
     K = x.shape[1] // 2 if silu else x.shape[1]
     N = w.shape[0]
+    if not silu and x.is_cuda and not st.has_delta and st.resid.shape == (M, N) and st.resid.is_contiguous():
+        splits = splitk_splits(M, N, K, x.dtype)
+        if splits:
+            # some tens of rows: clusters that share K add their sum to the stream in their epilogue
+            linear_splitk(x, w, st.resid, splits, add=True)
+            st.n_ssq = 0
+            return True
     if not (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M <= min(SMALL_M_MAX, RESID_SINK_MAX_M) and K % 8 == 0
             and not st.has_delta and st.ssq is not None and st.ssq.shape[1] >= -(-N // 16)
             and st.resid.shape == (M, N)):
@@ -418,6 +456,10 @@ def linear(x, w: torch.Tensor, out: torch.Tensor) -> None:
     _need(out.shape == (M, N) and out.dtype in (x.dtype, torch.float32), "linear: out must be [M, N] in x's dtype or float32")
     _need(x.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "linear: operands must be contiguous")
     out_f32 = int(out.dtype == torch.float32)
+    splits = splitk_splits(M, N, K, x.dtype)
+    if splits:
+        linear_splitk(x, w, out, splits)
+        return
     if (x.dtype == torch.bfloat16 and SWAP_MIN_M <= M <= SMALL_M_MAX and N >= SWAP_MIN_N and K % 8 == 0
             and TCGEN05_ENABLED and _program is None):
         # some tens of rows and many weight rows: the weights on the 128-row side of tcgen05.mma
@@ -481,7 +523,7 @@ def linear_silu_mul(gate_up: torch.Tensor, w: torch.Tensor, out: torch.Tensor, s
     M, I2 = gate_up.shape
     I = I2 // 2
     N = w.shape[0]
-    if M > FUSED_SILU_MAX_M or I > FUSED_SILU_MAX_K:
+    if M > FUSED_SILU_MAX_M or I > FUSED_SILU_MAX_K or splitk_splits(M, N, I, gate_up.dtype):
         act = scratch((M, I), gate_up.dtype)
         silu_mul(gate_up, act)
         linear(act, w, out)
@@ -519,8 +561,9 @@ def tcgen05_status() -> int:
     """0 if no bounded wait of the tcgen05 product kernels ever ran out; else the code of the first
     that did (1: a shared-memory slot never came free, 2: TMA bytes never landed, 3: the
     accumulator never completed, 4: an accumulator was never read out; 11-13: the same as 1-3 in the
-    kernel for some tens of rows).  Synchronises the device."""
-    return int(lib().qe_gemm_tc_status()) or int(lib().qe_gemm_tc_swap_status()) or int(lib().qe_gemm_tc_pair_status())
+    kernel for some tens of rows, 21-23 in its form that shares K within a cluster).  Synchronises the device."""
+    return (int(lib().qe_gemm_tc_status()) or int(lib().qe_gemm_tc_swap_status()) or int(lib().qe_gemm_tc_pair_status())
+            or int(lib().qe_gemm_tc_splitk_status()))
 
 
 ROPE_TABLE_MIN_T = 64   # tokens from which a step's rotation angles are computed once (below: in the kernel)

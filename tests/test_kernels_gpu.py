@@ -130,10 +130,11 @@ def test_linear_swiglu_fused(M, I, K, out_f32):
 @pytest.mark.parametrize("M", [17, 31, 48, 64])
 @pytest.mark.parametrize("N,K", [(3072, 64), (3080, 1024), (6144, 1032), (4100, 200)])
 @pytest.mark.parametrize("out_f32", [False, True])
-def test_linear_tcgen05_swapped(M, N, K, out_f32):
+def test_linear_tcgen05_swapped(M, N, K, out_f32, monkeypatch):
     """Some tens of rows against many weight rows in bfloat16: the kernel with the weights on the
     128-row side of the instruction; edges in M (not a multiple of 16), N and K."""
     assert ops.SWAP_MIN_M <= M <= ops.SMALL_M_MAX and N >= ops.SWAP_MIN_N
+    monkeypatch.setattr(ops, "SPLITK", False)
     x = _randn((M, K), torch.bfloat16, 18)
     w = _randn((N, K), torch.bfloat16, 19, 0.1)
     odt = torch.float32 if out_f32 else torch.bfloat16
@@ -144,6 +145,55 @@ def test_linear_tcgen05_swapped(M, N, K, out_f32):
     torch.cuda.synchronize()
     assert ops.tcgen05_status() == 0
     _close(got, want, torch.bfloat16, scale=float(want.float().abs().max()))
+
+
+@pytest.mark.parametrize("M", [1, 17, 33, 64])
+@pytest.mark.parametrize("N,K,splits", [(1024, 2048, 8), (1024, 3072, 8), (1000, 1032, 4), (132, 200, 2), (4096, 1024, 4),
+                                        (256, 192, 8), (6144, 1024, 2)])
+@pytest.mark.parametrize("mode", ["bf16", "f32", "add"])
+def test_linear_splitk(M, N, K, splits, mode):
+    """Up to 64 rows against few weight rows in bfloat16: clusters of CTAs that share K and add their partial
+    sums through distributed shared memory; edges in M, N and K, a K that leaves some CTAs of a
+    cluster without a share (192 = 3 blocks for 8 CTAs), and the sum added to a float32 stream."""
+    x = _randn((M, K), torch.bfloat16, 28)
+    w = _randn((N, K), torch.bfloat16, 29, 0.1)
+    odt = torch.bfloat16 if mode == "bf16" else torch.float32
+    want = torch.empty(M, N, dtype=torch.float32)
+    ref_ops.linear(x, w, want)
+    if mode == "add":
+        start = _randn((M, N), torch.float32, 30)
+        want = want + start
+        got = start.to(DEV)
+    else:
+        got = torch.full((M, N), float("nan"), dtype=odt, device=DEV)
+    ops.linear_splitk(x.to(DEV), w.to(DEV), got, splits, add=mode == "add")
+    torch.cuda.synchronize()
+    assert ops.tcgen05_status() == 0
+    _close(got, want.to(odt), odt, scale=float(want.abs().max()), tol16=8e-3)
+    # the same call again gives the same bits: the order of the sum is fixed
+    again = start.to(DEV) if mode == "add" else torch.empty_like(got)
+    ops.linear_splitk(x.to(DEV), w.to(DEV), again, splits, add=mode == "add")
+    assert torch.equal(again, got)
+
+
+def test_linear_picks_splitk():
+    """`linear` sends some tens of rows to the cluster kernel where the weight rows are too few for every SM, also
+    when the product is added to the residual stream; a few rows and many rows go elsewhere."""
+    assert ops.splitk_splits(64, 1024, 3072, torch.bfloat16) == 8
+    assert ops.splitk_splits(17, 4096, 1024, torch.bfloat16) == 4
+    assert ops.splitk_splits(32, 6144, 1024, torch.bfloat16) == 2
+    assert ops.splitk_splits(8, 1024, 3072, torch.bfloat16) == 0
+    assert ops.splitk_splits(65, 1024, 3072, torch.bfloat16) == 0
+    assert ops.splitk_splits(64, 151936, 1024, torch.bfloat16) == 0
+    assert ops.splitk_splits(64, 1024, 3072, torch.float32) == 0
+    M, N, K = 40, 1024, 3072
+    x = _randn((M, K), torch.bfloat16, 31)
+    w = _randn((N, K), torch.bfloat16, 32, 0.1)
+    want = torch.empty(M, N, dtype=torch.float32)
+    ref_ops.linear(x, w, want)
+    got = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    ops.linear(x.to(DEV), w.to(DEV), got)
+    _close(got, want.to(torch.bfloat16), torch.bfloat16, scale=float(want.abs().max()))
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 128, 256), (65, 128, 64), (300, 200, 136), (2048, 4096, 1024),
