@@ -20,6 +20,12 @@
 // Work items, parts and the merge by the CTA that finishes a request's last part are those of the
 // mma.sync kernel (attention_flash.cuh): same item layout, same scratch layout, same counters.
 //
+// CL: every request is cut into the same number of parts (2, 4 or 8) and the parts of a request are
+// the CTAs of one thread-block cluster.  Then the parts never leave the chip: each CTA keeps its
+// accumulator, max and sum in its shared memory, the cluster meets at a barrier, and its first CTA
+// combines the parts through distributed shared memory (same formula, same order) and writes the
+// output; no scratch memory, no counters, no round trips to L2 at the end of the kernel.
+//
 // FUSE: the kernel takes q, k and v as the QKV product left them and does what the rotary kernel
 // would have done in between (elementwise.cu, rope_d128.cuh: per-head RMS norm of q and k, rotation
 // of both by position x inverse frequency, the new keys and values into the cache), with the same
@@ -33,6 +39,7 @@
 #define AD_CH 160               // keys per chunk: 5 passes of 32
 #define AD_PASSES (AD_CH / 32)
 #define AD_D 128
+#define AD_PART_ALIGN 16        // a request's parts are multiples of this many keys
 
 struct AdFuse {
   const __nv_bfloat16* k; const __nv_bfloat16* v;   // the step's keys and values [T, Hkv, 128], strides as q's
@@ -50,6 +57,7 @@ struct AdSmem {
   float m_run[R], l_run[R], alpha[R];
   int tab[2][AD_CH + 2];                // pages of a chunk's keys (one entry per page the chunk touches)
   int last;
+  float fin[R][AD_D];                   // CL: this part's accumulator, for the cluster's first CTA
   alignas(16) float2 cs[R][64];         // FUSE: (cos, sin) of the rows' tokens' angles
   alignas(16) __nv_bfloat16 knew[R][AD_D];   // FUSE: the new tokens' keys after norm and rotation
 };
@@ -84,7 +92,7 @@ __device__ __forceinline__ void ad_norm_rotate(float (&x)[16], const float* w, f
   for (int i = 0; i < 16; ++i) x[i] = __bfloat162float(__float2bfloat16_rn(x[i]));
 }
 
-template <int R, bool FUSE>
+template <int R, bool FUSE, bool CL>
 __global__ void __launch_bounds__(AD_THREADS, 2)
 decode_attention_kernel(FaArgs A, AdFuse F) {
   static_assert(offsetof(AdSmem<R>, knew) % 16 == 0 && offsetof(AdSmem<R>, red) % 16 == 0 && offsetof(AdSmem<R>, cs) % 8 == 0,
@@ -109,7 +117,8 @@ decode_attention_kernel(FaArgs A, AdFuse F) {
   if (n_splits > 0) {
     const int total = ctx + q_len;
     const int lo = window > 0 ? max(0, ctx - window + 1) / FA_BN * FA_BN : 0;
-    const int per = ((total - lo + n_splits - 1) / n_splits + FA_BN - 1) / FA_BN * FA_BN;
+    // (parts of equal length up to 16 keys: this kernel has no key tiles that a part should be a multiple of)
+    const int per = ((total - lo + n_splits - 1) / n_splits + AD_PART_ALIGN - 1) / AD_PART_ALIGN * AD_PART_ALIGN;
     kv_lo = lo + split * per;
     kv_hi_item = min(total, kv_lo + per);
   }
@@ -118,8 +127,7 @@ decode_attention_kernel(FaArgs A, AdFuse F) {
   if (window > 0) kv_begin = max(kv_begin, first_pos - window + 1);
   const int n_chunks = kv_end > kv_begin ? (kv_end - kv_begin + AD_CH - 1) / AD_CH : 0;
   // FUSE: this CTA's keys include the new tokens' positions (they lie together at the end of the
-  // request, and parts are cut at multiples of 64 keys while a tile holds at most 64 / G tokens; a
-  // tile whose tokens straddle two parts is not launched with FUSE)
+  // request; a tile whose tokens straddle two parts is not launched with FUSE: every item holds one token)
   const bool own_new = FUSE && F.pages_out != nullptr && kv_begin <= first_pos && kv_end >= first_pos + ntok;
 
   const int* table = A.block_tables + (size_t)req * A.max_blocks;
@@ -369,7 +377,9 @@ decode_attention_kernel(FaArgs A, AdFuse F) {
 #pragma unroll
     for (int w = 0; w < AD_THREADS / 32; ++w) acc += sm.red[w][r][d];
     const float l = sm.l_run[r];
-    if (part < 0) {
+    if constexpr (CL) {
+      sm.fin[r][d] = acc;
+    } else if (part < 0) {
       const int ti = r / G, hg = r - ti * G;
       out_row0[(size_t)ti * ((size_t)Hq * D) + (size_t)(hkv * G + hg) * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
     } else {
@@ -377,6 +387,44 @@ decode_attention_kernel(FaArgs A, AdFuse F) {
       A.part_acc[slot * D + d] = acc;
       if (d == 0) { A.part_ml[2 * slot] = sm.m_run[r]; A.part_ml[2 * slot + 1] = l; }
     }
+  }
+  if constexpr (CL) {
+    // ---- the parts meet in the cluster's first CTA -------------------------------------------------------
+    cluster_sync_all();                             // every part's accumulator, max and sum are in place
+    if (cluster_cta_rank() == 0) {
+      const int S = (int)cluster_num_ctas();        // = n_splits, at most 8
+      for (int e = tid; e < nrows * D; e += AD_THREADS) {
+        const int r = e / D, d = e - r * D;
+        float mm[8], ll[8], aa[8];
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp) {
+          mm[sp] = -INFINITY; ll[sp] = 0.f; aa[sp] = 0.f;
+          if (sp < S) {
+            mm[sp] = cluster_ld_f32(cluster_map_shared(&sm.m_run[r], (uint32_t)sp));
+            ll[sp] = cluster_ld_f32(cluster_map_shared(&sm.l_run[r], (uint32_t)sp));
+            aa[sp] = cluster_ld_f32(cluster_map_shared(&sm.fin[r][d], (uint32_t)sp));
+          }
+        }
+        // out = sum_s 2^(m_s - m) acc_s / sum_s 2^(m_s - m) l_s, in float32, in the order of the parts
+        float m = -INFINITY;
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp) m = fmaxf(m, mm[sp]);
+        const float mb = m == -INFINITY ? 0.f : m;
+        float l = 0.f, acc = 0.f;
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp) {
+          if (sp < S) {
+            const float wgt = exp2f(mm[sp] - mb);
+            l += wgt * ll[sp];
+            acc += wgt * aa[sp];
+          }
+        }
+        const int ti = r / G, hg = r - ti * G;
+        out_row0[(size_t)ti * ((size_t)Hq * D) + (size_t)(hkv * G + hg) * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+      }
+    }
+    cluster_sync_all();                             // nobody reads this CTA's shared memory any more
+    return;
   }
   // ---- the CTA that finishes a request's last part combines the parts ---------------------------------
   if (part >= 0 && A.counters != nullptr && n_splits > 0) {
@@ -412,18 +460,31 @@ decode_attention_kernel(FaArgs A, AdFuse F) {
   }
 }
 
-template <int R, bool FUSE>
-static int launch_decode(const FaArgs& fa, const AdFuse& fu, int n_items, int Hkv, cudaStream_t stream) {
+template <int R, bool FUSE, bool CL>
+static int launch_decode_as(const FaArgs& fa, const AdFuse& fu, int n_items, int Hkv, int cluster, cudaStream_t stream) {
   const size_t smem = sizeof(AdSmem<R>);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<R, FUSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<R, FUSE, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) QE_REFUSE("decode_attention: shared memory %zu: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  qe_launch(decode_attention_kernel<R, FUSE>, dim3(n_items, Hkv), dim3(AD_THREADS), smem, stream, fa, fu);
+  if (CL)
+    qe_launch_cluster(decode_attention_kernel<R, FUSE, CL>, dim3(n_items, Hkv), dim3(AD_THREADS), smem, stream, (unsigned)cluster, fa, fu);
+  else
+    qe_launch(decode_attention_kernel<R, FUSE, CL>, dim3(n_items, Hkv), dim3(AD_THREADS), smem, stream, fa, fu);
   QE_CHECK_LAUNCH("decode_attention");
   return 0;
+}
+
+// cluster: 0, or the number of parts of every request (2, 4 or 8) when the items are exactly those
+// parts, request by request in the order of the parts: then the parts of a request form a cluster
+template <int R, bool FUSE>
+static int launch_decode(const FaArgs& fa, const AdFuse& fu, int n_items, int Hkv, int cluster, cudaStream_t stream) {
+  if (cluster == 0) return launch_decode_as<R, FUSE, false>(fa, fu, n_items, Hkv, 0, stream);
+  if ((cluster != 2 && cluster != 4 && cluster != 8) || n_items % cluster)
+    QE_REFUSE("decode_attention: %d items cannot form clusters of %d", n_items, cluster);
+  return launch_decode_as<R, FUSE, true>(fa, fu, n_items, Hkv, cluster, stream);
 }
 
 // Whether the kernel takes this geometry with at most max_rows rows (token x head of the group) per item.
@@ -433,23 +494,24 @@ extern "C" int qe_decode_attention_supported(int Hq, int Hkv, int D, int max_row
 
 // Same arguments as qe_flash_attention_fused_merge's (attention_flash.cu) where they share a name;
 // every item has at most max_rows rows; parts are combined by the CTA that finishes last (counters
-// as there).  Returns 0 when run, 1 when refused, 2 on a launch error.
+// as there), or inside clusters (`cluster`, see launch_decode; scratch and counters are then unused).
+// Returns 0 when run, 1 when refused, 2 on a launch error.
 extern "C" int qe_decode_attention(const void* q, long q_stride, const void* pages, const int* block_tables,
                                    int max_blocks, const int* items, int n_items, void* out, float* part_acc,
-                                   float* part_ml, int part_rows, int* counters, int max_rows, float scale, int window,
-                                   int Hq, int Hkv, int D, int page_size, cudaStream_t stream) {
+                                   float* part_ml, int part_rows, int* counters, int max_rows, int cluster, float scale,
+                                   int window, int Hq, int Hkv, int D, int page_size, cudaStream_t stream) {
   if (n_items <= 0) return 0;
   if (!qe_decode_attention_supported(Hq, Hkv, D, max_rows))
     QE_REFUSE("decode_attention: heads %d/%d, head_dim %d, %d rows are not supported", Hq, Hkv, D, max_rows);
   if ((((uintptr_t)q | (uintptr_t)pages) & 15) || (q_stride % 8)) QE_REFUSE("decode_attention: operands must be 16-byte aligned");
-  if (part_acc && counters == nullptr) QE_REFUSE("decode_attention: parts need the counters");
+  if (part_acc && counters == nullptr && !cluster) QE_REFUSE("decode_attention: parts need the counters");
   FaArgs fa{(const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pages, block_tables, max_blocks, items,
             (__nv_bfloat16*)out, part_acc, part_ml, part_rows, counters, scale * 1.4426950408889634f, window, Hq, Hkv,
             page_size};
   const AdFuse none{};
-  if (max_rows <= 1) return launch_decode<1, false>(fa, none, n_items, Hkv, stream);
-  if (max_rows <= 2) return launch_decode<2, false>(fa, none, n_items, Hkv, stream);
-  return launch_decode<4, false>(fa, none, n_items, Hkv, stream);
+  if (max_rows <= 1) return launch_decode<1, false>(fa, none, n_items, Hkv, cluster, stream);
+  if (max_rows <= 2) return launch_decode<2, false>(fa, none, n_items, Hkv, cluster, stream);
+  return launch_decode<4, false>(fa, none, n_items, Hkv, cluster, stream);
 }
 
 // The same with the per-head norm, the rotation and the cache write of the step's q, k, v done here
@@ -458,7 +520,7 @@ extern "C" int qe_decode_attention(const void* q, long q_stride, const void* pag
 // keys are there already; only the queries are normed and rotated).  Every item must hold one token.
 extern "C" int qe_decode_attention_fused(const void* qkv, long q_stride, void* pages, const int* block_tables,
                                          int max_blocks, const int* items, int n_items, void* out, float* part_acc,
-                                         float* part_ml, int part_rows, int* counters, int max_rows, float scale,
+                                         float* part_ml, int part_rows, int* counters, int max_rows, int cluster, float scale,
                                          int window, const float* qw, const float* kw, float eps, const float* inv_freq,
                                          int write_kv, int Hq, int Hkv, int D, int page_size, cudaStream_t stream) {
   if (n_items <= 0) return 0;
@@ -466,14 +528,14 @@ extern "C" int qe_decode_attention_fused(const void* qkv, long q_stride, void* p
     QE_REFUSE("decode_attention_fused: heads %d/%d, head_dim %d, %d rows are not supported", Hq, Hkv, D, max_rows);
   if ((((uintptr_t)qkv | (uintptr_t)pages | (uintptr_t)qw | (uintptr_t)kw) & 15) || (q_stride % 8))
     QE_REFUSE("decode_attention_fused: operands must be 16-byte aligned");
-  if (part_acc && counters == nullptr) QE_REFUSE("decode_attention_fused: parts need the counters");
+  if (part_acc && counters == nullptr && !cluster) QE_REFUSE("decode_attention_fused: parts need the counters");
   if (!inv_freq) QE_REFUSE("decode_attention_fused: needs the inverse frequencies");
   const __nv_bfloat16* q = (const __nv_bfloat16*)qkv;
   FaArgs fa{q, q_stride, (const __nv_bfloat16*)pages, block_tables, max_blocks, items,
             (__nv_bfloat16*)out, part_acc, part_ml, part_rows, counters, scale * 1.4426950408889634f, window, Hq, Hkv,
             page_size};
   AdFuse fu{q + (size_t)Hq * D, q + (size_t)(Hq + Hkv) * D, qw, kw, eps, inv_freq, write_kv ? (__nv_bfloat16*)pages : nullptr};
-  if (max_rows <= 1) return launch_decode<1, true>(fa, fu, n_items, Hkv, stream);
-  if (max_rows <= 2) return launch_decode<2, true>(fa, fu, n_items, Hkv, stream);
-  return launch_decode<4, true>(fa, fu, n_items, Hkv, stream);
+  if (max_rows <= 1) return launch_decode<1, true>(fa, fu, n_items, Hkv, cluster, stream);
+  if (max_rows <= 2) return launch_decode<2, true>(fa, fu, n_items, Hkv, cluster, stream);
+  return launch_decode<4, true>(fa, fu, n_items, Hkv, cluster, stream);
 }

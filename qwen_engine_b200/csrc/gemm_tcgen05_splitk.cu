@@ -41,18 +41,6 @@ struct __align__(1024) SkSmem {
   int abort_flag;
 };
 
-__device__ __forceinline__ uint32_t sk_map_to_cta(uint32_t local_addr, uint32_t cta) {
-  uint32_t remote;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(local_addr), "r"(cta));
-  return remote;
-}
-__device__ __forceinline__ float4 sk_ld_cluster(uint32_t addr) {
-  float4 v;
-  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];\n"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
-  return v;
-}
-
 template <typename TOut, int S, int STAGES, bool RESID>
 __global__ void __launch_bounds__(SK_THREADS, 1)
 gemm_tcgen05_splitk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
@@ -162,16 +150,15 @@ gemm_tcgen05_splitk_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
   if (warp >= 2) {
     // ---- CTA r: tokens r, r + S, ...; a warp per token, a lane per 4 weight rows -----------------------
     const int w4 = warp - 2;
-    const uint32_t local = smem_u32(&sm.part[0][0]);
     uint32_t base[S];
 #pragma unroll
-    for (int s = 0; s < S; ++s) base[s] = sk_map_to_cta(local, (uint32_t)s);
+    for (int s = 0; s < S; ++s) base[s] = cluster_map_shared(&sm.part[0][0], (uint32_t)s);
     const int n = n0 + 4 * lane;
 #pragma unroll 2
     for (int c = rank + S * w4; c < M; c += 4 * S) {
       float4 v[S];
 #pragma unroll
-      for (int s = 0; s < S; ++s) v[s] = sk_ld_cluster(base[s] + (uint32_t)(c * SK_BM + 4 * lane) * 4u);
+      for (int s = 0; s < S; ++s) v[s] = cluster_ld_f32x4(base[s] + (uint32_t)(c * SK_BM + 4 * lane) * 4u);
       float4 acc = v[0];
 #pragma unroll
       for (int s = 1; s < S; ++s) { acc.x += v[s].x; acc.y += v[s].y; acc.z += v[s].z; acc.w += v[s].w; }

@@ -126,16 +126,6 @@ __device__ __forceinline__ void tc_dealloc(uint32_t tmem, uint32_t cols) {
 // this bit; with it cleared, an address names the even ("leading") CTA's copy.
 #define TC_PEER_BIT_MASK 0xFEFFFFFFu
 
-__device__ __forceinline__ uint32_t cluster_cta_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
-  return r;
-}
-// all threads of all CTAs of the cluster
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
-}
 // arrive on a barrier that may lie in the other CTA of the cluster (bar_addr: a shared::cluster address)
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" :: "r"(bar_addr) : "memory");

@@ -40,6 +40,7 @@ DECODE_ATTENTION = True         # decoded tokens (few rows per kv head, head siz
 # Off: measured on a B200 at batch 8, context 1024, the step is 4 % slower with it (the attention kernel,
 # which the step waits for, grows by more than the rotary kernel's launch costs).  Kept as a tested option.
 FUSE_ROTARY_IN_DECODE = False   # the decode attention kernel norms and rotates q, k and writes the cache itself
+DECODE_ATTENTION_CLUSTERS = True    # parts of a request as a thread-block cluster that combines them through distributed shared memory
 DECODE_ATTENTION_MAX_ROWS = 2   # rows (token x head of the group) per item up to which it is used (measured: with 4 rows the mma.sync kernel is 11 % ahead; the kernel takes up to 4)
 DECODE_ATTENTION_MAX_KEYS = 512 # context up to which it serves contexts that are not split (longer: the pipelined kernel)
 DECODE_ATTENTION_MIN_CTAS = 128 # CTAs from which it is used: measured, it gains where the GPU is full and loses a little below
@@ -688,7 +689,8 @@ def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
     ``geometries``: the (heads, kv heads, head size, window) of the model's attention layers.
     ``tiles`` serves the generic kernel; for each geometry the flash kernel takes, ``fa<i>_items``
     and ``fa<i>_merge`` hold its work and merge items and ``fa<i>_info`` = [parts, rows per part,
-    whether every item has at most 16 rows, the most rows of an item]; requests that bring many rows go to the tcgen05 kernel
+    whether every item has at most 16 rows, the most rows of an item, the number of parts of every
+    request if all are cut into the same 2, 4 or 8 parts (they can then form clusters) else 0]; requests that bring many rows go to the tcgen05 kernel
     instead where it takes the geometry: ``tc<i>_items`` and ``tc<i>_info`` = [parts, rows per part].
     ``uniform_splits`` (geometry -> number of parts) fixes the number of parts of every request,
     so that the lists depend on the batch's shape only (for steps replayed from a CUDA graph)."""
@@ -744,7 +746,9 @@ def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
         items = [x for _, item in whole for x in item] + items
         plan[f"fa{gi}_items"] = items
         plan[f"fa{gi}_merge"] = merge
-        plan[f"fa{gi}_info"] = [n_parts, part_rows, int(max_rows <= 16), max_rows]
+        sizes = {m for m in merge[3::4]}
+        same = sizes.pop() if len(sizes) == 1 and not whole else 0
+        plan[f"fa{gi}_info"] = [n_parts, part_rows, int(max_rows <= 16), max_rows, same if same in (2, 4, 8) else 0]
         if tc_tiles:
             tc_items, tc_parts = _plan_tc_tiles(tc_tiles, Hkv)
             plan[f"tc{gi}_items"] = tc_items
@@ -785,7 +789,7 @@ def _decode_kernel_serves(plan, key, ctx, qkv: torch.Tensor, Hkv: int, D: int) -
     decoded tokens: few rows per item, head size 128, enough CTAs to fill the GPU, contexts split or short."""
     if not DECODE_ATTENTION or key is None or f"fa{key}_items" not in plan or f"tc{key}_items" in plan or D != 128:
         return False
-    n_parts, part_rows, small_tiles, max_rows = plan[f"fa{key}_info_host"]
+    n_parts, part_rows, small_tiles, max_rows, same_parts = plan[f"fa{key}_info_host"]
     n_items = plan[f"fa{key}_items"].numel() // FLASH_ITEM_INTS
     return (1 <= max_rows <= DECODE_ATTENTION_MAX_ROWS and n_items > 0 and n_items * Hkv >= DECODE_ATTENTION_MIN_CTAS
             and n_parts * Hkv <= _MERGE_COUNTERS and qkv.stride(0) % 8 == 0
@@ -839,7 +843,7 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
             Hq, Hkv, D, int(kv_pages.shape[3]), _stream()), "flash_attention_tc")
     if key is not None and f"fa{key}_items" in plan:
         items, merge = plan[f"fa{key}_items"], plan[f"fa{key}_merge"]
-        n_parts, part_rows, small_tiles, max_rows = plan[f"fa{key}_info_host"]
+        n_parts, part_rows, small_tiles, max_rows, same_parts = plan[f"fa{key}_info_host"]
         n_items, n_merge = items.numel() // FLASH_ITEM_INTS, merge.numel() // 4
         part_acc = part_ml = None
         if n_parts:
@@ -854,12 +858,14 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
                          ptrs=[qkv, kv_pages, block_tables, items, out, part_acc, part_ml, counters])
             return
         serves = _decode_kernel_serves(plan, key, ctx, qkv, Hkv, D)
+        # every request in the same few parts: the parts of a request form a cluster and meet on chip
+        cluster = int(same_parts) if DECODE_ATTENTION_CLUSTERS and n_items == n_parts else 0
         _need(fused is None or serves, "paged_attention: this step cannot take the rotation into the attention kernel")
         if fused is not None:
             _check(lib().qe_decode_attention_fused(
                 _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(block_tables), int(block_tables.shape[1]),
                 _ptr(items), n_items, _ptr(out), _ptr(part_acc), _ptr(part_ml), int(part_rows), _ptr(counters),
-                int(max_rows), ctypes.c_float(scale), int(window), _ptr(fused["q_norm_w"]), _ptr(fused["k_norm_w"]),
+                int(max_rows), cluster, ctypes.c_float(scale), int(window), _ptr(fused["q_norm_w"]), _ptr(fused["k_norm_w"]),
                 ctypes.c_float(fused["eps"]), _ptr(fused["inv_freq"]), int(bool(fused["write_kv"])),
                 Hq, Hkv, D, int(kv_pages.shape[3]), _stream()), "decode_attention_fused")
             return
@@ -868,7 +874,7 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
             _check(lib().qe_decode_attention(
                 _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(block_tables), int(block_tables.shape[1]),
                 _ptr(items), n_items, _ptr(out), _ptr(part_acc), _ptr(part_ml), int(part_rows), _ptr(counters),
-                int(max_rows), ctypes.c_float(scale), int(window), Hq, Hkv, D, int(kv_pages.shape[3]), _stream()),
+                int(max_rows), cluster, ctypes.c_float(scale), int(window), Hq, Hkv, D, int(kv_pages.shape[3]), _stream()),
                 "decode_attention")
             return
         _check(lib().qe_flash_attention_fused_merge(

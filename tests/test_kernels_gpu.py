@@ -357,14 +357,16 @@ def _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, seed, spike=
                 ctx=torch.tensor(ctx_lens, dtype=torch.int32), T=T)
 
 
-def _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, fn, dev, flash=True):
+def _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, fn, dev, flash=True, uniform=None):
     """Run one implementation.  On the GPU ``flash`` lets the step's plan carry the tensor-core
-    kernel's work items (used when the kernel takes the geometry); without it the generic kernel runs."""
+    kernel's work items (used when the kernel takes the geometry); without it the generic kernel runs.
+    ``uniform``: every request's context in that many parts, as in a decode step replayed from a graph."""
     from qwen_engine_b200.engine.runner import ModelRunner
     from qwen_engine_b200.parts.base import Arena
     scale = 1.0 / math.sqrt(D)
     geos = ((Hq, Hkv, D, window),) if (flash and dev != "cpu") else ()
-    plan = ops.plan_attention(list(q_lens), list(ctx_lens), P, geos, dtype)
+    plan = ops.plan_attention(list(q_lens), list(ctx_lens), P, geos, dtype,
+                              uniform_splits={geos[0]: uniform} if uniform and geos else None)
     devplan = ModelRunner._device_plan(
         plan, {"plan_" + k: torch.tensor(v, dtype=torch.int32, device=dev) for k, v in plan.items()}, geos)
     ctx = SimpleNamespace(cu_q=case["cu_q"].to(dev), ctx_lens=case["ctx"].to(dev), attn_plan=devplan,
@@ -444,6 +446,35 @@ def test_decode_attention(Hq, Hkv, P, q_lens, ctx_lens, window):
         ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_KEYS, ops.DECODE_ATTENTION_MAX_ROWS = saved
     _close(other, want, dtype)
     assert ops.launch_count == launches + 2
+
+
+@pytest.mark.parametrize("Hq,Hkv,P", [(16, 8, 16), (4, 4, 8), (8, 1, 32), (6, 3, 4)])
+@pytest.mark.parametrize("ctx_lens", [[77], [5, 130, 333], [1024] * 8, [0, 63, 64, 1500], [2000, 1, 700]])
+@pytest.mark.parametrize("parts", [2, 4, 8])
+@pytest.mark.parametrize("window", [0, 100])
+def test_decode_attention_parts_in_clusters(Hq, Hkv, P, ctx_lens, parts, window):
+    """A decode step whose requests are all cut into the same 2, 4 or 8 parts: the parts of a request run as a
+    thread-block cluster and meet through distributed shared memory (also parts that hold no key at
+    all: short contexts, parts outside the window); the same items merged through scratch memory by the
+    last CTA give the same bits."""
+    D, dtype = 128, torch.bfloat16
+    q_lens = [1] * len(ctx_lens)
+    geo = (Hq, Hkv, D, window)
+    plan = ops.plan_attention(q_lens, list(ctx_lens), P, (geo,), dtype, uniform_splits={geo: parts})
+    assert plan["fa0_info"][4] == parts and plan["fa0_info"][0] == parts * len(ctx_lens)
+    case = _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, seed=45)
+    want = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ref_ops.paged_attention, "cpu")
+    saved = ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_ROWS
+    ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_ROWS = 1, 4
+    try:
+        got = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ops.paged_attention, DEV, uniform=parts)
+        ops.DECODE_ATTENTION_CLUSTERS = False
+        other = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ops.paged_attention, DEV, uniform=parts)
+    finally:
+        ops.DECODE_ATTENTION_CLUSTERS = True
+        ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_ROWS = saved
+    _close(got, want, dtype)
+    assert torch.equal(got, other)
 
 
 @pytest.mark.parametrize("Hq,Hkv,P", [(16, 8, 16), (4, 4, 8), (8, 2, 32), (4, 1, 16)])
