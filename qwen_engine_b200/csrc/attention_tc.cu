@@ -469,6 +469,78 @@ extern "C" void qe_flash_attention_tc_clear_status() {
   cudaMemcpyToSymbol(g_at_status, &v, sizeof(int));
 }
 
+// Host side: how to cut a step's tiles so that the CTAs keep all SMs busy to the end.  A tile of a
+// prompt visits as many key steps as its place in the prompt asks for, so the tiles of one prompt
+// are as unequal as 1 : 2 : ... : n, and with fewer tiles than a few per SM the longest tile alone sets
+// the kernel's time.  Given the tiles' key steps, this tries a few caps (the most steps a work item may
+// have; longer tiles are cut into parts of equal length, at most max_parts), lays each candidate's
+// items out as the GPU will run them (longest first, each to the SM that is free first, every item
+// once per kv head) and returns the cap with the shortest schedule, 0 for "cut nothing".  Costs are in
+// key steps: item_cost for a CTA's start and end, part_cost on top for a part's scratch and merge.
+extern "C" int qe_flash_attention_tc_balance(const int* steps, int n_tiles, int Hkv, int sms, int min_part_steps,
+                                             int max_parts, float item_cost, float part_cost) {
+  if (n_tiles <= 0 || Hkv <= 0 || sms <= 0 || max_parts < 2) return 0;
+  int longest = 0;
+  for (int i = 0; i < n_tiles; ++i) longest = steps[i] > longest ? steps[i] : longest;
+  if (longest < 2 * min_part_steps) return 0;
+  auto schedule = [&](int cap) {
+    float* items = new float[(size_t)n_tiles * max_parts];
+    int n = 0;
+    for (int i = 0; i < n_tiles; ++i) {
+      int parts = cap > 0 ? (steps[i] + cap - 1) / cap : 1;
+      if (parts > max_parts) parts = max_parts;
+      if (parts <= 1) { items[n++] = (float)steps[i] + item_cost; continue; }
+      const int per = (steps[i] + parts - 1) / parts;
+      for (int done = 0; done < steps[i]; done += per) {
+        const int len = steps[i] - done < per ? steps[i] - done : per;
+        items[n++] = (float)len + item_cost + part_cost;
+      }
+    }
+    // longest first (insertion sort would do for these sizes; a simple heap sort keeps it n log n)
+    for (int i = 1; i < n; ++i) {
+      const float v = items[i];
+      int j = i - 1;
+      while (j >= 0 && items[j] < v) { items[j + 1] = items[j]; --j; }
+      items[j + 1] = v;
+    }
+    float* free_at = new float[sms];                // a binary min-heap of the SMs' free times
+    for (int i = 0; i < sms; ++i) free_at[i] = 0.f;
+    float end = 0.f;
+    for (int i = 0; i < n; ++i)
+      for (int h = 0; h < Hkv; ++h) {
+        float t = free_at[0] + items[i];
+        end = t > end ? t : end;
+        int k = 0;                                  // replace the root and sift down
+        for (;;) {
+          const int l = 2 * k + 1, r = l + 1;
+          int m = k;
+          float best = t;
+          if (l < sms && free_at[l] < best) { m = l; best = free_at[l]; }
+          if (r < sms && free_at[r] < best) { m = r; best = free_at[r]; }
+          if (m == k) break;
+          free_at[k] = free_at[m];
+          k = m;
+        }
+        free_at[k] = t;
+      }
+    delete[] items;
+    delete[] free_at;
+    return end;
+  };
+  const float whole = schedule(0);
+  float best = whole * 0.95f;                       // cutting has to gain something
+  int best_cap = 0, last = 0;
+  for (int f = 7; f >= 1; --f) {
+    int cap = (longest * f + 7) / 8;
+    if (cap < min_part_steps) cap = min_part_steps;
+    if (cap == last || cap >= longest) continue;
+    last = cap;
+    const float t = schedule(cap);
+    if (t < best) { best = t; best_cap = cap; }
+  }
+  return best_cap;
+}
+
 // Whether the kernel takes this geometry: head size 128; a group size (query heads per kv head) that
 // divides 128; pages of a power of two of at least 8 tokens.
 extern "C" int qe_flash_attention_tc_supported(int Hq, int Hkv, int D, int page_size) {

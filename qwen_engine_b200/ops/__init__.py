@@ -50,6 +50,10 @@ TC_MIN_ROWS = 65        # rows of a request's portion from which the tcgen05 ker
 TC_TARGET_CTAS = 148    # one CTA per SM
 TC_MIN_PART_STEPS = 8   # key steps of a part at least, when tiles are cut to fill idle SMs
 TC_MAX_PARTS = 8        # parts of one tile at most
+TC_BALANCE_BELOW_CTAS = 592   # tiles x kv heads below which the tiles' schedule is laid out and long tiles are cut (4 per SM)
+TC_ITEM_COST_STEPS = 1.0      # a CTA's start and end, in key steps
+TC_PART_COST_STEPS = 1.0      # a part's scratch and merge on top, in key steps
+TC_FORCE_CAP = -1       # the most key steps of a work item (0: cut nothing); below 0 the library works it out
 
 
 class ExtensionMissing(RuntimeError):
@@ -655,17 +659,23 @@ def tc_attention_supported(dtype: torch.dtype, num_heads: int, num_kv_heads: int
 
 def _plan_tc_tiles(tiles: list, Hkv: int) -> tuple[list[int], int]:
     """Work items of the tcgen05 kernel from its tiles (key steps, first key, last key, item fields),
-    sorted by their steps, longest first.  When the tiles are too few to give every SM a CTA (a short
-    portion behind a long context), tiles are cut into parts of whole steps, as many as SMs are idle
-    but none shorter than TC_MIN_PART_STEPS: a part costs a CTA's start and end and the merge, about as
-    much as a few steps.  Returns the items and the number of parts."""
-    n_ctas = len(tiles) * Hkv
-    most = min(TC_MAX_PARTS, TC_TARGET_CTAS // n_ctas) if n_ctas else 1
+    sorted by their steps, longest first.  Where the tiles alone would leave SMs idle (a short portion
+    behind a long context: few tiles; one prompt of a few thousand tokens: tiles as unequal as
+    1 : 2 : ... : n), the longer tiles are cut into parts of whole steps; the library works out the most
+    steps an item may have by laying out the candidates' schedules (a part costs a CTA's start and
+    end and the merge, about as much as a few steps).  Returns the items and the number of parts."""
+    cap = TC_FORCE_CAP
+    if cap < 0:
+        cap = 0
+        if tiles and len(tiles) * Hkv < TC_BALANCE_BELOW_CTAS:
+            steps = (ctypes.c_int * len(tiles))(*[t[0] for t in tiles])
+            cap = int(lib().qe_flash_attention_tc_balance(steps, len(tiles), Hkv, TC_TARGET_CTAS, TC_MIN_PART_STEPS, TC_MAX_PARTS,
+                                                          ctypes.c_float(TC_ITEM_COST_STEPS), ctypes.c_float(TC_PART_COST_STEPS)))
     out: list[tuple[int, list[int]]] = []
     n_parts = 0
     for steps, lo, hi, (r, q0, row0, n, c) in tiles:
-        parts = max(1, min(most, steps // TC_MIN_PART_STEPS))
-        if parts == 1:
+        parts = min(TC_MAX_PARTS, -(-steps // cap)) if cap else 1
+        if parts <= 1:
             out.append((steps, [r, q0, lo, hi, -1, 0, 0, row0, n, c, 0, 0]))
             continue
         per = -(-steps // parts)
