@@ -22,6 +22,12 @@ CSRC_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_NAME = "libqwen_engine_b200.so"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC"]
+if os.environ.get("QE_TIMELINE") == "1":
+    # the build whose kernels record when they start and when their predecessors end (common.cuh);
+    # a library of its own beside the plain one
+    NVCC_FLAGS = NVCC_FLAGS + ["-DQE_TIMELINE"]
+    LIB_NAME = "libqwen_engine_b200_timeline.so"
+BUILD_FOLDER = "_build_timeline" if "-DQE_TIMELINE" in NVCC_FLAGS else "_build"
 
 
 class BuildError(RuntimeError):
@@ -55,7 +61,7 @@ def _digest() -> str:
 
 
 def _build_dir() -> str:
-    in_tree = os.path.join(CSRC_DIR, "_build")
+    in_tree = os.path.join(CSRC_DIR, BUILD_FOLDER)
     try:
         os.makedirs(in_tree, exist_ok=True)
         probe = os.path.join(in_tree, f".w{os.getpid()}")
@@ -64,7 +70,7 @@ def _build_dir() -> str:
         os.remove(probe)
         return in_tree
     except OSError:
-        alt = os.path.join(tempfile.gettempdir(), f"qwen_engine_b200_build_{os.getuid()}")
+        alt = os.path.join(tempfile.gettempdir(), f"qwen_engine_b200{BUILD_FOLDER}_{os.getuid()}")
         os.makedirs(alt, exist_ok=True)
         return alt
 

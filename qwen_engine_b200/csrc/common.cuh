@@ -59,8 +59,60 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 // kernel of the chain start early in turn.  Every kernel of this library calls pdl_wait() in all of
 // its threads, so a kernel never completes before its predecessor has, and waiting on the
 // predecessor alone is enough.  qe_set_pdl(0) turns the attribute off (plain stream order).
+#ifndef QE_TIMELINE
+#define QE_TL_MARK(kind) do { } while (0)
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+#else
+// ---- timeline build (-DQE_TIMELINE; QE_TIMELINE=1 in the environment of the build) ------------------------
+// Every kernel of the library passes these two calls, so they double as probes: thread 0 of every CTA
+// writes the GPU's global timer when it lets its dependents start (about when the CTA started) and
+// when its wait for the predecessor returns (the predecessor has completed).  That is enough to lay a
+// step's kernels, their overlaps and the gaps between them on one time axis without a profiler.  An
+// event is four 64-bit words: (hash of the source file's name << 32 | line << 16 | kind), (the CTA's
+// linear index << 32 | CTAs of the grid), the time in ns, the SM.  Word 0 of the buffer counts the
+// events, word 1 is its capacity in events; the events follow from word 4 on.
+// Every translation unit keeps its own copy of the buffer's address; qe_timeline_begin sets them all.
+static __device__ unsigned long long* qe_tl_buf = nullptr;
+__host__ __device__ constexpr unsigned qe_tl_hash(const char* s) {
+  unsigned h = 2166136261u;
+  const char* base = s;
+  for (const char* p = s; *p; ++p) if (*p == '/') base = p + 1;       // the file's name without its folder
+  for (const char* p = base; *p; ++p) h = (h ^ (unsigned)*p) * 16777619u;
+  return h;
+}
+__device__ __forceinline__ void qe_tl_event(unsigned file_hash, unsigned line, unsigned kind) {
+  if (threadIdx.x != 0 || threadIdx.y != 0 || threadIdx.z != 0 || qe_tl_buf == nullptr) return;
+  unsigned long long t;
+  unsigned sm;
+  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+  asm volatile("mov.u32 %0, %%smid;\n" : "=r"(sm));
+  const unsigned long long idx = atomicAdd(qe_tl_buf, 1ull);
+  if (idx < qe_tl_buf[1]) {
+    const unsigned long long cta = blockIdx.x + (unsigned long long)gridDim.x * (blockIdx.y + (unsigned long long)gridDim.y * blockIdx.z);
+    const unsigned long long total = (unsigned long long)gridDim.x * gridDim.y * gridDim.z;
+    unsigned long long* e = qe_tl_buf + 4 + 4 * idx;
+    e[0] = ((unsigned long long)file_hash << 32) | ((unsigned long long)(line & 0xffffu) << 16) | (kind & 3u);
+    e[1] = (cta << 32) | (total & 0xffffffffull);
+    e[2] = t;
+    e[3] = sm;
+  }
+}
+__device__ __forceinline__ void pdl_wait_at(unsigned file_hash, unsigned line) {
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+  qe_tl_event(file_hash, line, 1);
+}
+__device__ __forceinline__ void pdl_launch_dependents_at(unsigned file_hash, unsigned line) {
+  qe_tl_event(file_hash, line, 0);
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+}
+#define QE_TL_MARK(kind) qe_tl_event(qe_tl_hash(__FILE__), __LINE__, kind)   // a kernel's own marks: kinds 2 and 3
+#define pdl_wait() pdl_wait_at(qe_tl_hash(__FILE__), __LINE__)
+#define pdl_launch_dependents() pdl_launch_dependents_at(qe_tl_hash(__FILE__), __LINE__)
+void qe_tl_register(void (*setter)(unsigned long long*));
+static void qe_tl_set_here(unsigned long long* p) { cudaMemcpyToSymbol(qe_tl_buf, &p, sizeof(p)); }
+static const int qe_tl_registered = (qe_tl_register(qe_tl_set_here), 0);
+#endif
 
 // ---- thread-block clusters ------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_cta_rank() {

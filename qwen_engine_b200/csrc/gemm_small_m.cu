@@ -36,6 +36,16 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
                    :: "l"(reinterpret_cast<const unsigned char*>(w + (size_t)blockIdx.x * 16 * K) + off), "r"(size) : "memory");
     }
   }
+  if (na.next_bytes) {
+    // pieces of 4 KB of the later kernel's weights, dealt to the CTAs and their threads in turn
+    const unsigned long long pieces = (na.next_bytes + 4095) >> 12;
+    const unsigned long long piece = (unsigned long long)threadIdx.x * gridDim.x + blockIdx.x;
+    if (piece < pieces) {
+      const unsigned long long off = piece << 12;
+      const unsigned size = (unsigned)min(4096ull, na.next_bytes - off) & ~15u;
+      if (size) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" :: "l"(na.next_w + off), "r"(size) : "memory");
+    }
+  }
   pdl_launch_dependents();
   pdl_wait();
   gsm_cta<MT, TOut, XMODE, RESID>(x, w, out, M, N, K, k_per_warp, na, blockIdx.x, red, s_rstd, c0, c1);
@@ -69,9 +79,24 @@ static int launch_small_m(const void* x, const void* w, void* out, int M, int N,
   return 0;
 }
 
+// The weights that the next product launched from this thread asks L2 for (see FuseArgs::next_w); one launch
+// takes them and clears them.  16-byte aligned; bytes 0 clears.
+static thread_local const unsigned char* g_next_w = nullptr;
+static thread_local unsigned long long g_next_bytes = 0;
+extern "C" int qe_small_m_prefetch_next(const void* w, unsigned long long bytes) {
+  if (((uintptr_t)w & 15) != 0) QE_REFUSE("small_m_prefetch_next: the weights must be 16-byte aligned");
+  g_next_w = (const unsigned char*)w;
+  g_next_bytes = w ? bytes : 0;
+  return 0;
+}
+
 template <int XMODE, bool RESID>
 static int dispatch_small_m(const void* x, const void* w, void* out, int M, int N, int K, int out_f32,
                             cudaStream_t stream, FuseArgs na = FuseArgs{}) {
+  na.next_w = g_next_w;
+  na.next_bytes = g_next_bytes;
+  g_next_w = nullptr;
+  g_next_bytes = 0;
   if (M <= 0 || N <= 0) return 0;
   if (M > 64) QE_REFUSE("linear_small_m: M = %d is above 64", M);
   if (K <= 0 || K % 8) QE_REFUSE("linear_small_m: K = %d is not a positive multiple of 8", K);

@@ -52,6 +52,11 @@ struct FuseArgs {
   float* ssq_out;                   // RESID: [M, ssq_ld]
   int n_ssq, ssq_ld;
   float eps;
+  // Weights that a later kernel of the step will read (nobody writes them): the CTAs ask L2 for them,
+  // a slice each, once their own weights are on their way.  A decode step is a chain of short kernels,
+  // and a kernel that starts on weights that are already on the chip is done sooner.
+  const unsigned char* next_w;
+  unsigned long long next_bytes;
 };
 
 // a chunk of weights: 64 k of 16 rows = four 16-byte loads per lane
@@ -178,6 +183,7 @@ __device__ __forceinline__ void gsm_cta(const __nv_bfloat16* __restrict__ x, con
     c0 = n0c;
     c1 = n1c;
   }
+  QE_TL_MARK(2);
   // acc[t][0..1]: weight row g, tokens 8t + 2c + {0,1};  acc[t][2..3]: weight row g + 8
   constexpr int MW = 8 * MT;
   float* mine = red + (size_t)warp * 16 * MW;
@@ -215,5 +221,6 @@ __device__ __forceinline__ void gsm_cta(const __nv_bfloat16* __restrict__ x, con
       if (i == 0 && m < M) na.ssq_out[(size_t)m * na.ssq_ld + vb] = sq;
     }
   }
+  QE_TL_MARK(3);
 }
 

@@ -155,12 +155,18 @@ class DecoderModel:
         stream = ops.ResidualStream(ctx.arena.alloc((T, H), torch.float32), ctx.arena.alloc((T, H), ctx.dtype), ssq)
         ops.embedding(ctx.token_ids, self.embed, stream.resid, ssq)
         stream.n_ssq = 1 if ssq is not None else 0
-        for entry in lo.plan:
-            view, group = None, None
-            if entry.cache_slot is not None:
-                view = cache.layer_view(entry.cache_slot)
-                group = cache.group_of_slot[entry.cache_slot][0]
+        views = [(cache.layer_view(e.cache_slot), cache.group_of_slot[e.cache_slot][0]) if e.cache_slot is not None
+                 else (None, None) for e in lo.plan]
+        for i, entry in enumerate(lo.plan):
+            view, group = views[i]
+            # a hint for mixers that can ask for it ahead of time: the cache that the next entry of the plan
+            # with a cache of the same group will read (the same pages at the same places)
+            ctx.extras["next_cache"] = next((v for v, g in views[i + 1:] if v is not None and g == group and v is not view), None)
+            # and the weights that the step reads first after this block
+            nxt = lo.plan[i + 1].layer if i + 1 < len(lo.plan) else None
+            ctx.extras["weights_after_ffn"] = self.blocks[nxt].first_weights() if nxt is not None else None
             self.blocks[entry.layer].forward(ctx, stream, view, group, entry.write_cache)
+        ctx.extras["next_cache"] = ctx.extras["weights_after_ffn"] = None
         if ctx.num_logit_rows == 0:
             return None
         N = ctx.num_logit_rows

@@ -9,6 +9,7 @@ operation lives with the tests (tests/ref_ops.py).
 from __future__ import annotations
 
 import ctypes
+import os
 import struct
 from typing import Optional
 
@@ -44,6 +45,10 @@ DECODE_ATTENTION_CLUSTERS = True    # parts of a request as a thread-block clust
 DECODE_ATTENTION_MAX_ROWS = 2   # rows (token x head of the group) per item up to which it is used (measured: with 4 rows the mma.sync kernel is 11 % ahead; the kernel takes up to 4)
 DECODE_ATTENTION_MAX_KEYS = 512 # context up to which it serves contexts that are not split (longer: the pipelined kernel)
 DECODE_ATTENTION_MIN_CTAS = 128 # CTAs from which it is used: measured, it gains where the GPU is full and loses a little below
+DECODE_ATTENTION_MMA = True         # decoded tokens (up to 16 rows per kv head, head size 128): warps with key groups and pipelines of their own, mma.sync arithmetic
+DECODE_ATTENTION_MMA_MIN_CTAS = 0   # CTAs from which that kernel is used
+DECODE_ATTENTION_MMA_STAGES = 3     # key groups a warp of that kernel keeps in flight (2 or 3; measured: 3 is 2.5 % ahead in the step)
+DECODE_PREFETCH_KV_MB = 0           # that kernel asks L2 for the next layer's keys and values when a layer's are at most this many MB (0: never)
 TC_ROWS = 256           # rows per work item of the tcgen05 attention kernel (two halves of 128)
 TC_BN = 128             # keys per step of the tcgen05 attention kernel
 TC_MIN_ROWS = 65        # rows of a request's portion from which the tcgen05 kernel serves it
@@ -220,6 +225,7 @@ def _record_gemm(x, w, out, M, N, K, xmode, resid, out_f32, norm=None, ssq_out=N
 
 
 launch_count = 0        # kernels launched through this module since import (read by the benchmark)
+last_attention_kernel = ""   # which kernel the last ``paged_attention`` call went to (read by tests)
 
 
 def _check(rc: int, name: str) -> None:
@@ -438,10 +444,37 @@ def _linear_into_stream(x: torch.Tensor, w: torch.Tensor, sink: ResidualSink, si
         return False
     _need(w.shape == (N, K) and x.is_contiguous() and w.is_contiguous(), "linear: operands do not fit")
     if not _record_gemm(x, w, st.resid, M, N, K, 1 if silu else 0, True, True, ssq_out=st.ssq, ssq_ld=int(st.ssq.shape[1])):
+        _hand_over_next_weights()
         _check(lib().qe_linear_small_m_resid(_ptr(x), _ptr(w), _ptr(st.resid), _ptr(st.ssq), int(st.ssq.shape[1]),
                                              M, N, K, int(silu), _stream()), "linear")
     st.n_ssq = -(-N // 16)
     return True
+
+
+PREFETCH_NEXT_WEIGHTS = True   # products of a few rows ask L2 for the weights of the product that follows them
+PREFETCH_NEXT_MAX_MB = 32      # ... when those are at most this many MB
+
+
+def prefetch_next(w: Optional[torch.Tensor]) -> None:
+    """Tell the next ``linear`` / ``linear_silu_mul`` call which weights the step reads after its own
+    (None: none).  Where that call is served by the kernel for a few rows, its CTAs ask L2 for them once
+    their own weights are on their way; every other kernel ignores the hint.  One call takes it."""
+    global _next_w
+    _next_w = None
+    if (w is not None and PREFETCH_NEXT_WEIGHTS and w.is_cuda and w.is_contiguous()
+            and w.numel() * w.element_size() <= PREFETCH_NEXT_MAX_MB << 20):
+        _next_w = w
+
+
+_next_w: Optional[torch.Tensor] = None
+
+
+def _hand_over_next_weights() -> None:
+    """Before a launch of the kernel for a few rows: the pending hint goes to the library (and is cleared)."""
+    global _next_w
+    if _next_w is not None:
+        w, _next_w = _next_w, None
+        lib().qe_small_m_prefetch_next(_ptr(w), ctypes.c_ulonglong(w.numel() * w.element_size()))
 
 
 def linear(x, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -474,6 +507,7 @@ def linear(x, w: torch.Tensor, out: torch.Tensor) -> None:
         # a few rows: stream every weight once through the tensor cores
         if _record_gemm(x, w, out, M, N, K, 0, False, out_f32):
             return
+        _hand_over_next_weights()
         _check(lib().qe_linear_small_m(_ptr(x), _ptr(w), _ptr(out), M, N, K, out_f32, _stream()), "linear")
         return
     if (x.dtype == torch.bfloat16 and TCGEN05_PAIRS and TCGEN05_ENABLED and K % 8 == 0
@@ -543,12 +577,49 @@ def linear_silu_mul(gate_up: torch.Tensor, w: torch.Tensor, out: torch.Tensor, s
     if gate_up.dtype == torch.bfloat16 and M <= SMALL_M_MAX and I % 8 == 0:
         if _record_gemm(gate_up, w, out, M, N, I, 1, False, out.dtype == torch.float32):
             return
+        _hand_over_next_weights()
         _check(lib().qe_linear_small_m_silu(_ptr(gate_up), _ptr(w), _ptr(out), M, N, I,
                                             int(out.dtype == torch.float32), _stream()), "linear_silu_mul")
         return
     act = scratch((M, I), gate_up.dtype)
     silu_mul(gate_up, act)
     linear(act, w, out)
+
+
+def timeline_begin(capacity: int = 1 << 20) -> None:
+    """Start recording in the timeline build of the library (QE_TIMELINE=1 in the environment when it is
+    built and loaded): from now on thread 0 of every CTA notes the GPU's clock when it lets its dependents
+    start and when its wait for the kernel before it returns.  Raises in the plain build."""
+    lib().qe_timeline_begin.restype = ctypes.c_long
+    got = int(lib().qe_timeline_begin(ctypes.c_long(int(capacity))))
+    if got < 0:
+        raise ExtensionMissing("this build of the library records no timeline (build and run with QE_TIMELINE=1)"
+                               if got == -1 else "no memory for the timeline")
+
+
+def timeline_events() -> list[tuple[str, int, int, int, int, int, int]]:
+    """The events since ``timeline_begin``, in the order of their times: (source file, line, kind, CTA's linear
+    index, CTAs of its grid, ns, SM); kind 0: the CTA let its dependents start (about its start), 1: its wait
+    for the predecessor returned."""
+    cap = 1 << 20
+    buf = (ctypes.c_ulonglong * (4 * cap))()
+    lib().qe_timeline_read.restype = ctypes.c_long
+    n = int(lib().qe_timeline_read(buf, ctypes.c_long(cap)))
+    if n < 0:
+        raise ExtensionMissing("this build of the library records no timeline (build and run with QE_TIMELINE=1)")
+
+    def fnv(name: str) -> int:
+        h = 2166136261
+        for ch in name.encode():
+            h = ((h ^ ch) * 16777619) & 0xFFFFFFFF
+        return h
+    names = {fnv(f): f for f in os.listdir(_build.CSRC_DIR) if f.endswith((".cu", ".cuh", ".h"))}
+    out = []
+    for i in range(n):
+        w, c, t, sm = (int(buf[4 * i + j]) for j in range(4))
+        out.append((names.get(w >> 32, hex(w >> 32)), (w >> 16) & 0xFFFF, w & 3, c >> 32, c & 0xFFFFFFFF, t, sm))
+    out.sort(key=lambda e: e[5])
+    return out
 
 
 def set_pdl(enabled: bool) -> None:
@@ -806,6 +877,17 @@ def _decode_kernel_serves(plan, key, ctx, qkv: torch.Tensor, Hkv: int, D: int) -
             and (n_parts > 0 or max(getattr(ctx, "ctx_lens_host", None) or [0]) <= DECODE_ATTENTION_MAX_KEYS))
 
 
+def _decode_mma_serves(plan, key, qkv: torch.Tensor, Hq: int, Hkv: int, D: int) -> bool:
+    """Whether the whole step's attention (geometry index ``key`` of the plan) goes to the tensor-core kernel
+    for decoded tokens: items of at most 16 rows, head size 128, none on the tcgen05 kernel."""
+    if not DECODE_ATTENTION_MMA or key is None or f"fa{key}_items" not in plan or f"tc{key}_items" in plan or D != 128:
+        return False
+    n_parts, part_rows, small_tiles, max_rows, same_parts = plan[f"fa{key}_info_host"]
+    n_items = plan[f"fa{key}_items"].numel() // FLASH_ITEM_INTS
+    return (1 <= max_rows <= 16 and Hq // Hkv <= 16 and n_items > 0 and n_items * Hkv >= DECODE_ATTENTION_MMA_MIN_CTAS
+            and n_parts * Hkv <= _MERGE_COUNTERS and qkv.stride(0) % 8 == 0)
+
+
 def attention_fuses_rotary(qkv: torch.Tensor, ctx, num_heads: int, num_kv_heads: int, head_dim: int, window: int,
                            rotary_dim: int) -> bool:
     """Whether ``paged_attention`` can take q, k, v as the QKV product left them and do the per-head norm,
@@ -822,22 +904,26 @@ def attention_fuses_rotary(qkv: torch.Tensor, ctx, num_heads: int, num_kv_heads:
 
 def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: torch.Tensor, ctx,
                     out: torch.Tensor, scale: float, window: int, num_heads: int, num_kv_heads: int,
-                    head_dim: int, fused: Optional[dict] = None) -> None:
+                    head_dim: int, fused: Optional[dict] = None, next_pages: Optional[torch.Tensor] = None) -> None:
     """Attention of the step's queries (the q part of qkv [T, (Hq+2Hkv) D]) over the keys and values
     of their requests in ``kv_pages``; out [T, Hq D].  ``ctx`` is the StepContext (cu_q, ctx_lens,
     the plan that ``plan_attention`` made, and the arena for the parts of split contexts).
 
     ``fused`` (only where ``attention_fuses_rotary`` said yes): q_norm_w, k_norm_w, eps, inv_freq,
-    write_kv of the per-head norm, rotation and cache write that this call then does itself."""
+    write_kv of the per-head norm, rotation and cache write that this call then does itself.
+    ``next_pages``: the cache of the layer that runs after this one, if it has the same shape (the same
+    pages at the same places): a decode step's kernel may ask L2 for that layer's keys and values."""
     Hq, Hkv, D = num_heads, num_kv_heads, head_dim
     T = qkv.shape[0]
     _need(out.shape == (T, Hq * D) and out.is_contiguous() and out.dtype == qkv.dtype, "paged_attention: out must be [T, Hq D]")
     _need(kv_pages.dtype == qkv.dtype and kv_pages.dim() == 5 and kv_pages.is_contiguous(),
           "paged_attention: kv_pages must be [pages, 2, Hkv, page, D] in q's dtype")
     _i32(block_tables, "block_tables")
+    global last_attention_kernel
     plan = ctx.attn_plan
     key = plan.get("geometry_index", {}).get((Hq, Hkv, D, window))
     if key is not None and f"tc{key}_items" in plan:
+        last_attention_kernel = "flash_attention_tc"
         tc_items = plan[f"tc{key}_items"]
         tc_parts, tc_rows = plan[f"tc{key}_info_host"]
         part_acc = part_ml = counters = None
@@ -872,6 +958,7 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
         cluster = int(same_parts) if DECODE_ATTENTION_CLUSTERS and n_items == n_parts else 0
         _need(fused is None or serves, "paged_attention: this step cannot take the rotation into the attention kernel")
         if fused is not None:
+            last_attention_kernel = "decode_attention_fused"
             _check(lib().qe_decode_attention_fused(
                 _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(block_tables), int(block_tables.shape[1]),
                 _ptr(items), n_items, _ptr(out), _ptr(part_acc), _ptr(part_ml), int(part_rows), _ptr(counters),
@@ -879,14 +966,32 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
                 ctypes.c_float(fused["eps"]), _ptr(fused["inv_freq"]), int(bool(fused["write_kv"])),
                 Hq, Hkv, D, int(kv_pages.shape[3]), _stream()), "decode_attention_fused")
             return
+        if _decode_mma_serves(plan, key, qkv, Hq, Hkv, D):
+            # decoded tokens: every warp streams key groups of its own through the tensor cores
+            last_attention_kernel = "decode_attention_mma"
+            lib().qe_decode_attention_mma_stages(int(DECODE_ATTENTION_MMA_STAGES))
+            ahead = None
+            if (next_pages is not None and DECODE_PREFETCH_KV_MB > 0 and next_pages.shape == kv_pages.shape
+                    and next_pages.dtype == kv_pages.dtype and next_pages.is_contiguous()):
+                tokens = sum(ctx.ctx_lens_host) + sum(ctx.q_lens_host)
+                if tokens * 2 * Hkv * D * kv_pages.element_size() <= DECODE_PREFETCH_KV_MB << 20:
+                    ahead = next_pages
+            _check(lib().qe_decode_attention_mma(
+                _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(ahead), _ptr(block_tables), int(block_tables.shape[1]),
+                _ptr(items), n_items, _ptr(out), _ptr(part_acc), _ptr(part_ml), int(part_rows), _ptr(counters),
+                int(max_rows), cluster, ctypes.c_float(scale), int(window), Hq, Hkv, D, int(kv_pages.shape[3]), _stream()),
+                "decode_attention_mma")
+            return
         if serves:
             # a few rows per kv head (decoded tokens): the kernel without matrix instructions
+            last_attention_kernel = "decode_attention"
             _check(lib().qe_decode_attention(
                 _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(block_tables), int(block_tables.shape[1]),
                 _ptr(items), n_items, _ptr(out), _ptr(part_acc), _ptr(part_ml), int(part_rows), _ptr(counters),
                 int(max_rows), cluster, ctypes.c_float(scale), int(window), Hq, Hkv, D, int(kv_pages.shape[3]), _stream()),
                 "decode_attention")
             return
+        last_attention_kernel = "flash_attention"
         _check(lib().qe_flash_attention_fused_merge(
             _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(block_tables), int(block_tables.shape[1]),
             _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), _ptr(items), n_items, _ptr(merge), n_merge, _ptr(out),
@@ -895,6 +1000,7 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
         return
     tiles = plan["tiles"]
     n_tiles = tiles.numel() // 2
+    last_attention_kernel = "paged_attention_generic"
     _check(lib().qe_paged_attention_generic(
         _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(block_tables), int(block_tables.shape[1]),
         _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), _ptr(tiles), n_tiles, _ptr(out), ctypes.c_float(scale), int(window),

@@ -17,7 +17,7 @@ import torch
 from .. import ops
 from ..cache.spec import PagedKVSpec
 from ..weights.spec import MATRIX, NORM, WeightSpec
-from .base import Mixer, PartSpec, StepContext, register
+from .base import Mixer, PartSpec, StepContext, register, step_hint
 from .rope import NeoxRope
 
 
@@ -73,11 +73,15 @@ class GQAAttention(Mixer):
         if self.pos is not None:
             self.pos.load(prefix, source, dtype, device)
 
+    def first_weights(self):
+        return self.w_qkv
+
     def forward(self, ctx: StepContext, x, cache, group, out, write_cache: bool = True) -> None:
         T = ctx.num_tokens
         H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
         view = ctx.groups[group]
         qkv = ctx.arena.alloc((T, self.q_width + 2 * self.kv_width), ctx.dtype)
+        ops.prefetch_next(self.w_o)
         ops.linear(x, self.w_qkv, qkv)
         fused_rope = isinstance(self.pos, NeoxRope)
         attn = ctx.arena.alloc((T, self.q_width), ctx.dtype)
@@ -107,5 +111,7 @@ class GQAAttention(Mixer):
                 cache, view.slot_mapping, H, Hkv, D, write_kv=write_cache,
                 cos_sin=self.pos.step_table(ctx) if fused_rope else None)
         ops.paged_attention(qkv, cache, view.block_tables, ctx, attn, self.scale,
-                            self.window or 0, H, Hkv, D)
+                            self.window or 0, H, Hkv, D, next_pages=step_hint(ctx, "next_cache"))
+        ops.prefetch_next(step_hint(ctx, "weights_after_mixer"))
         ops.linear(attn, self.w_o, out)
+        ops.prefetch_next(None)

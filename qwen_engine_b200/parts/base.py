@@ -147,6 +147,13 @@ class StepContext:
         return max((c + q for c, q in zip(self.ctx_lens_host, self.q_lens_host)), default=0)
 
 
+def step_hint(ctx, key: str):
+    """What the model or the block left in ``ctx.extras`` for the parts to use if they can (the cache the
+    next layer reads, the weights read after this part); None where nobody left anything (a part run alone)."""
+    extras = getattr(ctx, "extras", None)
+    return extras.get(key) if extras else None
+
+
 # --------------------------------------------------------------------------------------
 # the parts
 # --------------------------------------------------------------------------------------
@@ -159,6 +166,11 @@ class Part:
 
     def load(self, prefix: str, source: TensorSource, dtype: torch.dtype, device) -> None:
         pass
+
+    def first_weights(self) -> Optional[torch.Tensor]:
+        """The matrix that the part's forward reads first, if it has one and cares to say: the product
+        that runs just before the part may ask L2 for it ahead of time (``ops.prefetch_next``)."""
+        return None
 
 
 class Norm(Part):

@@ -33,10 +33,15 @@ class PreNormBlock(Block):
         for part, p in self._parts():
             part.load(prefix + p, source, dtype, device)
 
+    def first_weights(self):
+        return self.mixer.first_weights()
+
     def forward(self, ctx: StepContext, stream, cache, group, write_cache) -> None:
         mark = ctx.arena.mark()
         h = self.norm1.normed(ctx, stream, lazy=self.mixer.takes_lazy_input)
         out = self._branch_out(stream, self.mixer)
+        if getattr(ctx, "extras", None) is not None:
+            ctx.extras["weights_after_mixer"] = self.ffn.first_weights()
         self.mixer.forward(ctx, h, cache, group, out, write_cache)
         self._branch_done(stream, out)
         h = self.norm2.normed(ctx, stream, lazy=self.ffn.takes_lazy_input)

@@ -8,7 +8,7 @@ import torch
 
 from .. import ops
 from ..weights.spec import MATRIX, WeightSpec
-from .base import FeedForward, StepContext, register
+from .base import FeedForward, StepContext, register, step_hint
 
 
 @register("feed_forward", "swiglu")
@@ -32,6 +32,9 @@ class SwiGLU(FeedForward):
         self.w_gate_up = ops.prepare_matrix(stacked.to(dtype).to(device))
         self.w_down = ops.prepare_matrix(source.get(prefix + "down_proj.weight").to(dtype).to(device))
 
+    def first_weights(self):
+        return self.w_gate_up
+
     def forward(self, ctx: StepContext, x, out) -> None:
         T, I = ctx.num_tokens, self.intermediate_size
         if ops.swiglu_fused_applies(T, I, self.hidden_size, ctx.dtype):
@@ -43,5 +46,8 @@ class SwiGLU(FeedForward):
             ops.linear(act, self.w_down, out)
             return
         gate_up = ctx.arena.alloc((T, 2 * I), ctx.dtype)
+        ops.prefetch_next(self.w_down)
         ops.linear(x, self.w_gate_up, gate_up)
+        ops.prefetch_next(step_hint(ctx, "weights_after_ffn"))
         ops.linear_silu_mul(gate_up, self.w_down, out, ctx.arena.alloc)
+        ops.prefetch_next(None)

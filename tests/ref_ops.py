@@ -117,7 +117,7 @@ def plan_attention(q_lens, ctx_lens, page_size, geometries=(), dtype=None, unifo
     return {"tiles": tiles}
 
 
-def paged_attention(qkv, kv_pages, block_tables, ctx, out, scale, window, num_heads, num_kv_heads, head_dim):
+def paged_attention(qkv, kv_pages, block_tables, ctx, out, scale, window, num_heads, num_kv_heads, head_dim, next_pages=None):
     """For each request: gather its keys and values from the pages by its block table, then
     softmax(scale q k^T + mask) v with key j allowed for the query at position i iff
     j <= i and (window == 0 or j > i - window)."""

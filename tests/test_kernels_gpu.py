@@ -418,15 +418,25 @@ def test_flash_attention_split_contexts(Hq, Hkv, D, P, q_lens, ctx_lens):
     _close(got, want, dtype)
 
 
+@pytest.fixture(params=["mma", "plain"])
+def decode_kernel(request):
+    """Which kernel for decoded tokens ``ops.paged_attention`` picks: the one whose warps stream key groups
+    through mma.sync, or the one without matrix instructions."""
+    saved = ops.DECODE_ATTENTION_MMA
+    ops.DECODE_ATTENTION_MMA = request.param == "mma"
+    yield request.param
+    ops.DECODE_ATTENTION_MMA = saved
+
+
 @pytest.mark.parametrize("Hq,Hkv,P", [(16, 8, 16), (4, 4, 8), (8, 2, 32), (4, 1, 16), (6, 3, 4), (2, 1, 256)])
 @pytest.mark.parametrize("q_lens,ctx_lens", [([1], [77]), ([1, 1, 1], [5, 130, 333]), ([1] * 8, [1024] * 8),
                                              ([1, 1], [257, 2000]), ([1, 1, 1, 1], [0, 159, 160, 161]),
                                              ([1], [5000])])
 @pytest.mark.parametrize("window", [0, 100])
-def test_decode_attention(Hq, Hkv, P, q_lens, ctx_lens, window):
-    """Decoded tokens, head size 128: the kernel without matrix instructions (few rows per kv head),
-    with chunks of 160 keys, split contexts merged by the last CTA, and a window; against the plain
-    reference, and against the mma.sync kernel that serves the same items when it is switched off."""
+def test_decode_attention(Hq, Hkv, P, q_lens, ctx_lens, window, decode_kernel):
+    """Decoded tokens, head size 128: the kernels made for them (few rows per kv head; key groups or
+    chunks, split contexts merged by the last CTA, a window), against the plain reference, and against
+    the pipelined mma.sync kernel that serves the same items when they are switched off."""
     D, dtype = 128, torch.bfloat16
     plan = ops.plan_attention(list(q_lens), list(ctx_lens), P, ((Hq, Hkv, D, window),), dtype)
     assert 1 <= plan["fa0_info"][3] <= 4
@@ -439,10 +449,11 @@ def test_decode_attention(Hq, Hkv, P, q_lens, ctx_lens, window):
     try:
         got = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ops.paged_attention, DEV)
         _close(got, want, dtype)
-        ops.DECODE_ATTENTION = False
+        ops.DECODE_ATTENTION, mma = False, ops.DECODE_ATTENTION_MMA
+        ops.DECODE_ATTENTION_MMA = False
         other = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ops.paged_attention, DEV)
     finally:
-        ops.DECODE_ATTENTION = True
+        ops.DECODE_ATTENTION, ops.DECODE_ATTENTION_MMA = True, mma
         ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_KEYS, ops.DECODE_ATTENTION_MAX_ROWS = saved
     _close(other, want, dtype)
     assert ops.launch_count == launches + 2
@@ -452,7 +463,7 @@ def test_decode_attention(Hq, Hkv, P, q_lens, ctx_lens, window):
 @pytest.mark.parametrize("ctx_lens", [[77], [5, 130, 333], [1024] * 8, [0, 63, 64, 1500], [2000, 1, 700]])
 @pytest.mark.parametrize("parts", [2, 4, 8])
 @pytest.mark.parametrize("window", [0, 100])
-def test_decode_attention_parts_in_clusters(Hq, Hkv, P, ctx_lens, parts, window):
+def test_decode_attention_parts_in_clusters(Hq, Hkv, P, ctx_lens, parts, window, decode_kernel):
     """A decode step whose requests are all cut into the same 2, 4 or 8 parts: the parts of a request run as a
     thread-block cluster and meet through distributed shared memory (also parts that hold no key at
     all: short contexts, parts outside the window); the same items merged through scratch memory by the
@@ -523,8 +534,69 @@ def test_decode_attention_with_rotary_fused(Hq, Hkv, P, ctx_lens, norm, write_kv
         assert torch.equal(cache_gpu.cpu(), cache_ref)
 
 
+@pytest.mark.parametrize("Hq,Hkv,P", [(16, 1, 16), (32, 4, 16), (8, 1, 8), (12, 3, 4), (5, 1, 32)])
+@pytest.mark.parametrize("q_lens,ctx_lens", [([1], [77]), ([2, 1], [100, 37]), ([1, 1, 1], [5, 130, 1333]), ([1, 2], [3000, 15]),
+                                             ([1, 1, 1, 1], [0, 47, 48, 49])])
+@pytest.mark.parametrize("window", [0, 100])
+@pytest.mark.parametrize("stages", [2, 3])
+def test_decode_attention_mma_many_rows(Hq, Hkv, P, q_lens, ctx_lens, window, stages, monkeypatch):
+    """The tensor-core kernel for decoded tokens with up to 16 rows per kv head (large groups of query
+    heads, two tokens of a request in one item), page sizes below and above its key groups, contexts
+    that are split and not; against the plain reference.  The case must reach that kernel."""
+    D, dtype = 128, torch.bfloat16
+    G = Hq // Hkv
+    if max(q_lens) * G > 16:
+        pytest.skip("more than 16 rows per item: not this kernel's case")
+    plan = ops.plan_attention(list(q_lens), list(ctx_lens), P, ((Hq, Hkv, D, window),), dtype)
+    assert 1 <= plan["fa0_info"][3] <= 16 and "tc0_items" not in plan
+    case = _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, seed=47)
+    want = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ref_ops.paged_attention, "cpu")
+    assert ops.DECODE_ATTENTION_MMA
+    monkeypatch.setattr(ops, "DECODE_ATTENTION_MMA_STAGES", stages)
+    got = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ops.paged_attention, DEV)
+    assert ops.last_attention_kernel == "decode_attention_mma"
+    _close(got, want, dtype)
+
+
+def test_decode_attention_mma_asks_for_the_next_layers_cache(monkeypatch):
+    """With another layer's cache given (and allowed by size), the kernel asks L2 for that layer's keys and
+    values: the output is the same bits, and nothing of the other cache changes."""
+    Hq, Hkv, D, P, dtype = 16, 8, 128, 16, torch.bfloat16
+    q_lens, ctx_lens = [1, 1, 1], [5, 530, 1333]
+    case = _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, seed=48)
+    plain = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, ops.paged_attention, DEV)
+    assert ops.last_attention_kernel == "decode_attention_mma"
+    other = torch.randn_like(case["cache"]).to(DEV)
+    before = other.clone()
+    monkeypatch.setattr(ops, "DECODE_PREFETCH_KV_MB", 64)
+
+    def with_next(*a, **k):
+        return ops.paged_attention(*a, next_pages=other, **k)
+    got = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, with_next, DEV)
+    assert torch.equal(got, plain) and torch.equal(other, before)
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 1024, 2048), (3, 389, 80), (16, 72, 1032)])
+def test_linear_with_a_hint_of_the_next_weights(M, N, K):
+    """A product of a few rows that is told which weights the step reads next asks L2 for them and gives
+    the same bits; the hint is used once."""
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16().to(DEV)
+    nxt = torch.randn(1000, 1032, generator=g).bfloat16().to(DEV)          # 2 064 000 bytes: the last piece is partial
+    keep = nxt.clone()
+    out0 = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    out1 = torch.empty_like(out0)
+    ops.linear(x, w, out0)
+    ops.prefetch_next(nxt)
+    ops.linear(x, w, out1)
+    assert ops._next_w is None
+    torch.cuda.synchronize()
+    assert torch.equal(out0, out1) and torch.equal(nxt, keep)
+
+
 @pytest.mark.parametrize("key_pos", [0, 15, 16, 159, 160, 161, 255, 256, 700, 899])
-def test_decode_attention_far_key_stands_out(key_pos):
+def test_decode_attention_far_key_stands_out(key_pos, decode_kernel):
     """One key among hundreds carries almost all the weight: the output must be its value.  A kernel
     that misses a page, a chunk or a part would return something else."""
     Hq, Hkv, D, P = 4, 2, 128, 16
