@@ -4,15 +4,17 @@
 // loads organised for bandwidth: flash decoding as the reference's (src/layers/fused_ops/attn.py:374-594),
 // every key and value read once for all query heads of its kv head.
 //
-// One CTA (4 warps) serves one work item (a request's rows, a range of its keys) and one kv head.  The
-// keys are dealt to the warps in groups of 16: group i belongs to warp i mod 4, which copies the
+// One CTA (4 warps, or 8) serves one work item (a request's rows, a range of its keys) and one kv head.  The
+// keys are dealt to the warps in groups of 16: group i belongs to warp i mod 4 (8), which copies the
 // group's keys and values into shared memory of its own (cp.async, 16 bytes a lane, rows padded so
 // that ldmatrix meets no bank conflict), three groups ahead, and works on them alone: scores, masked
 // online softmax in float32 with a running max and sum of its own, P rounded to bfloat16 (attn.py:263),
-// P V.  No barrier of the CTA stands in the loop; the four warps' results are combined in shared
-// memory once at the end, by the formula that combines the parts of a split context.  Two CTAs fit an
-// SM, so up to 24 groups (192 KB) are in flight per SM.  Groups that hold only keys of earlier steps
-// are requested before the kernel waits for its predecessor (the rotary kernel wrote the new keys).
+// P V.  No barrier of the CTA stands in the loop; the warps' results are combined in shared
+// memory once at the end, by the formula that combines the parts of a split context.  Two CTAs of 4
+// warps fit an SM, or one of 8, so up to 24 groups (192 KB) are in flight per SM.  Groups that hold only
+// keys of earlier steps are requested before the kernel waits for its predecessor (the rotary kernel wrote
+// the new keys).  The wide form is for steps with no more CTAs than SMs: all of them start at once, beside
+// the CTAs of the kernel before, where two CTAs per SM would leave some waiting for room.
 //
 // A decode step is a chain of short kernels, each of which waits for the latency of its first loads.  The
 // keys and values do not depend on the step's activations, so this kernel can ask L2 for the NEXT
@@ -25,8 +27,7 @@
 // instructions (attention_decode.cu), whose entry point this one mirrors.
 #include "attention_flash.cuh"
 
-#define DM_WARPS 4
-#define DM_THREADS (DM_WARPS * 32)
+#define DM_MAX_WARPS 8            // warps of a CTA: 4 (two CTAs per SM) or 8 (one CTA per SM), a template parameter
 #define DM_D 128
 #define DM_LD (DM_D + 8)          // padded row of a tile in shared memory, in elements
 #define DM_GK 16                  // keys per group
@@ -37,7 +38,7 @@
 #define DM_TILE_BYTES (DM_GK * DM_LD * 2)                       // keys or values of a group: 4352
 #define DM_WARP_BYTES_OF(stages) ((stages) * 2 * DM_TILE_BYTES)     // a warp's stages: 17408 or 26112
 #define DM_Q_BYTES (DM_ROWS * DM_LD * 2)                        // the item's queries: 4352
-#define DM_SMEM_BYTES_OF(stages) (DM_Q_BYTES + DM_WARPS * DM_WARP_BYTES_OF(stages) + 512)
+#define DM_SMEM_BYTES_OF(stages, warps) (DM_Q_BYTES + (warps) * DM_WARP_BYTES_OF(stages) + (warps) * 128)
 static_assert(DM_WARP_BYTES_OF(2) >= 2 * DM_ROWS * DM_D * 4, "a warp's stages hold its float32 result and the CTA's at the end");
 
 __device__ __forceinline__ void dm_cp_async16_zfill(void* smem, const void* gmem, bool valid) {
@@ -46,16 +47,17 @@ __device__ __forceinline__ void dm_cp_async16_zfill(void* smem, const void* gmem
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" :: "r"(a), "l"(gmem), "r"(bytes));
 }
 
-template <bool CL, int DM_STAGES>
-__global__ void __launch_bounds__(DM_THREADS, 2)
+template <bool CL, int DM_STAGES, int DM_WARPS>
+__global__ void __launch_bounds__(DM_WARPS * 32, DM_WARPS == 4 ? 2 : 1)
 decode_attention_mma_kernel(FaArgs A, long long prefetch_delta) {
+  constexpr int DM_THREADS = DM_WARPS * 32;
   constexpr int DM_WARP_BYTES = DM_WARP_BYTES_OF(DM_STAGES);
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int D = DM_D, LD = DM_LD;
   __nv_bfloat16* sq = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   unsigned char* stages = smem_raw + DM_Q_BYTES;
-  float* s_m = reinterpret_cast<float*>(smem_raw + DM_Q_BYTES + DM_WARPS * DM_WARP_BYTES);   // [4][16] warps' maxima
-  float* s_l = s_m + DM_WARPS * DM_ROWS;                                                     // [4][16] warps' sums
+  float* s_m = reinterpret_cast<float*>(smem_raw + DM_Q_BYTES + DM_WARPS * DM_WARP_BYTES);   // [warps][16] warps' maxima
+  float* s_l = s_m + DM_WARPS * DM_ROWS;                                                     // [warps][16] warps' sums
   __shared__ float m_run[DM_ROWS], l_run[DM_ROWS];  // the CTA's max and sum (read by the cluster's first CTA)
   __shared__ int s_last;
   pdl_launch_dependents();
@@ -322,26 +324,28 @@ static int g_dm_stages = 3;
 // the kernels around it) or 3.
 extern "C" void qe_decode_attention_mma_stages(int stages) { g_dm_stages = stages >= 3 ? 3 : 2; }
 
-template <bool CL, int STAGES>
+template <bool CL, int STAGES, int WARPS>
 static int launch_decode_mma_as(const FaArgs& fa, long long prefetch_delta, int n_items, int Hkv, int cluster, cudaStream_t stream) {
-  constexpr int smem = DM_SMEM_BYTES_OF(STAGES);
+  constexpr int smem = DM_SMEM_BYTES_OF(STAGES, WARPS);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(decode_attention_mma_kernel<CL, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_mma_kernel<CL, STAGES, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) QE_REFUSE("decode_attention_mma: shared memory %d: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
   if (CL)
-    qe_launch_cluster(decode_attention_mma_kernel<CL, STAGES>, dim3(n_items, Hkv), dim3(DM_THREADS), smem, stream, (unsigned)cluster, fa, prefetch_delta);
+    qe_launch_cluster(decode_attention_mma_kernel<CL, STAGES, WARPS>, dim3(n_items, Hkv), dim3(WARPS * 32), smem, stream, (unsigned)cluster, fa, prefetch_delta);
   else
-    qe_launch(decode_attention_mma_kernel<CL, STAGES>, dim3(n_items, Hkv), dim3(DM_THREADS), smem, stream, fa, prefetch_delta);
+    qe_launch(decode_attention_mma_kernel<CL, STAGES, WARPS>, dim3(n_items, Hkv), dim3(WARPS * 32), smem, stream, fa, prefetch_delta);
   QE_CHECK_LAUNCH("decode_attention_mma");
   return 0;
 }
+// wide: CTAs of 8 warps, one per SM (for steps whose items are at most as many as SMs), else 4 warps, two per SM
 template <bool CL>
-static int launch_decode_mma(const FaArgs& fa, long long prefetch_delta, int n_items, int Hkv, int cluster, cudaStream_t stream) {
-  return g_dm_stages == 3 ? launch_decode_mma_as<CL, 3>(fa, prefetch_delta, n_items, Hkv, cluster, stream)
-                          : launch_decode_mma_as<CL, 2>(fa, prefetch_delta, n_items, Hkv, cluster, stream);
+static int launch_decode_mma(const FaArgs& fa, long long prefetch_delta, int n_items, int Hkv, int cluster, int wide, cudaStream_t stream) {
+  if (wide) return launch_decode_mma_as<CL, 3, 8>(fa, prefetch_delta, n_items, Hkv, cluster, stream);
+  return g_dm_stages == 3 ? launch_decode_mma_as<CL, 3, 4>(fa, prefetch_delta, n_items, Hkv, cluster, stream)
+                          : launch_decode_mma_as<CL, 2, 4>(fa, prefetch_delta, n_items, Hkv, cluster, stream);
 }
 
 // Whether the kernel takes this geometry with at most max_rows rows (token x head of the group) per item:
@@ -355,10 +359,11 @@ extern "C" int qe_decode_attention_mma_supported(int Hq, int Hkv, int D, int max
 // the number of parts of every request, 2, 4 or 8, when the items are exactly those parts in order).
 // prefetch_pages: null, or another layer's cache of the same shape whose keys and values for the same requests
 // L2 is asked for (see the top of this file).
+// wide: CTAs of 8 warps, one per SM, instead of 4 warps, two per SM (for steps with at most as many CTAs as SMs).
 // Returns 0 when run, 1 when refused, 2 on a launch error.
 extern "C" int qe_decode_attention_mma(const void* q, long q_stride, const void* pages, const void* prefetch_pages, const int* block_tables,
                                        int max_blocks, const int* items, int n_items, void* out, float* part_acc,
-                                       float* part_ml, int part_rows, int* counters, int max_rows, int cluster, float scale,
+                                       float* part_ml, int part_rows, int* counters, int max_rows, int cluster, int wide, float scale,
                                        int window, int Hq, int Hkv, int D, int page_size, cudaStream_t stream) {
   if (n_items <= 0) return 0;
   if (!qe_decode_attention_mma_supported(Hq, Hkv, D, max_rows))
@@ -370,8 +375,8 @@ extern "C" int qe_decode_attention_mma(const void* q, long q_stride, const void*
   FaArgs fa{(const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pages, block_tables, max_blocks, items,
             (__nv_bfloat16*)out, part_acc, part_ml, part_rows, counters, scale * 1.4426950408889634f, window, Hq, Hkv,
             page_size};
-  if (cluster == 0) return launch_decode_mma<false>(fa, delta, n_items, Hkv, 0, stream);
+  if (cluster == 0) return launch_decode_mma<false>(fa, delta, n_items, Hkv, 0, wide, stream);
   if ((cluster != 2 && cluster != 4 && cluster != 8) || n_items % cluster)
     QE_REFUSE("decode_attention_mma: %d items cannot form clusters of %d", n_items, cluster);
-  return launch_decode_mma<true>(fa, delta, n_items, Hkv, cluster, stream);
+  return launch_decode_mma<true>(fa, delta, n_items, Hkv, cluster, wide, stream);
 }

@@ -149,11 +149,20 @@ __global__ void add_rmsnorm_bf16_warp_kernel(float* __restrict__ resid, const __
                                              float eps, __nv_bfloat16* __restrict__ out, int n_rows) {
   constexpr int H = NC * 256;
   pdl_launch_dependents();
-  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  // the scale vector is a weight and the row list comes with the step's host copy: both are fetched
+  // while the kernel before this one is still running
+  float wv[NC][8];
+#pragma unroll
+  for (int c = 0; c < NC; ++c) {
+    const int h = (c * 32 + lane) * 8;
+    *reinterpret_cast<float4*>(wv[c]) = __ldg(reinterpret_cast<const float4*>(w + h));
+    *reinterpret_cast<float4*>(wv[c] + 4) = __ldg(reinterpret_cast<const float4*>(w + h + 4));
+  }
+  const int src_row = n < n_rows ? (rows ? __ldg(rows + n) : n) : 0;
+  pdl_wait();
   if (n >= n_rows) return;
-  const int src_row = rows ? rows[n] : n;
   float* r = resid + (size_t)src_row * H;
   const __nv_bfloat16* d = delta ? delta + (size_t)src_row * H : nullptr;
   float x[NC][8];
@@ -188,11 +197,8 @@ __global__ void add_rmsnorm_bf16_warp_kernel(float* __restrict__ resid, const __
 #pragma unroll
   for (int c = 0; c < NC; ++c) {
     const int h = (c * 32 + lane) * 8;
-    float wv[8];
-    *reinterpret_cast<float4*>(wv) = *reinterpret_cast<const float4*>(w + h);
-    *reinterpret_cast<float4*>(wv + 4) = *reinterpret_cast<const float4*>(w + h + 4);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) x[c][i] = x[c][i] * rstd * wv[i];
+    for (int i = 0; i < 8; ++i) x[c][i] = x[c][i] * rstd * wv[c][i];
     *reinterpret_cast<uint4*>(o + h) = f32_to_bf16x8(x[c]);
   }
 }
@@ -393,11 +399,20 @@ __global__ void qk_norm_rope_kv_write_kernel(T* __restrict__ q, T* __restrict__ 
 template <int U>
 __global__ void qk_norm_rope_kv_write_d128_kernel(RopeD128Args args) {
   pdl_launch_dependents();
-  pdl_wait();
   // the launcher keeps tokens x heads below 2^31
   const int heads_total = args.Hq + 2 * args.Hkv;
   const int item0 = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * U;
   const int t0 = item0 / heads_total, head0 = item0 - t0 * heads_total;
+  if constexpr (U == 1) {
+    // a small step (a decode step): position, angles, norm weights and cache slot are fetched and worked
+    // out while the kernel before this one (the QKV product) is still running
+    RopeD128Pre pre;
+    rope_d128_prepare(args, t0, head0, pre);
+    pdl_wait();
+    rope_d128_finish(args, t0, head0, rope_d128_load(args, t0, head0), &pre);
+    return;
+  }
+  pdl_wait();
   uint2 raw[U];
   int t[U], head[U];
 #pragma unroll

@@ -32,7 +32,34 @@ __device__ __forceinline__ uint2 rope_d128_load(const RopeD128Args& A, int t, in
   return __ldcg(reinterpret_cast<const uint2*>(src + 4 * lane));
 }
 
-__device__ __forceinline__ void rope_d128_finish(const RopeD128Args& A, int t, int head, const uint2 raw) {
+// What a lane needs besides the head's elements, none of it written by a kernel of the step (positions and
+// slots come with the step's host copy, the rest are weights): a kernel may fetch it before it waits for
+// its predecessor.  Angles only where the step has no table of them.
+struct RopeD128Pre {
+  float cs[4], sn[4];
+  float4 wv;
+  int slot;
+};
+__device__ __forceinline__ void rope_d128_prepare(const RopeD128Args& A, int t, int head, RopeD128Pre& P) {
+  const int lane = threadIdx.x & 31;
+  P.slot = 0;
+  P.wv = make_float4(1.f, 1.f, 1.f, 1.f);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { P.cs[i] = 1.f; P.sn[i] = 0.f; }
+  if (t >= A.T_tokens) return;
+  if (A.write_kv && head >= A.Hq) P.slot = __ldg(A.slot_mapping + t);
+  if (head >= A.Hq + A.Hkv) return;
+  const float* w = head < A.Hq ? A.qw : A.kw;
+  if (w) P.wv = __ldg(reinterpret_cast<const float4*>(w + 4 * lane));
+  if (A.inv_freq && !A.cos_sin) {
+    const float pos = (float)__ldg(A.positions + t);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) sincosf(pos * __ldg(A.inv_freq + ((4 * lane + i) & 63)), &P.sn[i], &P.cs[i]);
+  }
+}
+
+__device__ __forceinline__ void rope_d128_finish(const RopeD128Args& A, int t, int head, const uint2 raw,
+                                                 const RopeD128Pre* pre = nullptr) {
   constexpr int D = 128;
   __nv_bfloat16* q = A.q; __nv_bfloat16* k = A.k;
   const long q_stride = A.q_stride, k_stride = A.k_stride;
@@ -44,7 +71,7 @@ __device__ __forceinline__ void rope_d128_finish(const RopeD128Args& A, int t, i
   if (head >= Hq + Hkv) {           // a value head: copy into the cache
     if (!write_kv) return;
     const int h = head - Hq - Hkv;
-    const int slot = slot_mapping[t];
+    const int slot = pre ? pre->slot : slot_mapping[t];
     // slot = page * page_size + off: the row of (page, V, h, off) is slot + (page * (2 Hkv - 1) + Hkv + h) * page_size
     const int page = (page_size & (page_size - 1)) == 0 ? slot >> (__ffs(page_size) - 1) : slot / page_size;
     *reinterpret_cast<uint2*>(pages + ((size_t)slot + ((size_t)page * (2 * Hkv - 1) + Hkv + h) * page_size) * D + 4 * lane) = raw;
@@ -63,7 +90,7 @@ __device__ __forceinline__ void rope_d128_finish(const RopeD128Args& A, int t, i
   if (w) {
     const float ss = warp_sum(f[0] * f[0] + f[1] * f[1] + f[2] * f[2] + f[3] * f[3]);
     const float rstd = rsqrtf(ss / (float)D + eps);
-    const float4 wv = *reinterpret_cast<const float4*>(w + 4 * lane);
+    const float4 wv = pre ? pre->wv : *reinterpret_cast<const float4*>(w + 4 * lane);
     f[0] = f[0] * rstd * wv.x; f[1] = f[1] * rstd * wv.y; f[2] = f[2] * rstd * wv.z; f[3] = f[3] * rstd * wv.w;
   }
   if (inv_freq) {
@@ -74,6 +101,9 @@ __device__ __forceinline__ void rope_d128_finish(const RopeD128Args& A, int t, i
       const float4 t01 = __ldg(tp), t23 = __ldg(tp + 1);
       cs[0] = t01.x; sn[0] = t01.y; cs[1] = t01.z; sn[1] = t01.w;
       cs[2] = t23.x; sn[2] = t23.y; cs[3] = t23.z; sn[3] = t23.w;
+    } else if (pre) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { cs[i] = pre->cs[i]; sn[i] = pre->sn[i]; }
     } else {
       const float pos = (float)positions[t];
 #pragma unroll
@@ -93,7 +123,7 @@ __device__ __forceinline__ void rope_d128_finish(const RopeD128Args& A, int t, i
   }
   *reinterpret_cast<uint2*>(x) = res;
   if (!is_q && write_kv) {
-    const int slot = slot_mapping[t];
+    const int slot = pre ? pre->slot : slot_mapping[t];
     const int page = (page_size & (page_size - 1)) == 0 ? slot >> (__ffs(page_size) - 1) : slot / page_size;
     *reinterpret_cast<uint2*>(pages + ((size_t)slot + ((size_t)page * (2 * Hkv - 1) + h) * page_size) * D + 4 * lane) = res;
   }

@@ -48,6 +48,7 @@ DECODE_ATTENTION_MIN_CTAS = 128 # CTAs from which it is used: measured, it gains
 DECODE_ATTENTION_MMA = True         # decoded tokens (up to 16 rows per kv head, head size 128): warps with key groups and pipelines of their own, mma.sync arithmetic
 DECODE_ATTENTION_MMA_MIN_CTAS = 0   # CTAs from which that kernel is used
 DECODE_ATTENTION_MMA_STAGES = 3     # key groups a warp of that kernel keeps in flight (2 or 3; measured: 3 is 2.5 % ahead in the step)
+DECODE_ATTENTION_MMA_WIDE = True    # steps with at most as many attention CTAs as SMs: CTAs of 8 warps, one per SM (and contexts split for 148 CTAs, not 296)
 DECODE_PREFETCH_KV_MB = 0           # that kernel asks L2 for the next layer's keys and values when a layer's are at most this many MB (0: never)
 TC_ROWS = 256           # rows per work item of the tcgen05 attention kernel (two halves of 128)
 TC_BN = 128             # keys per step of the tcgen05 attention kernel
@@ -844,7 +845,11 @@ def decode_splits(num_reqs: int, max_tokens: int, geometries, dtype: torch.dtype
     for geo in geometries:
         Hq, Hkv, D, window = geo
         span = min(max_tokens, window) if window else max_tokens
-        want = max(1, FLASH_TARGET_CTAS // max(1, num_reqs * Hkv))      # all parts run in one wave
+        target = FLASH_TARGET_CTAS
+        if (DECODE_ATTENTION_MMA and DECODE_ATTENTION_MMA_WIDE and dtype == torch.bfloat16 and D == 128
+                and Hq // Hkv <= 16 and num_reqs * Hkv <= TC_TARGET_CTAS):
+            target = TC_TARGET_CTAS                                       # one CTA of 8 warps per SM
+        want = max(1, target // max(1, num_reqs * Hkv))                   # all parts run in one wave
         out[geo] = max(1, min(want, -(-span // FLASH_SPLIT)))
     return out
 
@@ -979,7 +984,8 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
             _check(lib().qe_decode_attention_mma(
                 _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(ahead), _ptr(block_tables), int(block_tables.shape[1]),
                 _ptr(items), n_items, _ptr(out), _ptr(part_acc), _ptr(part_ml), int(part_rows), _ptr(counters),
-                int(max_rows), cluster, ctypes.c_float(scale), int(window), Hq, Hkv, D, int(kv_pages.shape[3]), _stream()),
+                int(max_rows), cluster, int(DECODE_ATTENTION_MMA_WIDE and n_items * Hkv <= TC_TARGET_CTAS),
+                ctypes.c_float(scale), int(window), Hq, Hkv, D, int(kv_pages.shape[3]), _stream()),
                 "decode_attention_mma")
             return
         if serves:

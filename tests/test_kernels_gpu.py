@@ -418,14 +418,15 @@ def test_flash_attention_split_contexts(Hq, Hkv, D, P, q_lens, ctx_lens):
     _close(got, want, dtype)
 
 
-@pytest.fixture(params=["mma", "plain"])
+@pytest.fixture(params=["mma", "mma4", "plain"])
 def decode_kernel(request):
     """Which kernel for decoded tokens ``ops.paged_attention`` picks: the one whose warps stream key groups
-    through mma.sync, or the one without matrix instructions."""
-    saved = ops.DECODE_ATTENTION_MMA
-    ops.DECODE_ATTENTION_MMA = request.param == "mma"
+    through mma.sync (with CTAs of 8 warps where they are few; mma4: always 4 warps), or the one without
+    matrix instructions."""
+    saved = ops.DECODE_ATTENTION_MMA, ops.DECODE_ATTENTION_MMA_WIDE
+    ops.DECODE_ATTENTION_MMA, ops.DECODE_ATTENTION_MMA_WIDE = request.param != "plain", request.param == "mma"
     yield request.param
-    ops.DECODE_ATTENTION_MMA = saved
+    ops.DECODE_ATTENTION_MMA, ops.DECODE_ATTENTION_MMA_WIDE = saved
 
 
 @pytest.mark.parametrize("Hq,Hkv,P", [(16, 8, 16), (4, 4, 8), (8, 2, 32), (4, 1, 16), (6, 3, 4), (2, 1, 256)])
@@ -538,7 +539,7 @@ def test_decode_attention_with_rotary_fused(Hq, Hkv, P, ctx_lens, norm, write_kv
 @pytest.mark.parametrize("q_lens,ctx_lens", [([1], [77]), ([2, 1], [100, 37]), ([1, 1, 1], [5, 130, 1333]), ([1, 2], [3000, 15]),
                                              ([1, 1, 1, 1], [0, 47, 48, 49])])
 @pytest.mark.parametrize("window", [0, 100])
-@pytest.mark.parametrize("stages", [2, 3])
+@pytest.mark.parametrize("stages", [2, 3, 8])
 def test_decode_attention_mma_many_rows(Hq, Hkv, P, q_lens, ctx_lens, window, stages, monkeypatch):
     """The tensor-core kernel for decoded tokens with up to 16 rows per kv head (large groups of query
     heads, two tokens of a request in one item), page sizes below and above its key groups, contexts
@@ -552,7 +553,8 @@ def test_decode_attention_mma_many_rows(Hq, Hkv, P, q_lens, ctx_lens, window, st
     case = _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, seed=47)
     want = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ref_ops.paged_attention, "cpu")
     assert ops.DECODE_ATTENTION_MMA
-    monkeypatch.setattr(ops, "DECODE_ATTENTION_MMA_STAGES", stages)
+    monkeypatch.setattr(ops, "DECODE_ATTENTION_MMA_WIDE", stages == 8)     # 8: the form with 8 warps (3 stages)
+    monkeypatch.setattr(ops, "DECODE_ATTENTION_MMA_STAGES", min(stages, 3))
     got = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ops.paged_attention, DEV)
     assert ops.last_attention_kernel == "decode_attention_mma"
     _close(got, want, dtype)
