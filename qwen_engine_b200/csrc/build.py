@@ -22,12 +22,25 @@ CSRC_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_NAME = "libqwen_engine_b200.so"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC"]
-if os.environ.get("QE_TIMELINE") == "1":
-    # the build whose kernels record when they start and when their predecessors end (common.cuh);
-    # a library of its own beside the plain one
-    NVCC_FLAGS = NVCC_FLAGS + ["-DQE_TIMELINE"]
-    LIB_NAME = "libqwen_engine_b200_timeline.so"
-BUILD_FOLDER = "_build_timeline" if "-DQE_TIMELINE" in NVCC_FLAGS else "_build"
+
+
+def timeline_build() -> bool:
+    """QE_TIMELINE=1 in the environment (looked at when the library is first needed) asks for the build
+    whose kernels record when they start and when their predecessors end (common.cuh): a library of
+    its own, in a folder of its own beside the plain one."""
+    return os.environ.get("QE_TIMELINE") == "1"
+
+
+def nvcc_flags() -> list[str]:
+    return NVCC_FLAGS + (["-DQE_TIMELINE"] if timeline_build() else [])
+
+
+def lib_name() -> str:
+    return "libqwen_engine_b200_timeline.so" if timeline_build() else LIB_NAME
+
+
+def build_folder() -> str:
+    return "_build_timeline" if timeline_build() else "_build"
 
 
 class BuildError(RuntimeError):
@@ -56,12 +69,12 @@ def _digest() -> str:
         h.update(f.encode())
         with open(os.path.join(CSRC_DIR, f), "rb") as fh:
             h.update(fh.read())
-    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
+    h.update(" ".join(ARCH_FLAGS + nvcc_flags()).encode())
     return h.hexdigest()
 
 
 def _build_dir() -> str:
-    in_tree = os.path.join(CSRC_DIR, BUILD_FOLDER)
+    in_tree = os.path.join(CSRC_DIR, build_folder())
     try:
         os.makedirs(in_tree, exist_ok=True)
         probe = os.path.join(in_tree, f".w{os.getpid()}")
@@ -70,7 +83,7 @@ def _build_dir() -> str:
         os.remove(probe)
         return in_tree
     except OSError:
-        alt = os.path.join(tempfile.gettempdir(), f"qwen_engine_b200{BUILD_FOLDER}_{os.getuid()}")
+        alt = os.path.join(tempfile.gettempdir(), f"qwen_engine_b200{build_folder()}_{os.getuid()}")
         os.makedirs(alt, exist_ok=True)
         return alt
 
@@ -78,7 +91,7 @@ def _build_dir() -> str:
 def library_path(build_if_needed: bool = True, verbose: bool = True) -> str:
     """Path of an up-to-date library, compiling it first if it is stale or absent."""
     bdir = _build_dir()
-    lib = os.path.join(bdir, LIB_NAME)
+    lib = os.path.join(bdir, lib_name())
     stamp = os.path.join(bdir, "sources.sha256")
     digest = _digest()
     if os.path.isfile(lib) and os.path.isfile(stamp):
@@ -109,7 +122,7 @@ def _compile(bdir: str, lib: str, verbose: bool) -> None:
 
     def one(src: str) -> str:
         obj = os.path.join(bdir, src[:-3] + ".o")
-        cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, "-I", CSRC_DIR, "-c", os.path.join(CSRC_DIR, src), "-o", obj]
+        cmd = [nvcc, *ARCH_FLAGS, *nvcc_flags(), "-I", CSRC_DIR, "-c", os.path.join(CSRC_DIR, src), "-o", obj]
         t1 = time.time()
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:

@@ -20,8 +20,22 @@
 // the float32 accumulators, as 128 columns of out [M, I]: the activation never exists as gate_up in
 // memory (reference: src/layers/fused_ops/silumul.py:50-53 applies it to the rounded products).
 //
+// ROPE: w is an attention layer's stacked q, k, v weights with head size 128, so a tile's 256 columns are
+// two whole heads and an epilogue thread holds a token's whole head.  The epilogue does what the rotary
+// kernel would do to the product afterwards (elementwise.cu, rope_d128.cuh: the product rounded to
+// bfloat16, per-head RMS norm of q and k in float32, rotation of the pairs (d, d + 64) by the step's table
+// of angles, rounded once): q goes to out, k and v go straight into the cache pages at the tokens' slots
+// and are not written to out at all.  The rotary kernel's launch and its pass over the product disappear.
+//
 // Needs K % 8 == 0 and 16-byte aligned bases (TMA strides); the launcher refuses the rest.
 #include "tcgen05.cuh"
+
+struct PrRope {
+  const float* qw; const float* kw; float eps;      // norm weights [128] (null: no norm)
+  const float2* cos_sin;                            // [M, 64] (cos, sin) of every token's angles (null: no rotation)
+  __nv_bfloat16* pages; const int* slot_mapping;    // the cache [pages, 2, Hkv, page, 128] and the tokens' slots
+  int Hq, Hkv, page_size, write_kv;
+};
 
 #define PR_BM 128               // rows of x per CTA (256 per pair)
 #define PR_BK 64
@@ -42,11 +56,12 @@ struct __align__(1024) PrSmem {
 };
 
 // N: columns of the product (SWIGLU: 2 I); n_up: SWIGLU: the first row of up in w (= I), else 0
-template <typename TOut, int BN, int STAGES, bool SWIGLU>
+template <typename TOut, int BN, int STAGES, bool SWIGLU, bool ROPE = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PR_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                         TOut* __restrict__ out, int M, int N, int K, int n_up) {
+                         TOut* __restrict__ out, int M, int N, int K, int n_up, PrRope rp) {
   static_assert(!SWIGLU || BN == 256, "the fused activation pairs 128 columns of gate with 128 of up");
+  static_assert(!ROPE || (BN == 256 && !SWIGLU && sizeof(TOut) == 2), "the fused rotation takes two heads of 128 per tile, in bfloat16");
   extern __shared__ unsigned char smem_raw[];
   using Smem = PrSmem<BN, STAGES>;
   constexpr uint32_t TMEM_COLS = 2 * BN;
@@ -188,6 +203,106 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             }
           }
         }
+      } else if constexpr (ROPE) {
+        // two heads of 128 columns; this thread holds its token's whole head.  Per head two passes over the
+        // accumulator (tensor memory is cheap to read again): the sum of squares, then, for the columns
+        // (0-31, 64-95) and (32-63, 96-127), norm, rotation and store, with the angles' loads in flight
+        // beside the accumulator's.
+        const bool row_ok = row < M;
+        int slot = 0;
+        if (row_ok && rp.write_kv) slot = __ldg(rp.slot_mapping + row);
+        const float4* tp = reinterpret_cast<const float4*>(rp.cos_sin + (size_t)(row_ok ? row : 0) * 64);
+        const uint32_t tm_row = tmem + ((uint32_t)(quarter * 32) << 16) + buf * BN;
+        auto rnd = [](uint32_t u) { return __bfloat162float(__float2bfloat16_rn(__uint_as_float(u))); };   // as the plain product's output is rounded
+#pragma unroll 1
+        for (int hh = 0; hh < 2; ++hh) {
+          const int col0 = n0 + hh * 128, head = col0 >> 7;
+          const bool is_q = head < rp.Hq, is_v = head >= rp.Hq + rp.Hkv;
+          const bool wanted = row_ok && col0 < N && (is_q || rp.write_kv);   // (keys and values of a layer that reads another's cache are dropped)
+          const float* w = is_v ? nullptr : (is_q ? rp.qw : rp.kw);
+          float rstd = 1.f;
+          if (w) {                                   // warp-uniform
+            float s4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int c = 0; c < 4; c += 2) {
+              uint32_t a[32], b[32];
+              tc_ld_32x32b_x32(tm_row + hh * 128 + c * 32, a);
+              tc_ld_32x32b_x32(tm_row + hh * 128 + c * 32 + 32, b);
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                const float a0 = rnd(a[i]), a1 = rnd(a[i + 1]), b0 = rnd(b[i]), b1 = rnd(b[i + 1]);
+                s4[0] = fmaf(a0, a0, s4[0]); s4[1] = fmaf(a1, a1, s4[1]); s4[2] = fmaf(b0, b0, s4[2]); s4[3] = fmaf(b1, b1, s4[3]);
+              }
+            }
+            rstd = rsqrtf(((s4[0] + s4[1]) + (s4[2] + s4[3])) / 128.f + rp.eps);
+          }
+          __nv_bfloat16* dst = nullptr;
+          if (wanted) {
+            if (is_q) {
+              dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * N + col0;
+            } else {
+              // slot = page * page_size + off: the row of (page, K or V, h, off) in the cache
+              const int h = is_v ? head - rp.Hq - rp.Hkv : head - rp.Hq;
+              const int page = (rp.page_size & (rp.page_size - 1)) == 0 ? slot >> (__ffs(rp.page_size) - 1) : slot / rp.page_size;
+              dst = rp.pages + ((size_t)slot + ((size_t)page * (2 * rp.Hkv - 1) + (is_v ? rp.Hkv : 0) + h) * rp.page_size) * 128;
+            }
+          }
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {     // columns 32 half .. + 31 and their partners 64 further
+            uint32_t lo[32], hi[32];
+            tc_ld_32x32b_x32(tm_row + hh * 128 + half * 32, lo);
+            tc_ld_32x32b_x32(tm_row + hh * 128 + 64 + half * 32, hi);
+            float4 t[16];
+            const bool rotate = !is_v && rp.cos_sin != nullptr;
+            if (rotate && wanted) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) t[j] = __ldg(tp + half * 16 + j);     // (cos, sin) of elements 32 half + 2j, + 2j + 1
+            }
+            tc_wait_ld();
+            if (hh == 1 && half == 1) {
+              // the accumulator is in registers: tell the leading CTA's MMA thread
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive_cluster(smem_u32(&sm.acc_empty[buf]) & TC_PEER_BIT_MASK);
+            }
+            if (!wanted) continue;
+            float xl[32], xh[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) { xl[i] = rnd(lo[i]); xh[i] = rnd(hi[i]); }
+            if (w) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) {
+                const float4 wl = __ldg(reinterpret_cast<const float4*>(w + half * 32 + i));
+                const float4 wh = __ldg(reinterpret_cast<const float4*>(w + 64 + half * 32 + i));
+                xl[i] = xl[i] * rstd * wl.x; xl[i + 1] = xl[i + 1] * rstd * wl.y; xl[i + 2] = xl[i + 2] * rstd * wl.z; xl[i + 3] = xl[i + 3] * rstd * wl.w;
+                xh[i] = xh[i] * rstd * wh.x; xh[i + 1] = xh[i + 1] * rstd * wh.y; xh[i + 2] = xh[i + 2] * rstd * wh.z; xh[i + 3] = xh[i + 3] * rstd * wh.w;
+              }
+            }
+            if (rotate) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const float l0 = xl[2 * j], h0 = xh[2 * j], l1 = xl[2 * j + 1], h1 = xh[2 * j + 1];
+                xl[2 * j] = t[j].x * l0 - t[j].y * h0;      xh[2 * j] = t[j].y * l0 + t[j].x * h0;
+                xl[2 * j + 1] = t[j].z * l1 - t[j].w * h1;  xh[2 * j + 1] = t[j].w * l1 + t[j].z * h1;
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 v, u;
+              __nv_bfloat162 p0 = __floats2bfloat162_rn(xl[j], xl[j + 1]), p1 = __floats2bfloat162_rn(xl[j + 2], xl[j + 3]);
+              __nv_bfloat162 p2 = __floats2bfloat162_rn(xl[j + 4], xl[j + 5]), p3 = __floats2bfloat162_rn(xl[j + 6], xl[j + 7]);
+              v.x = *reinterpret_cast<uint32_t*>(&p0); v.y = *reinterpret_cast<uint32_t*>(&p1);
+              v.z = *reinterpret_cast<uint32_t*>(&p2); v.w = *reinterpret_cast<uint32_t*>(&p3);
+              __nv_bfloat162 q0 = __floats2bfloat162_rn(xh[j], xh[j + 1]), q1 = __floats2bfloat162_rn(xh[j + 2], xh[j + 3]);
+              __nv_bfloat162 q2 = __floats2bfloat162_rn(xh[j + 4], xh[j + 5]), q3 = __floats2bfloat162_rn(xh[j + 6], xh[j + 7]);
+              u.x = *reinterpret_cast<uint32_t*>(&q0); u.y = *reinterpret_cast<uint32_t*>(&q1);
+              u.z = *reinterpret_cast<uint32_t*>(&q2); u.w = *reinterpret_cast<uint32_t*>(&q3);
+              *reinterpret_cast<uint4*>(dst + half * 32 + j) = v;
+              *reinterpret_cast<uint4*>(dst + 64 + half * 32 + j) = u;
+            }
+          }
+        }
       } else {
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -242,8 +357,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   }
 }
 
-template <int BN, int STAGES, bool SWIGLU = false>
-static int launch_pair(const void* x, const void* w, void* out, int M, int N, int K, int out_f32, int sms, cudaStream_t stream) {
+template <int BN, int STAGES, bool SWIGLU = false, bool ROPE = false>
+static int launch_pair(const void* x, const void* w, void* out, int M, int N, int K, int out_f32, int sms, cudaStream_t stream,
+                       PrRope rp = PrRope{}) {
   const int n_up = SWIGLU ? N / 2 : 0;
   CUtensorMap map_x, map_w;
   {
@@ -261,8 +377,9 @@ static int launch_pair(const void* x, const void* w, void* out, int M, int N, in
   const size_t smem = sizeof(PrSmem<BN, STAGES>) + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<__nv_bfloat16, BN, STAGES, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<float, BN, STAGES, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<__nv_bfloat16, BN, STAGES, SWIGLU, ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if constexpr (!ROPE)
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<float, BN, STAGES, SWIGLU, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) QE_REFUSE("linear_tcgen05_pair: shared memory %zu: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
@@ -270,10 +387,14 @@ static int launch_pair(const void* x, const void* w, void* out, int M, int N, in
   const long tiles = n_blocks * ((M + 2 * PR_BM - 1) / (2 * PR_BM));
   const long pairs = tiles < sms / 2 ? tiles : sms / 2;
   const dim3 grid((unsigned)(2 * pairs));
-  if (out_f32)
-    qe_launch(gemm_tcgen05_pair_kernel<float, BN, STAGES, SWIGLU>, grid, dim3(PR_THREADS), smem, stream, map_x, map_w, (float*)out, M, N, K, n_up);
-  else
-    qe_launch(gemm_tcgen05_pair_kernel<__nv_bfloat16, BN, STAGES, SWIGLU>, grid, dim3(PR_THREADS), smem, stream, map_x, map_w, (__nv_bfloat16*)out, M, N, K, n_up);
+  if constexpr (ROPE) {
+    qe_launch(gemm_tcgen05_pair_kernel<__nv_bfloat16, BN, STAGES, false, true>, grid, dim3(PR_THREADS), smem, stream, map_x, map_w, (__nv_bfloat16*)out, M, N, K, n_up, rp);
+  } else {
+    if (out_f32)
+      qe_launch(gemm_tcgen05_pair_kernel<float, BN, STAGES, SWIGLU, false>, grid, dim3(PR_THREADS), smem, stream, map_x, map_w, (float*)out, M, N, K, n_up, rp);
+    else
+      qe_launch(gemm_tcgen05_pair_kernel<__nv_bfloat16, BN, STAGES, SWIGLU, false>, grid, dim3(PR_THREADS), smem, stream, map_x, map_w, (__nv_bfloat16*)out, M, N, K, n_up, rp);
+  }
   QE_CHECK_LAUNCH("linear_tcgen05_pair");
   return 0;
 }
@@ -310,4 +431,26 @@ extern "C" int qe_linear_swiglu_tcgen05_pair(const void* x, const void* w, void*
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (sms < 2) QE_REFUSE("linear_swiglu: needs at least two SMs");
   return launch_pair<256, 6, true>(x, w, out, M, 2 * I, K, out_f32, sms, stream);
+}
+
+// out[M, N] = the q columns of x · w^T for the stacked q, k, v weights w [N = (Hq + 2 Hkv) 128, K], normed per head
+// and rotated; the k and v columns go into the cache `pages` [pages, 2, Hkv, page_size, 128] at slot_mapping[row]
+// (write_kv 0: they are dropped: a layer that reads another layer's cache) and out's k and v columns are left as
+// they were (see ROPE above).  qw, kw: float32 [128] or null; cos_sin: float32 [M, 64, 2] or null.
+// Returns 0 when run, 1 when refused, 2 on a launch error.
+extern "C" int qe_linear_qkv_rope_tcgen05_pair(const void* x, const void* w, void* out, int M, int N, int K,
+                                               const float* qw, const float* kw, float eps, const void* cos_sin,
+                                               void* pages, const int* slot_mapping, int Hq, int Hkv, int page_size,
+                                               int write_kv, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8) QE_REFUSE("linear_qkv_rope: K = %d is not a positive multiple of 8", K);
+  if (Hq < 1 || Hkv < 1 || N != (Hq + 2 * Hkv) * 128) QE_REFUSE("linear_qkv_rope: N = %d is not (%d + 2 x %d) heads of 128", N, Hq, Hkv);
+  if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out | (uintptr_t)qw | (uintptr_t)kw | (uintptr_t)cos_sin | (uintptr_t)pages) & 15)
+    QE_REFUSE("linear_qkv_rope: operands must be 16-byte aligned");
+  if (write_kv && (!pages || !slot_mapping || page_size < 1)) QE_REFUSE("linear_qkv_rope: cache write without a cache");
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (sms < 2) QE_REFUSE("linear_qkv_rope: needs at least two SMs");
+  PrRope rp{qw, kw, eps, (const float2*)cos_sin, (__nv_bfloat16*)pages, slot_mapping, Hq, Hkv, page_size, write_kv ? 1 : 0};
+  return launch_pair<256, 6, false, true>(x, w, out, M, N, K, 0, sms, stream, rp);
 }

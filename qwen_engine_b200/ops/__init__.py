@@ -556,6 +556,51 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -
                                                int(out.dtype == torch.float32), _stream()), "linear_swiglu")
 
 
+QKV_ROPE_FUSED = True       # many rows: per-head norm, rotation and cache write in the epilogue of the QKV product
+QKV_ROPE_MIN_TILES = 74     # 256 x 256 tiles of the product from which it is used (one per pair of SMs)
+
+
+def qkv_rope_fused_applies(M: int, N: int, K: int, dtype: torch.dtype, head_dim: int, rotary_dim: int) -> bool:
+    """Whether ``linear_qkv_rope`` serves this shape: bfloat16, head size 128 rotated as a whole, and
+    enough 256 x 256 tiles for every pair of SMs (the kernel is the CTA-pair product)."""
+    return (QKV_ROPE_FUSED and TCGEN05_PAIRS and TCGEN05_ENABLED and _program is None and dtype == torch.bfloat16
+            and head_dim == 128 and rotary_dim == 128 and K % 8 == 0 and N % 128 == 0
+            and -(-M // 256) * -(-N // 256) >= QKV_ROPE_MIN_TILES)
+
+
+def linear_qkv_rope(x: torch.Tensor, w_qkv: torch.Tensor, qkv: torch.Tensor, q_norm_w: Optional[torch.Tensor],
+                    k_norm_w: Optional[torch.Tensor], eps: float, cos_sin: Optional[torch.Tensor],
+                    kv_pages: Optional[torch.Tensor], slot_mapping: Optional[torch.Tensor],
+                    num_heads: int, num_kv_heads: int, write_kv: bool = True) -> None:
+    """The QKV product with what ``qk_norm_rope_kv_write`` would do to it afterwards done in its epilogue
+    (head size 128, bfloat16): qkv[:, :Hq 128] = rotated, normed q; the rotated, normed k and v go to their
+    slots in ``kv_pages`` [pages, 2, Hkv, page, 128] only (the k and v columns of ``qkv`` are not written).
+    ``cos_sin``: float32 [T, 64, 2], the step's table of angles (None: no rotation)."""
+    M, K = x.shape
+    Hq, Hkv = num_heads, num_kv_heads
+    N = (Hq + 2 * Hkv) * 128
+    _need(x.dtype == torch.bfloat16 and w_qkv.dtype == torch.bfloat16 and w_qkv.shape == (N, K) and K % 8 == 0,
+          "linear_qkv_rope: bfloat16 operands, w [(Hq + 2 Hkv) 128, K] with K a multiple of 8")
+    _need(qkv.shape == (M, N) and qkv.dtype == torch.bfloat16 and qkv.is_contiguous() and x.is_contiguous() and w_qkv.is_contiguous(),
+          "linear_qkv_rope: qkv must be contiguous bfloat16 [M, (Hq + 2 Hkv) 128]")
+    for wt in (q_norm_w, k_norm_w):
+        _need(wt is None or (wt.dtype == torch.float32 and wt.shape == (128,)), "linear_qkv_rope: norm weights must be float32 [128]")
+    _need(cos_sin is None or (cos_sin.dtype == torch.float32 and cos_sin.shape == (M, 64, 2) and cos_sin.is_contiguous()),
+          "linear_qkv_rope: cos_sin must be float32 [M, 64, 2]")
+    page_size = 1
+    if write_kv:
+        _need(kv_pages is not None and slot_mapping is not None and kv_pages.dtype == torch.bfloat16 and kv_pages.is_contiguous()
+              and kv_pages.dim() == 5 and kv_pages.shape[1] == 2 and kv_pages.shape[2] == Hkv and kv_pages.shape[4] == 128,
+              "linear_qkv_rope: kv_pages must be bfloat16 [pages, 2, Hkv, page, 128]")
+        _i32(slot_mapping, "slot_mapping")
+        _need(slot_mapping.numel() >= M, "linear_qkv_rope: a slot for every row")
+        page_size = int(kv_pages.shape[3])
+    _check(lib().qe_linear_qkv_rope_tcgen05_pair(
+        _ptr(x), _ptr(w_qkv), _ptr(qkv), M, N, K, _ptr(q_norm_w), _ptr(k_norm_w), ctypes.c_float(eps), _ptr(cos_sin),
+        _ptr(kv_pages if write_kv else None), _ptr(slot_mapping if write_kv else None), Hq, Hkv, page_size,
+        int(bool(write_kv)), _stream()), "linear_qkv_rope")
+
+
 def linear_silu_mul(gate_up: torch.Tensor, w: torch.Tensor, out: torch.Tensor, scratch) -> None:
     """out[M, N] = (silu(gate_up[:, :I]) * gate_up[:, I:]) · w[N, I]^T.  For a few rows in bfloat16 the
     activation is formed while the product loads it; otherwise ``silu_mul`` runs first into a buffer

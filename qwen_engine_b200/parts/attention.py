@@ -81,10 +81,22 @@ class GQAAttention(Mixer):
         H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
         view = ctx.groups[group]
         qkv = ctx.arena.alloc((T, self.q_width + 2 * self.kv_width), ctx.dtype)
-        ops.prefetch_next(self.w_o)
-        ops.linear(x, self.w_qkv, qkv)
         fused_rope = isinstance(self.pos, NeoxRope)
         attn = ctx.arena.alloc((T, self.q_width), ctx.dtype)
+        if fused_rope and ops.qkv_rope_fused_applies(T, qkv.shape[1], self.hidden_size, ctx.dtype, D, self.pos.rotary_dim):
+            table = self.pos.step_table(ctx)
+            if table is not None:
+                # many rows: norm, rotation and cache write happen in the epilogue of the QKV product
+                if isinstance(x, ops.NormedInput):
+                    x = x.materialize()
+                ops.linear_qkv_rope(x, self.w_qkv, qkv, self.q_norm_w, self.k_norm_w, self.qk_norm_eps or 0.0, table,
+                                    cache, view.slot_mapping, H, Hkv, write_kv=write_cache)
+                ops.paged_attention(qkv, cache, view.block_tables, ctx, attn, self.scale,
+                                    self.window or 0, H, Hkv, D, next_pages=step_hint(ctx, "next_cache"))
+                ops.linear(attn, self.w_o, out)
+                return
+        ops.prefetch_next(self.w_o)
+        ops.linear(x, self.w_qkv, qkv)
         if fused_rope and ops.attention_fuses_rotary(qkv, ctx, H, Hkv, D, self.window or 0, self.pos.rotary_dim):
             # a decode step: the attention kernel norms and rotates q and k and writes the cache itself
             ops.paged_attention(qkv, cache, view.block_tables, ctx, attn, self.scale, self.window or 0, H, Hkv, D,

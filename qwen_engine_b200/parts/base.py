@@ -50,10 +50,12 @@ class Arena:
 
     def __init__(self, device, capacity: int = 1 << 20):
         self.device = torch.device(device)
+        capacity = -(-int(capacity) // self.ALIGN) * self.ALIGN
         self.capacity = capacity
         self.buffer = torch.empty(capacity, dtype=torch.uint8, device=self.device)
         self.offset = 0
         self.high_water = 0
+        self.top = capacity                   # step-lived allocations grow down from here (alloc_step)
         self._overflow: list[torch.Tensor] = []
         self._overflow_bytes = 0
         self._views: dict = {}
@@ -61,12 +63,37 @@ class Arena:
     def reset(self) -> None:
         if self._overflow:
             self._views = {}
-            self.capacity = int((self.high_water + self._overflow_bytes) * 1.25) + self.ALIGN
+            self.capacity = int((self.high_water + (self.capacity - self.top) + self._overflow_bytes) * 1.25) + self.ALIGN
+            self.capacity = -(-self.capacity // self.ALIGN) * self.ALIGN
             self._overflow = []
             self._overflow_bytes = 0
             self.buffer = torch.empty(self.capacity, dtype=torch.uint8, device=self.device)
         self.offset = 0
         self.high_water = 0
+        self.top = self.capacity
+
+    def alloc_step(self, shape, dtype: torch.dtype) -> torch.Tensor:
+        """Memory that lives until the step ends, whatever marks are released meanwhile (a table that the
+        first layer makes and every layer reads): taken from the buffer's far end, never given back
+        before ``reset()``."""
+        shape = tuple(int(s) for s in shape)
+        numel = 1
+        for s in shape:
+            numel *= s
+        nbytes = numel * dtype.itemsize
+        padded = -(-max(nbytes, 1) // self.ALIGN) * self.ALIGN
+        if self.top - padded < max(self.offset, self.high_water):
+            t = torch.empty(shape, dtype=dtype, device=self.device)
+            self._overflow.append(t)
+            self._overflow_bytes += padded
+            return t
+        self.top -= padded
+        key = ("step", self.top, shape, dtype)
+        view = self._views.get(key)
+        if view is None:
+            view = self.buffer[self.top:self.top + nbytes].view(dtype).view(shape)
+            self._views[key] = view
+        return view
 
     def mark(self) -> int:
         return self.offset
@@ -77,7 +104,7 @@ class Arena:
     def alloc(self, shape, dtype: torch.dtype) -> torch.Tensor:
         shape = tuple(shape)
         hit = self._views.get((self.offset, shape, dtype))
-        if hit is not None:
+        if hit is not None and hit[1] <= self.top:
             view, end = hit
             self.offset = end
             if end > self.high_water:
@@ -89,7 +116,7 @@ class Arena:
             numel *= s
         nbytes = numel * dtype.itemsize
         padded = -(-max(nbytes, 1) // self.ALIGN) * self.ALIGN
-        if self.offset + padded > self.capacity:
+        if self.offset + padded > self.top:
             t = torch.empty(shape, dtype=dtype, device=self.device)
             self._overflow.append(t)
             self._overflow_bytes += padded

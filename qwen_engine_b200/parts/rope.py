@@ -42,7 +42,8 @@ class NeoxRope(PositionEncoding):
         key = ("rope_table", self.theta, self.rotary_dim)
         table = ctx.extras.get(key)
         if table is None:
-            table = ctx.arena.alloc((ctx.num_tokens, self.rotary_dim // 2, 2), torch.float32)
+            # (for the whole step: a layer's own scratch is handed to the next layer when the layer is done)
+            table = ctx.arena.alloc_step((ctx.num_tokens, self.rotary_dim // 2, 2), torch.float32)
             ops.rope_table(ctx.positions, self.inv_freq, table)
             ctx.extras[key] = table
         return table

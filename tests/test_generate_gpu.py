@@ -218,3 +218,49 @@ def test_decode_program_agrees_with_separate_launches(tmp_path):
     assert torch.isfinite(a).all()
     scale = max(1.0, float(b.abs().max()))
     assert float((a - b).abs().max()) <= 1e-2 * scale
+
+
+@pytest.mark.parametrize("fused", [True, False])
+def test_norm_and_rotation_with_head_size_128(tmp_path, monkeypatch, fused):
+    """Prompt portions of many rows with head size 128 in bfloat16 take their rotation angles from a table that
+    the first layer makes for the step and every layer reads (it must outlive the layers' own scratch, also in
+    steps whose scratch no longer grows: portions of a size that came before); and with ``fused`` the per-head
+    norm, the rotation and the cache write happen in the epilogue of the QKV product (ops.linear_qkv_rope).
+    A prompt run whole, in portions of changing and of repeated sizes (some too small for table and
+    epilogue: the separate kernel with its own angles), then decoded tokens that read the cache all of these
+    left behind, against the plain implementation; and the ways of cutting against each other."""
+    from qwen_engine_b200 import ops
+    from qwen_engine_b200.engine.loading import load_model
+    from qwen_engine_b200.engine.runner import StepEntry
+    from qwen_engine_b200.registry import config_from_dict
+    from qwen_engine_b200.weights import write_model_folder
+    raw = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=4, hidden_size=200, num_attention_heads=6,
+               num_key_value_heads=3, head_dim=128, intermediate_size=272, vocab_size=611, rope_theta=1e6,
+               rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=4096)
+    folder = write_model_folder(config_from_dict(raw), str(tmp_path / "m"), seed=9, std=0.05, norm_std=0.1)
+    tokens = random_tokens(611, 700, 77)
+    want = helpers.plain_logits(folder, tokens)
+    monkeypatch.setattr(ops, "QKV_ROPE_MIN_TILES", 1 if fused else 10 ** 9)
+    used = []
+    real = ops.linear_qkv_rope
+    monkeypatch.setattr(ops, "linear_qkv_rope", lambda *a, **k: (used.append(a[0].shape[0]), real(*a, **k))[1])
+    got = []
+    for cut in ([660], [100, 37, 200, 2, 321], [100, 100, 100, 100, 100, 100, 64]):
+        loaded = load_model(folder, torch.bfloat16, "cuda:0", 16, 64, 4, enable_prefix_cache=False)
+        runner, rc = loaded.runner, loaded.cache.open(0)
+        rows, at = [], 0
+        for n in cut:
+            rows.append(runner.step([StepEntry(rc, tokens[at:at + n], list(range(n)))]).float().cpu().clone())
+            at += n
+        for t in tokens[at:]:
+            rows.append(runner.step([StepEntry(rc, [t], [0])]).float().cpu().clone())
+        got.append(torch.cat(rows))
+        helpers.assert_close_logits(got[-1], want, torch.bfloat16, f"cut {cut}")
+    if fused:
+        assert 660 in used and 321 in used and 64 in used and 37 not in used and 2 not in used, used
+    else:
+        assert not used
+    assert ops.tcgen05_status() == 0
+    scale = max(1.0, float(want.abs().max()))
+    for other in got[1:]:
+        assert float((got[0] - other).abs().max()) <= 2e-2 * scale

@@ -322,6 +322,47 @@ def test_qk_norm_rope_kv_write(dtype, Hq, Hkv, D, P, rot, norm):
     assert float(flat[mask].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("T,Hq,Hkv,K,P", [(300, 4, 2, 136, 16), (1000, 3, 1, 72, 4), (2048, 16, 8, 1024, 16), (257, 2, 2, 64, 256)])
+@pytest.mark.parametrize("norm", [True, False])
+@pytest.mark.parametrize("write_kv", [True, False])
+def test_linear_qkv_rope_fused(T, Hq, Hkv, K, P, norm, write_kv):
+    """The QKV product with per-head norm, rotation and cache write in its epilogue (head size 128), against
+    the plain product followed by the plain norm + rotation + cache write: q in place, k and v in the cache
+    only, untouched slots and (without a cache write) the whole cache unchanged; also rows and heads
+    that do not fill the 256 x 256 tiles."""
+    D, dtype = 128, torch.bfloat16
+    N = (Hq + 2 * Hkv) * D
+    x = _randn((T, K), dtype, 21)
+    w = (_randn((N, K), torch.float32, 22) / math.sqrt(K)).to(dtype)
+    positions = torch.randint(0, 40000, (T,), generator=torch.Generator().manual_seed(23), dtype=torch.int32)
+    positions[:4] = torch.tensor([0, 1, 2, 39999], dtype=torch.int32)
+    qw = (1 + 0.2 * _randn((D,), torch.float32, 24)) if norm else None
+    kw = (1 + 0.2 * _randn((D,), torch.float32, 25)) if norm else None
+    inv_freq = 1.0 / (1e6 ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+    pages = -(-T // P) + 3
+    slots = torch.randperm(pages * P, generator=torch.Generator().manual_seed(26))[:T].to(torch.int32)
+    # plain: product rounded to bfloat16, then norm + rotation + cache write
+    qkv_ref = (x.float() @ w.float().t()).to(dtype)
+    cache_ref = torch.zeros(pages, 2, Hkv, P, D, dtype=dtype)
+    ref_ops.qk_norm_rope_kv_write(qkv_ref, positions, qw, kw, 1e-6, inv_freq, D, cache_ref, slots, Hq, Hkv, D, write_kv=write_kv)
+    table = torch.empty(T, D // 2, 2, dtype=torch.float32, device=DEV)
+    ops.rope_table(positions.to(DEV), inv_freq.to(DEV), table)
+    cache_gpu = torch.zeros(pages, 2, Hkv, P, D, dtype=dtype, device=DEV)
+    qkv_gpu = torch.zeros(T, N, dtype=dtype, device=DEV)
+    ops.linear_qkv_rope(x.to(DEV), w.to(DEV), qkv_gpu, qw.to(DEV) if norm else None, kw.to(DEV) if norm else None, 1e-6,
+                        table, cache_gpu, slots.to(DEV), Hq, Hkv, write_kv=write_kv)
+    torch.cuda.synchronize()
+    assert ops.tcgen05_status() == 0
+    _close(qkv_gpu[:, :Hq * D], qkv_ref[:, :Hq * D], dtype)
+    assert float(qkv_gpu[:, Hq * D:].abs().max()) == 0.0          # k and v are not written to the product's buffer
+    _close(cache_gpu, cache_ref, dtype)
+    mask = torch.ones(pages * P, dtype=torch.bool)
+    if write_kv:
+        mask[slots.long()] = False
+    flat = cache_gpu.cpu().permute(0, 3, 1, 2, 4).reshape(pages * P, -1)
+    assert float(flat[mask].abs().max()) == 0.0
+
+
 def _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, seed, spike=None):
     """Build a paged cache with scattered pages for requests with ctx_lens[r] cached tokens and
     q_lens[r] new ones; returns everything both implementations need."""
