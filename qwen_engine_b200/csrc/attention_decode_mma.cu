@@ -49,7 +49,7 @@ __device__ __forceinline__ void dm_cp_async16_zfill(void* smem, const void* gmem
 
 template <bool CL, int DM_STAGES, int DM_WARPS>
 __global__ void __launch_bounds__(DM_WARPS * 32, DM_WARPS == 4 ? 2 : 1)
-decode_attention_mma_kernel(FaArgs A, long long prefetch_delta) {
+decode_attention_mma_kernel(FaArgs A, long long prefetch_delta, int early_issue) {
   constexpr int DM_THREADS = DM_WARPS * 32;
   constexpr int DM_WARP_BYTES = DM_WARP_BYTES_OF(DM_STAGES);
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -136,7 +136,7 @@ decode_attention_mma_kernel(FaArgs A, long long prefetch_delta) {
 #pragma unroll
   for (int s = 0; s < DM_STAGES; ++s) {
     const int gidx = warp + s * DM_WARPS;
-    early[s] = gidx < n_groups && kv_begin + (gidx + 1) * DM_GK <= ctx;
+    early[s] = early_issue && gidx < n_groups && kv_begin + (gidx + 1) * DM_GK <= ctx;
     if (early[s]) issue(gidx, s);
   }
   pdl_wait();                                       // q and the new tokens' keys and values: the previous kernels' outputs
@@ -320,6 +320,10 @@ decode_attention_mma_kernel(FaArgs A, long long prefetch_delta) {
 }
 
 static int g_dm_stages = 3;
+static int g_dm_early = 1;
+// Whether groups of earlier steps' keys are requested before the kernel waits for its predecessor (they then
+// compete for memory with the kernels that are still running, which are on the step's critical path).
+extern "C" void qe_decode_attention_mma_early(int early) { g_dm_early = early ? 1 : 0; }
 // How many groups of keys a warp keeps in flight: 2 (two CTAs of the kernel leave room on an SM for the CTAs of
 // the kernels around it) or 3.
 extern "C" void qe_decode_attention_mma_stages(int stages) { g_dm_stages = stages >= 3 ? 3 : 2; }
@@ -334,9 +338,9 @@ static int launch_decode_mma_as(const FaArgs& fa, long long prefetch_delta, int 
     configured = true;
   }
   if (CL)
-    qe_launch_cluster(decode_attention_mma_kernel<CL, STAGES, WARPS>, dim3(n_items, Hkv), dim3(WARPS * 32), smem, stream, (unsigned)cluster, fa, prefetch_delta);
+    qe_launch_cluster(decode_attention_mma_kernel<CL, STAGES, WARPS>, dim3(n_items, Hkv), dim3(WARPS * 32), smem, stream, (unsigned)cluster, fa, prefetch_delta, g_dm_early);
   else
-    qe_launch(decode_attention_mma_kernel<CL, STAGES, WARPS>, dim3(n_items, Hkv), dim3(WARPS * 32), smem, stream, fa, prefetch_delta);
+    qe_launch(decode_attention_mma_kernel<CL, STAGES, WARPS>, dim3(n_items, Hkv), dim3(WARPS * 32), smem, stream, fa, prefetch_delta, g_dm_early);
   QE_CHECK_LAUNCH("decode_attention_mma");
   return 0;
 }

@@ -48,6 +48,7 @@ DECODE_ATTENTION_MIN_CTAS = 128 # CTAs from which it is used: measured, it gains
 DECODE_ATTENTION_MMA = True         # decoded tokens (up to 16 rows per kv head, head size 128): warps with key groups and pipelines of their own, mma.sync arithmetic
 DECODE_ATTENTION_MMA_MIN_CTAS = 0   # CTAs from which that kernel is used
 DECODE_ATTENTION_MMA_STAGES = 3     # key groups a warp of that kernel keeps in flight (2 or 3; measured: 3 is 2.5 % ahead in the step)
+DECODE_ATTENTION_MMA_EARLY = True   # that kernel requests earlier steps' keys before it waits for the kernel before it
 DECODE_ATTENTION_MMA_WIDE = True    # steps with at most as many attention CTAs as SMs: CTAs of 8 warps, one per SM (and contexts split for 148 CTAs, not 296)
 DECODE_PREFETCH_KV_MB = 0           # that kernel asks L2 for the next layer's keys and values when a layer's are at most this many MB (0: never)
 TC_ROWS = 256           # rows per work item of the tcgen05 attention kernel (two halves of 128)
@@ -1020,6 +1021,7 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
             # decoded tokens: every warp streams key groups of its own through the tensor cores
             last_attention_kernel = "decode_attention_mma"
             lib().qe_decode_attention_mma_stages(int(DECODE_ATTENTION_MMA_STAGES))
+            lib().qe_decode_attention_mma_early(int(DECODE_ATTENTION_MMA_EARLY))
             ahead = None
             if (next_pages is not None and DECODE_PREFETCH_KV_MB > 0 and next_pages.shape == kv_pages.shape
                     and next_pages.dtype == kv_pages.dtype and next_pages.is_contiguous()):
