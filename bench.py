@@ -371,18 +371,29 @@ def main() -> int:
     ec = EngineConfig(dtype=dtype, device="cuda:0", block_size=page, num_blocks=pages, max_model_len=args.context + 4 * extra,
                       max_num_seqs=args.batch, max_num_batched_tokens=4096, enable_prefix_cache=False)
     eng = LLMEngine(loaded, ec)
-    sp = SamplingParams(max_new_tokens=args.warmup + args.steps + 2, ignore_eos=True)
+    # (at least 5 untimed decode steps: a step launched ahead is a shape of its own, run eagerly at first sight
+    # and captured in a CUDA graph at the second, after the one decode step that is not launched ahead)
+    e2e_warmup = max(args.warmup, 5)
+    sp = SamplingParams(max_new_tokens=e2e_warmup + args.steps + 8, ignore_eos=True)    # (the requests' ends lie outside the timed steps)
     for _ in range(args.batch):
         eng.add_request(tokens(args.context), sp)
-    while eng.stats.decode_tokens < args.batch * args.warmup:     # prompts, then W decode steps
+    while eng.stats.decode_tokens < args.batch * e2e_warmup:      # prompts, then the warm-up decode steps
         eng.step()
     torch.cuda.synchronize()
+    import gc
+    gc.collect()
+    gc.disable()                 # (a collection of the benchmark's own heap in mid-loop would stall the host for longer than a step)
     m0 = clocks.mark()
     t0 = time.perf_counter()
+    call_s = []
     for _ in range(args.steps):
+        t1 = time.perf_counter()
         eng.step()                                                  # host tokens in, sampled tokens out
+        call_s.append(time.perf_counter() - t1)
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
+    gc.enable()
+    print(f"[bench] end to end: {e2e_s / args.steps * 1e3:.3f} ms a step; calls (ms): " + " ".join(f"{c * 1e3:.2f}" for c in call_s), file=sys.stderr)
     spans.append((m0, clocks.mark()))
     e2e = {"value": round(args.batch * args.steps / e2e_s, 1), "unit": "tokens/s",
            "h2d_bytes_per_step": runner.last_h2d_bytes, "d2h_bytes_per_step": 4 * args.batch}
