@@ -45,6 +45,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--ignore-eos", action="store_true")
     ap.add_argument("--device", default="cuda:0")
     ap.add_argument("--stats", action="store_true", help="print the engine's counters at the end")
+    ap.add_argument("--profile", action="store_true",
+                    help="time every step on the device and print steps, tokens and device time by kind of step "
+                         "(prompt portions, decoded tokens, mixed) at the end")
     return ap
 
 
@@ -87,7 +90,8 @@ def main(argv=None) -> int:
     llm = LLM(model, dtype=parse_dtype(args.dtype), device=args.device, block_size=block_size,
               num_blocks=args.num_blocks, max_model_len=args.max_model_len, max_num_seqs=args.max_num_seqs,
               max_num_batched_tokens=args.max_num_batched_tokens, prefill_chunk_size=args.prefill_chunk,
-              enable_prefix_cache=not args.no_prefix_cache, run_ahead=not args.no_run_ahead, seed=args.sample_seed)
+              enable_prefix_cache=not args.no_prefix_cache, run_ahead=not args.no_run_ahead, seed=args.sample_seed,
+              profile=args.profile)
     sp = SamplingParams(max_new_tokens=args.max_new_tokens, temperature=args.temperature, top_k=args.top_k,
                         seed=args.sample_seed, ignore_eos=args.ignore_eos)
 
@@ -103,6 +107,8 @@ def main(argv=None) -> int:
     torch.cuda.synchronize()
     if args.stats:
         print(llm.stats())
+    if args.profile:
+        print(llm.stats().profile_table())
     return 0
 
 

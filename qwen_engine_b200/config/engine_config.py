@@ -42,6 +42,7 @@ class EngineConfig:
     use_cuda_graphs: bool = True
     run_ahead: bool = True                # launch the next decode step before the host has read this one's tokens
     seed: int = 0
+    profile: bool = False                 # time every step on the device (CUDA events) and keep sums per kind of step
 
     def __post_init__(self) -> None:
         self.dtype = parse_dtype(self.dtype)

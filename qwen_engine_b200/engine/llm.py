@@ -43,6 +43,19 @@ class EngineStats:
     peak_pages_used: int = 0
     pages_in_use: int = 0
     step_seconds: float = 0.0
+    # with EngineConfig.profile: steps, tokens and device time (ms, CUDA events around the step and its
+    # sampling) by kind of step: "decode" (single decoded tokens only), "prefill" (prompt portions only), "mixed"
+    profile: Optional[dict] = None
+
+    def profile_table(self) -> str:
+        if not self.profile:
+            return "no profile (EngineConfig.profile is off, or no step ran on a CUDA device)"
+        lines = [f"{'kind':8s} {'steps':>7s} {'tokens':>9s} {'device ms':>10s} {'ms/step':>8s} {'tokens/s':>10s}"]
+        for kind, p in self.profile.items():
+            ms = p["device_ms"]
+            lines.append(f"{kind:8s} {p['steps']:7d} {p['tokens']:9d} {ms:10.2f} {ms / max(1, p['steps']):8.3f} "
+                         f"{p['tokens'] / ms * 1e3 if ms > 0 else 0.0:10.0f}")
+        return "\n".join(lines)
 
 
 @dataclass
@@ -54,6 +67,7 @@ class _Flight:
     tokens: Optional[SampledTokens]     # None: the step samples nothing (prompt portions only)
     decode_tokens: int = 0
     prefill_tokens: int = 0
+    events: Optional[tuple] = None      # profile: CUDA events before and after the step's launches
 
 
 class LLMEngine:
@@ -141,13 +155,33 @@ class LLMEngine:
             else:
                 flight.prefill_tokens += sch.num_tokens
         device_tokens = before.tokens.device if (before is not None and before.tokens is not None) else None
+        timed = self.config.profile and self.runner.device.type == "cuda"
+        if timed:
+            import torch
+            flight.events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            flight.events[0].record()
         logits = self.runner.step(entries, device_tokens=device_tokens)
         if flight.wanting:
             params = [s.seq.sampling for s in flight.wanting]
             uniforms = [uniform_for(p.seed if p.seed is not None else self.config.seed, s.seq.seq_id,
                                     s.seq.output_len) for p, s in zip(params, flight.wanting)]
             flight.tokens = self.sampler.sample_async(logits, params, uniforms)
+        if timed:
+            flight.events[1].record()
         return flight
+
+    def _account(self, cur: _Flight) -> None:
+        """Profile: the device time of a step whose results the host has (or waits for here)."""
+        if cur.events is None:
+            return
+        cur.events[1].synchronize()
+        kind = "decode" if cur.prefill_tokens == 0 else ("prefill" if cur.decode_tokens == 0 else "mixed")
+        if self.stats.profile is None:
+            self.stats.profile = {}
+        p = self.stats.profile.setdefault(kind, {"steps": 0, "tokens": 0, "device_ms": 0.0})
+        p["steps"] += 1
+        p["tokens"] += cur.decode_tokens + cur.prefill_tokens
+        p["device_ms"] += float(cur.events[0].elapsed_time(cur.events[1]))
 
     def _can_run_ahead(self, cur: _Flight) -> bool:
         """Steady decoding: nothing waits, every running request gets a token from the step in
@@ -200,6 +234,7 @@ class LLMEngine:
             sampled = {s.seq.seq_id: t for s, t in zip(cur.wanting, cur.tokens.read())}
         self.stats.decode_tokens += cur.decode_tokens
         self.stats.prefill_tokens += cur.prefill_tokens
+        self._account(cur)
         ended = self.scheduler.update(cur.out, sampled, placed)
         st = self.stats
         st.steps += 1
@@ -259,7 +294,7 @@ class LLM:
     configuration (then ``seed`` draws random weights).  Keyword arguments are
     the fields of ``EngineConfig`` (dtype, block_size, num_blocks,
     max_model_len, max_num_seqs, max_num_batched_tokens, prefill_chunk_size,
-    enable_prefix_cache, seed, device)."""
+    enable_prefix_cache, seed, device, run_ahead, profile)."""
 
     def __init__(self, model: Union[str, ModelConfig], tokenizer=None, weights_seed: Optional[int] = None,
                  weights_std: float = 0.02, weights_norm_std: float = 0.1, **engine_kwargs):

@@ -174,11 +174,15 @@ def test_command_line(model_folders):
     prompt = random_tokens(helpers.vocab_of(name), 7, 5)
     proc = subprocess.run(
         [sys.executable, os.path.join(ROOT, "main.py"), "--model-name-or-path", folder, "--dtype", "float32",
-         "--prompt-ids", ",".join(map(str, prompt)), "--max-new-tokens", "5", "--block-size", "4", "--stats"],
+         "--prompt-ids", ",".join(map(str, prompt)), "--max-new-tokens", "5", "--block-size", "4", "--stats", "--profile"],
         capture_output=True, text=True, timeout=600)
     assert proc.returncode == 0, proc.stderr[-2000:]
     want = " ".join(str(t) for t in _plain_greedy(folder, prompt, 5))
     assert want in proc.stdout
+    # --profile: one prompt portion of 7 tokens, then 4 steps of one decoded token, each with its device time
+    rows = {l.split()[0]: l.split() for l in proc.stdout.splitlines() if l.split() and l.split()[0] in ("prefill", "decode", "mixed")}
+    assert rows["prefill"][1:3] == ["1", "7"] and rows["decode"][1:3] == ["4", "4"], proc.stdout[-1500:]
+    assert float(rows["prefill"][3]) > 0 and float(rows["decode"][3]) > 0
 
 
 def test_decode_program_agrees_with_separate_launches(tmp_path):

@@ -125,3 +125,21 @@ def test_bad_requests_are_refused(model_folders, cpu_ops):
         eng.add_request("some text")
     with pytest.raises(ValueError):
         eng.add_request(list(range(1, 200)))
+
+
+def test_profile_option_on_the_cpu_and_its_table(model_folders, cpu_ops):
+    """``EngineConfig.profile`` times steps with CUDA events: on the CPU there is nothing to time, the
+    engine runs as without it and says so; the table of a filled profile has a row per kind of step."""
+    from qwen_engine_b200.engine.llm import EngineStats
+    folder = model_folders["tiny-a"]
+    prompt = random_tokens(helpers.vocab_of("tiny-a"), 9, 71)
+    eng = make_engine(folder, "tiny-a", F32, device="cpu", profile=True)
+    eng.submit([prompt], max_new_tokens=4)
+    outs = eng.serving()
+    assert outs[0].output_token_ids == _plain_greedy(folder, prompt, 4)
+    assert eng.stats.profile is None and "no profile" in eng.stats.profile_table()
+    st = EngineStats(profile={"prefill": {"steps": 2, "tokens": 4096, "device_ms": 8.0},
+                              "decode": {"steps": 10, "tokens": 80, "device_ms": 10.0}})
+    lines = st.profile_table().splitlines()
+    assert lines[1].split() == ["prefill", "2", "4096", "8.00", "4.000", "512000"]
+    assert lines[2].split() == ["decode", "10", "80", "10.00", "1.000", "8000"]
