@@ -66,7 +66,11 @@ class RequestCache:
 class CacheManager:
     def __init__(self, specs: Sequence[Optional[CacheSpec]], page_size: int, num_pages: int,
                  num_state_slots: int, dtype: torch.dtype, device, enable_prefix_cache: bool = True,
-                 num_pages_of_group: Optional[dict[int, int]] = None, poison: bool = False):
+                 num_pages_of_group: Optional[dict[int, int]] = None, poison=False):
+        """``poison``: for tests, what fresh pages hold instead of zeros: True for NaN (any key or value read
+        before it was written shows in the logits), or a finite number for kernels that mask what they
+        read from a held page past a request's length (a large value shows a mask that is off by one,
+        where 0 x NaN would spoil every row)."""
         self.page_size = page_size
         self.dtype = dtype
         self.device = torch.device(device)
@@ -95,8 +99,8 @@ class CacheManager:
                 g.pool = PagePool(n, page_size, self.prefix_cache)
                 shape = (len(g.cache_slots), n, 2, g.spec.num_kv_heads, page_size, g.spec.head_dim)
                 g.tensor = torch.zeros(shape, dtype=dtype, device=self.device)
-                if poison:
-                    g.tensor.fill_(float("nan"))
+                if poison is not False and poison is not None:
+                    g.tensor.fill_(float("nan") if poison is True else float(poison))
             else:
                 assert isinstance(g.spec, FixedStateSpec)
                 shape = (len(g.cache_slots), num_state_slots) + tuple(g.spec.shape)
@@ -145,10 +149,12 @@ class CacheManager:
             if g.is_paged:
                 rc.tables[g.index] = []
                 rc.hashes[g.index] = []
+        queued = len(self._page_copies)
         try:
             if self.prefix_cache and known_tokens:
                 self._share_prefix(rc, list(known_tokens), max_shared_tokens)
         except Exception:
+            del self._page_copies[queued:]       # copies into pages that go back with the rest
             self._release_all(rc)
             raise
         self.live[req_id] = rc
@@ -158,7 +164,9 @@ class CacheManager:
         P = self.page_size
         limit = len(tokens) // P
         if max_shared_tokens is not None:
-            limit = min(limit, max(0, max_shared_tokens) // P)
+            # n pages count as n P tokens computed, or, when they are the whole of ``tokens``, as one less
+            cap = max(0, max_shared_tokens)
+            limit = limit if (limit * P == len(tokens) and len(tokens) - 1 <= cap) else min(limit, cap // P)
         matches = {g.index: g.pool.match_prefix(tokens, limit) for g in self.paged_groups}
         n_pages = min(len(pages) for pages, _ in matches.values())
         if n_pages == 0:
@@ -309,6 +317,10 @@ class CacheManager:
         self.live.pop(rc.req_id, None)
 
     def _release_all(self, rc: RequestCache) -> None:
+        if self._page_copies:
+            # copies into this request's private pages that no step has run yet go with the pages
+            own = {(g.index, p) for g in self.paged_groups for p in rc.tables.get(g.index, []) if p >= 0}
+            self._page_copies = [c for c in self._page_copies if (c[0], c[2]) not in own]
         for g in self.paged_groups:
             for p in rc.tables.get(g.index, []):
                 if p >= 0:
@@ -322,11 +334,14 @@ class CacheManager:
         copies, self._page_copies = self._page_copies, []
         return copies
 
-    def run_page_copies(self) -> None:
-        """Copy-on-write copies, all cache slots of the group at once."""
+    def page_copies_by_group(self) -> dict[int, list[int]]:
+        """The pending copy-on-write copies, taken: group -> flat list [src, dst, src, dst, ...].  The step
+        function copies the lists to the device with the rest of the step's index data and runs one
+        ``ops.copy_pages`` per group before anything of the step writes to the cache."""
+        out: dict[int, list[int]] = {}
         for gi, src, dst in self.take_page_copies():
-            t = self.groups[gi].tensor
-            t[:, dst].copy_(t[:, src])
+            out.setdefault(gi, []).extend((src, dst))
+        return out
 
     def zero_fresh_state(self, requests: Sequence[RequestCache]) -> None:
         fresh = [rc.state_slot for rc in requests if rc.fresh_state]

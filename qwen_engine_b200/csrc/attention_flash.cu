@@ -26,6 +26,7 @@ __global__ void flash_merge_kernel(const int* __restrict__ merge_items, const in
   for (int r = threadIdx.y; r < nrows; r += blockDim.y) {
     float m = -INFINITY;
     for (int s = 0; s < n; ++s) m = fmaxf(m, part_ml[2 * ((((size_t)first + s) * Hkv + hkv) * part_rows + r)]);
+    if (m == -INFINITY) m = 0.f;          // every part of the row empty: weights 0, not exp2(-inf + inf)
     float l = 0.f;
     for (int s = 0; s < n; ++s) {
       const size_t slot = (((size_t)first + s) * Hkv + hkv) * part_rows + r;
@@ -39,7 +40,7 @@ __global__ void flash_merge_kernel(const int* __restrict__ merge_items, const in
         const size_t slot = (((size_t)first + s) * Hkv + hkv) * part_rows + r;
         acc += exp2f(part_ml[2 * slot] - m) * part_acc[slot * D + d];
       }
-      dst[d] = __float2bfloat16_rn(acc / l);
+      dst[d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
     }
   }
 }
@@ -79,6 +80,10 @@ extern "C" int qe_flash_attention_status() {
   int v = 0;
   cudaMemcpyFromSymbol(&v, g_fa_status, sizeof(int));
   return v;
+}
+extern "C" void qe_flash_attention_clear_status() {
+  int v = 0;
+  cudaMemcpyToSymbol(g_fa_status, &v, sizeof(int));
 }
 
 extern "C" int qe_flash_attention_supported(int Hq, int Hkv, int D) {

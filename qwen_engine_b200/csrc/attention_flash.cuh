@@ -172,6 +172,7 @@ __device__ __forceinline__ void fa_merge_parts(const float* part_acc, const floa
     const int r = e / D, d = e - r * D;
     float m = -INFINITY;
     for (int sp = 0; sp < n; ++sp) m = fmaxf(m, __ldcg(part_ml + 2 * ((((size_t)first + sp) * Hkv + hkv) * part_rows + r)));
+    if (m == -INFINITY) m = 0.f;          // every part of the row empty: weights 0, not exp2(-inf + inf)
     float l = 0.f, acc = 0.f;
     for (int sp = 0; sp < n; ++sp) {
       const size_t slot = (((size_t)first + sp) * Hkv + hkv) * part_rows + r;
@@ -180,7 +181,7 @@ __device__ __forceinline__ void fa_merge_parts(const float* part_acc, const floa
       acc += wgt * __ldcg(part_acc + slot * D + d);
     }
     const int ti = r / G, hg = r - ti * G;
-    out_row0[(size_t)ti * ((size_t)Hq * D) + (size_t)(hkv * G + hg) * D + d] = __float2bfloat16_rn(acc / l);
+    out_row0[(size_t)ti * ((size_t)Hq * D) + (size_t)(hkv * G + hg) * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
   }
 }
 
@@ -447,7 +448,7 @@ __device__ __forceinline__ void flash_attention_cta(const FaArgs& A, int item_id
       }
       if (part < 0) {
         const int ti = r / G, hg = r - ti * G;
-        out_row0[(size_t)ti * ((size_t)Hq * D) + (size_t)(hkv * G + hg) * D + d] = __float2bfloat16_rn(acc / l);
+        out_row0[(size_t)ti * ((size_t)Hq * D) + (size_t)(hkv * G + hg) * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
       } else {
         const size_t slot = ((size_t)part * Hkv + hkv) * part_rows + r;
         part_acc[slot * D + d] = acc;

@@ -511,3 +511,45 @@ extern "C" int qe_place_tokens(int* dst, const int* rows, const int* src, const 
   QE_CHECK_LAUNCH("place_tokens");
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------
+// Copies of whole cache pages: for every pair (src, dst) the page src of every cache slot of a group is
+// copied to page dst of the same slot (a request that found its whole prompt in shared pages gets a private
+// copy of the last one before it writes there).  cache: [slots, pages, page_bytes]; pairs: int32 [n, 2] on the
+// device.  A pair that names a page outside the group is passed over.
+// ---------------------------------------------------------------------------------------
+template <typename U>
+__global__ void copy_pages_kernel(U* __restrict__ cache, long slot_units, long page_units, const int* __restrict__ pairs,
+                                  int n_pages) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int src = pairs[2 * blockIdx.z], dst = pairs[2 * blockIdx.z + 1];
+  if (src < 0 || dst < 0 || src >= n_pages || dst >= n_pages || src == dst) return;
+  U* base = cache + (long)blockIdx.y * slot_units;
+  const U* s = base + (long)src * page_units;
+  U* d = base + (long)dst * page_units;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < page_units; i += (long)gridDim.x * blockDim.x) d[i] = s[i];
+}
+
+extern "C" int qe_copy_pages(void* cache, int n_slots, int n_pages, long page_bytes, const int* pairs, int n_pairs,
+                             cudaStream_t stream) {
+  if (n_pairs <= 0 || n_slots <= 0) return 0;
+  if (page_bytes <= 0 || n_pages <= 0) QE_REFUSE("copy_pages: a group of %d pages of %ld bytes", n_pages, page_bytes);
+  if (n_slots > 65535 || n_pairs > 65535) QE_REFUSE("copy_pages: %d slots x %d pairs are too many for one launch", n_slots, n_pairs);
+  const int threads = 256;
+  if (page_bytes % 16 == 0 && ((uintptr_t)cache & 15) == 0) {
+    const long units = page_bytes / 16;
+    const unsigned blocks = (unsigned)((units + threads - 1) / threads < 64 ? (units + threads - 1) / threads : 64);
+    qe_launch(copy_pages_kernel<uint4>, dim3(blocks, n_slots, n_pairs), dim3(threads), 0, stream, (uint4*)cache,
+              (long)n_pages * units, units, pairs, n_pages);
+  } else if (page_bytes % 2 == 0 && ((uintptr_t)cache & 1) == 0) {
+    const long units = page_bytes / 2;
+    const unsigned blocks = (unsigned)((units + threads - 1) / threads < 64 ? (units + threads - 1) / threads : 64);
+    qe_launch(copy_pages_kernel<unsigned short>, dim3(blocks, n_slots, n_pairs), dim3(threads), 0, stream,
+              (unsigned short*)cache, (long)n_pages * units, units, pairs, n_pages);
+  } else {
+    QE_REFUSE("copy_pages: pages of %ld bytes", page_bytes);
+  }
+  QE_CHECK_LAUNCH("copy_pages");
+  return 0;
+}

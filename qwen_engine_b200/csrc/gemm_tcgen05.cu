@@ -38,10 +38,13 @@ struct __align__(1024) TcSmem {
   int abort_flag;
 };
 
-template <typename TOut, int BN, int STAGES>
+// STARVED (the self-test of the give-up path, qe_gemm_tc_selftest_starved): the producer issues no load and arms
+// no barrier, and the waits give up after `starved_limit` polls instead of TC_WAIT_LIMIT; everything else is
+// the product kernel as it is.
+template <typename TOut, int BN, int STAGES, bool STARVED = false>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                    TOut* __restrict__ out, int M, int N, int K) {
+                    TOut* __restrict__ out, int M, int N, int K, int starved_limit) {
   extern __shared__ unsigned char smem_raw[];
   using Smem = TcSmem<BN, STAGES>;
   constexpr uint32_t TMEM_COLS = 2 * BN;
@@ -52,6 +55,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   const int n_blocks = (N + BN - 1) / BN;
   const int n_tiles = n_blocks * ((M + TC_BM - 1) / TC_BM);
   volatile int* abort_flag = &sm.abort_flag;
+  const uint32_t wait_limit = STARVED ? (uint32_t)starved_limit : TC_WAIT_LIMIT;
 
   // Everything up to the first load of x needs nothing from the kernel before this one (the weights
   // are nobody's output): it runs before the wait for that kernel.
@@ -84,29 +88,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       int m0, n0, kb;
       // the ring's first round: the weights' tiles at once, x's after the wait for the kernel before
       for (uint32_t kc = 0; kc < ahead; ++kc) {
+        if (STARVED) break;
         coords(kc, m0, n0, kb);
         mbar_expect_tx(&sm.full[kc], (TC_BM + BN) * TC_BK * sizeof(__nv_bfloat16));
         tma_load_2d(sm.b[kc], &map_w, &sm.full[kc], kb * TC_BK, n0);
       }
       pdl_wait();
       for (uint32_t kc = 0; kc < ahead; ++kc) {
+        if (STARVED) break;
         coords(kc, m0, n0, kb);
         tma_load_2d(sm.a[kc], &map_x, &sm.full[kc], kb * TC_BK, m0);
       }
       uint32_t kc = ahead;
       for (; kc < total; ++kc) {
         const uint32_t s = kc % STAGES, round = kc / STAGES;
-        if (!mbar_wait(&sm.empty[s], (round - 1) & 1, abort_flag, 1, &g_tc_status)) break;
+        if (!mbar_wait(&sm.empty[s], (round - 1) & 1, abort_flag, 1, &g_tc_status, wait_limit)) break;
         coords(kc, m0, n0, kb);
         mbar_expect_tx(&sm.full[s], (TC_BM + BN) * TC_BK * sizeof(__nv_bfloat16));
         tma_load_2d(sm.a[s], &map_x, &sm.full[s], kb * TC_BK, m0);
         tma_load_2d(sm.b[s], &map_w, &sm.full[s], kb * TC_BK, n0);
       }
-      if (*abort_flag) {
+      if (*abort_flag && !STARVED) {
         // giving up: let the copies that are still in flight land before the CTA leaves (bounded)
         for (uint32_t i = kc > (uint32_t)STAGES ? kc - STAGES : 0; i < kc; ++i) {
           const uint32_t s = i % STAGES;
-          for (uint32_t spin = 0; spin < TC_WAIT_LIMIT; ++spin)
+          for (uint32_t spin = 0; spin < wait_limit; ++spin)
             if (mbar_try_wait(&sm.full[s], (i / STAGES) & 1)) break;
         }
       }
@@ -121,12 +127,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++it) {
         const int buf = it & 1;
         // the epilogue has read this accumulator's previous tile out of tensor memory
-        if (it >= 2 && !mbar_wait(&sm.acc_empty[buf], ((it >> 1) - 1) & 1, abort_flag, 4, &g_tc_status)) { ok = false; break; }
+        if (it >= 2 && !mbar_wait(&sm.acc_empty[buf], ((it >> 1) - 1) & 1, abort_flag, 4, &g_tc_status, wait_limit)) { ok = false; break; }
         tc_fence_after();
         const uint32_t acc = tmem + buf * BN;
         for (int kb = 0; kb < num_kb; ++kb, ++kc) {
           const uint32_t s = kc % STAGES;
-          if (!mbar_wait(&sm.full[s], (kc / STAGES) & 1, abort_flag, 2, &g_tc_status)) { ok = false; break; }
+          if (!mbar_wait(&sm.full[s], (kc / STAGES) & 1, abort_flag, 2, &g_tc_status, wait_limit)) { ok = false; break; }
           tc_fence_after();
           const uint64_t da = make_smem_desc(smem_u32(sm.a[s]));
           const uint64_t db = make_smem_desc(smem_u32(sm.b[s]));
@@ -147,7 +153,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
       const int buf = it & 1;
       const int m0 = (tile / n_blocks) * TC_BM, n0 = (tile % n_blocks) * BN;
-      const bool ok = __all_sync(0xffffffffu, mbar_wait(&sm.acc_full[buf], (it >> 1) & 1, abort_flag, 3, &g_tc_status));
+      const bool ok = __all_sync(0xffffffffu, mbar_wait(&sm.acc_full[buf], (it >> 1) & 1, abort_flag, 3, &g_tc_status, wait_limit));
       if (!ok) break;                                     // warp-uniform
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
@@ -237,10 +243,30 @@ static int launch_tc(const void* x, const void* w, void* out, int M, int N, int 
   const long tiles = (long)((N + BN - 1) / BN) * ((M + TC_BM - 1) / TC_BM);
   const dim3 grid((unsigned)(tiles < sms ? tiles : sms));
   if (out_f32)
-    qe_launch(gemm_tcgen05_kernel<float, BN, STAGES>, grid, dim3(TC_THREADS), smem, stream, map_x, map_w, (float*)out, M, N, K);
+    qe_launch(gemm_tcgen05_kernel<float, BN, STAGES>, grid, dim3(TC_THREADS), smem, stream, map_x, map_w, (float*)out, M, N, K, 0);
   else
-    qe_launch(gemm_tcgen05_kernel<__nv_bfloat16, BN, STAGES>, grid, dim3(TC_THREADS), smem, stream, map_x, map_w, (__nv_bfloat16*)out, M, N, K);
+    qe_launch(gemm_tcgen05_kernel<__nv_bfloat16, BN, STAGES>, grid, dim3(TC_THREADS), smem, stream, map_x, map_w, (__nv_bfloat16*)out, M, N, K, 0);
   QE_CHECK_LAUNCH("linear_tcgen05");
+  return 0;
+}
+
+// The give-up path on purpose, for a test: one CTA of the product kernel whose producer loads nothing, so that no
+// barrier ever flips, with waits of `limit` polls (some thousands: milliseconds).  The CTA must leave without a
+// store, free its tensor memory and record which wait ran out first (qe_gemm_tc_status: 1, 2 or 3).  Nothing
+// traps, faults or hangs; a product launched afterwards finds the SM as any other kernel leaves it.
+extern "C" int qe_gemm_tc_selftest_starved(const void* x, const void* w, void* out, int M, int N, int K, int limit,
+                                           cudaStream_t stream) {
+  if (M <= 0 || M > TC_BM || N <= 0 || N > 128 || K <= 0 || K % 8) QE_REFUSE("selftest: one tile of at most 128 x 128, K a multiple of 8");
+  if (limit < 1 || limit > (1 << 20)) QE_REFUSE("selftest: a limit of 1 .. 2^20 polls");
+  if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) QE_REFUSE("selftest: operands must be 16-byte aligned");
+  CUtensorMap map_x, map_w;
+  if (!get_map(x, M, K, TC_BM, &map_x) || !get_map(w, N, K, 128, &map_w)) return 1;
+  const size_t smem = sizeof(TcSmem<128, 6>) + 1024;
+  cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<__nv_bfloat16, 128, 6, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) QE_REFUSE("selftest: shared memory %zu: %s", smem, cudaGetErrorString(e));
+  qe_launch(gemm_tcgen05_kernel<__nv_bfloat16, 128, 6, true>, dim3(1), dim3(TC_THREADS), smem, stream, map_x, map_w,
+            (__nv_bfloat16*)out, M, N, K, limit);
+  QE_CHECK_LAUNCH("selftest");
   return 0;
 }
 

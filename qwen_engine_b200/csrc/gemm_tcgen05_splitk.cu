@@ -233,6 +233,10 @@ extern "C" int qe_gemm_tc_splitk_status() {
   cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int));
   return v;
 }
+extern "C" void qe_gemm_tc_splitk_clear_status() {
+  int v = 0;
+  cudaMemcpyToSymbol(g_tc_status, &v, sizeof(int));
+}
 
 // 1 <= M <= 64; splits: 2, 4 or 8 CTAs per 128 weight rows (each gets ceil(K / 64 / splits) blocks of
 // K; shares beyond K's end add nothing).  mode 0: out bfloat16; 1: out float32; 2: out float32 += the

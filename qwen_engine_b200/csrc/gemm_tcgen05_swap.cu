@@ -175,6 +175,10 @@ extern "C" int qe_gemm_tc_swap_status() {
   cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int));
   return v;
 }
+extern "C" void qe_gemm_tc_swap_clear_status() {
+  int v = 0;
+  cudaMemcpyToSymbol(g_tc_status, &v, sizeof(int));
+}
 
 // 1 <= M <= 256.  Returns 0 when run, 1 when refused (qe_last_error says why), 2 on a launch error.
 extern "C" int qe_linear_tcgen05_swap(const void* x, const void* w, void* out, int M, int N, int K, int out_f32,

@@ -36,7 +36,10 @@ extern "C" {
 #endif
 
 // Arguments as qe_flash_attention, without part_acc and part_ml; n_parts is the number of parts the
-// work items name (0 if no context is split) and part_rows the rows each part holds.
+// work items name (0 if no context is split) and part_rows the rows each part holds.  The work items
+// live in device memory, where this call cannot look: every part index in them must be below n_parts
+// and no item may bring more rows than part_rows, or a part is written past the space sized from
+// these two numbers (the same holds for the pointers given to qe_flash_attention).
 // Returns 0 on success, 1 if refused (sizes, alignment, scratch too small), 2 on a CUDA error.
 int qe_flash_attention_noalloc(const void* q, long q_stride, const void* pages, const int* block_tables,
                                int max_blocks, const int* cu_q, const int* ctx_lens, const int* items,

@@ -31,8 +31,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait: false if the barrier did not flip within the limit or the CTA is aborting.  A wait
 // that runs out raises the CTA's abort flag and records `code` in `*status` (if nothing is there yet).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code, int* status) {
-  for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code, int* status,
+                                          uint32_t limit = TC_WAIT_LIMIT) {
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 63) == 63 && *abort_flag) return false;
   }

@@ -98,6 +98,7 @@ class LLMEngine:
             eos_token_id=getattr(loaded.config, "eos_token_id", None))
         self._next_seq_id = 0
         self._flight: Optional[_Flight] = None
+        self._checks_device = loaded.runner.device.type == "cuda"
         self.stats = EngineStats()
 
     # ---- intake -------------------------------------------------------------------------
@@ -249,6 +250,15 @@ class LLMEngine:
     def has_work(self) -> bool:
         return self._flight is not None or self.scheduler.has_work()
 
+    def check_device(self) -> None:
+        """Every wait inside the kernels is bounded; one that runs out makes its kernel return without its
+        output and leaves a code in a status word.  This reads the words (it synchronises the device, so it
+        is called where the engine has nothing in flight: at the end of ``serving``, and by callers of
+        ``step`` when they see fit) and raises ``ops.DeviceWaitTimeout`` if any is set."""
+        if self._checks_device:
+            from .. import ops
+            ops.check_device_status()
+
     def _output_of(self, seq: Sequence) -> RequestOutput:
         text = None
         if self.tokenizer is not None:
@@ -264,6 +274,7 @@ class LLMEngine:
         done: list[Sequence] = []
         while self.has_work():
             done.extend(self.step())
+        self.check_device()
         done.sort(key=lambda s: s.seq_id)
         outs = [self._output_of(s) for s in done]
         if print_func is not None:

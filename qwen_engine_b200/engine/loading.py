@@ -34,7 +34,7 @@ def require_cuda(device) -> torch.device:
 def load_model(model_dir: Optional[str], dtype: torch.dtype, device, page_size: int, num_pages: int,
                num_state_slots: int, enable_prefix_cache: bool = True, config: Optional[ModelConfig] = None,
                random_seed: Optional[int] = None, random_std: float = 0.02, random_norm_std: float = 0.1,
-               poison_cache: bool = False, check_device: bool = True,
+               poison_cache=False, check_device: bool = True,
                use_cuda_graphs: bool = True) -> LoadedModel:
     """Read ``config.json``, pick the model class by its ``architectures`` entry, load
     ``model.safetensors`` by tensor name (or draw seeded random weights when ``model_dir``

@@ -290,11 +290,16 @@ class ModelRunner:
         if fix_rows:        # last, so that the places of everything a captured step reads stay where they are
             pack.add("fix_rows", fix_rows)
             pack.add("fix_src", fix_src)
+        page_copies = cache.page_copies_by_group()
+        for gi, pairs in page_copies.items():
+            pack.add(f"pc{gi}", pairs)
         dev = self._upload(pack)
         if fix_rows:
             ops.place_tokens(dev["token_ids"], dev["fix_rows"], device_tokens, dev["fix_src"])
 
-        cache.run_page_copies()
+        # private copies of shared pages that this step (or a later one) writes into: before any write
+        for gi in page_copies:
+            ops.copy_pages(cache.groups[gi].tensor, dev[f"pc{gi}"])
         cache.zero_fresh_state([e.cache for e in entries])
 
         groups = {g.index: GroupStepView(dev[f"bt{g.index}"].view(R, max_blocks[g.index]),

@@ -538,10 +538,11 @@ def linear_pairs(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 
 
 def swiglu_fused_applies(M: int, I: int, K: int, dtype: torch.dtype) -> bool:
-    """Whether ``linear_swiglu`` serves this shape: bfloat16 and enough 256-row x 128-column tiles of
-    the activation for every pair of SMs (the kernel is the CTA-pair product)."""
+    """Whether ``linear_swiglu`` serves this shape: bfloat16, more rows than the weight-streaming products
+    take, and enough 256-row x 128-column tiles of the activation for every pair of SMs (the kernel is the
+    CTA-pair product)."""
     return (TCGEN05_PAIRS and TCGEN05_ENABLED and SWIGLU_FUSED and dtype == torch.bfloat16 and K % 8 == 0
-            and -(-M // 256) * -(-I // 128) >= PAIR_MIN_TILES)
+            and M > SMALL_M_MAX and -(-M // 256) * -(-I // 128) >= PAIR_MIN_TILES)
 
 
 def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
@@ -566,7 +567,7 @@ def qkv_rope_fused_applies(M: int, N: int, K: int, dtype: torch.dtype, head_dim:
     enough 256 x 256 tiles for every pair of SMs (the kernel is the CTA-pair product)."""
     return (QKV_ROPE_FUSED and TCGEN05_PAIRS and TCGEN05_ENABLED and _program is None and dtype == torch.bfloat16
             and head_dim == 128 and rotary_dim == 128 and K % 8 == 0 and N % 128 == 0
-            and -(-M // 256) * -(-N // 256) >= QKV_ROPE_MIN_TILES)
+            and M > SMALL_M_MAX and -(-M // 256) * -(-N // 256) >= QKV_ROPE_MIN_TILES)
 
 
 def linear_qkv_rope(x: torch.Tensor, w_qkv: torch.Tensor, qkv: torch.Tensor, q_norm_w: Optional[torch.Tensor],
@@ -687,6 +688,62 @@ def tcgen05_status() -> int:
     kernel for some tens of rows, 21-23 in its form that shares K within a cluster).  Synchronises the device."""
     return (int(lib().qe_gemm_tc_status()) or int(lib().qe_gemm_tc_swap_status()) or int(lib().qe_gemm_tc_pair_status())
             or int(lib().qe_gemm_tc_splitk_status()))
+
+
+class DeviceWaitTimeout(RuntimeError):
+    """A bounded wait inside a kernel ran out: the kernel gave up without storing its output, so what
+    the step produced is not to be trusted."""
+
+
+_STATUS_WORDS = ("qe_gemm_tc", "qe_gemm_tc_swap", "qe_gemm_tc_pair", "qe_gemm_tc_splitk", "qe_flash_attention_tc",
+                 "qe_flash_attention")
+
+
+def device_status() -> dict[str, int]:
+    """The status words of the kernels whose waits are bounded that are not zero: kernel family -> code
+    of its first wait that ran out.  Synchronises the device (one small copy per word)."""
+    if _lib is None:
+        return {}                   # nothing was ever launched
+    out = {}
+    for name in _STATUS_WORDS:
+        code = int(getattr(lib(), name + "_status")())
+        if code:
+            out[name[3:]] = code
+    return out
+
+
+def clear_device_status() -> None:
+    """Set the status words back to zero, and the counters by which split contexts find their last part
+    (a kernel that gave up may have left them counted up)."""
+    if _lib is None:
+        return
+    for name in _STATUS_WORDS:
+        getattr(lib(), name + "_clear_status")()
+    for t in _merge_counter_tensors.values():
+        t.zero_()
+
+
+def check_device_status() -> None:
+    """Raise ``DeviceWaitTimeout`` if any bounded wait ran out since the words were last cleared (and clear
+    them).  The engine calls this where it synchronises anyway: at the end of ``serving``."""
+    bad = device_status()
+    if bad:
+        clear_device_status()
+        raise DeviceWaitTimeout(
+            "a bounded wait inside a kernel ran out and the kernel returned without its output: "
+            + ", ".join(f"{k} (code {v})" for k, v in bad.items())
+            + "; the tokens of the steps since the last check are not to be trusted")
+
+
+def selftest_starved_product(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, limit: int = 10000) -> None:
+    """For tests: one CTA of the tcgen05 product kernel whose loads are withheld, with waits of ``limit``
+    polls.  It must give up, store nothing into ``out``, free its tensor memory and leave a code in
+    ``tcgen05_status()``; the device stays usable."""
+    M, K = x.shape
+    N = w.shape[0]
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and out.shape == (M, N)
+          and x.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "selftest: contiguous bfloat16 operands")
+    _check(lib().qe_gemm_tc_selftest_starved(_ptr(x), _ptr(w), _ptr(out), M, N, K, int(limit), _stream()), "selftest")
 
 
 ROPE_TABLE_MIN_T = 64   # tokens from which a step's rotation angles are computed once (below: in the kernel)
@@ -1067,6 +1124,18 @@ def place_tokens(token_ids: torch.Tensor, rows: torch.Tensor, src: torch.Tensor,
     _need(rows.numel() == src_index.numel(), "place_tokens: one source index per row")
     _check(lib().qe_place_tokens(_ptr(token_ids), _ptr(rows), _ptr(src), _ptr(src_index), rows.numel(), _stream()),
            "place_tokens")
+
+
+def copy_pages(cache: torch.Tensor, pairs: torch.Tensor) -> None:
+    """cache[s, pairs[2 i + 1]] = cache[s, pairs[2 i]] for every cache slot s of a group's tensor
+    [slots, pages, ...] and every pair of the int32 list on the device: whole pages, one launch."""
+    _i32(pairs, "pairs")
+    _need(cache.dim() >= 3 and cache.is_contiguous(), "copy_pages: cache must be contiguous [slots, pages, ...]")
+    _need(pairs.numel() % 2 == 0, "copy_pages: pairs of (source page, destination page)")
+    n_slots, n_pages = int(cache.shape[0]), int(cache.shape[1])
+    page_bytes = cache[0, 0].numel() * cache.element_size()
+    _check(lib().qe_copy_pages(_ptr(cache), n_slots, n_pages, ctypes.c_long(page_bytes), _ptr(pairs), pairs.numel() // 2,
+                               _stream()), "copy_pages")
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:

@@ -10,7 +10,8 @@ from qwen_engine_b200.registry import config_from_dict
 from qwen_engine_b200.weights import write_model_folder
 
 # Tiny configurations that differ in every size and option.  tiny-a and tiny-b are the two of
-# the benchmark description; tiny-c has a head size that is no power of two and three groups.
+# the benchmark description; tiny-c has a head size that is no power of two and three groups; tiny-d
+# has the head size of the real models (128), which the kernels that the benchmark times are made for.
 TINY = {
     "tiny-a": dict(cfg=dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=64,
                             num_attention_heads=4, num_key_value_heads=2, head_dim=16,
@@ -27,6 +28,11 @@ TINY = {
                             intermediate_size=152, vocab_size=301, rope_theta=50000.0, rms_norm_eps=3e-6,
                             tie_word_embeddings=True, max_position_embeddings=1024),
                    seed=7, std=0.08, norm_std=0.3, page=16),
+    "tiny-d": dict(cfg=dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=256,
+                            num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+                            intermediate_size=640, vocab_size=997, rope_theta=1000000.0, rms_norm_eps=1e-6,
+                            tie_word_embeddings=True, max_position_embeddings=2048),
+                   seed=11, std=0.05, norm_std=0.1, page=16),
 }
 
 
@@ -121,9 +127,10 @@ def check_requests(got, folder, requests, dtype, what):
 
 
 
-def mixed_steps(reqs, seed):
-    """Up to four live requests; each step gives some a portion, some a single token, and leaves
-    some out; a finished request ends and a new one takes its place (and its pages)."""
+def mixed_steps(reqs, seed, sizes=(2, 3, 5, 8, 13, 21)):
+    """Up to four live requests; each step gives some a portion (of one of ``sizes`` tokens), some a
+    single token, and leaves some out; a finished request ends and a new one takes its place (and
+    its pages)."""
     import random
     rng = random.Random(seed)
     order = list(reqs)
@@ -140,7 +147,7 @@ def mixed_steps(reqs, seed):
             if rng.random() < 0.2 and len(live) > 1:
                 continue                                   # left out of this step
             mode = rng.random()
-            n = 1 if (mode < 0.4 and pos[rid] > 0) else min(left, rng.choice([2, 3, 5, 8, 13, 21]))
+            n = 1 if (mode < 0.4 and pos[rid] > 0) else min(left, rng.choice(list(sizes)))
             n = min(n, left)
             want = sorted(rng.sample(range(n), k=min(n, rng.choice([1, 2, n]))))
             entries.append({"id": rid, "tokens": reqs[rid][pos[rid]:pos[rid] + n], "want": want})
@@ -156,6 +163,48 @@ def mixed_steps(reqs, seed):
 
 
 
+def live_tokens_needed(steps, unit=64) -> int:
+    """The most tokens that the live requests of a trace hold at any time, each request's count
+    rounded up to ``unit``: the smallest ``max_tokens`` the trace can be replayed with."""
+    held, most = {}, 0
+    for st in steps:
+        for e in st["entries"]:
+            held[e["id"]] = held.get(e["id"], 0) + len(e["tokens"])
+        most = max(most, sum(-(-n // unit) * unit for n in held.values()))
+        for rid in st.get("end", []):
+            held.pop(rid, None)
+    return most
+
+
+class LaunchSpy:
+    """Counts the calls into the compiled library by entry point while it is active, so that a test
+    can say which kernels served it (``with LaunchSpy() as spy: ...; spy.count("qe_...")``)."""
+
+    class _Proxy:
+        def __init__(self, real, counts):
+            object.__setattr__(self, "_real", real)
+            object.__setattr__(self, "_counts", counts)
+
+        def __getattr__(self, name):
+            if name.startswith("qe_"):
+                self._counts[name] = self._counts.get(name, 0) + 1
+            return getattr(self._real, name)
+
+    def __enter__(self):
+        from qwen_engine_b200 import ops
+        self.counts: dict = {}
+        self._ops, self._real = ops, ops.lib()
+        ops._lib = LaunchSpy._Proxy(self._real, self.counts)
+        return self
+
+    def __exit__(self, *exc):
+        self._ops._lib = self._real
+        return False
+
+    def count(self, name: str) -> int:
+        return self.counts.get(name, 0)
+
+
 # ---- generation helpers ------------------------------------------------------------------------
 def make_engine(folder, name, dtype, device="cuda:0", **engine_kwargs):
     """An LLMEngine over a model folder; on the CPU the caller has put the plain operations in
@@ -166,9 +215,10 @@ def make_engine(folder, name, dtype, device="cuda:0", **engine_kwargs):
     kw = dict(dtype=dtype, device=device, block_size=TINY[name]["page"], max_model_len=128, max_num_seqs=4,
               max_num_batched_tokens=64)
     kw.update(engine_kwargs)
+    poison = kw.pop("poison_cache", False)
     ec = EngineConfig(**kw)
     loaded = load_model(folder, ec.dtype, ec.device, ec.block_size, ec.resolved_num_blocks(), ec.max_num_seqs,
-                        ec.enable_prefix_cache, check_device=(device != "cpu"))
+                        ec.enable_prefix_cache, poison_cache=poison, check_device=(device != "cpu"))
     return LLMEngine(loaded, ec)
 
 

@@ -200,7 +200,14 @@ def sample(logits, temperature, top_k, uniform, out):
         out[n] = sample_row(logits[n].cpu(), float(temperature[n]), int(top_k[n]), float(uniform[n]))
 
 
-_NAMES = ["prepare_matrix", "embedding", "add_rmsnorm", "add_rmsnorm_rows", "linear",
+def copy_pages(cache, pairs):
+    """cache [slots, pages, ...]: page pairs[2 i] of every slot is copied to page pairs[2 i + 1]."""
+    flat = pairs.tolist()
+    for src, dst in zip(flat[0::2], flat[1::2]):
+        cache[:, dst] = cache[:, src].clone()
+
+
+_NAMES = ["copy_pages", "prepare_matrix", "embedding", "add_rmsnorm", "add_rmsnorm_rows", "linear",
           "qk_norm_rope_kv_write", "rope_neox", "rope_table", "place_tokens", "swiglu_fused_applies", "attention_fuses_rotary", "plan_attention", "paged_attention", "silu_mul", "linear_silu_mul",
           "argmax", "sample"]
 

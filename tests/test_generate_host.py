@@ -143,3 +143,20 @@ def test_profile_option_on_the_cpu_and_its_table(model_folders, cpu_ops):
     lines = st.profile_table().splitlines()
     assert lines[1].split() == ["prefill", "2", "4096", "8.00", "4.000", "512000"]
     assert lines[2].split() == ["decode", "10", "80", "10.00", "1.000", "8000"]
+
+
+def test_a_wait_that_ran_out_on_the_device_surfaces_as_an_error(model_folders, cpu_ops, monkeypatch):
+    """Kernels give up a bounded wait by returning without their output and leaving a code in a status
+    word; the engine reads the words when ``serving`` is through and raises, instead of handing out the
+    tokens of such a step as if they were right."""
+    from qwen_engine_b200 import ops
+    eng = make_engine(model_folders["tiny-a"], "tiny-a", F32, device="cpu")
+    eng._checks_device = True                         # as on a CUDA device
+    cleared = []
+    monkeypatch.setattr(ops, "device_status", lambda: {} if cleared else {"gemm_tc": 2})
+    monkeypatch.setattr(ops, "clear_device_status", lambda: cleared.append(True))
+    eng.submit([[1, 2, 3]], max_new_tokens=2)
+    with pytest.raises(ops.DeviceWaitTimeout, match="gemm_tc .code 2."):
+        eng.serving()
+    assert cleared
+    eng.check_device()                                  # cleared: the next check passes

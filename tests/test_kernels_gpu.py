@@ -799,3 +799,38 @@ def test_sample(V):
     assert got.cpu().tolist() == want.tolist()
     # top_k = 1 is argmax whatever the temperature
     assert got[3].item() == int(torch.argmax(logits[3]))
+
+
+def test_a_bounded_wait_that_runs_out():
+    """Every wait on an mbarrier inside the tcgen05 kernels is bounded.  Here one is made to run out on
+    purpose, without any fault: one CTA of the product kernel whose loads are withheld (no barrier is ever
+    armed) and whose waits give up after 10 000 polls.  The kernel must return, store nothing (the output
+    keeps its fill value), leave the code of the wait that gave up in the status word, and free its tensor
+    memory: the same product launched normally right afterwards is served and is right."""
+    g = torch.Generator().manual_seed(5)
+    M, N, K = 100, 128, 512                      # 8 k-blocks for a ring of 6 slots: the producer waits for a slot as well
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(N, K, generator=g).to(torch.bfloat16).to(DEV)
+    out = torch.full((M, N), 7.0, dtype=torch.bfloat16, device=DEV)
+    ops.clear_device_status()
+    assert ops.device_status() == {}
+    ops.selftest_starved_product(x, w, out, limit=10000)
+    torch.cuda.synchronize()
+    assert ops.tcgen05_status() in (1, 2, 3)
+    assert set(ops.device_status()) == {"gemm_tc"}
+    assert bool((out == 7.0).all()), "a kernel that gave up stored something"
+    with pytest.raises(ops.DeviceWaitTimeout, match="gemm_tc"):
+        ops.check_device_status()
+    assert ops.device_status() == {}             # cleared by the check
+    for _ in range(3):                           # tensor memory was freed: the same SMs take full-size products again
+        big_x = torch.randn(300, K, generator=g).to(torch.bfloat16).to(DEV)
+        got = torch.empty(300, N, dtype=torch.bfloat16, device=DEV)
+        lib = ops.lib()
+        import ctypes
+        rc = lib.qe_linear_tcgen05(ctypes.c_void_p(big_x.data_ptr()), ctypes.c_void_p(w.data_ptr()), ctypes.c_void_p(got.data_ptr()),
+                                   300, N, K, 0, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        assert rc == 0
+        torch.cuda.synchronize()
+        want = big_x.float() @ w.float().t()
+        assert float((got.float() - want).abs().max()) <= 2e-2 * float(want.abs().max())
+    assert ops.tcgen05_status() == 0

@@ -548,25 +548,78 @@ def test_windowed_layer_gives_pages_back_and_still_agrees(dtype):
         del ARCHITECTURES["WindowToyForCausalLM"]
 
 
-# ---- the real layer sizes of the benchmark model, few layers, against the plain implementation -----------------
+# ---- the real layer sizes of the benchmark models, few layers, against the plain implementation -----------------
+REAL_SIZES = {
+    "qwen3-0.6b": dict(hidden_size=1024, num_attention_heads=16, num_key_value_heads=8, intermediate_size=3072),
+    "qwen3-1.7b": dict(hidden_size=2048, num_attention_heads=16, num_key_value_heads=8, intermediate_size=6144),
+    # groups of 4 query heads; an intermediate size above what the product that forms SiLU-mul itself takes
+    "qwen3-4b": dict(hidden_size=2560, num_attention_heads=32, num_key_value_heads=8, intermediate_size=9728),
+}
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_real_layer_sizes_of_qwen3_0_6b(dtype, tmp_path):
-    """Two layers with the widths of Qwen3-0.6B (hidden 1024, 16/8 heads of 128, intermediate 3072) and a
-    cut vocabulary: the tensor-core kernels at the sizes they are tuned for, inside the model, through
-    a whole prompt, portions and decoded tokens."""
+@pytest.mark.parametrize("sizes", list(REAL_SIZES))
+def test_real_layer_sizes(dtype, sizes, tmp_path):
+    """Two layers with the widths of Qwen3-0.6B, 1.7B and 4B (head size 128) and a cut vocabulary: the
+    kernels at the sizes they are tuned for, inside the model, through a whole prompt, portions, decoded
+    tokens, and steps that mix portions of two requests with decoded tokens of two others."""
     import helpers
     from qwen_engine_b200.weights import write_model_folder
-    raw = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, hidden_size=1024, num_attention_heads=16,
-               num_key_value_heads=8, head_dim=128, intermediate_size=3072, vocab_size=2048, rope_theta=1e6,
-               rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=4096)
+    raw = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, head_dim=128, vocab_size=2048, rope_theta=1e6,
+               rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=4096, **REAL_SIZES[sizes])
     folder = write_model_folder(config_from_dict(raw), str(tmp_path / "m"), seed=2, std=0.02, norm_std=0.1)
     from qwen_engine_b200.engine.loading import load_model
     from qwen_engine_b200.engine.trace import TraceReplayer
-    loaded = load_model(folder, dtype, DEV, 16, 64, 4)
+    loaded = load_model(folder, dtype, DEV, 16, 64, 4, poison_cache=(3.0e4 if dtype == torch.bfloat16 else True))
     rep = TraceReplayer(folder, dtype, 1024, page_size=16, loaded=loaded)
-    toks = helpers.random_tokens(2048, 200, 31)
-    steps = [{"entries": [{"id": "a", "tokens": toks[:130], "want": [0, 64, 129]}]},
-             {"entries": [{"id": "a", "tokens": toks[130:170], "want": list(range(40))}]}]
-    steps += [{"entries": [{"id": "a", "tokens": [t], "want": [0]}]} for t in toks[170:]]
+    reqs = {"a": helpers.random_tokens(2048, 200, 31), "b": helpers.random_tokens(2048, 150, 32),
+            "c": helpers.random_tokens(2048, 60, 33), "d": helpers.random_tokens(2048, 45, 34)}
+    a, b, c, d = (reqs[k] for k in "abcd")
+    steps = [{"entries": [{"id": "a", "tokens": a[:130], "want": [0, 64, 129]}]},
+             {"entries": [{"id": "a", "tokens": a[130:170], "want": list(range(40))}]}]
+    steps += [{"entries": [{"id": "a", "tokens": [t], "want": [0]}]} for t in a[170:180]]
+    # mixed: a and c decode, b and d bring portions (b's long enough for the attention kernel of prompt portions)
+    steps += [{"entries": [{"id": "c", "tokens": c[:50], "want": [49]}]},
+              {"entries": [{"id": "a", "tokens": a[180:181], "want": [0]}, {"id": "b", "tokens": b[:100], "want": [0, 99]},
+                           {"id": "c", "tokens": c[50:51], "want": [0]}, {"id": "d", "tokens": d[:21], "want": [20]}]},
+              {"entries": [{"id": "a", "tokens": a[181:182], "want": [0]}, {"id": "b", "tokens": b[100:], "want": [0, 49]},
+                           {"id": "c", "tokens": c[51:52], "want": [0]}, {"id": "d", "tokens": d[21:], "want": [0, 23]}]}]
+    # all four decode (some tens of rows would need more requests; four rows here), then the rest of a and c
+    steps += [{"entries": [{"id": "a", "tokens": [a[182 + i]], "want": [0]}, {"id": "c", "tokens": [c[52 + i]], "want": [0]}]}
+              for i in range(8)]
+    steps += [{"entries": [{"id": "a", "tokens": a[190:], "want": [9]}]}]
     got = helpers.run_steps(rep, steps)
-    helpers.check_requests(got, folder, {"a": toks}, dtype, "real layer sizes")
+    helpers.check_requests(got, folder, reqs, dtype, f"real layer sizes {sizes}")
+    if dtype == torch.bfloat16:
+        assert ops.tcgen05_status() == 0 and ops.tc_attention_status() == 0
+
+
+@pytest.mark.parametrize("sizes", ["qwen3-1.7b", "qwen3-4b"])
+def test_real_layer_sizes_some_tens_of_rows(sizes, tmp_path):
+    """Decode steps of 24 and 40 requests at the widths of Qwen3-1.7B and 4B in bfloat16: the products for some
+    tens of rows (weights on the wide side of the tensor-core instruction, K shared within a cluster where weight
+    rows are few) and the attention kernel for decoded tokens with groups of 2 and 4 query heads."""
+    import helpers
+    from qwen_engine_b200.weights import write_model_folder
+    raw = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=2, head_dim=128, vocab_size=2048, rope_theta=1e6,
+               rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=4096, **REAL_SIZES[sizes])
+    folder = write_model_folder(config_from_dict(raw), str(tmp_path / "m"), seed=3, std=0.02, norm_std=0.1)
+    from qwen_engine_b200.engine.loading import load_model
+    from qwen_engine_b200.engine.trace import TraceReplayer
+    n_req = 40
+    loaded = load_model(folder, torch.bfloat16, DEV, 16, n_req * 4, n_req, poison_cache=3.0e4)
+    rep = TraceReplayer(folder, torch.bfloat16, n_req * 64, page_size=16, loaded=loaded)
+    reqs = {f"r{i}": helpers.random_tokens(2048, 20 + (7 * i) % 30, 50 + i) for i in range(n_req)}
+    items = list(reqs.items())
+    steps = [{"entries": [{"id": rid, "tokens": t[:-2], "want": []} for rid, t in items[k:k + 8]]} for k in range(0, n_req, 8)]
+    steps.append({"entries": [{"id": rid, "tokens": [t[-2]], "want": [0]} for rid, t in items[:24]]})              # 24 rows
+    steps.append({"entries": [{"id": rid, "tokens": [t[-1] if i < 24 else t[-2]], "want": [0]}
+                              for i, (rid, t) in enumerate(items)]})                                              # 40 rows
+    steps.append({"entries": [{"id": rid, "tokens": [t[-1]], "want": [0]} for rid, t in items[24:]]})              # 16 rows
+    with helpers.LaunchSpy() as spy:
+        got = helpers.run_steps(rep, steps)
+    assert spy.count("qe_linear_tcgen05_swap") > 0 and spy.count("qe_linear_tcgen05_splitk") > 0, sorted(spy.counts)
+    assert spy.count("qe_decode_attention_mma") > 0
+    assert all(sorted(got[rid]) == [len(t) - 2, len(t) - 1] for rid, t in items)
+    helpers.check_requests(got, folder, reqs, torch.bfloat16, f"some tens of rows {sizes}")
+    assert ops.tcgen05_status() == 0

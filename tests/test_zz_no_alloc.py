@@ -6,16 +6,20 @@ timing.  For them the library keeps the scratch memory of flash decoding (the pa
 contexts) in a fixed 8 MiB array of its own.  This test calls that entry point through its exported
 C symbol, twice in a row with different inputs (the array keeps the first call's contents, which
 must not leak into the second), and compares with the ordinary entry point, whose scratch comes
-from the caller; it also checks that a request beyond the fixed size is refused, not truncated.
+from the caller, and with the plain PyTorch attention of tests/ref_ops.py (so that both entry points
+being wrong alike would show); it also checks that a request beyond the fixed size is refused, not
+truncated.
 
 The file name sorts last, so a run that stops at the first failure has run every other test before.
 """
 import ctypes
 import math
+from types import SimpleNamespace
 
 import pytest
 import torch
 
+import ref_ops
 from qwen_engine_b200 import ops
 
 pytestmark = pytest.mark.gpu
@@ -98,6 +102,13 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
         err = float((got.float() - want.float()).abs().max())
         assert err <= 1.6e-2 * scale, f"call {i}: max |diff| {err}"
         assert torch.equal(got, want), "same kernels, same order of sums: the bits agree"
+        # and against the plain attention (float32 on the CPU, from the same bfloat16 inputs)
+        plain = torch.zeros(got.shape, dtype=torch.float32)
+        ref_ops.paged_attention(case["qkv"].cpu(), case["cache"].cpu(), case["table"].cpu(),
+                                SimpleNamespace(cu_q=case["cu_q"].cpu(), ctx_lens=case["ctx"].cpu()), plain,
+                                1.0 / math.sqrt(D), 0, Hq, Hkv, D)
+        err = float((got.float().cpu() - plain).abs().max())
+        assert err <= 1.6e-2 * max(1.0, float(plain.abs().max())), f"call {i}: max |diff| to the plain attention {err}"
 
 
 def test_no_alloc_entry_point_refuses_what_does_not_fit():
