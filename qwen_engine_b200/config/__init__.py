@@ -1,5 +1,5 @@
-from .model_config import (ConfigError, ModelConfig, Qwen3Config, read_config_json,
-                           write_config_json)
+from .model_config import ConfigError, ModelConfig, read_config_json, write_config_json
+from .qwen3_config import Qwen3Config
 from .engine_config import EngineConfig, parse_dtype
 from .presets import PRESETS, preset_config_dict, preset_init
 

@@ -92,10 +92,15 @@ class LLMEngine:
         self.cache = loaded.cache
         self.runner = loaded.runner
         self.sampler = Sampler(loaded.runner.device)
+        limit = loaded.runner.max_positions
+        if limit is not None and engine_config.max_model_len > limit:
+            # found here, not in the middle of serving, where the step function would refuse the position
+            raise ValueError(f"max_model_len = {engine_config.max_model_len} is beyond the model's "
+                             f"max_position_embeddings = {limit}")
+        eos = getattr(loaded.config, "eos_token_ids", None) or getattr(loaded.config, "eos_token_id", None)
         self.scheduler = Scheduler(
             self.cache, engine_config.max_num_seqs, engine_config.max_num_batched_tokens,
-            engine_config.prefill_chunk_size, engine_config.max_model_len,
-            eos_token_id=getattr(loaded.config, "eos_token_id", None))
+            engine_config.prefill_chunk_size, engine_config.max_model_len, eos_token_id=eos)
         self._next_seq_id = 0
         self._flight: Optional[_Flight] = None
         self._checks_device = loaded.runner.device.type == "cuda"

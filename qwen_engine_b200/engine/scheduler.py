@@ -50,13 +50,15 @@ class SchedulerOutput:
 
 class Scheduler:
     def __init__(self, cache: CacheManager, max_num_seqs: int, max_num_batched_tokens: int,
-                 prefill_chunk_size: Optional[int], max_model_len: int, eos_token_id: Optional[int] = None):
+                 prefill_chunk_size: Optional[int], max_model_len: int, eos_token_id=None):
+        """``eos_token_id``: one id, several (any of them ends a request), or None."""
         self.cache = cache
         self.max_num_seqs = max_num_seqs
         self.max_num_batched_tokens = max_num_batched_tokens
         self.prefill_chunk_size = prefill_chunk_size or max_num_batched_tokens
         self.max_model_len = max_model_len
-        self.eos_token_id = eos_token_id
+        self.eos_token_ids = frozenset(
+            () if eos_token_id is None else ([int(eos_token_id)] if isinstance(eos_token_id, int) else map(int, eos_token_id)))
         self.waiting: deque[Sequence] = deque()
         self.running: list[Sequence] = []
         self.finished: list[Sequence] = []
@@ -176,7 +178,7 @@ class Scheduler:
         limit, "stop" for an end-of-sequence or stop token."""
         last = seq.output_token_ids[-1]
         sp = seq.sampling
-        if not sp.ignore_eos and self.eos_token_id is not None and last == self.eos_token_id:
+        if not sp.ignore_eos and last in self.eos_token_ids:
             return "stop"
         if last in sp.stop_token_ids:
             return "stop"

@@ -115,6 +115,12 @@ class DecoderModel:
         self.final_norm.load(lo.final_norm_prefix, source, dtype, device)
         if lo.tie_head:
             self.head = self.embed            # the same storage (model.py:417-418)
+            if lo.head_name in set(source.names()):
+                # the reference lets such a tensor overwrite the shared storage (whichever of the two is read
+                # last wins); here the embedding is the one that counts, and the user is told
+                import warnings
+                warnings.warn(f"{where}: the model ties its output head to the embedding; the stored "
+                              f"{lo.head_name!r} is not used", stacklevel=2)
         else:
             self.head = ops.prepare_matrix(source.get(lo.head_name).to(dtype).to(device))
 
@@ -147,14 +153,8 @@ class DecoderModel:
         [num_logit_rows, vocab] (None when no logits are wanted)."""
         lo = self.layout
         T, H = ctx.num_tokens, lo.hidden_size
-        # a few rows in bfloat16: kernels that write the stream leave its rows' sums of squares behind,
-        # ceil(H / 16) partial sums a row, for the norms fused into the products that follow
-        ssq = None
-        if ctx.dtype == torch.bfloat16 and T <= ops.SMALL_M_MAX:
-            ssq = ctx.arena.alloc((T, -(-(-(-H // 16)) // 4) * 4), torch.float32)
-        stream = ops.ResidualStream(ctx.arena.alloc((T, H), torch.float32), ctx.arena.alloc((T, H), ctx.dtype), ssq)
-        ops.embedding(ctx.token_ids, self.embed, stream.resid, ssq)
-        stream.n_ssq = 1 if ssq is not None else 0
+        stream = ops.ResidualStream.for_step(ctx.arena.alloc, T, H, ctx.dtype)
+        ops.embedding(ctx.token_ids, self.embed, stream)
         views = [(cache.layer_view(e.cache_slot), cache.group_of_slot[e.cache_slot][0]) if e.cache_slot is not None
                  else (None, None) for e in lo.plan]
         for i, entry in enumerate(lo.plan):

@@ -263,10 +263,16 @@ def prepare_matrix(w: torch.Tensor) -> torch.Tensor:
     return w.contiguous()
 
 
-def embedding(token_ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
+def embedding(token_ids: torch.Tensor, table: torch.Tensor, out,
               ssq: Optional[torch.Tensor] = None) -> None:
     """out[t] = float32(table[token_ids[t]]); out is the float32 residual stream [T, H].  With ``ssq``
-    [T, P] float32, ssq[t, 0] gets the row's sum of squares (one partial sum per row)."""
+    [T, P] float32, ssq[t, 0] gets the row's sum of squares (one partial sum per row).  ``out`` may be a
+    ``ResidualStream``: its rows are written and, if it keeps sums of squares, those too."""
+    if isinstance(out, ResidualStream):
+        stream = out
+        embedding(token_ids, table, stream.resid, stream.ssq)
+        stream.has_delta, stream.n_ssq = False, (1 if stream.ssq is not None else 0)
+        return
     _i32(token_ids, "token_ids")
     T, (V, H) = token_ids.numel(), table.shape
     _need(out.dtype == torch.float32 and out.shape == (T, H) and out.is_contiguous(), "embedding: out must be float32 [T, H]")
@@ -322,6 +328,17 @@ class ResidualStream:
         self.resid, self.delta, self.ssq = resid, delta, ssq
         self.has_delta = False
         self.n_ssq = 0
+
+    @classmethod
+    def for_step(cls, alloc, num_tokens: int, width: int, dtype: torch.dtype) -> "ResidualStream":
+        """The stream of a step of ``num_tokens`` rows of ``width``, from ``alloc(shape, dtype)``.  For a few rows
+        in bfloat16 it also gets room for the partial sums of squares that the products which add into the
+        stream leave behind (one per 16 columns, padded to whole float4s): their layout is the kernels'
+        business, so it is settled here, beside their fronts, and not by the model."""
+        ssq = None
+        if dtype == torch.bfloat16 and num_tokens <= SMALL_M_MAX:
+            ssq = alloc((num_tokens, -(-(-(-width // 16)) // 4) * 4), torch.float32)
+        return cls(alloc((num_tokens, width), torch.float32), alloc((num_tokens, width), dtype), ssq)
 
 
 class ResidualSink:
@@ -747,6 +764,12 @@ def selftest_starved_product(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor
 
 
 ROPE_TABLE_MIN_T = 64   # tokens from which a step's rotation angles are computed once (below: in the kernel)
+
+
+def rope_table_applies(num_tokens: int, dtype: torch.dtype, head_dim: int, rotary_dim: int) -> bool:
+    """Whether the kernels that rotate q and k take a table of this step's cosines and sines (``rope_table``)
+    instead of computing the angles themselves: many tokens, bfloat16, head size 128 rotated as a whole."""
+    return num_tokens >= ROPE_TABLE_MIN_T and dtype == torch.bfloat16 and head_dim == 128 and rotary_dim == head_dim
 
 
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor) -> None:

@@ -18,7 +18,6 @@ from .. import ops
 from ..cache.spec import PagedKVSpec
 from ..weights.spec import MATRIX, NORM, WeightSpec
 from .base import Mixer, PartSpec, StepContext, register, step_hint
-from .rope import NeoxRope
 
 
 @register("mixer", "gqa_attention")
@@ -81,10 +80,11 @@ class GQAAttention(Mixer):
         H, Hkv, D = self.num_heads, self.num_kv_heads, self.head_dim
         view = ctx.groups[group]
         qkv = ctx.arena.alloc((T, self.q_width + 2 * self.kv_width), ctx.dtype)
-        fused_rope = isinstance(self.pos, NeoxRope)
+        rot = self.pos.half_split_rotation() if self.pos is not None else None
+        fused_rope = rot is not None
         attn = ctx.arena.alloc((T, self.q_width), ctx.dtype)
-        if fused_rope and ops.qkv_rope_fused_applies(T, qkv.shape[1], self.hidden_size, ctx.dtype, D, self.pos.rotary_dim):
-            table = self.pos.step_table(ctx)
+        if fused_rope and ops.qkv_rope_fused_applies(T, qkv.shape[1], self.hidden_size, ctx.dtype, D, rot.rotary_dim):
+            table = rot.step_table(ctx)
             if table is not None:
                 # many rows: norm, rotation and cache write happen in the epilogue of the QKV product
                 if isinstance(x, ops.NormedInput):
@@ -97,11 +97,11 @@ class GQAAttention(Mixer):
                 return
         ops.prefetch_next(self.w_o)
         ops.linear(x, self.w_qkv, qkv)
-        if fused_rope and ops.attention_fuses_rotary(qkv, ctx, H, Hkv, D, self.window or 0, self.pos.rotary_dim):
+        if fused_rope and ops.attention_fuses_rotary(qkv, ctx, H, Hkv, D, self.window or 0, rot.rotary_dim):
             # a decode step: the attention kernel norms and rotates q and k and writes the cache itself
             ops.paged_attention(qkv, cache, view.block_tables, ctx, attn, self.scale, self.window or 0, H, Hkv, D,
                                 fused=dict(q_norm_w=self.q_norm_w, k_norm_w=self.k_norm_w, eps=self.qk_norm_eps or 0.0,
-                                           inv_freq=self.pos.inv_freq, write_kv=write_cache))
+                                           inv_freq=rot.inv_freq, write_kv=write_cache))
             ops.linear(attn, self.w_o, out)
             return
         if self.pos is not None and not fused_rope:
@@ -118,10 +118,10 @@ class GQAAttention(Mixer):
         else:
             ops.qk_norm_rope_kv_write(
                 qkv, ctx.positions, self.q_norm_w, self.k_norm_w, self.qk_norm_eps or 0.0,
-                self.pos.inv_freq if fused_rope else None,
-                self.pos.rotary_dim if fused_rope else 0,
+                rot.inv_freq if fused_rope else None,
+                rot.rotary_dim if fused_rope else 0,
                 cache, view.slot_mapping, H, Hkv, D, write_kv=write_cache,
-                cos_sin=self.pos.step_table(ctx) if fused_rope else None)
+                cos_sin=rot.step_table(ctx) if fused_rope else None)
         ops.paged_attention(qkv, cache, view.block_tables, ctx, attn, self.scale,
                             self.window or 0, H, Hkv, D, next_pages=step_hint(ctx, "next_cache"))
         ops.prefetch_next(step_hint(ctx, "weights_after_mixer"))

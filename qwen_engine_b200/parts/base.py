@@ -223,6 +223,13 @@ class PositionEncoding(Part):
         """Encode ``ctx.positions`` into q [T, Hq, D] and k [T, Hkv, D] in place."""
         raise NotImplementedError
 
+    def half_split_rotation(self):
+        """None, or, for an encoding that rotates the pairs (x[j], x[j + rotary_dim / 2]) by
+        position * inv_freq[j], an object with ``inv_freq`` (float32 on the device), ``rotary_dim`` and
+        ``step_table(ctx)``: a mixer may then hand the rotation to the kernel that also norms q and k and
+        writes the cache, instead of calling ``rotate``."""
+        return None
+
 
 class Mixer(Part):
     # False for a mixer whose forward reads device data on the host or allocates: steps of a model

@@ -36,8 +36,7 @@ class NeoxRope(PositionEncoding):
         """The cosines and sines of this step's angles [T, rotary_dim / 2, 2], computed once per step
         and shared by every layer with the same frequencies; None for small steps (the kernel then
         computes them itself) and where the fused kernel takes no table."""
-        if (ctx.num_tokens < ops.ROPE_TABLE_MIN_T or ctx.dtype != torch.bfloat16 or self.head_dim != 128
-                or self.rotary_dim != self.head_dim):
+        if not ops.rope_table_applies(ctx.num_tokens, ctx.dtype, self.head_dim, self.rotary_dim):
             return None
         key = ("rope_table", self.theta, self.rotary_dim)
         table = ctx.extras.get(key)
@@ -50,3 +49,6 @@ class NeoxRope(PositionEncoding):
 
     def rotate(self, ctx: StepContext, q, k) -> None:
         ops.rope_neox(q, k, ctx.positions, self.inv_freq, self.rotary_dim)
+
+    def half_split_rotation(self):
+        return self

@@ -22,6 +22,10 @@ def prepare_matrix(w):
 
 
 def embedding(token_ids, table, out, ssq=None):
+    from qwen_engine_b200.ops import ResidualStream
+    if isinstance(out, ResidualStream):
+        out.has_delta, out.n_ssq = False, 0
+        out = out.resid
     out.copy_(table[token_ids.long()].to(torch.float32))
 
 

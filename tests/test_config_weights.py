@@ -174,3 +174,18 @@ def test_tied_checkpoint_may_carry_a_head(tmp_path):
     t["lm_head.weight"] = t["model.embed_tokens.weight"].clone()
     save_file(t, path)
     check_against_manifest(SafetensorsSource(d), build_model(cfg).weight_manifest())
+    # loading it works; the stored head is not used, and the user is told so
+    model = build_model(cfg)
+    with pytest.warns(UserWarning, match="lm_head.weight"):
+        model.load_weights(SafetensorsSource(d), torch.float32, "cpu")
+    assert model.head is model.embed
+
+
+def test_every_end_of_sequence_id_is_kept():
+    cfg = config_from_dict(dict(preset_config_dict("tiny-a"), eos_token_id=[7, 9]))
+    assert cfg.eos_token_id == 7 and cfg.eos_token_ids == (7, 9)
+    assert cfg.to_dict()["eos_token_id"] == [7, 9] and "eos_token_ids" not in cfg.to_dict()
+    assert config_from_dict(cfg.to_dict()) == cfg
+    one = config_from_dict(dict(preset_config_dict("tiny-a"), eos_token_id=5))
+    assert one.eos_token_ids == (5,) and one.to_dict()["eos_token_id"] == 5
+    assert config_from_dict(preset_config_dict("tiny-a")).eos_token_ids == ()

@@ -160,3 +160,11 @@ def test_a_wait_that_ran_out_on_the_device_surfaces_as_an_error(model_folders, c
         eng.serving()
     assert cleared
     eng.check_device()                                  # cleared: the next check passes
+
+
+def test_a_length_limit_beyond_the_models_positions_is_refused_at_construction(model_folders, cpu_ops):
+    """tiny-a has 512 positions: an engine that would let a request grow past them is refused when it is
+    built, not in the middle of serving, where the other live requests would be lost with it."""
+    with pytest.raises(ValueError, match="max_position_embeddings = 512"):
+        make_engine(model_folders["tiny-a"], "tiny-a", F32, device="cpu", max_model_len=513, num_blocks=8)
+    make_engine(model_folders["tiny-a"], "tiny-a", F32, device="cpu", max_model_len=512, num_blocks=8)

@@ -227,3 +227,14 @@ def test_tokens_with_a_place_kept_for_them_holds_and_late_stops():
     assert [x.seq_id for x in s.running] == [2]
     with pytest.raises(RuntimeError):
         s.update(cur, {2: 1}, {2: 0})                   # no place is waiting there
+
+
+def test_any_of_several_end_of_sequence_ids_stops_a_request():
+    cm, s = _setup(eos=(7, 9))
+    a, b, c = _seq(0, 3, max_new=5), _seq(1, 3, max_new=5), _seq(2, 3, max_new=5, ignore_eos=True)
+    for q in (a, b, c):
+        s.add(q)
+    out = s.schedule()
+    ended = s.update(out, _fake_step(cm, out, token_of=lambda seq: (7, 9, 9)[seq.seq_id]))
+    assert {q.seq_id: q.finish_reason for q in ended} == {0: "stop", 1: "stop"}
+    assert c.status is SequenceStatus.RUNNING
