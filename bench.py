@@ -57,6 +57,15 @@ def load_peaks() -> tuple[dict, str]:
     return dict(FALLBACK_PEAKS), "fallback"
 
 
+def config_record(model, layers, layers_of_config, hidden, heads, kv_heads, head_dim, intermediate, vocab, batch, context,
+                  page_size, prefill_tokens) -> dict:
+    """The ``config`` of the JSON line: every size, flat, the same keys for both arms."""
+    return {"model": model, "layers": layers, "layers_of_config": layers_of_config, "hidden": hidden, "heads": heads,
+            "kv_heads": kv_heads, "head_dim": head_dim, "intermediate": intermediate, "vocab": vocab,
+            "global_batch": batch, "seq_len": context, "page_size": page_size, "prefill_tokens": prefill_tokens,
+            "l2": "inputs larger than L2", "parallelism": "single GPU"}
+
+
 class ClockSampler:
     """nvidia-smi in the background during the timed regions (read-only)."""
 
@@ -216,11 +225,10 @@ def reference_arm(args) -> int:
             "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "impl": "reference",
             "data": "synthetic: uniform random token ids, the reference's own random initialisation",
-            "config": {"model": "qwen3-0.6b", "layers": cfg.num_hidden_layers, "hidden": cfg.hidden_size,
-                       "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
-                       "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "global_batch": args.batch,
-                       "seq_len": args.context, "page_size": block, "prefill_tokens": args.prefill_tokens,
-                       "mode": "triton", "parallelism": "single GPU"},
+            "config": config_record("qwen3-0.6b", cfg.num_hidden_layers, cfg.num_hidden_layers, cfg.hidden_size,
+                                    cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.intermediate_size,
+                                    cfg.vocab_size, args.batch, args.context, block, args.prefill_tokens),
+            "mode": "triton",
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s"},
             "prefill": {"value": round(args.prefill_tokens / (prefill_ms / 1e3), 1), "tokens": args.prefill_tokens,
                         "ms": round(prefill_ms, 3)},
@@ -230,6 +238,215 @@ def reference_arm(args) -> int:
         msg = f"{type(e).__name__}: {e}".replace("\n", " ")[:300]
         print(json.dumps({"impl": "reference", "unavailable": f"the reference did not run here: {msg}"}))
         return 0
+
+
+
+def capture_context(runner, entries):
+    """Run one step eagerly and hand back the StepContext the model saw (index data, block tables and the
+    attention work lists on the device), for timing single kernels on a real step's data."""
+    seen = []
+    real = runner.model.forward
+    graphs = runner.use_cuda_graphs
+    runner.use_cuda_graphs = False
+    runner.model.forward = lambda ctx, cache: (seen.append(ctx), real(ctx, cache))[1]
+    try:
+        runner.step(entries)
+    finally:
+        runner.model.forward = real
+        runner.use_cuda_graphs = graphs
+    return seen[0]
+
+
+def kernel_chains(loaded, cfg, peaks, tag, ctx, torch, ops, out) -> None:
+    """Each kernel class of the step alone: one launch per layer, back to back over the layers' own weights and
+    caches (more bytes than L2 holds, as in the step), timed with CUDA events; microseconds a launch and the
+    launch's bytes (decode: weights or keys and values read once) or flops (prompt portions) over the measured
+    peak.  ``tag`` "decode": the classes of a decode step at the benchmark's batch; "prefill": those of its prompt.
+    ``ctx`` must be the context of the step that ran last (its index data lives in the step function's buffer)."""
+    model, cache = loaded.model, loaded.cache
+    blocks = model.blocks
+    L = len(blocks)
+    H, Hq, Hkv, D, I = cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.intermediate_size
+    dev = "cuda:0"
+    bf = torch.bfloat16
+    hbm, tflops = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+
+    def chain(fn, reps=5):
+        """us a launch of the chain's L launches, replayed from a CUDA graph (so that the host's launch rate,
+        a few microseconds a call from Python, does not show)."""
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        graph.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) * 1e3 / reps / L
+
+    def record(name, us, nbytes=None, flops=None):
+        e = {"us": round(us, 2)}
+        if nbytes is not None:
+            e["gbs"] = round(nbytes / us / 1e3, 1)
+            e["frac"] = round(nbytes / (us * 1e-6) / hbm, 3)
+        if flops is not None:
+            e["tflops"] = round(flops / us / 1e6, 1)
+            e["frac"] = round(flops / (us * 1e-6) / tflops, 3)
+        out[name] = e
+
+    T = ctx.num_tokens
+    g = torch.Generator(device=dev).manual_seed(1)
+    rnd = lambda *shape: (torch.randn(*shape, generator=g, device=dev) * 0.5).to(bf)      # noqa: E731
+    x, attn, act = rnd(T, H), rnd(T, Hq * D), rnd(T, I)
+    qkv, gate_up = rnd(T, (Hq + 2 * Hkv) * D), rnd(T, 2 * I)
+    y_qkv, y_h, y_gu = torch.empty_like(qkv), torch.empty(T, H, dtype=bf, device=dev), torch.empty_like(gate_up)
+    resid = torch.zeros(T, H, dtype=torch.float32, device=dev)
+    a_out = torch.empty(T, Hq * D, dtype=bf, device=dev)
+    dec = tag == "decode"
+    tokens_kv = sum(ctx.ctx_lens_host) + T
+    view = ctx.groups[cache.group_of_slot[0][0]]
+    mixers = [b.mixer for b in blocks]
+    ffns = [b.ffn for b in blocks]
+    ctx.arena.reset()
+
+    def products(name, ws, xin, yout, N, K):
+        us = chain(lambda: [ops.linear(xin, w, yout) for w in ws])
+        record(f"{tag}_{name}", us, nbytes=N * K * 2 if dec else None, flops=None if dec else 2.0 * T * N * K)
+    rot0 = mixers[0].pos.half_split_rotation()
+    if not dec and ops.qkv_rope_fused_applies(T, qkv.shape[1], H, bf, D, rot0.rotary_dim):
+        # as the step runs it: per-head norm, rotation and cache write in the product's epilogue
+        table = torch.empty(T, D // 2, 2, dtype=torch.float32, device=dev)
+        ops.rope_table(ctx.positions, rot0.inv_freq, table)
+        us = chain(lambda: [ops.linear_qkv_rope(x, m.w_qkv, y_qkv, m.q_norm_w, m.k_norm_w, cfg.rms_norm_eps, table,
+                                                cache.layer_view(i), view.slot_mapping, Hq, Hkv) for i, m in enumerate(mixers)])
+        record(f"{tag}_qkv_rope", us, flops=2.0 * T * (Hq + 2 * Hkv) * D * H)
+    else:
+        products("qkv", [m.w_qkv for m in mixers], x, y_qkv, (Hq + 2 * Hkv) * D, H)
+    products("o", [m.w_o for m in mixers], attn, y_h, H, Hq * D)
+    if not dec and ops.swiglu_fused_applies(T, I, H, bf):
+        us = chain(lambda: [ops.linear_swiglu(x, f.w_gate_up, act) for f in ffns])
+        record(f"{tag}_gate_up_swiglu", us, flops=2.0 * T * 2 * I * H)
+    else:
+        products("gate_up", [f.w_gate_up for f in ffns], x, y_gu, 2 * I, H)
+    if dec and I <= ops.FUSED_SILU_MAX_K:
+        us = chain(lambda: [ops.linear_silu_mul(gate_up, f.w_down, y_h, None) for f in ffns])
+        record(f"{tag}_down_silu", us, nbytes=H * I * 2)
+    else:
+        products("down", [f.w_down for f in ffns], act, y_h, H, I)
+
+    def attention():
+        for i, m in enumerate(mixers):
+            mark = ctx.arena.mark()
+            ops.paged_attention(qkv, cache.layer_view(i), view.block_tables, ctx, a_out, m.scale, 0, Hq, Hkv, D)
+            ctx.arena.release(mark)
+    us = chain(attention)
+    kv_bytes = tokens_kv * 2 * Hkv * D * 2
+    if dec:
+        record("decode_attention", us, nbytes=kv_bytes)
+    else:
+        flops = sum(4.0 * Hq * D * n * (c + (n + 1) / 2) for n, c in zip(ctx.q_lens_host, ctx.ctx_lens_host))
+        record("prefill_attention", us, flops=flops)
+    out[f"{tag}_attention"]["kernel"] = ops.last_attention_kernel
+
+    w_norm = blocks[0].norm1.weight
+    us = chain(lambda: [ops.add_rmsnorm(resid, y_h, b.norm1.weight, cfg.rms_norm_eps, x) for b in blocks])
+    record(f"{tag}_add_rmsnorm", us, nbytes=T * H * (4 + 4 + 2 + 2))
+    del w_norm
+
+    def rotary():
+        for i, m in enumerate(mixers):
+            rot = m.pos.half_split_rotation()
+            ops.qk_norm_rope_kv_write(qkv, ctx.positions, m.q_norm_w, m.k_norm_w, cfg.rms_norm_eps, rot.inv_freq, rot.rotary_dim,
+                                      cache.layer_view(i), view.slot_mapping, Hq, Hkv, D)
+    us = chain(rotary)
+    record(f"{tag}_qk_norm_rope_kv_write", us, nbytes=T * (Hq + 2 * Hkv) * D * 2 * 2)
+    if tag == "decode":
+        # the output head on the wanted rows, alone (one launch: the matrix is larger than L2 by itself)
+        N = ctx.num_logit_rows
+        normed = torch.randn(N, H, device=dev).to(bf)
+        logits = torch.empty(N, cfg.vocab_size, dtype=torch.float32, device=dev)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        times = []
+        for _ in range(4):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            ops.linear(normed, model.head, logits)
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) * 1e3)
+        us = sorted(times[1:])[1]
+        out["decode_lm_head"] = {"us": round(us, 2), "gbs": round(cfg.vocab_size * H * 2 / us / 1e3, 1),
+                                 "frac": round(cfg.vocab_size * H * 2 / (us * 1e-6) / hbm, 3)}
+
+
+def run_workload(name: str, torch, peaks) -> dict:
+    """A scheduler workload at the sizes of a larger model, end to end through ``LLMEngine.serving`` with random
+    weights: generated tokens a second (wall clock from the first step to the last), prompt tokens found in shared
+    pages, preemptions, and steps, tokens and device time by kind of step."""
+    from qwen_engine_b200.config import EngineConfig, preset_config_dict, preset_init
+    from qwen_engine_b200.engine.llm import LLMEngine
+    from qwen_engine_b200.engine.loading import load_model
+    from qwen_engine_b200.registry import config_from_dict
+    from qwen_engine_b200.sampling import SamplingParams
+    rng = random.Random(11)
+    if name == "mixed-1.7b":
+        preset, n_req, new_tokens, chunk, max_len = "qwen3-1.7b", 32, 256, 512, 2048 + 256 + 16
+        lens = [rng.randint(128, 2048) for _ in range(n_req)]
+        shared = 0
+    elif name == "shared-prefix-4b":
+        preset, n_req, new_tokens, chunk, max_len = "qwen3-4b", 16, 512, 2048, 4096
+        lens = [1024 + 256] * n_req
+        shared = 1024
+    else:
+        raise ValueError(f"unknown workload {name!r}")
+    cfg = config_from_dict(preset_config_dict(preset))
+    init = preset_init(preset)
+    page = init["block_size"]
+    V = cfg.vocab_size
+    common = [rng.randrange(V) for _ in range(shared)]
+    prompts = [common + [rng.randrange(V) for _ in range(n - shared)] for n in lens]
+    pages = sum(-(-(n + new_tokens) // page) + 1 for n in lens) + 64
+    t0 = time.time()
+    loaded = load_model(None, torch.bfloat16, "cuda:0", page, pages, n_req, enable_prefix_cache=True, config=cfg,
+                        random_seed=init["seed"], random_std=init["std"], random_norm_std=init["norm_std"])
+    print(f"[bench] {name}: model ready in {time.time() - t0:.1f}s", file=sys.stderr, flush=True)
+    ec = EngineConfig(dtype=torch.bfloat16, device="cuda:0", block_size=page, num_blocks=pages, max_model_len=max_len,
+                      max_num_seqs=n_req, max_num_batched_tokens=chunk + n_req, prefill_chunk_size=chunk,
+                      enable_prefix_cache=True, profile=True)
+    eng = LLMEngine(loaded, ec)
+    sp = SamplingParams(max_new_tokens=new_tokens, ignore_eos=True)
+    # warm-up outside the timed run: one short request through prompt and decoding (kernels loaded, arena sized)
+    eng.add_request(prompts[0][:64] if not shared else [rng.randrange(V) for _ in range(64)], SamplingParams(max_new_tokens=4, ignore_eos=True))
+    eng.serving()
+    eng.stats.__init__()
+    hit0, pre0 = eng.scheduler.prefix_hit_tokens, eng.scheduler.num_preemptions
+    for p in prompts:
+        eng.add_request(p, sp)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    outs = eng.serving()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    generated = sum(len(o.output_token_ids) for o in outs)
+    st = eng.stats
+    rec = {"model": preset, "layers": cfg.num_hidden_layers, "requests": n_req, "prompt_tokens": sum(lens),
+           "new_tokens_each": new_tokens, "prefill_chunk": chunk, "value": round(generated / wall, 1), "unit": "generated tokens/s",
+           "seconds": round(wall, 3), "generated_tokens": generated, "steps": st.steps,
+           "prefix_hit_tokens": eng.scheduler.prefix_hit_tokens - hit0, "preemptions": eng.scheduler.num_preemptions - pre0,
+           "graph_replays": loaded.runner.num_graph_replays,
+           "by_kind": {k: {"steps": v["steps"], "tokens": v["tokens"], "device_ms": round(v["device_ms"], 1)}
+                       for k, v in (st.profile or {}).items()}}
+    del eng, loaded
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
+    return rec
 
 
 def main() -> int:
@@ -245,6 +462,12 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--dtype", default="bfloat16")
+    ap.add_argument("--workload", choices=["mixed-1.7b", "shared-prefix-4b"], default=None,
+                    help="run only this scheduler workload (32 requests with prompts of 128..2048 tokens and 256 new tokens at "
+                         "Qwen3-1.7B sizes in portions of 512; 16 requests sharing 1,024 of 1,280 prompt tokens with 512 new "
+                         "tokens at Qwen3-4B sizes) and print its record as one JSON line")
+    ap.add_argument("--no-workloads", action="store_true", help="skip the two scheduler workloads at the end of the default run")
+    ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel-class timings")
     ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
                     help="bracket that timed region with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     args = ap.parse_args()
@@ -257,6 +480,11 @@ def main() -> int:
 
     import torch
     from qwen_engine_b200 import ops
+    if args.workload:
+        peaks, _ = load_peaks()
+        print(json.dumps({"metric": f"generated tok/s, workload {args.workload}", "impl": "ours", "n_gpus": 1,
+                          **run_workload(args.workload, torch, peaks)}))
+        return 0
     from qwen_engine_b200.config import EngineConfig, parse_dtype, preset_config_dict, preset_init
     from qwen_engine_b200.engine.llm import LLMEngine
     from qwen_engine_b200.engine.loading import load_model
@@ -322,13 +550,24 @@ def main() -> int:
     m0 = clocks.mark()
     prefill_ms = timed(prefill_once, 5 if args.profile is None else 1, "prefill")
     spans.append((m0, clocks.mark()))
+    # the first, eager run of a prompt length that has not come before (recurring shapes are replayed from a graph)
+    def prefill_eager(n):
+        rc = cache.open("prefill")
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        runner.step([StepEntry(rc, prompt[:n], [n - 1])])
+        torch.cuda.synchronize()
+        cache.close(rc)
+        return (time.perf_counter() - t0) * 1e3
+    eager_ms = min(prefill_eager(P - 16 * k) for k in (1, 2, 3)) if args.profile is None else None
     c = cfg
     gemm_params = c.num_hidden_layers * (c.hidden_size * (c.q_width + 2 * c.kv_width) + c.q_width * c.hidden_size
                                          + 3 * c.hidden_size * c.intermediate_size)
     prefill_flops = 2.0 * P * gemm_params + c.num_hidden_layers * 4.0 * c.num_attention_heads * c.head_dim * P * P / 2 \
         + 2.0 * c.vocab_size * c.hidden_size
     prefill = {"value": round(P / (prefill_ms / 1e3), 1), "tokens": P, "ms": round(prefill_ms, 3),
-               "frac": round(prefill_flops / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)}
+               "frac": round(prefill_flops / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4),
+               "first_run_ms": None if eager_ms is None else round(eager_ms, 3)}
 
     # ---- decode at batch 64, 8, 1 over real, scattered pages ----------------------------------------
     reqs = [cache.open(f"d{i}") for i in range(big_batch)]
@@ -355,15 +594,31 @@ def main() -> int:
         return batch * 1e3 / ms, ms
 
     points = {}
+    points_detail = {}
+
+    def point(name, batch, steps):
+        rate, ms = decode_rate(batch, steps, 3)
+        nbytes = weight_bytes + batch * reqs[0].num_tokens * kv_bytes_per_token
+        points[name] = round(rate, 1)
+        points_detail[name] = {"ms": round(ms, 4), "context": reqs[0].num_tokens, "gbs": round(nbytes / ms / 1e6, 1),
+                               "frac": round(nbytes / (ms / 1e3) / 1e9 / peaks["hbm_gbs"], 4)}
     if not args.no_points and big_batch >= 64:
-        points["decode_b64"] = round(decode_rate(64, max(5, args.steps // 2), 3)[0], 1)
+        point("decode_b64", 64, max(5, args.steps // 2))
     rec = {}
     value, ms_per_step = decode_rate(args.batch, args.steps, args.warmup, rec, "decode")
     ctx_now = reqs[0].num_tokens
     step_bytes = weight_bytes + args.batch * ctx_now * kv_bytes_per_token
     achieved = step_bytes / (ms_per_step / 1e3) / 1e9
     if not args.no_points:
-        points["decode_b1"] = round(decode_rate(1, args.steps, 3)[0], 1)
+        point("decode_b1", 1, args.steps)
+    kernels = {}
+    if not args.no_kernels and args.profile is None and dtype == torch.bfloat16:
+        dctx = capture_context(runner, [StepEntry(rc, [rng.randrange(V)], [0]) for rc in reqs[:args.batch]])
+        kernel_chains(loaded, cfg, peaks, "decode", dctx, torch, ops, kernels)
+        rc = cache.open("prefill")
+        pctx = capture_context(runner, [StepEntry(rc, prompt, [P - 1])])
+        kernel_chains(loaded, cfg, peaks, "prefill", pctx, torch, ops, kernels)
+        cache.close(rc)
     for rc in reqs:
         cache.close(rc)
 
@@ -399,6 +654,19 @@ def main() -> int:
            "h2d_bytes_per_step": runner.last_h2d_bytes, "d2h_bytes_per_step": 4 * args.batch}
     while eng.has_work():
         eng.step()
+    eng.check_device()               # no bounded wait inside a kernel ran out during any of the above
+    workloads = {}
+    if not args.no_workloads and args.profile is None and dtype == torch.bfloat16 and args.preset == "qwen3-0.6b" and not args.layers:
+        del eng, reqs, runner, cache, model
+        loaded.runner = loaded.cache = loaded.model = None
+        import gc as _gc
+        _gc.collect()
+        torch.cuda.empty_cache()
+        for w in ("mixed-1.7b", "shared-prefix-4b"):
+            try:
+                workloads[w] = run_workload(w, torch, peaks)
+            except Exception as e:      # noqa: BLE001 - the headline stands without them
+                workloads[w] = {"failed": f"{type(e).__name__}: {e}"[:200]}
     clocks.stop()
 
     line = {
@@ -406,17 +674,16 @@ def main() -> int:
         "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if dtype == torch.bfloat16 else "fp32",
         "data": "synthetic: uniform random token ids, random weights N(0, 0.02) seed 2", "impl": "ours",
-        "config": {"model": args.preset, "layers": cfg.num_hidden_layers, "layers_of_config": layers_of_config,
-                   "hidden": c.hidden_size, "heads": c.num_attention_heads, "kv_heads": c.num_key_value_heads,
-                   "head_dim": c.head_dim, "intermediate": c.intermediate_size, "vocab": c.vocab_size,
-                   "global_batch": args.batch, "seq_len": args.context, "context_at_timing": ctx_now,
-                   "page_size": page, "prefill_tokens": P, "l2": "inputs larger than L2", "parallelism": "single GPU",
-                   "peaks": peaks_src},
+        "config": config_record(args.preset, cfg.num_hidden_layers, layers_of_config, c.hidden_size, c.num_attention_heads,
+                                c.num_key_value_heads, c.head_dim, c.intermediate_size, c.vocab_size, args.batch,
+                                args.context, page, P),
+        "context_at_timing": ctx_now, "peaks": peaks_src,
         "e2e": e2e, "gpu_launches": rec.get("launches", 0),
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peaks["hbm_gbs"], 4)},
-        "points": points,
+        "points": points, "points_detail": points_detail,
+        "kernels": kernels, "workloads": workloads,
         "clocks": clocks.summary(spans),
     }
     print(json.dumps(line))

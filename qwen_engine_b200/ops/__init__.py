@@ -1072,6 +1072,8 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
         items, merge = plan[f"fa{key}_items"], plan[f"fa{key}_merge"]
         n_parts, part_rows, small_tiles, max_rows, same_parts = plan[f"fa{key}_info_host"]
         n_items, n_merge = items.numel() // FLASH_ITEM_INTS, merge.numel() // 4
+        if n_items == 0 and f"tc{key}_items" in plan:
+            return                      # every request of the step went to the kernel above
         part_acc = part_ml = None
         if n_parts:
             part_acc = ctx.arena.alloc((n_parts * Hkv * part_rows, D), torch.float32)
