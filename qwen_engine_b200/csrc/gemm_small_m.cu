@@ -51,9 +51,81 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
   gsm_cta<MT, TOut, XMODE, RESID>(x, w, out, M, N, K, k_per_warp, na, blockIdx.x, red, s_rstd, c0, c1);
 }
 
+// The same product by clusters of S CTAs that share 16 weight rows, a share of K each (see gsm_cta, CLUSTER): for weight
+// matrices of so few rows that one CTA per 16 of them would leave most SMs without work.
+template <int MT, typename TOut, int XMODE, bool RESID>
+__global__ void __launch_bounds__(512)
+gemm_small_m_cluster_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                            TOut* __restrict__ out, int M, int N, int K, int k_per_warp, int k_per_cta, FuseArgs na) {
+  extern __shared__ float red[];                    // [warps][16][8 MT], then this CTA's sums [16][8 MT]
+  __shared__ float s_rstd[8 * MT];
+  const int S = (int)cluster_num_ctas();
+  const int vb = (int)blockIdx.x / S;
+  const int k_off = (int)cluster_cta_rank() * k_per_cta;
+  GsmChunk c0, c1;
+  gsm_prefetch(w, N, K, k_per_warp, vb, c0, c1, k_off, k_per_cta);
+  if (na.next_bytes) {
+    const unsigned long long pieces = (na.next_bytes + 4095) >> 12;
+    const unsigned long long piece = (unsigned long long)threadIdx.x * gridDim.x + blockIdx.x;
+    if (piece < pieces) {
+      const unsigned long long off = piece << 12;
+      const unsigned size = (unsigned)min(4096ull, na.next_bytes - off) & ~15u;
+      if (size) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" :: "l"(na.next_w + off), "r"(size) : "memory");
+    }
+  }
+  pdl_launch_dependents();
+  pdl_wait();
+  gsm_cta<MT, TOut, XMODE, RESID, true>(x, w, out, M, N, K, k_per_warp, na, vb, red, s_rstd, c0, c1, k_off, k_per_cta);
+}
+
+// How many CTAs share 16 weight rows: 1 where the rows alone give (nearly) every SM a CTA, else 2 or 4 while every CTA
+// still has 512 or more of K.  A function of the weight matrix alone, never of the number of rows of the step, so that
+// the order of a row's sums does not depend on the batch.
+static int g_small_m_max_cluster = 4;
+// The most CTAs that may share 16 weight rows (1: never share; for measurements and tests).
+extern "C" void qe_small_m_max_cluster(int ctas) { g_small_m_max_cluster = ctas < 1 ? 1 : (ctas > 4 ? 4 : ctas); }
+static int small_m_cluster_size(int N, int K) {
+  const int ctas = (N + 15) / 16;
+  if (g_small_m_max_cluster >= 4 && ctas * 4 <= 148 && K >= 4 * 512) return 4;
+  if (g_small_m_max_cluster >= 2 && ctas * 2 <= 148 && K >= 2 * 512) return 2;
+  return 1;
+}
+
+template <int MT, int XMODE, bool RESID>
+static int launch_small_m_cluster(const void* x, const void* w, void* out, int M, int N, int K, int out_f32, int S,
+                                  cudaStream_t stream, FuseArgs na) {
+  const int ctas = (N + 15) / 16;
+  const int k_per_cta = ((K + S - 1) / S + 63) / 64 * 64;
+  int warps = 16;
+  int k_per_warp = ((k_per_cta + warps - 1) / warps + 63) / 64 * 64;
+  warps = (k_per_cta + k_per_warp - 1) / k_per_warp;
+  const size_t smem = (size_t)(warps + 1) * 16 * 8 * MT * sizeof(float);
+  static bool configured = false;
+  if (!configured) {
+    const int max_smem = 17 * 16 * 8 * MT * (int)sizeof(float);
+    cudaFuncSetAttribute(gemm_small_m_cluster_kernel<MT, float, XMODE, RESID>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (!RESID)
+      cudaFuncSetAttribute(gemm_small_m_cluster_kernel<MT, __nv_bfloat16, XMODE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    configured = true;
+  }
+  if (out_f32 || RESID) {
+    qe_launch_cluster(gemm_small_m_cluster_kernel<MT, float, XMODE, RESID>, dim3(ctas * S), dim3(warps * 32), smem, stream, (unsigned)S,
+                      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (float*)out, M, N, K, k_per_warp, k_per_cta, na);
+  } else {
+    qe_launch_cluster(gemm_small_m_cluster_kernel<MT, __nv_bfloat16, XMODE, false>, dim3(ctas * S), dim3(warps * 32), smem, stream, (unsigned)S,
+                      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, N, K, k_per_warp, k_per_cta, na);
+  }
+  QE_CHECK_LAUNCH("linear_small_m");
+  return 0;
+}
+
 template <int MT, int XMODE, bool RESID>
 static int launch_small_m(const void* x, const void* w, void* out, int M, int N, int K, int out_f32,
                           cudaStream_t stream, FuseArgs na) {
+  if (XMODE != X_NORM) {
+    const int S = small_m_cluster_size(N, K);
+    if (S > 1) return launch_small_m_cluster<MT, XMODE == X_NORM ? X_PLAIN : XMODE, RESID>(x, w, out, M, N, K, out_f32, S, stream, na);
+  }
   // warps split K in slices that are multiples of 64; more warps when there are few CTAs
   const int ctas = (N + 15) / 16;
   int warps = ctas >= 2048 ? 4 : (ctas >= 256 ? 8 : 16);
@@ -142,4 +214,57 @@ extern "C" int qe_linear_small_m_norm(const float* resid, const float* ssq, int 
   FuseArgs na{};
   na.resid = resid; na.ssq = ssq; na.norm_w = norm_w; na.n_ssq = n_ssq; na.ssq_ld = ssq_ld; na.eps = eps;
   return dispatch_small_m<X_NORM, false>(w, w, out, M, N, K, out_f32, stream, na);
+}
+
+// ---- gate and up projections with the activation in their epilogue -----------------------------------------------
+template <int MT>
+__global__ void __launch_bounds__(512)
+gemm_small_m_swiglu_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                           __nv_bfloat16* __restrict__ act, int M, int I, int K, int k_per_warp, FuseArgs na) {
+  extern __shared__ float red[];                    // 2 x [warps][16][8 MT]
+  if (na.next_bytes) {
+    const unsigned long long pieces = (na.next_bytes + 4095) >> 12;
+    const unsigned long long piece = (unsigned long long)threadIdx.x * gridDim.x + blockIdx.x;
+    if (piece < pieces) {
+      const unsigned long long off = piece << 12;
+      const unsigned size = (unsigned)min(4096ull, na.next_bytes - off) & ~15u;
+      if (size) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" :: "l"(na.next_w + off), "r"(size) : "memory");
+    }
+  }
+  pdl_launch_dependents();
+  gsm_cta_swiglu<MT>(x, w, act, M, I, K, k_per_warp, blockIdx.x, red);     // (waits for the kernel before it once its first weights are on their way)
+}
+
+// act[M, I] = silu(x · w[:I]^T) * (x · w[I:]^T) for the stacked weights w [2 I, K], M <= 16 rows, bfloat16: a CTA
+// takes the gate rows and the up rows of the same 16 columns, so the activation never exists as gate and up in memory.
+extern "C" int qe_linear_small_m_swiglu(const void* x, const void* w, void* act, int M, int I, int K, cudaStream_t stream) {
+  FuseArgs na{};
+  na.next_w = g_next_w;
+  na.next_bytes = g_next_bytes;
+  g_next_w = nullptr;
+  g_next_bytes = 0;
+  if (M <= 0 || I <= 0) return 0;
+  if (M > 16) QE_REFUSE("linear_small_m_swiglu: M = %d is above 16", M);
+  if (K <= 0 || K % 8) QE_REFUSE("linear_small_m_swiglu: K = %d is not a positive multiple of 8", K);
+  if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)act) & 15) QE_REFUSE("linear_small_m_swiglu: operands must be 16-byte aligned");
+  const int ctas = (I + 15) / 16;
+  int warps = ctas >= 1024 ? 4 : (ctas >= 128 ? 8 : 16);
+  int k_per_warp = ((K + warps - 1) / warps + 31) / 32 * 32;
+  warps = (K + k_per_warp - 1) / k_per_warp;
+  const int MT = M <= 8 ? 1 : 2;
+  const size_t smem = (size_t)2 * warps * 16 * 8 * MT * sizeof(float);
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(gemm_small_m_swiglu_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 16 * 16 * 8 * 4);
+    cudaFuncSetAttribute(gemm_small_m_swiglu_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 16 * 16 * 16 * 4);
+    configured = true;
+  }
+  if (MT == 1)
+    qe_launch(gemm_small_m_swiglu_kernel<1>, dim3(ctas), dim3(warps * 32), smem, stream, (const __nv_bfloat16*)x,
+              (const __nv_bfloat16*)w, (__nv_bfloat16*)act, M, I, K, k_per_warp, na);
+  else
+    qe_launch(gemm_small_m_swiglu_kernel<2>, dim3(ctas), dim3(warps * 32), smem, stream, (const __nv_bfloat16*)x,
+              (const __nv_bfloat16*)w, (__nv_bfloat16*)act, M, I, K, k_per_warp, na);
+  QE_CHECK_LAUNCH("linear_small_m_swiglu");
+  return 0;
 }

@@ -66,13 +66,13 @@ struct GsmChunk { uint4 a0, b0, a1, b1; };
 // slice of K.  They depend on nothing a kernel writes, so a caller issues them before it waits for
 // whatever produces the token operand (the previous kernel, or a grid barrier).
 __device__ __forceinline__ void gsm_prefetch(const __nv_bfloat16* __restrict__ w, int N, int K, int k_per_warp, int vb,
-                                             GsmChunk& c0, GsmChunk& c1) {
+                                             GsmChunk& c0, GsmChunk& c1, int k_off = 0, int k_len = 1 << 30) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
   const int n0 = vb * 16;
   const __nv_bfloat16* w0 = w + (size_t)min(n0 + g, N - 1) * K;
   const __nv_bfloat16* w1 = w + (size_t)min(n0 + g + 8, N - 1) * K;
-  const int kbeg = warp * k_per_warp, kend = min(K, kbeg + k_per_warp);
+  const int kbeg = k_off + warp * k_per_warp, kend = min(min(K, k_off + k_len), kbeg + k_per_warp);
   const uint4 zero = make_uint4(0, 0, 0, 0);
   auto load_chunk = [&](int k0, GsmChunk& ch) {
     const int ka = k0 + 8 * c, kb = k0 + 32 + 8 * c;
@@ -90,10 +90,15 @@ __device__ __forceinline__ void gsm_prefetch(const __nv_bfloat16* __restrict__ w
 // floats; c0, c1: what gsm_prefetch fetched for this vb.  Loads of everything a kernel may have
 // written bypass L1 (ld.global.cg), so the function may also run in a kernel that outlives the
 // producer of its operands.
-template <int MT, typename TOut, int XMODE, bool RESID>
+//
+// CLUSTER: the CTAs of a thread-block cluster share the 16 weight rows and take a share of K each (k_off, k_len:
+// this CTA's); their sums meet in the cluster's first CTA through distributed shared memory, in the order of the
+// CTAs, and that CTA alone writes the result.  For products whose weight rows are too few to give every SM a CTA.
+template <int MT, typename TOut, int XMODE, bool RESID, bool CLUSTER = false>
 __device__ __forceinline__ void gsm_cta(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                                         TOut* __restrict__ out, int M, int N, int K, int k_per_warp, const FuseArgs& na,
-                                        int vb, float* red, float* s_rstd, GsmChunk c0, GsmChunk c1) {
+                                        int vb, float* red, float* s_rstd, GsmChunk c0, GsmChunk c1, int k_off = 0,
+                                        int k_len = 1 << 30) {
   constexpr bool SILU = XMODE == X_SILU;
   constexpr bool NORM = XMODE == X_NORM;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
@@ -102,8 +107,9 @@ __device__ __forceinline__ void gsm_cta(const __nv_bfloat16* __restrict__ x, con
   const int r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1);     // clamped; discarded at the store
   const __nv_bfloat16* w0 = w + (size_t)r0 * K;
   const __nv_bfloat16* w1 = w + (size_t)r1 * K;
-  const int kbeg = warp * k_per_warp, kend = min(K, kbeg + k_per_warp);
+  const int kbeg = k_off + warp * k_per_warp, kend = min(min(K, k_off + k_len), kbeg + k_per_warp);
   const int x_ld = SILU ? 2 * K : K;
+  const bool writer = !CLUSTER || cluster_cta_rank() == 0;
 
   float acc[MT][4];
 #pragma unroll
@@ -159,7 +165,7 @@ __device__ __forceinline__ void gsm_cta(const __nv_bfloat16* __restrict__ x, con
     }
   };
   float resid_old = 0.f;                            // RESID: this thread's element of the stream, fetched early
-  if (RESID) {
+  if (RESID && writer) {
     const int m = threadIdx.x >> 4, n = n0 + (threadIdx.x & 15);
     if (threadIdx.x < 16 * 8 * MT && m < M && n < N) resid_old = __ldcg(reinterpret_cast<const float*>(out) + (size_t)m * N + n);
   }
@@ -195,20 +201,39 @@ __device__ __forceinline__ void gsm_cta(const __nv_bfloat16* __restrict__ x, con
     mine[(g + 8) * MW + t * 8 + 2 * c + 1] = acc[t][3];
   }
   __syncthreads();
+  float* part = red + (size_t)nwarps * 16 * MW;     // CLUSTER: this CTA's sums [16 MW], read by the cluster's first CTA
+  if (CLUSTER) {
+    for (int e = threadIdx.x; e < 16 * MW; e += blockDim.x) {
+      const int m = e >> 4, i = e & 15;
+      float s = 0.f;
+      for (int wi = 0; wi < nwarps; ++wi) s += red[((size_t)wi * 16 + i) * MW + m];
+      part[e] = s;
+    }
+    cluster_sync_all();                             // every CTA's sums are in place
+  }
+  if (writer)
   for (int e = threadIdx.x; e < 16 * MW; e += blockDim.x) {
     const int m = e >> 4, i = e & 15;               // consecutive threads: consecutive weight rows
     const int n = n0 + i;
+    // the sum over K: the warps' parts in order, or (CLUSTER) the CTAs' sums in order
+    auto total = [&]() {
+      float s = 0.f;
+      if (CLUSTER) {
+        const uint32_t S = cluster_num_ctas();
+        for (uint32_t r = 0; r < S; ++r) s += cluster_ld_f32(cluster_map_shared(&part[e], r));
+      } else {
+        for (int wi = 0; wi < nwarps; ++wi) s += red[((size_t)wi * 16 + i) * MW + m];
+      }
+      return s;
+    };
     if (!RESID) {
       if (m >= M || n >= N) continue;
-      float s = 0.f;
-      for (int wi = 0; wi < nwarps; ++wi) s += red[((size_t)wi * 16 + i) * MW + m];
-      out[(size_t)m * N + n] = from_f32<TOut>(s);
+      out[(size_t)m * N + n] = from_f32<TOut>(total());
     } else {
       // whole warps run this loop (16 MW is a multiple of 32); lanes outside the matrix add zero
       float v = 0.f;
       if (m < M && n < N) {
-        float s = 0.f;
-        for (int wi = 0; wi < nwarps; ++wi) s += red[((size_t)wi * 16 + i) * MW + m];
+        const float s = total();
         float* dst = reinterpret_cast<float*>(out) + (size_t)m * N + n;
         v = (e == threadIdx.x ? resid_old : __ldcg(dst)) + s;
         *dst = v;
@@ -220,6 +245,99 @@ __device__ __forceinline__ void gsm_cta(const __nv_bfloat16* __restrict__ x, con
       sq += __shfl_xor_sync(0xffffffffu, sq, 1);
       if (i == 0 && m < M) na.ssq_out[(size_t)m * na.ssq_ld + vb] = sq;
     }
+  }
+  if (CLUSTER) cluster_sync_all();                  // nobody reads this CTA's shared memory any more
+  QE_TL_MARK(3);
+}
+
+// The gate and up projections of a feed-forward and its activation in one: CTA `vb` takes the 16 gate rows from
+// 16 vb on AND the 16 up rows of the same columns (rows I + 16 vb ... of the stacked weights w [2 I, K]), and writes
+// act[m, n] = silu(g) * u for its 16 columns: g and u rounded to bfloat16 as if stored, silu in float32, rounded once
+// (reference src/models/qwen3/model.py:233-236, src/layers/fused_ops/silumul.py:50-53).  The token operand is loaded
+// once for both.  `red`: shared memory for 2 x (warps x 16 x 8 MT) floats.
+template <int MT>
+__device__ __forceinline__ void gsm_cta_swiglu(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                               __nv_bfloat16* __restrict__ act, int M, int I, int K, int k_per_warp,
+                                               int vb, float* red) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int g = lane >> 2, c = lane & 3;
+  const int n0 = vb * 16;
+  const int r0 = min(n0 + g, I - 1), r1 = min(n0 + g + 8, I - 1);     // clamped; discarded at the store
+  const __nv_bfloat16* wg0 = w + (size_t)r0 * K;
+  const __nv_bfloat16* wg1 = w + (size_t)r1 * K;
+  const __nv_bfloat16* wu0 = w + ((size_t)I + r0) * K;
+  const __nv_bfloat16* wu1 = w + ((size_t)I + r1) * K;
+  const int kbeg = warp * k_per_warp, kend = min(K, kbeg + k_per_warp);
+  float ag[MT][4], au[MT][4];
+#pragma unroll
+  for (int t = 0; t < MT; ++t)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { ag[t][i] = 0.f; au[t][i] = 0.f; }
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  struct Pair { uint4 ga, gb, ua, ub; };            // 32 k of the four rows
+  auto load_w = [&](int k) {
+    Pair p;
+    const int ka = k + 8 * c;
+    const bool ok = ka < kend;
+    p.ga = ok ? ld_stream16(wg0 + ka) : zero;
+    p.gb = ok ? ld_stream16(wg1 + ka) : zero;
+    p.ua = ok ? ld_stream16(wu0 + ka) : zero;
+    p.ub = ok ? ld_stream16(wu1 + ka) : zero;
+    return p;
+  };
+  // the weights are nobody's output: the first loads go out before the wait for the kernel before this one
+  Pair p0 = load_w(kbeg), p1 = load_w(kbeg + 32), p2 = load_w(kbeg + 64), p3 = load_w(kbeg + 96);
+  pdl_wait();
+  auto compute = [&](const Pair& p, int k) {
+    const int ka = k + 8 * c;
+#pragma unroll
+    for (int t = 0; t < MT; ++t) {
+      const int m = t * 8 + g;
+      const uint4 xa = (m < M && ka < kend) ? __ldcg(reinterpret_cast<const uint4*>(x + (size_t)m * K + ka)) : zero;
+      mma_bf16_16816(ag[t], p.ga.x, p.gb.x, p.ga.y, p.gb.y, xa.x, xa.y);
+      mma_bf16_16816(ag[t], p.ga.z, p.gb.z, p.ga.w, p.gb.w, xa.z, xa.w);
+      mma_bf16_16816(au[t], p.ua.x, p.ub.x, p.ua.y, p.ub.y, xa.x, xa.y);
+      mma_bf16_16816(au[t], p.ua.z, p.ub.z, p.ua.w, p.ub.w, xa.z, xa.w);
+    }
+  };
+  for (int k0 = kbeg; k0 < kend; k0 += 128) {
+    const Pair n0p = load_w(k0 + 128);
+    compute(p0, k0);
+    const Pair n1p = load_w(k0 + 160);
+    compute(p1, k0 + 32);
+    const Pair n2p = load_w(k0 + 192);
+    compute(p2, k0 + 64);
+    const Pair n3p = load_w(k0 + 224);
+    compute(p3, k0 + 96);
+    p0 = n0p; p1 = n1p; p2 = n2p; p3 = n3p;
+  }
+  QE_TL_MARK(2);
+  constexpr int MW = 8 * MT;
+  float* mine_g = red + (size_t)warp * 16 * MW;
+  float* mine_u = red + ((size_t)nwarps + warp) * 16 * MW;
+#pragma unroll
+  for (int t = 0; t < MT; ++t) {
+    mine_g[g * MW + t * 8 + 2 * c] = ag[t][0];
+    mine_g[g * MW + t * 8 + 2 * c + 1] = ag[t][1];
+    mine_g[(g + 8) * MW + t * 8 + 2 * c] = ag[t][2];
+    mine_g[(g + 8) * MW + t * 8 + 2 * c + 1] = ag[t][3];
+    mine_u[g * MW + t * 8 + 2 * c] = au[t][0];
+    mine_u[g * MW + t * 8 + 2 * c + 1] = au[t][1];
+    mine_u[(g + 8) * MW + t * 8 + 2 * c] = au[t][2];
+    mine_u[(g + 8) * MW + t * 8 + 2 * c + 1] = au[t][3];
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < 16 * MW; e += blockDim.x) {
+    const int m = e >> 4, i = e & 15;
+    const int n = n0 + i;
+    if (m >= M || n >= I) continue;
+    float sg = 0.f, su = 0.f;
+    for (int wi = 0; wi < nwarps; ++wi) {
+      sg += red[((size_t)wi * 16 + i) * MW + m];
+      su += red[((size_t)(nwarps + wi) * 16 + i) * MW + m];
+    }
+    const float gb = __bfloat162float(__float2bfloat16_rn(sg)), ub = __bfloat162float(__float2bfloat16_rn(su));
+    act[(size_t)m * I + n] = __float2bfloat16_rn(silu_fast(gb) * ub);
   }
   QE_TL_MARK(3);
 }

@@ -67,12 +67,6 @@ class ModelRunner:
         self.use_cuda_graphs = bool(use_cuda_graphs) and self._on_gpu and getattr(model, "capturable", True)
         # decode steps by shape: None after the first (eager) run, then (graph, logits, launches)
         self._graphs: dict[tuple, Optional[tuple]] = {}
-        # the recorded operations of such steps (ops.DecodeProgram segments), made on the eager run
-        self._programs: dict[tuple, list] = {}
-        # Off by default: measured on a B200 the program kernel is slower than the graph of launches
-        # (3.0 ms against 1.3 ms a step at batch 8): its grid barrier over 296 CTAs costs 2.5 us, as
-        # much as a dependent launch, and its products run at 8 warps a CTA.  Kept as a tested option.
-        self.use_decode_program = False
         self.capture_all_steps = True         # steps that are not all decoded tokens are captured too when they recur
         self.num_graph_replays = 0
         self.num_steps = 0
@@ -98,7 +92,6 @@ class ModelRunner:
             if self._dev_meta is None or self._dev_meta.numel() < n:
                 self._dev_meta = torch.empty(max(1 << 18, 2 * n), dtype=torch.int32, device=self.device)
                 self._graphs.clear()                  # captured steps point into the old buffer
-                self._programs.clear()
             dev = self._dev_meta[:n]
             dev.copy_(self._host[i][:n], non_blocking=True)
             ev = torch.cuda.Event()
@@ -109,50 +102,26 @@ class ModelRunner:
     def _forward(self, ctx: StepContext, graph_key) -> Optional[torch.Tensor]:
         if graph_key is None:
             return self.model.forward(ctx, self.cache)
-        # steps of a few rows in bfloat16: the operations are recorded as a program that one
-        # persistent kernel runs (ops.DecodeProgram); what cannot be recorded is launched as usual
-        program = (self.use_decode_program and self.dtype == torch.bfloat16
-                   and ctx.num_tokens <= ops.PROGRAM_MAX_M)
         if graph_key not in self._graphs:
-            # first time: run eagerly (also sizes the arena, and uploads the program's descriptors)
-            if program:
-                ops.program_begin(self.device)
-            try:
-                logits = self.model.forward(ctx, self.cache)
-                segments = ops.program_end() if program else None
-            except BaseException:
-                ops.program_abort()
-                raise
+            # first time: run eagerly (also sizes the arena)
+            logits = self.model.forward(ctx, self.cache)
             if not self.arena._overflow:                  # else the buffers move at the next reset: try again
                 self._graphs[graph_key] = None
-                if program:
-                    self._programs[graph_key] = segments
             return logits
         entry = self._graphs[graph_key]
         if entry is None:
             if len(self._graphs) > 512:                   # many shapes: drop the oldest captures
                 for k in list(self._graphs)[:256]:
                     del self._graphs[k]
-                    self._programs.pop(k, None)
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count
-            segments = self._programs.get(graph_key) if program else None
-            try:
-                with torch.cuda.graph(graph):
-                    if segments is not None:
-                        ops.program_begin(self.device, segments)
-                    logits = self.model.forward(ctx, self.cache)
-                    if segments is not None:
-                        ops.program_end()
-            except BaseException:
-                ops.program_abort()
-                raise
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(ctx, self.cache)
             entry = (graph, logits, ops.launch_count - before, self.arena.buffer)
             self._graphs[graph_key] = entry
         graph, logits, launches, arena_buffer = entry
         if arena_buffer is not self.arena.buffer:         # the arena grew since: record and capture again
             del self._graphs[graph_key]
-            self._programs.pop(graph_key, None)
             return self._forward(ctx, graph_key)
         graph.replay()
         ops.launch_count += launches
@@ -283,10 +252,9 @@ class ModelRunner:
         if graph_key is None and buckets is not None:
             # what decides the launches of a step that is not all decoded tokens: the rows of every request,
             # the widths of the block tables, the lengths of the work lists and what the plan says about
-            # them, and the one decision that is taken from the context lengths
+            # them
             graph_key = ("step", N, tuple(q_lens), buckets,
-                         tuple((k, tuple(v) if k.endswith("_info") else len(v)) for k, v in plan.items()),
-                         max(ctx_lens) <= ops.DECODE_ATTENTION_MAX_KEYS)
+                         tuple((k, tuple(v) if k.endswith("_info") else len(v)) for k, v in plan.items()))
         if fix_rows:        # last, so that the places of everything a captured step reads stay where they are
             pack.add("fix_rows", fix_rows)
             pack.add("fix_src", fix_src)

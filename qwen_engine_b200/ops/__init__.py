@@ -37,14 +37,7 @@ FLASH_BN = 64           # keys per tile of the flash kernel
 FLASH_ITEM_INTS = 12    # int32 per work item of the flash kernel
 FLASH_SPLIT = 256       # keys per part when a decoded token's context is split (reference attn.py:605)
 FLASH_TARGET_CTAS = 296  # two CTAs per SM: long contexts are split into as many parts as fit in one wave
-DECODE_ATTENTION = True         # decoded tokens (few rows per kv head, head size 128): the kernel made for them
-# Off: measured on a B200 at batch 8, context 1024, the step is 4 % slower with it (the attention kernel,
-# which the step waits for, grows by more than the rotary kernel's launch costs).  Kept as a tested option.
-FUSE_ROTARY_IN_DECODE = False   # the decode attention kernel norms and rotates q, k and writes the cache itself
 DECODE_ATTENTION_CLUSTERS = True    # parts of a request as a thread-block cluster that combines them through distributed shared memory
-DECODE_ATTENTION_MAX_ROWS = 2   # rows (token x head of the group) per item up to which it is used (measured: with 4 rows the mma.sync kernel is 11 % ahead; the kernel takes up to 4)
-DECODE_ATTENTION_MAX_KEYS = 512 # context up to which it serves contexts that are not split (longer: the pipelined kernel)
-DECODE_ATTENTION_MIN_CTAS = 128 # CTAs from which it is used: measured, it gains where the GPU is full and loses a little below
 DECODE_ATTENTION_MMA = True         # decoded tokens (up to 16 rows per kv head, head size 128): warps with key groups and pipelines of their own, mma.sync arithmetic
 DECODE_ATTENTION_MMA_MIN_CTAS = 0   # CTAs from which that kernel is used
 DECODE_ATTENTION_MMA_STAGES = 3     # key groups a warp of that kernel keeps in flight (2 or 3; measured: 3 is 2.5 % ahead in the step)
@@ -100,10 +93,7 @@ def _ptr(t: Optional[torch.Tensor]):
 
 
 def _stream():
-    """The current stream, for a launch.  Operations recorded for the decode program (see
-    ``DecodeProgram``) are launched first, so that the order of the step is kept."""
-    if _program is not None and _program.pending:
-        _program.flush()
+    """The current stream, for a launch."""
     if _raw_stream is not None:
         return ctypes.c_void_p(_raw_stream(_current_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
@@ -113,117 +103,6 @@ def _stream():
 # torch.cuda.current_stream() builds a Stream object per call, which costs more than a launch)
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 _current_device = getattr(torch._C, "_cuda_getDevice", None) or torch.cuda.current_device
-
-
-# ---- a decode step's operations as a program run by one persistent kernel -------------------------------
-_OP_FORMAT = "<ii14i2f4q10Q8x"          # type, work items, 14 ints, 2 floats, 4 int64, 10 pointers: 192 bytes
-_OP_GEMM, _OP_ROPE, _OP_ATTN = 1, 2, 3
-PROGRAM_MAX_M = 16                        # rows up to which a step's operations are recorded
-PROGRAM_WARPS = 8                         # warps of a CTA of the program kernel
-_program: Optional["DecodeProgram"] = None
-_program_barriers: dict = {}
-
-
-class ProgramMismatch(RuntimeError):
-    """A step recorded again differs from its first recording (its buffers moved)."""
-
-
-class DecodeProgram:
-    """Recorder of a decode step's operations (``program_begin`` .. ``program_end``).
-
-    While one is active, the products over a few rows, the fused rotary kernel and the decode
-    attention are not launched but written down as descriptors; ``flush`` (called before any other
-    launch and at the end) runs what is pending with ONE launch of a persistent cooperative kernel
-    that walks the list with grid barriers between operations (csrc/decode_program.cu).  The first
-    recording of a step's shape uploads the descriptors; later recordings (under CUDA graph
-    capture) must produce the same bytes and reuse the uploaded copy."""
-
-    def __init__(self, device, segments: Optional[list] = None):
-        self.device = torch.device(device)
-        self.pending: list[bytes] = []
-        self.reuse = segments is not None
-        self.segments: list = segments if segments is not None else []
-        self.index = 0
-        self._flushing = False
-
-    def add(self, op_type: int, n_items: int, ints=(), floats=(), longs=(), ptrs=()) -> None:
-        ints = list(ints) + [0] * (14 - len(ints))
-        floats = list(floats) + [0.0] * (2 - len(floats))
-        longs = list(longs) + [0] * (4 - len(longs))
-        ptrs = [0 if t is None else (t if isinstance(t, int) else t.data_ptr()) for t in ptrs]
-        ptrs += [0] * (10 - len(ptrs))
-        self.pending.append(struct.pack(_OP_FORMAT, op_type, int(n_items), *[int(v) for v in ints],
-                                        *[float(v) for v in floats], *[int(v) for v in longs], *ptrs))
-
-    def flush(self) -> None:
-        if not self.pending or self._flushing:
-            return
-        self._flushing = True
-        try:
-            blob, n = b"".join(self.pending), len(self.pending)
-            self.pending = []
-            if self.reuse:
-                if self.index >= len(self.segments) or self.segments[self.index][0] != blob:
-                    raise ProgramMismatch("the step's operations differ from their first recording")
-                dev = self.segments[self.index][1]
-            else:
-                dev = torch.frombuffer(bytearray(blob), dtype=torch.uint8).to(self.device)
-                self.segments.append((blob, dev, n))
-            self.index += 1
-            key = self.device.index
-            if key not in _program_barriers:
-                _program_barriers[key] = torch.zeros(4, dtype=torch.int32, device=self.device)
-            stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-            _check(lib().qe_run_decode_program(_ptr(dev), n, _ptr(_program_barriers[key]), stream), "decode_program")
-        finally:
-            self._flushing = False
-
-
-def program_begin(device, segments: Optional[list] = None) -> DecodeProgram:
-    global _program
-    assert lib().qe_program_op_bytes() == struct.calcsize(_OP_FORMAT)
-    _program = DecodeProgram(device, segments)
-    return _program
-
-
-def program_flush() -> None:
-    if _program is not None:
-        _program.flush()
-
-
-def program_end() -> list:
-    """Run what is pending, stop recording; returns the uploaded segments for later reuse."""
-    global _program
-    prog, _program = _program, None
-    if prog is None:
-        return []
-    prog.flush()
-    return prog.segments
-
-
-def program_abort() -> None:
-    global _program
-    _program = None
-
-
-def decode_program_status() -> int:
-    """0 if no grid barrier or tile wait of the program kernel ever ran out.  Synchronises the device."""
-    return int(lib().qe_decode_program_status())
-
-
-def _program_kpw(K: int) -> int:
-    return -(-(-(-K // PROGRAM_WARPS)) // 64) * 64
-
-
-def _record_gemm(x, w, out, M, N, K, xmode, resid, out_f32, norm=None, ssq_out=None, ssq_ld=0) -> bool:
-    if _program is None or M > PROGRAM_MAX_M:
-        return False
-    n_resid, n_ssq, n_w, eps, n_ssq_n, n_ld = None, None, None, 0.0, 0, ssq_ld
-    if norm is not None:
-        n_resid, n_ssq, n_w, eps, n_ssq_n, n_ld = norm
-    _program.add(_OP_GEMM, -(-N // 16), ints=[M, N, K, _program_kpw(K), xmode, int(resid), int(out_f32), n_ssq_n, n_ld],
-                 floats=[eps], ptrs=[x, w, out, n_resid, n_ssq, n_w, ssq_out])
-    return True
 
 
 launch_count = 0        # kernels launched through this module since import (read by the benchmark)
@@ -408,9 +287,6 @@ def _linear_normed(x: NormedInput, w: torch.Tensor, out: torch.Tensor) -> bool:
         return False
     _need(w.shape == (N, K) and out.shape == (M, N) and out.dtype in (torch.bfloat16, torch.float32)
           and w.is_contiguous() and out.is_contiguous(), "linear: operands do not fit the normed input")
-    if _record_gemm(w, w, out, M, N, K, 2, False, out.dtype == torch.float32,
-                    norm=(st.resid, st.ssq, x.weight, x.eps, int(st.n_ssq), int(st.ssq.shape[1]))):
-        return True
     _check(lib().qe_linear_small_m_norm(_ptr(st.resid), _ptr(st.ssq), int(st.n_ssq), int(st.ssq.shape[1]),
                                         _ptr(x.weight), ctypes.c_float(x.eps), _ptr(w), _ptr(out), M, N, K,
                                         int(out.dtype == torch.float32), _stream()), "linear")
@@ -421,7 +297,7 @@ def splitk_splits(M: int, N: int, K: int, dtype: torch.dtype) -> int:
     """How many CTAs share a tile of 128 weight rows, each with a share of K, in the product of some tens
     of rows (``linear_splitk``): as many of 8, 4, 2 as keep all clusters on the GPU at once; 0 where that
     kernel does not apply (few rows, enough weight rows for every SM, other types)."""
-    if not (TCGEN05_ENABLED and SPLITK and _program is None and dtype == torch.bfloat16
+    if not (TCGEN05_ENABLED and SPLITK and dtype == torch.bfloat16
             and SPLITK_MIN_M <= M <= SPLITK_MAX_M and K % 8 == 0 and N % 4 == 0):
         return 0
     tiles = -(-N // 128)
@@ -462,10 +338,9 @@ def _linear_into_stream(x: torch.Tensor, w: torch.Tensor, sink: ResidualSink, si
             and st.resid.shape == (M, N)):
         return False
     _need(w.shape == (N, K) and x.is_contiguous() and w.is_contiguous(), "linear: operands do not fit")
-    if not _record_gemm(x, w, st.resid, M, N, K, 1 if silu else 0, True, True, ssq_out=st.ssq, ssq_ld=int(st.ssq.shape[1])):
-        _hand_over_next_weights()
-        _check(lib().qe_linear_small_m_resid(_ptr(x), _ptr(w), _ptr(st.resid), _ptr(st.ssq), int(st.ssq.shape[1]),
-                                             M, N, K, int(silu), _stream()), "linear")
+    _hand_over_next_weights()
+    _check(lib().qe_linear_small_m_resid(_ptr(x), _ptr(w), _ptr(st.resid), _ptr(st.ssq), int(st.ssq.shape[1]),
+                                         M, N, K, int(silu), _stream()), "linear")
     st.n_ssq = -(-N // 16)
     return True
 
@@ -518,14 +393,12 @@ def linear(x, w: torch.Tensor, out: torch.Tensor) -> None:
         linear_splitk(x, w, out, splits)
         return
     if (x.dtype == torch.bfloat16 and SWAP_MIN_M <= M <= SMALL_M_MAX and N >= SWAP_MIN_N and K % 8 == 0
-            and TCGEN05_ENABLED and _program is None):
+            and TCGEN05_ENABLED):
         # some tens of rows and many weight rows: the weights on the 128-row side of tcgen05.mma
         _check(lib().qe_linear_tcgen05_swap(_ptr(x), _ptr(w), _ptr(out), M, N, K, out_f32, _stream()), "linear")
         return
     if x.dtype == torch.bfloat16 and M <= SMALL_M_MAX and K % 8 == 0:
         # a few rows: stream every weight once through the tensor cores
-        if _record_gemm(x, w, out, M, N, K, 0, False, out_f32):
-            return
         _hand_over_next_weights()
         _check(lib().qe_linear_small_m(_ptr(x), _ptr(w), _ptr(out), M, N, K, out_f32, _stream()), "linear")
         return
@@ -575,6 +448,31 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -
                                                int(out.dtype == torch.float32), _stream()), "linear_swiglu")
 
 
+SWIGLU_SMALL_MAX_M = 16     # rows up to which the weight-streaming product forms the activation in its epilogue
+
+
+def swiglu_small_applies(M: int, I: int, K: int, dtype: torch.dtype) -> bool:
+    """Whether ``linear_swiglu_small`` serves this shape: a few rows in bfloat16."""
+    return dtype == torch.bfloat16 and 1 <= M <= SWIGLU_SMALL_MAX_M and K % 8 == 0
+
+
+def linear_swiglu_small(x, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, I] = silu(x · w[:I]^T) * (x · w[I:]^T) for the stacked weights w [2 I, K] and a few rows (decode steps):
+    a CTA streams the gate rows and the up rows of the same 16 columns and forms the activation in its epilogue, so
+    that gate and up never exist in memory and the product that follows reads half the bytes, already activated."""
+    if isinstance(x, NormedInput):
+        x = x.materialize()
+    M, K = x.shape
+    I = w_gate_up.shape[0] // 2
+    _need(x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and w_gate_up.shape == (2 * I, K) and K % 8 == 0,
+          "linear_swiglu_small: bfloat16 operands, w [2 I, K] with K a multiple of 8")
+    _need(out.shape == (M, I) and out.dtype == torch.bfloat16 and M <= SWIGLU_SMALL_MAX_M,
+          f"linear_swiglu_small: out must be bfloat16 [M, I] with M <= {SWIGLU_SMALL_MAX_M}")
+    _need(x.is_contiguous() and w_gate_up.is_contiguous() and out.is_contiguous(), "linear_swiglu_small: operands must be contiguous")
+    _hand_over_next_weights()
+    _check(lib().qe_linear_small_m_swiglu(_ptr(x), _ptr(w_gate_up), _ptr(out), M, I, K, _stream()), "linear_swiglu_small")
+
+
 QKV_ROPE_FUSED = True       # many rows: per-head norm, rotation and cache write in the epilogue of the QKV product
 QKV_ROPE_MIN_TILES = 74     # 256 x 256 tiles of the product from which it is used (one per pair of SMs)
 
@@ -582,7 +480,7 @@ QKV_ROPE_MIN_TILES = 74     # 256 x 256 tiles of the product from which it is us
 def qkv_rope_fused_applies(M: int, N: int, K: int, dtype: torch.dtype, head_dim: int, rotary_dim: int) -> bool:
     """Whether ``linear_qkv_rope`` serves this shape: bfloat16, head size 128 rotated as a whole, and
     enough 256 x 256 tiles for every pair of SMs (the kernel is the CTA-pair product)."""
-    return (QKV_ROPE_FUSED and TCGEN05_PAIRS and TCGEN05_ENABLED and _program is None and dtype == torch.bfloat16
+    return (QKV_ROPE_FUSED and TCGEN05_PAIRS and TCGEN05_ENABLED and dtype == torch.bfloat16
             and head_dim == 128 and rotary_dim == 128 and K % 8 == 0 and N % 128 == 0
             and M > SMALL_M_MAX and -(-M // 256) * -(-N // 256) >= QKV_ROPE_MIN_TILES)
 
@@ -640,8 +538,6 @@ def linear_silu_mul(gate_up: torch.Tensor, w: torch.Tensor, out: torch.Tensor, s
     _need(out.shape == (M, N) and out.dtype in (gate_up.dtype, torch.float32), "linear_silu_mul: out must be [M, N]")
     _need(gate_up.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "linear_silu_mul: operands must be contiguous")
     if gate_up.dtype == torch.bfloat16 and M <= SMALL_M_MAX and I % 8 == 0:
-        if _record_gemm(gate_up, w, out, M, N, I, 1, False, out.dtype == torch.float32):
-            return
         _hand_over_next_weights()
         _check(lib().qe_linear_small_m_silu(_ptr(gate_up), _ptr(w), _ptr(out), M, N, I,
                                             int(out.dtype == torch.float32), _stream()), "linear_silu_mul")
@@ -810,13 +706,6 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, q_norm_w: 
     if inv_freq is not None:
         _need(inv_freq.dtype == torch.float32 and inv_freq.numel() == rotary_dim // 2,
               "qk_norm_rope_kv_write: inv_freq must be float32 [rotary_dim / 2]")
-    if (_program is not None and T <= PROGRAM_MAX_M and qkv.dtype == torch.bfloat16 and D == 128
-            and (inv_freq is None or rotary_dim == D) and stride % 4 == 0):
-        _program.add(_OP_ROPE, -(-T * (Hq + 2 * Hkv) // PROGRAM_WARPS), ints=[T, Hq, Hkv, page_size, int(bool(write_kv))],
-                     floats=[eps], longs=[stride, stride, stride],
-                     ptrs=[q.data_ptr(), k.data_ptr(), v.data_ptr(), positions, q_norm_w, k_norm_w, inv_freq,
-                           kv_pages if write_kv else None, slot_mapping if write_kv else None])
-        return
     _check(lib().qe_qk_norm_rope_kv_write(
         ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(k.data_ptr()), ctypes.c_void_p(v.data_ptr()),
         ctypes.c_long(stride), ctypes.c_long(stride), ctypes.c_long(stride), _ptr(positions),
@@ -996,18 +885,6 @@ def _merge_counters(device, kernel: str = "fa") -> torch.Tensor:
     return t
 
 
-def _decode_kernel_serves(plan, key, ctx, qkv: torch.Tensor, Hkv: int, D: int) -> bool:
-    """Whether the whole step's attention (geometry index ``key`` of the plan) goes to the kernel for
-    decoded tokens: few rows per item, head size 128, enough CTAs to fill the GPU, contexts split or short."""
-    if not DECODE_ATTENTION or key is None or f"fa{key}_items" not in plan or f"tc{key}_items" in plan or D != 128:
-        return False
-    n_parts, part_rows, small_tiles, max_rows, same_parts = plan[f"fa{key}_info_host"]
-    n_items = plan[f"fa{key}_items"].numel() // FLASH_ITEM_INTS
-    return (1 <= max_rows <= DECODE_ATTENTION_MAX_ROWS and n_items > 0 and n_items * Hkv >= DECODE_ATTENTION_MIN_CTAS
-            and n_parts * Hkv <= _MERGE_COUNTERS and qkv.stride(0) % 8 == 0
-            and (n_parts > 0 or max(getattr(ctx, "ctx_lens_host", None) or [0]) <= DECODE_ATTENTION_MAX_KEYS))
-
-
 def _decode_mma_serves(plan, key, qkv: torch.Tensor, Hq: int, Hkv: int, D: int) -> bool:
     """Whether the whole step's attention (geometry index ``key`` of the plan) goes to the tensor-core kernel
     for decoded tokens: items of at most 16 rows, head size 128, none on the tcgen05 kernel."""
@@ -1019,29 +896,13 @@ def _decode_mma_serves(plan, key, qkv: torch.Tensor, Hq: int, Hkv: int, D: int) 
             and n_parts * Hkv <= _MERGE_COUNTERS and qkv.stride(0) % 8 == 0)
 
 
-def attention_fuses_rotary(qkv: torch.Tensor, ctx, num_heads: int, num_kv_heads: int, head_dim: int, window: int,
-                           rotary_dim: int) -> bool:
-    """Whether ``paged_attention`` can take q, k, v as the QKV product left them and do the per-head norm,
-    the rotation and the cache write itself (``fused=``): a decode step served by the kernel for decoded
-    tokens, one token per request, the whole head rotated."""
-    if not FUSE_ROTARY_IN_DECODE or _program is not None or rotary_dim != head_dim or ctx.dtype != torch.bfloat16:
-        return False
-    if any(n != 1 for n in ctx.q_lens_host):
-        return False
-    plan = ctx.attn_plan
-    key = plan.get("geometry_index", {}).get((num_heads, num_kv_heads, head_dim, window))
-    return _decode_kernel_serves(plan, key, ctx, qkv, num_kv_heads, head_dim)
-
-
 def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: torch.Tensor, ctx,
                     out: torch.Tensor, scale: float, window: int, num_heads: int, num_kv_heads: int,
-                    head_dim: int, fused: Optional[dict] = None, next_pages: Optional[torch.Tensor] = None) -> None:
+                    head_dim: int, next_pages: Optional[torch.Tensor] = None) -> None:
     """Attention of the step's queries (the q part of qkv [T, (Hq+2Hkv) D]) over the keys and values
     of their requests in ``kv_pages``; out [T, Hq D].  ``ctx`` is the StepContext (cu_q, ctx_lens,
     the plan that ``plan_attention`` made, and the arena for the parts of split contexts).
 
-    ``fused`` (only where ``attention_fuses_rotary`` said yes): q_norm_w, k_norm_w, eps, inv_freq,
-    write_kv of the per-head norm, rotation and cache write that this call then does itself.
     ``next_pages``: the cache of the layer that runs after this one, if it has the same shape (the same
     pages at the same places): a decode step's kernel may ask L2 for that layer's keys and values."""
     Hq, Hkv, D = num_heads, num_kv_heads, head_dim
@@ -1079,26 +940,8 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
             part_acc = ctx.arena.alloc((n_parts * Hkv * part_rows, D), torch.float32)
             part_ml = ctx.arena.alloc((n_parts * Hkv * part_rows, 2), torch.float32)
         counters = _merge_counters(qkv.device) if 0 < n_parts * Hkv <= _MERGE_COUNTERS else None
-        if (_program is not None and T <= PROGRAM_MAX_M and D == 128 and small_tiles and n_items > 0
-                and (n_parts == 0 or counters is not None) and qkv.stride(0) % 8 == 0):
-            _program.add(_OP_ATTN, n_items * Hkv,
-                         ints=[n_items, Hkv, Hq, int(kv_pages.shape[3]), int(block_tables.shape[1]), int(part_rows), int(window)],
-                         floats=[scale * 1.4426950408889634], longs=[qkv.stride(0)],
-                         ptrs=[qkv, kv_pages, block_tables, items, out, part_acc, part_ml, counters])
-            return
-        serves = _decode_kernel_serves(plan, key, ctx, qkv, Hkv, D)
         # every request in the same few parts: the parts of a request form a cluster and meet on chip
         cluster = int(same_parts) if DECODE_ATTENTION_CLUSTERS and n_items == n_parts else 0
-        _need(fused is None or serves, "paged_attention: this step cannot take the rotation into the attention kernel")
-        if fused is not None:
-            last_attention_kernel = "decode_attention_fused"
-            _check(lib().qe_decode_attention_fused(
-                _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(block_tables), int(block_tables.shape[1]),
-                _ptr(items), n_items, _ptr(out), _ptr(part_acc), _ptr(part_ml), int(part_rows), _ptr(counters),
-                int(max_rows), cluster, ctypes.c_float(scale), int(window), _ptr(fused["q_norm_w"]), _ptr(fused["k_norm_w"]),
-                ctypes.c_float(fused["eps"]), _ptr(fused["inv_freq"]), int(bool(fused["write_kv"])),
-                Hq, Hkv, D, int(kv_pages.shape[3]), _stream()), "decode_attention_fused")
-            return
         if _decode_mma_serves(plan, key, qkv, Hq, Hkv, D):
             # decoded tokens: every warp streams key groups of its own through the tensor cores
             last_attention_kernel = "decode_attention_mma"
@@ -1116,15 +959,6 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
                 int(max_rows), cluster, int(DECODE_ATTENTION_MMA_WIDE and n_items * Hkv <= TC_TARGET_CTAS),
                 ctypes.c_float(scale), int(window), Hq, Hkv, D, int(kv_pages.shape[3]), _stream()),
                 "decode_attention_mma")
-            return
-        if serves:
-            # a few rows per kv head (decoded tokens): the kernel without matrix instructions
-            last_attention_kernel = "decode_attention"
-            _check(lib().qe_decode_attention(
-                _ptr(qkv), ctypes.c_long(qkv.stride(0)), _ptr(kv_pages), _ptr(block_tables), int(block_tables.shape[1]),
-                _ptr(items), n_items, _ptr(out), _ptr(part_acc), _ptr(part_ml), int(part_rows), _ptr(counters),
-                int(max_rows), cluster, ctypes.c_float(scale), int(window), Hq, Hkv, D, int(kv_pages.shape[3]), _stream()),
-                "decode_attention")
             return
         last_attention_kernel = "flash_attention"
         _check(lib().qe_flash_attention_fused_merge(

@@ -97,13 +97,6 @@ class GQAAttention(Mixer):
                 return
         ops.prefetch_next(self.w_o)
         ops.linear(x, self.w_qkv, qkv)
-        if fused_rope and ops.attention_fuses_rotary(qkv, ctx, H, Hkv, D, self.window or 0, rot.rotary_dim):
-            # a decode step: the attention kernel norms and rotates q and k and writes the cache itself
-            ops.paged_attention(qkv, cache, view.block_tables, ctx, attn, self.scale, self.window or 0, H, Hkv, D,
-                                fused=dict(q_norm_w=self.q_norm_w, k_norm_w=self.k_norm_w, eps=self.qk_norm_eps or 0.0,
-                                           inv_freq=rot.inv_freq, write_kv=write_cache))
-            ops.linear(attn, self.w_o, out)
-            return
         if self.pos is not None and not fused_rope:
             # another position encoding: norm first (the order of model.py:204-208),
             # then the part's own rotation, then the plain cache write

@@ -45,6 +45,15 @@ class SwiGLU(FeedForward):
             ops.linear_swiglu(x, self.w_gate_up, act)
             ops.linear(act, self.w_down, out)
             return
+        if ops.swiglu_small_applies(T, I, self.hidden_size, ctx.dtype):
+            # a few rows: the product that streams the gate and up weights forms the activation itself
+            act = ctx.arena.alloc((T, I), ctx.dtype)
+            ops.prefetch_next(self.w_down)
+            ops.linear_swiglu_small(x, self.w_gate_up, act)
+            ops.prefetch_next(step_hint(ctx, "weights_after_ffn"))
+            ops.linear(act, self.w_down, out)
+            ops.prefetch_next(None)
+            return
         gate_up = ctx.arena.alloc((T, 2 * I), ctx.dtype)
         ops.prefetch_next(self.w_down)
         ops.linear(x, self.w_gate_up, gate_up)

@@ -185,45 +185,6 @@ def test_command_line(model_folders):
     assert float(rows["prefill"][3]) > 0 and float(rows["decode"][3]) > 0
 
 
-def test_decode_program_agrees_with_separate_launches(tmp_path):
-    """Decode steps of a few rows in bfloat16 can run as one persistent kernel that walks the step's
-    recorded operations (ops.DecodeProgram, an option of the step function that is off by default);
-    with the recorder off the same operations are separate launches.  Both must give the same logits (up to the order of float32 sums), over many steps,
-    with contexts that grow across pages and parts, for 1 to 9 requests."""
-    from qwen_engine_b200 import ops
-    from qwen_engine_b200.engine.loading import load_model
-    from qwen_engine_b200.engine.runner import StepEntry
-    from qwen_engine_b200.registry import config_from_dict
-    from qwen_engine_b200.weights import write_model_folder
-    raw = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=3, hidden_size=256, num_attention_heads=4,
-               num_key_value_heads=2, head_dim=128, intermediate_size=384, vocab_size=1000, rope_theta=1e6,
-               rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=4096)
-    folder = write_model_folder(config_from_dict(raw), str(tmp_path / "m"), seed=5, std=0.05, norm_std=0.1)
-    results = {}
-    for use_program in (True, False):
-        loaded = load_model(folder, torch.bfloat16, "cuda:0", 16, 256, 12, enable_prefix_cache=False)
-        runner, cache = loaded.runner, loaded.cache
-        runner.use_decode_program = use_program
-        lens = [300, 5, 64, 257, 31, 700, 1, 16, 90]
-        reqs = [cache.open(i) for i in range(len(lens))]
-        for rc, n in zip(reqs, lens):
-            runner.step([StepEntry(rc, random_tokens(1000, n, 40 + n), [])])
-        rows = []
-        for step in range(40):
-            live = reqs[:1 + step % len(reqs)] if step < 20 else reqs
-            logits = runner.step([StepEntry(rc, [(7 * step + 3 * i) % 1000], [0]) for i, rc in enumerate(live)])
-            rows.append(logits.float().cpu().clone())
-        torch.cuda.synchronize()
-        results[use_program] = torch.cat(rows)
-        if use_program:
-            assert runner._programs, "no step was recorded as a program"
-            assert ops.decode_program_status() == 0, "a barrier of the program kernel ran out"
-    a, b = results[True], results[False]
-    assert torch.isfinite(a).all()
-    scale = max(1.0, float(b.abs().max()))
-    assert float((a - b).abs().max()) <= 1e-2 * scale
-
-
 @pytest.mark.parametrize("fused", [True, False])
 def test_norm_and_rotation_with_head_size_128(tmp_path, monkeypatch, fused):
     """Prompt portions of many rows with head size 128 in bfloat16 take their rotation angles from a table that

@@ -459,15 +459,14 @@ def test_flash_attention_split_contexts(Hq, Hkv, D, P, q_lens, ctx_lens):
     _close(got, want, dtype)
 
 
-@pytest.fixture(params=["mma", "mma4", "plain"])
+@pytest.fixture(params=["mma", "mma4"])
 def decode_kernel(request):
-    """Which kernel for decoded tokens ``ops.paged_attention`` picks: the one whose warps stream key groups
-    through mma.sync (with CTAs of 8 warps where they are few; mma4: always 4 warps), or the one without
-    matrix instructions."""
-    saved = ops.DECODE_ATTENTION_MMA, ops.DECODE_ATTENTION_MMA_WIDE
-    ops.DECODE_ATTENTION_MMA, ops.DECODE_ATTENTION_MMA_WIDE = request.param != "plain", request.param == "mma"
+    """Which form of the kernel for decoded tokens ``ops.paged_attention`` picks: CTAs of 8 warps where they are
+    few (mma), or always 4 warps (mma4)."""
+    saved = ops.DECODE_ATTENTION_MMA_WIDE
+    ops.DECODE_ATTENTION_MMA_WIDE = request.param == "mma"
     yield request.param
-    ops.DECODE_ATTENTION_MMA, ops.DECODE_ATTENTION_MMA_WIDE = saved
+    ops.DECODE_ATTENTION_MMA_WIDE = saved
 
 
 @pytest.mark.parametrize("Hq,Hkv,P", [(16, 8, 16), (4, 4, 8), (8, 2, 32), (4, 1, 16), (6, 3, 4), (2, 1, 256)])
@@ -485,18 +484,16 @@ def test_decode_attention(Hq, Hkv, P, q_lens, ctx_lens, window, decode_kernel):
     case = _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, seed=41)
     want = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ref_ops.paged_attention, "cpu")
     launches = ops.launch_count
-    saved = ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_KEYS, ops.DECODE_ATTENTION_MAX_ROWS
-    # whatever the size of the case, and up to the 4 rows the kernel takes
-    ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_KEYS, ops.DECODE_ATTENTION_MAX_ROWS = 1, 1 << 30, 4
+    got = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ops.paged_attention, DEV)
+    assert ops.last_attention_kernel == "decode_attention_mma"
+    _close(got, want, dtype)
+    saved = ops.DECODE_ATTENTION_MMA
+    ops.DECODE_ATTENTION_MMA = False
     try:
-        got = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ops.paged_attention, DEV)
-        _close(got, want, dtype)
-        ops.DECODE_ATTENTION, mma = False, ops.DECODE_ATTENTION_MMA
-        ops.DECODE_ATTENTION_MMA = False
         other = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ops.paged_attention, DEV)
     finally:
-        ops.DECODE_ATTENTION, ops.DECODE_ATTENTION_MMA = True, mma
-        ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_KEYS, ops.DECODE_ATTENTION_MAX_ROWS = saved
+        ops.DECODE_ATTENTION_MMA = saved
+    assert ops.last_attention_kernel == "flash_attention"
     _close(other, want, dtype)
     assert ops.launch_count == launches + 2
 
@@ -517,63 +514,14 @@ def test_decode_attention_parts_in_clusters(Hq, Hkv, P, ctx_lens, parts, window,
     assert plan["fa0_info"][4] == parts and plan["fa0_info"][0] == parts * len(ctx_lens)
     case = _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, seed=45)
     want = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ref_ops.paged_attention, "cpu")
-    saved = ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_ROWS
-    ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_ROWS = 1, 4
     try:
         got = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ops.paged_attention, DEV, uniform=parts)
         ops.DECODE_ATTENTION_CLUSTERS = False
         other = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ops.paged_attention, DEV, uniform=parts)
     finally:
         ops.DECODE_ATTENTION_CLUSTERS = True
-        ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_ROWS = saved
     _close(got, want, dtype)
     assert torch.equal(got, other)
-
-
-@pytest.mark.parametrize("Hq,Hkv,P", [(16, 8, 16), (4, 4, 8), (8, 2, 32), (4, 1, 16)])
-@pytest.mark.parametrize("ctx_lens", [[77], [5, 130, 333], [1024] * 8, [0, 159, 160, 161, 319, 320, 63, 64]])
-@pytest.mark.parametrize("norm", [True, False])
-@pytest.mark.parametrize("write_kv", [True, False])
-def test_decode_attention_with_rotary_fused(Hq, Hkv, P, ctx_lens, norm, write_kv):
-    """A decode step in which the attention kernel itself norms and rotates q and k and writes the
-    new keys and values into the cache: outputs and cache against the plain rotary step followed
-    by plain attention.  write_kv off: a layer that reads another layer's cache, which holds the
-    new token already."""
-    D, dtype, window = 128, torch.bfloat16, 0
-    q_lens = [1] * len(ctx_lens)
-    case = _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, seed=43)
-    g = torch.Generator().manual_seed(44)
-    qw = (1.0 + 0.2 * torch.randn(D, generator=g)) if norm else None
-    kw = (1.0 + 0.2 * torch.randn(D, generator=g)) if norm else None
-    inv_freq = (10000.0 ** (-torch.arange(0, D, 2, dtype=torch.float32) / D))
-    positions = torch.tensor(ctx_lens, dtype=torch.int32)
-    slots = torch.tensor([int(case["table"][r, c // P]) * P + c % P for r, c in enumerate(ctx_lens)], dtype=torch.int32)
-    # the plain way on the CPU: rotary step (writes the cache), then attention
-    qkv_ref, cache_ref = case["qkv"].clone(), case["cache"].clone()
-    ref_ops.qk_norm_rope_kv_write(qkv_ref, positions, qw, kw, 1e-6, inv_freq, D, cache_ref, slots, Hq, Hkv, D)
-    ref_case = dict(case, qkv=qkv_ref, cache=cache_ref)
-    want = _run_attention(ref_case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ref_ops.paged_attention, "cpu")
-    # the kernel: raw q, k, v; the cache without the new token (or, write_kv off, with it)
-    cache_gpu = (case["cache"] if write_kv else cache_ref).clone().to(DEV)
-    fused = dict(q_norm_w=qw.to(DEV) if norm else None, k_norm_w=kw.to(DEV) if norm else None, eps=1e-6,
-                 inv_freq=inv_freq.to(DEV), write_kv=write_kv)
-    saved = ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_KEYS, ops.DECODE_ATTENTION_MAX_ROWS
-    ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_KEYS, ops.DECODE_ATTENTION_MAX_ROWS = 1, 1 << 30, 4
-    try:
-        gpu_case = dict(case, cache=cache_gpu)
-        got = _run_attention(gpu_case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window,
-                             lambda *a: ops.paged_attention(*a, fused=fused), DEV)
-    finally:
-        ops.DECODE_ATTENTION_MIN_CTAS, ops.DECODE_ATTENTION_MAX_KEYS, ops.DECODE_ATTENTION_MAX_ROWS = saved
-    _close(got, want, dtype)
-    # the cache: the new token's key and value where the rotary kernel would have put them, nothing else touched
-    assert torch.equal(cache_gpu.cpu()[:, 1], cache_ref[:, 1])
-    _close(cache_gpu.cpu()[:, 0], cache_ref[:, 0], dtype, tol16=8e-3)
-    changed = (cache_gpu.cpu() != case["cache"]).any(dim=-1)          # [pages, 2, Hkv, P]
-    if write_kv:
-        assert int(changed.sum()) <= 2 * Hkv * len(ctx_lens)
-    else:
-        assert torch.equal(cache_gpu.cpu(), cache_ref)
 
 
 @pytest.mark.parametrize("Hq,Hkv,P", [(16, 1, 16), (32, 4, 16), (8, 1, 8), (12, 3, 4), (5, 1, 32)])
@@ -645,18 +593,13 @@ def test_decode_attention_far_key_stands_out(key_pos, decode_kernel):
     Hq, Hkv, D, P = 4, 2, 128, 16
     dtype = torch.bfloat16
     q_lens, ctx_lens = [1, 1], [900, 760]
-    saved = ops.DECODE_ATTENTION_MIN_CTAS
-    ops.DECODE_ATTENTION_MIN_CTAS = 1
-    try:
-        for r, head in ((0, 1), (1, 2)):
-            if key_pos > ctx_lens[r]:
-                continue
-            case = _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, seed=42, spike=(r, key_pos, head))
-            got = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, ops.paged_attention, DEV)
-            want = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, ref_ops.paged_attention, "cpu")
-            _close(got, want, dtype)
-    finally:
-        ops.DECODE_ATTENTION_MIN_CTAS = saved
+    for r, head in ((0, 1), (1, 2)):
+        if key_pos > ctx_lens[r]:
+            continue
+        case = _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, seed=42, spike=(r, key_pos, head))
+        got = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, ops.paged_attention, DEV)
+        want = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, 0, ref_ops.paged_attention, "cpu")
+        _close(got, want, dtype)
 
 
 TC_SHAPES = [(16, 8, 128, 16), (4, 4, 128, 8), (8, 1, 128, 32), (4, 2, 128, 128), (2, 1, 128, 256)]
@@ -834,3 +777,46 @@ def test_a_bounded_wait_that_runs_out():
         want = big_x.float() @ w.float().t()
         assert float((got.float() - want).abs().max()) <= 2e-2 * float(want.abs().max())
     assert ops.tcgen05_status() == 0
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 9, 16])
+@pytest.mark.parametrize("I,K", [(3072, 1024), (200, 72), (1032, 264), (16, 8), (9728, 2560)])
+def test_linear_swiglu_small(M, I, K):
+    """The gate and up projections of a few rows with the activation formed in the product's epilogue (a CTA takes
+    the gate rows and the up rows of the same 16 columns), against the plain operations: product, rounding to
+    bfloat16, silu(g) * u in float32.  Widths that are no multiple of a warp's share of K, columns no multiple of 16."""
+    x = _randn((M, K), torch.bfloat16, 1)
+    w = _randn((2 * I, K), torch.bfloat16, 2, K ** -0.5)
+    gu = (x.float() @ w.float().t()).to(torch.bfloat16).float()
+    want = (torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]).to(torch.bfloat16)
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert ops.swiglu_small_applies(M, I, K, torch.bfloat16)
+    ops.linear_swiglu_small(x.to(DEV), w.to(DEV), out)
+    _close(out, want, torch.bfloat16)
+
+
+@pytest.mark.parametrize("M", [1, 8, 13, 40])
+@pytest.mark.parametrize("N,K", [(1024, 2048), (1024, 3072), (1000, 1032), (592, 4096), (100, 2064), (1184, 1024)])
+@pytest.mark.parametrize("mode", ["bf16", "f32", "stream"])
+def test_linear_small_m_shares_k_in_clusters(M, N, K, mode, monkeypatch):
+    """Weight matrices of few rows: the CTAs of a cluster share 16 weight rows and a part of K each, and meet in
+    distributed shared memory (2 or 4 CTAs, chosen from the weight matrix alone).  Plain output, float32 output, and
+    the add into the residual stream with the sums of squares left behind."""
+    monkeypatch.setattr(ops, "SPLITK", False)              # (the tcgen05 kernel for some tens of rows is tested elsewhere)
+    x = _randn((M, K), torch.bfloat16, 3)
+    w = _randn((N, K), torch.bfloat16, 4, K ** -0.5)
+    want = x.float() @ w.float().t()
+    if mode == "stream":
+        resid = _randn((M, N), torch.float32, 5)
+        stream = ops.ResidualStream.for_step(lambda shape, dtype: torch.zeros(shape, dtype=dtype, device=DEV), M, N, torch.bfloat16)
+        stream.resid.copy_(resid)
+        ops.linear(x.to(DEV), w.to(DEV), ops.ResidualSink(stream))
+        assert not stream.has_delta and stream.n_ssq == -(-N // 16)
+        got = stream.resid.cpu()
+        _close(got, resid + want, torch.bfloat16)
+        ssq = stream.ssq[:, :stream.n_ssq].sum(dim=1).cpu()
+        assert torch.allclose(ssq, (got * got).sum(dim=1), rtol=1e-4)
+    else:
+        out = torch.empty(M, N, dtype=torch.float32 if mode == "f32" else torch.bfloat16, device=DEV)
+        ops.linear(x.to(DEV), w.to(DEV), out)
+        _close(out, want, torch.bfloat16)
