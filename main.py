@@ -34,6 +34,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--max-model-len", type=int, default=256)
     ap.add_argument("--block-size", type=int, default=16)
     ap.add_argument("--num-blocks", type=int, default=None, help="default: max_num_seqs * ceil(max_model_len / block_size)")
+    ap.add_argument("--gpu-memory-fraction", type=float, default=None,
+                    help="without --num-blocks: size the cache from what this share of the device's memory leaves after the weights")
     ap.add_argument("--max-num-batched-tokens", type=int, default=2048)
     ap.add_argument("--prefill-chunk", type=int, default=None, help="largest portion of a prompt in one step")
     ap.add_argument("--no-prefix-cache", action="store_true")
@@ -88,7 +90,7 @@ def main(argv=None) -> int:
         return 2
 
     llm = LLM(model, dtype=parse_dtype(args.dtype), device=args.device, block_size=block_size,
-              num_blocks=args.num_blocks, max_model_len=args.max_model_len, max_num_seqs=args.max_num_seqs,
+              num_blocks=args.num_blocks, gpu_memory_fraction=args.gpu_memory_fraction, max_model_len=args.max_model_len, max_num_seqs=args.max_num_seqs,
               max_num_batched_tokens=args.max_num_batched_tokens, prefill_chunk_size=args.prefill_chunk,
               enable_prefix_cache=not args.no_prefix_cache, run_ahead=not args.no_run_ahead, seed=args.sample_seed,
               profile=args.profile)

@@ -33,7 +33,8 @@ class EngineConfig:
     dtype: torch.dtype = torch.bfloat16
     device: str = "cuda:0"
     block_size: int = 16                  # tokens in a page (main.py:22)
-    num_blocks: Optional[int] = None      # pages per cache group; None: from max_num_seqs*max_model_len
+    num_blocks: Optional[int] = None      # pages per cache group; None: from gpu_memory_fraction, else max_num_seqs*max_model_len
+    gpu_memory_fraction: Optional[float] = None   # with num_blocks None: the cache takes what is left of this share of the device's memory
     max_model_len: int = 256              # most tokens one request may hold (main.py:21)
     max_num_seqs: int = 4                 # most live requests (main.py:20)
     max_num_batched_tokens: int = 2048    # token budget of one step
@@ -56,13 +57,18 @@ class EngineConfig:
             raise ValueError("max_num_batched_tokens must be >= 1")
         if self.prefill_chunk_size is not None and self.prefill_chunk_size < 1:
             raise ValueError("prefill_chunk_size must be >= 1")
+        if self.gpu_memory_fraction is not None and not (0.0 < self.gpu_memory_fraction <= 1.0):
+            raise ValueError("gpu_memory_fraction must be in (0, 1]")
 
     @property
     def blocks_per_seq(self) -> int:
         return -(-self.max_model_len // self.block_size)
 
-    def resolved_num_blocks(self) -> int:
-        """main.py:23: ``max_num_seqs * ceil(max_model_len / block_size)``."""
+    def resolved_num_blocks(self) -> Optional[int]:
+        """The number of pages per cache group: ``num_blocks`` if given; None if the loader is to size the cache
+        from ``gpu_memory_fraction``; else main.py:23: ``max_num_seqs * ceil(max_model_len / block_size)``."""
         if self.num_blocks is not None:
             return self.num_blocks
+        if self.gpu_memory_fraction is not None:
+            return None
         return self.max_num_seqs * self.blocks_per_seq

@@ -320,14 +320,15 @@ class LLM:
         ec = self.engine_config
         if isinstance(model, str):
             loaded = load_model(model, ec.dtype, ec.device, ec.block_size, ec.resolved_num_blocks(),
-                                ec.max_num_seqs, ec.enable_prefix_cache, use_cuda_graphs=ec.use_cuda_graphs)
+                                ec.max_num_seqs, ec.enable_prefix_cache, use_cuda_graphs=ec.use_cuda_graphs,
+                                gpu_memory_fraction=ec.gpu_memory_fraction)
             tokenizer = tokenizer or _load_tokenizer(model)
         else:
             loaded = load_model(None, ec.dtype, ec.device, ec.block_size, ec.resolved_num_blocks(),
                                 ec.max_num_seqs, ec.enable_prefix_cache, config=model,
                                 random_seed=ec.seed if weights_seed is None else weights_seed,
                                 random_std=weights_std, random_norm_std=weights_norm_std,
-                                use_cuda_graphs=ec.use_cuda_graphs)
+                                use_cuda_graphs=ec.use_cuda_graphs, gpu_memory_fraction=ec.gpu_memory_fraction)
         self.engine = LLMEngine(loaded, ec, tokenizer)
 
     def generate(self, prompts, sampling_params: Union[SamplingParams, Seq[SamplingParams], None] = None

@@ -229,3 +229,21 @@ def test_norm_and_rotation_with_head_size_128(tmp_path, monkeypatch, fused):
     scale = max(1.0, float(want.abs().max()))
     for other in got[1:]:
         assert float((got[0] - other).abs().max()) <= 2e-2 * scale
+
+
+def test_cache_sized_from_a_share_of_the_devices_memory(model_folders):
+    """``gpu_memory_fraction`` instead of ``num_blocks``: the cache takes what that share of the device's memory
+    leaves after the weights and a reserve; generation is what it is with any other cache size."""
+    from qwen_engine_b200 import LLM
+    name = "tiny-a"
+    folder = model_folders[name]
+    prompt = random_tokens(helpers.vocab_of(name), 9, 75)
+    free, total = torch.cuda.mem_get_info()
+    llm = LLM(folder, dtype="float32", block_size=helpers.TINY[name]["page"], max_model_len=64, gpu_memory_fraction=0.05)
+    group = llm.engine.cache.paged_groups[0]
+    page_bytes = group.tensor[:, 0].numel() * group.tensor.element_size()
+    assert 0.01 * total < group.pool.num_pages * page_bytes <= 0.05 * total
+    out = llm.generate([prompt], SamplingParams(max_new_tokens=6))[0]
+    assert out.output_token_ids == _plain_greedy(folder, prompt, 6)
+    del llm
+    torch.cuda.empty_cache()
