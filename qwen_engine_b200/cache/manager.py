@@ -89,10 +89,11 @@ class CacheManager:
             g.cache_slots.append(slot_id)
             self.group_of_slot[slot_id] = (g.index, len(g.cache_slots) - 1)
         paged = [g for g in self.groups if g.is_paged]
-        # A prefix can be shared only if every group can hand it over: all keys kept,
-        # and no state that would have to be rebuilt.
-        self.prefix_cache = bool(enable_prefix_cache and paged and all(
-            g.is_paged and g.spec.window is None for g in self.groups))
+        # A prefix can be shared if every group can hand over what the next query needs of it: a group that keeps
+        # all keys, every page of the prefix; a group that keeps a window of keys, the pages its window still
+        # reaches (pages it gave back stay findable until they are handed out again).  State of fixed size cannot
+        # be handed over (that would take snapshots of it at page boundaries): a model that has some shares nothing.
+        self.prefix_cache = bool(enable_prefix_cache and paged and all(g.is_paged for g in self.groups))
         for g in self.groups:
             if g.is_paged:
                 n = (num_pages_of_group or {}).get(g.index, num_pages)
@@ -173,15 +174,35 @@ class CacheManager:
             # n pages count as n P tokens computed, or, when they are the whole of ``tokens``, as one less
             cap = max(0, max_shared_tokens)
             limit = limit if (limit * P == len(tokens) and len(tokens) - 1 <= cap) else min(limit, cap // P)
-        matches = {g.index: g.pool.match_prefix(tokens, limit) for g in self.paged_groups}
-        n_pages = min(len(pages) for pages, _ in matches.values())
+        if limit == 0:
+            return
+        # the chained hashes of the leading full blocks (the same for every group), and what each group can find
+        hashes: list[int] = []
+        for b in range(limit):
+            hashes.append(hash_block(hashes[-1] if hashes else 0, tokens[b * P:(b + 1) * P]))
+        found = {g.index: [g.pool.find_page(hashes[b], tokens[b * P:(b + 1) * P]) for b in range(limit)]
+                 for g in self.paged_groups}
+
+        def first_needed(g: CacheGroup, n: int) -> int:
+            """The first block of a prefix of n pages that the group's next query still reads."""
+            if g.spec.window is None:
+                return 0
+            pos = n * P - 1 if n * P == len(tokens) else n * P       # the next token to run (the last one again on a full hit)
+            return max(0, pos - g.spec.window + 1) // P
+
+        n_pages = 0
+        for n in range(limit, 0, -1):                    # the longest prefix that every group can hand over
+            if all(all(found[g.index][b] is not None for b in range(first_needed(g, n), n)) for g in self.paged_groups):
+                n_pages = n
+                break
         if n_pages == 0:
             return
         for g in self.paged_groups:
-            pages, hashes = matches[g.index]
-            for p in pages[:n_pages]:
+            first = first_needed(g, n_pages)
+            pages = [-1] * first + [found[g.index][b] for b in range(first, n_pages)]
+            for p in pages[first:]:
                 g.pool.retain(p)
-            rc.tables[g.index] = list(pages[:n_pages])
+            rc.tables[g.index] = pages
             rc.hashes[g.index] = list(hashes[:n_pages])
         shared = n_pages * P
         if shared == len(tokens):

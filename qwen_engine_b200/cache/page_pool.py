@@ -147,6 +147,16 @@ class PagePool:
             parent = h
         return pages, hashes
 
+    def find_page(self, block_hash: int, block_tokens: Sequence[int]) -> Optional[int]:
+        """The findable page that answers to a block's chained hash and holds exactly its tokens, or None.
+        Nothing is retained."""
+        if not self.enable_prefix_cache:
+            return None
+        page = self._page_of_hash.get(block_hash)
+        if page is None or self._tokens_of_page.get(page) != tuple(int(t) for t in block_tokens):
+            return None
+        return page
+
     # ---- checks for tests ---------------------------------------------------------------
     def check_invariants(self, held: Optional[dict[int, int]] = None) -> None:
         """Every page is in exactly one place; with ``held`` (page -> holders as

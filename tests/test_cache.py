@@ -61,7 +61,7 @@ def test_groups_by_need_have_pages_of_their_own():
     assert cm.groups[0].tensor.shape == (2, 10, 2, 2, 4, 8)
     assert cm.groups[2].tensor.shape == (1, 3, 3, 5)
     assert cm.layer_view(2).shape == (10, 2, 2, 4, 8) and cm.layer_view(4) is None
-    assert not cm.prefix_cache                        # a window and a state rule sharing out
+    assert not cm.prefix_cache                        # state of fixed size cannot be handed over: nothing is shared
     rc = cm.open("a")
     _feed(cm, rc, list(range(9)))
     assert len(rc.tables[0]) == 3 and len(rc.tables[1]) == 3 and len(rc.tables[3]) == 3
@@ -265,3 +265,79 @@ def test_random_orders_keep_every_page_accounted_for(seed, prefix):
         cm.close(rc)
     cm.check_invariants()
     assert cm.pages_in_use() == 0 and cm.slots.num_free == 5
+
+
+def test_a_group_that_keeps_a_window_shares_what_its_window_still_reaches():
+    """Two groups, one keeping all keys and one keeping a window of 6: a second request with the same 16-token
+    prefix gets every page of the prefix in the first group and, in the windowed group, only the pages the next
+    query still reads (the earlier entries of its table stay -1); pages the first request already gave back are
+    found again as long as nobody has taken them.  When a needed page of the windowed group is gone, the shared
+    prefix shrinks to what both groups can hand over."""
+    specs = [PagedKVSpec(1, 8), PagedKVSpec(1, 8, window=6)]
+    cm = CacheManager(specs, 4, 12, 3, F32, "cpu", num_pages_of_group={1: 6})
+    assert cm.prefix_cache
+    prefix = list(range(100, 116))
+    a = cm.open("a", known_tokens=prefix + [1, 2, 3, 4])
+    _feed(cm, a, prefix + [1, 2, 3, 4])               # 20 tokens: the window (next query at 20) reaches back to key 15
+    assert a.tables[1][:3] == [-1, -1, -1] and all(p >= 0 for p in a.tables[0])
+    b = cm.open("b", known_tokens=prefix + [9, 9])
+    assert b.num_tokens == 16 and b.shared_tokens == 16
+    assert b.tables[0] == a.tables[0][:4]
+    # the next query (position 16) reads keys 11..: blocks 2 and 3; block 2 is a page that a gave back, found again
+    assert b.tables[1][:2] == [-1, -1] and b.tables[1][2] >= 0 and b.tables[1][3] == a.tables[1][3]
+    cm.check_invariants()
+    _feed(cm, b, [9, 9])
+    cm.check_invariants()
+    cm.close(b)
+    # take pages until the freed, findable ones of the windowed group are handed out again: block 2 is gone
+    hog = cm.open("hog")
+    assert cm.groups[1].pool.num_free == 4            # one page never shared, three that a gave back and that are still findable
+    _feed(cm, hog, list(range(500, 516)))
+    c = cm.open("c", known_tokens=prefix + [7])
+    assert c.num_tokens == 0, "without block 2 of the windowed group nothing of the prefix can be handed over whole"
+    cm.check_invariants()
+    for rc in (a, hog, c):
+        cm.close(rc)
+    assert cm.pages_in_use() == 0
+    cm.check_invariants()
+
+
+def test_random_requests_with_a_windowed_group_keep_the_books_right():
+    """Random opens, appends and closes over two groups (all keys / a window) with shared prefixes: after every
+    action no page is lost, held twice or freed twice, and a request's shared prefix is never longer than what it
+    asked for."""
+    import random
+    rng = random.Random(5)
+    cm = CacheManager([PagedKVSpec(1, 8), PagedKVSpec(1, 8, window=9)], 4, 40, 6, F32, "cpu")
+    stems = [[rng.randrange(50) for _ in range(24)] for _ in range(3)]
+    live = {}
+    for step in range(400):
+        action = rng.random()
+        if action < 0.35 and len(live) < 5:
+            toks = rng.choice(stems)[:rng.choice([8, 12, 16, 24])] + [rng.randrange(50) for _ in range(rng.randrange(1, 6))]
+            try:
+                rc = cm.open(step, known_tokens=toks)
+            except OutOfPages:
+                continue
+            assert rc.num_tokens < len(toks) and rc.num_tokens % 4 in (0, 3)
+            live[step] = (rc, toks)
+        elif action < 0.8 and live:
+            key = rng.choice(list(live))
+            rc, toks = live[key]
+            rest = toks[rc.num_tokens:] or [rng.randrange(50)]
+            n = rng.randrange(1, len(rest) + 1)
+            try:
+                cm.append(rc, rest[:n])
+            except OutOfPages:
+                continue
+            cm.commit(rc)
+            if rc.num_tokens >= len(toks):
+                live[key] = (rc, rc.tokens + [rng.randrange(50)])
+        elif live:
+            key = rng.choice(list(live))
+            cm.close(live.pop(key)[0])
+        cm.take_page_copies()
+        cm.check_invariants()
+    for rc, _ in live.values():
+        cm.close(rc)
+    assert cm.pages_in_use() == 0

@@ -525,7 +525,7 @@ def test_windowed_layer_gives_pages_back_and_still_agrees(dtype):
         tensors = _weights(model.weight_manifest(), 21)
         model.load_weights(DictSource(tensors), dtype, DEV)
         cm = CacheManager(model.cache_specs(), 4, 48, 2, dtype, DEV, poison=True)
-        assert [g.spec.window for g in cm.groups] == [None, 11] and not cm.prefix_cache
+        assert [g.spec.window for g in cm.groups] == [None, 11] and cm.prefix_cache
         runner = ModelRunner(model, cm, DEV, dtype)
         tokens = [(13 * i + 5) % cfg.vocab_size for i in range(150)]
         want = _window_toy_plain(cfg, {n: t.float() for n, t in tensors.items()}, tokens)
@@ -542,7 +542,22 @@ def test_windowed_layer_gives_pages_back_and_still_agrees(dtype):
             cm.check_invariants()
         assert p == len(tokens) and rc.tables[1][0] == -1 and all(pg >= 0 for pg in rc.tables[0])
         _close(torch.cat(rows), want, dtype, "windowed layer")
+        # a second request with the same first 40 tokens shares them: every page in the group that keeps all keys, and
+        # in the windowed group the pages its window still reaches (the first request gave them back long ago; they
+        # are found again because nobody has taken them since)
+        other = tokens[:40] + [(7 * i + 3) % cfg.vocab_size for i in range(30)]
+        want2 = _window_toy_plain(cfg, {n: t.float() for n, t in tensors.items()}, other)
+        rc2 = cm.open("s", known_tokens=other, max_shared_tokens=len(other) - 1)
+        assert rc2.shared_tokens == 40 and rc2.tables[0] == rc.tables[0][:10]
+        assert rc2.tables[1][:7] == [-1] * 7 and all(pg >= 0 for pg in rc2.tables[1][7:])
+        rows, p = [], 40
+        for n in [5, 1, 1, 23]:
+            rows.append(runner.step([StepEntry(rc2, other[p:p + n], list(range(n)))]).float().cpu().clone())
+            p += n
+            cm.check_invariants()
+        _close(torch.cat(rows), want2[40:], dtype, "windowed layer, shared prefix")
         cm.close(rc)
+        cm.close(rc2)
         assert cm.pages_in_use() == 0
     finally:
         del ARCHITECTURES["WindowToyForCausalLM"]
