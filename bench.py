@@ -331,13 +331,12 @@ def kernel_chains(loaded, cfg, peaks, tag, ctx, torch, ops, out) -> None:
     if not dec and ops.swiglu_fused_applies(T, I, H, bf):
         us = chain(lambda: [ops.linear_swiglu(x, f.w_gate_up, act) for f in ffns])
         record(f"{tag}_gate_up_swiglu", us, flops=2.0 * T * 2 * I * H)
+    elif dec and ops.swiglu_small_applies(T, I, H, bf):
+        us = chain(lambda: [ops.linear_swiglu_small(x, f.w_gate_up, act) for f in ffns])
+        record(f"{tag}_gate_up_swiglu", us, nbytes=2 * I * H * 2)
     else:
         products("gate_up", [f.w_gate_up for f in ffns], x, y_gu, 2 * I, H)
-    if dec and I <= ops.FUSED_SILU_MAX_K:
-        us = chain(lambda: [ops.linear_silu_mul(gate_up, f.w_down, y_h, None) for f in ffns])
-        record(f"{tag}_down_silu", us, nbytes=H * I * 2)
-    else:
-        products("down", [f.w_down for f in ffns], act, y_h, H, I)
+    products("down", [f.w_down for f in ffns], act, y_h, H, I)
 
     def attention():
         for i, m in enumerate(mixers):
