@@ -60,9 +60,50 @@ argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
   if (threadIdx.x == 0) out[blockIdx.x] = bi;
 }
 
+// A long row shared by the AM_CLUSTER CTAs of a cluster: each takes a contiguous share of the row, the first
+// CTA reads the others' results from their shared memory in rank order (lower shares hold lower indices, so
+// "larger, or equal and earlier" keeps the lowest index on a tie).  One CTA reads a row of 150 000 logits in
+// some tens of microseconds; eight take a few.
+#define AM_CLUSTER 8
+#define AM_MIN_V 16384     // rows at least this long go to the clusters
+
+__global__ void __launch_bounds__(SM_THREADS)
+argmax_cluster_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
+  __shared__ float sv[33];
+  __shared__ int si[33];
+  __shared__ float res_v;
+  __shared__ int res_i;
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t rank = cluster_cta_rank();
+  const int row = blockIdx.y;
+  const int share = (V + AM_CLUSTER - 1) / AM_CLUSTER;
+  const int lo = min(V, (int)rank * share), hi = min(V, lo + share);
+  float bv; int bi;
+  block_argmax(logits + (size_t)row * V + lo, hi - lo, bv, bi, sv, si);
+  if (threadIdx.x == 0) { res_v = hi > lo ? bv : -INFINITY; res_i = lo + bi; }
+  cluster_sync_all();
+  if (rank == 0 && threadIdx.x == 0) {
+    float best = res_v;
+    int at = res_i;
+    for (uint32_t r = 1; r < AM_CLUSTER; ++r) {
+      const float v = cluster_ld_f32(cluster_map_shared(&res_v, r));
+      const int i = __float_as_int(cluster_ld_f32(cluster_map_shared(&res_i, r)));
+      if (v > best) { best = v; at = i; }
+    }
+    out[row] = at;
+  }
+  cluster_sync_all();     // the others' shared memory stays until it has been read
+}
+
 extern "C" int qe_argmax(const float* logits, int* out, int N, int V, cudaStream_t stream) {
   if (N <= 0) return 0;
   if (V <= 0) QE_REFUSE("argmax: empty vocabulary");
+  if (V >= AM_MIN_V && N <= 65535) {
+    qe_launch_cluster(argmax_cluster_kernel, dim3(AM_CLUSTER, N), dim3(SM_THREADS), 0, stream, AM_CLUSTER, logits, out, V);
+    QE_CHECK_LAUNCH("argmax");
+    return 0;
+  }
   qe_launch(argmax_kernel, dim3(N), dim3(SM_THREADS), 0, stream, logits, out, V);
   QE_CHECK_LAUNCH("argmax");
   return 0;

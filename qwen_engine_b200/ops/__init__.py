@@ -853,6 +853,9 @@ def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
     return plan
 
 
+DECODE_CLUSTER4_MAX_SPAN = 4096   # keys up to which 4 parts in a cluster are preferred to more parts merged through memory
+
+
 def decode_splits(num_reqs: int, max_tokens: int, geometries, dtype: torch.dtype) -> dict:
     """The fixed number of parts per request for a decode step of ``num_reqs`` requests whose block
     tables hold up to ``max_tokens`` tokens: enough parts to fill the GPU, none shorter than a split."""
@@ -865,7 +868,22 @@ def decode_splits(num_reqs: int, max_tokens: int, geometries, dtype: torch.dtype
                 and Hq // Hkv <= 16 and num_reqs * Hkv <= TC_TARGET_CTAS):
             target = TC_TARGET_CTAS                                       # one CTA of 8 warps per SM
         want = max(1, target // max(1, num_reqs * Hkv))                   # all parts run in one wave
-        out[geo] = max(1, min(want, -(-span // FLASH_SPLIT)))
+        parts = max(1, min(want, -(-span // FLASH_SPLIT)))
+        if target == TC_TARGET_CTAS and DECODE_ATTENTION_CLUSTERS and parts > 2:
+            # 2, 4 or 8 parts of a request form a thread-block cluster and meet on chip, which beats the merge through
+            # global memory (measured at 0.6B sizes, context 1 024: 2 requests in 4 parts each 0.80 ms a step, in 5
+            # parts 0.95); clusters of 8 only while all of them still fit the GPU at once (at most 8 of them: 0.95 ms
+            # with 16 of them) or where 4 parts would be long ones
+            few = num_reqs * Hkv * 8 <= 64
+            if parts == 3:
+                parts = 4 if num_reqs * Hkv * 4 <= target else 2
+            elif parts < 8:
+                parts = 8 if few else 4
+            elif few or (parts == 8 and span > DECODE_CLUSTER4_MAX_SPAN):
+                parts = 8
+            elif span <= DECODE_CLUSTER4_MAX_SPAN:
+                parts = 4
+        out[geo] = parts
     return out
 
 

@@ -710,14 +710,18 @@ def test_paged_attention_far_key_stands_out(dtype, key_pos):
         assert float((out - value).abs().max()) < 0.05, "the far key's value did not come through"
 
 
-@pytest.mark.parametrize("V", [5, 389, 151936])
+@pytest.mark.parametrize("V", [5, 389, 16383, 16384, 20011, 151936])
 def test_argmax(V):
+    """Short rows by one CTA, long ones by a cluster whose CTAs take a share of the row each: the largest at
+    either end, ties across and within shares, a row of equal values."""
     logits = _randn((6, V), torch.float32, 30)
     logits[1, V - 1] = 50.0
     logits[2, 0] = 50.0
     logits[3, V // 2] = 9.0
     logits[3, V // 3] = 9.0          # a tie: the lower index wins
     logits[3].clamp_(max=9.0)
+    logits[4] = -3.5                 # all equal: index 0
+    logits[5, V - 2:] = 40.0         # a tie between the last two
     want = torch.empty(6, dtype=torch.int32)
     ref_ops.argmax(logits, want)
     got = torch.empty(6, dtype=torch.int32, device=DEV)
