@@ -77,12 +77,16 @@ class LLMEngine:
     runs until every queued request has ended (the reference's loop,
     llm_engine.py:101-152).
 
-    With ``EngineConfig.run_ahead`` a decode step is launched before the host has read the tokens of
-    the step before it: its token ids stay on the device, the requests' outputs hold a place for them
-    (``UNKNOWN_TOKEN``), and ``step`` returns what the older of the two steps produced.  A request
-    that turns out to have ended (a stop token) while the step launched ahead carried it loses that
-    step's token; one that ends by a count is known beforehand and is not carried.  Only steady
-    decoding runs ahead: nothing waiting, every running request getting a token, pages at hand."""
+    With ``EngineConfig.run_ahead`` a step is scheduled and launched before the host has read the tokens
+    of the step before it, so that the host's work on a step (scheduling, the work lists, the launches)
+    overlaps the device's work on the one before: the token ids that decoding requests need stay on the
+    device, the requests' outputs hold a place for them (``UNKNOWN_TOKEN``), and ``step`` returns what
+    the older of the two steps produced.  Prompt portions and admissions need no token of the step in
+    flight and go into the step launched ahead as into any other.  A request that turns out to have
+    ended (a stop token) while the step launched ahead carried it loses that step's token; one that
+    ends by a count is known beforehand and is not carried.  A step launched ahead never preempts: a
+    request that finds no pages sits it out, and when nothing can run the next step is scheduled with
+    the tokens read, preemption allowed."""
 
     def __init__(self, loaded: LoadedModel, engine_config: EngineConfig, tokenizer=None):
         self.loaded = loaded
@@ -190,26 +194,12 @@ class LLMEngine:
         p["device_ms"] += float(cur.events[0].elapsed_time(cur.events[1]))
 
     def _can_run_ahead(self, cur: _Flight) -> bool:
-        """Steady decoding: nothing waits, every running request gets a token from the step in
-        flight, and those that go on find their pages without anyone being preempted."""
-        sch = self.scheduler
-        if not self.config.run_ahead or sch.waiting or not cur.wanting or len(cur.wanting) != len(sch.running):
+        """Whether the next step may be scheduled and launched before the tokens of ``cur`` are read: the
+        requests that get a token from it are all still running (their next token's id is then taken
+        from the device)."""
+        if not self.config.run_ahead:
             return False
-        if any(not s.wants_logits for s in cur.out.scheduled):
-            return False
-        need: dict[int, int] = {}
-        go_on = 0
-        for s in cur.wanting:
-            if s.seq.status is not SequenceStatus.RUNNING or s.seq.cache is None:
-                return False
-            if sch.ends_by_length_after(s.seq, 1):
-                continue
-            go_on += 1
-            for g, n in self.cache.pages_needed(s.seq.cache, 1).items():
-                need[g] = need.get(g, 0) + n
-        if go_on == 0:
-            return False
-        return all(n <= self.cache.groups[g].pool.num_free for g, n in need.items())
+        return all(s.seq.status is SequenceStatus.RUNNING and s.seq.cache is not None for s in cur.wanting)
 
     def step(self) -> list[Sequence]:
         """Schedule, run and sample one batch; returns the requests that ended in the step whose
@@ -231,9 +221,9 @@ class LLMEngine:
                 seq.hold = self.scheduler.ends_by_length_after(seq, 1)
                 placed[seq.seq_id] = seq.output_len
                 seq.output_token_ids.append(UNKNOWN_TOKEN)
-            ahead = self.scheduler.schedule()
-            if ahead.preempted or ahead.admitted:
-                raise RuntimeError("a step launched ahead must not preempt or admit")
+            ahead = self.scheduler.schedule(may_preempt=False)
+            if ahead.preempted:
+                raise RuntimeError("a step launched ahead must not preempt")
             self._flight = self._launch(ahead, cur)
         sampled: dict[int, int] = {}
         if cur.tokens is not None:

@@ -11,6 +11,7 @@ on the host and copied once.
 """
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass, field
 from typing import Optional, Sequence
 
@@ -67,6 +68,7 @@ class ModelRunner:
         self.use_cuda_graphs = bool(use_cuda_graphs) and self._on_gpu and getattr(model, "capturable", True)
         # decode steps by shape: None after the first (eager) run, then (graph, logits, launches)
         self._graphs: dict[tuple, Optional[tuple]] = {}
+        self._capture_stream = None
         self.capture_all_steps = True         # steps that are not all decoded tokens are captured too when they recur
         self.num_graph_replays = 0
         self.num_steps = 0
@@ -115,8 +117,28 @@ class ModelRunner:
                     del self._graphs[k]
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count
-            with torch.cuda.graph(graph):
-                logits = self.model.forward(ctx, self.cache)
+            # captured on a stream of its own between capture_begin and capture_end: the context manager that torch
+            # offers for this also collects garbage and empties the allocator's cache on entry, some tens of
+            # milliseconds that a serving loop which meets new shapes all the time cannot afford.  What the
+            # collection is there for is kept: no cyclic garbage is collected while the capture runs (an old
+            # graph or device buffer destroyed then would invalidate the capture).
+            if self._capture_stream is None:
+                self._capture_stream = torch.cuda.Stream(device=self.device)
+            main = torch.cuda.current_stream(self.device)
+            self._capture_stream.wait_stream(main)
+            collecting = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.stream(self._capture_stream):
+                    graph.capture_begin()
+                    try:
+                        logits = self.model.forward(ctx, self.cache)
+                    finally:
+                        graph.capture_end()
+            finally:
+                if collecting:
+                    gc.enable()
+            main.wait_stream(self._capture_stream)
             entry = (graph, logits, ops.launch_count - before, self.arena.buffer)
             self._graphs[graph_key] = entry
         graph, logits, launches, arena_buffer = entry

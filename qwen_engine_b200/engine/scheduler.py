@@ -85,7 +85,9 @@ class Scheduler:
         return bool(self.waiting or self.running)
 
     # ---- one decision ---------------------------------------------------------------------
-    def schedule(self) -> SchedulerOutput:
+    def schedule(self, may_preempt: bool = True) -> SchedulerOutput:
+        """``may_preempt`` False (a step launched while the one before it is still in flight): a running
+        request that finds no pages is left out of the step instead of making room by preemption."""
         out = SchedulerOutput()
         budget = self.max_num_batched_tokens
         reserved: dict[int, int] = {g.index: 0 for g in self.cache.paged_groups}
@@ -108,11 +110,13 @@ class Scheduler:
             if budget <= 0:
                 break
             n = min(seq.num_remaining_tokens, self.prefill_chunk_size, budget)
-            while not reserve(seq, n):
+            fits = reserve(seq, n)
+            while not fits and may_preempt:
                 victim = self._preempt_newest(out, reserved)
                 if victim is seq:
                     break
-            if seq.status is not SequenceStatus.RUNNING:
+                fits = reserve(seq, n)
+            if not fits or seq.status is not SequenceStatus.RUNNING:
                 continue
             out.scheduled.append(ScheduledSeq(seq, seq.num_computed_tokens, n,
                                               n == seq.num_remaining_tokens))

@@ -42,6 +42,7 @@ DECODE_ATTENTION_MMA = True         # decoded tokens (up to 16 rows per kv head,
 DECODE_ATTENTION_MMA_MIN_CTAS = 0   # CTAs from which that kernel is used
 DECODE_ATTENTION_MMA_STAGES = 3     # key groups a warp of that kernel keeps in flight (2 or 3; measured: 3 is 2.5 % ahead in the step)
 DECODE_ATTENTION_MMA_EARLY = True   # that kernel requests earlier steps' keys before it waits for the kernel before it
+DECODE_ATTENTION_MMA_BESIDE_TC = True   # also for the decoded tokens of a step whose prompt portions go to the tcgen05 kernel
 DECODE_ATTENTION_MMA_WIDE = True    # steps with at most as many attention CTAs as SMs: CTAs of 8 warps, one per SM (and contexts split for 148 CTAs, not 296)
 DECODE_PREFETCH_KV_MB = 0           # that kernel asks L2 for the next layer's keys and values when a layer's are at most this many MB (0: never)
 TC_ROWS = 256           # rows per work item of the tcgen05 attention kernel (two halves of 128)
@@ -904,9 +905,11 @@ def _merge_counters(device, kernel: str = "fa") -> torch.Tensor:
 
 
 def _decode_mma_serves(plan, key, qkv: torch.Tensor, Hq: int, Hkv: int, D: int) -> bool:
-    """Whether the whole step's attention (geometry index ``key`` of the plan) goes to the tensor-core kernel
-    for decoded tokens: items of at most 16 rows, head size 128, none on the tcgen05 kernel."""
-    if not DECODE_ATTENTION_MMA or key is None or f"fa{key}_items" not in plan or f"tc{key}_items" in plan or D != 128:
+    """Whether the step's requests that are not on the tcgen05 kernel (geometry index ``key`` of the plan) go to
+    the tensor-core kernel for decoded tokens: items of at most 16 rows, head size 128."""
+    if not DECODE_ATTENTION_MMA or key is None or f"fa{key}_items" not in plan or D != 128:
+        return False
+    if f"tc{key}_items" in plan and not DECODE_ATTENTION_MMA_BESIDE_TC:
         return False
     n_parts, part_rows, small_tiles, max_rows, same_parts = plan[f"fa{key}_info_host"]
     n_items = plan[f"fa{key}_items"].numel() // FLASH_ITEM_INTS

@@ -133,9 +133,15 @@ def _preemption_with_sharing(folder, name, device):
     page = helpers.TINY[name]["page"]
     lengths_at_preemption = set()
     hits = 0
-    for plens in ((10, 10, 10), (9, 11, 12), (12, 10, 11), (11, 9, 8), (10, 12, 9)):
+    cases = [(plens, ahead) for ahead in (False, True)
+             for plens in ((10, 10, 10), (9, 11, 12), (12, 10, 11), (11, 9, 8), (10, 12, 9))]
+    for plens, ahead in cases:
+        # step by step, the newest request is preempted when an older one needs a page, at any length; with steps
+        # launched ahead (which never preempt) requests sit out until none can go on, so that the victim is one
+        # token into a page
         prompts = [random_tokens(V, n, 90 + i) for i, n in enumerate(plens)]
-        eng = make_engine(folder, name, F32, device=device, num_blocks=12, max_model_len=32, enable_prefix_cache=True)
+        eng = make_engine(folder, name, F32, device=device, num_blocks=12, max_model_len=32, enable_prefix_cache=True,
+                          run_ahead=ahead)
         real = eng.scheduler._preempt_newest
 
         def spy(out, reserved, real=real, eng=eng):
@@ -147,7 +153,7 @@ def _preemption_with_sharing(folder, name, device):
         outs = {o.request_id: o for o in eng.serving()}
         assert eng.stats.preemptions >= 1
         for i, p in zip(ids, prompts):
-            assert outs[i].output_token_ids == _plain_greedy(folder, p, 14), f"prompt lengths {plens}, request {i}"
+            assert outs[i].output_token_ids == _plain_greedy(folder, p, 14), f"prompt lengths {plens}, ahead {ahead}, request {i}"
         hits += sum(o.shared_prefix_len > 0 for o in outs.values() if o.num_preemptions)
         assert eng.cache.pages_in_use() == 0
         eng.cache.check_invariants()

@@ -247,3 +247,15 @@ def test_cache_sized_from_a_share_of_the_devices_memory(model_folders):
     assert out.output_token_ids == _plain_greedy(folder, prompt, 6)
     del llm
     torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", ["tiny-b", "tiny-d"])
+def test_prompt_portions_and_admissions_in_steps_launched_ahead_on_the_gpu(model_folders, name, dtype):
+    """Arrivals while others decode, prompts in small portions, few slots: steps launched ahead carry prompt
+    portions, admissions and decoded tokens together and change no token (against the step-by-step engine; in
+    32-bit against the plain implementation too)."""
+    from test_generate_host import _arrivals_with_portions, _plain_greedy
+    folder = model_folders[name]
+    plain_of = (lambda p, n: _plain_greedy(folder, p, n)) if dtype == torch.float32 else None
+    _arrivals_with_portions(folder, name, dtype, "cuda:0", plain_of)

@@ -110,6 +110,53 @@ def test_steps_launched_ahead_change_nothing(model_folders, cpu_ops, prefix_cach
             assert toks == plain and reason == "length"
 
 
+def _arrivals_with_portions(folder, name, dtype, device, plain_of):
+    """Requests that arrive while others decode, prompts in portions of at most 6 tokens under a budget of 8, three
+    slots, few pages: with steps launched ahead, prompt portions, admissions and decoded tokens go into one step
+    that is scheduled while the step before it is still in flight; tokens and finish reasons equal the
+    step-by-step engine's and (``plain_of`` given) the plain implementation's."""
+    V = helpers.vocab_of(name)
+    prompts = [random_tokens(V, n, 300 + n) for n in (23, 9, 31, 5, 17)]
+    lengths = [9, 14, 6, 11, 8]
+    arrive_at = [0, 0, 3, 5, 9]
+    results = {}
+    for ahead in (False, True):
+        eng = make_engine(folder, name, dtype, device=device, run_ahead=ahead, max_model_len=64, max_num_seqs=3,
+                          max_num_batched_tokens=8, prefill_chunk_size=6, num_blocks=28)
+        done, steps, mixed_ahead, admitted_ahead = [], 0, 0, 0
+        added = 0
+        while eng.has_work() or added < len(prompts):
+            while added < len(prompts) and arrive_at[added] <= steps:
+                eng.add_request(prompts[added], SamplingParams(max_new_tokens=lengths[added], ignore_eos=True))
+                added += 1
+            waiting_before = len(eng.scheduler.waiting)
+            flight_before = eng._flight
+            done.extend(eng.step())
+            steps += 1
+            fl = eng._flight
+            if fl is not None and fl is not flight_before:
+                mixed_ahead += fl.prefill_tokens > 0 and fl.decode_tokens > 0
+                admitted_ahead += len(fl.out.admitted)
+        eng.cache.check_invariants()
+        assert eng.cache.pages_in_use() == 0
+        if ahead:
+            assert mixed_ahead > 0, "no step with prompt portions beside decoded tokens was launched ahead"
+            assert admitted_ahead > 0, "no request was admitted by a step launched ahead"
+        else:
+            assert mixed_ahead == 0 and admitted_ahead == 0
+        results[ahead] = {s.seq_id: (list(s.output_token_ids), s.finish_reason) for s in done}
+        assert len(done) == len(prompts)
+    assert results[True] == results[False]
+    for i, (p, n) in enumerate(zip(prompts, lengths)):
+        if plain_of is not None:
+            assert results[True][i] == (plain_of(p, n), "length")
+
+
+def test_prompt_portions_and_admissions_go_into_steps_launched_ahead(model_folders, cpu_ops):
+    folder = model_folders["tiny-a"]
+    _arrivals_with_portions(folder, "tiny-a", F32, "cpu", lambda p, n: _plain_greedy(folder, p, n))
+
+
 def test_uniform_numbers_are_a_function_of_seed_request_and_position():
     assert uniform_for(1, 2, 3) == uniform_for(1, 2, 3)
     vals = {uniform_for(s, r, p) for s in range(3) for r in range(3) for p in range(3)}

@@ -229,6 +229,45 @@ def test_tokens_with_a_place_kept_for_them_holds_and_late_stops():
         s.update(cur, {2: 1}, {2: 0})                   # no place is waiting there
 
 
+def test_a_step_scheduled_ahead_leaves_out_who_finds_no_pages_and_may_admit():
+    """``schedule(may_preempt=False)`` is what the engine calls while a step is in flight: a running request that
+    needs a page when none is free is left out (nobody is preempted, its turn comes when pages are back or when
+    the next step is scheduled with preemption allowed); prompt portions and admissions go in as in any step."""
+    cm, s = _setup(num_pages=7, page=4, max_seqs=3, budget=64, max_len=24, prefix=False)
+    a, b = _seq(0, 8, max_new=12), _seq(1, 7, max_new=12)
+    s.add(a), s.add(b)
+    out = s.schedule()
+    s.update(out, _fake_step(cm, out))                  # a: 2 pages, full; b: 2 pages, one slot left; 3 pages free
+    c = _seq(2, 8, max_new=2)
+    s.add(c)
+    out = s.schedule(may_preempt=False)                 # a takes a page, b needs none, c is admitted on the last two
+    assert [x.seq.seq_id for x in out.scheduled] == [0, 1, 2] and out.admitted == [c] and not out.preempted
+    assert out.scheduled[2].num_tokens == 8
+    s.update(out, _fake_step(cm, out))
+    free = cm.paged_groups[0].pool.num_free
+    out = s.schedule(may_preempt=False)
+    who = [x.seq.seq_id for x in out.scheduled]
+    assert not out.preempted and s.num_preemptions == 0
+    needs_page = [q.seq_id for q in (a, b, c) if cm.pages_needed(q.cache, 1)[0] > 0]
+    assert len(needs_page) > free, "the case is meant to run out of pages"
+    assert all(i in who for i in (0, 1, 2) if i not in needs_page), "who needs no page runs"
+    assert len([i for i in who if i in needs_page]) == free, "the free pages go to the oldest that need one"
+    s.update(out, _fake_step(cm, out))
+    # when nobody can go on the step scheduled ahead is empty, and the next one, with preemption, makes room
+    for _ in range(40):
+        if not s.has_work():
+            break
+        out = s.schedule(may_preempt=False)
+        if not out.scheduled:
+            out = s.schedule()
+            assert out.preempted
+        s.update(out, _fake_step(cm, out))
+    assert not s.has_work() and s.num_preemptions >= 1
+    assert [len(q.output_token_ids) for q in (a, b, c)] == [12, 12, 2]
+    assert cm.pages_in_use() == 0
+    cm.check_invariants()
+
+
 def test_any_of_several_end_of_sequence_ids_stops_a_request():
     cm, s = _setup(eos=(7, 9))
     a, b, c = _seq(0, 3, max_new=5), _seq(1, 3, max_new=5), _seq(2, 3, max_new=5, ignore_eos=True)
