@@ -6,10 +6,12 @@
 // pull from L2 is what bounds these products.  (Contract of the reference's linear,
 // src/layers/ops/linear.py:101-122.)
 //
-// Persistent: a cluster of two CTAs per pair of SMs walks over the tiles.  Per CTA 6 warps: warp 0
+// Persistent: a cluster of two CTAs per pair of SMs walks over the tiles.  Per CTA 10 warps: warp 0
 // feeds TMA (its loads count their bytes on the leading CTA's `full` barrier), warp 1 owns tensor
-// memory (and, in the leading CTA, issues the MMAs), warps 2-5 read this CTA's 128 rows of the
-// accumulator and store them.  `empty` and `acc_full` are signalled to both CTAs by tcgen05.commit
+// memory (and, in the leading CTA, issues the MMAs), warps 2-9 read this CTA's 128 rows of the
+// accumulator and store them: a warp reaches the 32 rows of tensor memory that its number modulo 4
+// names, so warps 2-5 take the first half of the tile's columns and warps 6-9 the second (with a
+// short K the epilogue of a tile takes as long as its products: eight warps keep it off the critical path).  `empty` and `acc_full` are signalled to both CTAs by tcgen05.commit
 // with a CTA mask; `acc_empty` lives in the leading CTA and collects the epilogue warps of both.  No
 // TMA multicast.  Every wait on an mbarrier is bounded, as in gemm_tcgen05.cu.
 //
@@ -39,14 +41,28 @@ struct PrRope {
 
 #define PR_BM 128               // rows of x per CTA (256 per pair)
 #define PR_BK 64
-#define PR_THREADS 192
+#define PR_THREADS 320
+#define PR_EPI_WARPS 8          // two per quarter of the accumulator's rows, each with half of the tile's columns
 
 static __device__ int g_tc_status = 0;      // 0 = fine; else code of the first wait that ran out
 
-template <int BN, int STAGES>
+// the epilogue warps of a CTA among themselves
+__device__ __forceinline__ void pr_epilogue_sync() { asm volatile("bar.sync 1, %0;\n" :: "n"(PR_EPI_WARPS * 32) : "memory"); }
+// the same, and whether `ok` holds in all of their threads: after a wait that may have run out in some warps only,
+// so that all of them go on or none does
+__device__ __forceinline__ bool pr_epilogue_all(bool ok) {
+  uint32_t all;
+  asm volatile("{\n.reg .pred p, q;\nsetp.ne.u32 q, %1, 0;\nbar.red.and.pred p, 1, %2, q;\nselp.u32 %0, 1, 0, p;\n}\n"
+               : "=r"(all) : "r"((uint32_t)ok), "n"(PR_EPI_WARPS * 32) : "memory");
+  return all != 0;
+}
+
+template <int BN, int STAGES, bool ROPE = false>
 struct __align__(1024) PrSmem {
   __nv_bfloat16 a[STAGES][PR_BM * PR_BK];            // 16 KB each
   __nv_bfloat16 b[STAGES][(BN / 2) * PR_BK];         // this CTA's half of the tile's rows of w
+  __nv_bfloat16 stage[ROPE ? PR_BM * 128 : 8];       // ROPE: one head of this CTA's 128 rows, between the two halves of its epilogue
+  float stage_ssq[ROPE ? 2 * PR_BM : 2];             // ... and the sums of squares of the two halves of every row
   uint64_t full[STAGES];                             // used in the leading CTA
   uint64_t empty[STAGES];
   uint64_t acc_full[2];
@@ -63,7 +79,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   static_assert(!SWIGLU || BN == 256, "the fused activation pairs 128 columns of gate with 128 of up");
   static_assert(!ROPE || (BN == 256 && !SWIGLU && sizeof(TOut) == 2), "the fused rotation takes two heads of 128 per tile, in bfloat16");
   extern __shared__ unsigned char smem_raw[];
-  using Smem = PrSmem<BN, STAGES>;
+  using Smem = PrSmem<BN, STAGES, ROPE>;
   constexpr uint32_t TMEM_COLS = 2 * BN;
   constexpr uint32_t STAGE_BYTES = (PR_BM + BN / 2) * PR_BK * sizeof(__nv_bfloat16);
   pdl_launch_dependents();
@@ -82,7 +98,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     tma_prefetch_map(&map_x);
     tma_prefetch_map(&map_w);
     for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&sm.acc_full[s], 1); mbar_init(&sm.acc_empty[s], 8); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&sm.acc_full[s], 1); mbar_init(&sm.acc_empty[s], 2 * PR_EPI_WARPS); }
     sm.abort_flag = 0;
     mbar_init_fence();
   }
@@ -156,11 +172,43 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   } else {
     // ---- epilogue: this CTA's 128 rows of the accumulator ----------------------------------------
     const int quarter = warp & 3;
+    const int ch = (warp - 2) >> 2;                  // which half of the tile's columns
+    // ROPE: this lane's elements (2l, 2l + 1, 64 + 2l, 64 + 2l + 1) of the norm weights of q and of k
+    [[maybe_unused]] float4 nw_q = make_float4(1.f, 1.f, 1.f, 1.f), nw_k = nw_q;
+    if constexpr (ROPE) {
+      if (rp.qw) {
+        const float2 a = __ldg(reinterpret_cast<const float2*>(rp.qw) + lane), b = __ldg(reinterpret_cast<const float2*>(rp.qw + 64) + lane);
+        nw_q = make_float4(a.x, a.y, b.x, b.y);
+      }
+      if (rp.kw) {
+        const float2 a = __ldg(reinterpret_cast<const float2*>(rp.kw) + lane), b = __ldg(reinterpret_cast<const float2*>(rp.kw + 64) + lane);
+        nw_k = make_float4(a.x, a.y, b.x, b.y);
+      }
+    }
     int it = 0;
     for (int tile = pair; tile < n_tiles; tile += n_pairs, ++it) {
       const int buf = it & 1;
       const int m0 = (tile / n_blocks) * 2 * PR_BM + (int)rank * PR_BM, n0 = (tile % n_blocks) * BN;
-      const bool ok = __all_sync(0xffffffffu, mbar_wait(&sm.acc_full[buf], (it >> 1) & 1, abort_flag, 23, &g_tc_status));
+      // ROPE: what this warp's 16 rows need from memory besides the accumulator (their angles, their slots in the
+      // cache) is the same for both heads of the tile and is asked for before the wait for the tile's products
+      [[maybe_unused]] float4 rope_t[ROPE ? PR_BM / PR_EPI_WARPS : 1];
+      [[maybe_unused]] int rope_slot = 0;
+      if constexpr (ROPE) {
+        const int e = warp - 2;
+        if (rp.cos_sin != nullptr) {
+#pragma unroll
+          for (int i = 0; i < PR_BM / PR_EPI_WARPS; ++i) {
+            const int r = min(m0 + e + i * PR_EPI_WARPS, M - 1);
+            rope_t[i] = __ldg(reinterpret_cast<const float4*>(rp.cos_sin + (size_t)r * 64) + lane);   // (cos, sin) of elements 2l, 2l + 1
+          }
+        }
+        if (rp.write_kv && lane < PR_BM / PR_EPI_WARPS) {
+          const int r = m0 + e + lane * PR_EPI_WARPS;
+          rope_slot = r < M ? __ldg(rp.slot_mapping + r) : 0;
+        }
+      }
+      bool ok = __all_sync(0xffffffffu, mbar_wait(&sm.acc_full[buf], (it >> 1) & 1, abort_flag, 23, &g_tc_status));
+      if constexpr (ROPE) ok = pr_epilogue_all(ok);    // its warps meet at barriers below: all go on or none
       if (!ok) break;
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
@@ -168,12 +216,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         // columns c0.. of gate and of up -> 32 columns of the activation
         const int I = n_up, i0 = (tile % n_blocks) * (BN / 2);
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN / 2; c0 += 32) {
+        for (int c0 = ch * (BN / 4); c0 < (ch + 1) * (BN / 4); c0 += 32) {
           uint32_t g[32], u[32];
           tc_ld_32x32b_x32(tmem + ((uint32_t)(quarter * 32) << 16) + buf * BN + c0, g);
           tc_ld_32x32b_x32(tmem + ((uint32_t)(quarter * 32) << 16) + buf * BN + BN / 2 + c0, u);
           tc_wait_ld();
-          if (c0 + 32 == BN / 2) {
+          if (c0 + 32 == (ch + 1) * (BN / 4)) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(smem_u32(&sm.acc_empty[buf]) & TC_PEER_BIT_MASK);
@@ -204,112 +252,119 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
           }
         }
       } else if constexpr (ROPE) {
-        // two heads of 128 columns; this thread holds its token's whole head.  Per head two passes over the
-        // accumulator (tensor memory is cheap to read again): the sum of squares, then, for the columns
-        // (0-31, 64-95) and (32-63, 96-127), norm, rotation and store, with the angles' loads in flight
-        // beside the accumulator's.
-        const bool row_ok = row < M;
-        int slot = 0;
-        if (row_ok && rp.write_kv) slot = __ldg(rp.slot_mapping + row);
-        const float4* tp = reinterpret_cast<const float4*>(rp.cos_sin + (size_t)(row_ok ? row : 0) * 64);
+        // Two heads of 128 columns, one after the other, each in two halves.  First every thread takes 64 columns
+        // of its own row of the accumulator (a thread of warp w reaches row 32 (w mod 4) + lane of tensor memory),
+        // rounds them to bfloat16 as the plain product's output is rounded, and puts them into shared memory
+        // (16-byte chunks, their index XORed with the row's low bits: no bank conflicts either way).  Then the eight
+        // warps walk over the 128 rows, a row per warp at a time, lanes along the head: lane l holds elements 2l,
+        // 2l + 1 and their partners 64 further, the sum of squares is a warp reduction, the row's angles are one
+        // 512-byte load and its outputs two 128-byte stores.  (With lanes along the rows, as the accumulator comes
+        // out of tensor memory, every load of angles and every store touched 32 rows at once: the epilogue then
+        // took longer than the tile's products.)
+        unsigned char* stg = reinterpret_cast<unsigned char*>(sm.stage);
         const uint32_t tm_row = tmem + ((uint32_t)(quarter * 32) << 16) + buf * BN;
-        auto rnd = [](uint32_t u) { return __bfloat162float(__float2bfloat16_rn(__uint_as_float(u))); };   // as the plain product's output is rounded
+        const int r_mine = quarter * 32 + lane;          // this thread's row of the CTA's 128
+        const int e = warp - 2;                          // 0..7
 #pragma unroll 1
         for (int hh = 0; hh < 2; ++hh) {
           const int col0 = n0 + hh * 128, head = col0 >> 7;
           const bool is_q = head < rp.Hq, is_v = head >= rp.Hq + rp.Hkv;
-          const bool wanted = row_ok && col0 < N && (is_q || rp.write_kv);   // (keys and values of a layer that reads another's cache are dropped)
-          const float* w = is_v ? nullptr : (is_q ? rp.qw : rp.kw);
-          float rstd = 1.f;
-          if (w) {                                   // warp-uniform
-            float s4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int c = 0; c < 4; c += 2) {
-              uint32_t a[32], b[32];
-              tc_ld_32x32b_x32(tm_row + hh * 128 + c * 32, a);
-              tc_ld_32x32b_x32(tm_row + hh * 128 + c * 32 + 32, b);
-              tc_wait_ld();
-#pragma unroll
-              for (int i = 0; i < 32; i += 2) {
-                const float a0 = rnd(a[i]), a1 = rnd(a[i + 1]), b0 = rnd(b[i]), b1 = rnd(b[i + 1]);
-                s4[0] = fmaf(a0, a0, s4[0]); s4[1] = fmaf(a1, a1, s4[1]); s4[2] = fmaf(b0, b0, s4[2]); s4[3] = fmaf(b1, b1, s4[3]);
-              }
-            }
-            rstd = rsqrtf(((s4[0] + s4[1]) + (s4[2] + s4[3])) / 128.f + rp.eps);
-          }
-          __nv_bfloat16* dst = nullptr;
-          if (wanted) {
-            if (is_q) {
-              dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * N + col0;
-            } else {
-              // slot = page * page_size + off: the row of (page, K or V, h, off) in the cache
-              const int h = is_v ? head - rp.Hq - rp.Hkv : head - rp.Hq;
-              const int page = (rp.page_size & (rp.page_size - 1)) == 0 ? slot >> (__ffs(rp.page_size) - 1) : slot / rp.page_size;
-              dst = rp.pages + ((size_t)slot + ((size_t)page * (2 * rp.Hkv - 1) + (is_v ? rp.Hkv : 0) + h) * rp.page_size) * 128;
-            }
-          }
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {     // columns 32 half .. + 31 and their partners 64 further
-            uint32_t lo[32], hi[32];
-            tc_ld_32x32b_x32(tm_row + hh * 128 + half * 32, lo);
-            tc_ld_32x32b_x32(tm_row + hh * 128 + 64 + half * 32, hi);
-            float4 t[16];
-            const bool rotate = !is_v && rp.cos_sin != nullptr;
-            if (rotate && wanted) {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) t[j] = __ldg(tp + half * 16 + j);     // (cos, sin) of elements 32 half + 2j, + 2j + 1
-            }
+          const bool wanted = col0 < N && (is_q || rp.write_kv);   // (keys and values of a layer that reads another's cache are dropped)
+          {
+            uint32_t a[32], b[32];
+            tc_ld_32x32b_x32(tm_row + hh * 128 + ch * 64, a);
+            tc_ld_32x32b_x32(tm_row + hh * 128 + ch * 64 + 32, b);
             tc_wait_ld();
-            if (hh == 1 && half == 1) {
+            if (hh == 1) {
               // the accumulator is in registers: tell the leading CTA's MMA thread
               tc_fence_before();
               __syncwarp();
               if (lane == 0) mbar_arrive_cluster(smem_u32(&sm.acc_empty[buf]) & TC_PEER_BIT_MASK);
             }
-            if (!wanted) continue;
-            float xl[32], xh[32];
+            unsigned char* mine = stg + r_mine * 256;
+            float s4[4] = {0.f, 0.f, 0.f, 0.f};      // of the rounded values, as the norm of the plain product sees them
 #pragma unroll
-            for (int i = 0; i < 32; ++i) { xl[i] = rnd(lo[i]); xh[i] = rnd(hi[i]); }
-            if (w) {
+            for (int c = 0; c < 8; ++c) {
+              const uint32_t* src = c < 4 ? a + 8 * c : b + 8 * (c - 4);
+              uint32_t v[4];
 #pragma unroll
-              for (int i = 0; i < 32; i += 4) {
-                const float4 wl = __ldg(reinterpret_cast<const float4*>(w + half * 32 + i));
-                const float4 wh = __ldg(reinterpret_cast<const float4*>(w + 64 + half * 32 + i));
-                xl[i] = xl[i] * rstd * wl.x; xl[i + 1] = xl[i + 1] * rstd * wl.y; xl[i + 2] = xl[i + 2] * rstd * wl.z; xl[i + 3] = xl[i + 3] * rstd * wl.w;
-                xh[i] = xh[i] * rstd * wh.x; xh[i + 1] = xh[i + 1] * rstd * wh.y; xh[i + 2] = xh[i + 2] * rstd * wh.z; xh[i + 3] = xh[i + 3] * rstd * wh.w;
+              for (int j = 0; j < 4; ++j) {
+                __nv_bfloat162 pj = __floats2bfloat162_rn(__uint_as_float(src[2 * j]), __uint_as_float(src[2 * j + 1]));
+                v[j] = *reinterpret_cast<uint32_t*>(&pj);
+                const float x0 = __uint_as_float(v[j] << 16), x1 = __uint_as_float(v[j] & 0xffff0000u);
+                s4[j] = fmaf(x0, x0, fmaf(x1, x1, s4[j]));
               }
+              *reinterpret_cast<uint4*>(mine + (((ch * 8 + c) ^ (r_mine & 7)) << 4)) = make_uint4(v[0], v[1], v[2], v[3]);
             }
-            if (rotate) {
+            sm.stage_ssq[ch * PR_BM + r_mine] = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+          }
+          pr_epilogue_sync();                        // the head is in shared memory
+          if (wanted) {
+            const float* w = is_v ? nullptr : (is_q ? rp.qw : rp.kw);
+            const float w0 = is_q ? nw_q.x : nw_k.x, w1 = is_q ? nw_q.y : nw_k.y, w2 = is_q ? nw_q.z : nw_k.z, w3 = is_q ? nw_q.w : nw_k.w;
+            const bool rotate = !is_v && rp.cos_sin != nullptr;
+            const int kv_h = is_v ? head - rp.Hq - rp.Hkv : head - rp.Hq;
+            const int page_shift = (rp.page_size & (rp.page_size - 1)) == 0 ? __ffs(rp.page_size) - 1 : -1;
+            // 16 rows per warp, in two rounds of 8 whose loads are all issued before the first is used and whose
+            // arithmetic the compiler interleaves (a row alone is one chain of dependent shuffles and loads)
+            constexpr int ROUND = 8;
+#pragma unroll 1
+            for (int r0 = e; r0 < PR_BM; r0 += ROUND * PR_EPI_WARPS) {
+              const int i0 = (r0 - e) / PR_EPI_WARPS;        // 0 or ROUND: where this round's rows are among the warp's 16
+              uint32_t ul[ROUND], uh[ROUND];
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const float l0 = xl[2 * j], h0 = xh[2 * j], l1 = xl[2 * j + 1], h1 = xh[2 * j + 1];
-                xl[2 * j] = t[j].x * l0 - t[j].y * h0;      xh[2 * j] = t[j].y * l0 + t[j].x * h0;
-                xl[2 * j + 1] = t[j].z * l1 - t[j].w * h1;  xh[2 * j + 1] = t[j].w * l1 + t[j].z * h1;
+              for (int i = 0; i < ROUND; ++i) {
+                const int rr = r0 + i * PR_EPI_WARPS;
+                const unsigned char* src = stg + rr * 256 + ((lane & 3) << 2);
+                ul[i] = *reinterpret_cast<const uint32_t*>(src + (((lane >> 2) ^ (rr & 7)) << 4));
+                uh[i] = *reinterpret_cast<const uint32_t*>(src + (((8 + (lane >> 2)) ^ (rr & 7)) << 4));
               }
-            }
+              float rstd[ROUND];
+              if (w) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              uint4 v, u;
-              __nv_bfloat162 p0 = __floats2bfloat162_rn(xl[j], xl[j + 1]), p1 = __floats2bfloat162_rn(xl[j + 2], xl[j + 3]);
-              __nv_bfloat162 p2 = __floats2bfloat162_rn(xl[j + 4], xl[j + 5]), p3 = __floats2bfloat162_rn(xl[j + 6], xl[j + 7]);
-              v.x = *reinterpret_cast<uint32_t*>(&p0); v.y = *reinterpret_cast<uint32_t*>(&p1);
-              v.z = *reinterpret_cast<uint32_t*>(&p2); v.w = *reinterpret_cast<uint32_t*>(&p3);
-              __nv_bfloat162 q0 = __floats2bfloat162_rn(xh[j], xh[j + 1]), q1 = __floats2bfloat162_rn(xh[j + 2], xh[j + 3]);
-              __nv_bfloat162 q2 = __floats2bfloat162_rn(xh[j + 4], xh[j + 5]), q3 = __floats2bfloat162_rn(xh[j + 6], xh[j + 7]);
-              u.x = *reinterpret_cast<uint32_t*>(&q0); u.y = *reinterpret_cast<uint32_t*>(&q1);
-              u.z = *reinterpret_cast<uint32_t*>(&q2); u.w = *reinterpret_cast<uint32_t*>(&q3);
-              *reinterpret_cast<uint4*>(dst + half * 32 + j) = v;
-              *reinterpret_cast<uint4*>(dst + 64 + half * 32 + j) = u;
+                for (int i = 0; i < ROUND; ++i) {
+                  const int rr = r0 + i * PR_EPI_WARPS;
+                  rstd[i] = rsqrtf((sm.stage_ssq[rr] + sm.stage_ssq[PR_BM + rr]) / 128.f + rp.eps);
+                }
+              }
+#pragma unroll
+              for (int i = 0; i < ROUND; ++i) {
+                const int r = m0 + r0 + i * PR_EPI_WARPS;
+                float l0 = __uint_as_float(ul[i] << 16), l1 = __uint_as_float(ul[i] & 0xffff0000u);
+                float h0 = __uint_as_float(uh[i] << 16), h1 = __uint_as_float(uh[i] & 0xffff0000u);
+                if (w) { l0 = l0 * rstd[i] * w0; l1 = l1 * rstd[i] * w1; h0 = h0 * rstd[i] * w2; h1 = h1 * rstd[i] * w3; }
+                if (rotate) {
+                  const float a0 = l0, b0 = h0, a1 = l1, b1 = h1;
+                  const float4 t = i0 == 0 ? rope_t[i] : rope_t[ROUND + i];
+                  l0 = t.x * a0 - t.y * b0;  h0 = t.y * a0 + t.x * b0;
+                  l1 = t.z * a1 - t.w * b1;  h1 = t.w * a1 + t.z * b1;
+                }
+                const int slot = __shfl_sync(0xffffffffu, rope_slot, i0 + i);
+                __nv_bfloat16* dst;
+                if (is_q) {
+                  dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)r * N + col0;
+                } else {
+                  // slot = page * page_size + off: the row of (page, K or V, h, off) in the cache
+                  const int page = page_shift >= 0 ? slot >> page_shift : slot / rp.page_size;
+                  dst = rp.pages + ((size_t)slot + ((size_t)page * (2 * rp.Hkv - 1) + (is_v ? rp.Hkv : 0) + kv_h) * rp.page_size) * 128;
+                }
+                if (r < M) {
+                  __nv_bfloat162 pl = __floats2bfloat162_rn(l0, l1), ph = __floats2bfloat162_rn(h0, h1);
+                  reinterpret_cast<uint32_t*>(dst)[lane] = *reinterpret_cast<uint32_t*>(&pl);
+                  reinterpret_cast<uint32_t*>(dst + 64)[lane] = *reinterpret_cast<uint32_t*>(&ph);
+                }
+              }
             }
           }
+          pr_epilogue_sync();                        // the buffer is free for the next head
         }
       } else {
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = ch * (BN / 2); c0 < (ch + 1) * (BN / 2); c0 += 32) {
         uint32_t r[32];
         tc_ld_32x32b_x32(tmem + ((uint32_t)(quarter * 32) << 16) + buf * BN + c0, r);
         tc_wait_ld();
-        if (c0 + 32 == BN) {
+        if (c0 + 32 == (ch + 1) * (BN / 2)) {
           // the accumulator is in registers: tell the leading CTA's MMA thread
           tc_fence_before();
           __syncwarp();
@@ -374,7 +429,7 @@ static int launch_pair(const void* x, const void* w, void* out, int M, int N, in
     const uint32_t box[2] = {PR_BK, BN / 2};
     if (!qe_tensor_map_bf16(w, 2, dims, strides, box, &map_w)) return 1;
   }
-  const size_t smem = sizeof(PrSmem<BN, STAGES>) + 1024;
+  const size_t smem = sizeof(PrSmem<BN, STAGES, ROPE>) + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<__nv_bfloat16, BN, STAGES, SWIGLU, ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
