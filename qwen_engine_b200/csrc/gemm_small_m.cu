@@ -268,3 +268,70 @@ extern "C" int qe_linear_small_m_swiglu(const void* x, const void* w, void* act,
   QE_CHECK_LAUNCH("linear_small_m_swiglu");
   return 0;
 }
+
+
+// ---- the QKV product with per-head norm, rotation and cache write in its epilogue (see gsm_cta_qkv_rope) ---------
+template <int MT>
+__global__ void __cluster_dims__(8, 1, 1) __launch_bounds__(512)
+gemm_small_m_qkv_rope_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                             __nv_bfloat16* __restrict__ qkv, int M, int N, int K, int k_per_warp, GsmRope rp, FuseArgs na) {
+  extern __shared__ float red[];                    // [warps][16][8 MT]
+  __shared__ float s_val[16 * 8 * MT];              // this CTA's 16 columns of every row, read by the CTA four ranks away
+  __shared__ float s_ssq[8 * MT];                   // their sums of squares, read by all CTAs of the head
+  if (na.next_bytes) {
+    const unsigned long long pieces = (na.next_bytes + 4095) >> 12;
+    const unsigned long long piece = (unsigned long long)threadIdx.x * gridDim.x + blockIdx.x;
+    if (piece < pieces) {
+      const unsigned long long off = piece << 12;
+      const unsigned size = (unsigned)min(4096ull, na.next_bytes - off) & ~15u;
+      if (size) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" :: "l"(na.next_w + off), "r"(size) : "memory");
+    }
+  }
+  pdl_launch_dependents();
+  gsm_cta_qkv_rope<MT>(x, w, qkv, M, N, K, k_per_warp, rp, blockIdx.x, red, s_val, s_ssq);   // (waits for the kernel before it once its first weights are on their way)
+}
+
+// qkv[M, :Hq 128] = the q columns of x · w^T for the stacked q, k, v weights w [N = (Hq + 2 Hkv) 128, K], normed per
+// head and rotated; the k (normed, rotated) and v columns go into the cache `pages` [pages, 2, Hkv, page_size, 128] at
+// slot_mapping[row] (write_kv 0: they are dropped) and qkv's k and v columns are left as they were.  M <= 16 rows,
+// bfloat16.  qw, kw: float32 [128] or null; the angles: cos_sin float32 [M, 64, 2] if given, else position *
+// inv_freq[64] (both null: no rotation).  Returns 0 when run, 1 when refused, 2 on a launch error.
+extern "C" int qe_linear_small_m_qkv_rope(const void* x, const void* w, void* qkv, int M, int N, int K,
+                                          const float* qw, const float* kw, float eps, const int* positions,
+                                          const float* inv_freq, const void* cos_sin, void* pages, const int* slot_mapping,
+                                          int Hq, int Hkv, int page_size, int write_kv, cudaStream_t stream) {
+  FuseArgs na{};
+  na.next_w = g_next_w;
+  na.next_bytes = g_next_bytes;
+  g_next_w = nullptr;
+  g_next_bytes = 0;
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 16) QE_REFUSE("linear_small_m_qkv_rope: M = %d is above 16", M);
+  if (K <= 0 || K % 8) QE_REFUSE("linear_small_m_qkv_rope: K = %d is not a positive multiple of 8", K);
+  if (Hq < 1 || Hkv < 1 || N != (Hq + 2 * Hkv) * 128) QE_REFUSE("linear_small_m_qkv_rope: N = %d is not (%d + 2 x %d) heads of 128", N, Hq, Hkv);
+  if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)qkv) & 15) QE_REFUSE("linear_small_m_qkv_rope: operands must be 16-byte aligned");
+  if (inv_freq && !cos_sin && !positions) QE_REFUSE("linear_small_m_qkv_rope: angles need the positions");
+  if (write_kv && (!pages || !slot_mapping || page_size < 1)) QE_REFUSE("linear_small_m_qkv_rope: cache write without a cache");
+  const int ctas = N / 16;                           // 8 per head: the clusters
+  int warps = ctas >= 1024 ? 4 : (ctas >= 256 ? 8 : 16);
+  int k_per_warp = ((K + warps - 1) / warps + 63) / 64 * 64;
+  warps = (K + k_per_warp - 1) / k_per_warp;
+  const int MT = M <= 8 ? 1 : 2;
+  if (warps < 4 * MT) warps = 4 * MT;                // a thread per element of the CTA's 16 columns (a short K leaves some warps without a slice)
+  const size_t smem = (size_t)warps * 16 * 8 * MT * sizeof(float);
+  GsmRope rp{qw, kw, eps, positions, inv_freq, (const float2*)cos_sin, (__nv_bfloat16*)pages, slot_mapping, Hq, Hkv, page_size, write_kv ? 1 : 0};
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(gemm_small_m_qkv_rope_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 16 * 16 * 8 * 4);
+    cudaFuncSetAttribute(gemm_small_m_qkv_rope_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 16 * 16 * 16 * 4);
+    configured = true;
+  }
+  if (MT == 1)
+    qe_launch(gemm_small_m_qkv_rope_kernel<1>, dim3(ctas), dim3(warps * 32), smem, stream, (const __nv_bfloat16*)x,
+              (const __nv_bfloat16*)w, (__nv_bfloat16*)qkv, M, N, K, k_per_warp, rp, na);
+  else
+    qe_launch(gemm_small_m_qkv_rope_kernel<2>, dim3(ctas), dim3(warps * 32), smem, stream, (const __nv_bfloat16*)x,
+              (const __nv_bfloat16*)w, (__nv_bfloat16*)qkv, M, N, K, k_per_warp, rp, na);
+  QE_CHECK_LAUNCH("linear_small_m_qkv_rope");
+  return 0;
+}

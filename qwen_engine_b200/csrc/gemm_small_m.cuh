@@ -342,3 +342,149 @@ __device__ __forceinline__ void gsm_cta_swiglu(const __nv_bfloat16* __restrict__
   QE_TL_MARK(3);
 }
 
+
+// ---- the QKV product of a decode step with what follows it in its epilogue ---------------------------------------
+// A head of 128 columns is the work of a cluster of 8 CTAs (16 columns each).  After the product, the CTAs of a q or
+// k head exchange two things through distributed shared memory: the sums of squares of their 16 columns of every row
+// (the per-head RMS norm needs the head's), and the normed values, because the rotation pairs element d with d + 64,
+// which lies in the CTA four ranks away.  Then every CTA writes its 16 columns: q into the qkv buffer, k and v
+// straight into the cache page of the token's slot (the k and v columns of the qkv buffer are not written).  The
+// arithmetic is the rotary kernel's (rope_d128.cuh): the product rounded to bfloat16 first (as if stored), norm and
+// rotation in float32 with sincosf of position * inv_freq (or the step's table), rounded once.
+struct GsmRope {
+  const float* qw; const float* kw; float eps;       // norm weights [128] (null: no norm)
+  const int* positions; const float* inv_freq;       // angles = position * inv_freq[d mod 64] (inv_freq null: no rotation) ...
+  const float2* cos_sin;                             // ... or, if given, the step's table [M, 64] of (cos, sin)
+  __nv_bfloat16* pages; const int* slot_mapping;     // the cache [pages, 2, Hkv, page, 128] and the tokens' slots
+  int Hq, Hkv, page_size, write_kv;
+};
+
+template <int MT>
+__device__ __forceinline__ void gsm_cta_qkv_rope(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                                 __nv_bfloat16* __restrict__ qkv, int M, int N, int K, int k_per_warp,
+                                                 const GsmRope& rp, int vb, float* red, float* s_val, float* s_ssq) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const int g = lane >> 2, c = lane & 3;
+  const int n0 = vb * 16;
+  const __nv_bfloat16* w0 = w + (size_t)(n0 + g) * K;
+  const __nv_bfloat16* w1 = w + (size_t)(n0 + g + 8) * K;
+  const int kbeg = warp * k_per_warp, kend = min(K, kbeg + k_per_warp);
+  constexpr int MW = 8 * MT;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  auto load_chunk = [&](int k0) {
+    GsmChunk ch;
+    const int ka = k0 + 8 * c, kb = k0 + 32 + 8 * c;
+    ch.a0 = ka < kend ? ld_stream16(w0 + ka) : zero;
+    ch.b0 = ka < kend ? ld_stream16(w1 + ka) : zero;
+    ch.a1 = kb < kend ? ld_stream16(w0 + kb) : zero;
+    ch.b1 = kb < kend ? ld_stream16(w1 + kb) : zero;
+    return ch;
+  };
+  // the weights are nobody's output, and the angles come from the step's positions, which the host wrote: both are
+  // on their way before the wait for the kernel before this one
+  GsmChunk c0 = load_chunk(kbeg), c1 = load_chunk(kbeg + 64);
+  const uint32_t rank = cluster_cta_rank();            // which 16 columns of the head
+  const int head = n0 >> 7;
+  const bool is_q = head < rp.Hq, is_v = head >= rp.Hq + rp.Hkv;
+  const int e = threadIdx.x;                           // the epilogue's element of this thread: row e / 16, column e mod 16
+  const int em = e >> 4, ei = e & 15;
+  const int d = (int)rank * 16 + ei;                   // the element's place in its head
+  const bool mine = e < 16 * MW && em < M;
+  const bool rotate = !is_v && (rp.inv_freq != nullptr || rp.cos_sin != nullptr);
+  float cs = 1.f, sn = 0.f, nw_self = 1.f, nw_pair = 1.f;
+  int slot = 0;
+  if (mine) {
+    if (rotate) {
+      if (rp.cos_sin) { const float2 t = __ldg(rp.cos_sin + (size_t)em * 64 + (d & 63)); cs = t.x; sn = t.y; }
+      else sincosf((float)__ldg(rp.positions + em) * __ldg(rp.inv_freq + (d & 63)), &sn, &cs);
+    }
+    const float* nw = is_v ? nullptr : (is_q ? rp.qw : rp.kw);
+    if (nw) { nw_self = __ldg(nw + d); nw_pair = __ldg(nw + (d ^ 64)); }
+    if (!is_q && rp.write_kv) slot = __ldg(rp.slot_mapping + em);
+  }
+  pdl_wait();
+  float acc[MT][4];
+#pragma unroll
+  for (int t = 0; t < MT; ++t)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[t][i] = 0.f;
+  auto compute = [&](const GsmChunk& ch, int k0) {
+    const int ka = k0 + 8 * c, kb = k0 + 32 + 8 * c;
+#pragma unroll
+    for (int t = 0; t < MT; ++t) {
+      const int m = t * 8 + g;
+      const uint4 xa = (m < M && ka < kend) ? __ldcg(reinterpret_cast<const uint4*>(x + (size_t)m * K + ka)) : zero;
+      const uint4 xb = (m < M && kb < kend) ? __ldcg(reinterpret_cast<const uint4*>(x + (size_t)m * K + kb)) : zero;
+      mma_bf16_16816(acc[t], ch.a0.x, ch.b0.x, ch.a0.y, ch.b0.y, xa.x, xa.y);
+      mma_bf16_16816(acc[t], ch.a0.z, ch.b0.z, ch.a0.w, ch.b0.w, xa.z, xa.w);
+      mma_bf16_16816(acc[t], ch.a1.x, ch.b1.x, ch.a1.y, ch.b1.y, xb.x, xb.y);
+      mma_bf16_16816(acc[t], ch.a1.z, ch.b1.z, ch.a1.w, ch.b1.w, xb.z, xb.w);
+    }
+  };
+  for (int k0 = kbeg; k0 < kend; k0 += 128) {
+    const GsmChunk n0c = load_chunk(k0 + 128);
+    compute(c0, k0);
+    const GsmChunk n1c = load_chunk(k0 + 192);
+    compute(c1, k0 + 64);
+    c0 = n0c;
+    c1 = n1c;
+  }
+  QE_TL_MARK(2);
+  float* part = red + (size_t)warp * 16 * MW;
+#pragma unroll
+  for (int t = 0; t < MT; ++t) {
+    part[g * MW + t * 8 + 2 * c] = acc[t][0];
+    part[g * MW + t * 8 + 2 * c + 1] = acc[t][1];
+    part[(g + 8) * MW + t * 8 + 2 * c] = acc[t][2];
+    part[(g + 8) * MW + t * 8 + 2 * c + 1] = acc[t][3];
+  }
+  __syncthreads();
+  // the product's element (em, n0 + ei), the warps' parts in order, rounded as the plain product's output is
+  float y = 0.f;
+  if (e < 16 * MW) {
+    for (int wi = 0; wi < nwarps; ++wi) y += red[((size_t)wi * 16 + ei) * MW + em];
+    y = __bfloat162float(__float2bfloat16_rn(y));
+  }
+  const bool exchange = !is_v && (rotate || rp.qw != nullptr || rp.kw != nullptr);      // the same in all CTAs of the head
+  float outv = y;
+  if (exchange) {
+    if (e < 16 * MW) {                                 // whole warps (16 MW is a multiple of 32)
+      float sq = y * y;                                // over the 16 columns of the row: lanes ei = 0..15
+      sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+      sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+      if (ei == 0) s_ssq[em] = sq;
+      s_val[e] = y;
+    }
+    cluster_sync_all();                                // every CTA's values and sums of squares are in place
+    if (mine) {
+      float rstd = 1.f;
+      if ((is_q ? rp.qw : rp.kw) != nullptr) {
+        float ss = 0.f;
+#pragma unroll
+        for (uint32_t r = 0; r < 8; ++r) ss += cluster_ld_f32(cluster_map_shared(&s_ssq[em], r));
+        rstd = rsqrtf(ss / 128.f + rp.eps);
+      }
+      const float self = y * rstd * nw_self;
+      if (rotate) {
+        const float pair = cluster_ld_f32(cluster_map_shared(&s_val[e], rank ^ 4u)) * rstd * nw_pair;
+        outv = d < 64 ? cs * self - sn * pair : sn * pair + cs * self;      // (lo, hi) -> (cos lo - sin hi, sin lo + cos hi)
+      } else {
+        outv = self;
+      }
+    }
+  }
+  if (mine) {
+    if (is_q) {
+      qkv[(size_t)em * N + n0 + ei] = __float2bfloat16_rn(outv);
+    } else if (rp.write_kv) {
+      // slot = page * page_size + off: the row of (page, K or V, h, off) in the cache
+      const int h = is_v ? head - rp.Hq - rp.Hkv : head - rp.Hq;
+      const int page = slot / rp.page_size;
+      rp.pages[((size_t)slot + ((size_t)page * (2 * rp.Hkv - 1) + (is_v ? rp.Hkv : 0) + h) * rp.page_size) * 128 + d] = __float2bfloat16_rn(outv);
+    }
+  }
+  if (exchange) cluster_sync_all();                    // nobody reads this CTA's shared memory any more
+  QE_TL_MARK(3);
+}

@@ -519,6 +519,59 @@ def linear_qkv_rope(x: torch.Tensor, w_qkv: torch.Tensor, qkv: torch.Tensor, q_n
         int(bool(write_kv)), _stream()), "linear_qkv_rope")
 
 
+QKV_ROPE_SMALL = False       # a few rows: per-head norm, rotation and cache write in the epilogue of the QKV product (clusters of 8 CTAs per head).  Off: measured on a B200 (0.6B sizes, 8 rows, chains of 28): product + rotary kernel 3.83 us, fused 4.54 us (cluster launch + two cluster barriers cost more than the launch they save); the decode step 0.955 -> 0.978 ms.  Kept as a tested option.
+QKV_ROPE_SMALL_MAX_M = 16
+
+
+def qkv_rope_small_applies(M: int, N: int, K: int, dtype: torch.dtype, head_dim: int, rotary_dim: int) -> bool:
+    """Whether ``linear_qkv_rope_small`` serves this shape: a few rows in bfloat16, head size 128 rotated as a whole."""
+    return (QKV_ROPE_SMALL and dtype == torch.bfloat16 and head_dim == 128 and rotary_dim == 128 and K % 8 == 0
+            and N % 128 == 0 and 1 <= M <= QKV_ROPE_SMALL_MAX_M)
+
+
+def linear_qkv_rope_small(x, w_qkv: torch.Tensor, qkv: torch.Tensor, q_norm_w: Optional[torch.Tensor],
+                          k_norm_w: Optional[torch.Tensor], eps: float, positions: Optional[torch.Tensor],
+                          inv_freq: Optional[torch.Tensor], cos_sin: Optional[torch.Tensor],
+                          kv_pages: Optional[torch.Tensor], slot_mapping: Optional[torch.Tensor],
+                          num_heads: int, num_kv_heads: int, write_kv: bool = True) -> None:
+    """The QKV product of a few rows (decode steps) with what ``qk_norm_rope_kv_write`` would do to it afterwards in
+    its epilogue (head size 128, bfloat16): a head's 128 columns are the work of a cluster of 8 CTAs, which exchange
+    the sums of squares and the rotation's partners through distributed shared memory.  qkv[:, :Hq 128] = rotated,
+    normed q; the rotated, normed k and v go to their slots in ``kv_pages`` [pages, 2, Hkv, page, 128] only.  Angles:
+    ``cos_sin`` float32 [M, 64, 2] if given, else ``positions`` x ``inv_freq`` [64] (both None: no rotation)."""
+    if isinstance(x, NormedInput):
+        x = x.materialize()
+    M, K = x.shape
+    Hq, Hkv = num_heads, num_kv_heads
+    N = (Hq + 2 * Hkv) * 128
+    _need(x.dtype == torch.bfloat16 and w_qkv.dtype == torch.bfloat16 and w_qkv.shape == (N, K) and K % 8 == 0,
+          "linear_qkv_rope_small: bfloat16 operands, w [(Hq + 2 Hkv) 128, K] with K a multiple of 8")
+    _need(qkv.shape == (M, N) and qkv.dtype == torch.bfloat16 and qkv.is_contiguous() and x.is_contiguous() and w_qkv.is_contiguous()
+          and M <= QKV_ROPE_SMALL_MAX_M, f"linear_qkv_rope_small: qkv must be contiguous bfloat16 [M <= {QKV_ROPE_SMALL_MAX_M}, (Hq + 2 Hkv) 128]")
+    for wt in (q_norm_w, k_norm_w):
+        _need(wt is None or (wt.dtype == torch.float32 and wt.shape == (128,)), "linear_qkv_rope_small: norm weights must be float32 [128]")
+    _need(cos_sin is None or (cos_sin.dtype == torch.float32 and cos_sin.shape == (M, 64, 2) and cos_sin.is_contiguous()),
+          "linear_qkv_rope_small: cos_sin must be float32 [M, 64, 2]")
+    if inv_freq is not None:
+        _need(inv_freq.dtype == torch.float32 and inv_freq.numel() == 64, "linear_qkv_rope_small: inv_freq must be float32 [64]")
+        if cos_sin is None:
+            _need(positions is not None and positions.numel() >= M, "linear_qkv_rope_small: a position for every row")
+            _i32(positions, "positions")
+    page_size = 1
+    if write_kv:
+        _need(kv_pages is not None and slot_mapping is not None and kv_pages.dtype == torch.bfloat16 and kv_pages.is_contiguous()
+              and kv_pages.dim() == 5 and kv_pages.shape[1] == 2 and kv_pages.shape[2] == Hkv and kv_pages.shape[4] == 128,
+              "linear_qkv_rope_small: kv_pages must be bfloat16 [pages, 2, Hkv, page, 128]")
+        _i32(slot_mapping, "slot_mapping")
+        _need(slot_mapping.numel() >= M, "linear_qkv_rope_small: a slot for every row")
+        page_size = int(kv_pages.shape[3])
+    _hand_over_next_weights()
+    _check(lib().qe_linear_small_m_qkv_rope(
+        _ptr(x), _ptr(w_qkv), _ptr(qkv), M, N, K, _ptr(q_norm_w), _ptr(k_norm_w), ctypes.c_float(eps), _ptr(positions),
+        _ptr(inv_freq), _ptr(cos_sin), _ptr(kv_pages if write_kv else None), _ptr(slot_mapping if write_kv else None),
+        Hq, Hkv, page_size, int(bool(write_kv)), _stream()), "linear_qkv_rope_small")
+
+
 def linear_silu_mul(gate_up: torch.Tensor, w: torch.Tensor, out: torch.Tensor, scratch) -> None:
     """out[M, N] = (silu(gate_up[:, :I]) * gate_up[:, I:]) · w[N, I]^T.  For a few rows in bfloat16 the
     activation is formed while the product loads it; otherwise ``silu_mul`` runs first into a buffer

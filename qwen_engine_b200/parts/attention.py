@@ -95,6 +95,18 @@ class GQAAttention(Mixer):
                                     self.window or 0, H, Hkv, D, next_pages=step_hint(ctx, "next_cache"))
                 ops.linear(attn, self.w_o, out)
                 return
+        if fused_rope and ops.qkv_rope_small_applies(T, qkv.shape[1], self.hidden_size, ctx.dtype, D, rot.rotary_dim):
+            # a few rows: the same in the epilogue of the product that streams the weights (a cluster of CTAs per head)
+            ops.prefetch_next(self.w_o)
+            ops.linear_qkv_rope_small(x, self.w_qkv, qkv, self.q_norm_w, self.k_norm_w, self.qk_norm_eps or 0.0,
+                                      ctx.positions, rot.inv_freq, rot.step_table(ctx), cache, view.slot_mapping, H, Hkv,
+                                      write_kv=write_cache)
+            ops.paged_attention(qkv, cache, view.block_tables, ctx, attn, self.scale,
+                                self.window or 0, H, Hkv, D, next_pages=step_hint(ctx, "next_cache"))
+            ops.prefetch_next(step_hint(ctx, "weights_after_mixer"))
+            ops.linear(attn, self.w_o, out)
+            ops.prefetch_next(None)
+            return
         ops.prefetch_next(self.w_o)
         ops.linear(x, self.w_qkv, qkv)
         if self.pos is not None and not fused_rope:

@@ -204,6 +204,10 @@ def swiglu_small_applies(M, I, K, dtype):
     return False                 # the host-side tests take the route of separate operations
 
 
+def qkv_rope_small_applies(M, N, K, dtype, head_dim, rotary_dim):
+    return False                 # the host-side tests take the route of separate operations
+
+
 def copy_pages(cache, pairs):
     """cache [slots, pages, ...]: page pairs[2 i] of every slot is copied to page pairs[2 i + 1]."""
     flat = pairs.tolist()
@@ -211,7 +215,7 @@ def copy_pages(cache, pairs):
         cache[:, dst] = cache[:, src].clone()
 
 
-_NAMES = ["copy_pages", "swiglu_small_applies", "prepare_matrix", "embedding", "add_rmsnorm", "add_rmsnorm_rows", "linear",
+_NAMES = ["copy_pages", "swiglu_small_applies", "qkv_rope_small_applies", "prepare_matrix", "embedding", "add_rmsnorm", "add_rmsnorm_rows", "linear",
           "qk_norm_rope_kv_write", "rope_neox", "rope_table", "place_tokens", "swiglu_fused_applies", "plan_attention", "paged_attention", "silu_mul", "linear_silu_mul",
           "argmax", "sample"]
 

@@ -363,6 +363,54 @@ def test_linear_qkv_rope_fused(T, Hq, Hkv, K, P, norm, write_kv):
     assert float(flat[mask].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("T,Hq,Hkv,K,P", [(1, 16, 8, 1024, 16), (8, 16, 8, 1024, 16), (3, 4, 2, 136, 16), (13, 3, 1, 72, 4),
+                                          (16, 32, 8, 2560, 16), (9, 2, 2, 64, 24), (16, 4, 2, 256, 16)])
+@pytest.mark.parametrize("norm", [True, False])
+@pytest.mark.parametrize("angles", ["positions", "table", "none"])
+@pytest.mark.parametrize("write_kv", [True, False])
+def test_linear_qkv_rope_small(T, Hq, Hkv, K, P, norm, angles, write_kv):
+    """The QKV product of a few rows with per-head norm, rotation and cache write in its epilogue (a cluster of 8 CTAs
+    per head of 128, which exchange sums of squares and rotation partners through distributed shared memory), against
+    the plain product followed by the plain norm + rotation + cache write: q in place, k and v in the cache only,
+    untouched slots and (without a cache write) the whole cache unchanged; 1 to 16 rows, K down to one slice of a
+    single warp, a page size that is no power of two, angles from positions, from the step's table, or none."""
+    D, dtype = 128, torch.bfloat16
+    N = (Hq + 2 * Hkv) * D
+    x = _randn((T, K), dtype, 31)
+    w = (_randn((N, K), torch.float32, 32) / math.sqrt(K)).to(dtype)
+    positions = torch.randint(0, 40000, (T,), generator=torch.Generator().manual_seed(33), dtype=torch.int32)
+    positions[:1] = 39999
+    qw = (1 + 0.2 * _randn((D,), torch.float32, 34)) if norm else None
+    kw = (1 + 0.2 * _randn((D,), torch.float32, 35)) if norm else None
+    inv_freq = 1.0 / (1e6 ** (torch.arange(0, D, 2, dtype=torch.float32) / D))
+    pages = -(-T // P) + 3
+    slots = torch.randperm(pages * P, generator=torch.Generator().manual_seed(36))[:T].to(torch.int32)
+    qkv_ref = (x.float() @ w.float().t()).to(dtype)
+    cache_ref = torch.zeros(pages, 2, Hkv, P, D, dtype=dtype)
+    rotates = angles != "none"
+    ref_ops.qk_norm_rope_kv_write(qkv_ref, positions, qw, kw, 1e-6, inv_freq if rotates else None, D if rotates else 0,
+                                  cache_ref, slots, Hq, Hkv, D, write_kv=write_kv)
+    table = None
+    if angles == "table":
+        table = torch.empty(T, D // 2, 2, dtype=torch.float32, device=DEV)
+        ops.rope_table(positions.to(DEV), inv_freq.to(DEV), table)
+    cache_gpu = torch.zeros(pages, 2, Hkv, P, D, dtype=dtype, device=DEV)
+    qkv_gpu = torch.zeros(T, N, dtype=dtype, device=DEV)
+    assert not ops.QKV_ROPE_SMALL and not ops.qkv_rope_small_applies(T, N, K, dtype, D, D)      # off by default (measured slower than the two kernels)
+    ops.linear_qkv_rope_small(x.to(DEV), w.to(DEV), qkv_gpu, qw.to(DEV) if norm else None, kw.to(DEV) if norm else None, 1e-6,
+                              positions.to(DEV), inv_freq.to(DEV) if rotates else None, table, cache_gpu, slots.to(DEV),
+                              Hq, Hkv, write_kv=write_kv)
+    torch.cuda.synchronize()
+    _close(qkv_gpu[:, :Hq * D], qkv_ref[:, :Hq * D], dtype)
+    assert float(qkv_gpu[:, Hq * D:].abs().max()) == 0.0          # k and v are not written to the product's buffer
+    _close(cache_gpu, cache_ref, dtype)
+    mask = torch.ones(pages * P, dtype=torch.bool)
+    if write_kv:
+        mask[slots.long()] = False
+    flat = cache_gpu.cpu().permute(0, 3, 1, 2, 4).reshape(pages * P, -1)
+    assert float(flat[mask].abs().max()) == 0.0
+
+
 def _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, seed, spike=None):
     """Build a paged cache with scattered pages for requests with ctx_lens[r] cached tokens and
     q_lens[r] new ones; returns everything both implementations need."""
