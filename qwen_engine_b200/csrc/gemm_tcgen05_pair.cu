@@ -71,11 +71,56 @@ struct __align__(1024) PrSmem {
   int abort_flag;
 };
 
+// K split over S pairs of a cluster: CTA (pair `cpair`, parity `rank`) finishes 1 / S of the columns of its 128 rows.
+// `stg`: this CTA's sums in shared memory, row r at r x BN x 4 bytes, 16-byte chunks XORed with the row's low bits;
+// the other shares lie at the same place in the CTAs of the same parity.  The loads of four chunks' shares are all
+// in flight before the first is used (a load from another CTA's shared memory takes some hundreds of cycles).
+template <typename TOut, int BN, int S>
+__device__ __forceinline__ void pr_meet_shares(const unsigned char* stg, TOut* __restrict__ out, int M, int N, int m0, int n0,
+                                               uint32_t rank, uint32_t cpair) {
+  constexpr int CPR = (BN / 4) / S;                  // 16-byte chunks of a row that this CTA finishes
+  constexpr int BATCH = 4;
+  static_assert((PR_BM * CPR) % (PR_EPI_WARPS * 32 * BATCH) == 0, "whole batches per thread");
+  const int t = (int)threadIdx.x - 64;
+  uint32_t base[S];
+#pragma unroll
+  for (int sp = 0; sp < S; ++sp) base[sp] = cluster_map_shared(stg, (uint32_t)(2 * sp) + rank);
+#pragma unroll 1
+  for (int item0 = t; item0 < PR_BM * CPR; item0 += PR_EPI_WARPS * 32 * BATCH) {
+    float4 v[BATCH][S];
+#pragma unroll
+    for (int b = 0; b < BATCH; ++b) {
+      const int item = item0 + b * PR_EPI_WARPS * 32;
+      const int rr = item / CPR, chunk = (int)cpair * CPR + item % CPR;
+      const uint32_t off = (uint32_t)rr * (BN * 4) + (uint32_t)((chunk ^ (rr & 7)) << 4);
+#pragma unroll
+      for (int sp = 0; sp < S; ++sp) v[b][sp] = cluster_ld_f32x4(base[sp] + off);
+    }
+#pragma unroll
+    for (int b = 0; b < BATCH; ++b) {
+      const int item = item0 + b * PR_EPI_WARPS * 32;
+      const int rr = item / CPR, chunk = (int)cpair * CPR + item % CPR;
+      float4 acc = v[b][0];                          // in the order of the shares
+#pragma unroll
+      for (int sp = 1; sp < S; ++sp) { acc.x += v[b][sp].x; acc.y += v[b][sp].y; acc.z += v[b][sp].z; acc.w += v[b][sp].w; }
+      const int row = m0 + rr, col = n0 + chunk * 4;
+      if (row < M && col < N) {                      // N is a multiple of 8 here (the launcher's rule)
+        if constexpr (sizeof(TOut) == 2) {
+          __nv_bfloat162 p0 = __floats2bfloat162_rn(acc.x, acc.y), p1 = __floats2bfloat162_rn(acc.z, acc.w);
+          *reinterpret_cast<uint2*>(out + (size_t)row * N + col) = make_uint2(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1));
+        } else {
+          *reinterpret_cast<float4*>(out + (size_t)row * N + col) = acc;
+        }
+      }
+    }
+  }
+}
+
 // N: columns of the product (SWIGLU: 2 I); n_up: SWIGLU: the first row of up in w (= I), else 0
 template <typename TOut, int BN, int STAGES, bool SWIGLU, bool ROPE = false>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PR_THREADS, 1)
+__global__ void __launch_bounds__(PR_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                         TOut* __restrict__ out, int M, int N, int K, int n_up, PrRope rp) {
+                         TOut* __restrict__ out, int M, int N, int K, int n_up, PrRope rp, int splits) {
   static_assert(!SWIGLU || BN == 256, "the fused activation pairs 128 columns of gate with 128 of up");
   static_assert(!ROPE || (BN == 256 && !SWIGLU && sizeof(TOut) == 2), "the fused rotation takes two heads of 128 per tile, in bfloat16");
   extern __shared__ unsigned char smem_raw[];
@@ -85,11 +130,19 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   pdl_launch_dependents();
   Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t rank = cluster_cta_rank();          // 0: the leading CTA of the pair
-  const int num_kb = (K + PR_BK - 1) / PR_BK;
+  // The cluster is one pair, or (plain products with few tiles) `splits` pairs that work on the same tile with
+  // a share of K each; ranks 2p and 2p + 1 are pair p.
+  const uint32_t crank = cluster_cta_rank();
+  const uint32_t rank = crank & 1u;                  // 0: the leading CTA of the pair
+  const uint32_t cpair = crank >> 1;                 // which share of K
+  const uint16_t pair_mask = (uint16_t)(3u << (2 * cpair));
+  const int all_kb = (K + PR_BK - 1) / PR_BK;
+  const int kb_per = (all_kb + splits - 1) / splits;
+  const int kb_first = (int)cpair * kb_per;
+  const int num_kb = max(0, min(all_kb, kb_first + kb_per) - kb_first);     // this pair's k-blocks (the launcher leaves none empty)
   const int n_blocks = SWIGLU ? (n_up + BN / 2 - 1) / (BN / 2) : (N + BN - 1) / BN;
   const int n_tiles = n_blocks * ((M + 2 * PR_BM - 1) / (2 * PR_BM));
-  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int pair = (int)blockIdx.x / (2 * splits), n_pairs = (int)gridDim.x / (2 * splits);   // (with splits: which cluster, how many)
   volatile int* abort_flag = &sm.abort_flag;
 
   // Everything up to the first load of x needs nothing from the kernel before this one (the weights
@@ -107,6 +160,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   cluster_sync_all();                                // barriers and tensor memory of both CTAs are ready
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
+  bool split_staged = false;                         // K split over pairs: this thread has put its sums into shared memory
 
   if (warp == 0) {
     // ---- producer: this CTA's rows of x and its half of the rows of w; bytes counted in the leading CTA
@@ -116,7 +170,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
       const uint32_t ahead = total < (uint32_t)STAGES ? total : (uint32_t)STAGES;
       auto coords = [&](uint32_t kc, int& m0, int& n0, int& kb) {
         const int t = (int)(kc / (uint32_t)num_kb);
-        kb = (int)(kc - (uint32_t)t * (uint32_t)num_kb);
+        kb = kb_first + (int)(kc - (uint32_t)t * (uint32_t)num_kb);
         const int tile = pair + t * n_pairs;
         m0 = (tile / n_blocks) * 2 * PR_BM + (int)rank * PR_BM;
         n0 = SWIGLU ? (tile % n_blocks) * (BN / 2) + (int)rank * n_up      // gate rows, or the same rows of up
@@ -164,9 +218,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
           const uint64_t db = make_smem_desc(smem_u32(sm.b[s]));
 #pragma unroll
           for (int k = 0; k < PR_BK / 16; ++k) tc_mma_bf16_pair(acc, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
-          tc_commit_pair(&sm.empty[s], 3);             // both CTAs' producers may refill the slot
+          tc_commit_pair(&sm.empty[s], pair_mask);     // both CTAs' producers may refill the slot
         }
-        if (ok) tc_commit_pair(&sm.acc_full[buf], 3);
+        if (ok) tc_commit_pair(&sm.acc_full[buf], pair_mask);
       }
     }
   } else {
@@ -358,6 +412,23 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
           }
           pr_epilogue_sync();                        // the buffer is free for the next head
         }
+      } else if (splits > 1) {
+        // K split over the cluster's pairs: this pair's sums go to shared memory (the ring is idle: every load
+        // has been used and every product has retired), row r at r x BN x 4 bytes, 16-byte chunks XORed with the
+        // row's low bits; they meet after the cluster's barrier below
+        unsigned char* stg = reinterpret_cast<unsigned char*>(sm.a);
+        const int r_mine = quarter * 32 + lane;
+#pragma unroll 1
+        for (int c0 = ch * (BN / 2); c0 < (ch + 1) * (BN / 2); c0 += 32) {
+          uint32_t r[32];
+          tc_ld_32x32b_x32(tmem + ((uint32_t)(quarter * 32) << 16) + buf * BN + c0, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(stg + (size_t)r_mine * (BN * 4) + ((((c0 >> 2) + j) ^ (r_mine & 7)) << 4)) =
+                make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+        }
+        split_staged = true;
       } else {
 #pragma unroll 1
       for (int c0 = ch * (BN / 2); c0 < (ch + 1) * (BN / 2); c0 += 32) {
@@ -401,6 +472,19 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
       }   // plain epilogue
     }
   }
+  if (splits > 1) {
+    // ---- K split over the cluster's pairs: the shares meet ------------------------------------------------
+    // Every CTA finishes 1 / splits of the columns of its 128 rows: it adds up, in the order of the shares, what
+    // the CTAs with its rows (the same parity in every pair) hold for those columns, and stores them, lanes along
+    // the columns.  Reached by every thread of the cluster, whatever happened before.
+    cluster_sync_all();
+    if (warp >= 2 && split_staged) {
+      const int tile = pair;
+      const int m0 = (tile / n_blocks) * 2 * PR_BM + (int)rank * PR_BM, n0 = (tile % n_blocks) * BN;
+      if (splits == 2) pr_meet_shares<TOut, BN, 2>(reinterpret_cast<const unsigned char*>(sm.a), out, M, N, m0, n0, rank, cpair);
+      else pr_meet_shares<TOut, BN, 4>(reinterpret_cast<const unsigned char*>(sm.a), out, M, N, m0, n0, rank, cpair);
+    }
+  }
   // both CTAs meet here: neither leaves while the other may still signal its barriers, read its
   // shared memory or write its tensor memory; then the allocating warps free the tensor memory
   pdl_wait();                                        // no thread leaves before the kernel before this one has completed
@@ -414,7 +498,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
 
 template <int BN, int STAGES, bool SWIGLU = false, bool ROPE = false>
 static int launch_pair(const void* x, const void* w, void* out, int M, int N, int K, int out_f32, int sms, cudaStream_t stream,
-                       PrRope rp = PrRope{}) {
+                       PrRope rp = PrRope{}, int splits = 1) {
   const int n_up = SWIGLU ? N / 2 : 0;
   CUtensorMap map_x, map_w;
   {
@@ -440,18 +524,66 @@ static int launch_pair(const void* x, const void* w, void* out, int M, int N, in
   }
   const long n_blocks = SWIGLU ? (n_up + BN / 2 - 1) / (BN / 2) : (N + BN - 1) / BN;
   const long tiles = n_blocks * ((M + 2 * PR_BM - 1) / (2 * PR_BM));
-  const long pairs = tiles < sms / 2 ? tiles : sms / 2;
+  // one cluster per pair of SMs walks over the tiles; with K split, a cluster of `splits` pairs per tile
+  const long pairs = splits > 1 ? tiles * splits : (tiles < sms / 2 ? tiles : sms / 2);
   const dim3 grid((unsigned)(2 * pairs));
+  const unsigned cluster = 2u * (unsigned)splits;
   if constexpr (ROPE) {
-    qe_launch(gemm_tcgen05_pair_kernel<__nv_bfloat16, BN, STAGES, false, true>, grid, dim3(PR_THREADS), smem, stream, map_x, map_w, (__nv_bfloat16*)out, M, N, K, n_up, rp);
+    qe_launch_cluster(gemm_tcgen05_pair_kernel<__nv_bfloat16, BN, STAGES, false, true>, grid, dim3(PR_THREADS), smem, stream, cluster, map_x, map_w, (__nv_bfloat16*)out, M, N, K, n_up, rp, 1);
   } else {
     if (out_f32)
-      qe_launch(gemm_tcgen05_pair_kernel<float, BN, STAGES, SWIGLU, false>, grid, dim3(PR_THREADS), smem, stream, map_x, map_w, (float*)out, M, N, K, n_up, rp);
+      qe_launch_cluster(gemm_tcgen05_pair_kernel<float, BN, STAGES, SWIGLU, false>, grid, dim3(PR_THREADS), smem, stream, cluster, map_x, map_w, (float*)out, M, N, K, n_up, rp, splits);
     else
-      qe_launch(gemm_tcgen05_pair_kernel<__nv_bfloat16, BN, STAGES, SWIGLU, false>, grid, dim3(PR_THREADS), smem, stream, map_x, map_w, (__nv_bfloat16*)out, M, N, K, n_up, rp);
+      qe_launch_cluster(gemm_tcgen05_pair_kernel<__nv_bfloat16, BN, STAGES, SWIGLU, false>, grid, dim3(PR_THREADS), smem, stream, cluster, map_x, map_w, (__nv_bfloat16*)out, M, N, K, n_up, rp, splits);
   }
   QE_CHECK_LAUNCH("linear_tcgen05_pair");
   return 0;
+}
+
+// Into how many pairs per 256 x 256 tile the CTA-pair product splits K for this shape (1: it does not): as many of
+// 4, 2 as keep every cluster on the GPU at once.  sms <= 0: this device's.
+static int g_pair_split_max = 4;
+extern "C" void qe_pair_k_splits_max(int splits) { g_pair_split_max = splits < 1 ? 1 : (splits > 4 ? 4 : splits); }
+extern "C" int qe_pair_k_splits(int M, int N, int K, int sms) {
+  if (sms <= 0) {
+    int dev = 0;
+    sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  if (M <= 0 || N <= 0 || K <= 0 || N % 8) return 1;
+  const long tiles = (long)((N + 255) / 256) * ((M + 2 * PR_BM - 1) / (2 * PR_BM));
+  const int all_kb = (K + PR_BK - 1) / PR_BK;
+  // (clusters of 8 CTAs with an SM each fit a GPC of some 18 SMs twice: count 16 SMs a GPC for them)
+  for (int s = g_pair_split_max; s >= 2; s >>= 1)
+    if (tiles * s <= (s == 4 ? sms / 2 * 16 / 18 : sms / 2) && all_kb >= 4 * s) return s;
+  return 1;
+}
+
+// How many clusters of `cluster_ctas` CTAs of the plain 256-column kernel the device holds at once (their shared
+// memory leaves room for one CTA per SM, and a cluster has to lie in one GPC); 0 if the driver cannot say.
+extern "C" int qe_pair_max_active_clusters(int cluster_ctas) {
+  static int cached[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+  if (cluster_ctas < 2 || cluster_ctas > 8) return 0;
+  if (cached[cluster_ctas] == 0) {
+    const size_t smem = sizeof(PrSmem<256, 6, false>) + 1024;
+    auto kernel = gemm_tcgen05_pair_kernel<__nv_bfloat16, 256, 6, false, false>;
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)cluster_ctas * 64);
+    cfg.blockDim = dim3(PR_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)cluster_ctas;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) { cudaGetLastError(); n = -1; }
+    cached[cluster_ctas] = n > 0 ? n : -1;
+  }
+  return cached[cluster_ctas] > 0 ? cached[cluster_ctas] : 0;
 }
 
 extern "C" int qe_gemm_tc_pair_status() {
@@ -473,9 +605,12 @@ extern "C" int qe_linear_tcgen05_pair(const void* x, const void* w, void* out, i
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (sms < 2) QE_REFUSE("linear_tcgen05_pair: needs at least two SMs");
-  // wide tiles when they give every pair of SMs a tile; else narrow ones
+  // wide tiles when they give every pair of SMs a tile; with fewer, K is split over 2 or 4 pairs per tile where
+  // that still leaves every pair 4 k-blocks or more; else narrow tiles
   const long wide_tiles = (long)((N + 255) / 256) * ((M + 2 * PR_BM - 1) / (2 * PR_BM));
   if (wide_tiles >= sms / 2) return launch_pair<256, 6>(x, w, out, M, N, K, out_f32, sms, stream);
+  const int splits = qe_pair_k_splits(M, N, K, sms);
+  if (splits > 1) return launch_pair<256, 6>(x, w, out, M, N, K, out_f32, sms, stream, PrRope{}, splits);
   return launch_pair<128, 8>(x, w, out, M, N, K, out_f32, sms, stream);
 }
 

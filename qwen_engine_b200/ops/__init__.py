@@ -408,11 +408,24 @@ def linear(x, w: torch.Tensor, out: torch.Tensor) -> None:
         # enough 256 x 256 tiles for every pair of SMs: pairs of CTAs share a tile (tcgen05 cta_group::2)
         linear_pairs(x, w, out)
         return
+    if (x.dtype == torch.bfloat16 and TCGEN05_PAIRS and TCGEN05_ENABLED and PAIR_SPLIT_K and K % 8 == 0
+            and M > SMALL_M_MAX and pair_k_splits(M, N, K) > 1):
+        # too few such tiles, a long K: 2 or 4 pairs per tile with a share of K each, meeting on chip
+        linear_pairs(x, w, out)
+        return
     if x.dtype == torch.bfloat16 and M > SMALL_M_MAX and K % 8 == 0 and TCGEN05_ENABLED:
         # many rows: TMA-fed tcgen05 tensor cores with the accumulator in tensor memory
         _check(lib().qe_linear_tcgen05(_ptr(x), _ptr(w), _ptr(out), M, N, K, out_f32, _stream()), "linear")
         return
     _check(lib().qe_linear_generic(_ptr(x), _ptr(w), _ptr(out), M, N, K, _dt(x), out_f32, _stream()), "linear")
+
+
+PAIR_SPLIT_K = True     # products with few 256 x 256 tiles and a long K: K split over the pairs of a cluster
+
+
+def pair_k_splits(M: int, N: int, K: int) -> int:
+    """Into how many CTA pairs per 256 x 256 tile ``linear_pairs`` splits K for this shape (1: it does not)."""
+    return int(lib().qe_pair_k_splits(int(M), int(N), int(K), 0))
 
 
 def linear_pairs(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:

@@ -108,6 +108,30 @@ def test_linear_tcgen05_pairs(M, N, K, out_f32):
     _close(got, want, torch.bfloat16, scale=float(want.float().abs().max()))
 
 
+@pytest.mark.parametrize("M,N,K,splits", [(2048, 1024, 2048, 2), (2048, 1024, 3072, 2), (528, 2048, 6144, 2), (300, 1024, 1024, 4),
+                                          (128, 512, 4104, 4), (1000, 1000, 520, 2), (65, 2048, 2048, 4), (700, 2560, 9728, 2)])
+@pytest.mark.parametrize("out_f32", [False, True])
+def test_linear_tcgen05_pairs_that_split_k(M, N, K, splits, out_f32):
+    """Products with too few 256 x 256 tiles for every pair of SMs: 2 or 4 pairs of a cluster take a share of K of
+    the same tile and their sums meet through distributed shared memory, every CTA finishing a share of the
+    columns; edges in M, N and K (a last k-block that is not whole, shares of unequal length)."""
+    assert ops.pair_k_splits(M, N, K) == splits
+    x = _randn((M, K), torch.bfloat16, 28)
+    w = _randn((N, K), torch.bfloat16, 29, 0.1)
+    odt = torch.float32 if out_f32 else torch.bfloat16
+    want = torch.empty(M, N, dtype=odt)
+    ref_ops.linear(x, w, want)
+    got = torch.full((M, N), float("nan"), dtype=odt, device=DEV)
+    ops.linear_pairs(x.to(DEV), w.to(DEV), got)
+    torch.cuda.synchronize()
+    assert ops.tcgen05_status() == 0
+    _close(got, want, torch.bfloat16, scale=float(want.float().abs().max()))
+    # the route that `linear` takes for such shapes
+    got2 = torch.full((M, N), float("nan"), dtype=odt, device=DEV)
+    ops.linear(x.to(DEV), w.to(DEV), got2)
+    assert torch.equal(got2, got)
+
+
 @pytest.mark.parametrize("M,I,K", [(256, 128, 64), (300, 200, 136), (2048, 3072, 1024), (1000, 1032, 72), (4100, 392, 200)])
 @pytest.mark.parametrize("out_f32", [False, True])
 def test_linear_swiglu_fused(M, I, K, out_f32):
