@@ -106,12 +106,6 @@ class CacheManager:
                 assert isinstance(g.spec, FixedStateSpec)
                 shape = (len(g.cache_slots), num_state_slots) + tuple(g.spec.shape)
                 g.tensor = torch.zeros(shape, dtype=g.spec.dtype, device=self.device)
-        if self.device.type == "cuda":
-            # The fills above are done before any step is queued.  Seen on a B200: with the zero fill of a cache of
-            # several GB still running, steps queued behind it (kernels launched with programmatic dependent launch,
-            # a decode step launched ahead) now and then read the first prompt's keys wrongly, although every one of
-            # them is ordered behind the fill on the same stream; with the fill complete first, never.
-            torch.cuda.synchronize(self.device)
         self.live: dict[object, RequestCache] = {}
         self._page_copies: list[tuple[int, int, int]] = []     # (group, src page, dst page)
         # counters for the engine's statistics

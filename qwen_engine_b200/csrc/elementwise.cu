@@ -14,9 +14,11 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
                                  float* __restrict__ out, int H, int V, float* __restrict__ ssq_out, int ssq_ld) {
   __shared__ float scratch[33];
   const int t = blockIdx.x;
-  const int id = ids[t];                           // written by the host's copy, not by a kernel
   pdl_launch_dependents();
   pdl_wait();
+  // after the wait: the ids of a step launched ahead are put in place by a kernel (place_tokens) from the tokens
+  // that the step before it sampled; read earlier, an id could still be the place holder
+  const int id = ids[t];
   float* dst = out + (size_t)t * H;
   if (id < 0 || id >= V) {
     for (int h = threadIdx.x; h < H; h += blockDim.x) dst[h] = __int_as_float(0x7fc00000);
@@ -499,7 +501,10 @@ extern "C" int qe_qk_norm_rope_kv_write(void* q, void* k, const void* v, long q_
 // ---------------------------------------------------------------------------------------
 __global__ void place_tokens_kernel(int* __restrict__ dst, const int* __restrict__ rows, const int* __restrict__ src,
                                     const int* __restrict__ src_index, int n) {
-  pdl_launch_dependents();
+  // No early start of the kernels behind this one (no griddepcontrol.launch_dependents): they begin when this grid
+  // has completed.  The step's kernels do what reads only "the step's index data" before their own wait, and the
+  // token ids that this kernel writes are such data: a dependent that started early, and its dependents after it,
+  // could read an id before it is here.
   pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) dst[rows[i]] = src[src_index[i]];
@@ -521,7 +526,8 @@ extern "C" int qe_place_tokens(int* dst, const int* rows, const int* src, const 
 template <typename U>
 __global__ void copy_pages_kernel(U* __restrict__ cache, long slot_units, long page_units, const int* __restrict__ pairs,
                                   int n_pages) {
-  pdl_launch_dependents();
+  // No early start of the kernels behind this one (as place_tokens): the attention kernels ask for keys and values of
+  // earlier steps before their own wait, and a page copied here holds such keys.
   pdl_wait();
   const int src = pairs[2 * blockIdx.z], dst = pairs[2 * blockIdx.z + 1];
   if (src < 0 || dst < 0 || src >= n_pages || dst >= n_pages || src == dst) return;

@@ -540,25 +540,6 @@ static int launch_pair(const void* x, const void* w, void* out, int M, int N, in
   return 0;
 }
 
-// Into how many pairs per 256 x 256 tile the CTA-pair product splits K for this shape (1: it does not): as many of
-// 4, 2 as keep every cluster on the GPU at once.  sms <= 0: this device's.
-static int g_pair_split_max = 4;
-extern "C" void qe_pair_k_splits_max(int splits) { g_pair_split_max = splits < 1 ? 1 : (splits > 4 ? 4 : splits); }
-extern "C" int qe_pair_k_splits(int M, int N, int K, int sms) {
-  if (sms <= 0) {
-    int dev = 0;
-    sms = 148;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  }
-  if (M <= 0 || N <= 0 || K <= 0 || N % 8) return 1;
-  const long tiles = (long)((N + 255) / 256) * ((M + 2 * PR_BM - 1) / (2 * PR_BM));
-  const int all_kb = (K + PR_BK - 1) / PR_BK;
-  // (clusters of 8 CTAs with an SM each fit a GPC of some 18 SMs twice: count 16 SMs a GPC for them)
-  for (int s = g_pair_split_max; s >= 2; s >>= 1)
-    if (tiles * s <= (s == 4 ? sms / 2 * 16 / 18 : sms / 2) && all_kb >= 4 * s) return s;
-  return 1;
-}
-
 // How many clusters of `cluster_ctas` CTAs of the plain 256-column kernel the device holds at once (their shared
 // memory leaves room for one CTA per SM, and a cluster has to lie in one GPC); 0 if the driver cannot say.
 extern "C" int qe_pair_max_active_clusters(int cluster_ctas) {
@@ -586,6 +567,51 @@ extern "C" int qe_pair_max_active_clusters(int cluster_ctas) {
   return cached[cluster_ctas] > 0 ? cached[cluster_ctas] : 0;
 }
 
+// Which tcgen05 product kernel serves a plain bfloat16 product, by a model of their times fitted to measurements on
+// a B200 (microseconds; kb: k-blocks of 64; rounds: tiles per CTA or cluster):
+//   one CTA per 128 x 128 tile (gemm_tcgen05.cu)        2.1 + rounds x kb x 0.36
+//   a pair per 256 x 128 tile                           5.4 + rounds x kb x 0.31
+//   a pair per 256 x 256 tile                           3.1 + rounds x (0.4 + kb x 0.42)
+//   2 or 4 pairs per 256 x 256 tile, a share of K each  8.0 + kb / pairs x 0.33   (one tile per cluster; the device
+//                                                       holds 33 clusters of 4 CTAs and 15 of 8 at once)
+// (2048 rows: 1024 x 2048 13.7 / 15.3 / - / 12.7 us, 1024 x 3072 19.4 / 20.3 / - / 15.3, 2048 x 2048 24.4 / - / 16.9 / -,
+// 4096 x 1024 17.7 / - / 17.3 / -; 528 rows: 1024 x 3072 19.9 / 21.3 / - / 13.2, 4096 x 1024 13.3 / - / 11.3 / -.)
+// Returns 0: the single-CTA kernel, 1: pairs with narrow tiles, 2: pairs with wide tiles, 3 / 4: wide tiles with K
+// split over 2 / 4 pairs.  `pairs_only`: the best of 1..4.
+static int g_pair_split_max = 4;
+extern "C" void qe_pair_k_splits_max(int splits) { g_pair_split_max = splits < 1 ? 1 : (splits > 4 ? 4 : splits); }
+extern "C" int qe_tc_product_plan(int M, int N, int K, int pairs_only) {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0, v = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    sms = v > 1 ? v : 148;
+  }
+  if (M <= 0 || N <= 0 || K <= 0) return pairs_only ? 1 : 0;
+  const double kb = (double)((K + PR_BK - 1) / PR_BK);
+  auto rounds = [](long tiles, long slots) { return (double)((tiles + slots - 1) / slots); };
+  const long m128 = (M + 127) / 128, m256 = (M + 255) / 256, n128 = (N + 127) / 128, n256 = (N + 255) / 256;
+  double best = pairs_only ? 1e30 : 2.1 + rounds(m128 * n128, sms) * kb * 0.36;
+  int plan = 0;
+  const double narrow = 5.4 + rounds(m256 * n128, sms / 2) * kb * 0.31;
+  if (narrow < best) { best = narrow; plan = 1; }
+  const double wide = 3.1 + rounds(m256 * n256, sms / 2) * (0.4 + kb * 0.42);
+  if (wide < best) { best = wide; plan = 2; }
+  for (int s = 2; s <= g_pair_split_max; s <<= 1) {
+    const int cap = qe_pair_max_active_clusters(2 * s);
+    if (N % 8 || m256 * n256 > cap || kb < 4 * s) continue;
+    const double split = 8.0 + (double)(((long)kb + s - 1) / s) * 0.33;
+    if (split < best) { best = split; plan = s == 2 ? 3 : 4; }
+  }
+  return plan;
+}
+// Into how many pairs per tile the CTA-pair product splits K for this shape (1: it does not).
+extern "C" int qe_pair_k_splits(int M, int N, int K, int sms) {
+  (void)sms;
+  const int plan = qe_tc_product_plan(M, N, K, 1);
+  return plan == 3 ? 2 : (plan == 4 ? 4 : 1);
+}
+
 extern "C" int qe_gemm_tc_pair_status() {
   int v = 0;
   cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int));
@@ -605,12 +631,10 @@ extern "C" int qe_linear_tcgen05_pair(const void* x, const void* w, void* out, i
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (sms < 2) QE_REFUSE("linear_tcgen05_pair: needs at least two SMs");
-  // wide tiles when they give every pair of SMs a tile; with fewer, K is split over 2 or 4 pairs per tile where
-  // that still leaves every pair 4 k-blocks or more; else narrow tiles
-  const long wide_tiles = (long)((N + 255) / 256) * ((M + 2 * PR_BM - 1) / (2 * PR_BM));
-  if (wide_tiles >= sms / 2) return launch_pair<256, 6>(x, w, out, M, N, K, out_f32, sms, stream);
-  const int splits = qe_pair_k_splits(M, N, K, sms);
-  if (splits > 1) return launch_pair<256, 6>(x, w, out, M, N, K, out_f32, sms, stream, PrRope{}, splits);
+  // wide tiles, wide tiles with K split over 2 or 4 pairs, or narrow tiles: see qe_tc_product_plan
+  const int plan = qe_tc_product_plan(M, N, K, 1);
+  if (plan == 2) return launch_pair<256, 6>(x, w, out, M, N, K, out_f32, sms, stream);
+  if (plan >= 3) return launch_pair<256, 6>(x, w, out, M, N, K, out_f32, sms, stream, PrRope{}, plan == 3 ? 2 : 4);
   return launch_pair<128, 8>(x, w, out, M, N, K, out_f32, sms, stream);
 }
 

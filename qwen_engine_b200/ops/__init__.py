@@ -404,13 +404,11 @@ def linear(x, w: torch.Tensor, out: torch.Tensor) -> None:
         _check(lib().qe_linear_small_m(_ptr(x), _ptr(w), _ptr(out), M, N, K, out_f32, _stream()), "linear")
         return
     if (x.dtype == torch.bfloat16 and TCGEN05_PAIRS and TCGEN05_ENABLED and K % 8 == 0
-            and -(-M // 256) * -(-N // 256) >= PAIR_MIN_TILES):
-        # enough 256 x 256 tiles for every pair of SMs: pairs of CTAs share a tile (tcgen05 cta_group::2)
-        linear_pairs(x, w, out)
-        return
-    if (x.dtype == torch.bfloat16 and TCGEN05_PAIRS and TCGEN05_ENABLED and PAIR_SPLIT_K and K % 8 == 0
-            and M > SMALL_M_MAX and pair_k_splits(M, N, K) > 1):
-        # too few such tiles, a long K: 2 or 4 pairs per tile with a share of K each, meeting on chip
+            and (-(-M // 256) * -(-N // 256) >= PAIR_MIN_TILES
+                 or (PAIR_PLAN and M > SMALL_M_MAX and tc_product_plan(M, N, K) != 0))):
+        # pairs of CTAs share a 256-row tile (tcgen05 cta_group::2): enough 256 x 256 tiles for every pair of SMs,
+        # or the library's model of the kernels' times says so (fewer tiles: wide tiles all the same, or 2 or 4 pairs
+        # per tile with a share of a long K each, meeting on chip)
         linear_pairs(x, w, out)
         return
     if x.dtype == torch.bfloat16 and M > SMALL_M_MAX and K % 8 == 0 and TCGEN05_ENABLED:
@@ -420,7 +418,13 @@ def linear(x, w: torch.Tensor, out: torch.Tensor) -> None:
     _check(lib().qe_linear_generic(_ptr(x), _ptr(w), _ptr(out), M, N, K, _dt(x), out_f32, _stream()), "linear")
 
 
-PAIR_SPLIT_K = True     # products with few 256 x 256 tiles and a long K: K split over the pairs of a cluster
+PAIR_PLAN = True        # products of many rows with fewer than PAIR_MIN_TILES tiles go where the library's model of the kernels' times sends them
+
+
+def tc_product_plan(M: int, N: int, K: int) -> int:
+    """Which tcgen05 kernel serves a plain bfloat16 product of more than 64 rows: 0 the single-CTA kernel, 1 CTA
+    pairs with 256 x 128 tiles, 2 with 256 x 256 tiles, 3 / 4 with K split over 2 / 4 pairs per tile."""
+    return int(lib().qe_tc_product_plan(int(M), int(N), int(K), 0))
 
 
 def pair_k_splits(M: int, N: int, K: int) -> int:

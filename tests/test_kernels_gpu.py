@@ -109,7 +109,7 @@ def test_linear_tcgen05_pairs(M, N, K, out_f32):
 
 
 @pytest.mark.parametrize("M,N,K,splits", [(2048, 1024, 2048, 2), (2048, 1024, 3072, 2), (528, 2048, 6144, 2), (300, 1024, 1024, 4),
-                                          (128, 512, 4104, 4), (1000, 1000, 520, 2), (65, 2048, 2048, 4), (700, 2560, 9728, 2)])
+                                          (128, 512, 4104, 4), (1000, 1000, 2056, 2), (65, 2048, 2048, 4), (700, 2560, 9728, 2)])
 @pytest.mark.parametrize("out_f32", [False, True])
 def test_linear_tcgen05_pairs_that_split_k(M, N, K, splits, out_f32):
     """Products with too few 256 x 256 tiles for every pair of SMs: 2 or 4 pairs of a cluster take a share of K of
@@ -126,10 +126,24 @@ def test_linear_tcgen05_pairs_that_split_k(M, N, K, splits, out_f32):
     torch.cuda.synchronize()
     assert ops.tcgen05_status() == 0
     _close(got, want, torch.bfloat16, scale=float(want.float().abs().max()))
-    # the route that `linear` takes for such shapes
-    got2 = torch.full((M, N), float("nan"), dtype=odt, device=DEV)
-    ops.linear(x.to(DEV), w.to(DEV), got2)
-    assert torch.equal(got2, got)
+    if ops.tc_product_plan(M, N, K) != 0:              # the route that `linear` takes where the pairs are the faster kernel
+        got2 = torch.full((M, N), float("nan"), dtype=odt, device=DEV)
+        ops.linear(x.to(DEV), w.to(DEV), got2)
+        assert torch.equal(got2, got)
+
+
+def test_the_plan_of_the_tcgen05_products():
+    """Which kernel `linear` picks for products of many rows (a model of the kernels' times in the library): the
+    single-CTA kernel for few rows and a short K, CTA pairs with wide tiles where those fill most pairs of SMs, K
+    split over pairs where tiles are few and K is long."""
+    plan = ops.tc_product_plan
+    assert plan(128, 4096, 1024) == 0
+    assert plan(2048, 4096, 1024) == 2 and plan(2048, 6144, 1024) == 2
+    assert plan(2048, 2048, 2048) == 2                 # 64 tiles for 74 pairs: wide tiles, one round
+    assert plan(528, 4096, 1024) == 2
+    assert plan(2048, 1024, 2048) == 3 and plan(2048, 1024, 3072) == 3
+    assert plan(528, 1024, 3072) == 4
+    assert plan(8192, 2560, 9728) == 2
 
 
 @pytest.mark.parametrize("M,I,K", [(256, 128, 64), (300, 200, 136), (2048, 3072, 1024), (1000, 1032, 72), (4100, 392, 200)])
