@@ -103,6 +103,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
 flash_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, AtArgs A) {
   extern __shared__ unsigned char smem_raw[];
   pdl_launch_dependents();
+  QE_TL_STAMPS(128);                                // (timeline build: group g's step j leaves stamps 64 g + 4 j ..)
   AtSmem& sm = *reinterpret_cast<AtSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int Hq = A.Hq, Hkv = A.Hkv, window = A.window;
@@ -156,41 +157,41 @@ flash_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
           for (int half = 0; half < 2; ++half)
             tma_load_3d(sm.q[w][half], &map_q, &sm.q_full, half * 64, hkv * G, row0 + q0 + w * tpw);
       }
-      int issued = 0;
+      // Keys and values of a step are asked for separately, each as soon as its slot is free: the keys' slot when
+      // the scores of the step two before have been formed, the values' slot a whole step later, when that step's
+      // P V has retired.  (Asked for together, the keys of step j + 1 waited for the values' slot and arrived
+      // after the tensor cores wanted them: each group waited 1.4 us a step for its scores where the two products
+      // take 0.7.)
+      int issued_k = 0, issued_v = 0;
       for (int j = 0; j < n_steps; ++j) {
         const int st = j & 1;
-        bool ok = true;
-        if (j >= 2) {
-          const uint32_t par = ((j >> 1) - 1) & 1;
-          ok = mbar_wait(&sm.k_empty[st], par, abort_flag, 1, &g_at_status) &&
-               mbar_wait(&sm.v_empty[st], par, abort_flag, 2, &g_at_status);
-        }
-        if (!__all_sync(0xffffffffu, ok)) break;
-        if (lane == 0) {
-          mbar_expect_tx(&sm.k_full[st], AT_BN * AT_D * (uint32_t)sizeof(__nv_bfloat16));
-          mbar_expect_tx(&sm.v_full[st], AT_BN * AT_D * (uint32_t)sizeof(__nv_bfloat16));
-        }
-        __syncwarp();
+        const uint32_t par = ((j >> 1) - 1) & 1;
         const int kt = kt_first + j * AT_BN;
-        for (int idx = lane; idx < 4 * nb; idx += 32) {
-          const int kind = idx / (2 * nb), rem = idx - kind * 2 * nb;
-          const int box = rem >> 1, half = rem & 1;
-          const int key0 = kt + box * box_rows;
-          const int blk = key0 >> page_shift, y = key0 & (page_size - 1);
-          int page = blk < A.max_blocks ? table[blk] : -1;
-          if (page < 0) page = A.num_pages;         // outside the tensor: the box is filled with zeros
-          __nv_bfloat16* dst = (kind ? sm.v[st][half] : sm.k[st][half]) + (size_t)box * box_rows * 64;
-          tma_load_5d(dst, &map_kv, kind ? &sm.v_full[st] : &sm.k_full[st], half * 64, y, hkv, kind, page);
+        for (int kind = 0; kind < 2; ++kind) {
+          bool ok = true;
+          if (j >= 2) ok = mbar_wait(kind ? &sm.v_empty[st] : &sm.k_empty[st], par, abort_flag, 1 + kind, &g_at_status);
+          if (!__all_sync(0xffffffffu, ok)) { j = n_steps; break; }
+          if (lane == 0) mbar_expect_tx(kind ? &sm.v_full[st] : &sm.k_full[st], AT_BN * AT_D * (uint32_t)sizeof(__nv_bfloat16));
+          __syncwarp();
+          for (int idx = lane; idx < 2 * nb; idx += 32) {
+            const int box = idx >> 1, half = idx & 1;
+            const int key0 = kt + box * box_rows;
+            const int blk = key0 >> page_shift, y = key0 & (page_size - 1);
+            int page = blk < A.max_blocks ? table[blk] : -1;
+            if (page < 0) page = A.num_pages;       // outside the tensor: the box is filled with zeros
+            __nv_bfloat16* dst = (kind ? sm.v[st][half] : sm.k[st][half]) + (size_t)box * box_rows * 64;
+            tma_load_5d(dst, &map_kv, kind ? &sm.v_full[st] : &sm.k_full[st], half * 64, y, hkv, kind, page);
+          }
+          if (kind) ++issued_v; else ++issued_k;
         }
-        ++issued;
       }
       if (*abort_flag && lane == 0) {
         // giving up: let the copies that are still in flight land before the CTA leaves (bounded)
         for (uint32_t spin = 0; spin < TC_WAIT_LIMIT; ++spin) if (mbar_try_wait(&sm.q_full, 0)) break;
-        for (int i = max(0, issued - 2); i < issued; ++i) {
+        for (int i = max(0, issued_k - 2); i < issued_k; ++i)
           for (uint32_t spin = 0; spin < TC_WAIT_LIMIT; ++spin) if (mbar_try_wait(&sm.k_full[i & 1], (i >> 1) & 1)) break;
+        for (int i = max(0, issued_v - 2); i < issued_v; ++i)
           for (uint32_t spin = 0; spin < TC_WAIT_LIMIT; ++spin) if (mbar_try_wait(&sm.v_full[i & 1], (i >> 1) & 1)) break;
-        }
       }
     }
   } else if (warp == 9) {
@@ -230,6 +231,7 @@ flash_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
           if (!ok) break;
           tc_fence_after();
           issue_pv(w, st, j > 0);
+          if (w == groups - 1) tc_commit(&sm.v_empty[st]);      // the values' slot, as soon as the last P V that reads it retires
           if (more) {
             if (w == 0) {
               ok = mbar_wait(&sm.k_full[nst], ((j + 1) >> 1) & 1, abort_flag, 7, &g_at_status);
@@ -243,7 +245,6 @@ flash_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
           }
         }
         if (!ok) break;
-        tc_commit(&sm.v_empty[st]);
         if (more) tc_commit(&sm.k_empty[nst]);
       }
     }
@@ -267,10 +268,12 @@ flash_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         ok = __all_sync(0xffffffffu, mbar_wait(&sm.s_ready[w], j & 1, abort_flag, 8, &g_at_status));
         if (!ok) break;
         tc_fence_after();
+        QE_TL_STAMP(quarter == 0 && lane == 0 ? 64 * w + 4 * j + 0 : -1);   // (timeline build: the step's scores are ready)
         uint32_t s[4][32];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tc_ld_32x32b_x32(lane_base + s_col + c * 32, s[c]);
         tc_wait_ld();
+        QE_TL_STAMP(quarter == 0 && lane == 0 ? 64 * w + 4 * j + 1 : -1);   // (... and in registers)
         const int kt = kt_first + j * AT_BN;
         float mx = -INFINITY;
         if (kt >= lo && kt + AT_BN <= hi) {
@@ -324,6 +327,7 @@ flash_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
             pk[c >> 1][(c & 1) * 16 + (i >> 1)] = at_pack(p.x, p.y);
           }
         }
+        QE_TL_STAMP(quarter == 0 && lane == 0 ? 64 * w + 4 * j + 2 : -1);   // (... the exponentials are done)
         const float2 s01 = at_add2(sums[0], sums[1]), s23 = at_add2(sums[2], sums[3]);
         l_run = l_run * alpha + ((s01.x + s01.y) + (s23.x + s23.y));
         tc_st_32x32b_x32(lane_base + s_col, pk[0]);
@@ -331,6 +335,7 @@ flash_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(&sm.p_ready[w]);
+        QE_TL_STAMP(quarter == 0 && lane == 0 ? 64 * w + 4 * j + 3 : -1);   // (... P is handed over)
       }
       // ---- the tile's output, or this part's accumulator with max and sum ----------------------------
       if (ok && n_steps > 0) ok = __all_sync(0xffffffffu, mbar_wait(&sm.o_ready[w], 0, abort_flag, 9, &g_at_status));
@@ -453,6 +458,7 @@ flash_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
   // everyone meets here; the allocating warp frees the tensor memory
   tc_fence_before();
   __syncthreads();
+  QE_TL_FLUSH_STAMPS();
   if (warp == 9) {
     tc_fence_after();
     tc_dealloc(tmem, AT_TMEM_COLS);

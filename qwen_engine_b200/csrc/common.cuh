@@ -61,6 +61,9 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 // predecessor alone is enough.  qe_set_pdl(0) turns the attribute off (plain stream order).
 #ifndef QE_TIMELINE
 #define QE_TL_MARK(kind) do { } while (0)
+#define QE_TL_STAMPS(n) do { } while (0)
+#define QE_TL_STAMP(i) do { } while (0)
+#define QE_TL_FLUSH_STAMPS() do { } while (0)
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 #else
@@ -107,6 +110,20 @@ __device__ __forceinline__ void pdl_launch_dependents_at(unsigned file_hash, uns
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
 }
 #define QE_TL_MARK(kind) qe_tl_event(qe_tl_hash(__FILE__), __LINE__, kind)   // a kernel's own marks: kinds 2 and 3
+// Marks inside a loop, where an event (an atomic's round trip to L2) would cost as much as what it measures: a CTA
+// keeps up to n times in shared memory (QE_TL_STAMP(i) by whichever thread the kernel chooses: the i-th stamp;
+// indices outside 0..n-1 are dropped) and thread 0 writes those that were set as events of kind 2, with the stamp's
+// index in the place of the line, when the kernel calls QE_TL_FLUSH_STAMPS at its end (after a barrier).
+#define QE_TL_STAMPS(n) __shared__ unsigned long long qe_tl_stamps[n]; constexpr int qe_tl_max_stamps = n; \
+  for (int i_ = threadIdx.x; i_ < n; i_ += blockDim.x) qe_tl_stamps[i_] = 0ull      /* (a __syncthreads follows before the first stamp) */
+#define QE_TL_STAMP(i) do { if ((i) >= 0 && (i) < qe_tl_max_stamps) { unsigned long long t_; \
+  asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t_)); qe_tl_stamps[i] = t_; } } while (0)
+#define QE_TL_FLUSH_STAMPS() do { if (threadIdx.x == 0 && qe_tl_buf != nullptr) for (int i_ = 0; i_ < qe_tl_max_stamps; ++i_) { \
+  if (qe_tl_stamps[i_] == 0ull) continue; \
+  const unsigned long long idx_ = atomicAdd(qe_tl_buf, 1ull); if (idx_ < qe_tl_buf[1]) { unsigned long long* e_ = qe_tl_buf + 4 + 4 * idx_; \
+  e_[0] = ((unsigned long long)qe_tl_hash(__FILE__) << 32) | ((unsigned long long)(i_ & 0xffff) << 16) | 2ull; \
+  e_[1] = ((unsigned long long)(blockIdx.x + gridDim.x * (blockIdx.y + (unsigned long long)gridDim.y * blockIdx.z)) << 32) | (((unsigned long long)gridDim.x * gridDim.y * gridDim.z) & 0xffffffffull); \
+  e_[2] = qe_tl_stamps[i_]; e_[3] = 0; } } } while (0)
 #define pdl_wait() pdl_wait_at(qe_tl_hash(__FILE__), __LINE__)
 #define pdl_launch_dependents() pdl_launch_dependents_at(qe_tl_hash(__FILE__), __LINE__)
 void qe_tl_register(void (*setter)(unsigned long long*));
