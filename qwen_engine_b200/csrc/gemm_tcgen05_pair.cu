@@ -61,7 +61,7 @@ template <int BN, int STAGES, bool ROPE = false>
 struct __align__(1024) PrSmem {
   __nv_bfloat16 a[STAGES][PR_BM * PR_BK];            // 16 KB each
   __nv_bfloat16 b[STAGES][(BN / 2) * PR_BK];         // this CTA's half of the tile's rows of w
-  __nv_bfloat16 stage[ROPE ? PR_BM * 128 : 8];       // ROPE: one head of this CTA's 128 rows, between the two halves of its epilogue
+  __nv_bfloat16 stage[PR_BM * 128];                  // 32 KB between the accumulator and memory: ROPE: one head of this CTA's 128 rows; else 4 KB per epilogue warp
   float stage_ssq[ROPE ? 2 * PR_BM : 2];             // ... and the sums of squares of the two halves of every row
   uint64_t full[STAGES];                             // used in the leading CTA
   uint64_t empty[STAGES];
@@ -70,6 +70,40 @@ struct __align__(1024) PrSmem {
   uint32_t tmem_base;
   int abort_flag;
 };
+
+// 32 rows x COLS bfloat16 columns of the output, from the warp whose lane l holds row l (as the accumulator leaves
+// tensor memory: packed[i] = columns 2 i, 2 i + 1 of the lane's row), to memory with lanes along the columns: through
+// 4 KB of shared memory of the warp's own (16-byte chunks XORed with the row's low bits), then 128 or 64 bytes of a
+// row per 8 or 4 lanes.  Stored with lanes along the rows, every instruction touched 32 rows with 16 bytes each, and a
+// tile's epilogue took 3.5-5.8 us (measured with the timeline build), as long as its products.
+// dst: row 0, column 0 of the 32 x COLS block; ld: elements per row of the output; rows, cols: how many of them exist.
+template <int COLS>
+__device__ __forceinline__ void pr_store_block(unsigned char* wst, const uint32_t (&packed)[COLS / 2], __nv_bfloat16* dst, size_t ld,
+                                               int rows, int cols, int lane) {
+  constexpr int CH = COLS / 8, RB = COLS * 2, RPI = 32 / CH;     // chunks per row, bytes per row, rows per instruction
+#pragma unroll
+  for (int j = 0; j < CH; ++j)
+    *reinterpret_cast<uint4*>(wst + lane * RB + ((j ^ (lane & (CH - 1))) << 4)) =
+        make_uint4(packed[4 * j], packed[4 * j + 1], packed[4 * j + 2], packed[4 * j + 3]);
+  __syncwarp();
+  const int cj = lane % CH;
+#pragma unroll
+  for (int i = 0; i < CH; ++i) {
+    const int rr = i * RPI + lane / CH;
+    const uint4 v = *reinterpret_cast<const uint4*>(wst + rr * RB + ((cj ^ (rr & (CH - 1))) << 4));
+    if (rr < rows) {
+      __nv_bfloat16* d = dst + (size_t)rr * ld + cj * 8;
+      if (cj * 8 + 8 <= cols) {
+        *reinterpret_cast<uint4*>(d) = v;
+      } else {
+        const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
+        for (int k = 0; k < 8; ++k)
+          if (cj * 8 + k < cols) d[k] = e[k];
+      }
+    }
+  }
+  __syncwarp();
+}
 
 // K split over S pairs of a cluster: CTA (pair `cpair`, parity `rank`) finishes 1 / S of the columns of its 128 rows.
 // `stg`: this CTA's sums in shared memory, row r at r x BN x 4 bytes, 16-byte chunks XORed with the row's low bits;
@@ -128,6 +162,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   constexpr uint32_t TMEM_COLS = 2 * BN;
   constexpr uint32_t STAGE_BYTES = (PR_BM + BN / 2) * PR_BK * sizeof(__nv_bfloat16);
   pdl_launch_dependents();
+  QE_TL_STAMPS(32);
+  QE_TL_STAMP(threadIdx.x == 0 ? 0 : -1);           // (timeline build: the CTA's start)
   Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // The cluster is one pair, or (plain products with few tiles) `splits` pairs that work on the same tile with
@@ -158,6 +194,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   if (warp == 1) tc_alloc_pair(&sm.tmem_base, TMEM_COLS);   // the same warp in both CTAs
   tc_fence_before();
   cluster_sync_all();                                // barriers and tensor memory of both CTAs are ready
+  QE_TL_STAMP(threadIdx.x == 0 ? 1 : -1);           // (... set-up done in both CTAs)
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
   bool split_staged = false;                         // K split over pairs: this thread has put its sums into shared memory
@@ -184,6 +221,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         tma_load_2d_pair(sm.b[kc], &map_w, smem_u32(&sm.full[kc]) & TC_PEER_BIT_MASK, kb * PR_BK, n0);
       }
       pdl_wait();
+      QE_TL_STAMP(2);                                // (... the kernel before has completed)
       for (uint32_t kc = 0; kc < ahead; ++kc) {
         coords(kc, m0, n0, kb);
         tma_load_2d_pair(sm.a[kc], &map_x, smem_u32(&sm.full[kc]) & TC_PEER_BIT_MASK, kb * PR_BK, m0);
@@ -262,48 +300,63 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         }
       }
       bool ok = __all_sync(0xffffffffu, mbar_wait(&sm.acc_full[buf], (it >> 1) & 1, abort_flag, 23, &g_tc_status));
+      QE_TL_STAMP(warp == 2 && lane == 0 ? 16 + 2 * (it > 0) : -1);   // (... a tile's sums are ready: the first, the last)
       if constexpr (ROPE) ok = pr_epilogue_all(ok);    // its warps meet at barriers below: all go on or none
       if (!ok) break;
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
       if constexpr (SWIGLU) {
-        // columns c0.. of gate and of up -> 32 columns of the activation
+        // this warp's 64 columns of gate and of up -> 64 columns of the activation
         const int I = n_up, i0 = (tile % n_blocks) * (BN / 2);
+        constexpr int WC = BN / 4;                   // activation columns per warp
+        if (sizeof(TOut) == 2 && (I % 8) == 0) {
+          // bfloat16 rows whose pieces of 8 are 16-byte aligned: all loads from tensor memory in flight together, then
+          // the accumulator is free; stored with lanes along the columns
+          uint32_t g[WC / 32][32], u[WC / 32][32];
+#pragma unroll
+          for (int q = 0; q < WC / 32; ++q) {
+            tc_ld_32x32b_x32(tmem + ((uint32_t)(quarter * 32) << 16) + buf * BN + ch * WC + 32 * q, g[q]);
+            tc_ld_32x32b_x32(tmem + ((uint32_t)(quarter * 32) << 16) + buf * BN + BN / 2 + ch * WC + 32 * q, u[q]);
+          }
+          tc_wait_ld();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(smem_u32(&sm.acc_empty[buf]) & TC_PEER_BIT_MASK);
+          uint32_t pk[WC / 2];
+#pragma unroll
+          for (int q = 0; q < WC / 32; ++q)
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              const float g0 = __uint_as_float(g[q][j]), g1 = __uint_as_float(g[q][j + 1]);
+              __nv_bfloat162 pj = __floats2bfloat162_rn(__fdividef(g0, 1.f + __expf(-g0)) * __uint_as_float(u[q][j]),
+                                                        __fdividef(g1, 1.f + __expf(-g1)) * __uint_as_float(u[q][j + 1]));
+              pk[16 * q + (j >> 1)] = *reinterpret_cast<uint32_t*>(&pj);
+            }
+          const int r_first = m0 + quarter * 32, c0 = ch * WC;
+          pr_store_block<WC>(reinterpret_cast<unsigned char*>(sm.stage) + (warp - 2) * 4096, pk,
+                             reinterpret_cast<__nv_bfloat16*>(out) + (size_t)r_first * I + i0 + c0, (size_t)I,
+                             M - r_first, I - (i0 + c0), lane);
+        } else {
 #pragma unroll 1
-        for (int c0 = ch * (BN / 4); c0 < (ch + 1) * (BN / 4); c0 += 32) {
+        for (int c0 = ch * WC; c0 < (ch + 1) * WC; c0 += 32) {
           uint32_t g[32], u[32];
           tc_ld_32x32b_x32(tmem + ((uint32_t)(quarter * 32) << 16) + buf * BN + c0, g);
           tc_ld_32x32b_x32(tmem + ((uint32_t)(quarter * 32) << 16) + buf * BN + BN / 2 + c0, u);
           tc_wait_ld();
-          if (c0 + 32 == (ch + 1) * (BN / 4)) {
+          if (c0 + 32 == (ch + 1) * WC) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(smem_u32(&sm.acc_empty[buf]) & TC_PEER_BIT_MASK);
           }
           if (row < M && i0 + c0 < I) {
-            float a[32];
+            TOut* dst = out + (size_t)row * I + i0 + c0;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const float gv = __uint_as_float(g[j]);
-              a[j] = __fdividef(gv, 1.f + __expf(-gv)) * __uint_as_float(u[j]);
-            }
-            TOut* dst = out + (size_t)row * I + i0 + c0;
-            if (i0 + c0 + 32 <= I && (I % 8) == 0 && sizeof(TOut) == 2) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 v;
-                __nv_bfloat162 p0 = __floats2bfloat162_rn(a[j], a[j + 1]), p1 = __floats2bfloat162_rn(a[j + 2], a[j + 3]);
-                __nv_bfloat162 p2 = __floats2bfloat162_rn(a[j + 4], a[j + 5]), p3 = __floats2bfloat162_rn(a[j + 6], a[j + 7]);
-                v.x = *reinterpret_cast<uint32_t*>(&p0); v.y = *reinterpret_cast<uint32_t*>(&p1);
-                v.z = *reinterpret_cast<uint32_t*>(&p2); v.w = *reinterpret_cast<uint32_t*>(&p3);
-                *reinterpret_cast<uint4*>(dst + j) = v;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (i0 + c0 + j < I) dst[j] = from_f32<TOut>(a[j]);
+              if (i0 + c0 + j < I) dst[j] = from_f32<TOut>(__fdividef(gv, 1.f + __expf(-gv)) * __uint_as_float(u[j]));
             }
           }
+        }
         }
       } else if constexpr (ROPE) {
         // Two heads of 128 columns, one after the other, each in two halves.  First every thread takes 64 columns
@@ -429,6 +482,35 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                 make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
         }
         split_staged = true;
+      } else if (sizeof(TOut) == 2 && (N % 8) == 0) {
+        // bfloat16 rows whose pieces of 8 are 16-byte aligned: this warp's half of the columns in one go (all
+        // loads from tensor memory in flight together, then the accumulator is free), stored 64 columns at a time
+        // with lanes along the columns
+        constexpr int NLD = BN / 64;                 // loads of 32 columns
+        uint32_t r[NLD][32];
+#pragma unroll
+        for (int q = 0; q < NLD; ++q)
+          tc_ld_32x32b_x32(tmem + ((uint32_t)(quarter * 32) << 16) + buf * BN + ch * (BN / 2) + 32 * q, r[q]);
+        tc_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(smem_u32(&sm.acc_empty[buf]) & TC_PEER_BIT_MASK);
+        const int r_first = m0 + quarter * 32;
+#pragma unroll
+        for (int h = 0; h < NLD / 2; ++h) {
+          uint32_t pk[32];
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            __nv_bfloat162 pa = __floats2bfloat162_rn(__uint_as_float(r[2 * h][j]), __uint_as_float(r[2 * h][j + 1]));
+            __nv_bfloat162 pb = __floats2bfloat162_rn(__uint_as_float(r[2 * h + 1][j]), __uint_as_float(r[2 * h + 1][j + 1]));
+            pk[j >> 1] = *reinterpret_cast<uint32_t*>(&pa);
+            pk[16 + (j >> 1)] = *reinterpret_cast<uint32_t*>(&pb);
+          }
+          const int c0 = ch * (BN / 2) + 64 * h;
+          pr_store_block<64>(reinterpret_cast<unsigned char*>(sm.stage) + (warp - 2) * 4096, pk,
+                             reinterpret_cast<__nv_bfloat16*>(out) + (size_t)r_first * N + n0 + c0, (size_t)N,
+                             M - r_first, N - (n0 + c0), lane);
+        }
       } else {
 #pragma unroll 1
       for (int c0 = ch * (BN / 2); c0 < (ch + 1) * (BN / 2); c0 += 32) {
@@ -445,17 +527,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
           TOut* dst = out + (size_t)row * N + n0 + c0;
           if (n0 + c0 + 32 <= N && (N % 8) == 0) {
             if constexpr (sizeof(TOut) == 2) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 v;
-                __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
-                __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
-                __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
-                v.x = *reinterpret_cast<uint32_t*>(&p0); v.y = *reinterpret_cast<uint32_t*>(&p1);
-                v.z = *reinterpret_cast<uint32_t*>(&p2); v.w = *reinterpret_cast<uint32_t*>(&p3);
-                *reinterpret_cast<uint4*>(dst + j) = v;
-              }
             } else {
 #pragma unroll
               for (int j = 0; j < 32; j += 4)
@@ -470,6 +541,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         }
       }
       }   // plain epilogue
+      QE_TL_STAMP(warp == 2 && lane == 0 ? 17 + 2 * (it > 0) : -1);   // (... an epilogue warp is done with a tile: the first, the last)
     }
   }
   if (splits > 1) {
@@ -487,13 +559,16 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   }
   // both CTAs meet here: neither leaves while the other may still signal its barriers, read its
   // shared memory or write its tensor memory; then the allocating warps free the tensor memory
+  QE_TL_STAMP(threadIdx.x == 0 ? 24 : -1);          // (... all roles done in this CTA's first thread)
   pdl_wait();                                        // no thread leaves before the kernel before this one has completed
   tc_fence_before();
   cluster_sync_all();
+  QE_TL_STAMP(threadIdx.x == 0 ? 25 : -1);          // (timeline build: the tail's barrier passed)
   if (warp == 1) {
     tc_fence_after();
     tc_dealloc_pair(tmem, TMEM_COLS);
   }
+  QE_TL_FLUSH_STAMPS();
 }
 
 template <int BN, int STAGES, bool SWIGLU = false, bool ROPE = false>
