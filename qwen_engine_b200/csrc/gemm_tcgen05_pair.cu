@@ -405,7 +405,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             }
             sm.stage_ssq[ch * PR_BM + r_mine] = (s4[0] + s4[1]) + (s4[2] + s4[3]);
           }
+          QE_TL_STAMP(warp == 2 && lane == 0 && it == 0 ? 8 + 4 * hh : -1);      // (timeline build: first tile, head hh staged by this warp)
           pr_epilogue_sync();                        // the head is in shared memory
+          QE_TL_STAMP(warp == 2 && lane == 0 && it == 0 ? 9 + 4 * hh : -1);      // (... by all warps)
           if (wanted) {
             const float* w = is_v ? nullptr : (is_q ? rp.qw : rp.kw);
             const float w0 = is_q ? nw_q.x : nw_k.x, w1 = is_q ? nw_q.y : nw_k.y, w2 = is_q ? nw_q.z : nw_k.z, w3 = is_q ? nw_q.w : nw_k.w;
@@ -463,6 +465,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
               }
             }
           }
+          QE_TL_STAMP(warp == 2 && lane == 0 && it == 0 ? 10 + 4 * hh : -1);     // (... this warp's rows of the head are written)
           pr_epilogue_sync();                        // the buffer is free for the next head
         }
       } else if (splits > 1) {
@@ -588,7 +591,13 @@ static int launch_pair(const void* x, const void* w, void* out, int M, int N, in
     const uint32_t box[2] = {PR_BK, BN / 2};
     if (!qe_tensor_map_bf16(w, 2, dims, strides, box, &map_w)) return 1;
   }
+#ifdef QE_TIMELINE
+  // (the timeline build's stamps are 256 bytes of static shared memory, which precede the dynamic part and count as
+  // part of the slack for its alignment: the variant with the staged head uses every byte an SM has)
+  const size_t smem = sizeof(PrSmem<BN, STAGES, ROPE>) + 1024 - 256;
+#else
   const size_t smem = sizeof(PrSmem<BN, STAGES, ROPE>) + 1024;
+#endif
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<__nv_bfloat16, BN, STAGES, SWIGLU, ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
