@@ -438,7 +438,8 @@ def run_workload(name: str, torch, peaks) -> dict:
            "new_tokens_each": new_tokens, "prefill_chunk": chunk, "value": round(generated / wall, 1), "unit": "generated tokens/s",
            "seconds": round(wall, 3), "generated_tokens": generated, "steps": st.steps,
            "prefix_hit_tokens": eng.scheduler.prefix_hit_tokens - hit0, "preemptions": eng.scheduler.num_preemptions - pre0,
-           "graph_replays": loaded.runner.num_graph_replays,
+           "graph_replays": loaded.runner.num_graph_replays, "graph_captures": loaded.runner.num_graph_captures,
+           "capture_seconds": round(loaded.runner.graph_capture_seconds, 3),
            "by_kind": {k: {"steps": v["steps"], "tokens": v["tokens"], "device_ms": round(v["device_ms"], 1)}
                        for k, v in (st.profile or {}).items()}}
     del eng, loaded

@@ -12,6 +12,7 @@ on the host and copied once.
 from __future__ import annotations
 
 import gc
+import time
 from dataclasses import dataclass, field
 from typing import Optional, Sequence
 
@@ -71,6 +72,8 @@ class ModelRunner:
         self._capture_stream = None
         self.capture_all_steps = True         # steps that are not all decoded tokens are captured too when they recur
         self.num_graph_replays = 0
+        self.num_graph_captures = 0
+        self.graph_capture_seconds = 0.0      # host time spent capturing and instantiating graphs
         self.num_steps = 0
         self.last_h2d_bytes = 0
         self.num_tokens_run = 0
@@ -116,6 +119,7 @@ class ModelRunner:
                 for k in list(self._graphs)[:256]:
                     del self._graphs[k]
             graph = torch.cuda.CUDAGraph()
+            t_capture = time.perf_counter()
             before = ops.launch_count
             # captured on a stream of its own between capture_begin and capture_end: the context manager that torch
             # offers for this also collects garbage and empties the allocator's cache on entry, some tens of
@@ -139,6 +143,8 @@ class ModelRunner:
                 if collecting:
                     gc.enable()
             main.wait_stream(self._capture_stream)
+            self.num_graph_captures += 1
+            self.graph_capture_seconds += time.perf_counter() - t_capture
             entry = (graph, logits, ops.launch_count - before, self.arena.buffer)
             self._graphs[graph_key] = entry
         graph, logits, launches, arena_buffer = entry
