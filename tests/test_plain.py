@@ -106,3 +106,19 @@ def test_greedy_generate_is_repeated_argmax(model_folders):
     out = plain.greedy_generate(cfg, w, prompt, 3)
     assert out[0] == int(plain.forward_logits(cfg, w, prompt)[-1].argmax())
     assert out[1] == int(plain.forward_logits(cfg, w, prompt + out[:1])[-1].argmax())
+
+
+def test_the_smoke_tests_model_with_head_size_128_has_clear_first_choices(tmp_path):
+    """`__graft_entry__.smoke()` compares bfloat16 tokens with the plain implementation only while the plain choice is
+    clear (the best logit leads by more than 6 % of the largest); its model with head size 128 must give it something
+    to compare: at least three of its four tokens."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import __graft_entry__ as entry
+    from qwen_engine_b200.weights import write_model_folder
+    cfg, init, prompt = entry.smoke_model_d128()
+    folder = write_model_folder(cfg, str(tmp_path / "d128"), *init)
+    pc, pw = plain.read_model_folder(folder)
+    want = plain.greedy_generate(pc, pw, prompt, 4)
+    assert entry._same_tokens_while_clear(plain, pc, pw, prompt, want, want, "plain against itself") >= 3
