@@ -49,7 +49,7 @@ __device__ __forceinline__ void dm_cp_async16_zfill(void* smem, const void* gmem
 
 template <bool CL, int DM_STAGES, int DM_WARPS>
 __global__ void __launch_bounds__(DM_WARPS * 32, DM_WARPS == 4 ? 2 : 1)
-decode_attention_mma_kernel(FaArgs A, long long prefetch_delta, int early_issue) {
+decode_attention_mma_kernel(FaArgs A, long long prefetch_delta, int early_issue, int push_rows) {
   constexpr int DM_THREADS = DM_WARPS * 32;
   constexpr int DM_WARP_BYTES = DM_WARP_BYTES_OF(DM_STAGES);
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -60,7 +60,22 @@ decode_attention_mma_kernel(FaArgs A, long long prefetch_delta, int early_issue)
   float* s_l = s_m + DM_WARPS * DM_ROWS;                                                     // [warps][16] warps' sums
   __shared__ float m_run[DM_ROWS], l_run[DM_ROWS];  // the CTA's max and sum (read by the cluster's first CTA)
   __shared__ int s_last;
+  __shared__ uint64_t merge_bar;                    // CL, push_rows > 0: in the cluster's first CTA, counts the other parts' bytes
+  __shared__ int s_abort;
   pdl_launch_dependents();
+  if constexpr (CL) {
+    // Parts that meet by being pushed (push_rows > 0: the rows an item may have, for which the launcher has added an
+    // in-box per part behind the warps' memory): the first CTA's barrier is set up, and every CTA says so to the
+    // cluster now and looks for the others' word only when its own part is done.
+    if (push_rows > 0) {
+      if (threadIdx.x == 0) {
+        fa_bar_init(&merge_bar, 1);
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+      }
+      asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    }
+  }
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int hkv = blockIdx.y;
   const int Hq = A.Hq, Hkv = A.Hkv, window = A.window, page_size = A.page_size;
@@ -249,6 +264,71 @@ decode_attention_mma_kernel(FaArgs A, long long prefetch_delta, int early_issue)
     }
   }
   if constexpr (CL) {
+    if (push_rows > 0) {
+      // ---- the parts meet in the cluster's first CTA, pushed there ---------------------------------------
+      // Every other CTA stores its accumulator, max and sum into its in-box in the first CTA's shared memory with
+      // st.async, which counts the bytes on that CTA's barrier, and is done: no CTA waits for another except the first
+      // for the bytes.  (Pulled, the parts cost two barriers of the whole cluster on the step's critical path.)
+      asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");     // (arrived at the top: the barrier exists)
+      const uint32_t crank = cluster_cta_rank();
+      const int S = (int)cluster_num_ctas();        // = n_splits, at most 8
+      float* inbox = s_l + DM_WARPS * DM_ROWS;      // [S - 1][push_rows (D + 2)]: accumulators, then (max, sum) per row
+      const int per = push_rows * (D + 2);
+      if (crank != 0) {
+        const uint32_t dst = cluster_map_shared(inbox + (size_t)(crank - 1) * per, 0);
+        const uint32_t bar = cluster_map_shared(&merge_bar, 0);
+        for (int e = tid; e < nrows * D; e += DM_THREADS) {
+          asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];\n"
+                       :: "r"(dst + 4u * (uint32_t)e), "r"(__float_as_uint(fin[e])), "r"(bar) : "memory");
+          const int r = e / D;
+          if (e - r * D == 0) {
+            asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];\n"
+                         :: "r"(dst + 4u * (uint32_t)(push_rows * D + 2 * r)), "r"(__float_as_uint(m_run[r])), "r"(bar) : "memory");
+            asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];\n"
+                         :: "r"(dst + 4u * (uint32_t)(push_rows * D + 2 * r + 1)), "r"(__float_as_uint(l_run[r])), "r"(bar) : "memory");
+          }
+        }
+        return;
+      }
+      __syncthreads();                              // this CTA's own max and sum of every row are in place
+      if (tid == 0) {
+        const uint32_t bytes = (uint32_t)(S - 1) * (uint32_t)(nrows * D + 2 * nrows) * 4u;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" :: "r"(fa_smem(&merge_bar)), "r"(bytes) : "memory");
+      }
+      if (!fa_bar_wait(&merge_bar, 0, &s_abort, 5)) return;          // bounded: the word says so, nothing is written
+      for (int e = tid; e < nrows * D; e += DM_THREADS) {
+        const int r = e / D, d = e - r * D;
+        float mm[8], ll[8], aa[8];
+        mm[0] = m_run[r]; ll[0] = l_run[r]; aa[0] = fin[e];
+#pragma unroll
+        for (int sp = 1; sp < 8; ++sp) {
+          mm[sp] = -INFINITY; ll[sp] = 0.f; aa[sp] = 0.f;
+          if (sp < S) {
+            const float* box = inbox + (size_t)(sp - 1) * per;
+            mm[sp] = box[push_rows * D + 2 * r];
+            ll[sp] = box[push_rows * D + 2 * r + 1];
+            aa[sp] = box[e];
+          }
+        }
+        // out = sum_s 2^(m_s - m) acc_s / sum_s 2^(m_s - m) l_s, in float32, in the order of the parts
+        float m = -INFINITY;
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp) m = fmaxf(m, mm[sp]);
+        const float mb = m == -INFINITY ? 0.f : m;
+        float l = 0.f, acc = 0.f;
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp) {
+          if (sp < S) {
+            const float wgt = exp2f(mm[sp] - mb);
+            l += wgt * ll[sp];
+            acc += wgt * aa[sp];
+          }
+        }
+        const int ti = r / G, hg = r - ti * G;
+        out_row0[(size_t)ti * ((size_t)Hq * D) + (size_t)(hkv * G + hg) * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+      }
+      return;
+    }
     // ---- the parts meet in the cluster's first CTA -------------------------------------------------------
     cluster_sync_all();                             // every part's accumulator, max and sum are in place
     if (cluster_cta_rank() == 0) {
@@ -328,28 +408,37 @@ extern "C" void qe_decode_attention_mma_early(int early) { g_dm_early = early ? 
 // the kernels around it) or 3.
 extern "C" void qe_decode_attention_mma_stages(int stages) { g_dm_stages = stages >= 3 ? 3 : 2; }
 
+// Whether the parts of a cluster are pushed to its first CTA (1; else that CTA reads them from the others).
+static int g_dm_push = 1;
+extern "C" void qe_decode_attention_mma_push(int on) { g_dm_push = on ? 1 : 0; }
+
 template <bool CL, int STAGES, int WARPS>
-static int launch_decode_mma_as(const FaArgs& fa, long long prefetch_delta, int n_items, int Hkv, int cluster, cudaStream_t stream) {
-  constexpr int smem = DM_SMEM_BYTES_OF(STAGES, WARPS);
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(decode_attention_mma_kernel<CL, STAGES, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+static int launch_decode_mma_as(const FaArgs& fa, long long prefetch_delta, int n_items, int Hkv, int cluster, int max_rows, cudaStream_t stream) {
+  constexpr int base_smem = DM_SMEM_BYTES_OF(STAGES, WARPS);
+  constexpr int limit = 226 * 1024;                 // (an SM has 227 KB; the kernel's static variables take some)
+  // the in-boxes of the other parts behind the warps' memory, if they fit
+  const int inbox = CL ? (cluster - 1) * max_rows * (DM_D + 2) * 4 : 0;
+  const int push_rows = (CL && g_dm_push && base_smem + inbox <= limit) ? max_rows : 0;
+  const int smem = base_smem + (push_rows ? inbox : 0);
+  static int configured = 0;
+  if (configured < smem) {
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_mma_kernel<CL, STAGES, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, CL ? limit : base_smem);
     if (e != cudaSuccess) QE_REFUSE("decode_attention_mma: shared memory %d: %s", smem, cudaGetErrorString(e));
-    configured = true;
+    configured = CL ? limit : base_smem;
   }
   if (CL)
-    qe_launch_cluster(decode_attention_mma_kernel<CL, STAGES, WARPS>, dim3(n_items, Hkv), dim3(WARPS * 32), smem, stream, (unsigned)cluster, fa, prefetch_delta, g_dm_early);
+    qe_launch_cluster(decode_attention_mma_kernel<CL, STAGES, WARPS>, dim3(n_items, Hkv), dim3(WARPS * 32), smem, stream, (unsigned)cluster, fa, prefetch_delta, g_dm_early, push_rows);
   else
-    qe_launch(decode_attention_mma_kernel<CL, STAGES, WARPS>, dim3(n_items, Hkv), dim3(WARPS * 32), smem, stream, fa, prefetch_delta, g_dm_early);
+    qe_launch(decode_attention_mma_kernel<CL, STAGES, WARPS>, dim3(n_items, Hkv), dim3(WARPS * 32), smem, stream, fa, prefetch_delta, g_dm_early, 0);
   QE_CHECK_LAUNCH("decode_attention_mma");
   return 0;
 }
 // wide: CTAs of 8 warps, one per SM (for steps whose items are at most as many as SMs), else 4 warps, two per SM
 template <bool CL>
-static int launch_decode_mma(const FaArgs& fa, long long prefetch_delta, int n_items, int Hkv, int cluster, int wide, cudaStream_t stream) {
-  if (wide) return launch_decode_mma_as<CL, 3, 8>(fa, prefetch_delta, n_items, Hkv, cluster, stream);
-  return g_dm_stages == 3 ? launch_decode_mma_as<CL, 3, 4>(fa, prefetch_delta, n_items, Hkv, cluster, stream)
-                          : launch_decode_mma_as<CL, 2, 4>(fa, prefetch_delta, n_items, Hkv, cluster, stream);
+static int launch_decode_mma(const FaArgs& fa, long long prefetch_delta, int n_items, int Hkv, int cluster, int wide, int max_rows, cudaStream_t stream) {
+  if (wide) return launch_decode_mma_as<CL, 3, 8>(fa, prefetch_delta, n_items, Hkv, cluster, max_rows, stream);
+  return g_dm_stages == 3 ? launch_decode_mma_as<CL, 3, 4>(fa, prefetch_delta, n_items, Hkv, cluster, max_rows, stream)
+                          : launch_decode_mma_as<CL, 2, 4>(fa, prefetch_delta, n_items, Hkv, cluster, max_rows, stream);
 }
 
 // Whether the kernel takes this geometry with at most max_rows rows (token x head of the group) per item:
@@ -379,8 +468,19 @@ extern "C" int qe_decode_attention_mma(const void* q, long q_stride, const void*
   FaArgs fa{(const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pages, block_tables, max_blocks, items,
             (__nv_bfloat16*)out, part_acc, part_ml, part_rows, counters, scale * 1.4426950408889634f, window, Hq, Hkv,
             page_size};
-  if (cluster == 0) return launch_decode_mma<false>(fa, delta, n_items, Hkv, 0, wide, stream);
+  if (cluster == 0) return launch_decode_mma<false>(fa, delta, n_items, Hkv, 0, wide, max_rows, stream);
   if ((cluster != 2 && cluster != 4 && cluster != 8) || n_items % cluster)
     QE_REFUSE("decode_attention_mma: %d items cannot form clusters of %d", n_items, cluster);
-  return launch_decode_mma<true>(fa, delta, n_items, Hkv, cluster, wide, stream);
+  return launch_decode_mma<true>(fa, delta, n_items, Hkv, cluster, wide, max_rows, stream);
+}
+
+// The status word of the bounded wait for the pushed parts (0 = fine).
+extern "C" int qe_decode_attention_mma_status() {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_fa_status, sizeof(int));
+  return v;
+}
+extern "C" void qe_decode_attention_mma_clear_status() {
+  int v = 0;
+  cudaMemcpyToSymbol(g_fa_status, &v, sizeof(int));
 }
