@@ -53,12 +53,20 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
 
 // The same product by clusters of S CTAs that share 16 weight rows, a share of K each (see gsm_cta, CLUSTER): for weight
 // matrices of so few rows that one CTA per 16 of them would leave most SMs without work.
-template <int MT, typename TOut, int XMODE, bool RESID>
+template <int MT, typename TOut, int XMODE, bool RESID, bool PUSH>
 __global__ void __launch_bounds__(512)
 gemm_small_m_cluster_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                             TOut* __restrict__ out, int M, int N, int K, int k_per_warp, int k_per_cta, FuseArgs na) {
-  extern __shared__ float red[];                    // [warps][16][8 MT], then this CTA's sums [16][8 MT]
+  extern __shared__ float red[];                    // [warps][16][8 MT], then this CTA's sums [16][8 MT] (pushed: and the other CTAs')
   __shared__ float s_rstd[8 * MT];
+  __shared__ uint64_t push_bar;
+  if (PUSH) {
+    if (threadIdx.x == 0) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" :: "r"((uint32_t)__cvta_generic_to_shared(&push_bar)), "r"(1u));
+      asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+  }
   const int S = (int)cluster_num_ctas();
   const int vb = (int)blockIdx.x / S;
   const int k_off = (int)cluster_cta_rank() * k_per_cta;
@@ -75,7 +83,8 @@ gemm_small_m_cluster_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bflo
   }
   pdl_launch_dependents();
   pdl_wait();
-  gsm_cta<MT, TOut, XMODE, RESID, true>(x, w, out, M, N, K, k_per_warp, na, vb, red, s_rstd, c0, c1, k_off, k_per_cta);
+  gsm_cta<MT, TOut, XMODE, RESID, true, PUSH>(x, w, out, M, N, K, k_per_warp, na, vb, red, s_rstd, c0, c1, k_off, k_per_cta,
+                                              PUSH ? &push_bar : nullptr);
 }
 
 // How many CTAs share 16 weight rows: 1 where the rows alone give (nearly) every SM a CTA, else 2 or 4 while every CTA
@@ -84,6 +93,21 @@ gemm_small_m_cluster_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bflo
 static int g_small_m_max_cluster = 4;
 // The most CTAs that may share 16 weight rows (1: never share; for measurements and tests).
 extern "C" void qe_small_m_max_cluster(int ctas) { g_small_m_max_cluster = ctas < 1 ? 1 : (ctas > 4 ? 4 : ctas); }
+// Whether the CTAs of a cluster push their sums to the first (1: where it was measured to gain; 2: always; 0: never:
+// that one reads them).  The sums are added in the CTAs' order either way, so the result is the same to the bit.
+// Measured on a B200 (0.6B sizes, a decode step, pushed against pulled): one row 0.725 against 0.746 ms, two rows 0.812
+// against 0.800, four 0.842 against 0.836, eight 0.954 against 0.945: pushed for a single row only.
+static int g_small_m_push = 1;
+extern "C" void qe_small_m_push(int mode) { g_small_m_push = mode < 0 ? 0 : (mode > 2 ? 2 : mode); }
+extern "C" int qe_small_m_status() {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_gsm_status, sizeof(int));
+  return v;
+}
+extern "C" void qe_small_m_clear_status() {
+  int v = 0;
+  cudaMemcpyToSymbol(g_gsm_status, &v, sizeof(int));
+}
 static int small_m_cluster_size(int N, int K) {
   const int ctas = (N + 15) / 16;
   if (g_small_m_max_cluster >= 4 && ctas * 4 <= 148 && K >= 4 * 512) return 4;
@@ -99,21 +123,28 @@ static int launch_small_m_cluster(const void* x, const void* w, void* out, int M
   int warps = 16;
   int k_per_warp = ((k_per_cta + warps - 1) / warps + 63) / 64 * 64;
   warps = (k_per_cta + k_per_warp - 1) / k_per_warp;
-  const size_t smem = (size_t)(warps + 1) * 16 * 8 * MT * sizeof(float);
+  const bool push = g_small_m_push == 2 || (g_small_m_push == 1 && M == 1);
+  const size_t smem = (size_t)(warps + (push ? S : 1)) * 16 * 8 * MT * sizeof(float);
   static bool configured = false;
   if (!configured) {
-    const int max_smem = 17 * 16 * 8 * MT * (int)sizeof(float);
-    cudaFuncSetAttribute(gemm_small_m_cluster_kernel<MT, float, XMODE, RESID>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-    if (!RESID)
-      cudaFuncSetAttribute(gemm_small_m_cluster_kernel<MT, __nv_bfloat16, XMODE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    const int max_smem = 20 * 16 * 8 * MT * (int)sizeof(float);
+    cudaFuncSetAttribute(gemm_small_m_cluster_kernel<MT, float, XMODE, RESID, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    cudaFuncSetAttribute(gemm_small_m_cluster_kernel<MT, float, XMODE, RESID, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (!RESID) {
+      cudaFuncSetAttribute(gemm_small_m_cluster_kernel<MT, __nv_bfloat16, XMODE, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+      cudaFuncSetAttribute(gemm_small_m_cluster_kernel<MT, __nv_bfloat16, XMODE, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    }
     configured = true;
   }
+  const dim3 grid(ctas * S), block(warps * 32);
+  const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
+  const __nv_bfloat16* wb = (const __nv_bfloat16*)w;
   if (out_f32 || RESID) {
-    qe_launch_cluster(gemm_small_m_cluster_kernel<MT, float, XMODE, RESID>, dim3(ctas * S), dim3(warps * 32), smem, stream, (unsigned)S,
-                      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (float*)out, M, N, K, k_per_warp, k_per_cta, na);
+    if (push) qe_launch_cluster(gemm_small_m_cluster_kernel<MT, float, XMODE, RESID, true>, grid, block, smem, stream, (unsigned)S, xb, wb, (float*)out, M, N, K, k_per_warp, k_per_cta, na);
+    else qe_launch_cluster(gemm_small_m_cluster_kernel<MT, float, XMODE, RESID, false>, grid, block, smem, stream, (unsigned)S, xb, wb, (float*)out, M, N, K, k_per_warp, k_per_cta, na);
   } else {
-    qe_launch_cluster(gemm_small_m_cluster_kernel<MT, __nv_bfloat16, XMODE, false>, dim3(ctas * S), dim3(warps * 32), smem, stream, (unsigned)S,
-                      (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, N, K, k_per_warp, k_per_cta, na);
+    if (push) qe_launch_cluster(gemm_small_m_cluster_kernel<MT, __nv_bfloat16, XMODE, false, true>, grid, block, smem, stream, (unsigned)S, xb, wb, (__nv_bfloat16*)out, M, N, K, k_per_warp, k_per_cta, na);
+    else qe_launch_cluster(gemm_small_m_cluster_kernel<MT, __nv_bfloat16, XMODE, false, false>, grid, block, smem, stream, (unsigned)S, xb, wb, (__nv_bfloat16*)out, M, N, K, k_per_warp, k_per_cta, na);
   }
   QE_CHECK_LAUNCH("linear_small_m");
   return 0;

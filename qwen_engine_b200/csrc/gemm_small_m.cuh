@@ -94,11 +94,18 @@ __device__ __forceinline__ void gsm_prefetch(const __nv_bfloat16* __restrict__ w
 // CLUSTER: the CTAs of a thread-block cluster share the 16 weight rows and take a share of K each (k_off, k_len:
 // this CTA's); their sums meet in the cluster's first CTA through distributed shared memory, in the order of the
 // CTAs, and that CTA alone writes the result.  For products whose weight rows are too few to give every SM a CTA.
-template <int MT, typename TOut, int XMODE, bool RESID, bool CLUSTER = false>
+//
+// `push_bar` (CLUSTER only; null: the first CTA reads the others' sums from their shared memory between two barriers of
+// the cluster): an mbarrier of count 1, initialised in every CTA, after which every thread of the cluster has arrived at
+// the cluster's barrier (arrive only).  The other CTAs then push their sums into in-boxes behind the first CTA's own
+// sums with st.async, which counts the bytes on that CTA's barrier, and leave; the first CTA waits for the bytes
+// (bounded: on giving up it records code 1 in g_gsm_status and writes nothing).  The order of the sum stays the CTAs'.
+static __device__ int g_gsm_status = 0;
+template <int MT, typename TOut, int XMODE, bool RESID, bool CLUSTER = false, bool PUSH = false>
 __device__ __forceinline__ void gsm_cta(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                                         TOut* __restrict__ out, int M, int N, int K, int k_per_warp, const FuseArgs& na,
                                         int vb, float* red, float* s_rstd, GsmChunk c0, GsmChunk c1, int k_off = 0,
-                                        int k_len = 1 << 30) {
+                                        int k_len = 1 << 30, uint64_t* push_bar = nullptr) {
   constexpr bool SILU = XMODE == X_SILU;
   constexpr bool NORM = XMODE == X_NORM;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
@@ -201,15 +208,45 @@ __device__ __forceinline__ void gsm_cta(const __nv_bfloat16* __restrict__ x, con
     mine[(g + 8) * MW + t * 8 + 2 * c + 1] = acc[t][3];
   }
   __syncthreads();
-  float* part = red + (size_t)nwarps * 16 * MW;     // CLUSTER: this CTA's sums [16 MW], read by the cluster's first CTA
+  float* part = red + (size_t)nwarps * 16 * MW;     // CLUSTER: this CTA's sums [16 MW] (pulled: read by the cluster's first CTA; pushed: the others' follow)
+  constexpr bool pushed = CLUSTER && PUSH;          // (a template parameter: the pulled form stays as lean as it was)
   if (CLUSTER) {
+    uint32_t dst = 0, bar = 0;
+    if (pushed) {
+      asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");     // (arrived at the kernel's top: the first CTA's barrier exists)
+      if (!writer) {
+        dst = cluster_map_shared(part + (size_t)16 * MW * cluster_cta_rank(), 0);
+        bar = cluster_map_shared(push_bar, 0);
+      }
+    }
     for (int e = threadIdx.x; e < 16 * MW; e += blockDim.x) {
       const int m = e >> 4, i = e & 15;
       float s = 0.f;
       for (int wi = 0; wi < nwarps; ++wi) s += red[((size_t)wi * 16 + i) * MW + m];
-      part[e] = s;
+      if (pushed && !writer)
+        asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];\n"
+                     :: "r"(dst + 4u * (uint32_t)e), "r"(__float_as_uint(s)), "r"(bar) : "memory");
+      else
+        part[e] = s;
     }
-    cluster_sync_all();                             // every CTA's sums are in place
+    if (pushed) {
+      if (!writer) return;
+      if (threadIdx.x == 0) {
+        const uint32_t bytes = (cluster_num_ctas() - 1u) * (uint32_t)(16 * MW) * 4u;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n"
+                     :: "r"((uint32_t)__cvta_generic_to_shared(push_bar)), "r"(bytes) : "memory");
+      }
+      bool landed = false;
+      for (uint32_t spin = 0; spin < (1u << 22) && !landed; ++spin) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}\n"
+                     : "=r"(ok) : "r"((uint32_t)__cvta_generic_to_shared(push_bar)), "r"(0u) : "memory");
+        landed = ok != 0;
+      }
+      if (!landed) { atomicCAS(&g_gsm_status, 0, 1); return; }
+    } else {
+      cluster_sync_all();                           // every CTA's sums are in place
+    }
   }
   if (writer)
   for (int e = threadIdx.x; e < 16 * MW; e += blockDim.x) {
@@ -220,7 +257,8 @@ __device__ __forceinline__ void gsm_cta(const __nv_bfloat16* __restrict__ x, con
       float s = 0.f;
       if (CLUSTER) {
         const uint32_t S = cluster_num_ctas();
-        for (uint32_t r = 0; r < S; ++r) s += cluster_ld_f32(cluster_map_shared(&part[e], r));
+        if (pushed) for (uint32_t r = 0; r < S; ++r) s += part[(size_t)16 * MW * r + e];
+        else for (uint32_t r = 0; r < S; ++r) s += cluster_ld_f32(cluster_map_shared(&part[e], r));
       } else {
         for (int wi = 0; wi < nwarps; ++wi) s += red[((size_t)wi * 16 + i) * MW + m];
       }
@@ -246,7 +284,7 @@ __device__ __forceinline__ void gsm_cta(const __nv_bfloat16* __restrict__ x, con
       if (i == 0 && m < M) na.ssq_out[(size_t)m * na.ssq_ld + vb] = sq;
     }
   }
-  if (CLUSTER) cluster_sync_all();                  // nobody reads this CTA's shared memory any more
+  if (CLUSTER && !pushed) cluster_sync_all();       // nobody reads this CTA's shared memory any more
   QE_TL_MARK(3);
 }
 

@@ -680,7 +680,7 @@ class DeviceWaitTimeout(RuntimeError):
 
 
 _STATUS_WORDS = ("qe_gemm_tc", "qe_gemm_tc_swap", "qe_gemm_tc_pair", "qe_gemm_tc_splitk", "qe_flash_attention_tc",
-                 "qe_flash_attention", "qe_decode_attention_mma")
+                 "qe_flash_attention", "qe_decode_attention_mma", "qe_small_m")
 
 
 def device_status() -> dict[str, int]:

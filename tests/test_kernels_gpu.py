@@ -885,6 +885,34 @@ def test_linear_swiglu_small(M, I, K):
     _close(out, want, torch.bfloat16)
 
 
+@pytest.mark.parametrize("M", [1, 3, 8, 16])
+@pytest.mark.parametrize("N,K", [(1024, 2048), (1024, 3072), (264, 4096)])
+def test_cluster_sums_pushed_and_pulled_are_the_same_to_the_bit(M, N, K):
+    """The CTAs of a cluster that share K meet in the first CTA either by pushing their sums into its shared memory
+    (st.async counted on its mbarrier; used for single rows) or by being read from there between two cluster
+    barriers: the order of the sum is the CTAs' either way, so the results are identical, also when the product
+    adds into the residual stream; no status word is set."""
+    x = _randn((M, K), torch.bfloat16, 13).to(DEV)
+    w = _randn((N, K), torch.bfloat16, 14, K ** -0.5).to(DEV)
+    outs = {}
+    try:
+        for mode in (0, 2):
+            ops.lib().qe_small_m_push(mode)
+            out = torch.empty(M, N, dtype=torch.float32, device=DEV)
+            ops.linear(x, w, out)
+            stream = ops.ResidualStream.for_step(lambda shape, dtype: torch.zeros(shape, dtype=dtype, device=DEV), M, N, torch.bfloat16)
+            stream.resid.fill_(0.25)
+            ops.linear(x, w, ops.ResidualSink(stream))
+            outs[mode] = (out.cpu(), stream.resid.cpu(), stream.ssq[:, :stream.n_ssq].cpu())
+    finally:
+        ops.lib().qe_small_m_push(1)
+    torch.cuda.synchronize()
+    assert ops.device_status() == {}
+    for a, b in zip(outs[0], outs[2]):
+        assert torch.equal(a, b)
+    _close(outs[2][0], x.float().cpu() @ w.float().cpu().t(), torch.bfloat16)
+
+
 @pytest.mark.parametrize("M", [1, 8, 13, 40])
 @pytest.mark.parametrize("N,K", [(1024, 2048), (1024, 3072), (1000, 1032), (592, 4096), (100, 2064), (1184, 1024)])
 @pytest.mark.parametrize("mode", ["bf16", "f32", "stream"])
