@@ -226,9 +226,9 @@ decode_attention_mma_kernel(FaArgs A, long long prefetch_delta, int early_issue,
   {
     const int c = lane & 3;
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i) {
-      *reinterpret_cast<float2*>(mine + g * D + i * 8 + 2 * c) = make_float2(o[i][0], o[i][1]);
-      *reinterpret_cast<float2*>(mine + (g + 8) * D + i * 8 + 2 * c) = make_float2(o[i][2], o[i][3]);
+    for (int i = 0; i < D / 8; ++i) {               // (only the item's rows are read below)
+      if (g < nrows) *reinterpret_cast<float2*>(mine + g * D + i * 8 + 2 * c) = make_float2(o[i][0], o[i][1]);
+      if (g + 8 < nrows) *reinterpret_cast<float2*>(mine + (g + 8) * D + i * 8 + 2 * c) = make_float2(o[i][2], o[i][3]);
     }
     if (c == 0) {
       s_m[warp * DM_ROWS + g] = m_lo; s_m[warp * DM_ROWS + g + 8] = m_hi;
