@@ -154,6 +154,26 @@ decode_attention_mma_kernel(FaArgs A, long long prefetch_delta, int early_issue,
     early[s] = early_issue && gidx < n_groups && kv_begin + (gidx + 1) * DM_GK <= ctx;
     if (early[s]) issue(gidx, s);
   }
+  if (prefetch_delta != 0) {
+    // (before the wait for the kernel before this one: nothing here depends on it, and the CTA has microseconds to
+    // spare until that kernel is done)
+    // the same keys and values of the next layer, into L2: whole runs of a page where a group lies in one
+    // (two lanes: keys, values), else row by row (a lane each)
+    for (int gidx = warp; gidx < n_groups; gidx += DM_WARPS) {
+      const int j0 = kv_begin + gidx * DM_GK;
+      const int row = one_page ? 0 : (lane & 15), is_v = one_page ? lane : (lane >> 4);
+      const int j = j0 + row;
+      if (j < kv_end && is_v < 2) {
+        int blk, off;
+        if (page_shift >= 0) { blk = j >> page_shift; off = j & (page_size - 1); }
+        else { blk = j / page_size; off = j - blk * page_size; }
+        const __nv_bfloat16* src = head_base + (size_t)__ldg(table + blk) * page_stride + (size_t)off * D + (is_v ? v_off : 0);
+        const unsigned bytes = (unsigned)(one_page ? min(DM_GK, kv_end - j0) : 1) * (unsigned)(D * 2);
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n"
+                     :: "l"(reinterpret_cast<const unsigned char*>(src) + prefetch_delta), "r"(bytes) : "memory");
+      }
+    }
+  }
   pdl_wait();                                       // q and the new tokens' keys and values: the previous kernels' outputs
 #pragma unroll
   for (int s = 0; s < DM_STAGES; ++s) {
@@ -172,24 +192,6 @@ decode_attention_mma_kernel(FaArgs A, long long prefetch_delta, int early_issue,
     *reinterpret_cast<uint4*>(sq + r * LD + c8 * 8) = v;
   }
   if (tid == 0) s_last = 0;
-  if (prefetch_delta != 0) {
-    // the same keys and values of the next layer, into L2: whole runs of a page where a group lies in one
-    // (two lanes: keys, values), else row by row (a lane each)
-    for (int gidx = warp; gidx < n_groups; gidx += DM_WARPS) {
-      const int j0 = kv_begin + gidx * DM_GK;
-      const int row = one_page ? 0 : (lane & 15), is_v = one_page ? lane : (lane >> 4);
-      const int j = j0 + row;
-      if (j < kv_end && is_v < 2) {
-        int blk, off;
-        if (page_shift >= 0) { blk = j >> page_shift; off = j & (page_size - 1); }
-        else { blk = j / page_size; off = j - blk * page_size; }
-        const __nv_bfloat16* src = head_base + (size_t)__ldg(table + blk) * page_stride + (size_t)off * D + (is_v ? v_off : 0);
-        const unsigned bytes = (unsigned)(one_page ? min(DM_GK, kv_end - j0) : 1) * (unsigned)(D * 2);
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n"
-                     :: "l"(reinterpret_cast<const unsigned char*>(src) + prefetch_delta), "r"(bytes) : "memory");
-      }
-    }
-  }
   __syncthreads();
 
   // ---- this warp's groups ---------------------------------------------------------------------------------

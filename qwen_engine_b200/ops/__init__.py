@@ -44,7 +44,7 @@ DECODE_ATTENTION_MMA_STAGES = 3     # key groups a warp of that kernel keeps in 
 DECODE_ATTENTION_MMA_EARLY = True   # that kernel requests earlier steps' keys before it waits for the kernel before it
 DECODE_ATTENTION_MMA_BESIDE_TC = True   # also for the decoded tokens of a step whose prompt portions go to the tcgen05 kernel
 DECODE_ATTENTION_MMA_WIDE = True    # steps with at most as many attention CTAs as SMs: CTAs of 8 warps, one per SM (and contexts split for 148 CTAs, not 296)
-DECODE_PREFETCH_KV_MB = 0           # that kernel asks L2 for the next layer's keys and values when a layer's are at most this many MB (0: never)
+DECODE_PREFETCH_KV_MB = 12          # that kernel asks L2 for the next layer's keys and values when a layer's are at most this many MB (0: never).  Measured (0.6B, context 1 024, asked for before the kernel's dependency wait): 4.4 MB (one request) 0.698 -> 0.690 ms a step, 8.8 MB 0.777 -> 0.765, 17.6 MB equal, 35 MB (eight) 0.915 -> 0.957
 TC_ROWS = 256           # rows per work item of the tcgen05 attention kernel (two halves of 128)
 TC_BN = 128             # keys per step of the tcgen05 attention kernel
 TC_MIN_ROWS = 65        # rows of a request's portion from which the tcgen05 kernel serves it
