@@ -34,31 +34,42 @@
 // tensor memory and returns; the host reads the flag with qe_flash_attention_tc_status().
 #include "tcgen05.cuh"
 #include <math.h>
+#include <type_traits>
 
 #define AT_ROWS 128             // rows of a softmax group
 #define AT_BN 128               // keys per step
 #define AT_D 128                // head size
-#define AT_THREADS 320
+#define AT_THREADS 384             // 8 softmax warps, the fetching warp, the issuing warp, and two idle warps that fill the third group of four
+#define AT_UNITS_SMEM 48           // work units of a CTA whose descriptions are kept in shared memory
 #define AT_SOFTMAX_THREADS 256
 #define AT_ITEM_INTS 12
 #define AT_TMEM_COLS 512
 #define AT_RESCALE_STEP 8.0f    // log2 of the growth of the max that forces a rescale
 #define AT_MAX_PARTS 8          // parts of one tile at most
+#define AT_POLY_OF_8 0           // of every 8 pairs of exponentials in an unmasked step, so many are formed on the FMA pipe
 
 static __device__ int g_at_status = 0;          // 0 = fine; else code of the first wait that ran out
 
+// A work unit (a work item for one kv head) as every role of the CTA sees it.
+struct AtUnit {
+  int req, q0, part, n_parts, split, row0, hkv;
+  int nrows, first_pos, kv_begin, kv_end, kt_first, n_steps;
+  bool two;                                         // the second softmax group has rows
+};
 struct __align__(1024) AtSmem {
   __nv_bfloat16 q[2][2][AT_ROWS * 64];          // [group][half of D][row][64]: 128-byte swizzled rows
   __nv_bfloat16 k[2][2][AT_BN * 64];            // [stage][half of D][key][64]
   __nv_bfloat16 v[2][2][AT_BN * 64];
-  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_ready[2], p_ready[2], o_ready[2];
+  uint64_t q_full[2], q_empty[2], k_full[2], k_empty[2], v_full[2], v_empty[2], s_ready[2], p_ready[2], o_ready[2];
   uint32_t tmem_base;
   int abort_flag, last;
+  AtUnit units[AT_UNITS_SMEM];
+  uint4 stage[8][128];                          // 2 KB per softmax warp: rows on their way to global memory
 };
 
 struct AtArgs {
   const int* block_tables; int max_blocks; int num_pages;
-  const int* items; __nv_bfloat16* out;
+  const int* items; const int* sched; __nv_bfloat16* out;
   float* part_acc; float* part_ml; int part_rows; int* counters;
   float scale_log2; int window, Hq, Hkv, page_shift;
 };
@@ -72,6 +83,24 @@ __device__ __forceinline__ float at_ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
   return y;
+}
+// 2^x for a pair of finite x <= 100 on the FMA pipe, so that the special-function unit, which every exponential of
+// both softmax groups goes through, has fewer to do: x = n + f with n = round(x) and f in [-0.5, 0.5], 2^f by a cubic
+// (relative error 7.5e-5, far below the rounding of P to bfloat16), n added to the exponent's bits.
+__device__ __forceinline__ float2 at_add2(float2 a, float2 b);
+__device__ __forceinline__ float2 at_fma2(float2 a, float2 b, float2 c);
+__device__ __forceinline__ float2 at_ex2_poly2(float2 x) {
+  const float magic = 12582912.f;                   // 1.5 * 2^23: the sum's low mantissa bits are round(x)
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 t = at_add2(x, make_float2(magic, magic));
+  const float2 n = at_add2(t, make_float2(-magic, -magic));
+  const float2 f = at_fma2(n, make_float2(-1.f, -1.f), x);
+  float2 p = at_fma2(f, make_float2(0.05517164617776871f, 0.05517164617776871f), make_float2(0.2426111251115799f, 0.2426111251115799f));
+  p = at_fma2(p, f, make_float2(0.6932609677314758f, 0.6932609677314758f));
+  p = at_fma2(p, f, make_float2(0.9999280571937561f, 0.9999280571937561f));
+  return make_float2(__int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23)),
+                     __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23)));
 }
 __device__ __forceinline__ float at_max3(float a, float b, float c) {
   float d;
@@ -97,38 +126,71 @@ __device__ __forceinline__ float2 at_add2(float2 a, float2 b) {
       : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
   return d;
 }
+// A warp's 32 rows of 64 bytes, a row per lane in registers, to global memory through the warp's 2 KB of shared memory, so
+// that four lanes write a row's 64 bytes side by side (a row per lane would touch 32 lines per instruction).  dst_of(row)
+// says where the 64 bytes of the warp's row `row` go, nullptr for nowhere.  Chunk c of row r lies at 4 r + (c ^ (r / 2 & 3)):
+// neither the writes nor the reads meet in a bank.
+template <typename F>
+__device__ __forceinline__ void at_store_rows(uint4* stage, const uint32_t* v, int lane, F dst_of) {
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+    stage[lane * 4 + (c ^ ((lane >> 1) & 3))] = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+  __syncwarp();
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int row = 8 * k + (lane >> 2), c = lane & 3;
+    const uint4 x = stage[row * 4 + (c ^ ((row >> 1) & 3))];
+    char* dst = dst_of(row);
+    if (dst != nullptr) *reinterpret_cast<uint4*>(dst + 16 * c) = x;
+  }
+  __syncwarp();
+}
 __device__ __forceinline__ void at_softmax_sync() { asm volatile("bar.sync 1, %0;\n" :: "n"(AT_SOFTMAX_THREADS) : "memory"); }
 
+__device__ __forceinline__ AtUnit at_unit(const AtArgs& A, int unit) {
+  AtUnit U;
+  const int item_idx = unit / A.Hkv;
+  U.hkv = unit - item_idx * A.Hkv;
+  const int* it = A.items + (size_t)item_idx * AT_ITEM_INTS;      // (the work lists come from the host's copy, not from a kernel)
+  U.req = it[0]; U.q0 = it[1]; U.part = it[4]; U.n_parts = it[5]; U.split = it[6]; U.row0 = it[7];
+  const int q_len = it[8], ctx = it[9];
+  const int G = A.Hq / A.Hkv;
+  const int ntok = min(2 * (AT_ROWS / G), q_len - U.q0);
+  U.nrows = ntok * G;
+  U.two = U.nrows > AT_ROWS;
+  U.first_pos = ctx + U.q0;
+  U.kv_end = min(it[3], U.first_pos + ntok);        // causal frontier of the tile
+  U.kv_begin = max(it[2], 0);
+  if (A.window > 0) U.kv_begin = max(U.kv_begin, U.first_pos - A.window + 1);
+  U.kt_first = U.kv_begin / AT_BN * AT_BN;
+  U.n_steps = U.kv_end > U.kt_first ? (U.kv_end - U.kt_first + AT_BN - 1) / AT_BN : 0;
+  return U;
+}
+
+// A CTA runs the work units that the host's schedule gives it (sched[b] .. sched[b + 1] index the unit numbers behind
+// the CTAs' offsets), one after the other through the same pipelines: the key and value ring, the tensor-memory
+// columns and the barriers' phases run on across units, so a unit's first scores are formed while the softmax groups
+// still write the output of the unit before, and a unit costs its key steps plus about one step instead of a launch.
 __global__ void __launch_bounds__(AT_THREADS, 1)
 flash_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, AtArgs A) {
   extern __shared__ unsigned char smem_raw[];
   pdl_launch_dependents();
-  QE_TL_STAMPS(128);                                // (timeline build: group g's step j leaves stamps 64 g + 4 j ..)
+  QE_TL_STAMPS(128);                                // (timeline build: the CTA's n-th unit, n < 8, leaves stamps 16 n + 8 g + .. for softmax group g)
   AtSmem& sm = *reinterpret_cast<AtSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int Hq = A.Hq, Hkv = A.Hkv, window = A.window;
-  const int item_idx = blockIdx.x / Hkv, hkv = blockIdx.x - item_idx * Hkv;
-  volatile int* abort_flag = &sm.abort_flag;
-
-  // the work lists come from the host's copy, not from a kernel
-  const int* it = A.items + (size_t)item_idx * AT_ITEM_INTS;
-  const int req = it[0], q0 = it[1], part = it[4], n_parts_of_tile = it[5], split = it[6];
-  const int row0 = it[7], q_len = it[8], ctx = it[9];
   const int G = Hq / Hkv;
   const int tpw = AT_ROWS / G;                      // tokens of one softmax group
-  const int ntok = min(2 * tpw, q_len - q0);
-  const int nrows = ntok * G;
-  const bool two = nrows > AT_ROWS;                 // the second group has rows
-  const int first_pos = ctx + q0;
-  const int kv_end = min(it[3], first_pos + ntok);  // causal frontier of the tile
-  int kv_begin = max(it[2], 0);
-  if (window > 0) kv_begin = max(kv_begin, first_pos - window + 1);
-  const int kt_first = kv_begin / AT_BN * AT_BN;
-  const int n_steps = kv_end > kt_first ? (kv_end - kt_first + AT_BN - 1) / AT_BN : 0;
+  const int u_begin = A.sched[blockIdx.x], u_end = A.sched[blockIdx.x + 1];
+  volatile int* abort_flag = &sm.abort_flag;
+  // the CTA's units, worked out once (every role walks them, and a description is two dependent reads away)
+  if (threadIdx.x >= 32 && threadIdx.x - 32 < min(u_end - u_begin, AT_UNITS_SMEM))
+    sm.units[threadIdx.x - 32] = at_unit(A, A.sched[u_begin + threadIdx.x - 32]);
+  auto unit_at = [&](int ui) { return ui - u_begin < AT_UNITS_SMEM ? sm.units[ui - u_begin] : at_unit(A, A.sched[ui]); };
 
   if (threadIdx.x == 0) {
-    mbar_init(&sm.q_full, 1);
     for (int s = 0; s < 2; ++s) {
+      mbar_init(&sm.q_full[s], 1); mbar_init(&sm.q_empty[s], 1);
       mbar_init(&sm.k_full[s], 1); mbar_init(&sm.k_empty[s], 1);
       mbar_init(&sm.v_full[s], 1); mbar_init(&sm.v_empty[s], 1);
       mbar_init(&sm.s_ready[s], 1); mbar_init(&sm.p_ready[s], AT_ROWS); mbar_init(&sm.o_ready[s], 1);
@@ -144,33 +206,33 @@ flash_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
   const uint32_t tmem = sm.tmem_base;
   pdl_wait();                                       // q, the new keys and values: the previous kernels' outputs
 
+  // registers: the softmax threads hold a row of scores and of P each; the other warps need few
+  if (warp >= 8) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 88;\n");
   if (warp == 8) {
     // ================= producer ==========================================================================
-    if (n_steps > 0) {
-      const int page_shift = A.page_shift, page_size = 1 << page_shift;
-      const int box_rows = min(page_size, AT_BN);
-      const int nb = AT_BN / box_rows;              // boxes per half tile
-      const int* table = A.block_tables + (size_t)req * A.max_blocks;
-      if (lane == 0) {
-        mbar_expect_tx(&sm.q_full, (two ? 2 : 1) * AT_ROWS * AT_D * (uint32_t)sizeof(__nv_bfloat16));
-        for (int w = 0; w < (two ? 2 : 1); ++w)
-          for (int half = 0; half < 2; ++half)
-            tma_load_3d(sm.q[w][half], &map_q, &sm.q_full, half * 64, hkv * G, row0 + q0 + w * tpw);
-      }
-      // Keys and values of a step are asked for separately, each as soon as its slot is free: the keys' slot when
-      // the scores of the step two before have been formed, the values' slot a whole step later, when that step's
-      // P V has retired.  (Asked for together, the keys of step j + 1 waited for the values' slot and arrived
-      // after the tensor cores wanted them: each group waited 1.4 us a step for its scores where the two products
-      // take 0.7.)
-      int issued_k = 0, issued_v = 0;
-      for (int j = 0; j < n_steps; ++j) {
-        const int st = j & 1;
-        const uint32_t par = ((j >> 1) - 1) & 1;
-        const int kt = kt_first + j * AT_BN;
-        for (int kind = 0; kind < 2; ++kind) {
-          bool ok = true;
-          if (j >= 2) ok = mbar_wait(kind ? &sm.v_empty[st] : &sm.k_empty[st], par, abort_flag, 1 + kind, &g_at_status);
-          if (!__all_sync(0xffffffffu, ok)) { j = n_steps; break; }
+    const int page_shift = A.page_shift, page_size = 1 << page_shift;
+    const int box_rows = min(page_size, AT_BN);
+    const int nb = AT_BN / box_rows;                // boxes per half tile
+    // Keys and values of a step are asked for separately, each as soon as its slot is free: the keys' slot when
+    // the scores of the step two before have been formed, the values' slot a whole step later, when that step's
+    // P V has retired.  (Asked for together, the keys of step j + 1 waited for the values' slot and arrived
+    // after the tensor cores wanted them.)  A unit's queries are asked for behind its first keys, a group's as
+    // soon as the last Q K^T of the unit before has read that group's.
+    int gk = 0;                                     // key steps so far, over all units
+    int issued_k = 0, issued_v = 0, issued_q[2] = {0, 0};
+    bool ok = true;
+    for (int ui = u_begin; ok && ui < u_end; ++ui) {
+      const AtUnit U = unit_at(ui);
+      const int* table = A.block_tables + (size_t)U.req * A.max_blocks;
+      for (int j = 0; ok && j < U.n_steps; ++j, ++gk) {
+        const int st = gk & 1;
+        const uint32_t par = ((gk >> 1) - 1) & 1;
+        const int kt = U.kt_first + j * AT_BN;
+        for (int kind = 0; ok && kind < 2; ++kind) {
+          if (gk >= 2) ok = mbar_wait(kind ? &sm.v_empty[st] : &sm.k_empty[st], par, abort_flag, 1 + kind, &g_at_status);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
           if (lane == 0) mbar_expect_tx(kind ? &sm.v_full[st] : &sm.k_full[st], AT_BN * AT_D * (uint32_t)sizeof(__nv_bfloat16));
           __syncwarp();
           for (int idx = lane; idx < 2 * nb; idx += 32) {
@@ -180,279 +242,429 @@ flash_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
             int page = blk < A.max_blocks ? table[blk] : -1;
             if (page < 0) page = A.num_pages;       // outside the tensor: the box is filled with zeros
             __nv_bfloat16* dst = (kind ? sm.v[st][half] : sm.k[st][half]) + (size_t)box * box_rows * 64;
-            tma_load_5d(dst, &map_kv, kind ? &sm.v_full[st] : &sm.k_full[st], half * 64, y, hkv, kind, page);
+            tma_load_5d(dst, &map_kv, kind ? &sm.v_full[st] : &sm.k_full[st], half * 64, y, U.hkv, kind, page);
           }
           if (kind) ++issued_v; else ++issued_k;
+          if (kind == 0 && j == 0) {
+            for (int w = 0; ok && w < (U.two ? 2 : 1); ++w) {
+              if (issued_q[w] > 0) ok = mbar_wait(&sm.q_empty[w], (issued_q[w] - 1) & 1, abort_flag, 10, &g_at_status);
+              ok = __all_sync(0xffffffffu, ok);
+              if (!ok) break;
+              if (lane == 0) {
+                mbar_expect_tx(&sm.q_full[w], AT_ROWS * AT_D * (uint32_t)sizeof(__nv_bfloat16));
+                for (int half = 0; half < 2; ++half)
+                  tma_load_3d(sm.q[w][half], &map_q, &sm.q_full[w], half * 64, U.hkv * G, U.row0 + U.q0 + w * tpw);
+              }
+              ++issued_q[w];
+            }
+          }
         }
       }
-      if (*abort_flag && lane == 0) {
-        // giving up: let the copies that are still in flight land before the CTA leaves (bounded)
-        for (uint32_t spin = 0; spin < TC_WAIT_LIMIT; ++spin) if (mbar_try_wait(&sm.q_full, 0)) break;
-        for (int i = max(0, issued_k - 2); i < issued_k; ++i)
-          for (uint32_t spin = 0; spin < TC_WAIT_LIMIT; ++spin) if (mbar_try_wait(&sm.k_full[i & 1], (i >> 1) & 1)) break;
-        for (int i = max(0, issued_v - 2); i < issued_v; ++i)
-          for (uint32_t spin = 0; spin < TC_WAIT_LIMIT; ++spin) if (mbar_try_wait(&sm.v_full[i & 1], (i >> 1) & 1)) break;
-      }
+    }
+    if (*abort_flag && lane == 0) {
+      // giving up: let the copies that are still in flight land before the CTA leaves (bounded)
+      for (int w = 0; w < 2; ++w)
+        if (issued_q[w] > 0)
+          for (uint32_t spin = 0; spin < TC_WAIT_LIMIT; ++spin) if (mbar_try_wait(&sm.q_full[w], (issued_q[w] - 1) & 1)) break;
+      for (int i = max(0, issued_k - 2); i < issued_k; ++i)
+        for (uint32_t spin = 0; spin < TC_WAIT_LIMIT; ++spin) if (mbar_try_wait(&sm.k_full[i & 1], (i >> 1) & 1)) break;
+      for (int i = max(0, issued_v - 2); i < issued_v; ++i)
+        for (uint32_t spin = 0; spin < TC_WAIT_LIMIT; ++spin) if (mbar_try_wait(&sm.v_full[i & 1], (i >> 1) & 1)) break;
     }
   } else if (warp == 9) {
     // ================= MMA issuer: one thread ===========================================================
-    if (lane == 0 && n_steps > 0) {
+    if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc(AT_ROWS, AT_BN);
       constexpr uint32_t idesc_pv = make_idesc(AT_ROWS, AT_D, true);
-      const int groups = two ? 2 : 1;
+      // The operands' descriptors are worked out once: the issuing thread's own instructions, not the tensor cores, set
+      // the pace of the products otherwise (a descriptor built per instruction costs a dozen dependent operations, and a
+      // 128 x 128 x 16 product is over in 64 cycles).
+      const uint64_t dq00 = make_smem_desc(smem_u32(sm.q[0][0])), dq01 = make_smem_desc(smem_u32(sm.q[0][1]));
+      const uint64_t dq10 = make_smem_desc(smem_u32(sm.q[1][0])), dq11 = make_smem_desc(smem_u32(sm.q[1][1]));
+      const uint64_t dk00 = make_smem_desc(smem_u32(sm.k[0][0])), dk01 = make_smem_desc(smem_u32(sm.k[0][1]));
+      const uint64_t dk10 = make_smem_desc(smem_u32(sm.k[1][0])), dk11 = make_smem_desc(smem_u32(sm.k[1][1]));
+      const uint64_t dv0 = make_smem_desc_mn(smem_u32(sm.v[0][0]), AT_BN * 128, 1024);
+      const uint64_t dv1 = make_smem_desc_mn(smem_u32(sm.v[1][0]), AT_BN * 128, 1024);
       auto issue_qk = [&](int w, int st) {          // S_w = Q_w · K^T: 8 instructions of k = 16 over the head size
+        const uint64_t qa = w ? dq10 : dq00, qb = w ? dq11 : dq01;
+        const uint64_t ka = st ? dk10 : dk00, kb = st ? dk11 : dk01;
+        const uint32_t d = tmem + w * AT_BN;
 #pragma unroll
-        for (int ks = 0; ks < AT_D / 16; ++ks) {
-          const uint64_t da = make_smem_desc(smem_u32(sm.q[w][ks >> 2])) + 2 * (ks & 3);
-          const uint64_t db = make_smem_desc(smem_u32(sm.k[st][ks >> 2])) + 2 * (ks & 3);
-          tc_mma_bf16(tmem + w * AT_BN, da, db, idesc_qk, ks != 0);
-        }
+        for (int ks = 0; ks < AT_D / 16; ++ks)
+          tc_mma_bf16(d, (ks < 4 ? qa : qb) + 2 * (ks & 3), (ks < 4 ? ka : kb) + 2 * (ks & 3), idesc_qk, ks != 0);
       };
       auto issue_pv = [&](int w, int st, bool acc) {  // O_w (+)= P_w · V: 8 instructions of k = 16 over the keys
-        const uint64_t dv = make_smem_desc_mn(smem_u32(sm.v[st][0]), AT_BN * 128, 1024);
+        const uint64_t dv = st ? dv1 : dv0;
+        const uint32_t d = tmem + 2 * AT_BN + w * AT_D, a = tmem + w * AT_BN;
 #pragma unroll
         for (int ks = 0; ks < AT_BN / 16; ++ks)
-          tc_mma_bf16_ts(tmem + 2 * AT_BN + w * AT_D, tmem + w * AT_BN + ks * 8, dv + ks * (2048 >> 4), idesc_pv,
-                         acc || ks != 0);
+          tc_mma_bf16_ts(d, a + ks * 8, dv + ks * (2048 >> 4), idesc_pv, acc || ks != 0);
       };
-      bool ok = mbar_wait(&sm.q_full, 0, abort_flag, 3, &g_at_status) &&
-                mbar_wait(&sm.k_full[0], 0, abort_flag, 4, &g_at_status);
-      if (ok) {
-        tc_fence_after();
-        for (int w = 0; w < groups; ++w) { issue_qk(w, 0); tc_commit(&sm.s_ready[w]); }
-        tc_commit(&sm.k_empty[0]);
-      }
-      for (int j = 0; ok && j < n_steps; ++j) {
-        const int st = j & 1, nst = st ^ 1;
-        const bool more = j + 1 < n_steps;
-        ok = mbar_wait(&sm.v_full[st], (j >> 1) & 1, abort_flag, 5, &g_at_status);
-        for (int w = 0; ok && w < groups; ++w) {
-          ok = mbar_wait(&sm.p_ready[w], j & 1, abort_flag, 6, &g_at_status);
-          if (!ok) break;
+      int ui = u_begin;
+      auto next_unit = [&](AtUnit& U) {             // the next unit that has keys to visit
+        while (ui < u_end) {
+          U = unit_at(ui++);
+          if (U.n_steps > 0) return true;
+        }
+        return false;
+      };
+      uint32_t began = 0, taken = 0;                // bit w: the phase of group w's queries' barrier, of its P's barrier
+      // the scores of a step for group w; `first`: the step opens a unit (its queries must have landed), `last`: it
+      // closes one (nothing reads the group's queries after it)
+      auto scores = [&](int w, int st, bool first, bool last) {
+        if (first) {
+          if (!mbar_wait(&sm.q_full[w], (began >> w) & 1, abort_flag, 3, &g_at_status)) return false;
+          began ^= 1u << w;
           tc_fence_after();
-          issue_pv(w, st, j > 0);
-          if (w == groups - 1) tc_commit(&sm.v_empty[st]);      // the values' slot, as soon as the last P V that reads it retires
-          if (more) {
+        }
+        issue_qk(w, st);
+        tc_commit(&sm.s_ready[w]);
+        if (last) tc_commit(&sm.q_empty[w]);
+        return true;
+      };
+      AtUnit cur, nxt;
+      bool have = next_unit(cur);
+      bool ok = true;
+      int gj = 0;                                   // key steps so far, over all units
+      if (have) {
+        ok = mbar_wait(&sm.k_full[0], 0, abort_flag, 4, &g_at_status);
+        if (ok) {
+          tc_fence_after();
+#pragma unroll
+          for (int w = 0; w < 2; ++w)
+            if (ok && (w == 0 || cur.two)) ok = scores(w, 0, true, cur.n_steps == 1);
+          if (ok) tc_commit(&sm.k_empty[0]);
+        }
+      }
+      while (ok && have) {
+        const int groups = cur.two ? 2 : 1;
+        // ---- all steps but the unit's last: the step after is the same unit's --------------------------------
+        for (int j = 0; ok && j + 1 < cur.n_steps; ++j, ++gj) {
+          const int st = gj & 1, nst = st ^ 1;
+          const bool closes = j + 2 == cur.n_steps;           // the scores formed here are the unit's last
+          ok = mbar_wait(&sm.v_full[st], (gj >> 1) & 1, abort_flag, 5, &g_at_status);
+#pragma unroll
+          for (int w = 0; w < 2; ++w) {
+            if (!ok || w >= groups) continue;
+            ok = mbar_wait(&sm.p_ready[w], (taken >> w) & 1, abort_flag, 6, &g_at_status);
+            if (!ok) continue;
+            taken ^= 1u << w;
+            tc_fence_after();
+            issue_pv(w, st, j > 0);
+            if (w == groups - 1) tc_commit(&sm.v_empty[st]);        // the values' slot, as soon as the last P V that reads it retires
             if (w == 0) {
-              ok = mbar_wait(&sm.k_full[nst], ((j + 1) >> 1) & 1, abort_flag, 7, &g_at_status);
-              if (!ok) break;
+              ok = mbar_wait(&sm.k_full[nst], ((gj + 1) >> 1) & 1, abort_flag, 7, &g_at_status);
+              if (!ok) continue;
               tc_fence_after();
             }
             issue_qk(w, nst);
             tc_commit(&sm.s_ready[w]);
-          } else {
-            tc_commit(&sm.o_ready[w]);
+            if (closes) tc_commit(&sm.q_empty[w]);
           }
+          if (ok) tc_commit(&sm.k_empty[nst]);
         }
-        if (!ok) break;
-        if (more) tc_commit(&sm.k_empty[nst]);
+        // ---- the unit's last step: the step after, if any, opens the next unit -------------------------------
+        bool have_next = false;
+        if (ok) {
+          const int st = gj & 1, nst = st ^ 1;
+          const bool acc = cur.n_steps > 1;
+          have_next = next_unit(nxt);
+          const int n_groups = have_next ? (nxt.two ? 2 : 1) : 0;
+          const bool n_last = have_next && nxt.n_steps == 1;
+          const uint32_t k_par = ((gj + 1) >> 1) & 1;
+          ok = mbar_wait(&sm.v_full[st], (gj >> 1) & 1, abort_flag, 5, &g_at_status);
+          bool keys_here = false;
+          uint32_t scored = 0;
+#pragma unroll
+          for (int w = 0; w < 2; ++w) {
+            if (ok && w < groups) {
+              ok = mbar_wait(&sm.p_ready[w], (taken >> w) & 1, abort_flag, 6, &g_at_status);
+              if (ok) {
+                taken ^= 1u << w;
+                tc_fence_after();
+                issue_pv(w, st, acc);
+                if (w == groups - 1) tc_commit(&sm.v_empty[st]);
+                tc_commit(&sm.o_ready[w]);
+              }
+            }
+            // The next unit's first scores wait for its queries, which may still be on their way: the other group's
+            // P V must not wait behind them, so they are formed here only if everything has landed, else below.
+            if (ok && w < n_groups && mbar_try_wait(&sm.q_full[w], (began >> w) & 1) &&
+                (keys_here || mbar_try_wait(&sm.k_full[nst], k_par))) {
+              if (!keys_here) { tc_fence_after(); keys_here = true; }
+              ok = scores(w, nst, true, n_last);
+              scored |= 1u << w;
+            }
+          }
+#pragma unroll
+          for (int w = 0; w < 2; ++w) {
+            if (!ok || w >= n_groups || ((scored >> w) & 1)) continue;
+            if (!keys_here) {
+              ok = mbar_wait(&sm.k_full[nst], k_par, abort_flag, 7, &g_at_status);
+              tc_fence_after();
+              keys_here = true;
+            }
+            if (ok) ok = scores(w, nst, true, n_last);
+          }
+          if (ok && n_groups > 0) tc_commit(&sm.k_empty[nst]);
+          ++gj;
+        }
+        cur = nxt;
+        have = have_next;
       }
     }
+  }
+  // (warps 10 and 11 are idle: they only make the third group of four warps whole)
   } else {
     // ================= softmax groups ====================================================================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;\n");
     const int w = warp >> 2, quarter = warp & 3;
     const int r = w * AT_ROWS + quarter * 32 + lane;        // row of the tile
-    const bool active = w == 0 || two;
-    const bool valid = r < nrows;
-    const int ti = r / G, hg = r - ti * G;
-    const int pos = valid ? first_pos + ti : -1;
-    const int hi = valid ? min(kv_end, pos + 1) : 0;          // keys [lo, hi) are allowed for this row
-    const int lo = window > 0 ? max(kv_begin, pos - window + 1) : kv_begin;
     const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
     const uint32_t s_col = w * AT_BN, o_col = 2 * AT_BN + w * AT_D;
     const float scale_log2 = A.scale_log2;
-    float m_run = -INFINITY, l_run = 0.f;
+    int seen_s = 0, seen_o = 0;                             // phases of this group's score and output barriers
     bool ok = true;
-    if (active) {
-      for (int j = 0; j < n_steps; ++j) {
-        ok = __all_sync(0xffffffffu, mbar_wait(&sm.s_ready[w], j & 1, abort_flag, 8, &g_at_status));
-        if (!ok) break;
-        tc_fence_after();
-        QE_TL_STAMP(quarter == 0 && lane == 0 ? 64 * w + 4 * j + 0 : -1);   // (timeline build: the step's scores are ready)
-        uint32_t s[4][32];
+    for (int ui = u_begin; ui < u_end; ++ui) {
+      const AtUnit U = unit_at(ui);
+      const int n_steps = U.n_steps, hkv = U.hkv, part = U.part;
+      const bool active = w == 0 || U.two;
+      const bool valid = r < U.nrows;
+      const int pos = valid ? U.first_pos + r / G : -1;
+      const int hi = valid ? min(U.kv_end, pos + 1) : 0;      // keys [lo, hi) are allowed for this row
+      const int lo = window > 0 ? max(U.kv_begin, pos - window + 1) : U.kv_begin;
+      float m_run = -INFINITY, l_run = 0.f;
+      // (timeline build: 0 the unit's first scores are ready, 1 its first P is handed over, 2 its last P, 3 its last P V has
+      // retired, 4 its output is written, 5 the parts are merged, if that fell to this CTA)
+#define AT_STAMP(k) QE_TL_STAMP(quarter == 0 && lane == 0 && ui - u_begin < 8 ? 16 * (ui - u_begin) + 8 * w + (k) : -1)
+      if (active && ok) {
+        for (int j = 0; j < n_steps; ++j) {
+          ok = __all_sync(0xffffffffu, mbar_wait(&sm.s_ready[w], seen_s & 1, abort_flag, 8, &g_at_status));
+          if (!ok) break;
+          ++seen_s;
+          tc_fence_after();
+          if (j == 0) AT_STAMP(0);
+          uint32_t s[4][32];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) tc_ld_32x32b_x32(lane_base + s_col + c * 32, s[c]);
-        tc_wait_ld();
-        QE_TL_STAMP(quarter == 0 && lane == 0 ? 64 * w + 4 * j + 1 : -1);   // (... and in registers)
-        const int kt = kt_first + j * AT_BN;
-        float mx = -INFINITY;
-        if (kt >= lo && kt + AT_BN <= hi) {
-          float mc[4];                                  // four chains of three-input maxima
+          for (int c = 0; c < 4; ++c) tc_ld_32x32b_x32(lane_base + s_col + c * 32, s[c]);
+          tc_wait_ld();
+          const int kt = U.kt_first + j * AT_BN;
+          float mx = -INFINITY;
+          const bool whole = kt >= lo && kt + AT_BN <= hi;     // every key of the step is allowed for this row
+          if (whole) {
+            float mc[4];                                  // four chains of three-input maxima
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            mc[c] = fmaxf(__uint_as_float(s[c][0]), __uint_as_float(s[c][1]));
+            for (int c = 0; c < 4; ++c) {
+              mc[c] = fmaxf(__uint_as_float(s[c][0]), __uint_as_float(s[c][1]));
 #pragma unroll
-            for (int i = 2; i < 32; i += 2) mc[c] = at_max3(mc[c], __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
-          }
-          mx = fmaxf(fmaxf(mc[0], mc[1]), fmaxf(mc[2], mc[3]));
-        } else {
-#pragma unroll
-          for (int c = 0; c < 4; ++c)
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int key = kt + c * 32 + i;
-              const float v = (key >= lo && key < hi) ? __uint_as_float(s[c][i]) : -INFINITY;
-              s[c][i] = __float_as_uint(v);
-              mx = fmaxf(mx, v);
+              for (int i = 2; i < 32; i += 2) mc[c] = at_max3(mc[c], __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
             }
+            mx = fmaxf(fmaxf(mc[0], mc[1]), fmaxf(mc[2], mc[3]));
+          } else {
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const int key = kt + c * 32 + i;
+                const float v = (key >= lo && key < hi) ? __uint_as_float(s[c][i]) : -INFINITY;
+                s[c][i] = __float_as_uint(v);
+                mx = fmaxf(mx, v);
+              }
+          }
+          mx *= scale_log2;                               // the scale is positive
+          // the reference max moves only when the row's max has grown by more than the step
+          const bool grow = mx > m_run + AT_RESCALE_STEP;
+          const float alpha = grow ? exp2f(m_run - mx) : 1.f;
+          if (grow) m_run = mx;
+          const float base = m_run == -INFINITY ? 0.f : m_run;   // a row with nothing allowed so far
+          if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+              uint32_t o[32];
+              tc_ld_32x32b_x32(lane_base + o_col + c * 32, o);
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tc_st_32x32b_x32(lane_base + o_col + c * 32, o);
+            }
+          }
+          uint32_t pk[2][32];
+          float2 sums[4];
+          const float2 sc2 = make_float2(scale_log2, scale_log2), nb2 = make_float2(-base, -base);
+          if (whole) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              sums[c] = make_float2(0.f, 0.f);
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                const float2 x = at_fma2(make_float2(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])), sc2, nb2);
+                const float2 p = ((i >> 1) & 7) < AT_POLY_OF_8 ? at_ex2_poly2(x) : make_float2(at_ex2(x.x), at_ex2(x.y));
+                sums[c] = at_add2(sums[c], p);
+                pk[c >> 1][(c & 1) * 16 + (i >> 1)] = at_pack(p.x, p.y);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              sums[c] = make_float2(0.f, 0.f);
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                const float2 x = at_fma2(make_float2(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])), sc2, nb2);
+                const float2 p = make_float2(at_ex2(x.x), at_ex2(x.y));
+                sums[c] = at_add2(sums[c], p);
+                pk[c >> 1][(c & 1) * 16 + (i >> 1)] = at_pack(p.x, p.y);
+              }
+            }
+          }
+          const float2 s01 = at_add2(sums[0], sums[1]), s23 = at_add2(sums[2], sums[3]);
+          l_run = l_run * alpha + ((s01.x + s01.y) + (s23.x + s23.y));
+          tc_st_32x32b_x32(lane_base + s_col, pk[0]);
+          tc_st_32x32b_x32(lane_base + s_col + 32, pk[1]);
+          tc_wait_st();
+          tc_fence_before();
+          mbar_arrive(&sm.p_ready[w]);
+          if (j == 0) AT_STAMP(1);
+          if (j == n_steps - 1) AT_STAMP(2);
         }
-        mx *= scale_log2;                               // the scale is positive
-        // the reference max moves only when the row's max has grown by more than the step
-        const bool grow = mx > m_run + AT_RESCALE_STEP;
-        const float alpha = grow ? exp2f(m_run - mx) : 1.f;
-        if (grow) m_run = mx;
-        const float base = m_run == -INFINITY ? 0.f : m_run;   // a row with nothing allowed so far
-        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        // ---- the tile's output, or this part's accumulator with max and sum ----------------------------
+        if (ok && n_steps > 0) {
+          ok = __all_sync(0xffffffffu, mbar_wait(&sm.o_ready[w], seen_o & 1, abort_flag, 9, &g_at_status));
+          ++seen_o;
+        }
+        AT_STAMP(3);
+        if (ok) {
+          tc_fence_after();
+          const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+          const size_t slot = part >= 0 ? ((size_t)part * Hkv + hkv) * A.part_rows + r : 0;
+          const int wrow0 = w * AT_ROWS + quarter * 32;       // the warp's first row of the tile
+          uint4* stage = sm.stage[warp];
+          __nv_bfloat16* out_tok0 = A.out + (size_t)(U.row0 + U.q0) * ((size_t)Hq * AT_D) + (size_t)(hkv * G) * AT_D;
+          float* part0 = part >= 0 ? A.part_acc + (((size_t)part * Hkv + hkv) * A.part_rows + wrow0) * AT_D : nullptr;
+          const int nrows = U.nrows;
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
             uint32_t o[32];
-            tc_ld_32x32b_x32(lane_base + o_col + c * 32, o);
-            tc_wait_ld();
+            if (n_steps > 0) {
+              tc_ld_32x32b_x32(lane_base + o_col + c * 32, o);
+              tc_wait_ld();
+            } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tc_st_32x32b_x32(lane_base + o_col + c * 32, o);
+              for (int i = 0; i < 32; ++i) o[i] = 0u;
+            }
+            if (part < 0) {
+              uint32_t pk[16];
+#pragma unroll
+              for (int i = 0; i < 16; ++i) pk[i] = at_pack(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
+              at_store_rows(stage, pk, lane, [&](int row) -> char* {
+                const int rr = wrow0 + row;
+                if (rr >= nrows) return nullptr;
+                const int t2 = rr / G, h2 = rr - t2 * G;
+                return reinterpret_cast<char*>(out_tok0 + (size_t)t2 * ((size_t)Hq * AT_D) + (size_t)h2 * AT_D + c * 32);
+              });
+            } else {
+#pragma unroll
+              for (int half = 0; half < 2; ++half)
+                at_store_rows(stage, o + 16 * half, lane, [&](int row) -> char* {
+                  if (wrow0 + row >= nrows) return nullptr;
+                  return reinterpret_cast<char*>(part0 + (size_t)row * AT_D + c * 32 + half * 16);
+                });
+            }
           }
+          if (valid && part >= 0) { A.part_ml[2 * slot] = m_run; A.part_ml[2 * slot + 1] = l_run; }
         }
-        uint32_t pk[2][32];
-        float2 sums[4];
-        const float2 sc2 = make_float2(scale_log2, scale_log2), nb2 = make_float2(-base, -base);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          sums[c] = make_float2(0.f, 0.f);
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float2 x = at_fma2(make_float2(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])), sc2, nb2);
-            const float2 p = make_float2(at_ex2(x.x), at_ex2(x.y));
-            sums[c] = at_add2(sums[c], p);
-            pk[c >> 1][(c & 1) * 16 + (i >> 1)] = at_pack(p.x, p.y);
-          }
-        }
-        QE_TL_STAMP(quarter == 0 && lane == 0 ? 64 * w + 4 * j + 2 : -1);   // (... the exponentials are done)
-        const float2 s01 = at_add2(sums[0], sums[1]), s23 = at_add2(sums[2], sums[3]);
-        l_run = l_run * alpha + ((s01.x + s01.y) + (s23.x + s23.y));
-        tc_st_32x32b_x32(lane_base + s_col, pk[0]);
-        tc_st_32x32b_x32(lane_base + s_col + 32, pk[1]);
-        tc_wait_st();
-        tc_fence_before();
-        mbar_arrive(&sm.p_ready[w]);
-        QE_TL_STAMP(quarter == 0 && lane == 0 ? 64 * w + 4 * j + 3 : -1);   // (... P is handed over)
+        AT_STAMP(4);
       }
-      // ---- the tile's output, or this part's accumulator with max and sum ----------------------------
-      if (ok && n_steps > 0) ok = __all_sync(0xffffffffu, mbar_wait(&sm.o_ready[w], 0, abort_flag, 9, &g_at_status));
-      if (ok) {
-        tc_fence_after();
-        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        __nv_bfloat16* dst = A.out + (size_t)(row0 + q0 + ti) * ((size_t)Hq * AT_D) + (size_t)(hkv * G + hg) * AT_D;
-        const size_t slot = part >= 0 ? ((size_t)part * Hkv + hkv) * A.part_rows + r : 0;
+      // ---- the CTA that finishes a tile's last part combines the parts ---------------------------------
+      if (part >= 0 && A.counters != nullptr && U.n_parts > 0) {
+        const int first = part - U.split, n_parts_of_tile = U.n_parts, nrows = U.nrows;
+        if (!ok) sm.abort_flag = 1;
+        __threadfence();                              // this CTA's part is visible before it is counted
+        at_softmax_sync();
+        if (threadIdx.x == 0) {
+          int is_last = 0;
+          if (!sm.abort_flag) {
+            const int done = atomicAdd(&A.counters[first * Hkv + hkv], 1);
+            is_last = (done == n_parts_of_tile - 1);
+            if (is_last) A.counters[first * Hkv + hkv] = 0;    // ready for the next launch
+          }
+          sm.last = is_last;
+        }
+        at_softmax_sync();
+        const bool merges = sm.last != 0;             // (read before the next unit's first meeting, behind which it may change)
+        if (merges) {
+          __threadfence();
+          __nv_bfloat16* out_row0 = A.out + (size_t)(U.row0 + U.q0) * ((size_t)Hq * AT_D);
+          // out = sum_s 2^(m_s - m) acc_s / sum_s 2^(m_s - m) l_s, in float32, in the order of the parts
+          // (reference attn.py:520-594).  A warp takes the rows warp, warp + 8, ...: lane i first works
+          // out the parts' weights of the warp's i-th row, then the warp adds up 16 rows at a time,
+          // one 16-byte piece of a row per lane, with all the loads of a part in flight together.
+          const int mwarp = threadIdx.x >> 5;
+          float f[AT_MAX_PARTS];
+          {
+            const int rr = mwarp + 8 * lane;
+            float mm[AT_MAX_PARTS], ll[AT_MAX_PARTS];
+#pragma unroll
+            for (int sp = 0; sp < AT_MAX_PARTS; ++sp) {
+              mm[sp] = -INFINITY; ll[sp] = 0.f;
+              if (sp < n_parts_of_tile && rr < nrows) {
+                const size_t sl = (((size_t)first + sp) * Hkv + hkv) * A.part_rows + rr;
+                mm[sp] = __ldcg(A.part_ml + 2 * sl);
+                ll[sp] = __ldcg(A.part_ml + 2 * sl + 1);
+              }
+            }
+            float m = -INFINITY;
+#pragma unroll
+            for (int sp = 0; sp < AT_MAX_PARTS; ++sp) m = fmaxf(m, mm[sp]);
+            const float mb = m == -INFINITY ? 0.f : m;
+            float l = 0.f;
+#pragma unroll
+            for (int sp = 0; sp < AT_MAX_PARTS; ++sp) { f[sp] = exp2f(mm[sp] - mb); l += f[sp] * ll[sp]; }
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+            for (int sp = 0; sp < AT_MAX_PARTS; ++sp) f[sp] *= inv;
+          }
+          // 32 loads of 16 bytes per lane are in flight at a time: the fewer parts, the more rows at once
+          auto add_up = [&](auto p2_tag) {
+            constexpr int P2 = decltype(p2_tag)::value, RB = 32 / P2;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t o[32];
-          if (n_steps > 0) {
-            tc_ld_32x32b_x32(lane_base + o_col + c * 32, o);
-            tc_wait_ld();
-          } else {
+            for (int b0 = 0; b0 < 32; b0 += RB) {
+              float4 a4[P2][RB];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = 0u;
-          }
-          if (!valid) continue;
-          if (part < 0) {
+              for (int sp = 0; sp < P2; ++sp)
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              uint4 v4;
-              v4.x = at_pack(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
-              v4.y = at_pack(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
-              v4.z = at_pack(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
-              v4.w = at_pack(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
-              *reinterpret_cast<uint4*>(dst + c * 32 + i) = v4;
+                for (int u = 0; u < RB; ++u) {
+                  const int rr = mwarp + 8 * (b0 + u);
+                  const size_t sl = (((size_t)first + sp) * Hkv + hkv) * A.part_rows + rr;
+                  a4[sp][u] = sp < n_parts_of_tile && rr < nrows ? __ldcg(reinterpret_cast<const float4*>(A.part_acc + sl * AT_D) + lane)
+                                                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+              for (int u = 0; u < RB; ++u) {
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int sp = 0; sp < P2; ++sp) {
+                  const float wgt = __shfl_sync(0xffffffffu, f[sp], b0 + u);
+                  acc.x += wgt * a4[sp][u].x; acc.y += wgt * a4[sp][u].y; acc.z += wgt * a4[sp][u].z; acc.w += wgt * a4[sp][u].w;
+                }
+                const int rr = mwarp + 8 * (b0 + u);
+                if (rr >= nrows) continue;
+                const int t2 = rr / G, h2 = rr - t2 * G;
+                uint2 v2;
+                v2.x = at_pack(acc.x, acc.y);
+                v2.y = at_pack(acc.z, acc.w);
+                *reinterpret_cast<uint2*>(out_row0 + (size_t)t2 * ((size_t)Hq * AT_D) + (size_t)(hkv * G + h2) * AT_D + 4 * lane) = v2;
+              }
             }
-          } else {
-            float* pa = A.part_acc + slot * AT_D + c * 32;
-#pragma unroll
-            for (int i = 0; i < 32; i += 4)
-              *reinterpret_cast<uint4*>(pa + i) = make_uint4(o[i], o[i + 1], o[i + 2], o[i + 3]);
-          }
-        }
-        if (valid && part >= 0) { A.part_ml[2 * slot] = m_run; A.part_ml[2 * slot + 1] = l_run; }
-      }
-    }
-    // ---- the CTA that finishes a tile's last part combines the parts ---------------------------------
-    if (part >= 0 && A.counters != nullptr && n_parts_of_tile > 0) {
-      const int first = part - split;
-      if (!ok) sm.abort_flag = 1;
-      __threadfence();                              // this CTA's part is visible before it is counted
-      at_softmax_sync();
-      if (threadIdx.x == 0 && !sm.abort_flag) {
-        const int done = atomicAdd(&A.counters[first * Hkv + hkv], 1);
-        sm.last = (done == n_parts_of_tile - 1);
-        if (sm.last) A.counters[first * Hkv + hkv] = 0;      // ready for the next launch
-      }
-      at_softmax_sync();
-      if (sm.last) {
-        __threadfence();
-        __nv_bfloat16* out_row0 = A.out + (size_t)(row0 + q0) * ((size_t)Hq * AT_D);
-        // out = sum_s 2^(m_s - m) acc_s / sum_s 2^(m_s - m) l_s, in float32, in the order of the parts
-        // (reference attn.py:520-594).  A warp takes the rows warp, warp + 8, ...: lane i first works
-        // out the parts' weights of the warp's i-th row, then the warp adds up 16 rows at a time,
-        // one 16-byte piece of a row per lane, with all the loads of a part in flight together.
-        const int mwarp = threadIdx.x >> 5;
-        float f[AT_MAX_PARTS];
-        {
-          const int rr = mwarp + 8 * lane;
-          float mm[AT_MAX_PARTS], ll[AT_MAX_PARTS];
-#pragma unroll
-          for (int sp = 0; sp < AT_MAX_PARTS; ++sp) {
-            mm[sp] = -INFINITY; ll[sp] = 0.f;
-            if (sp < n_parts_of_tile && rr < nrows) {
-              const size_t sl = (((size_t)first + sp) * Hkv + hkv) * A.part_rows + rr;
-              mm[sp] = __ldcg(A.part_ml + 2 * sl);
-              ll[sp] = __ldcg(A.part_ml + 2 * sl + 1);
-            }
-          }
-          float m = -INFINITY;
-#pragma unroll
-          for (int sp = 0; sp < AT_MAX_PARTS; ++sp) m = fmaxf(m, mm[sp]);
-          const float mb = m == -INFINITY ? 0.f : m;
-          float l = 0.f;
-#pragma unroll
-          for (int sp = 0; sp < AT_MAX_PARTS; ++sp) { f[sp] = exp2f(mm[sp] - mb); l += f[sp] * ll[sp]; }
-          const float inv = l > 0.f ? 1.f / l : 0.f;
-#pragma unroll
-          for (int sp = 0; sp < AT_MAX_PARTS; ++sp) f[sp] *= inv;
-        }
-#pragma unroll 1
-        for (int b0 = 0; b0 < 32; b0 += 16) {
-          float4 acc[16];
-#pragma unroll
-          for (int u = 0; u < 16; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-          for (int sp = 0; sp < AT_MAX_PARTS; ++sp) {
-            if (sp >= n_parts_of_tile) break;
-            float4 a4[16];
-#pragma unroll
-            for (int u = 0; u < 16; ++u) {
-              const int rr = mwarp + 8 * (b0 + u);
-              const size_t sl = (((size_t)first + sp) * Hkv + hkv) * A.part_rows + rr;
-              a4[u] = rr < nrows ? __ldcg(reinterpret_cast<const float4*>(A.part_acc + sl * AT_D) + lane)
-                                 : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-#pragma unroll
-            for (int u = 0; u < 16; ++u) {
-              const float wgt = __shfl_sync(0xffffffffu, f[sp], b0 + u);
-              acc[u].x += wgt * a4[u].x; acc[u].y += wgt * a4[u].y; acc[u].z += wgt * a4[u].z; acc[u].w += wgt * a4[u].w;
-            }
-          }
-#pragma unroll
-          for (int u = 0; u < 16; ++u) {
-            const int rr = mwarp + 8 * (b0 + u);
-            if (rr >= nrows) continue;
-            const int t2 = rr / G, h2 = rr - t2 * G;
-            uint2 v2;
-            v2.x = at_pack(acc[u].x, acc[u].y);
-            v2.y = at_pack(acc[u].z, acc[u].w);
-            *reinterpret_cast<uint2*>(out_row0 + (size_t)t2 * ((size_t)Hq * AT_D) + (size_t)(hkv * G + h2) * AT_D + 4 * lane) = v2;
-          }
+          };
+          if (n_parts_of_tile <= 2) add_up(std::integral_constant<int, 2>());
+          else if (n_parts_of_tile <= 4) add_up(std::integral_constant<int, 4>());
+          else add_up(std::integral_constant<int, AT_MAX_PARTS>());
         }
       }
+      AT_STAMP(5);
+#undef AT_STAMP
+      // (a group whose wait ran out walks the remaining units without work: the other group may be waiting for it
+      // at a meeting above)
     }
   }
   // everyone meets here; the allocating warp frees the tensor memory
@@ -557,16 +769,62 @@ extern "C" int qe_flash_attention_tc_supported(int Hq, int Hkv, int D, int page_
   return 1;
 }
 
+// Which CTA runs which work units: the units (item i for kv head h is unit i Hkv + h) in the order of the item list,
+// which the caller has sorted by key steps, longest first, each to the CTA with the least work so far (a unit costs its
+// steps plus unit_cost).  out: n_ctas + 1 offsets into out itself, then the CTAs' unit numbers; it must hold
+// n_ctas + 1 + n_items Hkv ints.  Returns the number of ints written, 0 if the arguments make no sense.
+extern "C" int qe_flash_attention_tc_schedule(const int* item_steps, int n_items, int Hkv, int n_ctas, float unit_cost, int* out) {
+  if (n_items <= 0 || Hkv <= 0 || n_ctas <= 0) return 0;
+  const long n_units = (long)n_items * Hkv;
+  if (n_units > 0x3fffffffL) return 0;
+  struct Slot { float load; int cta; };
+  Slot* heap = new Slot[n_ctas];                    // a binary min-heap by (load, cta)
+  int* owner = new int[n_units];
+  int* count = new int[n_ctas];
+  for (int i = 0; i < n_ctas; ++i) { heap[i] = Slot{0.f, i}; count[i] = 0; }
+  auto less = [](const Slot& a, const Slot& b) { return a.load < b.load || (a.load == b.load && a.cta < b.cta); };
+  for (long u = 0; u < n_units; ++u) {
+    Slot top = heap[0];
+    owner[u] = top.cta;
+    ++count[top.cta];
+    top.load += (float)item_steps[u / Hkv] + unit_cost;
+    int k = 0;                                      // replace the root and sift down
+    for (;;) {
+      const int l = 2 * k + 1, r = l + 1;
+      int m = k;
+      Slot best = top;
+      if (l < n_ctas && less(heap[l], best)) { m = l; best = heap[l]; }
+      if (r < n_ctas && less(heap[r], best)) { m = r; best = heap[r]; }
+      if (m == k) break;
+      heap[k] = heap[m];
+      k = m;
+    }
+    heap[k] = top;
+  }
+  int at = n_ctas + 1;
+  for (int c = 0; c < n_ctas; ++c) { out[c] = at; at += count[c]; count[c] = out[c]; }
+  out[n_ctas] = at;
+  for (long u = 0; u < n_units; ++u) out[count[owner[u]]++] = (int)u;
+  delete[] heap;
+  delete[] owner;
+  delete[] count;
+  return at;
+}
+
 // q: the step's queries [T, Hq, 128] with q_stride elements between tokens; pages [num_pages, 2, Hkv,
 // page_size, 128]; items: 12 ints each (see attention_flash.cuh; a tile here is 256 / G tokens, and
-// n_splits is the number of parts of the tile when part >= 0); counters: one int per (first part, kv
+// n_splits is the number of parts of the tile when part >= 0); sched: what qe_flash_attention_tc_schedule
+// wrote for these items and n_ctas CTAs, on the device; counters: one int per (first part, kv
 // head), zero before the first launch, needed when any item has part >= 0.
 extern "C" int qe_flash_attention_tc(const void* q, long q_stride, int T, const void* pages, int num_pages,
                                      const int* block_tables, int max_blocks, const int* items, int n_items,
+                                     const int* sched, int n_ctas,
                                      void* out, float* part_acc, float* part_ml, int part_rows, int* counters,
                                      float scale, int window, int Hq, int Hkv, int D, int page_size,
                                      cudaStream_t stream) {
   if (n_items <= 0) return 0;
+  if (sched == nullptr || n_ctas <= 0 || (long)n_ctas > (long)n_items * Hkv)
+    QE_REFUSE("flash_attention_tc: a schedule for 1 to %ld CTAs is needed, not one for %d", (long)n_items * Hkv, n_ctas);
   if (part_acc && part_rows != 2 * AT_ROWS) QE_REFUSE("flash_attention_tc: parts have %d rows, not %d", part_rows, 2 * AT_ROWS);
   if (!qe_flash_attention_tc_supported(Hq, Hkv, D, page_size))
     QE_REFUSE("flash_attention_tc: heads %d/%d, head_dim %d, page size %d are not supported", Hq, Hkv, D, page_size);
@@ -591,7 +849,7 @@ extern "C" int qe_flash_attention_tc(const void* q, long q_stride, int T, const 
   }
   int page_shift = 0;
   while ((1 << page_shift) < page_size) ++page_shift;
-  AtArgs args{block_tables, max_blocks, num_pages, items, (__nv_bfloat16*)out, part_acc, part_ml, part_rows, counters,
+  AtArgs args{block_tables, max_blocks, num_pages, items, sched, (__nv_bfloat16*)out, part_acc, part_ml, part_rows, counters,
               scale * 1.4426950408889634f, window, Hq, Hkv, page_shift};
   const size_t smem = sizeof(AtSmem) + 1024;
   static bool configured = false;
@@ -600,7 +858,7 @@ extern "C" int qe_flash_attention_tc(const void* q, long q_stride, int T, const 
     if (e != cudaSuccess) QE_REFUSE("flash_attention_tc: shared memory %zu: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  qe_launch(flash_attention_tc_kernel, dim3((unsigned)(n_items * Hkv)), dim3(AT_THREADS), smem, stream, map_q, map_kv, args);
+  qe_launch(flash_attention_tc_kernel, dim3((unsigned)n_ctas), dim3(AT_THREADS), smem, stream, map_q, map_kv, args);
   QE_CHECK_LAUNCH("flash_attention_tc");
   return 0;
 }

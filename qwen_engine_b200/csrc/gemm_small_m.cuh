@@ -223,11 +223,17 @@ __device__ __forceinline__ void gsm_cta(const __nv_bfloat16* __restrict__ x, con
       const int m = e >> 4, i = e & 15;
       float s = 0.f;
       for (int wi = 0; wi < nwarps; ++wi) s += red[((size_t)wi * 16 + i) * MW + m];
-      if (pushed && !writer)
-        asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];\n"
-                     :: "r"(dst + 4u * (uint32_t)e), "r"(__float_as_uint(s)), "r"(bar) : "memory");
-      else
-        part[e] = s;
+      part[e] = s;
+    }
+    if (pushed && !writer) {
+      // 16 bytes a thread: a quarter of the stores and of the barrier's updates
+      __syncthreads();
+      for (int e4 = threadIdx.x; e4 < 4 * MW; e4 += blockDim.x) {
+        const float4 v = *reinterpret_cast<const float4*>(part + 4 * e4);
+        asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];\n"
+                     :: "r"(dst + 16u * (uint32_t)e4), "r"(__float_as_uint(v.x)), "r"(__float_as_uint(v.y)),
+                        "r"(__float_as_uint(v.z)), "r"(__float_as_uint(v.w)), "r"(bar) : "memory");
+      }
     }
     if (pushed) {
       if (!writer) return;

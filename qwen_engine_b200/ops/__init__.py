@@ -815,13 +815,16 @@ def tc_attention_supported(dtype: torch.dtype, num_heads: int, num_kv_heads: int
     return G <= 128 and G & (G - 1) == 0 and page_size >= 8 and page_size & (page_size - 1) == 0
 
 
-def _plan_tc_tiles(tiles: list, Hkv: int) -> tuple[list[int], int]:
+def _plan_tc_tiles(tiles: list, Hkv: int) -> tuple[list[int], int, list[int], int]:
     """Work items of the tcgen05 kernel from its tiles (key steps, first key, last key, item fields),
     sorted by their steps, longest first.  Where the tiles alone would leave SMs idle (a short portion
     behind a long context: few tiles; one prompt of a few thousand tokens: tiles as unequal as
     1 : 2 : ... : n), the longer tiles are cut into parts of whole steps; the library works out the most
-    steps an item may have by laying out the candidates' schedules (a part costs a CTA's start and
-    end and the merge, about as much as a few steps).  Returns the items and the number of parts."""
+    steps an item may have by laying out the candidates' schedules (a part costs its scratch and the
+    merge, about as much as a step).  The kernel's CTAs, one per SM at most, run the units (an item for one kv
+    head) one after the other; the library deals them out, longest first, each to the CTA with the least work
+    so far.  Returns the items, the number of parts, the schedule (the CTAs' offsets into the list itself,
+    then their unit numbers) and the number of CTAs."""
     cap = TC_FORCE_CAP
     if cap < 0:
         cap = 0
@@ -845,7 +848,12 @@ def _plan_tc_tiles(tiles: list, Hkv: int) -> tuple[list[int], int]:
             out.append((min(per, steps - sp * per), [r, q0, k0, k1, n_parts + sp, parts, sp, row0, n, c, 0, 0]))
         n_parts += parts
     out.sort(key=lambda kv: -kv[0])
-    return [x for _, item in out for x in item], n_parts
+    n_ctas = min(len(out) * Hkv, TC_TARGET_CTAS)
+    item_steps = (ctypes.c_int * len(out))(*[st for st, _ in out])
+    sched = (ctypes.c_int * (n_ctas + 1 + len(out) * Hkv))()
+    n = int(lib().qe_flash_attention_tc_schedule(item_steps, len(out), Hkv, n_ctas, ctypes.c_float(TC_ITEM_COST_STEPS), sched))
+    _need(n == len(sched), "plan_attention: the schedule of the tcgen05 kernel could not be made")
+    return [x for _, item in out for x in item], n_parts, list(sched), n_ctas
 
 
 def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
@@ -859,7 +867,8 @@ def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
     and ``fa<i>_merge`` hold its work and merge items and ``fa<i>_info`` = [parts, rows per part,
     whether every item has at most 16 rows, the most rows of an item, the number of parts of every
     request if all are cut into the same 2, 4 or 8 parts (they can then form clusters) else 0]; requests that bring many rows go to the tcgen05 kernel
-    instead where it takes the geometry: ``tc<i>_items`` and ``tc<i>_info`` = [parts, rows per part].
+    instead where it takes the geometry: ``tc<i>_items``, ``tc<i>_sched`` (which CTA runs which
+    item for which kv head) and ``tc<i>_info`` = [parts, rows per part, CTAs].
     ``uniform_splits`` (geometry -> number of parts) fixes the number of parts of every request,
     so that the lists depend on the batch's shape only (for steps replayed from a CUDA graph)."""
     tiles: list[int] = []
@@ -918,9 +927,10 @@ def plan_attention(q_lens: list[int], ctx_lens: list[int], page_size: int,
         same = sizes.pop() if len(sizes) == 1 and not whole else 0
         plan[f"fa{gi}_info"] = [n_parts, part_rows, int(max_rows <= 16), max_rows, same if same in (2, 4, 8) else 0]
         if tc_tiles:
-            tc_items, tc_parts = _plan_tc_tiles(tc_tiles, Hkv)
+            tc_items, tc_parts, tc_sched, tc_ctas = _plan_tc_tiles(tc_tiles, Hkv)
             plan[f"tc{gi}_items"] = tc_items
-            plan[f"tc{gi}_info"] = [tc_parts, TC_ROWS]
+            plan[f"tc{gi}_sched"] = tc_sched
+            plan[f"tc{gi}_info"] = [tc_parts, TC_ROWS, tc_ctas]
     return plan
 
 
@@ -1008,7 +1018,7 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
     if key is not None and f"tc{key}_items" in plan:
         last_attention_kernel = "flash_attention_tc"
         tc_items = plan[f"tc{key}_items"]
-        tc_parts, tc_rows = plan[f"tc{key}_info_host"]
+        tc_parts, tc_rows, tc_ctas = plan[f"tc{key}_info_host"]
         part_acc = part_ml = counters = None
         if tc_parts:
             _need(tc_parts * Hkv <= _MERGE_COUNTERS, "paged_attention: too many parts")
@@ -1017,7 +1027,8 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
             counters = _merge_counters(qkv.device, "tc")
         _check(lib().qe_flash_attention_tc(
             _ptr(qkv), ctypes.c_long(qkv.stride(0)), T, _ptr(kv_pages), int(kv_pages.shape[0]), _ptr(block_tables),
-            int(block_tables.shape[1]), _ptr(tc_items), tc_items.numel() // FLASH_ITEM_INTS, _ptr(out),
+            int(block_tables.shape[1]), _ptr(tc_items), tc_items.numel() // FLASH_ITEM_INTS,
+            _ptr(plan[f"tc{key}_sched"]), int(tc_ctas), _ptr(out),
             _ptr(part_acc), _ptr(part_ml), int(tc_rows), _ptr(counters), ctypes.c_float(scale), int(window),
             Hq, Hkv, D, int(kv_pages.shape[3]), _stream()), "flash_attention_tc")
     if key is not None and f"fa{key}_items" in plan:

@@ -727,6 +727,42 @@ def test_tc_attention_parts(q_lens, ctx_lens):
         _close(got, want, dtype)
 
 
+@pytest.mark.parametrize("ctas", [1, 3, 7])
+@pytest.mark.parametrize("Hq,Hkv,P,q_lens,ctx_lens,window,cap", [
+    (16, 8, 16, [300], [0], 0, 0),                      # three tiles of eight kv heads: every CTA runs several units
+    (4, 2, 16, [200, 40, 70], [100, 50, 0], 0, 0),       # units with one softmax group between units with two
+    (4, 2, 32, [33, 70, 129, 640], [95, 64, 1000, 77], 0, 0),
+    (4, 2, 16, [2048], [0], 0, 8),                      # parts of a tile, merged by whichever CTA comes last
+    (4, 2, 16, [1024, 600], [3000, 0], 0, 3),             # many short parts: a CTA may hold several parts of one tile
+    (2, 1, 256, [130, 515], [5000, 0], 0, 2),
+    (4, 2, 16, [260, 35, 150], [30, 70, 400], 100, 0),   # a window: units of one step, units that begin late
+    (4, 4, 8, [700], [0], 129, 2),
+])
+def test_tc_attention_units_one_after_the_other(ctas, Hq, Hkv, P, q_lens, ctx_lens, window, cap, monkeypatch):
+    """With fewer CTAs than work units a CTA runs its units one after the other through the same pipelines (the ring of
+    keys and values, tensor memory and the barriers' phases run on across units).  The outputs must be those of the
+    plain reference, and to the bit those of a CTA per unit.  (Every request here brings enough rows for this kernel: the
+    number of CTAs also sways which form of the kernel for decoded tokens is picked.)"""
+    D, dtype = 128, torch.bfloat16
+    monkeypatch.setattr(ops, "TC_FORCE_CAP", cap)
+    case = _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, seed=36)
+    want = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ref_ops.paged_attention, "cpu")
+    plan = ops.plan_attention(list(q_lens), list(ctx_lens), P, ((Hq, Hkv, D, window),), dtype)
+    units = len(plan["tc0_items"]) // ops.FLASH_ITEM_INTS * Hkv
+    assert plan["tc0_info"][2] == min(units, ops.TC_TARGET_CTAS) and not plan.get("fa0_items")
+    each = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ops.paged_attention, DEV)
+    _close(each, want, dtype)
+    monkeypatch.setattr(ops, "TC_TARGET_CTAS", ctas)
+    plan = ops.plan_attention(list(q_lens), list(ctx_lens), P, ((Hq, Hkv, D, window),), dtype)
+    sched, n = plan["tc0_sched"], plan["tc0_info"][2]
+    assert n == min(ctas, units) and sched[0] == n + 1 and sched[n] == len(sched)
+    assert sorted(sched[n + 1:]) == list(range(units)), "every unit is run once"
+    for _ in range(2):                     # twice: the merge counters are back at zero after a launch
+        got = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ops.paged_attention, DEV)
+        assert ops.tc_attention_status() == 0
+        assert torch.equal(got, each)
+
+
 @pytest.mark.parametrize("q_lens,ctx_lens", [([200], [30000]), ([1, 1], [30000, 17]), ([3], [40000])])
 def test_attention_long_context(q_lens, ctx_lens):
     """Tens of thousands of keys (the model's limit is 40 960 positions): a portion on the tcgen05
