@@ -127,21 +127,19 @@ __device__ __forceinline__ float2 at_add2(float2 a, float2 b) {
   return d;
 }
 // A warp's 32 rows of 64 bytes, a row per lane in registers, to global memory through the warp's 2 KB of shared memory, so
-// that four lanes write a row's 64 bytes side by side (a row per lane would touch 32 lines per instruction).  dst_of(row)
-// says where the 64 bytes of the warp's row `row` go, nullptr for nowhere.  Chunk c of row r lies at 4 r + (c ^ (r / 2 & 3)):
-// neither the writes nor the reads meet in a bank.
-template <typename F>
-__device__ __forceinline__ void at_store_rows(uint4* stage, const uint32_t* v, int lane, F dst_of) {
+// that four lanes write a row's 64 bytes side by side (a row per lane would touch 32 lines per instruction).  dst[k]: where
+// this lane's 16 bytes of the warp's row 8 k + lane / 4 go (nullptr: nowhere); the caller works them out once for all
+// passes.  Chunk c of row r lies at 4 r + (c ^ (r / 2 & 3)): neither the writes nor the reads meet in a bank.
+__device__ __forceinline__ void at_store_rows(uint4* stage, const uint32_t* v, int lane, char* const (&dst)[4], int offset) {
 #pragma unroll
   for (int c = 0; c < 4; ++c)
     stage[lane * 4 + (c ^ ((lane >> 1) & 3))] = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
   __syncwarp();
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
-    const int row = 8 * k + (lane >> 2), c = lane & 3;
-    const uint4 x = stage[row * 4 + (c ^ ((row >> 1) & 3))];
-    char* dst = dst_of(row);
-    if (dst != nullptr) *reinterpret_cast<uint4*>(dst + 16 * c) = x;
+    const int row = 8 * k + (lane >> 2);
+    const uint4 x = stage[row * 4 + ((lane & 3) ^ ((row >> 1) & 3))];
+    if (dst[k] != nullptr) *reinterpret_cast<uint4*>(dst[k] + offset) = x;
   }
   __syncwarp();
 }
@@ -526,21 +524,64 @@ flash_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
           if (j == 0) AT_STAMP(1);
           if (j == n_steps - 1) AT_STAMP(2);
         }
-        // ---- the tile's output, or this part's accumulator with max and sum ----------------------------
         if (ok && n_steps > 0) {
           ok = __all_sync(0xffffffffu, mbar_wait(&sm.o_ready[w], seen_o & 1, abort_flag, 9, &g_at_status));
           ++seen_o;
         }
         AT_STAMP(3);
-        if (ok) {
+      }
+      // ---- a part of a tile: is this the last of the tile's parts to get here? ---------------------------------
+      // 0: a whole tile; 1: a part, and others are still at work: its accumulator goes to scratch memory with max and
+      // sum; 2: the last part to get here: it takes the others' from scratch memory and writes the tile's output, its
+      // own accumulator never leaving tensor memory; 3: the CTA is giving up.
+      int role = 0;
+      const bool is_part = part >= 0 && A.counters != nullptr && U.n_parts > 0;
+      int* const arrived = is_part ? A.counters + 2 * ((part - U.split) * Hkv + hkv) : nullptr;     // [1]: parts written
+      if (is_part) {
+        if (!ok) sm.abort_flag = 1;
+        at_softmax_sync();
+        if (threadIdx.x == 0) {
+          int r2 = 3;
+          if (!sm.abort_flag) r2 = atomicAdd(arrived, 1) == U.n_parts - 1 ? 2 : 1;
+          if (r2 == 2) {
+            // the others have their tickets, so they are running and will get there; wait until they have written
+            bool there = false;
+            for (uint32_t spin = 0; spin < TC_WAIT_LIMIT && !there; ++spin) {
+              there = *reinterpret_cast<volatile int*>(arrived + 1) == U.n_parts - 1;
+              if (!there) __nanosleep(64);
+            }
+            if (there) { arrived[0] = 0; arrived[1] = 0; }     // ready for the next launch
+            else { sm.abort_flag = 1; atomicCAS(&g_at_status, 0, 11); r2 = 3; }
+          }
+          sm.last = r2;
+        }
+        at_softmax_sync();
+        role = sm.last;                               // (read before the next meeting, behind which it may change)
+        AT_STAMP(7);
+        if (role == 2) __threadfence();
+      }
+      // ---- the tile's output, or this part's accumulator with max and sum ----------------------------
+      if (active && ok && role < 2) {
+        {
           tc_fence_after();
           const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
           const size_t slot = part >= 0 ? ((size_t)part * Hkv + hkv) * A.part_rows + r : 0;
           const int wrow0 = w * AT_ROWS + quarter * 32;       // the warp's first row of the tile
           uint4* stage = sm.stage[warp];
-          __nv_bfloat16* out_tok0 = A.out + (size_t)(U.row0 + U.q0) * ((size_t)Hq * AT_D) + (size_t)(hkv * G) * AT_D;
-          float* part0 = part >= 0 ? A.part_acc + (((size_t)part * Hkv + hkv) * A.part_rows + wrow0) * AT_D : nullptr;
           const int nrows = U.nrows;
+          // where this lane's 16 bytes of the warp's rows 8 k + lane / 4 go: the output's row (token, head) or the part's
+          char* dst[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int row = 8 * k + (lane >> 2), rr = wrow0 + row;
+            if (rr >= nrows) { dst[k] = nullptr; continue; }
+            if (part < 0) {
+              const int t2 = rr / G, h2 = rr - t2 * G;
+              dst[k] = reinterpret_cast<char*>(A.out + (size_t)(U.row0 + U.q0 + t2) * ((size_t)Hq * AT_D) + (size_t)(hkv * G + h2) * AT_D) + 16 * (lane & 3);
+            } else {
+              dst[k] = reinterpret_cast<char*>(A.part_acc + (((size_t)part * Hkv + hkv) * A.part_rows + rr) * AT_D) + 16 * (lane & 3);
+            }
+          }
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
             uint32_t o[32];
@@ -555,111 +596,137 @@ flash_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
               uint32_t pk[16];
 #pragma unroll
               for (int i = 0; i < 16; ++i) pk[i] = at_pack(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
-              at_store_rows(stage, pk, lane, [&](int row) -> char* {
-                const int rr = wrow0 + row;
-                if (rr >= nrows) return nullptr;
-                const int t2 = rr / G, h2 = rr - t2 * G;
-                return reinterpret_cast<char*>(out_tok0 + (size_t)t2 * ((size_t)Hq * AT_D) + (size_t)h2 * AT_D + c * 32);
-              });
+              at_store_rows(stage, pk, lane, dst, c * 64);
             } else {
-#pragma unroll
-              for (int half = 0; half < 2; ++half)
-                at_store_rows(stage, o + 16 * half, lane, [&](int row) -> char* {
-                  if (wrow0 + row >= nrows) return nullptr;
-                  return reinterpret_cast<char*>(part0 + (size_t)row * AT_D + c * 32 + half * 16);
-                });
+              at_store_rows(stage, o, lane, dst, c * 128);
+              at_store_rows(stage, o + 16, lane, dst, c * 128 + 64);
             }
           }
           if (valid && part >= 0) { A.part_ml[2 * slot] = m_run; A.part_ml[2 * slot + 1] = l_run; }
         }
         AT_STAMP(4);
       }
-      // ---- the CTA that finishes a tile's last part combines the parts ---------------------------------
-      if (part >= 0 && A.counters != nullptr && U.n_parts > 0) {
-        const int first = part - U.split, n_parts_of_tile = U.n_parts, nrows = U.nrows;
-        if (!ok) sm.abort_flag = 1;
-        __threadfence();                              // this CTA's part is visible before it is counted
+      if (role == 1) {
+        __threadfence();                              // this CTA's part is visible before it is counted as written
         at_softmax_sync();
-        if (threadIdx.x == 0) {
-          int is_last = 0;
-          if (!sm.abort_flag) {
-            const int done = atomicAdd(&A.counters[first * Hkv + hkv], 1);
-            is_last = (done == n_parts_of_tile - 1);
-            if (is_last) A.counters[first * Hkv + hkv] = 0;    // ready for the next launch
-          }
-          sm.last = is_last;
-        }
-        at_softmax_sync();
-        const bool merges = sm.last != 0;             // (read before the next unit's first meeting, behind which it may change)
-        if (merges) {
-          __threadfence();
-          __nv_bfloat16* out_row0 = A.out + (size_t)(U.row0 + U.q0) * ((size_t)Hq * AT_D);
-          // out = sum_s 2^(m_s - m) acc_s / sum_s 2^(m_s - m) l_s, in float32, in the order of the parts
-          // (reference attn.py:520-594).  A warp takes the rows warp, warp + 8, ...: lane i first works
-          // out the parts' weights of the warp's i-th row, then the warp adds up 16 rows at a time,
-          // one 16-byte piece of a row per lane, with all the loads of a part in flight together.
-          const int mwarp = threadIdx.x >> 5;
-          float f[AT_MAX_PARTS];
-          {
-            const int rr = mwarp + 8 * lane;
-            float mm[AT_MAX_PARTS], ll[AT_MAX_PARTS];
+        if (threadIdx.x == 0) atomicAdd(arrived + 1, 1);
+      }
+      // ---- the last part: out = sum_s 2^(m_s - m) acc_s / sum_s 2^(m_s - m) l_s, in float32, in the order of the
+      // parts whichever of them this is (reference attn.py:520-594) ---------------------------------------------
+      if (role == 2 && active) {
+        tc_fence_after();
+        const int first = part - U.split, me = U.split, n_parts_of_tile = U.n_parts, nrows = U.nrows;
+        const int wrow0 = w * AT_ROWS + quarter * 32;
+        uint4* stage = sm.stage[warp];
+        const size_t part_stride = (size_t)Hkv * A.part_rows;        // rows between a part and the next
+        auto merged_out = [&](auto p2_tag, auto ch_tag) {
+          // P2: the parts, rounded up; CH: columns of the others' accumulators asked for at a time (all loads in flight)
+          constexpr int P2 = decltype(p2_tag)::value, CH = decltype(ch_tag)::value, PASSES = CH / 16;
+          // this lane works on 16 bytes of the warp's rows 8 k + lane / 4: the parts' weights for those rows
+          float fw[4][P2];
+          const float* src[4];
+          char* outp[4];
 #pragma unroll
-            for (int sp = 0; sp < AT_MAX_PARTS; ++sp) {
+          for (int k = 0; k < 4; ++k) {
+            const int row = 8 * k + (lane >> 2), rr = wrow0 + row;
+            const float m_own = __shfl_sync(0xffffffffu, m_run, row), l_own = __shfl_sync(0xffffffffu, l_run, row);
+            const bool in = rr < nrows;
+            const size_t sl0 = ((size_t)first * Hkv + hkv) * A.part_rows + rr;
+            float mm[P2], ll[P2];
+#pragma unroll
+            for (int sp = 0; sp < P2; ++sp) {
               mm[sp] = -INFINITY; ll[sp] = 0.f;
-              if (sp < n_parts_of_tile && rr < nrows) {
-                const size_t sl = (((size_t)first + sp) * Hkv + hkv) * A.part_rows + rr;
-                mm[sp] = __ldcg(A.part_ml + 2 * sl);
-                ll[sp] = __ldcg(A.part_ml + 2 * sl + 1);
+              if (sp == me) { mm[sp] = m_own; ll[sp] = l_own; }
+              else if (sp < n_parts_of_tile && in) {
+                mm[sp] = __ldcg(A.part_ml + 2 * (sl0 + sp * part_stride));
+                ll[sp] = __ldcg(A.part_ml + 2 * (sl0 + sp * part_stride) + 1);
               }
             }
             float m = -INFINITY;
 #pragma unroll
-            for (int sp = 0; sp < AT_MAX_PARTS; ++sp) m = fmaxf(m, mm[sp]);
+            for (int sp = 0; sp < P2; ++sp) m = fmaxf(m, mm[sp]);
             const float mb = m == -INFINITY ? 0.f : m;
             float l = 0.f;
 #pragma unroll
-            for (int sp = 0; sp < AT_MAX_PARTS; ++sp) { f[sp] = exp2f(mm[sp] - mb); l += f[sp] * ll[sp]; }
+            for (int sp = 0; sp < P2; ++sp) { fw[k][sp] = exp2f(mm[sp] - mb); l += fw[k][sp] * ll[sp]; }
             const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
-            for (int sp = 0; sp < AT_MAX_PARTS; ++sp) f[sp] *= inv;
+            for (int sp = 0; sp < P2; ++sp) fw[k][sp] *= inv;
+            src[k] = in ? A.part_acc + sl0 * AT_D + 4 * (lane & 3) : nullptr;
+            const int t2 = rr / G, h2 = rr - t2 * G;
+            outp[k] = in ? reinterpret_cast<char*>(A.out + (size_t)(U.row0 + U.q0 + t2) * ((size_t)Hq * AT_D) + (size_t)(hkv * G + h2) * AT_D) + 8 * (lane & 3)
+                         : nullptr;
           }
-          // 32 loads of 16 bytes per lane are in flight at a time: the fewer parts, the more rows at once
-          auto add_up = [&](auto p2_tag) {
-            constexpr int P2 = decltype(p2_tag)::value, RB = 32 / P2;
-#pragma unroll 1
-            for (int b0 = 0; b0 < 32; b0 += RB) {
-              float4 a4[P2][RB];
+          uint32_t o[32];
+#pragma unroll
+          for (int c0 = 0; c0 < AT_D; c0 += CH) {
+            // (with many parts the loads of a row are asked for only when the row's turn comes: registers)
+            constexpr bool AHEAD = P2 <= 4;
+            float4 oth[AHEAD ? PASSES : 1][AHEAD ? 4 : 1][P2];
+            auto ask = [&](int ps, int k, float4 (&into)[P2]) {
 #pragma unroll
               for (int sp = 0; sp < P2; ++sp)
+                into[sp] = sp != me && sp < n_parts_of_tile && src[k] != nullptr
+                               ? __ldcg(reinterpret_cast<const float4*>(src[k] + sp * part_stride * AT_D + c0 + ps * 16))
+                               : make_float4(0.f, 0.f, 0.f, 0.f);
+            };
+            if (AHEAD) {
 #pragma unroll
-                for (int u = 0; u < RB; ++u) {
-                  const int rr = mwarp + 8 * (b0 + u);
-                  const size_t sl = (((size_t)first + sp) * Hkv + hkv) * A.part_rows + rr;
-                  a4[sp][u] = sp < n_parts_of_tile && rr < nrows ? __ldcg(reinterpret_cast<const float4*>(A.part_acc + sl * AT_D) + lane)
-                                                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+              for (int ps = 0; ps < PASSES; ++ps)
+#pragma unroll
+                for (int k = 0; k < 4; ++k) ask(ps, k, oth[AHEAD ? ps : 0][AHEAD ? k : 0]);
+            }
+#pragma unroll
+            for (int ps = 0; ps < PASSES; ++ps) {
+              const int col = c0 + ps * 16;
+              if (col % 32 == 0) {
+                if (n_steps > 0) {
+                  tc_ld_32x32b_x32(lane_base + o_col + col, o);
+                  tc_wait_ld();
+                } else {
+#pragma unroll
+                  for (int i = 0; i < 32; ++i) o[i] = 0u;
                 }
+              }
+              // this warp's own 32 rows x 16 columns, from a row per lane to 16 bytes of four rows per lane
+              const uint32_t* v = o + (col % 32);
 #pragma unroll
-              for (int u = 0; u < RB; ++u) {
+              for (int c = 0; c < 4; ++c)
+                stage[lane * 4 + (c ^ ((lane >> 1) & 3))] = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+              __syncwarp();
+              uint4 own[4];
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const int row = 8 * k + (lane >> 2);
+                own[k] = stage[row * 4 + ((lane & 3) ^ ((row >> 1) & 3))];
+              }
+              __syncwarp();
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
                 float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                float4 (&theirs)[P2] = oth[AHEAD ? ps : 0][AHEAD ? k : 0];
+                if (!AHEAD) ask(ps, k, theirs);
 #pragma unroll
                 for (int sp = 0; sp < P2; ++sp) {
-                  const float wgt = __shfl_sync(0xffffffffu, f[sp], b0 + u);
-                  acc.x += wgt * a4[sp][u].x; acc.y += wgt * a4[sp][u].y; acc.z += wgt * a4[sp][u].z; acc.w += wgt * a4[sp][u].w;
+                  const bool mine = sp == me;
+                  const float4 x = make_float4(mine ? __uint_as_float(own[k].x) : theirs[sp].x, mine ? __uint_as_float(own[k].y) : theirs[sp].y,
+                                               mine ? __uint_as_float(own[k].z) : theirs[sp].z, mine ? __uint_as_float(own[k].w) : theirs[sp].w);
+                  const float wgt = fw[k][sp];
+                  acc.x += wgt * x.x; acc.y += wgt * x.y; acc.z += wgt * x.z; acc.w += wgt * x.w;
                 }
-                const int rr = mwarp + 8 * (b0 + u);
-                if (rr >= nrows) continue;
-                const int t2 = rr / G, h2 = rr - t2 * G;
-                uint2 v2;
-                v2.x = at_pack(acc.x, acc.y);
-                v2.y = at_pack(acc.z, acc.w);
-                *reinterpret_cast<uint2*>(out_row0 + (size_t)t2 * ((size_t)Hq * AT_D) + (size_t)(hkv * G + h2) * AT_D + 4 * lane) = v2;
+                if (outp[k] != nullptr) {
+                  uint2 v2;
+                  v2.x = at_pack(acc.x, acc.y);
+                  v2.y = at_pack(acc.z, acc.w);
+                  *reinterpret_cast<uint2*>(outp[k] + 2 * col) = v2;
+                }
               }
             }
-          };
-          if (n_parts_of_tile <= 2) add_up(std::integral_constant<int, 2>());
-          else if (n_parts_of_tile <= 4) add_up(std::integral_constant<int, 4>());
-          else add_up(std::integral_constant<int, AT_MAX_PARTS>());
-        }
+          }
+        };
+        if (n_parts_of_tile <= 2) merged_out(std::integral_constant<int, 2>(), std::integral_constant<int, 64>());
+        else if (n_parts_of_tile <= 4) merged_out(std::integral_constant<int, 4>(), std::integral_constant<int, 16>());
+        else merged_out(std::integral_constant<int, AT_MAX_PARTS>(), std::integral_constant<int, 16>());
       }
       AT_STAMP(5);
 #undef AT_STAMP
@@ -770,10 +837,11 @@ extern "C" int qe_flash_attention_tc_supported(int Hq, int Hkv, int D, int page_
 }
 
 // Which CTA runs which work units: the units (item i for kv head h is unit i Hkv + h) in the order of the item list,
-// which the caller has sorted by key steps, longest first, each to the CTA with the least work so far (a unit costs its
-// steps plus unit_cost).  out: n_ctas + 1 offsets into out itself, then the CTAs' unit numbers; it must hold
+// which the caller has sorted by key steps, longest first, each to the CTA with the least work so far; item_cost[i] is
+// what a unit of item i costs (its key steps plus what its start, its end and, for a part, its scratch and merge
+// cost, in key steps).  out: n_ctas + 1 offsets into out itself, then the CTAs' unit numbers; it must hold
 // n_ctas + 1 + n_items Hkv ints.  Returns the number of ints written, 0 if the arguments make no sense.
-extern "C" int qe_flash_attention_tc_schedule(const int* item_steps, int n_items, int Hkv, int n_ctas, float unit_cost, int* out) {
+extern "C" int qe_flash_attention_tc_schedule(const float* item_cost, int n_items, int Hkv, int n_ctas, int* out) {
   if (n_items <= 0 || Hkv <= 0 || n_ctas <= 0) return 0;
   const long n_units = (long)n_items * Hkv;
   if (n_units > 0x3fffffffL) return 0;
@@ -787,7 +855,7 @@ extern "C" int qe_flash_attention_tc_schedule(const int* item_steps, int n_items
     Slot top = heap[0];
     owner[u] = top.cta;
     ++count[top.cta];
-    top.load += (float)item_steps[u / Hkv] + unit_cost;
+    top.load += item_cost[u / Hkv];
     int k = 0;                                      // replace the root and sift down
     for (;;) {
       const int l = 2 * k + 1, r = l + 1;
@@ -814,8 +882,8 @@ extern "C" int qe_flash_attention_tc_schedule(const int* item_steps, int n_items
 // q: the step's queries [T, Hq, 128] with q_stride elements between tokens; pages [num_pages, 2, Hkv,
 // page_size, 128]; items: 12 ints each (see attention_flash.cuh; a tile here is 256 / G tokens, and
 // n_splits is the number of parts of the tile when part >= 0); sched: what qe_flash_attention_tc_schedule
-// wrote for these items and n_ctas CTAs, on the device; counters: one int per (first part, kv
-// head), zero before the first launch, needed when any item has part >= 0.
+// wrote for these items and n_ctas CTAs, on the device; counters: two ints per (first part, kv
+// head), zero before the first launch (the kernel leaves them zero), needed when any item has part >= 0.
 extern "C" int qe_flash_attention_tc(const void* q, long q_stride, int T, const void* pages, int num_pages,
                                      const int* block_tables, int max_blocks, const int* items, int n_items,
                                      const int* sched, int n_ctas,

@@ -49,11 +49,11 @@ TC_ROWS = 256           # rows per work item of the tcgen05 attention kernel (tw
 TC_BN = 128             # keys per step of the tcgen05 attention kernel
 TC_MIN_ROWS = 65        # rows of a request's portion from which the tcgen05 kernel serves it
 TC_TARGET_CTAS = 148    # one CTA per SM
-TC_MIN_PART_STEPS = 8   # key steps of a part at least, when tiles are cut to fill idle SMs
+TC_MIN_PART_STEPS = 4   # key steps of a part at least, when tiles are cut to fill idle SMs
 TC_MAX_PARTS = 8        # parts of one tile at most
 TC_BALANCE_BELOW_CTAS = 592   # tiles x kv heads below which the tiles' schedule is laid out and long tiles are cut (4 per SM)
-TC_ITEM_COST_STEPS = 1.0      # a CTA's start and end, in key steps
-TC_PART_COST_STEPS = 1.0      # a part's scratch and merge on top, in key steps
+TC_ITEM_COST_STEPS = 2.0      # a work unit's first scores, masked step and output, in key steps
+TC_PART_COST_STEPS = 5.0      # a part's scratch or merge on top, in key steps (the parts of a step move through L2 together)
 TC_FORCE_CAP = -1       # the most key steps of a work item (0: cut nothing); below 0 the library works it out
 
 
@@ -849,9 +849,9 @@ def _plan_tc_tiles(tiles: list, Hkv: int) -> tuple[list[int], int, list[int], in
         n_parts += parts
     out.sort(key=lambda kv: -kv[0])
     n_ctas = min(len(out) * Hkv, TC_TARGET_CTAS)
-    item_steps = (ctypes.c_int * len(out))(*[st for st, _ in out])
+    costs = (ctypes.c_float * len(out))(*[st + TC_ITEM_COST_STEPS + (TC_PART_COST_STEPS if item[4] >= 0 else 0.0) for st, item in out])
     sched = (ctypes.c_int * (n_ctas + 1 + len(out) * Hkv))()
-    n = int(lib().qe_flash_attention_tc_schedule(item_steps, len(out), Hkv, n_ctas, ctypes.c_float(TC_ITEM_COST_STEPS), sched))
+    n = int(lib().qe_flash_attention_tc_schedule(costs, len(out), Hkv, n_ctas, sched))
     _need(n == len(sched), "plan_attention: the schedule of the tcgen05 kernel could not be made")
     return [x for _, item in out for x in item], n_parts, list(sched), n_ctas
 
@@ -1021,7 +1021,7 @@ def paged_attention(qkv: torch.Tensor, kv_pages: torch.Tensor, block_tables: tor
         tc_parts, tc_rows, tc_ctas = plan[f"tc{key}_info_host"]
         part_acc = part_ml = counters = None
         if tc_parts:
-            _need(tc_parts * Hkv <= _MERGE_COUNTERS, "paged_attention: too many parts")
+            _need(2 * tc_parts * Hkv <= _MERGE_COUNTERS, "paged_attention: too many parts")   # (two counters a tile and kv head)
             part_acc = ctx.arena.alloc((tc_parts * Hkv * tc_rows, D), torch.float32)
             part_ml = ctx.arena.alloc((tc_parts * Hkv * tc_rows, 2), torch.float32)
             counters = _merge_counters(qkv.device, "tc")
