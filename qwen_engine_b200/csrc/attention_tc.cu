@@ -46,7 +46,6 @@
 #define AT_TMEM_COLS 512
 #define AT_RESCALE_STEP 8.0f    // log2 of the growth of the max that forces a rescale
 #define AT_MAX_PARTS 8          // parts of one tile at most
-#define AT_POLY_OF_8 0           // of every 8 pairs of exponentials in an unmasked step, so many are formed on the FMA pipe
 
 static __device__ int g_at_status = 0;          // 0 = fine; else code of the first wait that ran out
 
@@ -83,24 +82,6 @@ __device__ __forceinline__ float at_ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
   return y;
-}
-// 2^x for a pair of finite x <= 100 on the FMA pipe, so that the special-function unit, which every exponential of
-// both softmax groups goes through, has fewer to do: x = n + f with n = round(x) and f in [-0.5, 0.5], 2^f by a cubic
-// (relative error 7.5e-5, far below the rounding of P to bfloat16), n added to the exponent's bits.
-__device__ __forceinline__ float2 at_add2(float2 a, float2 b);
-__device__ __forceinline__ float2 at_fma2(float2 a, float2 b, float2 c);
-__device__ __forceinline__ float2 at_ex2_poly2(float2 x) {
-  const float magic = 12582912.f;                   // 1.5 * 2^23: the sum's low mantissa bits are round(x)
-  x.x = fmaxf(x.x, -126.f);
-  x.y = fmaxf(x.y, -126.f);
-  const float2 t = at_add2(x, make_float2(magic, magic));
-  const float2 n = at_add2(t, make_float2(-magic, -magic));
-  const float2 f = at_fma2(n, make_float2(-1.f, -1.f), x);
-  float2 p = at_fma2(f, make_float2(0.05517164617776871f, 0.05517164617776871f), make_float2(0.2426111251115799f, 0.2426111251115799f));
-  p = at_fma2(p, f, make_float2(0.6932609677314758f, 0.6932609677314758f));
-  p = at_fma2(p, f, make_float2(0.9999280571937561f, 0.9999280571937561f));
-  return make_float2(__int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23)),
-                     __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23)));
 }
 __device__ __forceinline__ float at_max3(float a, float b, float c) {
   float d;
@@ -448,8 +429,12 @@ flash_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
           tc_wait_ld();
           const int kt = U.kt_first + j * AT_BN;
           float mx = -INFINITY;
-          const bool whole = kt >= lo && kt + AT_BN <= hi;     // every key of the step is allowed for this row
-          if (whole) {
+          // A step's 128 keys as four runs of 32: where a run is allowed for all of the warp's rows (every run of a step
+          // before the diagonal) the maxima are chains of three-input instructions; where it is forbidden for all of
+          // them (behind the diagonal of the warp's first rows, before a window) nothing is computed for it at all; only
+          // the runs that the mask's edge crosses are masked key by key.  The decisions are the warp's, so no lane idles.
+          uint32_t live = 0;                              // bit c: run c has a key that some row of the warp may see
+          if (__all_sync(0xffffffffu, kt >= lo && kt + AT_BN <= hi)) {
             float mc[4];                                  // four chains of three-input maxima
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
@@ -458,16 +443,33 @@ flash_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
               for (int i = 2; i < 32; i += 2) mc[c] = at_max3(mc[c], __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
             }
             mx = fmaxf(fmaxf(mc[0], mc[1]), fmaxf(mc[2], mc[3]));
-          } else {
+            live = 15u;
+          } else
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
+          for (int c = 0; c < 4; ++c) {
+            const int k0 = kt + 32 * c;
+            const bool all_in = __all_sync(0xffffffffu, k0 >= lo && k0 + 32 <= hi);
+            const bool all_out = !all_in && __all_sync(0xffffffffu, k0 >= hi || k0 + 32 <= lo);
+            if (all_in) {
+              float mc = at_max3(__uint_as_float(s[c][0]), __uint_as_float(s[c][1]), __uint_as_float(s[c][2]));
+              float md = at_max3(__uint_as_float(s[c][3]), __uint_as_float(s[c][4]), __uint_as_float(s[c][5]));
+#pragma unroll
+              for (int i = 6; i < 30; i += 4) {
+                mc = at_max3(mc, __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
+                md = at_max3(md, __uint_as_float(s[c][i + 2]), __uint_as_float(s[c][i + 3]));
+              }
+              mx = at_max3(mx, fmaxf(mc, __uint_as_float(s[c][30])), fmaxf(md, __uint_as_float(s[c][31])));
+              live |= 1u << c;
+            } else if (!all_out) {
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
-                const int key = kt + c * 32 + i;
+                const int key = k0 + i;
                 const float v = (key >= lo && key < hi) ? __uint_as_float(s[c][i]) : -INFINITY;
                 s[c][i] = __float_as_uint(v);
                 mx = fmaxf(mx, v);
               }
+              live |= 1u << c;
+            }
           }
           mx *= scale_log2;                               // the scale is positive
           // the reference max moves only when the row's max has grown by more than the step
@@ -489,29 +491,20 @@ flash_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
           uint32_t pk[2][32];
           float2 sums[4];
           const float2 sc2 = make_float2(scale_log2, scale_log2), nb2 = make_float2(-base, -base);
-          if (whole) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              sums[c] = make_float2(0.f, 0.f);
+          for (int c = 0; c < 4; ++c) {
+            sums[c] = make_float2(0.f, 0.f);
+            if (!((live >> c) & 1)) {                     // nothing of this run is allowed: its P is zero
 #pragma unroll
-              for (int i = 0; i < 32; i += 2) {
-                const float2 x = at_fma2(make_float2(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])), sc2, nb2);
-                const float2 p = ((i >> 1) & 7) < AT_POLY_OF_8 ? at_ex2_poly2(x) : make_float2(at_ex2(x.x), at_ex2(x.y));
-                sums[c] = at_add2(sums[c], p);
-                pk[c >> 1][(c & 1) * 16 + (i >> 1)] = at_pack(p.x, p.y);
-              }
+              for (int i = 0; i < 16; ++i) pk[c >> 1][(c & 1) * 16 + i] = 0u;
+              continue;
             }
-          } else {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              sums[c] = make_float2(0.f, 0.f);
-#pragma unroll
-              for (int i = 0; i < 32; i += 2) {
-                const float2 x = at_fma2(make_float2(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])), sc2, nb2);
-                const float2 p = make_float2(at_ex2(x.x), at_ex2(x.y));
-                sums[c] = at_add2(sums[c], p);
-                pk[c >> 1][(c & 1) * 16 + (i >> 1)] = at_pack(p.x, p.y);
-              }
+            for (int i = 0; i < 32; i += 2) {
+              const float2 x = at_fma2(make_float2(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])), sc2, nb2);
+              const float2 p = make_float2(at_ex2(x.x), at_ex2(x.y));
+              sums[c] = at_add2(sums[c], p);
+              pk[c >> 1][(c & 1) * 16 + (i >> 1)] = at_pack(p.x, p.y);
             }
           }
           const float2 s01 = at_add2(sums[0], sums[1]), s23 = at_add2(sums[2], sums[3]);
