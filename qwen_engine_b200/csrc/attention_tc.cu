@@ -179,6 +179,14 @@ flash_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
     mbar_init_fence();
   }
   if (warp == 9) tc_alloc(&sm.tmem_base, AT_TMEM_COLS);
+  if (warp == 8 && u_begin < u_end) {
+    // what the first copies will need and no kernel writes: the tensor maps, and the block-table entries of the first
+    // unit's first keys (the step's index data come from the host's copy)
+    if (lane == 0) { tma_prefetch_map(&map_q); tma_prefetch_map(&map_kv); }
+    const AtUnit U0 = at_unit(A, A.sched[u_begin]);
+    const int blk = (U0.kt_first >> A.page_shift) + lane;
+    if (blk < A.max_blocks) asm volatile("prefetch.global.L1 [%0];\n" :: "l"(A.block_tables + (size_t)U0.req * A.max_blocks + blk));
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
