@@ -13,7 +13,7 @@
 // fixed order.  Any N; K a multiple of 8 (16-byte rows); the launcher refuses the rest.
 #include "gemm_small_m.cuh"
 
-template <int MT, typename TOut, int XMODE, bool RESID>
+template <int MT, typename TOut, int XMODE, bool RESID, int ROWS = 16>
 __global__ void __launch_bounds__(512)
 gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                     TOut* __restrict__ out, int M, int N, int K, int k_per_warp, FuseArgs na) {
@@ -22,18 +22,18 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
   // The weights are nobody's output: their first two chunks are on their way before this kernel
   // waits for the one before it, whose output the token operand is.
   GsmChunk c0, c1;
-  gsm_prefetch(w, N, K, k_per_warp, blockIdx.x, c0, c1);
+  gsm_prefetch<ROWS>(w, N, K, k_per_warp, blockIdx.x, c0, c1);
   if (gridDim.x <= 1024) {
     // (a grid that is resident all at once, waiting for the kernel before it: a layer's product, not
-    // the vocabulary's) and L2 is asked for the rest of this CTA's 16 rows (one contiguous block), in
+    // the vocabulary's) and L2 is asked for the rest of this CTA's rows (one contiguous block), in
     // pieces of 8 KB
-    const int rows = min(16, N - (int)blockIdx.x * 16);
+    const int rows = min(ROWS, N - (int)blockIdx.x * ROWS);
     const unsigned bytes = (unsigned)rows * (unsigned)K * 2u;
     const unsigned off = threadIdx.x * 8192u;
     if (off < bytes) {
       const unsigned size = min(8192u, bytes - off);
       asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n"
-                   :: "l"(reinterpret_cast<const unsigned char*>(w + (size_t)blockIdx.x * 16 * K) + off), "r"(size) : "memory");
+                   :: "l"(reinterpret_cast<const unsigned char*>(w + (size_t)blockIdx.x * ROWS * K) + off), "r"(size) : "memory");
     }
   }
   if (na.next_bytes) {
@@ -48,7 +48,7 @@ gemm_small_m_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
   }
   pdl_launch_dependents();
   pdl_wait();
-  gsm_cta<MT, TOut, XMODE, RESID>(x, w, out, M, N, K, k_per_warp, na, blockIdx.x, red, s_rstd, c0, c1);
+  gsm_cta<MT, TOut, XMODE, RESID, false, false, ROWS>(x, w, out, M, N, K, k_per_warp, na, blockIdx.x, red, s_rstd, c0, c1);
 }
 
 // The same product by clusters of S CTAs that share 16 weight rows, a share of K each (see gsm_cta, CLUSTER): for weight
@@ -150,10 +150,46 @@ static int launch_small_m_cluster(const void* x, const void* w, void* out, int M
   return 0;
 }
 
+// Matrices of so few rows that 16 per CTA leave half of the SMs idle, and 8 per CTA fill them: 8 rows a CTA and the
+// whole of K, instead of clusters of two that share 16 rows and meet (the meeting costs more than the loop over K).
+static int g_small_m_rows8 = 0;                    // (off: see ops.SMALL_M_ROWS8)
+extern "C" void qe_small_m_rows8(int on) { g_small_m_rows8 = on != 0; }
+extern "C" int qe_small_m_tile_cols(int N, int K) {
+  return g_small_m_rows8 && small_m_cluster_size(N, K) == 2 && (N + 7) / 8 <= 148 ? 8 : 16;
+}
+
+template <int MT, int XMODE, bool RESID>
+static int launch_small_m_rows8(const void* x, const void* w, void* out, int M, int N, int K, int out_f32,
+                                cudaStream_t stream, FuseArgs na) {
+  const int ctas = (N + 7) / 8;
+  int warps = 16;
+  int k_per_warp = ((K + warps - 1) / warps + 127) / 128 * 128;
+  warps = (K + k_per_warp - 1) / k_per_warp;
+  const size_t smem = (size_t)warps * 16 * 8 * MT * sizeof(float);
+  static bool configured = false;
+  if (!configured) {
+    const int max_smem = 16 * 16 * 8 * MT * (int)sizeof(float);
+    cudaFuncSetAttribute(gemm_small_m_kernel<MT, float, XMODE, RESID, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (!RESID)
+      cudaFuncSetAttribute(gemm_small_m_kernel<MT, __nv_bfloat16, XMODE, false, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    configured = true;
+  }
+  if (out_f32 || RESID) {
+    qe_launch(gemm_small_m_kernel<MT, float, XMODE, RESID, 8>, dim3(ctas), dim3(warps * 32), smem, stream,
+              (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (float*)out, M, N, K, k_per_warp, na);
+  } else {
+    qe_launch(gemm_small_m_kernel<MT, __nv_bfloat16, XMODE, false, 8>, dim3(ctas), dim3(warps * 32), smem, stream,
+              (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, M, N, K, k_per_warp, na);
+  }
+  QE_CHECK_LAUNCH("linear_small_m");
+  return 0;
+}
+
 template <int MT, int XMODE, bool RESID>
 static int launch_small_m(const void* x, const void* w, void* out, int M, int N, int K, int out_f32,
                           cudaStream_t stream, FuseArgs na) {
   if (XMODE != X_NORM) {
+    if (qe_small_m_tile_cols(N, K) == 8) return launch_small_m_rows8<MT, XMODE, RESID>(x, w, out, M, N, K, out_f32, stream, na);
     const int S = small_m_cluster_size(N, K);
     if (S > 1) return launch_small_m_cluster<MT, XMODE == X_NORM ? X_PLAIN : XMODE, RESID>(x, w, out, M, N, K, out_f32, S, stream, na);
   }
@@ -227,7 +263,8 @@ extern "C" int qe_linear_small_m_silu(const void* gate_up, const void* w, void* 
 // ssq_out[m, j] = sum of squares of resid[m, 16 j .. 16 j + 15] for j < ceil(N / 16).
 extern "C" int qe_linear_small_m_resid(const void* x, const void* w, float* resid, float* ssq_out, int ssq_ld,
                                        int M, int N, int K, int silu, cudaStream_t stream) {
-  if (!ssq_out || ssq_ld < (N + 15) / 16) QE_REFUSE("linear_small_m_resid: ssq_out must hold %d columns", (N + 15) / 16);
+  const int ssq_cols = (N + qe_small_m_tile_cols(N, K) - 1) / qe_small_m_tile_cols(N, K);
+  if (!ssq_out || ssq_ld < ssq_cols) QE_REFUSE("linear_small_m_resid: ssq_out must hold %d columns", ssq_cols);
   FuseArgs na{};
   na.ssq_out = ssq_out;
   na.ssq_ld = ssq_ld;

@@ -59,30 +59,33 @@ struct FuseArgs {
   unsigned long long next_bytes;
 };
 
-// a chunk of weights: 64 k of 16 rows = four 16-byte loads per lane
+// a chunk of weights: 64 k of 16 rows = four 16-byte loads per lane (a: row g, b: row g + 8); where a CTA has 8
+// rows (ROWS = 8), 128 k of 8 rows (a: k .. k + 63, b: k + 64 .. k + 127 of row g)
 struct GsmChunk { uint4 a0, b0, a1, b1; };
 
 // The first two chunks of the weights of CTA `vb` (16 rows from 16 vb on), for the calling warp's
 // slice of K.  They depend on nothing a kernel writes, so a caller issues them before it waits for
 // whatever produces the token operand (the previous kernel, or a grid barrier).
+template <int ROWS = 16>
 __device__ __forceinline__ void gsm_prefetch(const __nv_bfloat16* __restrict__ w, int N, int K, int k_per_warp, int vb,
                                              GsmChunk& c0, GsmChunk& c1, int k_off = 0, int k_len = 1 << 30) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
-  const int n0 = vb * 16;
+  const int n0 = vb * ROWS;
   const __nv_bfloat16* w0 = w + (size_t)min(n0 + g, N - 1) * K;
-  const __nv_bfloat16* w1 = w + (size_t)min(n0 + g + 8, N - 1) * K;
+  const __nv_bfloat16* w1 = ROWS == 16 ? w + (size_t)min(n0 + g + 8, N - 1) * K : w0 + 64;     // (8 rows: the same row, 64 k on)
   const int kbeg = k_off + warp * k_per_warp, kend = min(min(K, k_off + k_len), kbeg + k_per_warp);
   const uint4 zero = make_uint4(0, 0, 0, 0);
   auto load_chunk = [&](int k0, GsmChunk& ch) {
     const int ka = k0 + 8 * c, kb = k0 + 32 + 8 * c;
+    const int far = ROWS == 16 ? 0 : 64;
     ch.a0 = ka < kend ? ld_stream16(w0 + ka) : zero;
-    ch.b0 = ka < kend ? ld_stream16(w1 + ka) : zero;
+    ch.b0 = ka + far < kend ? ld_stream16(w1 + ka) : zero;
     ch.a1 = kb < kend ? ld_stream16(w0 + kb) : zero;
-    ch.b1 = kb < kend ? ld_stream16(w1 + kb) : zero;
+    ch.b1 = kb + far < kend ? ld_stream16(w1 + kb) : zero;
   };
   load_chunk(kbeg, c0);
-  load_chunk(kbeg + 64, c1);
+  load_chunk(kbeg + (ROWS == 16 ? 64 : 128), c1);
 }
 
 // The work of CTA `vb` of the product, by all threads of the calling CTA (blockDim.x / 32 warps split
@@ -101,7 +104,11 @@ __device__ __forceinline__ void gsm_prefetch(const __nv_bfloat16* __restrict__ w
 // sums with st.async, which counts the bytes on that CTA's barrier, and leave; the first CTA waits for the bytes
 // (bounded: on giving up it records code 1 in g_gsm_status and writes nothing).  The order of the sum stays the CTAs'.
 static __device__ int g_gsm_status = 0;
-template <int MT, typename TOut, int XMODE, bool RESID, bool CLUSTER = false, bool PUSH = false>
+//
+// ROWS = 8: the CTA owns 8 weight rows instead of 16 (the instructions' rows 8 to 15 stay empty) and a chunk is 128 k of
+// them: twice the CTAs without a cluster's meeting, for matrices of so few rows that 16 per CTA leave half of the SMs idle
+// (not with CLUSTER).  k_per_warp is then a multiple of 128.
+template <int MT, typename TOut, int XMODE, bool RESID, bool CLUSTER = false, bool PUSH = false, int ROWS = 16>
 __device__ __forceinline__ void gsm_cta(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                                         TOut* __restrict__ out, int M, int N, int K, int k_per_warp, const FuseArgs& na,
                                         int vb, float* red, float* s_rstd, GsmChunk c0, GsmChunk c1, int k_off = 0,
@@ -110,10 +117,11 @@ __device__ __forceinline__ void gsm_cta(const __nv_bfloat16* __restrict__ x, con
   constexpr bool NORM = XMODE == X_NORM;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const int g = lane >> 2, c = lane & 3;
-  const int n0 = vb * 16;
+  static_assert(ROWS == 16 || (ROWS == 8 && !CLUSTER), "8 rows a CTA: without clusters");
+  const int n0 = vb * ROWS;
   const int r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1);     // clamped; discarded at the store
   const __nv_bfloat16* w0 = w + (size_t)r0 * K;
-  const __nv_bfloat16* w1 = w + (size_t)r1 * K;
+  const __nv_bfloat16* w1 = ROWS == 16 ? w + (size_t)r1 * K : w0 + 64;
   const int kbeg = k_off + warp * k_per_warp, kend = min(min(K, k_off + k_len), kbeg + k_per_warp);
   const int x_ld = SILU ? 2 * K : K;
   const bool writer = !CLUSTER || cluster_cta_rank() == 0;
@@ -128,10 +136,11 @@ __device__ __forceinline__ void gsm_cta(const __nv_bfloat16* __restrict__ x, con
   auto load_chunk = [&](int k0) {
     GsmChunk ch;
     const int ka = k0 + 8 * c, kb = k0 + 32 + 8 * c;
+    const int far = ROWS == 16 ? 0 : 64;
     ch.a0 = ka < kend ? ld_stream16(w0 + ka) : zero;
-    ch.b0 = ka < kend ? ld_stream16(w1 + ka) : zero;
+    ch.b0 = ka + far < kend ? ld_stream16(w1 + ka) : zero;
     ch.a1 = kb < kend ? ld_stream16(w0 + kb) : zero;
-    ch.b1 = kb < kend ? ld_stream16(w1 + kb) : zero;
+    ch.b1 = kb + far < kend ? ld_stream16(w1 + kb) : zero;
     return ch;
   };
   auto load_x = [&](int m, int k) {
@@ -165,16 +174,29 @@ __device__ __forceinline__ void gsm_cta(const __nv_bfloat16* __restrict__ x, con
     for (int t = 0; t < MT; ++t) {
       const uint4 xa = load_x(t * 8 + g, ka);
       const uint4 xb = load_x(t * 8 + g, kb);
-      mma_bf16_16816(acc[t], ch.a0.x, ch.b0.x, ch.a0.y, ch.b0.y, xa.x, xa.y);
-      mma_bf16_16816(acc[t], ch.a0.z, ch.b0.z, ch.a0.w, ch.b0.w, xa.z, xa.w);
-      mma_bf16_16816(acc[t], ch.a1.x, ch.b1.x, ch.a1.y, ch.b1.y, xb.x, xb.y);
-      mma_bf16_16816(acc[t], ch.a1.z, ch.b1.z, ch.a1.w, ch.b1.w, xb.z, xb.w);
+      if (ROWS == 16) {
+        mma_bf16_16816(acc[t], ch.a0.x, ch.b0.x, ch.a0.y, ch.b0.y, xa.x, xa.y);
+        mma_bf16_16816(acc[t], ch.a0.z, ch.b0.z, ch.a0.w, ch.b0.w, xa.z, xa.w);
+        mma_bf16_16816(acc[t], ch.a1.x, ch.b1.x, ch.a1.y, ch.b1.y, xb.x, xb.y);
+        mma_bf16_16816(acc[t], ch.a1.z, ch.b1.z, ch.a1.w, ch.b1.w, xb.z, xb.w);
+      } else {
+        const uint4 xc = load_x(t * 8 + g, ka + 64);
+        const uint4 xd = load_x(t * 8 + g, kb + 64);
+        mma_bf16_16816(acc[t], ch.a0.x, 0u, ch.a0.y, 0u, xa.x, xa.y);
+        mma_bf16_16816(acc[t], ch.a0.z, 0u, ch.a0.w, 0u, xa.z, xa.w);
+        mma_bf16_16816(acc[t], ch.a1.x, 0u, ch.a1.y, 0u, xb.x, xb.y);
+        mma_bf16_16816(acc[t], ch.a1.z, 0u, ch.a1.w, 0u, xb.z, xb.w);
+        mma_bf16_16816(acc[t], ch.b0.x, 0u, ch.b0.y, 0u, xc.x, xc.y);
+        mma_bf16_16816(acc[t], ch.b0.z, 0u, ch.b0.w, 0u, xc.z, xc.w);
+        mma_bf16_16816(acc[t], ch.b1.x, 0u, ch.b1.y, 0u, xd.x, xd.y);
+        mma_bf16_16816(acc[t], ch.b1.z, 0u, ch.b1.w, 0u, xd.z, xd.w);
+      }
     }
   };
   float resid_old = 0.f;                            // RESID: this thread's element of the stream, fetched early
   if (RESID && writer) {
-    const int m = threadIdx.x >> 4, n = n0 + (threadIdx.x & 15);
-    if (threadIdx.x < 16 * 8 * MT && m < M && n < N) resid_old = __ldcg(reinterpret_cast<const float*>(out) + (size_t)m * N + n);
+    const int m = threadIdx.x / ROWS, n = n0 + (threadIdx.x & (ROWS - 1));
+    if (threadIdx.x < ROWS * 8 * MT && m < M && n < N) resid_old = __ldcg(reinterpret_cast<const float*>(out) + (size_t)m * N + n);
   }
   if (NORM) {
     // the row norms from the partial sums of squares: a warp per row, all loads at once, summed in a
@@ -188,11 +210,12 @@ __device__ __forceinline__ void gsm_cta(const __nv_bfloat16* __restrict__ x, con
     }
     __syncthreads();
   }
-  for (int k0 = kbeg; k0 < kend; k0 += 128) {
-    const GsmChunk n0c = load_chunk(k0 + 128);
+  constexpr int CK = ROWS == 16 ? 64 : 128;         // k of a chunk
+  for (int k0 = kbeg; k0 < kend; k0 += 2 * CK) {
+    const GsmChunk n0c = load_chunk(k0 + 2 * CK);
     compute(c0, k0);
-    const GsmChunk n1c = load_chunk(k0 + 192);
-    compute(c1, k0 + 64);
+    const GsmChunk n1c = load_chunk(k0 + 3 * CK);
+    compute(c1, k0 + CK);
     c0 = n0c;
     c1 = n1c;
   }
@@ -255,8 +278,8 @@ __device__ __forceinline__ void gsm_cta(const __nv_bfloat16* __restrict__ x, con
     }
   }
   if (writer)
-  for (int e = threadIdx.x; e < 16 * MW; e += blockDim.x) {
-    const int m = e >> 4, i = e & 15;               // consecutive threads: consecutive weight rows
+  for (int e = threadIdx.x; e < ROWS * MW; e += blockDim.x) {
+    const int m = e / ROWS, i = e & (ROWS - 1);     // consecutive threads: consecutive weight rows
     const int n = n0 + i;
     // the sum over K: the warps' parts in order, or (CLUSTER) the CTAs' sums in order
     auto total = [&]() {
@@ -274,7 +297,7 @@ __device__ __forceinline__ void gsm_cta(const __nv_bfloat16* __restrict__ x, con
       if (m >= M || n >= N) continue;
       out[(size_t)m * N + n] = from_f32<TOut>(total());
     } else {
-      // whole warps run this loop (16 MW is a multiple of 32); lanes outside the matrix add zero
+      // whole warps run this loop (ROWS MW is a multiple of 32); lanes outside the matrix add zero
       float v = 0.f;
       if (m < M && n < N) {
         const float s = total();
@@ -282,8 +305,8 @@ __device__ __forceinline__ void gsm_cta(const __nv_bfloat16* __restrict__ x, con
         v = (e == threadIdx.x ? resid_old : __ldcg(dst)) + s;
         *dst = v;
       }
-      float sq = v * v;                              // over the 16 columns of the row: lanes i = 0..15
-      sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+      float sq = v * v;                              // over the CTA's columns of the row: lanes i = 0 .. ROWS - 1
+      if (ROWS == 16) sq += __shfl_xor_sync(0xffffffffu, sq, 8);
       sq += __shfl_xor_sync(0xffffffffu, sq, 4);
       sq += __shfl_xor_sync(0xffffffffu, sq, 2);
       sq += __shfl_xor_sync(0xffffffffu, sq, 1);

@@ -213,11 +213,11 @@ class ResidualStream:
     def for_step(cls, alloc, num_tokens: int, width: int, dtype: torch.dtype) -> "ResidualStream":
         """The stream of a step of ``num_tokens`` rows of ``width``, from ``alloc(shape, dtype)``.  For a few rows
         in bfloat16 it also gets room for the partial sums of squares that the products which add into the
-        stream leave behind (one per 16 columns, padded to whole float4s): their layout is the kernels'
+        stream leave behind (one per 16 or per 8 columns, padded to whole float4s): their layout is the kernels'
         business, so it is settled here, beside their fronts, and not by the model."""
         ssq = None
         if dtype == torch.bfloat16 and num_tokens <= SMALL_M_MAX:
-            ssq = alloc((num_tokens, -(-(-(-width // 16)) // 4) * 4), torch.float32)
+            ssq = alloc((num_tokens, -(-(-(-width // 8)) // 4) * 4), torch.float32)
         return cls(alloc((num_tokens, width), torch.float32), alloc((num_tokens, width), dtype), ssq)
 
 
@@ -271,6 +271,8 @@ class NormedInput:
 #   SiLU-mul into the product that consumes it               0.6B equal, 4B 1 960 / 2 080: on up to 4 096 columns
 #       of gate/up per half (every CTA reads both halves of gate_up).
 #   the branch's add into the stream in the product's epilogue   0.6B 6 870 / 6 820, 4B 2 070 / 1 740: on.
+SMALL_M_ROWS8 = False   # products of a few rows with so few weight rows that clusters of two share 16: 8 rows a CTA instead (a tested
+                        # option that is off: no meeting, but every CTA reads all of x, and the batch-8 step went from 0.913 to 0.943 ms)
 FUSED_NORM_MAX_M = 0    # rows up to which a norm is fused into the product that follows (0: never)
 FUSED_SILU_MAX_M = 64   # rows up to which SiLU-mul is formed by the product that consumes it ...
 FUSED_SILU_MAX_K = 4096  # ... when the activation has at most this many columns
@@ -335,14 +337,17 @@ def _linear_into_stream(x: torch.Tensor, w: torch.Tensor, sink: ResidualSink, si
             st.n_ssq = 0
             return True
     if not (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and M <= min(SMALL_M_MAX, RESID_SINK_MAX_M) and K % 8 == 0
-            and not st.has_delta and st.ssq is not None and st.ssq.shape[1] >= -(-N // 16)
-            and st.resid.shape == (M, N)):
+            and not st.has_delta and st.ssq is not None and st.resid.shape == (M, N)):
+        return False
+    lib().qe_small_m_rows8(int(SMALL_M_ROWS8))
+    cols = int(lib().qe_small_m_tile_cols(N, K))        # columns of a CTA: it leaves one partial sum of squares per row
+    if st.ssq.shape[1] < -(-N // cols):
         return False
     _need(w.shape == (N, K) and x.is_contiguous() and w.is_contiguous(), "linear: operands do not fit")
     _hand_over_next_weights()
     _check(lib().qe_linear_small_m_resid(_ptr(x), _ptr(w), _ptr(st.resid), _ptr(st.ssq), int(st.ssq.shape[1]),
                                          M, N, K, int(silu), _stream()), "linear")
-    st.n_ssq = -(-N // 16)
+    st.n_ssq = -(-N // cols)
     return True
 
 
@@ -401,6 +406,7 @@ def linear(x, w: torch.Tensor, out: torch.Tensor) -> None:
     if x.dtype == torch.bfloat16 and M <= SMALL_M_MAX and K % 8 == 0:
         # a few rows: stream every weight once through the tensor cores
         _hand_over_next_weights()
+        lib().qe_small_m_rows8(int(SMALL_M_ROWS8))
         _check(lib().qe_linear_small_m(_ptr(x), _ptr(w), _ptr(out), M, N, K, out_f32, _stream()), "linear")
         return
     if (x.dtype == torch.bfloat16 and TCGEN05_PAIRS and TCGEN05_ENABLED and K % 8 == 0
@@ -610,6 +616,7 @@ def linear_silu_mul(gate_up: torch.Tensor, w: torch.Tensor, out: torch.Tensor, s
     _need(gate_up.is_contiguous() and w.is_contiguous() and out.is_contiguous(), "linear_silu_mul: operands must be contiguous")
     if gate_up.dtype == torch.bfloat16 and M <= SMALL_M_MAX and I % 8 == 0:
         _hand_over_next_weights()
+        lib().qe_small_m_rows8(int(SMALL_M_ROWS8))
         _check(lib().qe_linear_small_m_silu(_ptr(gate_up), _ptr(w), _ptr(out), M, N, I,
                                             int(out.dtype == torch.float32), _stream()), "linear_silu_mul")
         return

@@ -923,11 +923,12 @@ def test_linear_swiglu_small(M, I, K):
 
 @pytest.mark.parametrize("M", [1, 3, 8, 16])
 @pytest.mark.parametrize("N,K", [(1024, 2048), (1024, 3072), (264, 4096)])
-def test_cluster_sums_pushed_and_pulled_are_the_same_to_the_bit(M, N, K):
+def test_cluster_sums_pushed_and_pulled_are_the_same_to_the_bit(M, N, K, monkeypatch):
     """The CTAs of a cluster that share K meet in the first CTA either by pushing their sums into its shared memory
     (st.async counted on its mbarrier; used for single rows) or by being read from there between two cluster
     barriers: the order of the sum is the CTAs' either way, so the results are identical, also when the product
     adds into the residual stream; no status word is set."""
+    monkeypatch.setattr(ops, "SMALL_M_ROWS8", False)       # (clusters of two, where 8 rows a CTA would serve otherwise)
     x = _randn((M, K), torch.bfloat16, 13).to(DEV)
     w = _randn((N, K), torch.bfloat16, 14, K ** -0.5).to(DEV)
     outs = {}
@@ -952,11 +953,17 @@ def test_cluster_sums_pushed_and_pulled_are_the_same_to_the_bit(M, N, K):
 @pytest.mark.parametrize("M", [1, 8, 13, 40])
 @pytest.mark.parametrize("N,K", [(1024, 2048), (1024, 3072), (1000, 1032), (592, 4096), (100, 2064), (1184, 1024)])
 @pytest.mark.parametrize("mode", ["bf16", "f32", "stream"])
-def test_linear_small_m_shares_k_in_clusters(M, N, K, mode, monkeypatch):
+@pytest.mark.parametrize("rows8", [True, False])
+def test_linear_small_m_shares_k_in_clusters(M, N, K, mode, rows8, monkeypatch):
     """Weight matrices of few rows: the CTAs of a cluster share 16 weight rows and a part of K each, and meet in
-    distributed shared memory (2 or 4 CTAs, chosen from the weight matrix alone).  Plain output, float32 output, and
-    the add into the residual stream with the sums of squares left behind."""
+    distributed shared memory (2 or 4 CTAs, chosen from the weight matrix alone); or, where clusters of two would
+    serve and 8 rows a CTA fill the SMs (``rows8``), CTAs of 8 rows and the whole of K, no meeting.  Plain output,
+    float32 output, and the add into the residual stream with the sums of squares left behind."""
     monkeypatch.setattr(ops, "SPLITK", False)              # (the tcgen05 kernel for some tens of rows is tested elsewhere)
+    monkeypatch.setattr(ops, "SMALL_M_ROWS8", rows8)
+    ops.lib().qe_small_m_rows8(int(rows8))
+    cols = int(ops.lib().qe_small_m_tile_cols(N, K))
+    assert cols == (8 if rows8 and (N, K) in ((1024, 2048), (1024, 3072), (1000, 1032), (1184, 1024)) else 16)
     x = _randn((M, K), torch.bfloat16, 3)
     w = _randn((N, K), torch.bfloat16, 4, K ** -0.5)
     want = x.float() @ w.float().t()
@@ -965,7 +972,7 @@ def test_linear_small_m_shares_k_in_clusters(M, N, K, mode, monkeypatch):
         stream = ops.ResidualStream.for_step(lambda shape, dtype: torch.zeros(shape, dtype=dtype, device=DEV), M, N, torch.bfloat16)
         stream.resid.copy_(resid)
         ops.linear(x.to(DEV), w.to(DEV), ops.ResidualSink(stream))
-        assert not stream.has_delta and stream.n_ssq == -(-N // 16)
+        assert not stream.has_delta and stream.n_ssq == -(-N // cols)
         got = stream.resid.cpu()
         _close(got, resid + want, torch.bfloat16)
         ssq = stream.ssq[:, :stream.n_ssq].sum(dim=1).cpu()
