@@ -272,7 +272,7 @@ class NormedInput:
 #       of gate/up per half (every CTA reads both halves of gate_up).
 #   the branch's add into the stream in the product's epilogue   0.6B 6 870 / 6 820, 4B 2 070 / 1 740: on.
 SMALL_M_ROWS8 = False   # products of a few rows with so few weight rows that clusters of two share 16: 8 rows a CTA instead (a tested
-                        # option that is off: no meeting, but every CTA reads all of x, and the batch-8 step went from 0.913 to 0.943 ms)
+                        # option that is off: no meeting, but every CTA reads all of x, and the batch-8 step went from 0.919 to 0.941 ms)
 FUSED_NORM_MAX_M = 0    # rows up to which a norm is fused into the product that follows (0: never)
 FUSED_SILU_MAX_M = 64   # rows up to which SiLU-mul is formed by the product that consumes it ...
 FUSED_SILU_MAX_K = 4096  # ... when the activation has at most this many columns
