@@ -2,6 +2,7 @@
 and bfloat16, at sizes other than the engine's models: widths and vocabularies that are no
 power of two, head sizes in steps of 16, odd numbers of heads and groups."""
 import math
+import random
 from types import SimpleNamespace
 
 import pytest
@@ -761,6 +762,27 @@ def test_tc_attention_units_one_after_the_other(ctas, Hq, Hkv, P, q_lens, ctx_le
         got = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ops.paged_attention, DEV)
         assert ops.tc_attention_status() == 0
         assert torch.equal(got, each)
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_tc_attention_random_batches(seed, monkeypatch):
+    """Random batches, geometries, windows, page sizes, numbers of CTAs and ways of cutting the tiles, against the plain
+    reference: whatever the schedule, a row's output is that of its keys."""
+    rng = random.Random(1000 + seed)
+    Hq, Hkv = rng.choice([(16, 8), (4, 2), (8, 1), (4, 4), (2, 1), (32, 8)])
+    P = rng.choice([8, 16, 32, 128])
+    window = rng.choice([0, 0, 0, 70, 128, 513])
+    n = rng.randint(1, 5)
+    q_lens = [rng.choice([1, 2, 40, 64, 65, 127, 128, 129, 200, 333, 700, 1300]) for _ in range(n)]
+    ctx_lens = [rng.choice([0, 0, 5, 64, 127, 128, 900, 2100]) for _ in range(n)]
+    D, dtype = 128, torch.bfloat16
+    monkeypatch.setattr(ops, "TC_TARGET_CTAS", rng.choice([1, 2, 5, 31, 148]))
+    monkeypatch.setattr(ops, "TC_FORCE_CAP", rng.choice([-1, -1, 0, 1, 2, 3, 5]))
+    case = _attention_case(dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, seed=2000 + seed)
+    want = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ref_ops.paged_attention, "cpu")
+    got = _run_attention(case, dtype, Hq, Hkv, D, P, q_lens, ctx_lens, window, ops.paged_attention, DEV)
+    assert ops.tc_attention_status() == 0 and ops.device_status() == {}
+    _close(got, want, dtype)
 
 
 @pytest.mark.parametrize("q_lens,ctx_lens", [([200], [30000]), ([1, 1], [30000, 17]), ([3], [40000])])
