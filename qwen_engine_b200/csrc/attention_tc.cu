@@ -5,15 +5,19 @@
 // kernel leaves the instructions to the compiler; here S = Q·K^T and O += P·V are tcgen05.mma with
 // the accumulators, and P itself, in tensor memory.)
 //
-// One CTA serves one kv head and a tile of 256 "rows" (a row is a query token x a query head of the kv
+// A work unit is one kv head and a tile of 256 "rows" (a row is a query token x a query head of the kv
 // head's group, so the keys and values are read once for the whole group), as two halves of 128 rows,
-// one per softmax group.  Ten warps:
-//   warps 0-3, 4-7  the two softmax groups: one thread per row (= tensor-memory lane).  Per key step
-//                   a thread reads its row of S from tensor memory, masks, takes the running max,
-//                   exponentiates, writes P (bfloat16) back over S, and rescales O when the max grew;
-//   warp 8          fetches Q once and the key and value tiles of every step (128 keys) with TMA, page
-//                   by page from the block table, through a two-stage ring;
-//   warp 9          owns tensor memory and issues all MMAs from one thread.
+// one per softmax group.  The kernel runs one CTA per SM at most; each walks the units that the host's
+// schedule gives it (qe_flash_attention_tc_schedule), one after the other through the same pipelines.
+// Twelve warps:
+//   warps 0-3, 4-7  the two softmax groups: one thread per row (= tensor-memory lane), 208 registers a
+//                   thread (setmaxnreg).  Per key step a thread reads its row of S from tensor memory,
+//                   masks, takes the running max, exponentiates, writes P (bfloat16) back over S, and
+//                   rescales O when the max grew; at a unit's end it writes the rows out;
+//   warp 8          fetches a unit's Q and the key and value tiles of every step (128 keys) with TMA, page
+//                   by page from the block table, through a two-stage ring that runs on across units;
+//   warp 9          owns tensor memory and issues all MMAs from one thread;
+//   warps 10, 11    idle (they make the third group of four warps whole, for setmaxnreg).
 // While one group works on its softmax, the tensor core runs the other group's products.
 // Tensor memory (512 columns): S of group 0 | S of group 1 | O of group 0 | O of group 1; P lies over
 // the first 64 columns of its S.
@@ -21,16 +25,17 @@
 // The running max is allowed to lag: O and the running sum are rescaled only when the max grew by more
 // than 2^8 since the last rescale, which leaves the quotient O / sum unchanged but for rounding.
 //
-// A work item may cover only a range of keys (a part of a long context); then the CTA writes its
-// unnormalised accumulator with max and sum in float32 to scratch memory, and the CTA that finishes a
-// tile's last part combines the parts (same protocol as the mma.sync kernel, attention_flash.cuh).
+// A work item may cover only a range of keys (a part of a long tile).  Of a tile's parts, those that are
+// not the last to get to their end write their unnormalised accumulator with max and sum in float32 to
+// scratch memory; the last one adds them to its own, which never leaves tensor memory, in the order of
+// the parts, and writes the tile's rows (two counters a tile and kv head: parts arrived, parts written).
 //
 // Keys of a tile that lie in no page (block table entry -1, or past the table) are read as zeros; keys
 // of a held page past the request's length are read as they are and masked, so pages must hold finite
 // values (the cache starts as zeros and only kernels write to it).
 //
-// Every wait on an mbarrier is bounded: a wait that runs out records a code in a device flag, raises a
-// CTA-wide abort that the other roles see in their own waits, and the CTA skips its stores, frees its
+// Every wait on an mbarrier, and the last part's wait for the others' to be written, is bounded: a wait that
+// runs out records a code in a device flag, raises a CTA-wide abort that the other roles see in their own waits, and the CTA skips its stores, frees its
 // tensor memory and returns; the host reads the flag with qe_flash_attention_tc_status().
 #include "tcgen05.cuh"
 #include <math.h>
