@@ -26,6 +26,8 @@ SPLITK = True           # products of some tens of rows by clusters of CTAs that
 SPLITK_MIN_M = 17       # rows from which, up to SPLITK_MAX_M, that kernel serves
 SPLITK_MAX_M = 64
 SPLITK_MAX_CTAS = 148   # clusters x CTAs at most: all on the GPU at once
+SPLITK_MAX_CLUSTERS_OF_8 = 8   # clusters of 8 CTAs at most (16 of them, 2 048 weight rows, took 8.9 us where 16 clusters of 4 take 5.5: a
+                               # cluster needs its SMs in one part of the GPU)
 SWAP_MIN_M = 17         # rows from which, up to SMALL_M_MAX, wide products go to the swapped tcgen05 kernel
 SWAP_MIN_N = 3072       # weight rows from which it has enough CTAs (one per 128) to pull the weights fast enough
 SWIGLU_FUSED = True     # SiLU-mul in the epilogue of the gate/up product where the CTA-pair kernel serves it
@@ -298,13 +300,15 @@ def _linear_normed(x: NormedInput, w: torch.Tensor, out: torch.Tensor) -> bool:
 
 def splitk_splits(M: int, N: int, K: int, dtype: torch.dtype) -> int:
     """How many CTAs share a tile of 128 weight rows, each with a share of K, in the product of some tens
-    of rows (``linear_splitk``): as many of 8, 4, 2 as keep all clusters on the GPU at once; 0 where that
+    of rows (``linear_splitk``): as many of 8, 4, 2 as keep all clusters on the GPU at once (8 only for few clusters); 0 where that
     kernel does not apply (few rows, enough weight rows for every SM, other types)."""
     if not (TCGEN05_ENABLED and SPLITK and dtype == torch.bfloat16
             and SPLITK_MIN_M <= M <= SPLITK_MAX_M and K % 8 == 0 and N % 4 == 0):
         return 0
     tiles = -(-N // 128)
     for s in (8, 4, 2):
+        if s == 8 and tiles > SPLITK_MAX_CLUSTERS_OF_8:
+            continue
         if tiles * s <= SPLITK_MAX_CTAS and -(-K // 64) >= 2 * s:
             return s
     return 0

@@ -220,6 +220,7 @@ def test_linear_picks_splitk():
     when the product is added to the residual stream; a few rows and many rows go elsewhere."""
     assert ops.splitk_splits(64, 1024, 3072, torch.bfloat16) == 8
     assert ops.splitk_splits(17, 4096, 1024, torch.bfloat16) == 4
+    assert ops.splitk_splits(32, 2048, 6144, torch.bfloat16) == 4      # 16 clusters: of 4 CTAs, not of 8
     assert ops.splitk_splits(32, 6144, 1024, torch.bfloat16) == 2
     assert ops.splitk_splits(8, 1024, 3072, torch.bfloat16) == 0
     assert ops.splitk_splits(65, 1024, 3072, torch.bfloat16) == 0
