@@ -195,7 +195,7 @@ static int launch_small_m(const void* x, const void* w, void* out, int M, int N,
   }
   // warps split K in slices that are multiples of 64; more warps when there are few CTAs
   const int ctas = (N + 15) / 16;
-  int warps = ctas >= 2048 ? 4 : (ctas >= 256 ? 8 : 16);
+  int warps = ctas >= 2048 ? 4 : (ctas > 148 ? 8 : 16);     // (more CTAs than SMs: 8 warps, so that two CTAs fit an SM and all start at once)
   int k_per_warp = ((K + warps - 1) / warps + 63) / 64 * 64;
   warps = (K + k_per_warp - 1) / k_per_warp;
   const size_t smem = (size_t)warps * 16 * 8 * MT * sizeof(float);

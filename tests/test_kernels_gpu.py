@@ -186,9 +186,9 @@ def test_linear_tcgen05_swapped(M, N, K, out_f32, monkeypatch):
     _close(got, want, torch.bfloat16, scale=float(want.float().abs().max()))
 
 
-@pytest.mark.parametrize("M", [1, 17, 33, 64])
+@pytest.mark.parametrize("M", [1, 9, 17, 33, 64])
 @pytest.mark.parametrize("N,K,splits", [(1024, 2048, 8), (1024, 3072, 8), (1000, 1032, 4), (132, 200, 2), (4096, 1024, 4),
-                                        (256, 192, 8), (6144, 1024, 2)])
+                                        (256, 192, 8), (6144, 1024, 2), (2560, 4096, 4)])
 @pytest.mark.parametrize("mode", ["bf16", "f32", "add"])
 def test_linear_splitk(M, N, K, splits, mode):
     """Up to 64 rows against few weight rows in bfloat16: clusters of CTAs that share K and add their partial
@@ -221,6 +221,9 @@ def test_linear_picks_splitk():
     assert ops.splitk_splits(64, 1024, 3072, torch.bfloat16) == 8
     assert ops.splitk_splits(17, 4096, 1024, torch.bfloat16) == 4
     assert ops.splitk_splits(32, 2048, 6144, torch.bfloat16) == 4      # 16 clusters: of 4 CTAs, not of 8
+    assert ops.splitk_splits(12, 2560, 9728, torch.bfloat16) == 4      # a long K and more CTAs of 16 rows than SMs: from 9 rows on
+    assert ops.splitk_splits(8, 2560, 9728, torch.bfloat16) == 0 and ops.splitk_splits(12, 4096, 1024, torch.bfloat16) == 0
+    assert ops.splitk_splits(12, 6144, 4096, torch.bfloat16) == 0      # (only two CTAs a cluster would fit)
     assert ops.splitk_splits(32, 6144, 1024, torch.bfloat16) == 2
     assert ops.splitk_splits(8, 1024, 3072, torch.bfloat16) == 0
     assert ops.splitk_splits(65, 1024, 3072, torch.bfloat16) == 0
