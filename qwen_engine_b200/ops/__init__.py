@@ -28,6 +28,8 @@ SPLITK_MAX_M = 64
 SPLITK_MAX_CTAS = 148   # clusters x CTAs at most: all on the GPU at once
 SPLITK_LONG_K = 4096    # K from which that kernel serves from SPLITK_LONG_K_MIN_M rows on, where the weight rows / 16 exceed the SMs (0: never)
 SPLITK_LONG_K_MIN_M = 9
+SPLITK_VERY_LONG_K = 8192   # K from which, under the same conditions, every number of rows goes there (Qwen3-4B's down product)
+SPLITK_VERY_LONG_K_MIN_M = 1
 SPLITK_MAX_CLUSTERS_OF_8 = 8   # clusters of 8 CTAs at most (16 of them, 2 048 weight rows, took 8.9 us where 16 clusters of 4 take 5.5: a
                                # cluster needs its SMs in one part of the GPU)
 SWAP_MIN_M = 17         # rows from which, up to SMALL_M_MAX, wide products go to the swapped tcgen05 kernel
@@ -306,9 +308,10 @@ def splitk_splits(M: int, N: int, K: int, dtype: torch.dtype) -> int:
     kernel does not apply (few rows, enough weight rows for every SM, other types)."""
     if not (TCGEN05_ENABLED and SPLITK and dtype == torch.bfloat16 and M <= SPLITK_MAX_M and K % 8 == 0 and N % 4 == 0):
         return 0
-    # From 9 rows on already where the streaming kernel is at its worst: more CTAs of 16 weight rows than SMs (they do not
+    # From 9 rows on already (from the first, where K is very long) where the streaming kernel is at its worst: more CTAs of 16 weight rows than SMs (they do not
     # all start at once), a long K, and two tiles of tokens per instruction; then only with 4 or 8 CTAs per cluster.
-    early = SPLITK_LONG_K > 0 and K >= SPLITK_LONG_K and -(-N // 16) > SPLITK_MAX_CTAS and M >= SPLITK_LONG_K_MIN_M
+    early = (SPLITK_LONG_K > 0 and K >= SPLITK_LONG_K and -(-N // 16) > SPLITK_MAX_CTAS
+             and M >= (SPLITK_VERY_LONG_K_MIN_M if 0 < SPLITK_VERY_LONG_K <= K else SPLITK_LONG_K_MIN_M))
     if M < SPLITK_MIN_M and not early:
         return 0
     tiles = -(-N // 128)

@@ -18,9 +18,11 @@ def _products(name):
 
 @pytest.mark.parametrize("name", list(SIZES))
 def test_up_to_eight_rows_stream_the_weights(name):
-    for N, K in _products(name).values():
+    """... but for the one product whose K is so long and whose weight rows are so awkward a number (2 560: 160 CTAs of
+    16 rows for 148 SMs) that clusters sharing K are faster at any number of rows: Qwen3-4B's down projection."""
+    for what, (N, K) in _products(name).items():
         for M in (1, 4, 8):
-            assert ops.splitk_splits(M, N, K, BF) == 0
+            assert ops.splitk_splits(M, N, K, BF) == (4 if (name, what) == ("4b", "down") else 0)
 
 
 def test_nine_to_sixteen_rows_share_k_only_where_the_streaming_kernel_is_at_its_worst():

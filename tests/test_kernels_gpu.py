@@ -222,7 +222,8 @@ def test_linear_picks_splitk():
     assert ops.splitk_splits(17, 4096, 1024, torch.bfloat16) == 4
     assert ops.splitk_splits(32, 2048, 6144, torch.bfloat16) == 4      # 16 clusters: of 4 CTAs, not of 8
     assert ops.splitk_splits(12, 2560, 9728, torch.bfloat16) == 4      # a long K and more CTAs of 16 rows than SMs: from 9 rows on
-    assert ops.splitk_splits(8, 2560, 9728, torch.bfloat16) == 0 and ops.splitk_splits(12, 4096, 1024, torch.bfloat16) == 0
+    assert ops.splitk_splits(8, 2560, 9728, torch.bfloat16) == 4 and ops.splitk_splits(8, 2560, 4096, torch.bfloat16) == 0
+    assert ops.splitk_splits(12, 4096, 1024, torch.bfloat16) == 0
     assert ops.splitk_splits(12, 6144, 4096, torch.bfloat16) == 0      # (only two CTAs a cluster would fit)
     assert ops.splitk_splits(32, 6144, 1024, torch.bfloat16) == 2
     assert ops.splitk_splits(8, 1024, 3072, torch.bfloat16) == 0
