@@ -23,8 +23,9 @@
 // they arrive during the kernels between the two attentions, and the next layer's attention finds them
 // on the chip.  The caller asks for that only when a layer's keys and values are a fraction of L2.
 //
-// Work items, parts, scratch, counters and clusters are those of the kernel without matrix
-// instructions (attention_decode.cu), whose entry point this one mirrors.
+// Work items, parts, scratch and counters are those of the flash kernel for few rows (attention_flash.cuh: 12 ints an
+// item; a part writes its accumulator, max and sum to scratch memory and the last CTA to finish combines them), or the
+// parts of a request form a thread-block cluster and meet in its first CTA's shared memory.
 #include "attention_flash.cuh"
 
 #define DM_MAX_WARPS 8            // warps of a CTA: 4 (two CTAs per SM) or 8 (one CTA per SM), a template parameter
@@ -33,7 +34,7 @@
 #define DM_GK 16                  // keys per group
 #define DM_MAX_STAGES 3           // groups in flight per warp at most (a template parameter chooses 2 or 3)
 #define DM_ROWS 16                // rows of an item at most
-#define DM_PART_ALIGN 16          // a request's parts are multiples of this many keys (as in attention_decode.cu)
+#define DM_PART_ALIGN 16          // a request's parts are multiples of this many keys (the host's plan cuts them so)
 
 #define DM_TILE_BYTES (DM_GK * DM_LD * 2)                       // keys or values of a group: 4352
 #define DM_WARP_BYTES_OF(stages) ((stages) * 2 * DM_TILE_BYTES)     // a warp's stages: 17408 or 26112
@@ -449,7 +450,7 @@ extern "C" int qe_decode_attention_mma_supported(int Hq, int Hkv, int D, int max
   return (D == DM_D && Hkv >= 1 && Hkv <= 65535 && Hq % Hkv == 0 && Hq / Hkv <= DM_ROWS && max_rows >= 1 && max_rows <= DM_ROWS) ? 1 : 0;
 }
 
-// Same arguments as qe_decode_attention's (attention_decode.cu): every item has at most max_rows rows, all of
+// q, pages, block tables, items, out and scratch as for the flash kernel; every item has at most max_rows rows, all of
 // whole tokens; parts are combined by the CTA that finishes last (counters), or inside clusters (`cluster`:
 // the number of parts of every request, 2, 4 or 8, when the items are exactly those parts in order).
 // prefetch_pages: null, or another layer's cache of the same shape whose keys and values for the same requests
