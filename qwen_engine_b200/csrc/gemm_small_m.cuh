@@ -1,5 +1,5 @@
-// Device functions of the product for a few rows (see gemm_small_m.cu): shared by the stand-alone
-// kernel and by the persistent kernel that runs a decode step's operations as a program.
+// Device functions of the product for a few rows (see gemm_small_m.cu), as a header so that the kernels of that
+// file (a CTA per 16 weight rows, clusters that share K, the fused epilogues) are built from the same pieces.
 #pragma once
 #include "common.cuh"
 
@@ -65,7 +65,7 @@ struct GsmChunk { uint4 a0, b0, a1, b1; };
 
 // The first two chunks of the weights of CTA `vb` (16 rows from 16 vb on), for the calling warp's
 // slice of K.  They depend on nothing a kernel writes, so a caller issues them before it waits for
-// whatever produces the token operand (the previous kernel, or a grid barrier).
+// whatever produces the token operand (the previous kernel).
 template <int ROWS = 16>
 __device__ __forceinline__ void gsm_prefetch(const __nv_bfloat16* __restrict__ w, int N, int K, int k_per_warp, int vb,
                                              GsmChunk& c0, GsmChunk& c1, int k_off = 0, int k_len = 1 << 30) {

@@ -1,5 +1,5 @@
 // The fused per-head norm + rotary encoding + cache write for head size 128 in bfloat16 as a device
-// function (see elementwise.cu): shared by the stand-alone kernel and the decode program kernel.
+// function (see elementwise.cu), as a header so that another kernel can do the same for its own rows.
 #pragma once
 #include "common.cuh"
 
